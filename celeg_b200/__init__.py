@@ -1,0 +1,2 @@
+"""celeg_b200: a single-GPU inference engine for NVIDIA B200 (sm_100a)."""
+__version__ = "0.1.0"

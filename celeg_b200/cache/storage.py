@@ -1,0 +1,38 @@
+"""Device memory behind the cache manager: page storage per group, the state-slot slab."""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+import torch
+
+from .manager import PagedNeed, StateLayout
+
+
+class CacheStorage:
+    """Keys and values of group g: ``k[g]``, ``v[g]`` of shape
+    [layers of the group, pages, kv_heads, page_tokens, head_dim] in the path's element type,
+    so one (layer, page, head) tile is a contiguous [page_tokens, head_dim] box.
+    Fixed-size state: ``state`` [slots, slot_elements] float32."""
+
+    def __init__(self, groups: Sequence[Tuple[PagedNeed, int]], group_pages: Sequence[int], page_tokens: int,
+                 state_layout: StateLayout, slots: int, dtype: torch.dtype, device: torch.device):
+        self.page_tokens = page_tokens
+        self.k: List[torch.Tensor] = []
+        self.v: List[torch.Tensor] = []
+        for (need, layers), pages in zip(groups, group_pages):
+            shape = (layers, max(pages, 1), need.kv_heads, page_tokens, need.head_dim)
+            # zeros, not empty: a page that was never written must not hold NaN bit patterns,
+            # because masked keys are still multiplied by a zero weight in some kernels
+            self.k.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+        self.slot_elements = max(state_layout.slot_elements, 4)
+        self.state = torch.zeros((max(slots, 1), self.slot_elements), dtype=torch.float32, device=device)
+
+    def clear_slot(self, slot: int) -> None:
+        self.state[slot].zero_()
+
+    def bytes(self) -> int:
+        total = self.state.numel() * 4
+        for tensor in (*self.k, *self.v):
+            total += tensor.numel() * tensor.element_size()
+        return total

@@ -1,0 +1,184 @@
+// Sampling from float32 logits, one block per row, with celeg's rules
+// (src/backend/cpu/sampler.cpp:26-101; CUDA twin packed_sample_topk_kernel,
+// src/backend/cuda/kernels/sampling.cu:400-461):
+//   * repetition penalty p > 1 on tokens the request has seen: l >= 0 ? l / p : l * p (also when greedy)
+//   * temperature <= 0 or top_k == 1: arg-max, the first maximum wins
+//   * else scores = l / temperature; the top_k best (score descending, then token ascending),
+//     softmax over them in float32, top_p keeps the shortest prefix whose mass reaches p,
+//     and one xorshift64* draw u = ((bits >> 11) + 0.5) / 2^53 walks that prefix.
+// Each request has its own generator state and seen-table (indexed by its state slot), so its
+// tokens do not depend on what else is in the batch. The sampled token is marked seen.
+#include "common.cuh"
+
+namespace celeg_b200 {
+
+constexpr int kMaxTopK = 128;      // celeg's kMaxTopK (include/celeg/model/runtime_types.hpp:37)
+
+struct Best {
+    float score;
+    int token;
+};
+
+__device__ __forceinline__ bool better(float sa, int ta, float sb, int tb) {
+    return sa > sb || (sa == sb && ta < tb);
+}
+
+__device__ __forceinline__ Best warp_best(Best b) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float s = __shfl_xor_sync(0xffffffffu, b.score, offset);
+        const int t = __shfl_xor_sync(0xffffffffu, b.token, offset);
+        if (t >= 0 && (b.token < 0 || better(s, t, b.score, b.token))) {
+            b.score = s;
+            b.token = t;
+        }
+    }
+    return b;
+}
+
+__device__ Best block_best(Best b, Best* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    b = warp_best(b);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = b;
+    __syncthreads();
+    if (warp == 0) {
+        Best t = lane < warps ? scratch[lane] : Best{0.0f, -1};
+        t = warp_best(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__device__ __forceinline__ float penalised(const float* logits, const uint8_t* seen, int token, float penalty) {
+    float v = logits[token];
+    if (seen && penalty > 1.0f && seen[token]) v = v >= 0.0f ? v / penalty : v * penalty;
+    return v;
+}
+
+__global__ void sample_kernel(const float* __restrict__ logits, long long ld, int vocab,
+                              const int* __restrict__ row_slot, uint8_t* __restrict__ seen_base,
+                              unsigned long long* __restrict__ rng, const float* __restrict__ temperature,
+                              const int* __restrict__ top_k, const float* __restrict__ top_p,
+                              const float* __restrict__ penalty, int* __restrict__ out) {
+    __shared__ Best scratch[33];
+    __shared__ float cand_score[kMaxTopK];
+    __shared__ int cand_token[kMaxTopK];
+    const int row = blockIdx.x;
+    const float* l = logits + (size_t)row * ld;
+    const int slot = row_slot ? row_slot[row] : row;
+    uint8_t* seen = seen_base ? seen_base + (size_t)slot * vocab : nullptr;
+    const float temp = temperature ? temperature[row] : 0.0f;
+    const float pen = penalty ? penalty[row] : 1.0f;
+    int k = top_k ? top_k[row] : 1;
+    const bool greedy = temp <= 0.0f || k == 1;
+    k = greedy ? 1 : min(min(k, kMaxTopK), vocab);
+    const float inv_unused = 0.0f;
+    (void)inv_unused;
+
+    float prev_score = INFINITY;
+    int prev_token = -1;
+    for (int pick = 0; pick < k; ++pick) {
+        Best mine{0.0f, -1};
+        for (int token = threadIdx.x; token < vocab; token += blockDim.x) {
+            float v = penalised(l, seen, token, pen);
+            if (!greedy) v = v / temp;
+            // only candidates that come after the previous pick in (score desc, token asc) order
+            if (pick > 0 && !better(prev_score, prev_token, v, token)) continue;
+            if (mine.token < 0 || better(v, token, mine.score, mine.token)) {
+                mine.score = v;
+                mine.token = token;
+            }
+        }
+        const Best best = block_best(mine, scratch);
+        if (threadIdx.x == 0) {
+            cand_score[pick] = best.score;
+            cand_token[pick] = best.token;
+        }
+        prev_score = best.score;
+        prev_token = best.token;
+        if (best.token < 0) {            // fewer distinct candidates than k (NaNs): stop here
+            k = pick;
+            break;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    int chosen;
+    if (greedy || k <= 1) {
+        chosen = k >= 1 ? cand_token[0] : 0;
+    } else {
+        const float maximum = cand_score[0];
+        float total = 0.0f;
+        for (int i = 0; i < k; ++i) {
+            cand_score[i] = expf(cand_score[i] - maximum);
+            total += cand_score[i];
+        }
+        for (int i = 0; i < k; ++i) cand_score[i] /= total;
+        int active = k;
+        const float p = top_p ? top_p[row] : 1.0f;
+        if (p < 1.0f) {
+            float cumulative = 0.0f;
+            active = 0;
+            do {
+                cumulative += cand_score[active++];
+            } while (active < k && cumulative < p);
+            total = 0.0f;
+            for (int i = 0; i < active; ++i) total += cand_score[i];
+        } else {
+            total = 1.0f;
+        }
+        unsigned long long state = rng[slot];
+        state ^= state >> 12;
+        state ^= state << 25;
+        state ^= state >> 27;
+        rng[slot] = state;
+        const unsigned long long bits = state * 2685821657736338717ULL;
+        const float unit = (float)(((double)(bits >> 11) + 0.5) * (1.0 / 9007199254740992.0));
+        float target = unit * total;
+        chosen = cand_token[active - 1];
+        for (int i = 0; i < active; ++i) {
+            target -= cand_score[i];
+            if (target <= 0.0f) {
+                chosen = cand_token[i];
+                break;
+            }
+        }
+    }
+    out[row] = chosen;
+    if (seen) seen[chosen] = 1;
+}
+
+__global__ void mark_seen_kernel(uint8_t* __restrict__ seen_base, int vocab, const int* __restrict__ tokens,
+                                 const int* __restrict__ token_slot, int count) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const int token = tokens[i];
+    if (token >= 0 && token < vocab) seen_base[(size_t)token_slot[i] * vocab + token] = 1;
+}
+
+}  // namespace celeg_b200
+
+using namespace celeg_b200;
+
+CELEG_API int celeg_sample(const float* logits, long long ld, int vocab, int rows, const int* row_slot,
+                           uint8_t* seen, unsigned long long* rng, const float* temperature, const int* top_k,
+                           const float* top_p, const float* penalty, int* out, cudaStream_t stream) {
+    CELEG_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "sample: invalid sizes rows=%d vocab=%d ld=%lld", rows,
+                  vocab, ld);
+    CELEG_REQUIRE(rng != nullptr || temperature == nullptr, "sample: temperature sampling needs generator states");
+    if (rows == 0) return 0;
+    const int threads = vocab >= 16384 ? 1024 : 256;
+    sample_kernel<<<rows, threads, 0, stream>>>(logits, ld, vocab, row_slot, seen, rng, temperature, top_k, top_p,
+                                                penalty, out);
+    return check_launch("sample");
+}
+
+CELEG_API int celeg_mark_seen(uint8_t* seen, int vocab, const int* tokens, const int* token_slot, int count,
+                              cudaStream_t stream) {
+    CELEG_REQUIRE(count >= 0 && vocab > 0, "mark_seen: invalid sizes count=%d vocab=%d", count, vocab);
+    if (count == 0) return 0;
+    mark_seen_kernel<<<(count + 255) / 256, 256, 0, stream>>>(seen, vocab, tokens, token_slot, count);
+    return check_launch("mark_seen");
+}

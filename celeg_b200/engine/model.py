@@ -1,0 +1,141 @@
+"""A model built from a description: parts looked up in the registries, weights handed to
+them by name, caches bound per position of the run order."""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional, Tuple
+
+import torch
+
+from .. import kernels
+from ..cache.manager import PagedNeed, StateLayout, StateNeed
+from ..cache.storage import CacheStorage
+from ..config.spec import LayerSpec, ModelSpec, PartSpec
+from ..parts import PagedBinding, Runtime, StateBinding, StepContext, part_factory
+
+
+def _weights_of(part: PartSpec, tensors: Mapping[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    return {role: tensors[ref.name] for role, ref in part.tensors.items()}
+
+
+def build_part(category: str, part: Optional[PartSpec], tensors: Mapping[str, torch.Tensor], rt: Runtime):
+    if part is None:
+        return None
+    factory = part_factory(category, part.kind)
+    if category == "norm":
+        return factory(part.params, _weights_of(part, tensors), rt)
+    if category == "position":
+        return factory(part.params, rt)
+    children = {name: build_part("position" if name == "position" else name, child, tensors, rt)
+                for name, child in part.parts.items()}
+    return factory(part.params, _weights_of(part, tensors), children, rt)
+
+
+class Layer:
+    def __init__(self, spec: LayerSpec, tensors: Mapping[str, torch.Tensor], rt: Runtime):
+        self.name = spec.name
+        self.parts = {
+            "mixer_norm": build_part("norm", spec.mixer_norm, tensors, rt),
+            "mixer": build_part("mixer", spec.mixer, tensors, rt),
+            "feed_forward_norm": build_part("norm", spec.feed_forward_norm, tensors, rt),
+            "feed_forward": build_part("feed_forward", spec.feed_forward, tensors, rt),
+        }
+        self.mixer = self.parts["mixer"]
+        self.block = part_factory("arrangement", spec.arrangement)(self.parts, rt)
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], rt: Runtime):
+        spec.validate()
+        self.spec = spec
+        self.rt = rt
+        self.vocab_size = spec.vocab_size
+        self.hidden_size = spec.hidden_size
+        self.layers = [Layer(layer, tensors, rt) for layer in spec.layers]
+        self.order = list(spec.order)
+        self.embedding = rt.matrix(tensors[spec.embedding.name])
+        self.head = self.embedding if spec.lm_head is None else rt.matrix(tensors[spec.lm_head.name])
+        self.final_norm = build_part("norm", spec.final_norm, tensors, rt)
+        self.residual = rt.scratch("model.residual", spec.hidden_size, torch.float32)
+        self.final_normed = rt.scratch("model.final_normed", spec.hidden_size)
+        self.bindings: List[object] = [None] * len(self.order)
+        self._rebind = len({entry.layer for entry in self.order}) != len(self.order)
+        self._plan_caches()
+
+    # ------------------------------------------------------------------ caches
+    def _plan_caches(self) -> None:
+        """Group the mixers' needs: one paged group per distinct need, one slot layout."""
+        self.group_keys: List[tuple] = []
+        self.group_needs: List[PagedNeed] = []
+        self.group_members: List[List[int]] = []        # run-order positions that OWN a layer of the group
+        self.state_layout = StateLayout()
+        self.position_group: Dict[int, Tuple[int, int]] = {}   # position -> (group, layer index in group)
+        for position, entry in enumerate(self.order):
+            mixer = self.layers[entry.layer].mixer
+            need = mixer.cache_need()
+            if entry.cache_of is not None:
+                source_need = self.layers[self.order[entry.cache_of].layer].mixer.cache_need()
+                if type(need) is not type(source_need) or need != source_need:
+                    raise ValueError(f"run order position {position} reads the cache of position "
+                                     f"{entry.cache_of}, whose need {source_need} differs from its own {need}")
+                continue
+            if need is None:
+                continue
+            if isinstance(need, PagedNeed):
+                key = need.group_key()
+                if key not in self.group_keys:
+                    self.group_keys.append(key)
+                    self.group_needs.append(need)
+                    self.group_members.append([])
+                group = self.group_keys.index(key)
+                self.position_group[position] = (group, len(self.group_members[group]))
+                self.group_members[group].append(position)
+            elif isinstance(need, StateNeed):
+                self.state_layout.add(position, need.elements)
+            else:
+                raise TypeError(f"mixer of layer {entry.layer} asks for an unknown cache need {need!r}")
+
+    def attach(self, storage: CacheStorage) -> None:
+        """Give every position of the run order the place its cache lives in."""
+        for position, entry in enumerate(self.order):
+            mixer = self.layers[entry.layer].mixer
+            need = mixer.cache_need()
+            if need is None:
+                continue
+            source = position if entry.cache_of is None else entry.cache_of
+            owner = entry.cache_of is None
+            if isinstance(need, PagedNeed):
+                group, index = self.position_group[source]
+                self.bindings[position] = PagedBinding(group=group, k=storage.k[group][index],
+                                                       v=storage.v[group][index],
+                                                       page_tokens=storage.page_tokens, owner=owner)
+            else:
+                offset = self.state_layout.offsets[source]
+                self.bindings[position] = StateBinding(state=storage.state[:, offset:],
+                                                       slot_stride=storage.state.stride(0), owner=owner)
+        if not self._rebind:
+            for position, entry in enumerate(self.order):
+                if self.bindings[position] is not None:
+                    self.layers[entry.layer].mixer.bind_cache(self.bindings[position])
+
+    # ----------------------------------------------------------------- forward
+    def forward(self, step: StepContext, logit_rows: torch.Tensor, n_logits: int, logits: torch.Tensor) -> None:
+        """Run the step's tokens through every position of the run order and write the logits
+        of the wanted rows into ``logits[:n_logits]`` (float32)."""
+        rt = self.rt
+        kernels.embedding(self.embedding, step.token_ids[:step.tokens], self.residual,
+                          self.spec.embedding_multiplier)
+        pending = None
+        for position, entry in enumerate(self.order):
+            layer = self.layers[entry.layer]
+            if self._rebind and self.bindings[position] is not None:
+                layer.mixer.bind_cache(self.bindings[position])
+            pending = layer.block.run(self.residual, pending, step)
+        if n_logits == 0:
+            return
+        self.final_norm.add_norm(self.residual, pending, self.final_normed, n_logits, rows=logit_rows)
+        if rt.act_dtype == torch.float32:
+            kernels.gemm_f32(self.final_normed, self.head, logits, n_logits)
+        else:
+            rt.linear(self.final_normed, self.head, logits, n_logits)
+        if self.spec.logits_multiplier != 1.0:
+            logits[:n_logits].mul_(self.spec.logits_multiplier)

@@ -1,0 +1,258 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the
+cache that earlier steps left, returning the logits at the wanted places.
+
+A batch may hold portions of prompts beside single decoded tokens, cut anywhere. celeg runs
+two passes per engine step, a ragged prefill and a packed decode
+(src/backend/cuda/packed/execution.cu:141-224, 234-384; never both in one pass:
+src/backend/cuda/runtime/engine_control.cpp:4-23); both already treat a token as a row with its
+own position and page table, and here they are one pass.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, NO_PAGE, OutOfPages
+from ..cache.storage import CacheStorage
+from ..parts import Runtime, StepContext
+from .model import Model
+
+
+class StepInputError(ValueError):
+    """The batch is malformed; the message names the request."""
+
+
+class DeviceCheckError(RuntimeError):
+    """A kernel met an index the host should have made impossible."""
+
+
+@dataclass
+class StepEntry:
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()          # places among ``tokens`` whose logits are wanted
+
+
+def _align4(n: int) -> int:
+    return (n + 3) // 4 * 4
+
+
+class StepFunction:
+    def __init__(self, model: Model, manager: CacheManager, storage: CacheStorage, rt: Runtime,
+                 max_tokens: int, max_spans: int, max_context: int, use_graphs: bool = False):
+        self.model = model
+        self.manager = manager
+        self.storage = storage
+        self.rt = rt
+        self.max_tokens = max_tokens
+        self.max_spans = max_spans
+        self.max_context = max_context
+        self.page_tokens = manager.page_tokens
+        self.max_pages = (max_context + self.page_tokens - 1) // self.page_tokens
+        self.groups = len(manager.groups)
+        capacity = (3 * _align4(max_tokens) + _align4(max_spans + 1) + _align4(max_spans) + _align4(max_tokens)
+                    + self.groups * _align4(max_spans * self.max_pages))
+        # a ring of pinned staging buffers: a buffer is refilled only after the copy that read it
+        # last has finished on the device
+        self._ring = [torch.empty(capacity, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._ring_events: List[Optional[torch.cuda.Event]] = [None] * len(self._ring)
+        self._ring_next = 0
+        self._host = self._ring[0]
+        self._host_np = self._host.numpy()
+        self._dev = torch.zeros(capacity, dtype=torch.int32, device=rt.device)
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=rt.device)
+        self._decode_logits = torch.empty((max_spans, model.vocab_size), dtype=torch.float32, device=rt.device)
+        self._wide_logits: Optional[torch.Tensor] = None
+        self.use_graphs = use_graphs
+        self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self.steps_run = 0
+        self.kernel_steps_graphed = 0
+
+    # ------------------------------------------------------------------ requests
+    def begin(self, request_id: Hashable):
+        return self.manager.open(request_id)
+
+    def end(self, request_id: Hashable) -> None:
+        self.manager.close(request_id)
+
+    def position_of(self, request_id: Hashable) -> int:
+        return self.manager.get(request_id).tokens
+
+    # ---------------------------------------------------------------------- step
+    def run(self, entries: Sequence[StepEntry], auto_begin: bool = False) -> torch.Tensor:
+        """Returns float32 logits [wanted, vocab] in the order of the entries and of ``want``.
+        The tensor is a view of a buffer that the next call overwrites."""
+        vocab = self.model.vocab_size
+        if not entries:
+            return self._decode_logits[:0]
+        if len(entries) > self.max_spans:
+            raise StepInputError(f"{len(entries)} requests in one step, the limit is {self.max_spans}")
+        seen_ids = set()
+        total = 0
+        wanted = 0
+        caches = []
+        for entry in entries:
+            if entry.request_id in seen_ids:
+                raise StepInputError(f"request {entry.request_id!r} appears twice in one step")
+            seen_ids.add(entry.request_id)
+            count = len(entry.tokens)
+            if count == 0:
+                raise StepInputError(f"request {entry.request_id!r} brings no tokens")
+            for token in entry.tokens:
+                if not 0 <= int(token) < vocab:
+                    raise StepInputError(f"request {entry.request_id!r}: token id {token} is outside the "
+                                         f"vocabulary of {vocab}")
+            for place in entry.want:
+                if not 0 <= int(place) < count:
+                    raise StepInputError(f"request {entry.request_id!r}: wanted place {place} is outside its "
+                                         f"{count} tokens")
+            try:
+                cache = self.manager.get(entry.request_id)
+            except KeyError:
+                if not auto_begin:
+                    raise StepInputError(f"request {entry.request_id!r} was not begun") from None
+                cache = self.manager.open(entry.request_id)
+            if cache.tokens + count > self.max_context:
+                raise StepInputError(f"request {entry.request_id!r} would reach {cache.tokens + count} positions, "
+                                     f"the context limit is {self.max_context}")
+            caches.append(cache)
+            total += count
+            wanted += len(entry.want)
+        if total > self.max_tokens:
+            raise StepInputError(f"{total} tokens in one step, the limit is {self.max_tokens}")
+
+        # pages for the whole batch, all or nothing
+        need = [0] * self.groups
+        for entry, cache in zip(entries, caches):
+            for g, pages in enumerate(self.manager.pages_needed(cache, cache.tokens + len(entry.tokens))):
+                need[g] += pages
+        for g, group in enumerate(self.manager.groups):
+            if need[g] > group.pool.free_pages:
+                raise OutOfPages(f"the step needs {need[g]} more page(s) of group {group.key}, "
+                                 f"{group.pool.free_pages} free")
+        for entry, cache in zip(entries, caches):
+            self.manager.reserve(cache, cache.tokens + len(entry.tokens))
+
+        spans = len(entries)
+        all_decode = all(len(entry.tokens) == 1 for entry in entries)
+        max_ctx = max(cache.tokens + len(entry.tokens) for entry, cache in zip(entries, caches))
+        if all_decode and self.use_graphs:
+            stride = self.max_pages                         # fixed, so the captured addresses hold
+        else:
+            stride = (max_ctx + self.page_tokens - 1) // self.page_tokens
+        slot = self._ring_next
+        self._ring_next = (slot + 1) % len(self._ring)
+        if self._ring_events[slot] is not None:
+            self._ring_events[slot].synchronize()
+        self._host = self._ring[slot]
+        self._host_np = self._host.numpy()
+        step, logit_rows, n_words = self._stage(entries, caches, total, spans, wanted, stride, max_ctx)
+        self._dev[:n_words].copy_(self._host[:n_words], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._ring_events[slot] = event
+
+        if wanted <= self.max_spans:
+            logits = self._decode_logits
+        else:
+            if self._wide_logits is None or self._wide_logits.shape[0] < wanted:
+                self._wide_logits = torch.empty((wanted, vocab), dtype=torch.float32, device=self.rt.device)
+            logits = self._wide_logits
+
+        graph_key = (spans, wanted) if (all_decode and self.use_graphs and wanted <= self.max_spans) else None
+        if graph_key is not None:
+            self._run_graphed(graph_key, step, logit_rows, wanted, logits)
+        else:
+            self.model.forward(step, logit_rows, wanted, logits)
+        for entry, cache in zip(entries, caches):
+            self.manager.advance(cache, cache.tokens + len(entry.tokens))
+        self.steps_run += 1
+        return logits[:wanted]
+
+    def _run_graphed(self, key, step, logit_rows, wanted, logits) -> None:
+        graph = self._graphs.get(key)
+        if graph is None:
+            # Warm up outside capture (library handles, lazy allocations), then capture. The
+            # warm-up advances the fixed-size state once and the replay below would advance it
+            # again, so the state from before the warm-up is put back in between (cache pages
+            # are written with the same values both times).
+            saved = self.storage.state.clone()
+            self.model.forward(step, logit_rows, wanted, logits)
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.model.forward(step, logit_rows, wanted, logits)
+            self.storage.state.copy_(saved)
+            self._graphs[key] = graph
+        graph.replay()
+        self.kernel_steps_graphed += 1
+
+    def _stage(self, entries, caches, total, spans, wanted, stride, max_ctx):
+        """Fill the pinned staging buffer; returns the StepContext, the logit-row tensor and the
+        number of int32 words to copy. The layout depends only on (T, R, F, stride), so steps of
+        the same shape use the same device addresses."""
+        host = self._host_np
+        offsets = {}
+        cursor = 0
+        for name, size in (("token_ids", total), ("positions", total), ("token_span", total),
+                           ("span_begin", spans + 1), ("span_slot", spans), ("logit_rows", max(wanted, 1))):
+            offsets[name] = cursor
+            cursor += _align4(size)
+        table_offsets = []
+        for _ in range(self.groups):
+            table_offsets.append(cursor)
+            cursor += _align4(spans * stride)
+        token_ids = host[offsets["token_ids"]:offsets["token_ids"] + total]
+        positions = host[offsets["positions"]:offsets["positions"] + total]
+        token_span = host[offsets["token_span"]:offsets["token_span"] + total]
+        span_begin = host[offsets["span_begin"]:offsets["span_begin"] + spans + 1]
+        span_slot = host[offsets["span_slot"]:offsets["span_slot"] + spans]
+        logit_rows_host = host[offsets["logit_rows"]:offsets["logit_rows"] + max(wanted, 1)]
+        tables = [host[o:o + spans * stride].reshape(spans, stride) for o in table_offsets]
+        row = 0
+        out = 0
+        lengths = []
+        for index, (entry, cache) in enumerate(zip(entries, caches)):
+            count = len(entry.tokens)
+            token_ids[row:row + count] = np.asarray(entry.tokens, dtype=np.int32)
+            positions[row:row + count] = np.arange(cache.tokens, cache.tokens + count, dtype=np.int32)
+            token_span[row:row + count] = index
+            span_begin[index] = row
+            span_slot[index] = cache.slot
+            for place in entry.want:
+                logit_rows_host[out] = row + int(place)
+                out += 1
+            for g in range(self.groups):
+                table = cache.tables[g]
+                used = min(len(table), stride)
+                tables[g][index, :used] = table[:used]
+                tables[g][index, used:] = NO_PAGE
+            lengths.append(count)
+            row += count
+        span_begin[spans] = row
+        dev = self._dev
+
+        def view(name, size):
+            return dev[offsets[name]:offsets[name] + size]
+
+        step = StepContext(
+            tokens=total, spans=spans,
+            token_ids=view("token_ids", total), positions=view("positions", total),
+            token_span=view("token_span", total), span_begin=view("span_begin", spans + 1),
+            span_slot=view("span_slot", spans),
+            block_tables=[dev[o:o + spans * stride].view(spans, stride) for o in table_offsets],
+            error_flag=self.error_flag, max_span=max(lengths), max_context=max_ctx,
+            host_span_lengths=lengths)
+        return step, view("logit_rows", max(wanted, 1)), cursor
+
+    # -------------------------------------------------------------------- checks
+    def raise_on_device_error(self) -> None:
+        """Synchronises and raises if any kernel flagged an impossible index."""
+        code = int(self.error_flag.item())
+        if code:
+            self.error_flag.zero_()
+            raise DeviceCheckError(f"a kernel reported error code {code} (1: cache write without a page, "
+                                   f"2: attention read without a page)")

@@ -1,0 +1,80 @@
+"""Trace replay: feed given token ids through the model step by step and write logits.
+
+It samples nothing and has no forward pass, cache or loader of its own: every step goes through
+the StepFunction that generation uses. celeg has no such tool; its closest pieces are
+``--dump-logits`` after prefill (src/app/cuda/main.cpp:554-558) and forced-token evaluation
+(src/backend/cpu/model.cpp:162-178).
+
+Input, one JSON object a line:
+    {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
+For a step in which something is wanted, ``<out>/<step>.f32`` holds the logits at the wanted
+places, little-endian float32 [wanted, vocab]. After every step a line ``done <step>`` is
+printed and flushed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from typing import IO, Optional
+
+PAGE_ROUNDING = 64      # --max-tokens counts every live request rounded up to a multiple of this
+
+
+def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[str], done: IO[str],
+           device: str = "cuda:0", page_tokens: Optional[int] = None, max_requests: int = 8,
+           max_batched_tokens: Optional[int] = None) -> int:
+    import torch
+
+    from .loading import DEFAULT_PAGE_TOKENS, load_model
+    from .step import StepEntry
+
+    os.makedirs(out_dir, exist_ok=True)
+    page_tokens = page_tokens or DEFAULT_PAGE_TOKENS
+    if PAGE_ROUNDING % page_tokens and page_tokens % PAGE_ROUNDING:
+        raise ValueError(f"page size {page_tokens} neither divides nor is a multiple of {PAGE_ROUNDING}")
+    loaded = load_model(model_dir, dtype=dtype, device=device, cache_tokens=max_tokens, page_tokens=page_tokens,
+                        max_requests=max_requests,
+                        max_batched_tokens=max_batched_tokens or max(max_tokens, PAGE_ROUNDING))
+    step_fn = loaded.step
+    for line in lines:
+        line = line.strip()
+        if not line:
+            continue
+        record = json.loads(line)
+        number = record["step"]
+        entries = [StepEntry(request_id=item["id"], tokens=item["tokens"], want=item.get("want", []))
+                   for item in record.get("entries", [])]
+        if entries:
+            logits = step_fn.run(entries, auto_begin=True)
+            if logits.shape[0] > 0:
+                host = logits.to("cpu", copy=True).contiguous().numpy().astype("<f4", copy=False)
+                with open(os.path.join(out_dir, f"{number}.f32"), "wb") as handle:
+                    handle.write(host.tobytes())
+            else:
+                torch.cuda.current_stream().synchronize()
+            step_fn.raise_on_device_error()
+        for request_id in record.get("end", []):
+            step_fn.end(request_id)
+        done.write(f"done {number}\n")
+        done.flush()
+    return 0
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
+    parser.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    parser.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
+    parser.add_argument("--max-tokens", type=int, required=True,
+                        help="most tokens live requests hold at any time, each rounded up to 64")
+    parser.add_argument("--device", default="cuda:0")
+    parser.add_argument("--page-tokens", type=int, default=None)
+    args = parser.parse_args(argv)
+    try:
+        return replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, sys.stdout,
+                      device=args.device, page_tokens=args.page_tokens)
+    except Exception as exc:  # one line for the user, non-zero exit
+        print(f"error: {type(exc).__name__}: {exc}", file=sys.stderr, flush=True)
+        return 1

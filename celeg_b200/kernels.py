@@ -1,0 +1,196 @@
+"""Python face of the CUDA kernel library: loads (building it first if needed) the shared
+object made from ``celeg_b200/csrc`` and wraps each entry point for torch tensors.
+
+There is no fallback: if the library cannot be built or loaded, :func:`library` raises
+:class:`KernelLibraryError`, and every wrapper raises it when a kernel reports an error.
+Kernels run on torch's current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+FLOAT32 = 0
+BFLOAT16 = 1
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+_LIB: Optional[ctypes.CDLL] = None
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return FLOAT32
+    if dtype == torch.bfloat16:
+        return BFLOAT16
+    raise KernelLibraryError(f"the kernels handle float32 and bfloat16, not {dtype}")
+
+
+_SIGNATURES = {
+    "celeg_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "celeg_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int,
+                          c_void_p],
+    "celeg_rmsnorm_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "celeg_short_conv": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                         c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_qk_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                 c_int, c_void_p, c_int, c_void_p],
+    "celeg_attention_generic": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int,
+                                c_void_p],
+    "celeg_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "celeg_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                     c_void_p, c_void_p, c_void_p],
+    "celeg_mark_seen": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p],
+}
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library; built at the first call in a fresh checkout."""
+    global _LIB
+    if _LIB is None:
+        try:
+            path = _build.ensure_built()
+            lib = ctypes.CDLL(path)
+        except (_build.BuildError, OSError) as exc:
+            raise KernelLibraryError(f"the CUDA kernel library of celeg_b200 is not available: {exc}") from exc
+        lib.celeg_last_error.restype = ctypes.c_char_p
+        lib.celeg_last_error.argtypes = []
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _LIB = lib
+    return _LIB
+
+
+def library_path() -> str:
+    library()
+    return _LIB._name  # type: ignore[union-attr]
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        raise KernelLibraryError(library().celeg_last_error().decode("utf-8", "replace"))
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    if tensor is None:
+        return None
+    return tensor.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(tensor: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if tensor.dtype != dtype or not tensor.is_cuda or not tensor.is_contiguous():
+        raise KernelLibraryError(f"{name} must be a contiguous CUDA tensor of {dtype}, got {tensor.dtype} "
+                                 f"on {tensor.device}, contiguous={tensor.is_contiguous()}")
+
+
+# ------------------------------------------------------------------------------ wrappers
+def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, multiplier: float = 1.0) -> None:
+    rows = tokens.shape[0]
+    _need(tokens, torch.int32, "tokens")
+    _need(out, torch.float32, "out")
+    vocab, hidden = table.shape
+    assert out.shape[0] >= rows and out.shape[1] == hidden
+    _check(library().celeg_embedding(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(out), rows, hidden,
+                                     vocab, multiplier, _stream()))
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                eps: float, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
+                write_residual: bool = True) -> None:
+    """out[i] = rmsnorm(residual[r] + delta[r]) * weight; residual[r] updated when not gathering."""
+    _need(residual, torch.float32, "residual")
+    _need(weight, torch.float32, "weight")
+    width = residual.shape[-1]
+    if n_rows is None:
+        n_rows = rows.shape[0] if rows is not None else residual.shape[0]
+    if delta is not None:
+        assert delta.dtype == out.dtype and delta.shape[-1] == width
+    _check(library().celeg_add_rmsnorm(_ptr(residual), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n_rows,
+                                       width, eps, int(write_residual and rows is None), dtype_code(out.dtype),
+                                       _stream()))
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, n_rows: int) -> None:
+    _need(weight, torch.float32, "weight")
+    _check(library().celeg_rmsnorm_rows(_ptr(x), _ptr(weight), _ptr(out), n_rows, x.shape[-1], eps,
+                                        dtype_code(x.dtype), _stream()))
+
+
+def short_conv(proj: torch.Tensor, kernel: torch.Tensor, state: torch.Tensor, slot_stride: int, out: torch.Tensor,
+               token_span: torch.Tensor, span_begin: torch.Tensor, span_slot: torch.Tensor, tokens: int, spans: int,
+               hidden: int, taps: int) -> None:
+    """``state`` points at this layer's state inside slot 0; ``slot_stride`` floats separate slots."""
+    _need(kernel, torch.float32, "conv kernel")
+    assert state.dtype == torch.float32
+    _check(library().celeg_short_conv(_ptr(proj), _ptr(kernel), _ptr(state), slot_stride, _ptr(out),
+                                      _ptr(token_span), _ptr(span_begin), _ptr(span_slot), tokens, spans, hidden,
+                                      taps, dtype_code(proj.dtype), _stream()))
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                       inv_freq: Optional[torch.Tensor], positions: torch.Tensor, token_span: torch.Tensor,
+                       block_table: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                       tokens: int, q_heads: int, kv_heads: int, head_dim: int, rotary_dim: int, page_tokens: int,
+                       eps: float, store_kv: bool, error_flag: torch.Tensor) -> None:
+    """k_cache / v_cache: one layer's pages, [pages, kv_heads, page_tokens, head_dim]."""
+    page_stride = k_cache.stride(0) if k_cache is not None else 0
+    _check(library().celeg_qk_norm_rope_store(
+        _ptr(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), _ptr(positions), _ptr(token_span),
+        _ptr(block_table), block_table.stride(0), _ptr(k_cache), _ptr(v_cache), page_stride, tokens, q_heads,
+        kv_heads, head_dim, rotary_dim, page_tokens, eps, int(store_kv), _ptr(error_flag), dtype_code(qkv.dtype),
+        _stream()))
+
+
+def attention_generic(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_cache: torch.Tensor,
+                      v_cache: torch.Tensor, positions: torch.Tensor, token_span: torch.Tensor,
+                      block_table: torch.Tensor, tokens: int, q_heads: int, kv_heads: int, head_dim: int,
+                      page_tokens: int, window: Optional[int], scale: float, error_flag: torch.Tensor) -> None:
+    _check(library().celeg_attention_generic(
+        _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
+        _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim,
+        page_tokens, int(window or 0), scale, _ptr(error_flag), dtype_code(q.dtype), _stream()))
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, tokens: int, inner: int) -> None:
+    _check(library().celeg_swiglu(_ptr(gate_up), _ptr(out), tokens, inner, dtype_code(gate_up.dtype), _stream()))
+
+
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, accumulate: bool = False) -> None:
+    """y[:m] (+)= x[:m] @ w.T with float32 operands and FFMA accumulation."""
+    _need(w, torch.float32, "w")
+    assert x.dtype == torch.float32 and y.dtype == torch.float32
+    n, k = w.shape
+    assert x.stride(-1) == 1 and y.stride(-1) == 1 and x.shape[-1] == k and y.shape[-1] == n
+    _check(library().celeg_gemm_f32(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), y.stride(0),
+                                    int(accumulate), _stream()))
+
+
+def sample(logits: torch.Tensor, rows: int, row_slot: Optional[torch.Tensor], seen: Optional[torch.Tensor],
+           rng: Optional[torch.Tensor], temperature: Optional[torch.Tensor], top_k: Optional[torch.Tensor],
+           top_p: Optional[torch.Tensor], penalty: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    _need(logits, torch.float32, "logits")
+    _need(out, torch.int32, "out")
+    _check(library().celeg_sample(_ptr(logits), logits.stride(0), logits.shape[1], rows, _ptr(row_slot), _ptr(seen),
+                                  _ptr(rng), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(penalty), _ptr(out),
+                                  _stream()))
+
+
+def mark_seen(seen: torch.Tensor, tokens: torch.Tensor, token_slot: torch.Tensor, count: int) -> None:
+    _check(library().celeg_mark_seen(_ptr(seen), seen.shape[1], _ptr(tokens), _ptr(token_slot), count, _stream()))

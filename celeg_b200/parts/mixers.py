@@ -1,0 +1,158 @@
+"""Mixer parts. Interface of a mixer:
+
+    Mixer(params, weights, parts, rt)       parts: built nested parts (e.g. {"position": ...})
+    cache_need() -> PagedNeed | StateNeed | None
+    bind_cache(binding)                     PagedBinding or StateBinding from the cache storage
+    forward(x, out, step)                   x: normed activations [T, hidden]; writes the
+                                            mixer's output (to be added to the residual) to out
+
+A mixer does not know which model or layer it is in; everything it needs about the step is
+in the StepContext, everything about its cache in the binding.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Mapping, Optional
+
+import torch
+
+from .. import kernels
+from ..cache.manager import PagedNeed, StateNeed
+from .registry import register_part
+from .runtime import Runtime, StepContext
+
+
+@dataclass
+class PagedBinding:
+    """Where a paged mixer's keys and values live: one layer of a group's storage,
+    [pages, kv_heads, page_tokens, head_dim] each; ``owner`` False = read only (the cache
+    belongs to an earlier layer of the run order)."""
+    group: int
+    k: torch.Tensor
+    v: torch.Tensor
+    page_tokens: int
+    owner: bool = True
+
+
+@dataclass
+class StateBinding:
+    """Where a fixed-state mixer's state lives: ``state`` is a view [slots, elements] of the
+    slot slab; ``slot_stride`` floats separate one slot from the next."""
+    state: torch.Tensor
+    slot_stride: int
+    owner: bool = True
+
+
+@register_part("mixer", "attention")
+class AttentionMixer:
+    """Causal grouped-query attention over the paged cache with optional per-head q/k RMSNorm,
+    a position encoding, an optional window, and softmax scale given by the configuration.
+    Order of operations as in celeg (src/backend/cpu/operators/attention_token.cpp:151-204;
+    src/backend/cuda/packed/operators.cu:66-99, 101-246, 494-529): fused q|k|v projection,
+    norm, rotation, cache write, attention, output projection."""
+
+    def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["num_heads"])
+        self.kv_heads = int(params["num_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.window = params.get("window")
+        self.scale = float(params.get("softmax_scale", self.head_dim ** -0.5))
+        self.eps = float(params.get("qk_norm_eps", 1e-6))
+        self.reads_only = bool(params.get("reads_cache_only", False))
+        if self.heads % self.kv_heads:
+            raise ValueError(f"{self.heads} query heads are not a multiple of {self.kv_heads} kv heads")
+        self.position = parts.get("position")
+        q_width = self.heads * self.head_dim
+        kv_width = self.kv_heads * self.head_dim
+        if self.reads_only:
+            self.stored_kv_heads = 0
+            fused = weights["q_proj"]
+        else:
+            self.stored_kv_heads = self.kv_heads
+            fused = torch.cat([weights["q_proj"], weights["k_proj"], weights["v_proj"]], dim=0)
+        self.qkv_width = q_width + 2 * self.stored_kv_heads * self.head_dim
+        self.w_qkv = rt.matrix(fused)
+        self.w_out = rt.matrix(weights["out_proj"])
+        self.q_norm = rt.vector(weights["q_norm"]) if "q_norm" in weights else None
+        self.k_norm = rt.vector(weights["k_norm"]) if "k_norm" in weights else None
+        self.binding: Optional[PagedBinding] = None
+        self.qkv = rt.scratch("attention.qkv", self.qkv_width)
+        self.attended = rt.scratch("attention.out", q_width)
+        assert kv_width >= 0
+
+    def cache_need(self):
+        return PagedNeed(kv_heads=self.kv_heads, head_dim=self.head_dim, window=self.window)
+
+    def bind_cache(self, binding: PagedBinding) -> None:
+        if binding.owner and self.reads_only:
+            raise ValueError("an attention mixer without k/v projections cannot own a cache")
+        self.binding = binding
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        rt, b, t = self.rt, self.binding, step.tokens
+        rt.linear(x, self.w_qkv, self.qkv, t)
+        table = step.block_tables[b.group]
+        fused = self.position.fused() if self.position is not None else {"inv_freq": None, "rotary_dim": 0}
+        store = b.owner and not self.reads_only
+        if fused is not None:
+            kernels.qk_norm_rope_store(self.qkv, self.q_norm, self.k_norm, fused["inv_freq"], step.positions,
+                                       step.token_span, table, b.k, b.v, t, self.heads, self.stored_kv_heads,
+                                       self.head_dim, fused["rotary_dim"], b.page_tokens, self.eps, store,
+                                       step.error_flag)
+        else:
+            # unfused: normalise in place, let the position part rewrite q and k, then store
+            kernels.qk_norm_rope_store(self.qkv, self.q_norm, self.k_norm, None, step.positions, step.token_span,
+                                       table, b.k, b.v, t, self.heads, self.stored_kv_heads, self.head_dim, 0,
+                                       b.page_tokens, self.eps, False, step.error_flag)
+            rows = self.qkv[:t]
+            q_width = self.heads * self.head_dim
+            kv_width = self.stored_kv_heads * self.head_dim
+            q_view = rows[:, :q_width].unflatten(1, (self.heads, self.head_dim))
+            k_view = rows[:, q_width:q_width + kv_width].unflatten(1, (self.stored_kv_heads, self.head_dim))
+            self.position.apply(q_view, k_view, step.positions[:t], t)
+            if store:
+                kernels.qk_norm_rope_store(self.qkv, None, None, None, step.positions, step.token_span, table,
+                                           b.k, b.v, t, self.heads, self.stored_kv_heads, self.head_dim, 0,
+                                           b.page_tokens, self.eps, True, step.error_flag)
+        self.attend(step, table)
+        rt.linear(self.attended, self.w_out, out, t)
+
+    def attend(self, step: StepContext, table: torch.Tensor) -> None:
+        b = self.binding
+        kernels.attention_generic(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
+                                  step.token_span, table, step.tokens, self.heads, self.kv_heads, self.head_dim,
+                                  b.page_tokens, self.window, self.scale, step.error_flag)
+
+
+@register_part("mixer", "short_conv")
+class ShortConvMixer:
+    """Gated short convolution: [B|C|X] = in_proj(x); conv over B*X with a depthwise causal
+    kernel of ``taps`` taps; out_proj(C * conv). Per-request state: the last taps-1 values of
+    B*X per channel, float32 (celeg src/backend/cpu/kernels/convolution.cpp:7-28;
+    src/backend/cuda/packed/operators.cu:31-62)."""
+
+    def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.taps = int(params["taps"])
+        self.w_in = rt.matrix(weights["in_proj"])
+        self.w_out = rt.matrix(weights["out_proj"])
+        self.kernel = rt.vector(weights["conv"].reshape(self.hidden, self.taps))
+        self.binding: Optional[StateBinding] = None
+        self.projected = rt.scratch("short_conv.proj", 3 * self.hidden)
+        self.gated = rt.scratch("short_conv.out", self.hidden)
+
+    def cache_need(self):
+        return StateNeed(elements=(self.taps - 1) * self.hidden)
+
+    def bind_cache(self, binding: StateBinding) -> None:
+        self.binding = binding
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        rt, t = self.rt, step.tokens
+        rt.linear(x, self.w_in, self.projected, t)
+        kernels.short_conv(self.projected, self.kernel, self.binding.state, self.binding.slot_stride, self.gated,
+                           step.token_span, step.span_begin, step.span_slot, t, step.spans, self.hidden, self.taps)
+        rt.linear(self.gated, self.w_out, out, t)

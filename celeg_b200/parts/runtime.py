@@ -1,0 +1,77 @@
+"""What parts share at run time: the device, the precision of the path, scratch buffers, the
+matrix product, and the description of the step being run."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from .. import kernels
+
+
+class Runtime:
+    """One per model instance. ``act_dtype`` is float32 (everything in true 32-bit) or bfloat16
+    (the serving path: bfloat16 matrices and activations; residual stream, norms, softmax,
+    rotation angles and conv state in float32)."""
+
+    def __init__(self, device: torch.device, act_dtype: torch.dtype, max_tokens: int):
+        if act_dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"dtype must be float32 or bfloat16, got {act_dtype}")
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise kernels.KernelLibraryError("celeg_b200 runs on a CUDA device only; there is no CPU path")
+        self.act_dtype = act_dtype
+        self.max_tokens = max_tokens
+        self._scratch: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
+        kernels.library()                       # fail now, not at the first step, if it is missing
+
+    def scratch(self, tag: str, columns: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """A persistent [max_tokens, columns] buffer. Parts that ask with the same tag, width and
+        type share it, which is safe because layers run one after another."""
+        dtype = dtype or self.act_dtype
+        key = (tag, columns, dtype)
+        if key not in self._scratch:
+            self._scratch[key] = torch.empty((self.max_tokens, columns), dtype=dtype, device=self.device)
+        return self._scratch[key]
+
+    def matrix(self, weight: torch.Tensor) -> torch.Tensor:
+        """A projection weight on the device in the path's matrix precision."""
+        return weight.to(device=self.device, dtype=self.act_dtype).contiguous()
+
+    def vector(self, weight: torch.Tensor) -> torch.Tensor:
+        """A small weight (norm scale, conv kernel) on the device in float32 (exact widening)."""
+        return weight.to(device=self.device, dtype=torch.float32).contiguous()
+
+    def linear(self, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int) -> None:
+        """out[:rows] = x[:rows] @ weight.T.  float32: this package's FFMA kernel. bfloat16: the
+        library product (cuBLAS through torch), as celeg uses cuBLAS for these
+        (src/backend/cuda/runtime/gemm_dispatcher.cpp:49-64), float32 accumulation."""
+        if rows == 0:
+            return
+        if self.act_dtype == torch.float32:
+            kernels.gemm_f32(x, weight, out, rows)
+        elif out.dtype == torch.float32:
+            torch.mm(x[:rows], weight.t(), out_dtype=torch.float32, out=out[:rows])
+        else:
+            torch.mm(x[:rows], weight.t(), out=out[:rows])
+
+
+@dataclass
+class StepContext:
+    """Device-side description of one step, the same for every layer. All index tensors are
+    int32 and persistent (their addresses do not change between steps)."""
+    tokens: int                       # T: tokens in this step
+    spans: int                        # R: requests in this step
+    token_ids: torch.Tensor           # [T]
+    positions: torch.Tensor           # [T] absolute position of each token in its request
+    token_span: torch.Tensor          # [T] index of the span a token belongs to
+    span_begin: torch.Tensor          # [R+1] first token of each span (prefix sums)
+    span_slot: torch.Tensor           # [R] state slot of each span's request
+    block_tables: List[torch.Tensor]  # per paged group: [R, max_pages] page ids, -1 = none
+    error_flag: torch.Tensor          # [1] set by a kernel that met an impossible index
+    max_span: int = 1                 # longest span (host knowledge, for kernel choice)
+    max_context: int = 0              # largest position + 1 in the step
+    host_positions: Optional[list] = None
+    host_span_lengths: Optional[list] = None
+    extras: Dict[str, object] = field(default_factory=dict)

@@ -1,0 +1,304 @@
+"""Each CUDA kernel alone against a plain float64 reference of the same operation, at sizes
+other than the engine's tiny models (odd widths, head sizes in steps of 16, ragged spans)."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def dev(x, dtype=None):
+    t = torch.as_tensor(x)
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda().contiguous()
+
+
+def rounded(x: np.ndarray, dtype) -> np.ndarray:
+    """The values a tensor of ``dtype`` holds, as float64."""
+    return torch.as_tensor(x).to(dtype).to(torch.float64).numpy()
+
+
+def close(got: torch.Tensor, want: np.ndarray, dtype, scale=1.0):
+    got = got.detach().to(torch.float64).cpu().numpy()
+    tol = 2e-5 if dtype == torch.float32 else 1.2e-2
+    err = np.abs(got - want)
+    bound = tol * scale + tol * np.abs(want)
+    assert (err <= bound).all(), f"max err {err.max():.3e} at {np.unravel_index(err.argmax(), err.shape)}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(40, 33), (1536, 100)])
+def test_embedding(dtype, hidden, vocab):
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(0)
+    table = rounded(rng.normal(size=(vocab, hidden)), dtype)
+    tokens = rng.integers(0, vocab, size=19)
+    out = torch.zeros((19, hidden), dtype=torch.float32, device="cuda")
+    kernels.embedding(dev(table, dtype), dev(tokens, torch.int32), out, 1.0)
+    close(out, table[tokens], torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,eps", [(40, 1e-5), (1000, 1e-6), (2048, 1e-5), (4100, 1e-3)])
+def test_add_rmsnorm(dtype, width, eps):
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(1)
+    rows = 7
+    residual = rng.normal(size=(rows, width)).astype(np.float32).astype(np.float64)
+    delta = rounded(rng.normal(size=(rows, width)), dtype)
+    weight = (1 + 0.05 * rng.normal(size=width)).astype(np.float32).astype(np.float64)
+    res_dev = dev(residual, torch.float32)
+    out = torch.zeros((rows, width), dtype=dtype, device="cuda")
+    kernels.add_rmsnorm(res_dev, dev(delta, dtype), dev(weight, torch.float32), out, eps)
+    summed = (residual + delta).astype(np.float32).astype(np.float64)
+    close(res_dev, summed, torch.float32)
+    close(out, plain_lfm2.rmsnorm(summed, weight, eps), dtype)
+    # gathered, without delta, residual untouched
+    pick = np.array([5, 0, 5], dtype=np.int32)
+    out2 = torch.zeros((3, width), dtype=dtype, device="cuda")
+    before = res_dev.clone()
+    kernels.add_rmsnorm(res_dev, None, dev(weight, torch.float32), out2, eps, rows=dev(pick))
+    assert torch.equal(before, res_dev)
+    close(out2, plain_lfm2.rmsnorm(summed[pick], weight, eps), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,inner", [(5, 136), (33, 1000)])
+def test_swiglu(dtype, tokens, inner):
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(2)
+    gate_up = rounded(rng.normal(size=(tokens, 2 * inner)) * 2, dtype)
+    out = torch.zeros((tokens, inner), dtype=dtype, device="cuda")
+    kernels.swiglu(dev(gate_up, dtype), out, tokens, inner)
+    g, u = gate_up[:, :inner], gate_up[:, inner:]
+    close(out, g / (1 + np.exp(-g)) * u, dtype)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 70, 33), (5, 64, 64), (67, 130, 100), (130, 257, 513)])
+def test_gemm_f32(m, n, k):
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(3)
+    x = rng.normal(size=(m, k)).astype(np.float32)
+    w = rng.normal(size=(n, k)).astype(np.float32)
+    y = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    kernels.gemm_f32(dev(x), dev(w), y, m)
+    close(y, x.astype(np.float64) @ w.astype(np.float64).T, torch.float32, scale=math.sqrt(k))
+    # a row's result does not depend on the other rows of the batch
+    y1 = torch.zeros((1, n), dtype=torch.float32, device="cuda")
+    kernels.gemm_f32(dev(x[m - 1:m]), dev(w), y1, 1)
+    assert torch.equal(y1[0], y[m - 1])
+
+
+def conv_reference(proj, kernel, history, spans):
+    """Per span: bx history (taps-1 values before the span) ++ span; returns out and new history."""
+    hidden = kernel.shape[0]
+    taps = kernel.shape[1]
+    out = np.zeros((proj.shape[0], hidden))
+    new_history = []
+    for (begin, end), hist in zip(spans, history):
+        b, c, x = (proj[begin:end, i * hidden:(i + 1) * hidden] for i in range(3))
+        bx = np.concatenate([hist, b * x], axis=0)
+        for j in range(end - begin):
+            conv = sum(kernel[:, tap] * bx[j + tap] for tap in range(taps))
+            out[begin + j] = c[j] * conv
+        new_history.append(bx[bx.shape[0] - (taps - 1):] if taps > 1 else bx[:0])
+    return out, new_history
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,taps", [(40, 3), (300, 4), (64, 2), (48, 1), (96, 7)])
+def test_short_conv_spans_and_state(dtype, hidden, taps):
+    """Spans shorter and longer than the kernel, two steps in a row so the carried state is used,
+    slots out of order."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(4)
+    keep = taps - 1
+    slots = 5
+    slot_stride = keep * hidden + 12
+    state = torch.zeros((slots, slot_stride), dtype=torch.float32, device="cuda")
+    offset = 4
+    kernel = rng.normal(size=(hidden, taps)).astype(np.float32).astype(np.float64)
+    span_slots = [3, 0, 4, 1]
+    history = [np.zeros((keep, hidden)) for _ in span_slots]
+    for lengths in ([1, 2, 9, 3], [2, 1, 1, 12], [5, 1, 2, 1]):
+        tokens = sum(lengths)
+        begins = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+        spans = [(int(begins[i]), int(begins[i + 1])) for i in range(len(lengths))]
+        token_span = np.concatenate([np.full(n, i) for i, n in enumerate(lengths)]).astype(np.int32)
+        proj = rounded(rng.normal(size=(tokens, 3 * hidden)), dtype)
+        out = torch.zeros((tokens, hidden), dtype=dtype, device="cuda")
+        kernels.short_conv(dev(proj, dtype), dev(kernel, torch.float32), state[:, offset:], slot_stride, out,
+                           dev(token_span), dev(begins), dev(np.array(span_slots, dtype=np.int32)), tokens,
+                           len(lengths), hidden, taps)
+        want, history = conv_reference(proj, kernel, history, spans)
+        close(out, want, dtype, scale=3.0)
+        for slot, hist in zip(span_slots, history):
+            got = state[slot, offset:offset + keep * hidden].reshape(keep, hidden)
+            close(got, hist.astype(np.float32).astype(np.float64), torch.float32)
+    assert float(state[2].abs().sum()) == 0.0          # a slot no span named stays untouched
+
+
+def paged_setup(rng, dtype, lengths, kv_heads, head_dim, page_tokens, pages):
+    """Random K/V for several requests scattered over shuffled pages."""
+    order = rng.permutation(pages)
+    k_cache = torch.zeros((pages, kv_heads, page_tokens, head_dim), dtype=dtype, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    max_pages = max((n + page_tokens - 1) // page_tokens for n in lengths)
+    table = np.full((len(lengths), max_pages), -1, dtype=np.int32)
+    ks, vs, used = [], [], 0
+    for r, n in enumerate(lengths):
+        k = rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype)
+        v = rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype)
+        for p in range((n + page_tokens - 1) // page_tokens):
+            page = int(order[used])
+            used += 1
+            table[r, p] = page
+            lo, hi = p * page_tokens, min(n, (p + 1) * page_tokens)
+            k_cache[page, :, :hi - lo] = dev(k[lo:hi], dtype).transpose(0, 1)
+            v_cache[page, :, :hi - lo] = dev(v[lo:hi], dtype).transpose(0, 1)
+        ks.append(k)
+        vs.append(v)
+    return k_cache, v_cache, table, ks, vs
+
+
+def attention_reference(q, k, v, pos, scale, window):
+    """q [heads, d] at absolute position pos over keys k,v [n, kv_heads, d]."""
+    heads, kv_heads = q.shape[0], k.shape[1]
+    out = np.zeros_like(q)
+    first = max(0, pos - window + 1) if window else 0
+    for h in range(heads):
+        kh = h // (heads // kv_heads)
+        s = (k[first:pos + 1, kh] @ q[h]) * scale
+        w = np.exp(s - s.max())
+        w /= w.sum()
+        out[h] = w @ v[first:pos + 1, kh]
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (5, 5, 48, 16, None), (8, 2, 64, 64, None),
+    (6, 3, 80, 16, 37), (2, 1, 128, 32, None), (4, 4, 24, 16, 5),
+])
+def test_attention_generic(dtype, heads, kv_heads, head_dim, page_tokens, window):
+    """Mixed batch: a long portion, a decoded token far into a sequence, a two-token portion, a
+    first token; with one key made to stand out so a missed far key shows."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(5)
+    lengths = [150, 301, 40, 1]                  # keys each request has AFTER this step
+    span_len = [70, 1, 2, 1]                     # tokens it brings to this step
+    k_cache, v_cache, table, ks, vs = paged_setup(rng, dtype, lengths, kv_heads, head_dim, page_tokens, 64)
+    # request 1: key 3 is far from the query at position 300 and dominates its scores
+    tokens = sum(span_len)
+    q = rounded(rng.normal(size=(tokens, heads, head_dim)), dtype)
+    positions, token_span = [], []
+    for r, (n, m) in enumerate(zip(lengths, span_len)):
+        positions += list(range(n - m, n))
+        token_span += [r] * m
+    far_row = span_len[0]
+    if not window:
+        q[far_row] = rounded(ks[1][3, 0][None, :].repeat(heads, 0) * 3.0, dtype)
+    scale = head_dim ** -0.5
+    out = torch.zeros((tokens, heads * head_dim), dtype=dtype, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kernels.attention_generic(dev(q.reshape(tokens, -1), dtype), heads * head_dim, out, k_cache, v_cache,
+                              dev(np.array(positions, dtype=np.int32)), dev(np.array(token_span, dtype=np.int32)),
+                              dev(table), tokens, heads, kv_heads, head_dim, page_tokens, window, scale, flag)
+    assert int(flag.item()) == 0
+    want = np.stack([attention_reference(q[t], ks[token_span[t]], vs[token_span[t]], positions[t], scale, window)
+                     for t in range(tokens)]).reshape(tokens, -1)
+    close(out, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,theta,eps", [
+    (4, 2, 16, 16, 1e4, 1e-5), (3, 1, 32, 8, 1e6, 1e-6), (5, 5, 48, 16, 5e4, 3e-6), (2, 2, 80, 32, 1e6, 1e-5),
+])
+def test_qk_norm_rope_store(dtype, heads, kv_heads, head_dim, page_tokens, theta, eps):
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(6)
+    start = [37, 0, 255]
+    count = [9, 5, 1]
+    tokens = sum(count)
+    pages = 40
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = rounded(rng.normal(size=(tokens, width)), dtype)
+    q_w = (1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32).astype(np.float64)
+    k_w = (1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32).astype(np.float64)
+    positions, token_span = [], []
+    for r, (s, n) in enumerate(zip(start, count)):
+        positions += list(range(s, s + n))
+        token_span += [r] * n
+    positions = np.array(positions)
+    max_pages = max((s + n + page_tokens - 1) // page_tokens for s, n in zip(start, count))
+    order = rng.permutation(pages)
+    table = np.full((3, max_pages), -1, dtype=np.int32)
+    used = 0
+    for r, (s, n) in enumerate(zip(start, count)):
+        for p in range((s + n + page_tokens - 1) // page_tokens):
+            table[r, p] = order[used]
+            used += 1
+    k_cache = torch.zeros((pages, kv_heads, page_tokens, head_dim), dtype=dtype, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    half = head_dim // 2
+    inv_freq = (theta ** (-2.0 * np.arange(half) / head_dim)).astype(np.float32)
+    qkv_dev = dev(qkv, dtype)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kernels.qk_norm_rope_store(qkv_dev, dev(q_w, torch.float32), dev(k_w, torch.float32), dev(inv_freq),
+                               dev(positions.astype(np.int32)), dev(np.array(token_span, dtype=np.int32)),
+                               dev(table), k_cache, v_cache, tokens, heads, kv_heads, head_dim, head_dim,
+                               page_tokens, eps, True, flag)
+    assert int(flag.item()) == 0
+    q = qkv[:, :heads * head_dim].reshape(tokens, heads, head_dim)
+    k = qkv[:, heads * head_dim:(heads + kv_heads) * head_dim].reshape(tokens, kv_heads, head_dim)
+    v = qkv[:, (heads + kv_heads) * head_dim:].reshape(tokens, kv_heads, head_dim)
+    q_want = plain_lfm2.rope_split_half(plain_lfm2.rmsnorm(q, q_w, eps), positions, theta)
+    k_want = plain_lfm2.rope_split_half(plain_lfm2.rmsnorm(k, k_w, eps), positions, theta)
+    close(qkv_dev[:, :heads * head_dim], q_want.reshape(tokens, -1), dtype, scale=3.0)
+    for t in range(tokens):
+        page = table[token_span[t], positions[t] // page_tokens]
+        inside = positions[t] % page_tokens
+        close(k_cache[page, :, inside], k_want[t], dtype, scale=3.0)
+        close(v_cache[page, :, inside], v[t], dtype)
+
+
+def test_sampling_greedy_and_seeded():
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(7)
+    vocab, rows = 1000, 6
+    logits = rng.normal(size=(rows, vocab)).astype(np.float32) * 3
+    logits[0, 17] = logits[0, 400] = logits[0].max() + 1        # a tie: the first maximum wins
+    seen = np.zeros((8, vocab), dtype=np.uint8)
+    seen[:, rng.integers(0, vocab, size=200)] = 1
+    slots = np.array([5, 2, 7, 0, 1, 3], dtype=np.int32)
+    temperature = np.array([0.0, 0.8, 1.0, 0.7, 1.3, 0.1], dtype=np.float32)
+    top_k = np.array([50, 50, 128, 1, 5, 40], dtype=np.int32)
+    top_p = np.array([1.0, 1.0, 0.9, 1.0, 0.5, 1.0], dtype=np.float32)
+    penalty = np.array([1.0, 1.05, 1.3, 1.0, 1.0, 2.0], dtype=np.float32)
+    rng_state = np.array([1, 7, 99, 12345, 2**40 + 3, 5, 6, 8], dtype=np.uint64)
+    seen_dev, rng_dev = dev(seen), dev(rng_state.view(np.int64)).view(torch.int64)
+    out = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    states = rng_state.copy()
+    seen_host = seen.copy()
+    for _ in range(4):                                          # several draws advance the generators
+        kernels.sample(dev(logits), rows, dev(slots), seen_dev, rng_dev, dev(temperature), dev(top_k), dev(top_p),
+                       dev(penalty), out)
+        got = out.cpu().numpy()
+        for r in range(rows):
+            slot = slots[r]
+            token, new_state = plain_lfm2.sample_token(logits[r], seen_host[slot], int(states[slot]),
+                                                       float(temperature[r]), int(top_k[r]), float(top_p[r]),
+                                                       float(penalty[r]))
+            assert got[r] == token, f"row {r}: kernel {got[r]}, plain {token}"
+            states[slot] = new_state
+            seen_host[slot, token] = 1
+    assert np.array_equal(seen_dev.cpu().numpy(), seen_host)
