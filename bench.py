@@ -1,0 +1,353 @@
+#!/usr/bin/env python3
+"""Benchmark of celeg_b200 on one B200: decode tokens per second at LFM2-1.2B sizes with random
+weights (batch 8, 512-token prompts, context 4,096), plus prefill of 2,048 tokens and decode at
+batch 1 and 64. Prints ONE JSON line.
+
+  python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+A "step" is one decode step of the whole batch. ``value`` is timed on the device (CUDA events
+around K steps of step function + sampling kernel, synthetic token ids); ``e2e`` is the same
+through ``Engine.step()``: host token ids in through pinned memory, sampled ids back to the host
+every step. Weights (2.3 GB) are larger than L2, so no flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: LFM2-1.2B sizes
+LFM2_1P2B = {
+    "model_type": "lfm2", "vocab_size": 65536, "hidden_size": 2048, "num_hidden_layers": 16,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
+    "conv_L_cache": 3, "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_word_embeddings": True,
+    "max_position_embeddings": 4096,
+    "layer_types": ["full_attention" if i in (2, 5, 8, 10, 12, 14) else "conv" for i in range(16)],
+    "bos_token_id": 1, "eos_token_id": 7, "pad_token_id": 0,
+}
+FULL_LAYERS = 16
+CONTEXT = 4096
+PROMPT_TOKENS = 512
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path, "r", encoding="utf-8") as handle:
+            data = json.load(handle)
+        return {k: float(data[k]) for k in FALLBACK_PEAKS}, "measured"
+    except (OSError, KeyError, ValueError):
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+def model_config(layers: int) -> dict:
+    raw = dict(LFM2_1P2B)
+    if layers != FULL_LAYERS:
+        raw["num_hidden_layers"] = layers
+        raw["layer_types"] = LFM2_1P2B["layer_types"][:layers]
+    return raw
+
+
+def model_folder(raw: dict, seed: int = 0) -> str:
+    """Random-weights model folder, reused if a finished one of the same configuration exists."""
+    from celeg_b200 import write_random_model
+    tag = hashlib.sha256((json.dumps(raw, sort_keys=True) + str(seed)).encode()).hexdigest()[:16]
+    folder = os.path.join(tempfile.gettempdir(), f"celeg_b200_bench_{os.getuid()}_{tag}")
+    if not os.path.isfile(os.path.join(folder, "complete")):
+        started = time.time()
+        write_random_model(folder, raw, seed)
+        with open(os.path.join(folder, "complete"), "w") as handle:
+            handle.write("ok")
+        print(f"[bench] wrote random weights to {folder} in {time.time() - started:.0f} s", file=sys.stderr)
+    return folder
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.rows = []
+        self.process = None
+        self.index = index
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.rows.append([part.strip() for part in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.process is not None:
+            time.sleep(0.25)
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+
+    def summary(self) -> dict:
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            try:
+                clocks.append(float(row[0]))
+                maxima.append(float(row[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, value in zip(names, row[3:7]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+                "sm_max_mhz": max(maxima) if maxima else None, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def decode_bytes(raw: dict, batch: int, context_tokens: int) -> float:
+    """Bytes one decode step has to read: every weight once (the tied table once, as the head),
+    the KV of the live requests, their conv state, and the embedding rows."""
+    h, inner, v = raw["hidden_size"], raw["intermediate_size"], raw["vocab_size"]
+    q = raw["num_attention_heads"] * raw["head_dim"]
+    kv = raw["num_key_value_heads"] * raw["head_dim"]
+    taps = raw["conv_L_cache"]
+    conv = raw["layer_types"].count("conv")
+    attn = raw["layer_types"].count("full_attention")
+    per_conv = 3 * h * h + h * h + h * taps
+    per_attn = (q + 2 * kv) * h + h * q + 2 * raw["head_dim"]
+    per_ffn = 3 * h * inner + 2 * h
+    weights = 2.0 * (conv * (per_conv + per_ffn) + attn * (per_attn + per_ffn) + v * h + h)
+    kv_bytes = 2.0 * 2 * kv * attn * context_tokens * batch
+    state = 4.0 * (taps - 1) * h * conv * batch
+    return weights + kv_bytes + state + 2.0 * batch * h
+
+
+def prefill_flops(raw: dict, tokens: int) -> float:
+    h, inner, v = raw["hidden_size"], raw["intermediate_size"], raw["vocab_size"]
+    q = raw["num_attention_heads"] * raw["head_dim"]
+    kv = raw["num_key_value_heads"] * raw["head_dim"]
+    conv = raw["layer_types"].count("conv")
+    attn = raw["layer_types"].count("full_attention")
+    linear = conv * (3 * h * h + h * h) + attn * ((q + 2 * kv) * h + h * q) + (conv + attn) * 3 * h * inner
+    causal = attn * 2 * q * tokens * (tokens + 1) / 2            # QK^T and PV, lower triangle
+    return 2.0 * tokens * linear + 2.0 * causal + 2.0 * v * h    # head on the last row only
+
+
+def time_decode(loaded, sampler, batch: int, steps: int, warmup: int, prompt_tokens: int, seed: int):
+    """Prefill ``batch`` requests, then time ``steps`` decode steps on the device."""
+    import torch
+    from celeg_b200 import kernels
+    from celeg_b200.engine.step import StepEntry
+    from celeg_b200.sampling import GREEDY
+    step_fn = loaded.step
+    vocab = loaded.model.vocab_size
+    generator = torch.Generator().manual_seed(seed)
+    names = [f"b{batch}_{i}" for i in range(batch)]
+    chunk = step_fn.max_tokens
+    for name in names:
+        prompt = torch.randint(0, vocab, (prompt_tokens,), generator=generator).tolist()
+        for at in range(0, prompt_tokens, chunk):
+            step_fn.run([StepEntry(name, prompt[at:at + chunk], [])], auto_begin=True)
+    slots = [(loaded.manager.get(name).slot, GREEDY) for name in names]
+    feed = torch.randint(0, vocab, (warmup + steps, batch), generator=generator).tolist()
+
+    def one(i):
+        logits = step_fn.run([StepEntry(name, [feed[i][j]], [0]) for j, name in enumerate(names)])
+        kernels.sample(logits, batch, sampler._dev_i[:batch], None, None, None, None, None, None, sampler.out)
+
+    sampler._dev_i[:batch].copy_(torch.tensor([s for s, _ in slots], dtype=torch.int32))
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    launches_before = kernels.LAUNCHES
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    launches = kernels.LAUNCHES - launches_before
+    context = prompt_tokens + warmup + steps // 2
+    for name in names:
+        step_fn.end(name)
+    return ms, launches, context
+
+
+def time_prefill(loaded, tokens: int, repeats: int, seed: int):
+    import torch
+    from celeg_b200.engine.step import StepEntry
+    step_fn = loaded.step
+    vocab = loaded.model.vocab_size
+    generator = torch.Generator().manual_seed(seed)
+    best = None
+    for i in range(repeats + 2):
+        prompt = torch.randint(0, vocab, (tokens,), generator=generator).tolist()
+        entries = [StepEntry(f"prefill{i}", prompt, [tokens - 1])]
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        step_fn.run(entries, auto_begin=True)
+        stop.record()
+        torch.cuda.synchronize()
+        step_fn.end(f"prefill{i}")
+        if i >= 2:
+            ms = start.elapsed_time(stop)
+            best = ms if best is None else min(best, ms)
+    return best
+
+
+def time_e2e(engine, batch: int, steps: int, warmup: int, prompt_tokens: int, seed: int):
+    """The same decode through Engine.step(): pinned host inputs in, sampled ids out, every step."""
+    import torch
+    from celeg_b200 import RequestOptions, SamplingParams
+    vocab = engine.loaded.model.vocab_size
+    generator = torch.Generator().manual_seed(seed)
+    options = RequestOptions(max_new_tokens=warmup + steps + 8, eos_tokens=(),
+                             generation=SamplingParams(temperature=0.0, top_k=1, repetition_penalty=1.0))
+    ids = [engine.submit(torch.randint(0, vocab, (prompt_tokens,), generator=generator).tolist(), options)
+           for _ in range(batch)]
+    scheduler = engine.scheduler
+    while any(scheduler.status(i).value in ("queued", "prefill") for i in ids):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall = time.perf_counter()
+    start.record()
+    for _ in range(steps):
+        engine.step()
+    stop.record()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - wall) * 1e3 / steps
+    ms = max(start.elapsed_time(stop) / steps, wall_ms)
+    produced = sum(len(engine.poll(i).tokens) for i in ids)
+    for i in ids:
+        engine.cancel(i)
+    engine.step()
+    step_words = engine.loaded.step
+    table_words = batch * step_words.max_pages
+    h2d = 4 * (3 * ((batch + 3) // 4 * 4) + (batch + 1 + 3) // 4 * 4 + 2 * ((batch + 3) // 4 * 4) + table_words) \
+        + engine.sampler._host_i.numel() * 4 + engine.sampler._host_f.numel() * 4
+    d2h = engine.sampler._out_host.numel() * 4
+    return ms, h2d, d2h, produced
+
+
+def run_ours(args) -> dict:
+    import torch
+    from celeg_b200 import Engine, EngineOptions, kernels
+    from celeg_b200.sampling import Sampler
+    batch = 8
+    raw = model_config(args.layers)
+    folder = model_folder(raw)
+    peak, peak_source = peaks()
+    max_batch = 64
+    options = EngineOptions(max_active_requests=max_batch, max_batched_tokens=PREFILL_TOKENS,
+                            prefill_chunk_tokens=PREFILL_TOKENS, page_tokens=args.page_tokens,
+                            logical_kv_pages=max_batch * CONTEXT // args.page_tokens)
+    engine = Engine(folder, max_context=CONTEXT, dtype="bfloat16", device="cuda:0", options=options,
+                    use_cuda_graph=not args.no_cuda_graph)
+    loaded = engine.loaded
+    sampler = Sampler(raw["vocab_size"], max_batch, max_batch, engine.device)
+
+    with ClockSampler() as clocks:
+        ms, launches, context = time_decode(loaded, sampler, batch, args.steps, args.warmup, PROMPT_TOKENS, 1)
+    clock_summary = clocks.summary()
+    value = batch * 1e3 / ms
+    achieved = decode_bytes(raw, batch, context) / (ms * 1e-3) / 1e9
+
+    prefill_ms = time_prefill(loaded, PREFILL_TOKENS, 3, 2)
+    prefill_frac = prefill_flops(raw, PREFILL_TOKENS) / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12)
+
+    points = {}
+    for b, key in ((1, "decode_b1"), (64, "decode_b64")):
+        point_ms, _, _ = time_decode(loaded, sampler, b, max(8, args.steps // 2), args.warmup, PROMPT_TOKENS, 3 + b)
+        points[key] = round(b * 1e3 / point_ms, 1)
+
+    e2e_ms, h2d, d2h, _ = time_e2e(engine, batch, args.steps, args.warmup, PROMPT_TOKENS, 5)
+
+    return {
+        "metric": "decode tok/s at batch 8 (LFM2-1.2B sizes, random weights, 512-token prompts, context 4096)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights (seed 0), uniform-random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "LFM2-1.2B sizes", "global_batch": batch, "seq_len": CONTEXT, "prompt_tokens": PROMPT_TOKENS,
+            "parallelism": "single GPU", "vocab_size": raw["vocab_size"], "hidden_size": raw["hidden_size"],
+            "layers": raw["num_hidden_layers"], "layers_of_config": FULL_LAYERS,
+            "attention_layers": raw["layer_types"].count("full_attention"),
+            "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+            "head_dim": raw["head_dim"], "intermediate_size": raw["intermediate_size"],
+            "conv_L_cache": raw["conv_L_cache"], "page_tokens": args.page_tokens,
+            "cuda_graph": not args.no_cuda_graph, "l2": "inputs larger than L2 (2.3 GB of weights per step)",
+        },
+        "e2e": {"value": round(batch * 1e3 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS * 1e3 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3), "frac": round(prefill_frac, 4),
+                    "peak_tflops": peak["bf16_tflops"], "of": peak_source},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4), "of": peak_source,
+                     "context_tokens": context},
+        "points": points,
+        "clocks": clock_summary,
+        "kernel_library": kernels.library_path(),
+    }
+
+
+def run_reference(args) -> dict:
+    """The reference arm: celeg is a C++/CUDA project built with CMake (no Python package), so there
+    is nothing ``pip install /root/reference`` can install; see DESIGN.md."""
+    return {"impl": "reference",
+            "unavailable": "celsowm/celeg is a CMake C++/CUDA project without setup.py or pyproject.toml: "
+                           "'pip install --no-index ... /root/reference' answers 'not installable'"}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--warmup", type=int, default=16)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--layers", type=int, default=FULL_LAYERS,
+                        help="fewer layers of the same sizes, when memory or time needs it")
+    parser.add_argument("--page-tokens", type=int, default=16)
+    parser.add_argument("--no-cuda-graph", action="store_true")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -74,8 +74,6 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ld, in
     int k = top_k ? top_k[row] : 1;
     const bool greedy = temp <= 0.0f || k == 1;
     k = greedy ? 1 : min(min(k, kMaxTopK), vocab);
-    const float inv_unused = 0.0f;
-    (void)inv_unused;
 
     float prev_score = INFINITY;
     int prev_token = -1;
@@ -150,12 +148,14 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ld, in
     if (seen) seen[chosen] = 1;
 }
 
+// Marks the tokens of a step as seen by their requests: slot = span_slot[token_span[i]].
 __global__ void mark_seen_kernel(uint8_t* __restrict__ seen_base, int vocab, const int* __restrict__ tokens,
-                                 const int* __restrict__ token_slot, int count) {
+                                 const int* __restrict__ token_span, const int* __restrict__ span_slot,
+                                 int count) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
     const int token = tokens[i];
-    if (token >= 0 && token < vocab) seen_base[(size_t)token_slot[i] * vocab + token] = 1;
+    if (token >= 0 && token < vocab) seen_base[(size_t)span_slot[token_span[i]] * vocab + token] = 1;
 }
 
 }  // namespace celeg_b200
@@ -175,10 +175,10 @@ CELEG_API int celeg_sample(const float* logits, long long ld, int vocab, int row
     return check_launch("sample");
 }
 
-CELEG_API int celeg_mark_seen(uint8_t* seen, int vocab, const int* tokens, const int* token_slot, int count,
-                              cudaStream_t stream) {
+CELEG_API int celeg_mark_seen(uint8_t* seen, int vocab, const int* tokens, const int* token_span,
+                              const int* span_slot, int count, cudaStream_t stream) {
     CELEG_REQUIRE(count >= 0 && vocab > 0, "mark_seen: invalid sizes count=%d vocab=%d", count, vocab);
     if (count == 0) return 0;
-    mark_seen_kernel<<<(count + 255) / 256, 256, 0, stream>>>(seen, vocab, tokens, token_slot, count);
+    mark_seen_kernel<<<(count + 255) / 256, 256, 0, stream>>>(seen, vocab, tokens, token_span, span_slot, count);
     return check_launch("mark_seen");
 }

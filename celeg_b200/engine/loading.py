@@ -61,7 +61,7 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0", *, max_context
     finally:
         repository.close()
     context = min(max_context or spec.max_context, spec.max_context) if max_context else spec.max_context
-    rt = Runtime(device, dtype, max_batched_tokens)
+    rt = Runtime(device, dtype, max_batched_tokens, max_requests=max_requests, max_context=context)
     with torch.cuda.device(device):
         model = Model(spec, tensors, rt)
         del tensors

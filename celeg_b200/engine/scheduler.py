@@ -1,0 +1,412 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+finishes and frees. It is host logic over two collaborators, so it runs without a GPU in tests:
+
+* a :class:`~celeg_b200.cache.manager.CacheManager` (slots and pages), and
+* a *runner* with ``run(entries, sample_rows) -> list[int]``: runs one step over the entries and
+  returns one sampled token per entry that wants one, plus ``reset_request(slot, seed)`` and
+  ``save_generator(slot)`` / ``restore_generator(slot, state)`` for per-request sampling state.
+
+Policy, names and defaults follow celeg's CUDA engine
+(include/celeg/backend/cuda/concurrency.hpp:18-32; admission
+src/backend/cuda/runtime/request_lifecycle.cpp:103-198; prefill budget
+src/backend/cuda/runtime/prefill_scheduler.cpp:7-37; decode and page growth
+src/backend/cuda/runtime/decode_scheduler.cpp:10-99), with two differences: prompt portions and
+decoded tokens go into ONE step, and a pool that cannot serve any live request is resolved by
+preempting one request instead of stalling (see :meth:`Scheduler._break_deadlock`).
+"""
+from __future__ import annotations
+
+import enum
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence, Tuple
+
+from ..cache.manager import CacheManager, RequestCache
+from ..cache.pages import OutOfPages
+from ..sampling.params import SamplingParams
+from .step import StepEntry
+
+
+class RequestStatus(enum.Enum):
+    QUEUED = "queued"
+    PREFILL = "prefill"
+    DECODING = "decoding"
+    FINISHED = "finished"
+    CANCELLED = "cancelled"
+    FAILED = "failed"
+
+    @property
+    def terminal(self) -> bool:
+        return self in (RequestStatus.FINISHED, RequestStatus.CANCELLED, RequestStatus.FAILED)
+
+
+class SchedulerPolicy(enum.Enum):
+    GUARANTEED_NO_EVICT = "guaranteed-no-evict"   # reserve prompt + max_new_tokens at admission
+    MAX_UTILIZATION = "max-utilization"           # reserve prompt + one page, grow while decoding
+
+
+@dataclass
+class EngineOptions:
+    """celeg's ``ConcurrentEngineOptions`` (same names and defaults) for what this engine keeps."""
+    max_active_requests: int = 8
+    max_batched_tokens: int = 512
+    prefill_chunk_tokens: int = 256
+    page_tokens: int = 16
+    logical_kv_pages: int = 0                    # 0: ceil(max_context / page_tokens) * max_active_requests
+    scheduler_policy: SchedulerPolicy = SchedulerPolicy.GUARANTEED_NO_EVICT
+
+    def validate(self) -> None:
+        for name in ("max_active_requests", "max_batched_tokens", "prefill_chunk_tokens", "page_tokens"):
+            if getattr(self, name) <= 0:
+                raise ValueError(f"{name} must be positive, got {getattr(self, name)}")
+        if self.logical_kv_pages < 0:
+            raise ValueError("logical_kv_pages must not be negative")
+
+
+@dataclass
+class RequestOptions:
+    """celeg's ``ConcurrentRequestOptions`` (include/celeg/runtime/request_types.hpp:16-22).
+    ``eos_tokens=None`` takes the stop ids of the model's configuration."""
+    max_new_tokens: int = 128
+    eos_tokens: Optional[Sequence[int]] = None
+    priority: int = 0
+    generation: SamplingParams = field(default_factory=SamplingParams)
+
+
+@dataclass
+class Request:
+    id: int
+    prompt: List[int]
+    options: RequestOptions
+    eos_tokens: Tuple[int, ...]
+    status: RequestStatus = RequestStatus.QUEUED
+    generated: List[int] = field(default_factory=list)
+    output: Deque[int] = field(default_factory=deque)       # tokens not polled yet
+    prefill_offset: int = 0           # tokens of ``feed`` already in the cache
+    feed: List[int] = field(default_factory=list)           # what prefill has to run (prompt, or
+    #                                                         prompt + generated after a preemption)
+    cache: Optional[RequestCache] = None
+    cancel_requested: bool = False
+    error: str = ""
+    generator_state: Optional[int] = None                   # saved across a preemption
+    preemptions: int = 0
+    submitted_at: float = 0.0
+    first_token_at: Optional[float] = None
+    last_token_at: Optional[float] = None
+
+
+@dataclass
+class Metrics:
+    """celeg's ``ConcurrentMetrics`` counters that apply here
+    (include/celeg/runtime/concurrency/metrics.hpp:8-58)."""
+    submitted: int = 0
+    completed: int = 0
+    cancelled: int = 0
+    failed: int = 0
+    preempted: int = 0
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    max_step_tokens: int = 0
+    max_step_requests: int = 0
+    skipped_for_pages: int = 0
+    ttft_seconds_sum: float = 0.0
+    ttft_count: int = 0
+    itl_seconds_sum: float = 0.0
+    itl_count: int = 0
+
+
+@dataclass
+class PlannedEntry:
+    request: Request
+    tokens: List[int]
+    samples: bool                     # the step's last token of this entry yields a new token
+    is_decode: bool
+
+
+@dataclass
+class Plan:
+    entries: List[PlannedEntry] = field(default_factory=list)
+    skipped_for_pages: List[Request] = field(default_factory=list)
+
+
+@dataclass
+class PollResult:
+    status: RequestStatus
+    tokens: List[int]
+    finished: bool
+    error: str = ""
+
+
+class Scheduler:
+    def __init__(self, manager: CacheManager, runner, options: EngineOptions, max_context: int,
+                 vocab_size: int, default_eos: Sequence[int] = ()):
+        options.validate()
+        self.manager = manager
+        self.runner = runner
+        self.options = options
+        self.max_context = max_context
+        self.vocab_size = vocab_size
+        self.default_eos = tuple(default_eos)
+        self.requests: Dict[int, Request] = {}
+        self.queue: List[int] = []                  # ids of QUEUED requests
+        self.live: List[int] = []                   # ids of PREFILL / DECODING requests
+        self.metrics = Metrics()
+        self._next_id = 1
+        self._hold_admission = False      # set by a preemption: the freed pages go to the others first
+
+    # ------------------------------------------------------------------ public
+    def submit(self, prompt: Sequence[int], options: Optional[RequestOptions] = None) -> int:
+        """Checks of celeg's submit (src/backend/cuda/runtime/request_lifecycle.cpp:10-32) plus
+        the token range (src/backend/cpu/concurrent.cpp:358-362)."""
+        options = options or RequestOptions()
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise ValueError("the prompt is empty")
+        if len(prompt) > self.max_context:
+            raise ValueError(f"the prompt has {len(prompt)} tokens, the context holds {self.max_context}")
+        if options.max_new_tokens <= 0:
+            raise ValueError("max_new_tokens must be positive")
+        if len(prompt) + options.max_new_tokens > self.max_context:
+            raise ValueError(f"prompt ({len(prompt)}) + max_new_tokens ({options.max_new_tokens}) exceeds the "
+                             f"context of {self.max_context}")
+        for token in prompt:
+            if not 0 <= token < self.vocab_size:
+                raise ValueError(f"token id {token} is outside the vocabulary of {self.vocab_size}")
+        options.generation.validate()
+        eos = tuple(options.eos_tokens) if options.eos_tokens is not None else self.default_eos
+        request = Request(id=self._next_id, prompt=prompt, options=options, eos_tokens=eos,
+                          feed=list(prompt), submitted_at=time.monotonic())
+        self._next_id += 1
+        self.requests[request.id] = request
+        self.queue.append(request.id)
+        self.metrics.submitted += 1
+        return request.id
+
+    def cancel(self, request_id: int) -> bool:
+        request = self.requests.get(request_id)
+        if request is None or request.status.terminal:
+            return False
+        request.cancel_requested = True
+        return True
+
+    def status(self, request_id: int) -> RequestStatus:
+        return self._get(request_id).status
+
+    def poll(self, request_id: int, max_tokens: int = 0) -> PollResult:
+        """Pops tokens that were produced since the last poll; ``finished`` once the request is
+        terminal and nothing is left to pop (request_lifecycle.cpp:57-73)."""
+        request = self._get(request_id)
+        count = len(request.output) if max_tokens <= 0 else min(max_tokens, len(request.output))
+        tokens = [request.output.popleft() for _ in range(count)]
+        return PollResult(status=request.status, tokens=tokens,
+                          finished=request.status.terminal and not request.output, error=request.error)
+
+    def release(self, request_id: int) -> bool:
+        """Forget a terminal request (request_lifecycle.cpp:47-55)."""
+        request = self.requests.get(request_id)
+        if request is None or not request.status.terminal:
+            return False
+        del self.requests[request_id]
+        return True
+
+    def has_work(self) -> bool:
+        return bool(self.queue or self.live)
+
+    # -------------------------------------------------------------------- step
+    def step(self) -> bool:
+        """One engine step: admit, run one batch, accept tokens, admit again. Returns whether
+        anything advanced."""
+        self._honour_cancellations()
+        if not self._hold_admission:
+            self._admit()
+        plan = self.plan()
+        if not plan.entries:
+            self._hold_admission = False
+            if self.live and self._break_deadlock():
+                return True
+            return False
+        progressed = self._execute(plan)
+        self._hold_admission = False
+        self._honour_cancellations()
+        self._admit()
+        return progressed
+
+    # --------------------------------------------------------------- admission
+    def _priority_key(self, request_id: int):
+        request = self.requests[request_id]
+        return (-request.options.priority, request.id)          # priority desc, then id asc
+
+    def _reservation(self, request: Request) -> int:
+        total = len(request.prompt) + request.options.max_new_tokens
+        if self.options.scheduler_policy is SchedulerPolicy.GUARANTEED_NO_EVICT:
+            return total
+        return min(total, len(request.feed) + self.options.page_tokens)
+
+    def _admit(self) -> None:
+        while self.queue and len(self.live) < self.options.max_active_requests and self.manager.free_slots > 0:
+            request_id = min(self.queue, key=self._priority_key)
+            request = self.requests[request_id]
+            if request.cancel_requested:
+                self.queue.remove(request_id)
+                self._finish(request, RequestStatus.CANCELLED)
+                continue
+            cache = self.manager.open(request.id)
+            try:
+                self.manager.reserve(cache, self._reservation(request))
+            except OutOfPages:
+                self.manager.close(request.id)
+                break                                            # stays queued; stop admitting
+            self.queue.remove(request_id)
+            request.cache = cache
+            request.status = RequestStatus.PREFILL
+            request.prefill_offset = 0
+            seed = request.generator_state if request.generator_state is not None \
+                else request.options.generation.seed
+            self.runner.reset_request(cache.slot, seed)
+            self.live.append(request.id)
+
+    # ---------------------------------------------------------------- planning
+    def plan(self) -> Plan:
+        """Decoding requests first, one token each; what is left of ``max_batched_tokens`` goes to
+        prompt portions in priority order, each ``min(remaining, prefill_chunk_tokens, budget)``."""
+        plan = Plan()
+        ordered = sorted(self.live, key=self._priority_key)
+        decoding = [self.requests[i] for i in ordered if self.requests[i].status is RequestStatus.DECODING]
+        prefilling = [self.requests[i] for i in ordered if self.requests[i].status is RequestStatus.PREFILL]
+        budget = self.options.max_batched_tokens
+        free = [group.pool.free_pages for group in self.manager.groups]
+        for request in decoding:
+            if budget <= 0:
+                break
+            needed = self.manager.pages_needed(request.cache, request.cache.tokens + 1)
+            if any(n > f for n, f in zip(needed, free)):
+                plan.skipped_for_pages.append(request)           # retried next step
+                continue
+            free = [f - n for f, n in zip(free, needed)]
+            plan.entries.append(PlannedEntry(request, [request.generated[-1]], samples=True, is_decode=True))
+            budget -= 1
+        for request in prefilling:
+            remaining = len(request.feed) - request.prefill_offset
+            count = min(remaining, self.options.prefill_chunk_tokens, budget)
+            if count <= 0:
+                continue
+            needed = self.manager.pages_needed(request.cache, request.cache.tokens + count)
+            if any(n > f for n, f in zip(needed, free)):
+                plan.skipped_for_pages.append(request)
+                continue
+            free = [f - n for f, n in zip(free, needed)]
+            tokens = request.feed[request.prefill_offset:request.prefill_offset + count]
+            plan.entries.append(PlannedEntry(request, tokens, samples=(count == remaining), is_decode=False))
+            budget -= count
+        return plan
+
+    # --------------------------------------------------------------- execution
+    def _execute(self, plan: Plan) -> bool:
+        entries = [StepEntry(request_id=p.request.id, tokens=p.tokens,
+                             want=[len(p.tokens) - 1] if p.samples else [])
+                   for p in plan.entries]
+        sample_rows = [(p.request.cache.slot, p.request.options.generation) for p in plan.entries if p.samples]
+        try:
+            tokens = self.runner.run(entries, sample_rows)
+        except Exception as exc:        # failure isolation: the requests of this step fail, others live on
+            for planned in plan.entries:
+                planned.request.error = f"{type(exc).__name__}: {exc}"
+                self._finish(planned.request, RequestStatus.FAILED)
+            return True
+        now = time.monotonic()
+        self.metrics.steps += 1
+        self.metrics.skipped_for_pages += len(plan.skipped_for_pages)
+        total = sum(len(p.tokens) for p in plan.entries)
+        self.metrics.max_step_tokens = max(self.metrics.max_step_tokens, total)
+        self.metrics.max_step_requests = max(self.metrics.max_step_requests, len(plan.entries))
+        produced = iter(tokens)
+        for planned in plan.entries:
+            request = planned.request
+            if planned.is_decode:
+                self.metrics.decode_tokens += 1
+            else:
+                request.prefill_offset += len(planned.tokens)
+                self.metrics.prefill_tokens += len(planned.tokens)
+            if planned.samples:
+                if request.status is RequestStatus.PREFILL:
+                    request.status = RequestStatus.DECODING
+                self._accept(request, int(next(produced)), now)
+        return True
+
+    def _accept(self, request: Request, token: int, now: float) -> None:
+        """decode_scheduler.cpp:68-99: the token goes out (an eos token too), then the stop test."""
+        request.generated.append(token)
+        request.output.append(token)
+        if request.first_token_at is None:
+            request.first_token_at = now
+            self.metrics.ttft_seconds_sum += now - request.submitted_at
+            self.metrics.ttft_count += 1
+        else:
+            self.metrics.itl_seconds_sum += now - request.last_token_at
+            self.metrics.itl_count += 1
+        request.last_token_at = now
+        if token in request.eos_tokens or len(request.generated) >= request.options.max_new_tokens:
+            self._finish(request, RequestStatus.FINISHED)
+
+    def _finish(self, request: Request, status: RequestStatus) -> None:
+        """The one place where a request gives back what it holds."""
+        if request.cache is not None:
+            self.manager.close(request.id)
+            request.cache = None
+        if request.id in self.live:
+            self.live.remove(request.id)
+        request.status = status
+        if status is RequestStatus.FINISHED:
+            self.metrics.completed += 1
+        elif status is RequestStatus.CANCELLED:
+            self.metrics.cancelled += 1
+        elif status is RequestStatus.FAILED:
+            self.metrics.failed += 1
+
+    def _honour_cancellations(self) -> None:
+        for request_id in list(self.live):
+            request = self.requests[request_id]
+            if request.cancel_requested:
+                self._finish(request, RequestStatus.CANCELLED)
+        for request_id in list(self.queue):
+            request = self.requests[request_id]
+            if request.cancel_requested:
+                self.queue.remove(request_id)
+                self._finish(request, RequestStatus.CANCELLED)
+
+    # ------------------------------------------------------- when pages run out
+    def _break_deadlock(self) -> bool:
+        """No live request can advance because the pool is empty (only under MAX_UTILIZATION, or
+        with a pool smaller than one request). celeg skips such requests "this step" forever
+        (decode_scheduler.cpp:23-66). Here the live request of lowest priority, and among those
+        the youngest, is preempted: its pages and slot are given back and it returns to the queue
+        with prompt + generated tokens to prefill again, its generator state kept, so its output
+        continues as if nothing happened. If it is the only live request, the pool cannot hold
+        it at all and it fails with a message that says so."""
+        victim = self.requests[max(self.live, key=self._priority_key)]
+        if len(self.live) == 1:
+            victim.error = (f"out of cache pages: request {victim.id} needs more pages than the pool has "
+                            f"({[g.pool.total_pages for g in self.manager.groups]} pages of "
+                            f"{self.options.page_tokens} tokens)")
+            self._finish(victim, RequestStatus.FAILED)
+            return True
+        victim.generator_state = self.runner.save_generator(victim.cache.slot)
+        self.manager.close(victim.id)
+        victim.cache = None
+        self.live.remove(victim.id)
+        victim.feed = victim.prompt + victim.generated
+        victim.prefill_offset = 0
+        victim.status = RequestStatus.QUEUED
+        victim.preemptions += 1
+        self.queue.append(victim.id)
+        self.metrics.preempted += 1
+        self._hold_admission = True
+        return True
+
+    def _get(self, request_id: int) -> Request:
+        try:
+            return self.requests[request_id]
+        except KeyError:
+            raise KeyError(f"unknown request id {request_id}") from None

@@ -15,6 +15,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import kernels
 from ..cache.manager import CacheManager, NO_PAGE, OutOfPages
 from ..cache.storage import CacheStorage
 from ..parts import Runtime, StepContext
@@ -34,6 +35,13 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()          # places among ``tokens`` whose logits are wanted
+
+
+def _context_bucket(tokens: int) -> int:
+    bucket = 256
+    while bucket < tokens:
+        bucket *= 2
+    return bucket
 
 
 def _align4(n: int) -> int:
@@ -68,8 +76,10 @@ class StepFunction:
         self._wide_logits: Optional[torch.Tensor] = None
         self.use_graphs = use_graphs
         self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self._graph_launches: Dict[tuple, int] = {}
         self.steps_run = 0
         self.kernel_steps_graphed = 0
+        self.last_step: Optional[StepContext] = None
 
     # ------------------------------------------------------------------ requests
     def begin(self, request_id: Hashable):
@@ -154,6 +164,7 @@ class StepFunction:
         event = torch.cuda.Event()
         event.record()
         self._ring_events[slot] = event
+        self.last_step = step
 
         if wanted <= self.max_spans:
             logits = self._decode_logits
@@ -162,7 +173,7 @@ class StepFunction:
                 self._wide_logits = torch.empty((wanted, vocab), dtype=torch.float32, device=self.rt.device)
             logits = self._wide_logits
 
-        graph_key = (spans, wanted) if (all_decode and self.use_graphs and wanted <= self.max_spans) else None
+        graph_key = (spans, wanted, _context_bucket(max_ctx)) if (all_decode and self.use_graphs and wanted <= self.max_spans) else None
         if graph_key is not None:
             self._run_graphed(graph_key, step, logit_rows, wanted, logits)
         else:
@@ -183,11 +194,14 @@ class StepFunction:
             self.model.forward(step, logit_rows, wanted, logits)
             torch.cuda.current_stream().synchronize()
             graph = torch.cuda.CUDAGraph()
+            before = kernels.LAUNCHES
             with torch.cuda.graph(graph):
                 self.model.forward(step, logit_rows, wanted, logits)
+            self._graph_launches[key] = kernels.LAUNCHES - before
             self.storage.state.copy_(saved)
             self._graphs[key] = graph
         graph.replay()
+        kernels.LAUNCHES += self._graph_launches[key]      # kernels of this package inside the graph
         self.kernel_steps_graphed += 1
 
     def _stage(self, entries, caches, total, spans, wanted, stride, max_ctx):
@@ -245,7 +259,7 @@ class StepFunction:
             span_slot=view("span_slot", spans),
             block_tables=[dev[o:o + spans * stride].view(spans, stride) for o in table_offsets],
             error_flag=self.error_flag, max_span=max(lengths), max_context=max_ctx,
-            host_span_lengths=lengths)
+            context_bucket=_context_bucket(max_ctx), host_span_lengths=lengths)
         return step, view("logit_rows", max(wanted, 1)), cursor
 
     # -------------------------------------------------------------------- checks

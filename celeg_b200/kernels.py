@@ -47,11 +47,14 @@ _SIGNATURES = {
     "celeg_attention_generic": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int,
                                 c_void_p],
+    "celeg_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "celeg_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p, c_void_p],
-    "celeg_mark_seen": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "celeg_mark_seen": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
 }
 
 
@@ -79,7 +82,12 @@ def library_path() -> str:
     return _LIB._name  # type: ignore[union-attr]
 
 
+LAUNCHES = 0        # entry-point calls made so far (each is one kernel launch unless it returned early)
+
+
 def _check(code: int) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if code != 0:
         raise KernelLibraryError(library().celeg_last_error().decode("utf-8", "replace"))
 
@@ -168,6 +176,31 @@ def attention_generic(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_c
         page_tokens, int(window or 0), scale, _ptr(error_flag), dtype_code(q.dtype), _stream()))
 
 
+def attention_decode_supported(q_heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Shapes the split-key decode kernel takes; everything else goes to the general kernel."""
+    return (dtype == torch.bfloat16 and q_heads % kv_heads == 0 and q_heads // kv_heads <= 16
+            and head_dim % 8 == 0 and head_dim <= 256)
+
+
+def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_cache: torch.Tensor,
+                     v_cache: torch.Tensor, positions: torch.Tensor, token_span: torch.Tensor,
+                     block_table: torch.Tensor, tokens: int, q_heads: int, kv_heads: int, head_dim: int,
+                     page_tokens: int, window: Optional[int], scale: float, chunk: int, max_splits: int,
+                     partial_o: torch.Tensor, partial_ml: torch.Tensor, counters: torch.Tensor,
+                     error_flag: torch.Tensor) -> None:
+    """One query token per row, keys split into chunks of ``chunk``; scratch: partial_o float32
+    [tokens*q_heads*max_splits*head_dim], partial_ml float32 [tokens*q_heads*max_splits*2],
+    counters int32 [tokens*kv_heads] (zero before the first call, left zero by every call)."""
+    assert partial_o.numel() >= tokens * q_heads * max_splits * head_dim
+    assert partial_ml.numel() >= tokens * q_heads * max_splits * 2
+    assert counters.numel() >= tokens * kv_heads
+    _check(library().celeg_attention_decode(
+        _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
+        _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim,
+        page_tokens, int(window or 0), scale, chunk, max_splits, _ptr(partial_o), _ptr(partial_ml),
+        _ptr(counters), _ptr(error_flag), _stream()))
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, tokens: int, inner: int) -> None:
     _check(library().celeg_swiglu(_ptr(gate_up), _ptr(out), tokens, inner, dtype_code(gate_up.dtype), _stream()))
 
@@ -192,5 +225,7 @@ def sample(logits: torch.Tensor, rows: int, row_slot: Optional[torch.Tensor], se
                                   _stream()))
 
 
-def mark_seen(seen: torch.Tensor, tokens: torch.Tensor, token_slot: torch.Tensor, count: int) -> None:
-    _check(library().celeg_mark_seen(_ptr(seen), seen.shape[1], _ptr(tokens), _ptr(token_slot), count, _stream()))
+def mark_seen(seen: torch.Tensor, tokens: torch.Tensor, token_span: torch.Tensor, span_slot: torch.Tensor,
+              count: int) -> None:
+    _check(library().celeg_mark_seen(_ptr(seen), seen.shape[1], _ptr(tokens), _ptr(token_span), _ptr(span_slot),
+                                     count, _stream()))

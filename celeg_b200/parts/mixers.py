@@ -121,6 +121,26 @@ class AttentionMixer:
 
     def attend(self, step: StepContext, table: torch.Tensor) -> None:
         b = self.binding
+        rt = self.rt
+        if (step.max_span == 1 and step.tokens <= rt.max_requests and
+                kernels.attention_decode_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype)):
+            # one query token per request: split the keys so that few requests still fill the GPU
+            bucket = step.context_bucket
+            if self.window:
+                bucket = min(bucket, 1 << max(8, (self.window - 1).bit_length()))
+            chunk = max(64, bucket // 32)
+            max_splits = bucket // chunk
+            cap_splits = max(1, (1 << max(8, (rt.max_context - 1).bit_length())) // 64)
+            cap_splits = min(cap_splits, 32)
+            rows = rt.max_requests * self.heads * cap_splits
+            partial_o = rt.flat_scratch("attention.partial_o", rows * self.head_dim, torch.float32)
+            partial_ml = rt.flat_scratch("attention.partial_ml", rows * 2, torch.float32)
+            counters = rt.flat_scratch("attention.counters", rt.max_requests * self.kv_heads, torch.int32, zero=True)
+            kernels.attention_decode(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
+                                     step.token_span, table, step.tokens, self.heads, self.kv_heads,
+                                     self.head_dim, b.page_tokens, self.window, self.scale, chunk, max_splits,
+                                     partial_o, partial_ml, counters, step.error_flag)
+            return
         kernels.attention_generic(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
                                   step.token_span, table, step.tokens, self.heads, self.kv_heads, self.head_dim,
                                   b.page_tokens, self.window, self.scale, step.error_flag)

@@ -15,7 +15,8 @@ class Runtime:
     (the serving path: bfloat16 matrices and activations; residual stream, norms, softmax,
     rotation angles and conv state in float32)."""
 
-    def __init__(self, device: torch.device, act_dtype: torch.dtype, max_tokens: int):
+    def __init__(self, device: torch.device, act_dtype: torch.dtype, max_tokens: int, max_requests: int = 8,
+                 max_context: int = 4096):
         if act_dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"dtype must be float32 or bfloat16, got {act_dtype}")
         self.device = torch.device(device)
@@ -23,6 +24,9 @@ class Runtime:
             raise kernels.KernelLibraryError("celeg_b200 runs on a CUDA device only; there is no CPU path")
         self.act_dtype = act_dtype
         self.max_tokens = max_tokens
+        self.max_requests = max_requests
+        self.max_context = max_context
+        self._flat: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         self._scratch: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         kernels.library()                       # fail now, not at the first step, if it is missing
 
@@ -34,6 +38,14 @@ class Runtime:
         if key not in self._scratch:
             self._scratch[key] = torch.empty((self.max_tokens, columns), dtype=dtype, device=self.device)
         return self._scratch[key]
+
+    def flat_scratch(self, tag: str, elements: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """A persistent 1-D buffer shared by parts that ask with the same tag, size and type."""
+        key = (tag, elements, dtype)
+        if key not in self._flat:
+            make = torch.zeros if zero else torch.empty
+            self._flat[key] = make(elements, dtype=dtype, device=self.device)
+        return self._flat[key]
 
     def matrix(self, weight: torch.Tensor) -> torch.Tensor:
         """A projection weight on the device in the path's matrix precision."""
@@ -72,6 +84,7 @@ class StepContext:
     error_flag: torch.Tensor          # [1] set by a kernel that met an impossible index
     max_span: int = 1                 # longest span (host knowledge, for kernel choice)
     max_context: int = 0              # largest position + 1 in the step
+    context_bucket: int = 0           # max_context rounded up to a power of two (launch shapes use this)
     host_positions: Optional[list] = None
     host_span_lengths: Optional[list] = None
     extras: Dict[str, object] = field(default_factory=dict)

@@ -1,0 +1,70 @@
+"""Device-side sampling state and the call that draws one token per wanted row.
+
+Each request's generator state and seen-table live in arrays indexed by the request's state
+slot, so what a request draws does not depend on the batch it is in (celeg keeps the same per
+lane: src/backend/cuda/packed/metadata.cu:20-24)."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import kernels
+from .params import SamplingParams
+
+
+class Sampler:
+    def __init__(self, vocab_size: int, slots: int, max_rows: int, device: torch.device):
+        self.vocab_size = vocab_size
+        self.device = device
+        self.max_rows = max_rows
+        self.seen = torch.zeros((slots, vocab_size), dtype=torch.uint8, device=device)
+        self.rng = torch.ones(slots, dtype=torch.int64, device=device)
+        # staging: [slot | top_k] int32 and [temperature | top_p | penalty] float32, one copy each
+        self._host_i = torch.empty(2 * max_rows, dtype=torch.int32).pin_memory()
+        self._host_f = torch.empty(3 * max_rows, dtype=torch.float32).pin_memory()
+        self._dev_i = torch.zeros(2 * max_rows, dtype=torch.int32, device=device)
+        self._dev_f = torch.zeros(3 * max_rows, dtype=torch.float32, device=device)
+        self.out = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self._out_host = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
+
+    def reset_slot(self, slot: int, seed: int) -> None:
+        """A new request takes the slot: nothing seen, generator at its seed."""
+        self.seen[slot].zero_()
+        self.set_rng(slot, seed)
+
+    def set_rng(self, slot: int, state: int) -> None:
+        self.rng[slot] = state - (1 << 64) if state >= (1 << 63) else state
+
+    def get_rng(self, slot: int) -> int:
+        value = int(self.rng[slot].item())
+        return value + (1 << 64) if value < 0 else value
+
+    def mark_step(self, step) -> None:
+        """The tokens a step fed count as seen by their requests."""
+        kernels.mark_seen(self.seen, step.token_ids, step.token_span, step.span_slot, step.tokens)
+
+    def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[int, SamplingParams]]) -> List[int]:
+        """One token per row of ``logits``; ``rows[i]`` = (state slot, options). Synchronises."""
+        count = len(rows)
+        if count == 0:
+            return []
+        if count > self.max_rows:
+            raise ValueError(f"{count} rows to sample, the sampler was sized for {self.max_rows}")
+        torch.cuda.current_stream().synchronize()        # staging buffers of the last call are free
+        m = self.max_rows
+        hi, hf = self._host_i.numpy(), self._host_f.numpy()
+        for i, (slot, params) in enumerate(rows):
+            hi[i] = slot
+            hi[m + i] = params.top_k
+            hf[i] = params.temperature
+            hf[m + i] = params.top_p
+            hf[2 * m + i] = params.repetition_penalty
+        self._dev_i.copy_(self._host_i, non_blocking=True)
+        self._dev_f.copy_(self._host_f, non_blocking=True)
+        kernels.sample(logits, count, self._dev_i[:m], self.seen, self.rng, self._dev_f[:m], self._dev_i[m:],
+                       self._dev_f[m:2 * m], self._dev_f[2 * m:], self.out)
+        self._out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._out_host[:count].tolist()

@@ -1,0 +1,160 @@
+"""The cache manager on the host: no page lost, held twice or freed twice, under random orders
+of requests; windows give pages back; slots are cleared and reused."""
+from __future__ import annotations
+
+import random
+
+import pytest
+
+from celeg_b200.cache import (NO_PAGE, CacheManager, OutOfPages, PageError, PagedNeed, PagePool, StateLayout)
+
+
+def make(pages=(8,), windows=(None,), page_tokens=4, slots=3, cleared=None):
+    groups = [(("g", i, w), PagedNeed(kv_heads=1, head_dim=8, window=w)) for i, w in enumerate(windows)]
+    layout = StateLayout()
+    layout.add(0, 10)
+    layout.add(3, 7)
+    return CacheManager(page_tokens, list(pages), groups, layout, slots,
+                        clear_slot=(cleared.append if cleared is not None else None))
+
+
+def test_pool_allocation_is_all_or_nothing_and_lifo():
+    pool = PagePool(4, 16)
+    assert pool.allocate(5) is None and pool.free_pages == 4
+    first = pool.allocate(3)
+    assert first == [0, 1, 2]
+    pool.release([1])
+    assert pool.allocate(1) == [1]                      # the page just given back is used again first
+    assert pool.allocate_tokens(17) is None             # needs 2, one free
+    assert pool.pages_for(16) == 1 and pool.pages_for(17) == 2
+
+
+def test_pool_refuses_double_free_and_bad_ids():
+    pool = PagePool(3, 4)
+    pages = pool.allocate(2)
+    pool.release(pages)
+    with pytest.raises(PageError):
+        pool.release(pages)
+    with pytest.raises(PageError):
+        pool.release([7])
+    with pytest.raises(PageError):
+        pool.retain([0])
+    held = pool.allocate(1)
+    pool.retain(held)
+    assert pool.ref_count(held[0]) == 2
+    with pytest.raises(PageError):
+        pool.release([held[0]] * 3)                     # validated before anything changes
+    assert pool.ref_count(held[0]) == 2
+    pool.release(held)
+    pool.release(held)
+    assert pool.free_pages == 3
+
+
+def test_state_layout_is_aligned():
+    layout = StateLayout()
+    assert layout.add(0, 10) == 0 and layout.add(1, 7) == 12 and layout.slot_elements == 20
+
+
+def test_open_reserve_advance_close():
+    cleared = []
+    manager = make(cleared=cleared)
+    a = manager.open("a")
+    assert cleared == [a.slot]
+    manager.reserve(a, 9)                               # 3 pages of 4 tokens
+    assert len(a.tables[0]) == 3 and manager.groups[0].pool.free_pages == 5
+    manager.reserve(a, 9)                               # nothing more needed
+    assert len(a.tables[0]) == 3
+    with pytest.raises(PageError):
+        manager.advance(a, 13)                          # beyond what was reserved
+    manager.advance(a, 9)
+    with pytest.raises(ValueError):
+        manager.advance(a, 8)
+    manager.check_invariants()
+    manager.close("a")
+    assert manager.groups[0].pool.free_pages == 8 and manager.free_slots == 3
+    with pytest.raises(PageError):
+        manager.close("a")
+    with pytest.raises(PageError):
+        manager.reserve(a, 4)
+
+
+def test_reserve_across_groups_is_all_or_nothing():
+    manager = make(pages=(8, 2), windows=(None, None))
+    a = manager.open("a")
+    with pytest.raises(OutOfPages):
+        manager.reserve(a, 12)                          # 3 pages: group 1 has only 2
+    assert manager.groups[0].pool.free_pages == 8 and a.tables == [[], []]
+    manager.reserve(a, 8)
+    assert [len(t) for t in a.tables] == [2, 2]
+
+
+def test_no_slot_no_request():
+    manager = make(slots=1)
+    manager.open("a")
+    assert not manager.can_hold(1)
+    with pytest.raises(OutOfPages):
+        manager.open("b")
+    with pytest.raises(ValueError):
+        manager.open("a")
+
+
+def test_window_gives_pages_back_as_it_passes():
+    manager = make(pages=(8, 8), windows=(None, 6))
+    a = manager.open("a")
+    total = 0
+    for step in (5, 4, 3, 7, 1, 1, 1):
+        manager.reserve(a, total + step)
+        total += step
+        released = manager.advance(a, total)
+        manager.check_invariants()
+        # the next query sits at `total` and reads positions > total - 6
+        first_needed = max(0, total - 6 + 1)
+        table = a.tables[1]
+        for logical, page in enumerate(table):
+            if (logical + 1) * 4 <= first_needed:
+                assert page == NO_PAGE
+            else:
+                assert page != NO_PAGE
+        assert all(group == 1 for group, _ in released)
+        assert NO_PAGE not in a.tables[0]
+    assert manager.groups[1].pool.used_pages <= 3       # ceil((6-1)/4)+1 pages in steady state
+    manager.close("a")
+    assert manager.groups[1].pool.free_pages == 8
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_traffic_keeps_the_books(seed):
+    rng = random.Random(seed)
+    cleared = []
+    manager = make(pages=(12, 9), windows=(None, 10), page_tokens=4, slots=4, cleared=cleared)
+    live, lengths, serial = {}, {}, 0
+    for _ in range(400):
+        action = rng.random()
+        if action < 0.25 and manager.free_slots:
+            name = f"r{serial}"
+            serial += 1
+            live[name] = manager.open(name)
+            lengths[name] = 0
+        elif action < 0.85 and live:
+            name = rng.choice(sorted(live))
+            grow = rng.randint(1, 9)
+            before = [list(t) for t in live[name].tables]
+            try:
+                manager.reserve(live[name], lengths[name] + grow)
+            except OutOfPages:
+                assert [list(t) for t in live[name].tables] == before
+            else:
+                lengths[name] += grow
+                manager.advance(live[name], lengths[name])
+        elif live:
+            name = rng.choice(sorted(live))
+            manager.close(name)
+            del live[name], lengths[name]
+        manager.check_invariants()
+        for name, cache in live.items():
+            assert cache.tokens == lengths[name]
+    for name in list(live):
+        manager.close(name)
+    manager.check_invariants()
+    assert all(group.pool.free_pages == group.pool.total_pages for group in manager.groups)
+    assert manager.free_slots == 4 and len(cleared) == serial

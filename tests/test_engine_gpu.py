@@ -1,0 +1,401 @@
+"""The engine through its Python entry point and its parts on the GPU: greedy and seeded
+generation against the plain implementation, long decoding, first tokens, parts alone, and a toy
+mixer with state of its own that is registered, built and stepped from outside the package."""
+from __future__ import annotations
+
+import copy
+import dataclasses
+import io
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2
+from tiny_models import CONFIGS, TINY_A, TINY_B, write_tiny
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    base = tmp_path_factory.mktemp("engine_models")
+    out = {}
+    for name in ("A", "B", "C"):
+        folder = write_tiny(base, name)
+        config, weights = plain_lfm2.load_model_folder(folder)
+        out[name] = (folder, config, weights)
+    return out
+
+
+def prompts_of(vocab, lengths, seed):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, vocab, size=n).tolist() for n in lengths]
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_matches_plain_model_float32(models, graphs):
+    """BASELINE workload of tiny A: prompts of 5, 17 and 31 tokens, 16 greedy tokens each, run
+    together through the scheduler."""
+    from celeg_b200 import Engine
+    folder, config, weights = models["A"]
+    prompts = prompts_of(config["vocab_size"], [5, 17, 31], seed=20)
+    engine = Engine(folder, dtype="float32", use_cuda_graph=graphs)
+    got = engine.generate(prompts, max_new_tokens=16, temperature=0.0, repetition_penalty=1.0, eos_tokens=())
+    for prompt, tokens in zip(prompts, got):
+        assert tokens == plain_lfm2.generate(config, weights, prompt, 16, eos_tokens=())
+    metrics = engine.metrics()
+    assert metrics.completed == 3 and metrics.prefill_tokens == 53 and metrics.decode_tokens == 45
+    engine.loaded.manager.check_invariants()
+    assert engine.loaded.manager.free_slots == engine.options.max_active_requests
+
+
+def test_greedy_generation_bfloat16_follows_plain_model(models):
+    from celeg_b200 import Engine
+    folder, config, weights = models["B"]
+    prompts = prompts_of(config["vocab_size"], [9, 40], seed=21)
+    engine = Engine(folder, dtype="bfloat16")
+    got = engine.generate(prompts, max_new_tokens=12, temperature=0.0, repetition_penalty=1.0, eos_tokens=())
+    for prompt, tokens in zip(prompts, got):
+        # bf16 rounding may flip a near-tie; then the continuation differs, so compare step by
+        # step against the plain model fed with the engine's own tokens
+        sequence = list(prompt)
+        for token in tokens:
+            logits = plain_lfm2.forward(config, weights, sequence)[-1]
+            best = float(logits.max())
+            assert logits[token] >= best - 0.05, (token, int(logits.argmax()))
+            sequence.append(token)
+
+
+def test_seeded_sampling_is_independent_of_the_batch(models):
+    """Tiny B's workload: chunked prefill beside decoding requests, temperature 0.8, seed 7. A
+    request alone and the same request among others draw the same tokens (float32 path, so the
+    logits agree to rounding), and they match the plain sampler fed with plain logits."""
+    from celeg_b200 import Engine, EngineOptions
+    folder, config, weights = models["B"]
+    prompts = prompts_of(config["vocab_size"], [33, 1, 64, 20], seed=22)
+    options = EngineOptions(max_active_requests=4, max_batched_tokens=24, prefill_chunk_tokens=7)
+    kwargs = dict(max_new_tokens=24, temperature=0.8, top_k=50, top_p=0.95, repetition_penalty=1.1, seed=7,
+                  eos_tokens=())
+    together = Engine(folder, dtype="float32", options=options).generate(prompts, **kwargs)
+    alone = Engine(folder, dtype="float32", options=options)
+    for prompt, tokens in zip(prompts, together):
+        assert alone.generate(prompt, **kwargs) == tokens
+    want = plain_lfm2.generate(config, weights, prompts[0], 24, temperature=0.8, top_k=50, top_p=0.95,
+                               repetition_penalty=1.1, seed=7)
+    assert together[0] == want
+
+
+def test_eos_stops_generation(models):
+    from celeg_b200 import Engine
+    folder, config, weights = models["A"]
+    (prompt,) = prompts_of(config["vocab_size"], [11], seed=23)
+    free_run = plain_lfm2.generate(config, weights, prompt, 10, eos_tokens=())
+    stop = free_run[4]
+    engine = Engine(folder, dtype="float32")
+    got = engine.generate(prompt, max_new_tokens=10, temperature=0.0, repetition_penalty=1.0, eos_tokens=[stop])
+    assert got == free_run[:free_run.index(stop) + 1]
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-4), ("bfloat16", 8e-2)])
+def test_long_decoding(models, dtype, tol):
+    """A short prompt, then 200 tokens decoded one by one with CUDA graphs on: pages fill and
+    follow one another, the context bucket of the graph changes, positions grow."""
+    from celeg_b200 import Engine, StepEntry
+    folder, config, weights = models["A"]
+    (sequence,) = prompts_of(config["vocab_size"], [215], seed=24)
+    engine = Engine(folder, dtype=dtype, use_cuda_graph=True)
+    want = plain_lfm2.forward(config, weights, sequence)
+    got = [engine.forward([StepEntry("long", sequence[:15], [14])])[0].cpu().numpy()]
+    for token in sequence[15:]:
+        got.append(engine.forward([StepEntry("long", [token], [0])])[0].cpu().numpy())
+    got = np.stack(got)
+    err = np.abs(got - want[14:])
+    assert err.max() < tol, f"worst at step {int(err.max(axis=1).argmax())}: {err.max():.3e}"
+    engine.end("long")
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 6e-2)])
+def test_first_tokens_of_a_sequence(models, dtype, tol):
+    """Positions 0..5 one by one: fewer tokens than the conv kernel has taps, one key only."""
+    from celeg_b200 import Engine, StepEntry
+    for name in ("A", "B", "C"):
+        folder, config, weights = models[name]
+        (sequence,) = prompts_of(config["vocab_size"], [6], seed=25)
+        engine = Engine(folder, dtype=dtype)
+        want = plain_lfm2.forward(config, weights, sequence)
+        for i, token in enumerate(sequence):
+            got = engine.forward([StepEntry("first", [token], [0])])[0].cpu().numpy()
+            assert np.abs(got - want[i]).max() < tol, (name, i)
+
+
+def test_step_input_errors_name_the_request(models):
+    from celeg_b200 import Engine, StepEntry
+    from celeg_b200.engine.step import StepInputError
+    folder, config, _ = models["A"]
+    engine = Engine(folder, dtype="float32")
+    with pytest.raises(StepInputError, match="'x'"):
+        engine.forward([StepEntry("x", [1, 99999], [])])
+    with pytest.raises(StepInputError, match="twice"):
+        engine.forward([StepEntry("y", [1], []), StepEntry("y", [2], [])])
+    with pytest.raises(StepInputError, match="wanted place"):
+        engine.forward([StepEntry("z", [1, 2], [2])])
+    with pytest.raises(StepInputError, match="context"):
+        engine.forward([StepEntry("w", [1] * 300, [])])
+
+
+def test_out_of_pages_leaves_everything_as_it_was(models):
+    from celeg_b200 import Engine, EngineOptions, StepEntry
+    from celeg_b200.cache import OutOfPages
+    folder, config, weights = models["A"]
+    engine = Engine(folder, dtype="float32", options=EngineOptions(logical_kv_pages=3, max_active_requests=2))
+    sequence = prompts_of(config["vocab_size"], [40], seed=26)[0]
+    engine.forward([StepEntry("a", sequence[:30], [])])              # 2 of 3 pages
+    with pytest.raises(OutOfPages):
+        engine.forward([StepEntry("a", sequence[30:32], []), StepEntry("b", sequence[:20], [])])
+    engine.loaded.manager.check_invariants()
+    assert engine.loaded.manager.get("a").tokens == 30
+    got = engine.forward([StepEntry("a", sequence[30:40], [9])])[0].cpu().numpy()
+    want = plain_lfm2.forward(config, weights, sequence)[39]
+    assert np.abs(got - want).max() < 2e-4
+
+
+# ------------------------------------------------------------------------- parts alone
+def tiny_runtime(dtype, max_tokens=64):
+    from celeg_b200.parts import Runtime
+    return Runtime(torch.device("cuda:0"), dtype, max_tokens, max_requests=4, max_context=256)
+
+
+def step_context(spans, page_tokens=16, slots=None):
+    """spans: list of (start position, token count); every request gets fresh pages in order."""
+    from celeg_b200.parts import StepContext
+    positions, token_span, begins = [], [], [0]
+    for index, (start, count) in enumerate(spans):
+        positions += list(range(start, start + count))
+        token_span += [index] * count
+        begins.append(begins[-1] + count)
+    max_pages = max((s + c + page_tokens - 1) // page_tokens for s, c in spans)
+    table = np.full((len(spans), max_pages), -1, dtype=np.int32)
+    page = 0
+    for index, (start, count) in enumerate(spans):
+        for logical in range((start + count + page_tokens - 1) // page_tokens):
+            table[index, logical] = page
+            page += 1
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    return StepContext(tokens=len(positions), spans=len(spans), token_ids=i32([0] * len(positions)),
+                       positions=i32(positions), token_span=i32(token_span), span_begin=i32(begins),
+                       span_slot=i32(slots or list(range(len(spans)))), block_tables=[i32(table)],
+                       error_flag=torch.zeros(1, dtype=torch.int32, device="cuda"),
+                       max_span=max(c for _, c in spans), max_context=max(s + c for s, c in spans),
+                       context_bucket=256), page
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 4e-2)])
+def test_parts_alone_against_their_plain_functions(dtype, tol):
+    """Each part built from the registry with its own sizes, outside any model."""
+    from celeg_b200.parts import PagedBinding, StateBinding, part_factory
+    rng = np.random.default_rng(30)
+    rt = tiny_runtime(dtype)
+    w = lambda *shape, std=0.3: torch.tensor(rng.normal(size=shape) * std).to(torch.bfloat16)
+    f64 = lambda t: t.to(torch.float64).numpy()
+    hidden, tokens = 72, 23
+    x_host = w(tokens, hidden, std=1.0)
+    x = torch.zeros((64, hidden), dtype=dtype, device="cuda")
+    x[:tokens] = x_host.to(dtype).cuda()
+    out = torch.zeros((64, hidden), dtype=dtype, device="cuda")
+
+    def check(got, want, scale=1.0):
+        err = np.abs(got[:tokens].to(torch.float64).cpu().numpy() - want)
+        # intermediate rounding scales with the size of the terms that were summed, not of the result
+        bound = tol * scale * max(1.0, float(np.sqrt(np.mean(want * want))))
+        assert err.max() <= bound, (err.max(), bound)
+
+    # norm
+    norm_w = (1 + 0.1 * torch.tensor(rng.normal(size=hidden))).to(torch.bfloat16)
+    norm = part_factory("norm", "rmsnorm")({"width": hidden, "eps": 2e-5}, {"weight": norm_w}, rt)
+    residual = torch.zeros((64, hidden), dtype=torch.float32, device="cuda")
+    residual[:tokens] = x_host.float().cuda()
+    norm.add_norm(residual, None, out, tokens)
+    check(out, plain_lfm2.rmsnorm(f64(x_host), f64(norm_w), 2e-5))
+
+    # feed-forward
+    inner = 100
+    ffn_w = {"gate": w(inner, hidden), "up": w(inner, hidden), "down": w(hidden, inner)}
+    ffn = part_factory("feed_forward", "swiglu")({"hidden_size": hidden, "intermediate_size": inner}, ffn_w, {}, rt)
+    step, _ = step_context([(0, tokens)])
+    ffn.forward(x, out, step)
+    check(out, plain_lfm2.swiglu(f64(x_host), f64(ffn_w["gate"]), f64(ffn_w["up"]), f64(ffn_w["down"])), 4.0)
+
+    # short convolution, in two portions (5 taps, the second portion shorter than the kernel)
+    taps = 5
+    conv_w = {"in_proj": w(3 * hidden, hidden), "conv": w(hidden, 1, taps), "out_proj": w(hidden, hidden)}
+    conv = part_factory("mixer", "short_conv")({"hidden_size": hidden, "taps": taps}, conv_w, {}, rt)
+    assert conv.cache_need().elements == (taps - 1) * hidden
+    state = torch.zeros((2, (taps - 1) * hidden + 8), dtype=torch.float32, device="cuda")
+    conv.bind_cache(StateBinding(state=state[:, 4:], slot_stride=state.stride(0)))
+    want = plain_lfm2.short_conv_mixer(f64(x_host), f64(conv_w["in_proj"]), f64(conv_w["conv"]),
+                                       f64(conv_w["out_proj"]))
+    cut = tokens - 3
+    step, _ = step_context([(0, cut)], slots=[1])
+    conv.forward(x, out, step)
+    tail_in = torch.zeros_like(x)
+    tail_in[:3] = x[cut:tokens]
+    tail_out = torch.zeros_like(out)
+    step, _ = step_context([(cut, 3)], slots=[1])
+    conv.forward(tail_in, tail_out, step)
+    got = torch.cat([out[:cut], tail_out[:3]])
+    check(got, want, 4.0)
+    assert float(state[0].abs().sum()) == 0.0
+
+    # attention: 3 heads on 1 kv head, head size 24, in two portions over pages of 8
+    heads, kv_heads, head_dim, theta, eps = 3, 1, 24, 5000.0, 1e-5
+    attn_w = {"q_proj": w(heads * head_dim, hidden), "k_proj": w(kv_heads * head_dim, hidden),
+              "v_proj": w(kv_heads * head_dim, hidden), "out_proj": w(hidden, heads * head_dim),
+              "q_norm": (1 + 0.1 * torch.tensor(rng.normal(size=head_dim))).to(torch.bfloat16),
+              "k_norm": (1 + 0.1 * torch.tensor(rng.normal(size=head_dim))).to(torch.bfloat16)}
+    position = part_factory("position", "rope_split_half")(
+        {"theta": theta, "head_dim": head_dim, "rotary_dim": head_dim}, rt)
+    attention = part_factory("mixer", "attention")(
+        {"hidden_size": hidden, "num_heads": heads, "num_kv_heads": kv_heads, "head_dim": head_dim,
+         "qk_norm_eps": eps, "window": None, "softmax_scale": head_dim ** -0.5}, attn_w, {"position": position}, rt)
+    need = attention.cache_need()
+    assert (need.kv_heads, need.head_dim, need.window) == (kv_heads, head_dim, None)
+    k_cache = torch.zeros((8, kv_heads, 8, head_dim), dtype=dtype, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    attention.bind_cache(PagedBinding(group=0, k=k_cache, v=v_cache, page_tokens=8))
+    want = plain_lfm2.attention_mixer(f64(x_host), *(f64(attn_w[n]) for n in
+                                                     ("q_proj", "k_proj", "v_proj", "out_proj", "q_norm", "k_norm")),
+                                      heads, kv_heads, head_dim, theta, eps)
+    step, _ = step_context([(0, cut)], page_tokens=8)
+    attention.forward(x, out, step)
+    step, _ = step_context([(cut, 3)], page_tokens=8)
+    attention.forward(tail_in, tail_out, step)
+    got = torch.cat([out[:cut], tail_out[:3]])
+    check(got, want, 4.0)
+
+
+# --------------------------------------------------------- a toy mixer from outside the package
+def test_toy_mixer_with_its_own_state_is_registered_built_and_stepped(tmp_path):
+    """An exponential moving average over the sequence, y_t = s_t W with s_t = a*s_{t-1} + x_t and
+    per-request state s of fixed size, is defined here, registered, put into a model description
+    in place of one LFM2 layer's mixer, and run through the engine's own loader, cache manager
+    and step function in portions, against a plain computation."""
+    from celeg_b200.cache import StateNeed
+    from celeg_b200.config import (Architecture, Lfm2Config, PartSpec, TensorRef, build_lfm2_spec,
+                                   register_architecture)
+    from celeg_b200.config.lfm2_arch import lfm2_random_init
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    from celeg_b200.parts import register_part
+    from celeg_b200.weights import write_random_model
+
+    decay = 0.75
+
+    @register_part("mixer", "toy_ema", replace=True)
+    class ToyEma:
+        def __init__(self, params, weights, parts, rt):
+            self.rt = rt
+            self.hidden = params["hidden_size"]
+            self.decay = params["decay"]
+            self.weight = rt.matrix(weights["proj"])
+            self.binding = None
+            self.mixed = rt.scratch("toy.mixed", self.hidden)
+
+        def cache_need(self):
+            return StateNeed(elements=self.hidden)
+
+        def bind_cache(self, binding):
+            self.binding = binding
+
+        def forward(self, x, out, step):
+            # plain torch on the device: a toy part is free to be slow
+            state = self.binding.state
+            begins = step.span_begin[:step.spans + 1].tolist()
+            slots = step.span_slot[:step.spans].tolist()
+            for index, slot in enumerate(slots):
+                s = state[slot, :self.hidden].clone()
+                for t in range(begins[index], begins[index + 1]):
+                    s = self.decay * s + x[t].float()
+                    self.mixed[t] = s.to(self.mixed.dtype)
+                state[slot, :self.hidden] = s
+            self.rt.linear(self.mixed, self.weight, out, step.tokens)
+
+    def toy_spec(config):
+        spec = build_lfm2_spec(config)
+        layers = list(spec.layers)
+        hidden = config.hidden_size
+        toy = PartSpec(kind="toy_ema", params={"hidden_size": hidden, "decay": decay},
+                       tensors={"proj": TensorRef("model.layers.1.toy.proj.weight", (hidden, hidden))})
+        layers[1] = dataclasses.replace(layers[1], mixer=toy)
+        return dataclasses.replace(spec, layers=tuple(layers), architecture="toy_lfm2")
+
+    register_architecture(Architecture(
+        name="toy_lfm2", parse_config=Lfm2Config.from_dict,
+        resolve_config=lambda config, shapes: dataclasses.replace(
+            config, tie_word_embeddings=True if config.tie_word_embeddings is None else config.tie_word_embeddings),
+        build_spec=toy_spec, random_init=lfm2_random_init), replace=True)
+
+    raw = copy.deepcopy(TINY_A)
+    raw["model_type"] = "toy_lfm2"
+    folder = write_random_model(str(tmp_path / "toy"), raw, 5)
+    loaded = load_model(folder, dtype="float32", max_requests=3, cache_tokens=128, max_batched_tokens=64)
+    assert loaded.model.state_layout.sizes[1] == 64          # the toy's state sits in the slot beside the convs'
+    assert len(loaded.model.state_layout.offsets) == 3       # two conv layers (0, 3) + the toy (1)
+
+    config, weights = plain_lfm2.load_model_folder(folder)
+
+    def plain_forward(tokens):
+        x = weights["model.embed_tokens.weight"][np.asarray(tokens)]
+        for index, kind in enumerate(config["layer_types"]):
+            if index != 1:
+                x = plain_lfm2.block(x, index, kind, config, weights)
+                continue
+            p = "model.layers.1."
+            n = plain_lfm2.rmsnorm(x, weights[p + "operator_norm.weight"], config["norm_eps"])
+            s, mixed = np.zeros(x.shape[1]), np.zeros_like(x)
+            for t in range(len(tokens)):
+                s = decay * s + n[t]
+                mixed[t] = s
+            h = x + mixed @ weights[p + "toy.proj.weight"].T
+            n2 = plain_lfm2.rmsnorm(h, weights[p + "ffn_norm.weight"], config["norm_eps"])
+            x = h + plain_lfm2.swiglu(n2, weights[p + "feed_forward.w1.weight"], weights[p + "feed_forward.w3.weight"],
+                                      weights[p + "feed_forward.w2.weight"])
+        z = plain_lfm2.rmsnorm(x, weights["model.embedding_norm.weight"], config["norm_eps"])
+        return z @ weights["model.embed_tokens.weight"].T
+
+    sequences = prompts_of(config["vocab_size"], [30, 21], seed=31)
+    want = [plain_forward(s) for s in sequences]
+    step = loaded.step
+    cuts = [(7, 2), (1, 9), (10, 1), (12, 9)]                   # portions of the two requests, step by step
+    at = [0, 0]
+    for a, b in cuts:
+        entries = [StepEntry("r0", sequences[0][at[0]:at[0] + a], list(range(a))),
+                   StepEntry("r1", sequences[1][at[1]:at[1] + b], list(range(b)))]
+        logits = step.run(entries, auto_begin=True).cpu().numpy()
+        assert np.abs(logits[:a] - want[0][at[0]:at[0] + a]).max() < 3e-4
+        assert np.abs(logits[a:] - want[1][at[1]:at[1] + b]).max() < 3e-4
+        at = [at[0] + a, at[1] + b]
+    step.end("r0")
+    # a new request in r0's slot starts from a cleared state
+    logits = step.run([StepEntry("r2", sequences[0][:5], [4])], auto_begin=True).cpu().numpy()
+    assert np.abs(logits[0] - want[0][4]).max() < 3e-4
+
+
+def test_cli_generates_and_dumps_logits(models, tmp_path, capsys):
+    from celeg_b200.cli import main
+    folder, config, weights = models["A"]
+    prompt = prompts_of(config["vocab_size"], [12], seed=32)[0]
+    dump = str(tmp_path / "last.f32")
+    code = main(["--model", folder, "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6",
+                 "--dtype", "fp32", "--temperature", "0", "--repetition-penalty", "1.0", "--runtime-tokens",
+                 "--dump-logits", dump, "--runtime-metrics", "--context", "128"])
+    assert code == 0
+    captured = capsys.readouterr()
+    want = [t for t in plain_lfm2.generate(config, weights, prompt, 6, eos_tokens=(7,))]
+    assert f"CELEG_GENERATED_TOKEN_IDS=[{','.join(map(str, want))}]" in captured.out
+    assert "runtime.decode_tokens_per_second=" in captured.err
+    logits = np.fromfile(dump, dtype="<f4")
+    assert np.abs(logits - plain_lfm2.forward(config, weights, prompt)[-1]).max() < 2e-4
+    assert main(["--model", folder, "--prompt", "hello"]) == 1
+    assert "error:" in capsys.readouterr().err

@@ -302,3 +302,41 @@ def test_sampling_greedy_and_seeded():
             states[slot] = new_state
             seen_host[slot, token] = 1
     assert np.array_equal(seen_dev.cpu().numpy(), seen_host)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,window,chunk", [
+    (4, 2, 16, 16, None, 64), (3, 1, 32, 8, None, 64), (5, 5, 48, 16, None, 128), (32, 8, 64, 16, None, 64),
+    (6, 3, 80, 32, 37, 64), (16, 1, 128, 64, None, 256), (4, 4, 24, 16, 5, 64),
+])
+def test_attention_decode_split_keys(heads, kv_heads, head_dim, page_tokens, window, chunk):
+    """One query token per request at very different context lengths (one key, a page edge,
+    hundreds), twice in a row so the counters' reset is used; a far key made to dominate."""
+    from celeg_b200 import kernels
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(8)
+    lengths = [1, 16, 17, 300, 511, 64]
+    pages = sum((n + page_tokens - 1) // page_tokens for n in lengths) + 7
+    k_cache, v_cache, table, ks, vs = paged_setup(rng, dtype, lengths, kv_heads, head_dim, page_tokens, pages)
+    tokens = len(lengths)
+    q = rounded(rng.normal(size=(tokens, heads, head_dim)), dtype)
+    if not window:
+        q[3] = rounded(ks[3][2, 0][None, :].repeat(heads, 0) * 3.0, dtype)      # key 2 of 300 stands out
+    positions = np.array([n - 1 for n in lengths], dtype=np.int32)
+    token_span = np.arange(tokens, dtype=np.int32)
+    scale = head_dim ** -0.5
+    max_splits = (512 + chunk - 1) // chunk
+    partial_o = torch.empty(tokens * heads * max_splits * head_dim, dtype=torch.float32, device="cuda")
+    partial_ml = torch.empty(tokens * heads * max_splits * 2, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(tokens * kv_heads, dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    want = np.stack([attention_reference(q[t], ks[t], vs[t], int(positions[t]), scale, window)
+                     for t in range(tokens)]).reshape(tokens, -1)
+    for _ in range(2):
+        out = torch.zeros((tokens, heads * head_dim), dtype=dtype, device="cuda")
+        kernels.attention_decode(dev(q.reshape(tokens, -1), dtype), heads * head_dim, out, k_cache, v_cache,
+                                 dev(positions), dev(token_span), dev(table), tokens, heads, kv_heads, head_dim,
+                                 page_tokens, window, scale, chunk, max_splits, partial_o, partial_ml, counters,
+                                 flag)
+        assert int(flag.item()) == 0
+        assert int(counters.abs().sum().item()) == 0
+        close(out, want, dtype)
