@@ -256,3 +256,98 @@ CELEG_API int celeg_attention_decode(const void* q, int q_row_stride, void* out,
     attention_decode_kernel<<<grid, kDecodeThreads, smem, stream>>>(p);
     return check_launch("attention_decode");
 }
+
+// ---------------------------------------------------------------------------------------------
+// celeg_attention_decode_static: the same kernel for callers that cannot allocate.
+//
+// Some hosts of this library must not, or cannot, call cudaMalloc when they need attention: a
+// serving process that has handed every remaining byte of device memory to its own pool (a
+// later cudaMalloc simply fails), or a latency-critical loop for which the implicit
+// device-wide synchronisation of cudaMalloc/cudaFree is not acceptable. For them the scratch
+// memory of the split-key kernel lives in a fixed array inside this library instead of being
+// passed in. This entry point has no counterpart in celeg.
+//
+// Cost and limits: every GPU that loads this library holds kStaticScratchBytes (8 MiB) until the
+// process exits. A call whose partial results, maxima/denominators and counters do not fit is
+// refused with an error message, nothing is launched. All calls share the one array: it keeps
+// whatever the previous call left, so the counters are cleared on the stream before every
+// launch, and two calls that overlap on the GPU (different streams, no ordering between them)
+// race on it and give wrong results. The FIRST call on each device looks up the array's device
+// address (cudaGetSymbolAddress, with that device current) and remembers it; make that first
+// call before any stream capture begins. No cudaMalloc, cudaFree or allocating library routine
+// is called here.
+#include <mutex>
+
+namespace celeg_b200 {
+
+constexpr long long kStaticScratchBytes = 8ll * 1024 * 1024;
+constexpr int kMaxDevices = 64;
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a pointer to pass on.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+static std::mutex g_static_mutex;
+static void* g_static_address[kMaxDevices] = {};
+
+static int static_scratch_for_current_device(void** address) {
+    int device = -1;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        set_error("attention_decode_static: cannot tell the current device (%s)",
+                  status == cudaSuccess ? "index out of range" : cudaGetErrorString(status));
+        return -3;
+    }
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_address[device] == nullptr) {
+        void* found = nullptr;
+        status = cudaGetSymbolAddress(&found, g_static_scratch);
+        if (status != cudaSuccess || found == nullptr) {
+            set_error("attention_decode_static: cudaGetSymbolAddress failed on device %d: %s", device,
+                      cudaGetErrorString(status));
+            return -3;
+        }
+        g_static_address[device] = found;
+    }
+    *address = g_static_address[device];
+    return 0;
+}
+
+}  // namespace celeg_b200
+
+CELEG_API long long celeg_attention_decode_static_capacity() { return kStaticScratchBytes; }
+
+CELEG_API int celeg_attention_decode_static(const void* q, int q_row_stride, void* out, const void* k_cache,
+                                            const void* v_cache, long long page_stride, const int* positions,
+                                            const int* token_span, const int* block_table, int table_stride,
+                                            int tokens, int q_heads, int kv_heads, int head_dim, int page_tokens,
+                                            int window, float scale, int chunk, int max_splits, int* error_flag,
+                                            cudaStream_t stream) {
+    CELEG_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && head_dim > 0 && max_splits > 0,
+                  "attention_decode_static: invalid sizes tokens=%d q_heads=%d kv_heads=%d head_dim=%d "
+                  "max_splits=%d", tokens, q_heads, kv_heads, head_dim, max_splits);
+    // layout inside the array, each part on a 256-byte boundary: counters | maxima and sums | partial outputs
+    const long long counter_bytes = ((long long)tokens * kv_heads * 4 + 255) / 256 * 256;
+    const long long ml_bytes = ((long long)tokens * q_heads * max_splits * 2 * 4 + 255) / 256 * 256;
+    const long long o_bytes = (long long)tokens * q_heads * max_splits * head_dim * 4;
+    const long long needed = counter_bytes + ml_bytes + o_bytes;
+    CELEG_REQUIRE(needed <= kStaticScratchBytes,
+                  "attention_decode_static: this call needs %lld bytes of scratch (tokens=%d q_heads=%d "
+                  "max_splits=%d head_dim=%d), the built-in array holds %lld; use celeg_attention_decode with "
+                  "caller-provided scratch for sizes beyond it", needed, tokens, q_heads, max_splits, head_dim,
+                  kStaticScratchBytes);
+    if (tokens == 0) return 0;
+    void* base = nullptr;
+    const int found = static_scratch_for_current_device(&base);
+    if (found != 0) return found;
+    unsigned char* bytes = static_cast<unsigned char*>(base);
+    int* counters = reinterpret_cast<int*>(bytes);
+    float* partial_ml = reinterpret_cast<float*>(bytes + counter_bytes);
+    float* partial_o = reinterpret_cast<float*>(bytes + counter_bytes + ml_bytes);
+    const cudaError_t cleared = cudaMemsetAsync(counters, 0, (size_t)counter_bytes, stream);
+    CELEG_REQUIRE(cleared == cudaSuccess, "attention_decode_static: clearing the counters failed: %s",
+                  cudaGetErrorString(cleared));
+    return celeg_attention_decode(q, q_row_stride, out, k_cache, v_cache, page_stride, positions, token_span,
+                                  block_table, table_stride, tokens, q_heads, kv_heads, head_dim, page_tokens,
+                                  window, scale, chunk, max_splits, partial_o, partial_ml, counters, error_flag,
+                                  stream);
+}
