@@ -273,6 +273,17 @@ def run_ours(args) -> dict:
     loaded = engine.loaded
     sampler = Sampler(raw["vocab_size"], max_batch, max_batch, engine.device)
 
+    if args.phase == "decode":          # a short run of one phase, for profilers
+        ms, launches, context = time_decode(loaded, sampler, args.batch, args.steps, args.warmup, PROMPT_TOKENS, 1)
+        return {"phase": "decode", "batch": args.batch, "ms_per_step": round(ms, 4),
+                "tokens_per_s": round(args.batch * 1e3 / ms, 1), "gpu_launches": launches,
+                "hbm_frac": round(decode_bytes(raw, args.batch, context) / (ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
+    if args.phase == "prefill":
+        prefill_ms = time_prefill(loaded, args.prefill_tokens, max(1, args.steps), 2)
+        return {"phase": "prefill", "tokens": args.prefill_tokens, "ms": round(prefill_ms, 3),
+                "tokens_per_s": round(args.prefill_tokens * 1e3 / prefill_ms, 1),
+                "frac": round(prefill_flops(raw, args.prefill_tokens) / (prefill_ms * 1e-3)
+                              / (peak["bf16_tflops"] * 1e12), 4)}
     with ClockSampler() as clocks:
         ms, launches, context = time_decode(loaded, sampler, batch, args.steps, args.warmup, PROMPT_TOKENS, 1)
     clock_summary = clocks.summary()
@@ -338,6 +349,10 @@ def main() -> int:
                         help="fewer layers of the same sizes, when memory or time needs it")
     parser.add_argument("--page-tokens", type=int, default=16)
     parser.add_argument("--no-cuda-graph", action="store_true")
+    parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
+                        help="run one phase only and print a short record (for profilers)")
+    parser.add_argument("--batch", type=int, default=8, help="batch of --phase decode")
+    parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of --phase prefill")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

@@ -132,25 +132,52 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(const 
     }
     __syncthreads();
 
-    // weighted sum of values: thread owns (head g, dims c..c+7)
+    // weighted sum of values: the block's threads form `lanes_k` groups that take every lanes_k-th
+    // key; inside a group a thread owns (head g, dims c..c+7). The groups' sums meet in shared
+    // memory (the score rows of heads are no longer needed once every thread has its weights,
+    // but they are read during the loop, so the meeting place is the q area plus the tail).
     const int vecs = d / 8;
-    for (int item = tid; item < group * vecs; item += kDecodeThreads) {
-        const int g = item / vecs, c = (item % vecs) * 8;
-        const float* row = s_s + g * p.chunk;
+    const int items = group * vecs;                       // (head, 8 dims) pairs
+    const int lanes_k = items >= kDecodeThreads ? 1 : kDecodeThreads / items;
+    float* red_s = reinterpret_cast<float*>(off_s + p.chunk);        // [lanes_k][group * d]
+    for (int base_item = 0; base_item < items; base_item += kDecodeThreads) {
+        const int item = base_item + (lanes_k > 1 ? tid % items : tid);
+        const int kg = lanes_k > 1 ? tid / items : 0;
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-        for (int k = 0; k < count; ++k) {
-            float vf[8];
-            bf16x8_to_float(*reinterpret_cast<const uint4*>(p.v_cache + off_s[k] + c), vf);
-            const float w = row[k];
+        const bool active = item < items && kg < lanes_k;
+        const int g = active ? item / vecs : 0, c = active ? (item % vecs) * 8 : 0;
+        if (active) {
+            const float* row = s_s + g * p.chunk;
+#pragma unroll 4
+            for (int k = kg; k < count; k += lanes_k) {
+                float vf[8];
+                bf16x8_to_float(*reinterpret_cast<const uint4*>(p.v_cache + off_s[k] + c), vf);
+                const float w = row[k];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] += w * vf[i];
+                for (int i = 0; i < 8; ++i) acc[i] += w * vf[i];
+            }
+            if (lanes_k > 1) {
+                float* dst = red_s + (size_t)kg * group * d + g * d + c;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dst[i] = acc[i];
+            } else {
+                const int h = kvh * group + g;
+                float* dst = p.partial_o + (((size_t)t * p.q_heads + h) * p.max_splits + split) * d + c;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dst[i] = acc[i];
+            }
         }
-        const int h = kvh * group + g;
-        float* dst = p.partial_o + (((size_t)t * p.q_heads + h) * p.max_splits + split) * d + c;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) dst[i] = acc[i];
+    }
+    if (lanes_k > 1) {
+        __syncthreads();
+        for (int i = tid; i < group * d; i += kDecodeThreads) {
+            float sum = 0.0f;
+            for (int kg = 0; kg < lanes_k; ++kg) sum += red_s[(size_t)kg * group * d + i];
+            const int h = kvh * group + i / d;
+            p.partial_o[(((size_t)t * p.q_heads + h) * p.max_splits + split) * d + i % d] = sum;
+        }
     }
     if (tid < group) {
         const int h = kvh * group + tid;
@@ -222,9 +249,12 @@ CELEG_API int celeg_attention_decode(const void* q, int q_row_stride, void* out,
                   "attention_decode: invalid split chunk=%d max_splits=%d", chunk, max_splits);
     if (tokens == 0) return 0;
     const int group = q_heads / kv_heads;
-    size_t smem = (size_t)(group * head_dim + group * chunk + 1) * sizeof(float) + (size_t)chunk * sizeof(long long);
+    const int items = group * (head_dim / 8);
+    const int lanes_k = items >= kDecodeThreads ? 1 : kDecodeThreads / items;
+    size_t smem = (size_t)(group * head_dim + group * chunk + 1) * sizeof(float) + (size_t)chunk * sizeof(long long) +
+                  (lanes_k > 1 ? (size_t)lanes_k * group * head_dim * sizeof(float) : 0);
     CELEG_REQUIRE(smem <= 200 * 1024, "attention_decode: chunk %d needs %zu bytes of shared memory", chunk, smem);
-    if (smem > 48 * 1024) {
+    if (smem > 40 * 1024) {       // static shared memory counts against the 48 KiB default as well
         const cudaError_t status = cudaFuncSetAttribute(attention_decode_kernel,
                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         CELEG_REQUIRE(status == cudaSuccess, "attention_decode: %s", cudaGetErrorString(status));

@@ -50,6 +50,9 @@ _SIGNATURES = {
     "celeg_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "celeg_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                c_void_p, c_void_p],
     "celeg_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -199,6 +202,22 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_ca
         _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim,
         page_tokens, int(window or 0), scale, chunk, max_splits, _ptr(partial_o), _ptr(partial_ml),
         _ptr(counters), _ptr(error_flag), _stream()))
+
+
+def attention_prefill_supported(q_heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Shapes the tensor-core kernel for prompt portions takes; the rest goes to the general kernel."""
+    return dtype == torch.bfloat16 and q_heads % kv_heads == 0 and head_dim % 8 == 0 and head_dim <= 256
+
+
+def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_cache: torch.Tensor,
+                      v_cache: torch.Tensor, positions: torch.Tensor, span_begin: torch.Tensor,
+                      block_table: torch.Tensor, tokens: int, spans: int, q_heads: int, kv_heads: int,
+                      head_dim: int, page_tokens: int, window: Optional[int], scale: float,
+                      error_flag: torch.Tensor) -> None:
+    _check(library().celeg_attention_prefill(
+        _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
+        _ptr(span_begin), _ptr(block_table), block_table.stride(0), tokens, spans, q_heads, kv_heads, head_dim,
+        page_tokens, int(window or 0), scale, _ptr(error_flag), _stream()))
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, tokens: int, inner: int) -> None:

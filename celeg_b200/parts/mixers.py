@@ -141,6 +141,11 @@ class AttentionMixer:
                                      self.head_dim, b.page_tokens, self.window, self.scale, chunk, max_splits,
                                      partial_o, partial_ml, counters, step.error_flag)
             return
+        if kernels.attention_prefill_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype):
+            kernels.attention_prefill(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
+                                      step.span_begin, table, step.tokens, step.spans, self.heads, self.kv_heads,
+                                      self.head_dim, b.page_tokens, self.window, self.scale, step.error_flag)
+            return
         kernels.attention_generic(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
                                   step.token_span, table, step.tokens, self.heads, self.kv_heads, self.head_dim,
                                   b.page_tokens, self.window, self.scale, step.error_flag)

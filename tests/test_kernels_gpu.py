@@ -340,3 +340,39 @@ def test_attention_decode_split_keys(heads, kv_heads, head_dim, page_tokens, win
         assert int(flag.item()) == 0
         assert int(counters.abs().sum().item()) == 0
         close(out, want, dtype)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (5, 5, 48, 16, None), (8, 2, 64, 64, None),
+    (6, 3, 80, 16, 37), (2, 1, 128, 32, None), (4, 4, 24, 16, 5), (2, 1, 256, 16, None), (4, 1, 112, 16, 100),
+])
+def test_attention_prefill_tensor_cores(heads, kv_heads, head_dim, page_tokens, window):
+    """The same mixed batch as the general kernel's test plus a portion that spans three query
+    tiles and starts in the middle of a page."""
+    from celeg_b200 import kernels
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(9)
+    lengths = [150, 301, 40, 1, 333]             # keys each request has AFTER this step
+    span_len = [70, 1, 2, 1, 150]                # tokens it brings to this step
+    pages = sum((n + page_tokens - 1) // page_tokens for n in lengths) + 5
+    k_cache, v_cache, table, ks, vs = paged_setup(rng, dtype, lengths, kv_heads, head_dim, page_tokens, pages)
+    tokens = sum(span_len)
+    q = rounded(rng.normal(size=(tokens, heads, head_dim)), dtype)
+    positions, token_span, begins = [], [], [0]
+    for r, (n, m) in enumerate(zip(lengths, span_len)):
+        positions += list(range(n - m, n))
+        token_span += [r] * m
+        begins.append(begins[-1] + m)
+    if not window:
+        q[span_len[0]] = rounded(ks[1][3, 0][None, :].repeat(heads, 0) * 3.0, dtype)   # far key 3 dominates
+    scale = head_dim ** -0.5
+    out = torch.zeros((tokens, heads * head_dim), dtype=dtype, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kernels.attention_prefill(dev(q.reshape(tokens, -1), dtype), heads * head_dim, out, k_cache, v_cache,
+                              dev(np.array(positions, dtype=np.int32)), dev(np.array(begins, dtype=np.int32)),
+                              dev(table), tokens, len(lengths), heads, kv_heads, head_dim, page_tokens, window,
+                              scale, flag)
+    assert int(flag.item()) == 0
+    want = np.stack([attention_reference(q[t], ks[token_span[t]], vs[token_span[t]], positions[t], scale, window)
+                     for t in range(tokens)]).reshape(tokens, -1)
+    close(out, want, dtype, scale=1.5)
