@@ -1,0 +1,214 @@
+// Small-batch matrix product for decoding: Y[M,N] = X[M,K] * W[N,K]^T with M <= 16 rows of
+// activations, bfloat16 operands, float32 accumulation. With so few rows the product is bound by
+// reading W once from HBM, so the kernel is organised around that stream:
+//
+//   * W rows are the M dimension of mma.sync.m16n8k16 ("swap A and B"): a block owns 16 weight rows
+//     (32 with the SwiGLU epilogue: 16 gate rows and their 16 up rows), its 8 warps take every
+//     8th 32-element slice of K, and the eight partial tiles meet in shared memory.
+//   * A thread loads 16 contiguous bytes of a weight row straight from global memory into the
+//     registers of two MMAs: because the sum over k may run in any order, the 8 elements a thread
+//     holds are declared to be k-slots {2c,2c+1,2c+8,2c+9} of two successive k16 steps, and the
+//     activation fragment is loaded with the same permutation (also 16 contiguous bytes). No
+//     shared-memory staging and no ldmatrix are needed, and every load is a full 16-byte vector.
+//   * Several slices are in flight per warp (unrolled loads) to cover HBM latency.
+//
+// Epilogues: store (bfloat16 or float32), add into the float32 residual stream, SwiGLU.
+// Any N; K must be a multiple of 8 (16-byte rows); otherwise the caller uses the library product.
+//
+// Counterpart in celeg: bf16_gemv_kernel for M = 1 (include/celeg/backend/cuda/kernels/gemv_kernels.cuh:12-44,
+// one warp per output row, no tensor cores) and cuBLAS for M > 1.
+#include "common.cuh"
+
+namespace celeg_b200 {
+
+constexpr int kGemvWarps = 8;
+constexpr int kGemvThreads = kGemvWarps * 32;
+constexpr int kGemvUnroll = 4;
+
+enum GemvMode : int { kGemvStoreBf16 = 0, kGemvStoreF32 = 1, kGemvAddResidual = 2, kGemvSwiGlu = 3 };
+
+__device__ __forceinline__ uint4 ldg_stream(const void* ptr) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(ptr));
+    return v;
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// MT: 8-row tiles of activations (M <= 8*MT). WT: 16-row tiles of W per block (1, or 2 for SwiGLU).
+template <int MT, int WT, int MODE>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
+                 void* __restrict__ y, int ldy, int m, int n, int k, int second_tile_offset) {
+    __shared__ float partial[kGemvWarps][WT][MT][32][4];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    const int row0 = blockIdx.x * 16;
+
+    // weight rows of this thread: tile t covers rows row0 + t*second_tile_offset + {g, g+8}
+    const __nv_bfloat16* w_lo[WT];
+    const __nv_bfloat16* w_hi[WT];
+#pragma unroll
+    for (int t = 0; t < WT; ++t) {
+        const int base = row0 + t * second_tile_offset;
+        const int r_lo = min(base + g, n - 1 + t * second_tile_offset);     // rows past the end repeat the last one
+        const int r_hi = min(base + g + 8, n - 1 + t * second_tile_offset);
+        w_lo[t] = w + (size_t)r_lo * ldw + c * 8;
+        w_hi[t] = w + (size_t)r_hi * ldw + c * 8;
+    }
+    // activation rows of this thread: tile j covers row j*8 + g (rows past m read row m-1, results unused)
+    const __nv_bfloat16* x_row[MT];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) x_row[j] = x + (size_t)min(j * 8 + g, m - 1) * ldx + c * 8;
+
+    float acc[WT][MT][4];
+#pragma unroll
+    for (int t = 0; t < WT; ++t)
+#pragma unroll
+        for (int j = 0; j < MT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[t][j][e] = 0.0f;
+
+    const int slices = k / 32;                       // full 32-element slices; the tail is handled below
+    for (int s0 = warp; s0 < slices; s0 += kGemvWarps * kGemvUnroll) {
+        uint4 a_lo[kGemvUnroll][WT], a_hi[kGemvUnroll][WT];
+#pragma unroll
+        for (int u = 0; u < kGemvUnroll; ++u) {
+            const int s = s0 + u * kGemvWarps;
+            if (s < slices) {
+#pragma unroll
+                for (int t = 0; t < WT; ++t) {
+                    a_lo[u][t] = ldg_stream(w_lo[t] + s * 32);
+                    a_hi[u][t] = ldg_stream(w_hi[t] + s * 32);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kGemvUnroll; ++u) {
+            const int s = s0 + u * kGemvWarps;
+            if (s < slices) {
+#pragma unroll
+                for (int j = 0; j < MT; ++j) {
+                    const uint4 b = *reinterpret_cast<const uint4*>(x_row[j] + s * 32);
+#pragma unroll
+                    for (int t = 0; t < WT; ++t) {
+                        mma_bf16_16816(acc[t][j], a_lo[u][t].x, a_hi[u][t].x, a_lo[u][t].y, a_hi[u][t].y, b.x, b.y);
+                        mma_bf16_16816(acc[t][j], a_lo[u][t].z, a_hi[u][t].z, a_lo[u][t].w, a_hi[u][t].w, b.z, b.w);
+                    }
+                }
+            }
+        }
+    }
+    // tail of K (k % 32 in {8, 16, 24}): 8-element groups beyond the last full slice, zero-filled
+    const int tail = k - slices * 32;
+    if (tail > 0 && warp == (slices % kGemvWarps)) {
+        const bool have = c * 8 < tail;
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+            const uint4 b = have ? *reinterpret_cast<const uint4*>(x_row[j] + slices * 32) : zero;
+#pragma unroll
+            for (int t = 0; t < WT; ++t) {
+                const uint4 lo = have ? ldg_stream(w_lo[t] + slices * 32) : zero;
+                const uint4 hi = have ? ldg_stream(w_hi[t] + slices * 32) : zero;
+                mma_bf16_16816(acc[t][j], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
+                mma_bf16_16816(acc[t][j], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+            }
+        }
+    }
+
+#pragma unroll
+    for (int t = 0; t < WT; ++t)
+#pragma unroll
+        for (int j = 0; j < MT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) partial[warp][t][j][lane][e] = acc[t][j][e];
+    __syncthreads();
+
+    // 16 x (8*MT) outputs per weight tile; thread `i` sums the 8 warps' partials of one element
+    for (int i = threadIdx.x; i < MT * 128; i += kGemvThreads) {
+        const int j = i / 128, ln = (i % 128) / 4, e = i % 4;
+        float sum[WT];
+#pragma unroll
+        for (int t = 0; t < WT; ++t) {
+            float v = 0.0f;
+#pragma unroll
+            for (int wp = 0; wp < kGemvWarps; ++wp) v += partial[wp][t][j][ln][e];
+            sum[t] = v;
+        }
+        // accumulator element e of lane ln: weight row (ln/4) + 8*(e/2), activation row 2*(ln%4) + (e%2)
+        const int out_col = row0 + (ln >> 2) + ((e >> 1) << 3);
+        const int out_row = j * 8 + ((ln & 3) << 1) + (e & 1);
+        if (out_row >= m || out_col >= n) continue;
+        if (MODE == kGemvStoreBf16) {
+            reinterpret_cast<__nv_bfloat16*>(y)[(size_t)out_row * ldy + out_col] = __float2bfloat16_rn(sum[0]);
+        } else if (MODE == kGemvStoreF32) {
+            reinterpret_cast<float*>(y)[(size_t)out_row * ldy + out_col] = sum[0];
+        } else if (MODE == kGemvAddResidual) {
+            float* dst = reinterpret_cast<float*>(y) + (size_t)out_row * ldy + out_col;
+            *dst += sum[0];
+        } else {
+            // the product with the up projection uses the gate as it would be stored: one rounding
+            // each, as when the two halves are written by a plain product and read back
+            const float gate = __bfloat162float(__float2bfloat16_rn(sum[0]));
+            const float up = __bfloat162float(__float2bfloat16_rn(sum[WT - 1]));
+            reinterpret_cast<__nv_bfloat16*>(y)[(size_t)out_row * ldy + out_col] =
+                __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+        }
+    }
+}
+
+template <int MT>
+static int launch_gemv(int mode, const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw, void* y, int ldy,
+                       int m, int n, int k, cudaStream_t stream) {
+    const int blocks = (n + 15) / 16;
+    switch (mode) {
+        case kGemvStoreBf16:
+            gemv_bf16_kernel<MT, 1, kGemvStoreBf16><<<blocks, kGemvThreads, 0, stream>>>(x, ldx, w, ldw, y, ldy, m, n, k, 0);
+            break;
+        case kGemvStoreF32:
+            gemv_bf16_kernel<MT, 1, kGemvStoreF32><<<blocks, kGemvThreads, 0, stream>>>(x, ldx, w, ldw, y, ldy, m, n, k, 0);
+            break;
+        case kGemvAddResidual:
+            gemv_bf16_kernel<MT, 1, kGemvAddResidual><<<blocks, kGemvThreads, 0, stream>>>(x, ldx, w, ldw, y, ldy, m, n, k, 0);
+            break;
+        case kGemvSwiGlu:
+            // n = inner width; rows [0, n) are the gate, rows [n, 2n) the up projection
+            gemv_bf16_kernel<MT, 2, kGemvSwiGlu><<<blocks, kGemvThreads, 0, stream>>>(x, ldx, w, ldw, y, ldy, m, n, k, n);
+            break;
+        default:
+            set_error("gemv_bf16: unknown mode %d", mode);
+            return -1;
+    }
+    return check_launch("gemv_bf16");
+}
+
+}  // namespace celeg_b200
+
+using namespace celeg_b200;
+
+// mode 0: y bf16 [m, n] = x w^T; 1: y float32; 2: y float32 += x w^T; 3: w is [2n, k] (gate rows then up
+// rows), y bf16 [m, n] = silu(x gate^T) * (x up^T).
+CELEG_API int celeg_gemv_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int m, int n, int k,
+                              int mode, cudaStream_t stream) {
+    CELEG_REQUIRE(m >= 0 && n > 0 && k > 0, "gemv_bf16: invalid sizes m=%d n=%d k=%d", m, n, k);
+    CELEG_REQUIRE(m <= 16, "gemv_bf16: %d activation rows exceed 16; use the library product", m);
+    CELEG_REQUIRE(k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
+                  "gemv_bf16: k=%d, ldx=%d and ldw=%d must be multiples of 8 (16-byte rows)", k, ldx, ldw);
+    CELEG_REQUIRE(ldx >= k && ldw >= k && ldy >= n, "gemv_bf16: leading dimensions ldx=%d ldw=%d ldy=%d too small",
+                  ldx, ldw, ldy);
+    CELEG_REQUIRE((((size_t)x | (size_t)w) & 15) == 0, "gemv_bf16: operands must be 16-byte aligned");
+    if (m == 0) return 0;
+    const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+    const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
+    if (m <= 8) return launch_gemv<1>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, stream);
+    return launch_gemv<2>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, stream);
+}

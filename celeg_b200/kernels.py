@@ -53,6 +53,7 @@ _SIGNATURES = {
     "celeg_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                 c_void_p, c_void_p],
+    "celeg_gemv_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -218,6 +219,29 @@ def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_c
         _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
         _ptr(span_begin), _ptr(block_table), block_table.stride(0), tokens, spans, q_heads, kv_heads, head_dim,
         page_tokens, int(window or 0), scale, _ptr(error_flag), _stream()))
+
+
+GEMV_MAX_ROWS = 16
+GEMV_STORE, GEMV_STORE_F32, GEMV_ADD_RESIDUAL, GEMV_SWIGLU = 0, 1, 2, 3
+
+
+def gemv_supported(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (0 < rows <= GEMV_MAX_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_STORE) -> None:
+    """y[:rows] = x[:rows] @ w.T for at most 16 rows, streaming w once. mode GEMV_STORE: y bfloat16;
+    GEMV_STORE_F32: y float32; GEMV_ADD_RESIDUAL: y float32, accumulated; GEMV_SWIGLU: w is
+    [2*inner, k] (gate rows, then up rows) and y bfloat16 [rows, inner] = silu(gate) * up."""
+    n = w.shape[0] // 2 if mode == GEMV_SWIGLU else w.shape[0]
+    k = w.shape[1]
+    assert x.shape[-1] == k and y.shape[-1] >= n
+    want = torch.bfloat16 if mode in (GEMV_STORE, GEMV_SWIGLU) else torch.float32
+    if y.dtype != want:
+        raise KernelLibraryError(f"gemv_bf16 mode {mode} writes {want}, got {y.dtype}")
+    _check(library().celeg_gemv_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(y), y.stride(0), rows, n, k,
+                                     mode, _stream()))
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, tokens: int, inner: int) -> None:

@@ -31,6 +31,5 @@ class SwiGluFeedForward:
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
         rt, t = self.rt, step.tokens
-        rt.linear(x, self.w_gate_up, self.gate_up, t)
-        kernels.swiglu(self.gate_up, self.activated, t, self.inner)
+        rt.linear_swiglu(x, self.w_gate_up, self.gate_up, self.activated, t, self.inner)
         rt.linear(self.activated, self.w_down, out, t)

@@ -63,10 +63,27 @@ class Runtime:
             return
         if self.act_dtype == torch.float32:
             kernels.gemm_f32(x, weight, out, rows)
+        elif kernels.gemv_supported(rows, x, weight):
+            # few rows: this package's weight-streaming kernel (celeg: its own GEMV for one row)
+            kernels.gemv_bf16(x, weight, out, rows,
+                              kernels.GEMV_STORE_F32 if out.dtype == torch.float32 else kernels.GEMV_STORE)
         elif out.dtype == torch.float32:
             torch.mm(x[:rows], weight.t(), out_dtype=torch.float32, out=out[:rows])
         else:
             torch.mm(x[:rows], weight.t(), out=out[:rows])
+
+
+    def linear_swiglu(self, x: torch.Tensor, gate_up_weight: torch.Tensor, scratch: torch.Tensor,
+                      out: torch.Tensor, rows: int, inner: int) -> None:
+        """out[:rows] = silu(x gate^T) * (x up^T) with gate_up_weight = [gate rows; up rows]. Few
+        bfloat16 rows: one kernel; otherwise the product into ``scratch`` and the activation kernel."""
+        if rows == 0:
+            return
+        if self.act_dtype == torch.bfloat16 and kernels.gemv_supported(rows, x, gate_up_weight):
+            kernels.gemv_bf16(x, gate_up_weight, out, rows, kernels.GEMV_SWIGLU)
+            return
+        self.linear(x, gate_up_weight, scratch, rows)
+        kernels.swiglu(scratch, out, rows, inner)
 
 
 @dataclass

@@ -376,3 +376,32 @@ def test_attention_prefill_tensor_cores(heads, kv_heads, head_dim, page_tokens, 
     want = np.stack([attention_reference(q[t], ks[token_span[t]], vs[token_span[t]], positions[t], scale, window)
                      for t in range(tokens)]).reshape(tokens, -1)
     close(out, want, dtype, scale=1.5)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (8, 2048, 2048), (3, 70, 136), (8, 100, 8200), (16, 48, 520),
+                                   (11, 1000, 96), (5, 33, 24), (2, 16, 8)])
+def test_gemv_bf16_modes(m, n, k):
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(10)
+    x = rounded(rng.normal(size=(m, k)), torch.bfloat16)
+    w = rounded(rng.normal(size=(n, k)) * 0.1, torch.bfloat16)
+    want = x @ w.T
+    x_dev, w_dev = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    assert kernels.gemv_supported(m, x_dev, w_dev)
+    y = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    kernels.gemv_bf16(x_dev, w_dev, y, m, kernels.GEMV_STORE)
+    close(y, want, torch.bfloat16)
+    y32 = torch.full((m, n), 7.0, dtype=torch.float32, device="cuda")
+    kernels.gemv_bf16(x_dev, w_dev, y32, m, kernels.GEMV_STORE_F32)
+    close(y32, want, torch.float32, scale=50 * math.sqrt(k))       # products are exact, sums are float32
+    before = rng.normal(size=(m, n)).astype(np.float32)
+    res = dev(before)
+    kernels.gemv_bf16(x_dev, w_dev, res, m, kernels.GEMV_ADD_RESIDUAL)
+    close(res, before.astype(np.float64) + want, torch.float32, scale=50 * math.sqrt(k))
+    if n % 2 == 0:
+        inner = n // 2
+        act = torch.zeros((m, inner), dtype=torch.bfloat16, device="cuda")
+        kernels.gemv_bf16(x_dev, w_dev, act, m, kernels.GEMV_SWIGLU)
+        gate = rounded(want[:, :inner], torch.bfloat16)
+        up = rounded(want[:, inner:], torch.bfloat16)
+        close(act, gate / (1 + np.exp(-gate)) * up, torch.bfloat16, scale=2.0)
