@@ -52,6 +52,8 @@ __device__ __forceinline__ void bf16x8_to_float(const uint4& raw, float* f) {
 
 __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    chain_release();
+    chain_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int group = p.q_heads / p.kv_heads;
@@ -283,7 +285,7 @@ CELEG_API int celeg_attention_decode(const void* q, int q_row_stride, void* out,
     p.counters = counters;
     p.error_flag = error_flag;
     dim3 grid(max_splits, kv_heads, tokens);
-    attention_decode_kernel<<<grid, kDecodeThreads, smem, stream>>>(p);
+    launch_chained(attention_decode_kernel, grid, kDecodeThreads, smem, stream, p);
     return check_launch("attention_decode");
 }
 

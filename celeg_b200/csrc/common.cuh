@@ -49,9 +49,44 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return scratch[32];
 }
 
+// Programmatic dependent launch. A kernel launched through launch_chained() may start while its
+// predecessor in the stream is still running; it must call chain_wait() before it reads anything
+// a predecessor wrote and before it writes anything a predecessor may still read (only constant
+// data such as weights may be touched earlier). chain_release() lets the successor start
+// launching; the successor's chain_wait() still returns only when this whole grid has finished
+// and its writes are visible, so releasing early is always safe.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;"); }
+
 // Host side: the last error text of this library (thread local).
 void set_error(const char* format, ...);
 int check_launch(const char* what);
+bool chaining_enabled(int kernel_class = 2);
+enum ChainClass : int { kChainGemv = 0, kChainNorm = 1, kChainOther = 2 };
+
+// Launch with the programmatic-serialization attribute (when enabled), so that the kernel's
+// prologue overlaps the tail of the kernel before it. Works under stream capture as well.
+template <typename... KernelArgs, typename... Args>
+inline void launch_chained_class(int kernel_class, void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                                 size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = chaining_enabled(kernel_class) ? 1 : 0;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
+template <typename... KernelArgs, typename... Args>
+inline void launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                           Args&&... args) {
+    launch_chained_class(kChainOther, kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
+}
 
 }  // namespace celeg_b200
 

@@ -6,8 +6,10 @@
 namespace celeg_b200 {
 
 template <typename W>
-__global__ void embedding_kernel(const W* __restrict__ table, const int* __restrict__ tokens,
-                                 float* __restrict__ out, int hidden, int vocab, float multiplier) {
+__global__ void embedding_kernel(const W* __restrict__ table, const int* tokens,
+                                 float* out, int hidden, int vocab, float multiplier) {
+    chain_release();
+    chain_wait();
     const int row = blockIdx.x;
     const int token = tokens[row];
     float* dst = out + (size_t)row * hidden;
@@ -30,11 +32,11 @@ CELEG_API int celeg_embedding(const void* table, int table_dtype, const int* tok
     if (rows == 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == kFloat32)
-        embedding_kernel<float><<<rows, threads, 0, stream>>>((const float*)table, tokens, out, hidden, vocab,
-                                                              multiplier);
+        launch_chained(embedding_kernel<float>, rows, threads, 0, stream, (const float*)table, tokens, out, hidden,
+                       vocab, multiplier);
     else if (table_dtype == kBFloat16)
-        embedding_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out,
-                                                                      hidden, vocab, multiplier);
+        launch_chained(embedding_kernel<__nv_bfloat16>, rows, threads, 0, stream, (const __nv_bfloat16*)table,
+                       tokens, out, hidden, vocab, multiplier);
     else
         CELEG_REQUIRE(false, "embedding: unknown dtype code %d", table_dtype);
     return check_launch("embedding");

@@ -35,6 +35,16 @@ __device__ __forceinline__ uint4 ldg_stream(const void* ptr) {
     return v;
 }
 
+// Activations are written by the kernel before this one: the load is a volatile asm so that the
+// compiler cannot move it above the wait for that kernel.
+__device__ __forceinline__ uint4 ld_activation(const void* ptr) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(ptr));
+    return v;
+}
+
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                                unsigned b0, unsigned b1) {
     asm volatile(
@@ -46,7 +56,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsig
 // MT: 8-row tiles of activations (M <= 8*MT). WT: 16-row tiles of W per block (1, or 2 for SwiGLU).
 template <int MT, int WT, int MODE>
 __global__ void __launch_bounds__(kGemvThreads)
-gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
+gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
                  void* __restrict__ y, int ldy, int m, int n, int k, int second_tile_offset) {
     __shared__ float partial[kGemvWarps][WT][MT][32][4];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -78,6 +88,8 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
             for (int e = 0; e < 4; ++e) acc[t][j][e] = 0.0f;
 
     const int slices = k / 32;                       // full 32-element slices; the tail is handled below
+    chain_release();
+    bool waited = false;
     for (int s0 = warp; s0 < slices; s0 += kGemvWarps * kGemvUnroll) {
         uint4 a_lo[kGemvUnroll][WT], a_hi[kGemvUnroll][WT];
 #pragma unroll
@@ -91,22 +103,39 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
                 }
             }
         }
+        // the first batch of weights (constant data) is already on its way when the kernel starts
+        // to wait for the activations of the kernel before it
+        if (!waited) {
+            chain_wait();
+            waited = true;
+        }
+        uint4 b[kGemvUnroll][MT];
+#pragma unroll
+        for (int u = 0; u < kGemvUnroll; ++u) {
+            const int s = s0 + u * kGemvWarps;
+            if (s < slices) {
+#pragma unroll
+                for (int j = 0; j < MT; ++j) b[u][j] = ld_activation(x_row[j] + s * 32);
+            }
+        }
 #pragma unroll
         for (int u = 0; u < kGemvUnroll; ++u) {
             const int s = s0 + u * kGemvWarps;
             if (s < slices) {
 #pragma unroll
                 for (int j = 0; j < MT; ++j) {
-                    const uint4 b = *reinterpret_cast<const uint4*>(x_row[j] + s * 32);
 #pragma unroll
                     for (int t = 0; t < WT; ++t) {
-                        mma_bf16_16816(acc[t][j], a_lo[u][t].x, a_hi[u][t].x, a_lo[u][t].y, a_hi[u][t].y, b.x, b.y);
-                        mma_bf16_16816(acc[t][j], a_lo[u][t].z, a_hi[u][t].z, a_lo[u][t].w, a_hi[u][t].w, b.z, b.w);
+                        mma_bf16_16816(acc[t][j], a_lo[u][t].x, a_hi[u][t].x, a_lo[u][t].y, a_hi[u][t].y, b[u][j].x,
+                                       b[u][j].y);
+                        mma_bf16_16816(acc[t][j], a_lo[u][t].z, a_hi[u][t].z, a_lo[u][t].w, a_hi[u][t].w, b[u][j].z,
+                                       b[u][j].w);
                     }
                 }
             }
         }
     }
+    if (!waited) chain_wait();
     // tail of K (k % 32 in {8, 16, 24}): 8-element groups beyond the last full slice, zero-filled
     const int tail = k - slices * 32;
     if (tail > 0 && warp == (slices % kGemvWarps)) {
@@ -114,7 +143,7 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
         const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
-            const uint4 b = have ? *reinterpret_cast<const uint4*>(x_row[j] + slices * 32) : zero;
+            const uint4 b = have ? ld_activation(x_row[j] + slices * 32) : zero;
 #pragma unroll
             for (int t = 0; t < WT; ++t) {
                 const uint4 lo = have ? ldg_stream(w_lo[t] + slices * 32) : zero;
@@ -172,17 +201,17 @@ static int launch_gemv(int mode, const __nv_bfloat16* x, int ldx, const __nv_bfl
     const int blocks = (n + 15) / 16;
     switch (mode) {
         case kGemvStoreBf16:
-            gemv_bf16_kernel<MT, 1, kGemvStoreBf16><<<blocks, kGemvThreads, 0, stream>>>(x, ldx, w, ldw, y, ldy, m, n, k, 0);
+            launch_chained_class(kChainGemv, gemv_bf16_kernel<MT, 1, kGemvStoreBf16>, blocks, kGemvThreads, 0, stream, x, ldx, w, ldw, y, ldy, m, n, k, 0);
             break;
         case kGemvStoreF32:
-            gemv_bf16_kernel<MT, 1, kGemvStoreF32><<<blocks, kGemvThreads, 0, stream>>>(x, ldx, w, ldw, y, ldy, m, n, k, 0);
+            launch_chained_class(kChainGemv, gemv_bf16_kernel<MT, 1, kGemvStoreF32>, blocks, kGemvThreads, 0, stream, x, ldx, w, ldw, y, ldy, m, n, k, 0);
             break;
         case kGemvAddResidual:
-            gemv_bf16_kernel<MT, 1, kGemvAddResidual><<<blocks, kGemvThreads, 0, stream>>>(x, ldx, w, ldw, y, ldy, m, n, k, 0);
+            launch_chained_class(kChainGemv, gemv_bf16_kernel<MT, 1, kGemvAddResidual>, blocks, kGemvThreads, 0, stream, x, ldx, w, ldw, y, ldy, m, n, k, 0);
             break;
         case kGemvSwiGlu:
             // n = inner width; rows [0, n) are the gate, rows [n, 2n) the up projection
-            gemv_bf16_kernel<MT, 2, kGemvSwiGlu><<<blocks, kGemvThreads, 0, stream>>>(x, ldx, w, ldw, y, ldy, m, n, k, n);
+            launch_chained_class(kChainGemv, gemv_bf16_kernel<MT, 2, kGemvSwiGlu>, blocks, kGemvThreads, 0, stream, x, ldx, w, ldw, y, ldy, m, n, k, n);
             break;
         default:
             set_error("gemv_bf16: unknown mode %d", mode);

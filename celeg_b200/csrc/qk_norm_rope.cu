@@ -18,15 +18,17 @@ namespace celeg_b200 {
 constexpr int kMaxHeadDim = 512;
 
 template <typename A>
-__global__ void qk_norm_rope_store_kernel(A* __restrict__ qkv, const float* __restrict__ q_weight,
+__global__ void qk_norm_rope_store_kernel(A* qkv, const float* __restrict__ q_weight,
                                           const float* __restrict__ k_weight,
-                                          const float* __restrict__ inv_freq, const int* __restrict__ positions,
-                                          const int* __restrict__ token_span,
-                                          const int* __restrict__ block_table, int table_stride,
-                                          A* __restrict__ k_cache, A* __restrict__ v_cache,
+                                          const float* __restrict__ inv_freq, const int* positions,
+                                          const int* token_span,
+                                          const int* block_table, int table_stride,
+                                          A* k_cache, A* v_cache,
                                           long long page_stride, int tokens, int q_heads, int kv_heads,
                                           int head_dim, int rotary_dim, int page_tokens, float eps,
-                                          int store_kv, int* __restrict__ error_flag) {
+                                          int store_kv, int* error_flag) {
+    chain_release();
+    chain_wait();
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const int heads = q_heads + 2 * kv_heads;
@@ -117,12 +119,12 @@ CELEG_API int celeg_qk_norm_rope_store(void* qkv, const float* q_weight, const f
     const unsigned blocks = (unsigned)((units + warps - 1) / warps);
     if (!inv_freq) rotary_dim = head_dim & ~1;       // without rotation the pair loop just normalises
     if (act_dtype == kFloat32)
-        qk_norm_rope_store_kernel<float><<<blocks, warps * 32, 0, stream>>>(
+        launch_chained(qk_norm_rope_store_kernel<float>, blocks, warps * 32, 0, stream,
             (float*)qkv, q_weight, k_weight, inv_freq, positions, token_span, block_table, table_stride,
             (float*)k_cache, (float*)v_cache, page_stride, tokens, q_heads, kv_heads, head_dim, rotary_dim,
             page_tokens, eps, store_kv, error_flag);
     else if (act_dtype == kBFloat16)
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>(
+        launch_chained(qk_norm_rope_store_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream,
             (__nv_bfloat16*)qkv, q_weight, k_weight, inv_freq, positions, token_span, block_table, table_stride,
             (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_stride, tokens, q_heads, kv_heads, head_dim,
             rotary_dim, page_tokens, eps, store_kv, error_flag);

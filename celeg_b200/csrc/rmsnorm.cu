@@ -12,10 +12,12 @@
 namespace celeg_b200 {
 
 template <typename A>
-__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const A* __restrict__ delta,
-                                   const float* __restrict__ weight, A* __restrict__ out,
-                                   const int* __restrict__ rows, int width, float eps, int write_residual) {
+__global__ void add_rmsnorm_kernel(float* residual, const A* delta,
+                                   const float* __restrict__ weight, A* out,
+                                   const int* rows, int width, float eps, int write_residual) {
     __shared__ float scratch[33];
+    chain_release();
+    chain_wait();
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
     float* res = residual + (size_t)r * width;
@@ -40,8 +42,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const A* __rest
 // Plain RMSNorm over rows of `width` elements of an activation tensor (used for parts that
 // normalise something other than the residual stream).
 template <typename A>
-__global__ void rmsnorm_rows_kernel(const A* __restrict__ in, const float* __restrict__ weight,
-                                    A* __restrict__ out, int width, float eps) {
+__global__ void rmsnorm_rows_kernel(const A* in, const float* __restrict__ weight,
+                                    A* out, int width, float eps) {
     __shared__ float scratch[33];
     const A* src = in + (size_t)blockIdx.x * width;
     float sum = 0.0f;
@@ -71,11 +73,11 @@ CELEG_API int celeg_add_rmsnorm(float* residual, const void* delta, const float*
     if (n_rows == 0) return 0;
     const int threads = norm_threads(width);
     if (act_dtype == kFloat32)
-        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(residual, (const float*)delta, weight,
-                                                                  (float*)out, rows, width, eps, write_residual);
+        launch_chained_class(kChainNorm, add_rmsnorm_kernel<float>, n_rows, threads, 0, stream, residual, (const float*)delta,
+                       weight, (float*)out, rows, width, eps, write_residual);
     else if (act_dtype == kBFloat16)
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
-            residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, width, eps, write_residual);
+        launch_chained_class(kChainNorm, add_rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, residual,
+                       (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, width, eps, write_residual);
     else
         CELEG_REQUIRE(false, "add_rmsnorm: unknown dtype code %d", act_dtype);
     return check_launch("add_rmsnorm");

@@ -57,14 +57,16 @@ __device__ __forceinline__ float penalised(const float* logits, const uint8_t* s
     return v;
 }
 
-__global__ void sample_kernel(const float* __restrict__ logits, long long ld, int vocab,
-                              const int* __restrict__ row_slot, uint8_t* __restrict__ seen_base,
-                              unsigned long long* __restrict__ rng, const float* __restrict__ temperature,
-                              const int* __restrict__ top_k, const float* __restrict__ top_p,
-                              const float* __restrict__ penalty, int* __restrict__ out) {
+__global__ void sample_kernel(const float* logits, long long ld, int vocab,
+                              const int* row_slot, uint8_t* seen_base,
+                              unsigned long long* rng, const float* temperature,
+                              const int* top_k, const float* top_p,
+                              const float* penalty, int* out) {
     __shared__ Best scratch[33];
     __shared__ float cand_score[kMaxTopK];
     __shared__ int cand_token[kMaxTopK];
+    chain_release();
+    chain_wait();
     const int row = blockIdx.x;
     const float* l = logits + (size_t)row * ld;
     const int slot = row_slot ? row_slot[row] : row;
@@ -149,8 +151,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ld, in
 }
 
 // Marks the tokens of a step as seen by their requests: slot = span_slot[token_span[i]].
-__global__ void mark_seen_kernel(uint8_t* __restrict__ seen_base, int vocab, const int* __restrict__ tokens,
-                                 const int* __restrict__ token_span, const int* __restrict__ span_slot,
+__global__ void mark_seen_kernel(uint8_t* seen_base, int vocab, const int* tokens,
+                                 const int* token_span, const int* span_slot,
                                  int count) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
@@ -170,8 +172,8 @@ CELEG_API int celeg_sample(const float* logits, long long ld, int vocab, int row
     CELEG_REQUIRE(rng != nullptr || temperature == nullptr, "sample: temperature sampling needs generator states");
     if (rows == 0) return 0;
     const int threads = vocab >= 16384 ? 1024 : 256;
-    sample_kernel<<<rows, threads, 0, stream>>>(logits, ld, vocab, row_slot, seen, rng, temperature, top_k, top_p,
-                                                penalty, out);
+    launch_chained(sample_kernel, rows, threads, 0, stream, logits, ld, vocab, row_slot, seen, rng, temperature,
+                   top_k, top_p, penalty, out);
     return check_launch("sample");
 }
 

@@ -26,18 +26,20 @@ namespace celeg_b200 {
 constexpr int kMaxTaps = 16;
 
 template <typename A>
-__global__ void short_conv_kernel(const A* __restrict__ proj, const float* __restrict__ kernel,
-                                  float* __restrict__ state, long long slot_stride, A* __restrict__ out,
-                                  const int* __restrict__ token_span, const int* __restrict__ span_begin,
-                                  const int* __restrict__ span_slot, int tokens, int spans, int hidden,
+__global__ void short_conv_kernel(const A* proj, const float* __restrict__ kernel,
+                                  float* state, long long slot_stride, A* out,
+                                  const int* token_span, const int* span_begin,
+                                  const int* span_slot, int tokens, int spans, int hidden,
                                   int taps) {
+    chain_release();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= hidden) return;
     const int y = blockIdx.y;
     const size_t row = (size_t)3 * hidden;
     float w[kMaxTaps];
 #pragma unroll
-    for (int i = 0; i < kMaxTaps; ++i) w[i] = i < taps ? kernel[(size_t)c * taps + i] : 0.0f;
+    for (int i = 0; i < kMaxTaps; ++i) w[i] = i < taps ? kernel[(size_t)c * taps + i] : 0.0f;   // constant data
+    chain_wait();
 
     if (y < tokens) {
         const int t = y;
@@ -107,13 +109,12 @@ CELEG_API int celeg_short_conv(const void* proj, const float* kernel, float* sta
     const int threads = hidden >= 256 ? 256 : ((hidden + 31) / 32) * 32;
     dim3 grid((hidden + threads - 1) / threads, tokens + spans);
     if (act_dtype == kFloat32)
-        short_conv_kernel<float><<<grid, threads, 0, stream>>>((const float*)proj, kernel, state, slot_stride,
-                                                               (float*)out, token_span, span_begin, span_slot,
-                                                               tokens, spans, hidden, taps);
+        launch_chained(short_conv_kernel<float>, grid, threads, 0, stream, (const float*)proj, kernel, state,
+                       slot_stride, (float*)out, token_span, span_begin, span_slot, tokens, spans, hidden, taps);
     else if (act_dtype == kBFloat16)
-        short_conv_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-            (const __nv_bfloat16*)proj, kernel, state, slot_stride, (__nv_bfloat16*)out, token_span, span_begin,
-            span_slot, tokens, spans, hidden, taps);
+        launch_chained(short_conv_kernel<__nv_bfloat16>, grid, threads, 0, stream, (const __nv_bfloat16*)proj,
+                       kernel, state, slot_stride, (__nv_bfloat16*)out, token_span, span_begin, span_slot, tokens,
+                       spans, hidden, taps);
     else
         CELEG_REQUIRE(false, "short_conv: unknown dtype code %d", act_dtype);
     return check_launch("short_conv");

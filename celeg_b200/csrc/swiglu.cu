@@ -7,7 +7,9 @@
 namespace celeg_b200 {
 
 template <typename A>
-__global__ void swiglu_kernel(const A* __restrict__ in, A* __restrict__ out, long long total, int inner) {
+__global__ void swiglu_kernel(const A* in, A* out, long long total, int inner) {
+    chain_release();
+    chain_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
         const long long t = idx / inner;
@@ -32,10 +34,11 @@ CELEG_API int celeg_swiglu(const void* gate_up, void* out, int tokens, int inner
     const unsigned blocks = (unsigned)((total + threads - 1) / threads < 148LL * 16 ? (total + threads - 1) / threads
                                                                                       : 148LL * 16);
     if (act_dtype == kFloat32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, inner);
+        launch_chained(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total,
+                       inner);
     else if (act_dtype == kBFloat16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up,
-                                                                     (__nv_bfloat16*)out, total, inner);
+        launch_chained(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up,
+                       (__nv_bfloat16*)out, total, inner);
     else
         CELEG_REQUIRE(false, "swiglu: unknown dtype code %d", act_dtype);
     return check_launch("swiglu");
