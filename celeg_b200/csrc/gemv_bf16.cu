@@ -12,8 +12,14 @@
 //     shared-memory staging and no ldmatrix are needed, and every load is a full 16-byte vector.
 //   * Several slices are in flight per warp (unrolled loads) to cover HBM latency.
 //
-// Epilogues: store (bfloat16 or float32), add into the float32 residual stream, SwiGLU.
-// Any N; K must be a multiple of 8 (16-byte rows); otherwise the caller uses the library product.
+// Epilogues: store (bfloat16 or float32), add into the float32 residual stream, SwiGLU, and the short
+// convolution's gate (three weight tiles per block: the B, C and X rows of the same 16 channels of the
+// input projection; bx = B*X, taps over the request's carried state, C * conv, state shifted; for steps
+// in which every request brings ONE token).
+// The number of warps per block (8, 16 or 32, all on the same 16 weight rows) is chosen by the host:
+// a narrow matrix has few blocks, and only more warps per block put enough loads in flight to keep
+// HBM busy. Any N; K must be a multiple of 8 (16-byte rows); otherwise the caller uses the library
+// product.
 //
 // Counterpart in celeg: bf16_gemv_kernel for M = 1 (include/celeg/backend/cuda/kernels/gemv_kernels.cuh:12-44,
 // one warp per output row, no tensor cores) and cuBLAS for M > 1.
@@ -21,11 +27,17 @@
 
 namespace celeg_b200 {
 
-constexpr int kGemvWarps = 8;
-constexpr int kGemvThreads = kGemvWarps * 32;
-constexpr int kGemvUnroll = 4;
+constexpr int kGemvMaxConvTaps = 16;
 
-enum GemvMode : int { kGemvStoreBf16 = 0, kGemvStoreF32 = 1, kGemvAddResidual = 2, kGemvSwiGlu = 3 };
+enum GemvMode : int { kGemvStoreBf16 = 0, kGemvStoreF32 = 1, kGemvAddResidual = 2, kGemvSwiGlu = 3, kGemvConv = 4 };
+
+struct GemvConvArgs {
+    const float* conv_w;         // [channels, taps]
+    int taps;
+    float* state;                // this layer's state inside slot 0: [taps-1][channels] per slot
+    long long slot_stride;
+    const int* span_slot;        // state slot of row i (row i is the single token of span i)
+};
 
 __device__ __forceinline__ uint4 ldg_stream(const void* ptr) {
     uint4 v;
@@ -54,11 +66,13 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsig
 }
 
 // MT: 8-row tiles of activations (M <= 8*MT). WT: 16-row tiles of W per block (1, or 2 for SwiGLU).
-template <int MT, int WT, int MODE>
-__global__ void __launch_bounds__(kGemvThreads)
+template <int MT, int WT, int MODE, int kGemvUnroll, int kGemvWarps>
+__global__ void __launch_bounds__(kGemvWarps * 32)
 gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
-                 void* __restrict__ y, int ldy, int m, int n, int k, int second_tile_offset) {
-    __shared__ float partial[kGemvWarps][WT][MT][32][4];
+                 void* __restrict__ y, int ldy, int m, int n, int k, int second_tile_offset, GemvConvArgs conv) {
+    constexpr int kGemvThreads = kGemvWarps * 32;
+    extern __shared__ __align__(16) float partial_raw[];
+    float (*partial)[WT][MT][32][4] = reinterpret_cast<float (*)[WT][MT][32][4]>(partial_raw);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, c = lane & 3;
     const int row0 = blockIdx.x * 16;
@@ -184,6 +198,25 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
         } else if (MODE == kGemvAddResidual) {
             float* dst = reinterpret_cast<float*>(y) + (size_t)out_row * ldy + out_col;
             *dst += sum[0];
+        } else if (MODE == kGemvConv) {
+            // B, C, X as a plain product would store them (one rounding each), then the span kernel's
+            // arithmetic in the same order, so that both ways give the same bits
+            const float bb = __bfloat162float(__float2bfloat16_rn(sum[0]));
+            const float cc = __bfloat162float(__float2bfloat16_rn(sum[WT >= 3 ? 1 : 0]));
+            const float xx = __bfloat162float(__float2bfloat16_rn(sum[WT - 1]));
+            const float bx = bb * xx;
+            const int keep = conv.taps - 1;
+            float* st = conv.state + (size_t)conv.span_slot[out_row] * conv.slot_stride + out_col;   // [keep][n]
+            const float* cw = conv.conv_w + (size_t)out_col * conv.taps;
+            float history[kGemvMaxConvTaps];
+#pragma unroll
+            for (int tp = 0; tp < kGemvMaxConvTaps; ++tp) history[tp] = tp < keep ? st[(size_t)tp * n] : 0.0f;
+            float acc_conv = 0.0f;
+            for (int tp = 0; tp < keep; ++tp) acc_conv += cw[tp] * history[tp];
+            acc_conv += cw[keep] * bx;
+            reinterpret_cast<__nv_bfloat16*>(y)[(size_t)out_row * ldy + out_col] = __float2bfloat16_rn(cc * acc_conv);
+            for (int tp = 0; tp + 1 < keep; ++tp) st[(size_t)tp * n] = history[tp + 1];
+            if (keep > 0) st[(size_t)(keep - 1) * n] = bx;
         } else {
             // the product with the up projection uses the gate as it would be stored: one rounding
             // each, as when the two halves are written by a plain product and read back
@@ -195,39 +228,60 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
     }
 }
 
-template <int MT>
-static int launch_gemv(int mode, const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw, void* y, int ldy,
-                       int m, int n, int k, cudaStream_t stream) {
-    const int blocks = (n + 15) / 16;
-    switch (mode) {
-        case kGemvStoreBf16:
-            launch_chained_class(kChainGemv, gemv_bf16_kernel<MT, 1, kGemvStoreBf16>, blocks, kGemvThreads, 0, stream, x, ldx, w, ldw, y, ldy, m, n, k, 0);
-            break;
-        case kGemvStoreF32:
-            launch_chained_class(kChainGemv, gemv_bf16_kernel<MT, 1, kGemvStoreF32>, blocks, kGemvThreads, 0, stream, x, ldx, w, ldw, y, ldy, m, n, k, 0);
-            break;
-        case kGemvAddResidual:
-            launch_chained_class(kChainGemv, gemv_bf16_kernel<MT, 1, kGemvAddResidual>, blocks, kGemvThreads, 0, stream, x, ldx, w, ldw, y, ldy, m, n, k, 0);
-            break;
-        case kGemvSwiGlu:
-            // n = inner width; rows [0, n) are the gate, rows [n, 2n) the up projection
-            launch_chained_class(kChainGemv, gemv_bf16_kernel<MT, 2, kGemvSwiGlu>, blocks, kGemvThreads, 0, stream, x, ldx, w, ldw, y, ldy, m, n, k, n);
-            break;
-        default:
-            set_error("gemv_bf16: unknown mode %d", mode);
-            return -1;
+template <int MT, int WT, int MODE, int UNROLL, int WARPS>
+static int launch_one(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw, void* y, int ldy, int m,
+                      int n, int k, int tile_offset, const GemvConvArgs& conv, cudaStream_t stream) {
+    const size_t smem = (size_t)WARPS * WT * MT * 128 * sizeof(float);
+    auto kernel = gemv_bf16_kernel<MT, WT, MODE, UNROLL, WARPS>;
+    if (smem > 40 * 1024) {
+        const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) {
+            set_error("gemv_bf16: %s", cudaGetErrorString(status));
+            return -2;
+        }
     }
+    launch_chained_class(kChainGemv, kernel, (n + 15) / 16, WARPS * 32, smem, stream, x, ldx, w, ldw, y, ldy, m, n, k,
+                         tile_offset, conv);
     return check_launch("gemv_bf16");
 }
+
+template <int MT, int WARPS, int UNROLL>
+static int launch_gemv(int mode, const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw, void* y, int ldy,
+                       int m, int n, int k, const GemvConvArgs& conv, cudaStream_t stream) {
+    switch (mode) {
+        case kGemvStoreBf16:
+            return launch_one<MT, 1, kGemvStoreBf16, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, stream);
+        case kGemvStoreF32:
+            return launch_one<MT, 1, kGemvStoreF32, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, stream);
+        case kGemvAddResidual:
+            return launch_one<MT, 1, kGemvAddResidual, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, stream);
+        case kGemvSwiGlu:
+            // n = inner width; rows [0, n) are the gate, rows [n, 2n) the up projection
+            return launch_one<MT, 2, kGemvSwiGlu, (UNROLL > 2 ? 2 : UNROLL) * (WARPS == 8 ? 2 : 1), WARPS>(
+                x, ldx, w, ldw, y, ldy, m, n, k, n, conv, stream);
+        case kGemvConv:
+            // n = channels; rows [0, n) are B, [n, 2n) C, [2n, 3n) X
+            return launch_one<MT, 3, kGemvConv, 2, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, n, conv, stream);
+    }
+    set_error("gemv_bf16: unknown mode %d", mode);
+    return -1;
+}
+
+static int g_gemv_warps = 0;      // 0: chosen from the shape; 8, 16 or 32: forced (for measurements)
 
 }  // namespace celeg_b200
 
 using namespace celeg_b200;
 
+CELEG_API void celeg_gemv_set_warps(int warps) { g_gemv_warps = warps; }
+
 // mode 0: y bf16 [m, n] = x w^T; 1: y float32; 2: y float32 += x w^T; 3: w is [2n, k] (gate rows then up
-// rows), y bf16 [m, n] = silu(x gate^T) * (x up^T).
+// rows), y bf16 [m, n] = silu(x gate^T) * (x up^T); 4: w is [3n, k] (B, C, X rows of the short convolution),
+// y bf16 [m, n] = C * conv(B*X) over the carried state, which is shifted (needs the conv arguments; row i
+// of x is the only token of request i in this step).
 CELEG_API int celeg_gemv_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int m, int n, int k,
-                              int mode, cudaStream_t stream) {
+                              int mode, const float* conv_w, int taps, float* state, long long slot_stride,
+                              const int* span_slot, cudaStream_t stream) {
     CELEG_REQUIRE(m >= 0 && n > 0 && k > 0, "gemv_bf16: invalid sizes m=%d n=%d k=%d", m, n, k);
     CELEG_REQUIRE(m <= 16, "gemv_bf16: %d activation rows exceed 16; use the library product", m);
     CELEG_REQUIRE(k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
@@ -235,9 +289,36 @@ CELEG_API int celeg_gemv_bf16(const void* x, int ldx, const void* w, int ldw, vo
     CELEG_REQUIRE(ldx >= k && ldw >= k && ldy >= n, "gemv_bf16: leading dimensions ldx=%d ldw=%d ldy=%d too small",
                   ldx, ldw, ldy);
     CELEG_REQUIRE((((size_t)x | (size_t)w) & 15) == 0, "gemv_bf16: operands must be 16-byte aligned");
+    if (mode == kGemvConv)
+        CELEG_REQUIRE(conv_w && state && span_slot && taps >= 1 && taps <= kGemvMaxConvTaps,
+                      "gemv_bf16: the convolution epilogue needs kernel, state and slots (taps=%d, at most %d)", taps,
+                      kGemvMaxConvTaps);
     if (m == 0) return 0;
     const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
-    if (m <= 8) return launch_gemv<1>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, stream);
-    return launch_gemv<2>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, stream);
+    GemvConvArgs conv = {conv_w, taps, state, slot_stride, span_slot};
+    // blocks = n/16. A narrow matrix has fewer blocks than SMs; then only more warps per block put
+    // enough loads in flight (each warp keeps 4 x 1 KiB of weights in flight, HBM needs some 50 KiB
+    // per SM). Measured on B200 at 8 rows: 2048x8192 11.2 us with 8 warps, 8.7 us with 32; 2048x2048
+    // 4.2 -> 3.7 us with 16; wider matrices are fastest with 8.
+    const int blocks = (n + 15) / 16;
+    const int slices = k / 32;
+    int warps = g_gemv_warps;
+    if (warps == 0) {
+        if (blocks <= 148)
+            warps = slices >= 128 ? 32 : 16;
+        else
+            warps = 8;
+        if (mode == kGemvConv && warps > 16) warps = 16;
+    }
+    if (slices <= 16 && warps > 8) warps = 8;
+#define CELEG_GEMV_DISPATCH(MT)                                                                                    \
+    if (warps == 8) return launch_gemv<MT, 8, 4>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, conv, stream);           \
+    if (warps == 16) return launch_gemv<MT, 16, 4>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, conv, stream);         \
+    return launch_gemv<MT, 32, 2>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, conv, stream);
+    if (m <= 8) {
+        CELEG_GEMV_DISPATCH(1)
+    }
+    CELEG_GEMV_DISPATCH(2)
+#undef CELEG_GEMV_DISPATCH
 }

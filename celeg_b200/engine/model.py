@@ -11,6 +11,7 @@ from ..cache.manager import PagedNeed, StateLayout, StateNeed
 from ..cache.storage import CacheStorage
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
 from ..parts import PagedBinding, Runtime, StateBinding, StepContext, part_factory
+from ..parts.runtime import ResidualStream
 
 
 def _weights_of(part: PartSpec, tensors: Mapping[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
@@ -55,7 +56,8 @@ class Model:
         self.embedding = rt.matrix(tensors[spec.embedding.name])
         self.head = self.embedding if spec.lm_head is None else rt.matrix(tensors[spec.lm_head.name])
         self.final_norm = build_part("norm", spec.final_norm, tensors, rt)
-        self.residual = rt.scratch("model.residual", spec.hidden_size, torch.float32)
+        self.stream = ResidualStream(rt, spec.hidden_size)
+        self.residual = self.stream.residual
         self.final_normed = rt.scratch("model.final_normed", spec.hidden_size)
         self.bindings: List[object] = [None] * len(self.order)
         self._rebind = len({entry.layer for entry in self.order}) != len(self.order)
@@ -122,20 +124,21 @@ class Model:
         """Run the step's tokens through every position of the run order and write the logits
         of the wanted rows into ``logits[:n_logits]`` (float32)."""
         rt = self.rt
+        stream = self.stream
+        stream.begin()
         kernels.embedding(self.embedding, step.token_ids[:step.tokens], self.residual,
                           self.spec.embedding_multiplier)
-        pending = None
         for position, entry in enumerate(self.order):
             layer = self.layers[entry.layer]
             if self._rebind and self.bindings[position] is not None:
                 layer.mixer.bind_cache(self.bindings[position])
-            pending = layer.block.run(self.residual, pending, step)
+            layer.block.run(stream, step)
         if n_logits == 0:
             return
-        self.final_norm.add_norm(self.residual, pending, self.final_normed, n_logits, rows=logit_rows)
-        if rt.act_dtype == torch.float32:
-            kernels.gemm_f32(self.final_normed, self.head, logits, n_logits)
+        if step.logits_of_all_rows:
+            normed = stream.normed(self.final_norm, self.final_normed, n_logits)
         else:
-            rt.linear(self.final_normed, self.head, logits, n_logits)
+            normed = stream.normed(self.final_norm, self.final_normed, n_logits, gather=logit_rows)
+        rt.linear(normed, self.head, logits, n_logits)
         if self.spec.logits_multiplier != 1.0:
             logits[:n_logits].mul_(self.spec.logits_multiplier)

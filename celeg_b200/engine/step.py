@@ -259,7 +259,9 @@ class StepFunction:
             span_slot=view("span_slot", spans),
             block_tables=[dev[o:o + spans * stride].view(spans, stride) for o in table_offsets],
             error_flag=self.error_flag, max_span=max(lengths), max_context=max_ctx,
-            context_bucket=_context_bucket(max_ctx), host_span_lengths=lengths)
+            context_bucket=_context_bucket(max_ctx), host_span_lengths=lengths,
+            logits_of_all_rows=(wanted == total and
+                                all(int(logit_rows_host[i]) == i for i in range(wanted))))
         return step, view("logit_rows", max(wanted, 1)), cursor
 
     # -------------------------------------------------------------------- checks

@@ -53,7 +53,8 @@ _SIGNATURES = {
     "celeg_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                 c_void_p, c_void_p],
-    "celeg_gemv_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_gemv_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                        c_void_p, c_longlong, c_void_p, c_void_p],
     "celeg_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -222,7 +223,7 @@ def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_c
 
 
 GEMV_MAX_ROWS = 16
-GEMV_STORE, GEMV_STORE_F32, GEMV_ADD_RESIDUAL, GEMV_SWIGLU = 0, 1, 2, 3
+GEMV_STORE, GEMV_STORE_F32, GEMV_ADD_RESIDUAL, GEMV_SWIGLU, GEMV_CONV = 0, 1, 2, 3, 4
 
 
 def gemv_supported(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -230,18 +231,24 @@ def gemv_supported(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
 
-def gemv_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_STORE) -> None:
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_STORE, *,
+              conv_w: Optional[torch.Tensor] = None, taps: int = 0, state: Optional[torch.Tensor] = None,
+              slot_stride: int = 0, span_slot: Optional[torch.Tensor] = None) -> None:
     """y[:rows] = x[:rows] @ w.T for at most 16 rows, streaming w once. mode GEMV_STORE: y bfloat16;
     GEMV_STORE_F32: y float32; GEMV_ADD_RESIDUAL: y float32, accumulated; GEMV_SWIGLU: w is
-    [2*inner, k] (gate rows, then up rows) and y bfloat16 [rows, inner] = silu(gate) * up."""
-    n = w.shape[0] // 2 if mode == GEMV_SWIGLU else w.shape[0]
+    [2*inner, k] (gate rows, then up rows) and y bfloat16 [rows, inner] = silu(gate) * up; GEMV_CONV: w is
+    [3*channels, k] (B, C, X rows of the short convolution's input projection), y bfloat16
+    [rows, channels] = C * conv(B*X) over each request's carried state, which is shifted; row i is the
+    single token of request i, whose state slot is span_slot[i]."""
+    blocks = {GEMV_SWIGLU: 2, GEMV_CONV: 3}.get(mode, 1)
+    n = w.shape[0] // blocks
     k = w.shape[1]
     assert x.shape[-1] == k and y.shape[-1] >= n
-    want = torch.bfloat16 if mode in (GEMV_STORE, GEMV_SWIGLU) else torch.float32
+    want = torch.float32 if mode in (GEMV_STORE_F32, GEMV_ADD_RESIDUAL) else torch.bfloat16
     if y.dtype != want:
         raise KernelLibraryError(f"gemv_bf16 mode {mode} writes {want}, got {y.dtype}")
     _check(library().celeg_gemv_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(y), y.stride(0), rows, n, k,
-                                     mode, _stream()))
+                                     mode, _ptr(conv_w), taps, _ptr(state), slot_stride, _ptr(span_slot), _stream()))
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, tokens: int, inner: int) -> None:

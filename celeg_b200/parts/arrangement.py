@@ -3,20 +3,17 @@ stream. Interface:
 
     Arrangement(layer_parts, rt)     layer_parts: dict with mixer_norm, mixer, feed_forward_norm,
                                      feed_forward (the last two may be None)
-    run(residual, pending, step) -> pending
-        residual: float32 [T, hidden], the residual stream, updated in place
-        pending:  an activation-type [T, hidden] output of the previous sub-layer that has NOT
-                  been added to the residual yet, or None; the returned tensor has the same
-                  meaning for the next block. Carrying it lets the add fuse with the next norm.
+    run(stream, step)                stream: the step's ResidualStream, updated in place
+
+A part's ``forward(x, out, step)`` gets the normed activations and a buffer for its output; the
+arrangement hands that buffer to the residual stream, which adds it inside the next norm kernel.
 """
 from __future__ import annotations
 
-from typing import Mapping, Optional
-
-import torch
+from typing import Mapping
 
 from .registry import register_part
-from .runtime import Runtime, StepContext
+from .runtime import ResidualStream, Runtime, StepContext
 
 
 @register_part("arrangement", "prenorm_residual")
@@ -35,14 +32,11 @@ class PreNormResidual:
         self.delta_a = rt.scratch("block.delta_a", hidden)
         self.delta_b = rt.scratch("block.delta_b", hidden)
 
-    def run(self, residual: torch.Tensor, pending: Optional[torch.Tensor], step: StepContext,
-            mixer=None) -> torch.Tensor:
-        mixer = mixer or self.mixer
-        t = step.tokens
-        self.mixer_norm.add_norm(residual, pending, self.normed, t)
-        mixer.forward(self.normed, self.delta_a, step)
-        if self.ffn is None:
-            return self.delta_a
-        self.ffn_norm.add_norm(residual, self.delta_a, self.normed, t)
-        self.ffn.forward(self.normed, self.delta_b, step)
-        return self.delta_b
+    def _sublayer(self, norm, part, delta, stream: ResidualStream, step: StepContext) -> None:
+        part.forward(stream.normed(norm, self.normed, step.tokens), delta, step)
+        stream.add_later(delta)
+
+    def run(self, stream: ResidualStream, step: StepContext) -> None:
+        self._sublayer(self.mixer_norm, self.mixer, self.delta_a, stream, step)
+        if self.ffn is not None:
+            self._sublayer(self.ffn_norm, self.ffn, self.delta_b, stream, step)

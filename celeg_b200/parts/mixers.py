@@ -177,7 +177,9 @@ class ShortConvMixer:
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
         rt, t = self.rt, step.tokens
-        rt.linear(x, self.w_in, self.projected, t)
-        kernels.short_conv(self.projected, self.kernel, self.binding.state, self.binding.slot_stride, self.gated,
-                           step.token_span, step.span_begin, step.span_slot, t, step.spans, self.hidden, self.taps)
+        if not rt.linear_short_conv(x, self.w_in, self.kernel, self.taps, self.binding, self.gated, step):
+            rt.linear(x, self.w_in, self.projected, t)
+            kernels.short_conv(self.projected, self.kernel, self.binding.state, self.binding.slot_stride,
+                               self.gated, step.token_span, step.span_begin, step.span_slot, t, step.spans,
+                               self.hidden, self.taps)
         rt.linear(self.gated, self.w_out, out, t)

@@ -10,6 +10,33 @@ import torch
 from .. import kernels
 
 
+class ResidualStream:
+    """The float32 residual stream of one step, with what is still owed to it: a part writes its
+    output to a buffer, the buffer becomes ``pending``, and it is added inside the next norm kernel
+    (residual add and norm are one launch)."""
+
+    def __init__(self, rt: "Runtime", hidden: int):
+        self.rt = rt
+        self.hidden = hidden
+        self.residual = rt.scratch("stream.residual", hidden, torch.float32)
+        self.pending: Optional[torch.Tensor] = None
+
+    def begin(self) -> None:
+        self.pending = None
+
+    def normed(self, norm, out: torch.Tensor, rows: int, gather: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """out = norm(stream + pending) for the first ``rows`` rows (or the gathered ones). Without
+        ``gather`` what was pending is added for good."""
+        norm.add_norm(self.residual, self.pending, out, rows, rows=gather)
+        if gather is None:
+            self.pending = None
+        return out
+
+    def add_later(self, delta: torch.Tensor) -> None:
+        assert self.pending is None
+        self.pending = delta
+
+
 class Runtime:
     """One per model instance. ``act_dtype`` is float32 (everything in true 32-bit) or bfloat16
     (the serving path: bfloat16 matrices and activations; residual stream, norms, softmax,
@@ -26,6 +53,7 @@ class Runtime:
         self.max_tokens = max_tokens
         self.max_requests = max_requests
         self.max_context = max_context
+        self.fuse_small_batches = True       # decode steps of few rows run the fused products
         self._flat: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         self._scratch: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         kernels.library()                       # fail now, not at the first step, if it is missing
@@ -55,23 +83,27 @@ class Runtime:
         """A small weight (norm scale, conv kernel) on the device in float32 (exact widening)."""
         return weight.to(device=self.device, dtype=torch.float32).contiguous()
 
+    def small_batch(self, rows: int) -> bool:
+        """Whether a step of ``rows`` tokens takes the fused small-batch products."""
+        return (self.fuse_small_batches and self.act_dtype == torch.bfloat16 and
+                0 < rows <= kernels.GEMV_MAX_ROWS)
+
     def linear(self, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int) -> None:
-        """out[:rows] = x[:rows] @ weight.T.  float32: this package's FFMA kernel. bfloat16: the
-        library product (cuBLAS through torch), as celeg uses cuBLAS for these
-        (src/backend/cuda/runtime/gemm_dispatcher.cpp:49-64), float32 accumulation."""
+        """out[:rows] = x[:rows] @ weight.T. float32 path: this package's FFMA kernel. bfloat16 path: at
+        most 16 rows go to this package's weight-streaming kernel, more rows to the library product
+        (cuBLAS through torch), as celeg uses cuBLAS for these
+        (src/backend/cuda/runtime/gemm_dispatcher.cpp:49-64); float32 accumulation everywhere."""
         if rows == 0:
             return
         if self.act_dtype == torch.float32:
             kernels.gemm_f32(x, weight, out, rows)
         elif kernels.gemv_supported(rows, x, weight):
-            # few rows: this package's weight-streaming kernel (celeg: its own GEMV for one row)
             kernels.gemv_bf16(x, weight, out, rows,
                               kernels.GEMV_STORE_F32 if out.dtype == torch.float32 else kernels.GEMV_STORE)
         elif out.dtype == torch.float32:
             torch.mm(x[:rows], weight.t(), out_dtype=torch.float32, out=out[:rows])
         else:
             torch.mm(x[:rows], weight.t(), out=out[:rows])
-
 
     def linear_swiglu(self, x: torch.Tensor, gate_up_weight: torch.Tensor, scratch: torch.Tensor,
                       out: torch.Tensor, rows: int, inner: int) -> None:
@@ -84,6 +116,20 @@ class Runtime:
             return
         self.linear(x, gate_up_weight, scratch, rows)
         kernels.swiglu(scratch, out, rows, inner)
+
+    def linear_short_conv(self, x: torch.Tensor, in_weight: torch.Tensor, conv_kernel: torch.Tensor, taps: int,
+                          binding, out: torch.Tensor, step: "StepContext") -> bool:
+        """The short convolution's input projection with its gate fused in, for steps in which every
+        request brings one token and there are few of them. Returns False when that does not apply
+        and the caller has to run projection and convolution separately."""
+        rows = step.tokens
+        hidden = conv_kernel.shape[0]
+        if not (self.small_batch(rows) and step.max_span == 1 and step.spans == rows and taps <= 16
+                and kernels.gemv_supported(rows, x, in_weight)):
+            return False
+        kernels.gemv_bf16(x, in_weight, out, rows, kernels.GEMV_CONV, conv_w=conv_kernel, taps=taps,
+                          state=binding.state, slot_stride=binding.slot_stride, span_slot=step.span_slot)
+        return True
 
 
 @dataclass
@@ -102,6 +148,7 @@ class StepContext:
     max_span: int = 1                 # longest span (host knowledge, for kernel choice)
     max_context: int = 0              # largest position + 1 in the step
     context_bucket: int = 0           # max_context rounded up to a power of two (launch shapes use this)
+    logits_of_all_rows: bool = False  # the wanted rows are exactly rows 0..tokens-1 in order
     host_positions: Optional[list] = None
     host_span_lengths: Optional[list] = None
     extras: Dict[str, object] = field(default_factory=dict)

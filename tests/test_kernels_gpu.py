@@ -405,3 +405,66 @@ def test_gemv_bf16_modes(m, n, k):
         gate = rounded(want[:, :inner], torch.bfloat16)
         up = rounded(want[:, inner:], torch.bfloat16)
         close(act, gate / (1 + np.exp(-gate)) * up, torch.bfloat16, scale=2.0)
+
+
+@pytest.mark.parametrize("m,hidden,k,taps", [(1, 64, 64, 3), (8, 2048, 2048, 3), (5, 40, 136, 4), (16, 48, 520, 2),
+                                             (3, 33, 64, 1), (7, 96, 96, 7), (8, 2048, 512, 3)])
+def test_gemv_conv_epilogue_matches_the_separate_kernels(m, hidden, k, taps):
+    """Input projection + gate + taps over the carried state + state shift in one kernel, against the
+    projection followed by the span kernel, three decode steps in a row: same bits, same state."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(13)
+    w = dev(rounded(rng.normal(size=(3 * hidden, k)) * 0.1, torch.bfloat16), torch.bfloat16)
+    conv_w = dev(rng.normal(size=(hidden, taps)).astype(np.float32))
+    keep = taps - 1
+    slot_stride = keep * hidden + 8
+    slots = [5, 0, 9, 3, 1, 2, 4, 6, 7, 8, 10, 11, 12, 13, 14, 15][:m]
+    state_a = torch.zeros((16, slot_stride), dtype=torch.float32, device="cuda")
+    state_a[:] = dev(rng.normal(size=(16, slot_stride)).astype(np.float32))
+    state_b = state_a.clone()
+    span_slot = dev(np.array(slots, dtype=np.int32))
+    token_span = dev(np.arange(m, dtype=np.int32))
+    span_begin = dev(np.arange(m + 1, dtype=np.int32))
+    kernels.library().celeg_gemv_set_warps(8)        # the same summation order on both sides
+    for _ in range(3):
+        x = dev(rounded(rng.normal(size=(m, k)), torch.bfloat16), torch.bfloat16)
+        fused = torch.zeros((m, hidden), dtype=torch.bfloat16, device="cuda")
+        kernels.gemv_bf16(x, w, fused, m, kernels.GEMV_CONV, conv_w=conv_w, taps=taps, state=state_a[:, 4:],
+                          slot_stride=slot_stride, span_slot=span_slot)
+        proj = torch.zeros((m, 3 * hidden), dtype=torch.bfloat16, device="cuda")
+        kernels.gemv_bf16(x, w, proj, m)
+        separate = torch.zeros((m, hidden), dtype=torch.bfloat16, device="cuda")
+        kernels.short_conv(proj, conv_w, state_b[:, 4:], slot_stride, separate, token_span, span_begin, span_slot, m,
+                           m, hidden, taps)
+        assert torch.equal(fused, separate)
+        assert torch.equal(state_a, state_b)
+    kernels.library().celeg_gemv_set_warps(0)
+    # with the block size the host would pick, the result agrees to rounding
+    x = dev(rounded(rng.normal(size=(m, k)), torch.bfloat16), torch.bfloat16)
+    auto = torch.zeros((m, hidden), dtype=torch.bfloat16, device="cuda")
+    kernels.gemv_bf16(x, w, auto, m, kernels.GEMV_CONV, conv_w=conv_w, taps=taps, state=state_a[:, 4:],
+                      slot_stride=slot_stride, span_slot=span_slot)
+    kernels.library().celeg_gemv_set_warps(8)
+    forced = torch.zeros((m, hidden), dtype=torch.bfloat16, device="cuda")
+    kernels.gemv_bf16(x, w, forced, m, kernels.GEMV_CONV, conv_w=conv_w, taps=taps, state=state_b[:, 4:],
+                      slot_stride=slot_stride, span_slot=span_slot)
+    kernels.library().celeg_gemv_set_warps(0)
+    close(auto, forced.double().cpu().numpy(), torch.bfloat16, scale=2.0)
+
+
+@pytest.mark.parametrize("warps", [8, 16, 32])
+def test_gemv_bf16_with_every_block_size(warps):
+    """The host picks 8, 16 or 32 warps per block from the shape; here each is forced in turn."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(15)
+    lib = kernels.library()
+    try:
+        lib.celeg_gemv_set_warps(warps)
+        for m, n, k in ((8, 100, 8200), (13, 48, 520), (1, 64, 2048)):
+            x = rounded(rng.normal(size=(m, k)), torch.bfloat16)
+            w = rounded(rng.normal(size=(n, k)) * 0.1, torch.bfloat16)
+            y = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+            kernels.gemv_bf16(dev(x, torch.bfloat16), dev(w, torch.bfloat16), y, m, kernels.GEMV_STORE_F32)
+            close(y, x @ w.T, torch.float32, scale=50 * math.sqrt(k))
+    finally:
+        lib.celeg_gemv_set_warps(0)
