@@ -175,7 +175,8 @@ def time_decode(loaded, sampler, batch: int, steps: int, warmup: int, prompt_tok
 
     def one(i):
         logits = step_fn.run([StepEntry(name, [feed[i][j]], [0]) for j, name in enumerate(names)])
-        kernels.sample(logits, batch, sampler._dev_i[:batch], None, None, None, None, None, None, sampler.out)
+        kernels.sample_greedy(logits, batch, sampler._dev_i[:batch], None, None, sampler.out,
+                              sampler._partial_score, sampler._partial_token)
 
     sampler._dev_i[:batch].copy_(torch.tensor([s for s, _ in slots], dtype=torch.int32))
     for i in range(warmup):

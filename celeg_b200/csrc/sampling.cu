@@ -151,6 +151,72 @@ __global__ void sample_kernel(const float* logits, long long ld, int vocab,
 }
 
 // Marks the tokens of a step as seen by their requests: slot = span_slot[token_span[i]].
+// Greedy rows only (every row of the call has temperature <= 0 or top_k == 1): the vocabulary is
+// cut into `chunks` pieces so that a few rows still use many SMs; a second, tiny kernel picks the
+// best piece per row. The first maximum wins, as in the general kernel.
+__global__ void argmax_partial_kernel(const float* logits, long long ld, int vocab, const int* row_slot,
+                                      const uint8_t* seen_base, const float* penalty, int chunks,
+                                      float* partial_score, int* partial_token) {
+    __shared__ Best scratch[33];
+    chain_release();
+    chain_wait();
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    const float* l = logits + (size_t)row * ld;
+    const int slot = row_slot ? row_slot[row] : row;
+    const float pen = penalty ? penalty[row] : 1.0f;
+    const uint8_t* seen = (seen_base && pen > 1.0f) ? seen_base + (size_t)slot * vocab : nullptr;
+    const int per = (vocab + chunks - 1) / chunks;
+    const int begin = chunk * per, end = min(vocab, begin + per);
+    Best mine{0.0f, -1};
+    constexpr int kBatch = 8;
+    for (int base = begin + threadIdx.x; base < end; base += blockDim.x * kBatch) {
+        float v[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int token = base + u * blockDim.x;
+            v[u] = token < end ? l[token] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int token = base + u * blockDim.x;
+            if (token >= end) continue;
+            float value = v[u];
+            if (seen && seen[token]) value = value >= 0.0f ? value / pen : value * pen;
+            if (mine.token < 0 || better(value, token, mine.score, mine.token)) {
+                mine.score = value;
+                mine.token = token;
+            }
+        }
+    }
+    const Best best = block_best(mine, scratch);
+    if (threadIdx.x == 0) {
+        partial_score[row * chunks + chunk] = best.score;
+        partial_token[row * chunks + chunk] = best.token;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* partial_score, const int* partial_token, int chunks, int vocab,
+                                    const int* row_slot, uint8_t* seen_base, int* out) {
+    chain_release();
+    chain_wait();
+    const int row = blockIdx.x;
+    Best mine{0.0f, -1};
+    for (int i = threadIdx.x; i < chunks; i += 32) {
+        const float s = partial_score[row * chunks + i];
+        const int t = partial_token[row * chunks + i];
+        if (t >= 0 && (mine.token < 0 || better(s, t, mine.score, mine.token))) {
+            mine.score = s;
+            mine.token = t;
+        }
+    }
+    mine = warp_best(mine);
+    if (threadIdx.x == 0) {
+        const int chosen = mine.token < 0 ? 0 : mine.token;
+        out[row] = chosen;
+        if (seen_base) seen_base[(size_t)(row_slot ? row_slot[row] : row) * vocab + chosen] = 1;
+    }
+}
+
 __global__ void mark_seen_kernel(uint8_t* seen_base, int vocab, const int* tokens,
                                  const int* token_span, const int* span_slot,
                                  int count) {
@@ -175,6 +241,25 @@ CELEG_API int celeg_sample(const float* logits, long long ld, int vocab, int row
     launch_chained(sample_kernel, rows, threads, 0, stream, logits, ld, vocab, row_slot, seen, rng, temperature,
                    top_k, top_p, penalty, out);
     return check_launch("sample");
+}
+
+// All rows greedy. partial_score / partial_token: scratch of rows * 64 elements each.
+CELEG_API int celeg_sample_greedy(const float* logits, long long ld, int vocab, int rows, const int* row_slot,
+                                  uint8_t* seen, const float* penalty, int* out, float* partial_score,
+                                  int* partial_token, cudaStream_t stream) {
+    CELEG_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "sample_greedy: invalid sizes rows=%d vocab=%d ld=%lld", rows,
+                  vocab, ld);
+    CELEG_REQUIRE(rows <= 65535, "sample_greedy: %d rows exceed one launch", rows);
+    if (rows == 0) return 0;
+    int chunks = (vocab + 2047) / 2048;
+    chunks = chunks < 1 ? 1 : chunks > 64 ? 64 : chunks;
+    launch_chained(argmax_partial_kernel, dim3(chunks, rows), 256, 0, stream, logits, ld, vocab, row_slot,
+                   (const uint8_t*)seen, penalty, chunks, partial_score, partial_token);
+    int status = check_launch("sample_greedy (partial)");
+    if (status != 0) return status;
+    launch_chained(argmax_final_kernel, rows, 32, 0, stream, (const float*)partial_score, (const int*)partial_token,
+                   chunks, vocab, row_slot, seen, out);
+    return check_launch("sample_greedy (final)");
 }
 
 CELEG_API int celeg_mark_seen(uint8_t* seen, int vocab, const int* tokens, const int* token_span,

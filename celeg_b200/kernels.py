@@ -59,6 +59,8 @@ _SIGNATURES = {
     "celeg_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p, c_void_p],
+    "celeg_sample_greedy": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p],
     "celeg_mark_seen": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
 }
 
@@ -273,6 +275,20 @@ def sample(logits: torch.Tensor, rows: int, row_slot: Optional[torch.Tensor], se
     _check(library().celeg_sample(_ptr(logits), logits.stride(0), logits.shape[1], rows, _ptr(row_slot), _ptr(seen),
                                   _ptr(rng), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(penalty), _ptr(out),
                                   _stream()))
+
+
+def sample_greedy(logits: torch.Tensor, rows: int, row_slot: Optional[torch.Tensor], seen: Optional[torch.Tensor],
+                  penalty: Optional[torch.Tensor], out: torch.Tensor, partial_score: torch.Tensor,
+                  partial_token: torch.Tensor) -> None:
+    """Arg-max (first maximum) of every row after the repetition penalty; scratch: rows*64 each."""
+    _need(logits, torch.float32, "logits")
+    _need(out, torch.int32, "out")
+    assert partial_score.numel() >= rows * 64 and partial_token.numel() >= rows * 64
+    _check(library().celeg_sample_greedy(_ptr(logits), logits.stride(0), logits.shape[1], rows, _ptr(row_slot),
+                                         _ptr(seen), _ptr(penalty), _ptr(out), _ptr(partial_score),
+                                         _ptr(partial_token), _stream()))
+    global LAUNCHES
+    LAUNCHES += 1                                     # two kernels
 
 
 def mark_seen(seen: torch.Tensor, tokens: torch.Tensor, token_span: torch.Tensor, span_slot: torch.Tensor,

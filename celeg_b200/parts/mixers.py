@@ -128,10 +128,15 @@ class AttentionMixer:
             bucket = step.context_bucket
             if self.window:
                 bucket = min(bucket, 1 << max(8, (self.window - 1).bit_length()))
-            chunk = max(64, bucket // 32)
-            max_splits = bucket // chunk
-            cap_splits = max(1, (1 << max(8, (rt.max_context - 1).bit_length())) // 64)
-            cap_splits = min(cap_splits, 32)
+            # enough blocks for about one and a half per SM, but no more splits than that needs: with
+            # many requests one block per (request, kv head) reads all keys and nothing is merged
+            blocks_wanted = 224
+            splits = max(1, min(32, bucket // 128, -(-blocks_wanted // (step.tokens * self.kv_heads))))
+            splits = min(32, max(splits, -(-bucket // 4096)))      # a block's keys must fit its shared memory
+            chunk = -(-bucket // splits)
+            chunk = (chunk + 63) // 64 * 64
+            max_splits = -(-bucket // chunk)
+            cap_splits = 32
             rows = rt.max_requests * self.heads * cap_splits
             partial_o = rt.flat_scratch("attention.partial_o", rows * self.head_dim, torch.float32)
             partial_ml = rt.flat_scratch("attention.partial_ml", rows * 2, torch.float32)

@@ -27,6 +27,8 @@ class Sampler:
         self._dev_i = torch.zeros(2 * max_rows, dtype=torch.int32, device=device)
         self._dev_f = torch.zeros(3 * max_rows, dtype=torch.float32, device=device)
         self.out = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self._partial_score = torch.zeros(max_rows * 64, dtype=torch.float32, device=device)
+        self._partial_token = torch.zeros(max_rows * 64, dtype=torch.int32, device=device)
         self._out_host = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
 
     def reset_slot(self, slot: int, seed: int) -> None:
@@ -63,8 +65,12 @@ class Sampler:
             hf[2 * m + i] = params.repetition_penalty
         self._dev_i.copy_(self._host_i, non_blocking=True)
         self._dev_f.copy_(self._host_f, non_blocking=True)
-        kernels.sample(logits, count, self._dev_i[:m], self.seen, self.rng, self._dev_f[:m], self._dev_i[m:],
-                       self._dev_f[m:2 * m], self._dev_f[2 * m:], self.out)
+        if all(params.greedy for _, params in rows):
+            kernels.sample_greedy(logits, count, self._dev_i[:m], self.seen, self._dev_f[2 * m:], self.out,
+                                  self._partial_score, self._partial_token)
+        else:
+            kernels.sample(logits, count, self._dev_i[:m], self.seen, self.rng, self._dev_f[:m], self._dev_i[m:],
+                           self._dev_f[m:2 * m], self._dev_f[2 * m:], self.out)
         self._out_host.copy_(self.out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self._out_host[:count].tolist()

@@ -468,3 +468,31 @@ def test_gemv_bf16_with_every_block_size(warps):
             close(y, x @ w.T, torch.float32, scale=50 * math.sqrt(k))
     finally:
         lib.celeg_gemv_set_warps(0)
+
+
+@pytest.mark.parametrize("vocab", [1000, 65536, 3000])
+def test_greedy_sampling_fast_path(vocab):
+    """Arg-max in two kernels equals the general kernel's greedy rows, ties and penalty included."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(16)
+    rows = 5
+    logits = rng.normal(size=(rows, vocab)).astype(np.float32) * 3
+    logits[0, 17] = logits[0, vocab - 3] = logits[0].max() + 1          # a tie across two pieces
+    logits[1, vocab - 1] = logits[1].max() + 2                          # the very last token
+    seen = np.zeros((8, vocab), dtype=np.uint8)
+    seen[:, rng.integers(0, vocab, size=vocab // 5)] = 1
+    best2 = int(np.argmax(logits[2]))
+    seen[3, best2] = 1                                                  # row 2 uses slot 3: its best is penalised
+    slots = np.array([5, 2, 3, 0, 1], dtype=np.int32)
+    penalty = np.array([1.0, 1.05, 50.0, 1.0, 1.3], dtype=np.float32)
+    seen_dev = dev(seen)
+    out = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    kernels.sample_greedy(dev(logits), rows, dev(slots), seen_dev, dev(penalty), out,
+                          torch.zeros(rows * 64, device="cuda"), torch.zeros(rows * 64, dtype=torch.int32, device="cuda"))
+    got = out.cpu().numpy()
+    for r in range(rows):
+        want, _ = plain_lfm2.sample_token(logits[r], seen[slots[r]], 1, 0.0, 1, 1.0, float(penalty[r]))
+        assert got[r] == want, (r, got[r], want)
+        seen[slots[r], want] = 1
+    assert got[0] == 17 and got[1] == vocab - 1 and got[2] != best2
+    assert np.array_equal(seen_dev.cpu().numpy(), seen)
