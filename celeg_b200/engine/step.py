@@ -229,23 +229,44 @@ class StepFunction:
         row = 0
         out = 0
         lengths = []
-        for index, (entry, cache) in enumerate(zip(entries, caches)):
-            count = len(entry.tokens)
-            token_ids[row:row + count] = np.asarray(entry.tokens, dtype=np.int32)
-            positions[row:row + count] = np.arange(cache.tokens, cache.tokens + count, dtype=np.int32)
-            token_span[row:row + count] = index
-            span_begin[index] = row
-            span_slot[index] = cache.slot
-            for place in entry.want:
-                logit_rows_host[out] = row + int(place)
-                out += 1
+        if total == spans:
+            # every request brings one token (a decode step): fill whole arrays at once
+            token_ids[:] = [entry.tokens[0] for entry in entries]
+            positions[:] = [cache.tokens for cache in caches]
+            token_span[:] = range(spans)
+            span_begin[:spans] = range(spans)
+            span_slot[:] = [cache.slot for cache in caches]
+            for index, entry in enumerate(entries):
+                if entry.want:
+                    logit_rows_host[out] = index
+                    out += 1
             for g in range(self.groups):
-                table = cache.tables[g]
-                used = min(len(table), stride)
-                tables[g][index, :used] = table[:used]
-                tables[g][index, used:] = NO_PAGE
-            lengths.append(count)
-            row += count
+                grid = tables[g]
+                grid.fill(NO_PAGE)
+                for index, cache in enumerate(caches):
+                    table = cache.tables[g]
+                    used = min(len(table), stride)
+                    grid[index, :used] = table[:used]
+            lengths = [1] * spans
+            row = spans
+        else:
+            for index, (entry, cache) in enumerate(zip(entries, caches)):
+                count = len(entry.tokens)
+                token_ids[row:row + count] = np.asarray(entry.tokens, dtype=np.int32)
+                positions[row:row + count] = np.arange(cache.tokens, cache.tokens + count, dtype=np.int32)
+                token_span[row:row + count] = index
+                span_begin[index] = row
+                span_slot[index] = cache.slot
+                for place in entry.want:
+                    logit_rows_host[out] = row + int(place)
+                    out += 1
+                for g in range(self.groups):
+                    table = cache.tables[g]
+                    used = min(len(table), stride)
+                    tables[g][index, :used] = table[:used]
+                    tables[g][index, used:] = NO_PAGE
+                lengths.append(count)
+                row += count
         span_begin[spans] = row
         dev = self._dev
 

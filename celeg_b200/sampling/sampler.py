@@ -30,6 +30,8 @@ class Sampler:
         self._partial_score = torch.zeros(max_rows * 64, dtype=torch.float32, device=device)
         self._partial_token = torch.zeros(max_rows * 64, dtype=torch.int32, device=device)
         self._out_host = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
+        self._staged = None
+        self._all_greedy = False
 
     def reset_slot(self, slot: int, seed: int) -> None:
         """A new request takes the slot: nothing seen, generator at its seed."""
@@ -54,18 +56,23 @@ class Sampler:
             return []
         if count > self.max_rows:
             raise ValueError(f"{count} rows to sample, the sampler was sized for {self.max_rows}")
-        torch.cuda.current_stream().synchronize()        # staging buffers of the last call are free
         m = self.max_rows
-        hi, hf = self._host_i.numpy(), self._host_f.numpy()
-        for i, (slot, params) in enumerate(rows):
-            hi[i] = slot
-            hi[m + i] = params.top_k
-            hf[i] = params.temperature
-            hf[m + i] = params.top_p
-            hf[2 * m + i] = params.repetition_penalty
-        self._dev_i.copy_(self._host_i, non_blocking=True)
-        self._dev_f.copy_(self._host_f, non_blocking=True)
-        if all(params.greedy for _, params in rows):
+        signature = tuple((slot, params) for slot, params in rows)
+        if signature != self._staged:
+            # the rows or their options changed: stage them again (the copies of the last staging have
+            # long been consumed: every call ends with a synchronisation)
+            hi, hf = self._host_i.numpy(), self._host_f.numpy()
+            for i, (slot, params) in enumerate(rows):
+                hi[i] = slot
+                hi[m + i] = params.top_k
+                hf[i] = params.temperature
+                hf[m + i] = params.top_p
+                hf[2 * m + i] = params.repetition_penalty
+            self._dev_i.copy_(self._host_i, non_blocking=True)
+            self._dev_f.copy_(self._host_f, non_blocking=True)
+            self._staged = signature
+            self._all_greedy = all(params.greedy for _, params in rows)
+        if self._all_greedy:
             kernels.sample_greedy(logits, count, self._dev_i[:m], self.seen, self._dev_f[2 * m:], self.out,
                                   self._partial_score, self._partial_token)
         else:
