@@ -39,6 +39,66 @@ __global__ void add_rmsnorm_kernel(float* residual, const A* delta,
     }
 }
 
+// Widths that are a multiple of 4 with 16-byte aligned rows: a thread keeps its elements in registers
+// between the two passes (the residual is read once), four at a time.
+template <typename A, int kPerThread>
+__global__ void add_rmsnorm_vec4_kernel(float* residual, const A* delta, const float* __restrict__ weight, A* out,
+                                        const int* rows, int width, float eps, int write_residual) {
+    __shared__ float scratch[33];
+    chain_release();
+    chain_wait();
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float4* res = reinterpret_cast<float4*>(residual + (size_t)r * width);
+    const int quads = width >> 2;
+    float4 x[kPerThread];
+    float sum = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+        const int q = threadIdx.x + u * blockDim.x;
+        if (q < quads) {
+            float4 v = res[q];
+            if (delta) {
+                const A* d = delta + (size_t)r * width + 4 * q;
+                if (sizeof(A) == 2) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(d);
+                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                    v.x += lo.x; v.y += lo.y; v.z += hi.x; v.w += hi.y;
+                } else {
+                    const float4 dv = *reinterpret_cast<const float4*>(d);
+                    v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+                }
+                if (write_residual) res[q] = v;
+            }
+            x[u] = v;
+            sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    }
+    sum = block_sum(sum, scratch);
+    const float inv = 1.0f / sqrtf(sum / (float)width + eps);
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+        const int q = threadIdx.x + u * blockDim.x;
+        if (q < quads) {
+            const float4 w = __ldg(reinterpret_cast<const float4*>(weight) + q);
+            const float4 v = x[u];
+            A* dst = out + (size_t)i * width + 4 * q;
+            if (sizeof(A) == 2) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv * w.x, v.y * inv * w.y);
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * inv * w.z, v.w * inv * w.w);
+                uint2 raw;
+                raw.x = *reinterpret_cast<const unsigned*>(&lo);
+                raw.y = *reinterpret_cast<const unsigned*>(&hi);
+                *reinterpret_cast<uint2*>(dst) = raw;
+            } else {
+                *reinterpret_cast<float4*>(dst) = make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z,
+                                                              v.w * inv * w.w);
+            }
+        }
+    }
+}
+
 // Plain RMSNorm over rows of `width` elements of an activation tensor (used for parts that
 // normalise something other than the residual stream).
 template <typename A>
@@ -71,6 +131,22 @@ CELEG_API int celeg_add_rmsnorm(float* residual, const void* delta, const float*
                   n_rows, width, eps);
     CELEG_REQUIRE(!(rows && write_residual), "add_rmsnorm: a gathered norm does not write the residual back");
     if (n_rows == 0) return 0;
+    constexpr int kPerThread = 4;
+    const bool aligned = (((size_t)residual | (size_t)delta | (size_t)weight | (size_t)out) & 15) == 0;
+    if (width % 4 == 0 && width <= 1024 * 4 * kPerThread && aligned && (act_dtype == kFloat32 || act_dtype == kBFloat16)) {
+        const int quads = width / 4;
+        int vec_threads = (quads + kPerThread - 1) / kPerThread;
+        vec_threads = (vec_threads + 31) / 32 * 32;
+        if (vec_threads < 64) vec_threads = 64;
+        if (act_dtype == kFloat32)
+            launch_chained_class(kChainNorm, add_rmsnorm_vec4_kernel<float, kPerThread>, n_rows, vec_threads, 0, stream,
+                                 residual, (const float*)delta, weight, (float*)out, rows, width, eps, write_residual);
+        else
+            launch_chained_class(kChainNorm, add_rmsnorm_vec4_kernel<__nv_bfloat16, kPerThread>, n_rows, vec_threads, 0,
+                                 stream, residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, width,
+                                 eps, write_residual);
+        return check_launch("add_rmsnorm");
+    }
     const int threads = norm_threads(width);
     if (act_dtype == kFloat32)
         launch_chained_class(kChainNorm, add_rmsnorm_kernel<float>, n_rows, threads, 0, stream, residual, (const float*)delta,

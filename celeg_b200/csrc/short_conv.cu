@@ -9,10 +9,11 @@
 // L-1 values of bx per channel, oldest first, in float32. Positions before the sequence are
 // zero (a slot is zeroed when a request takes it).
 //
-// Work split. Tokens whose taps all lie inside the span (index in span >= L-1) are independent:
-// one block row per token. Everything that touches the slot - the first L-1 tokens of a span
-// and the slot's new content - is done by ONE thread per (span, channel), which reads the old
-// state into registers before it writes, so the update is in place without a second buffer.
+// Work split, two launches. Tokens whose taps all lie inside the span (index in span >= L-1) are
+// independent: one block row per token (eight channels per thread for bfloat16). Everything that
+// touches the slot - the first L-1 tokens of a span and the slot's new content - is done by ONE
+// thread per (span, channel), which reads the old state into registers before it writes, so the
+// update is in place without a second buffer.
 // Both paths add the taps in the same order, so a token's result does not depend on where the
 // span was cut.
 //
@@ -25,37 +26,86 @@ namespace celeg_b200 {
 
 constexpr int kMaxTaps = 16;
 
+// Tokens whose taps all lie inside their span (index in span >= taps-1): one block row per token,
+// one channel per thread.
 template <typename A>
-__global__ void short_conv_kernel(const A* proj, const float* __restrict__ kernel,
-                                  float* state, long long slot_stride, A* out,
-                                  const int* token_span, const int* span_begin,
-                                  const int* span_slot, int tokens, int spans, int hidden,
-                                  int taps) {
+__global__ void short_conv_tokens_kernel(const A* proj, const float* __restrict__ kernel, A* out,
+                                         const int* token_span, const int* span_begin, int hidden, int taps) {
     chain_release();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= hidden) return;
-    const int y = blockIdx.y;
+    float w[kMaxTaps];
+#pragma unroll
+    for (int i = 0; i < kMaxTaps; ++i) w[i] = i < taps ? kernel[(size_t)c * taps + i] : 0.0f;   // constant data
+    chain_wait();
+    const int t = blockIdx.y;
+    const size_t row = (size_t)3 * hidden;
+    const int first = span_begin[token_span[t]];
+    if (t - first < taps - 1) return;               // handled with the state by the span kernel
+    float conv = 0.0f;
+    for (int tap = 0; tap < taps; ++tap) {
+        const A* p = proj + (size_t)(t - (taps - 1) + tap) * row;
+        conv += w[tap] * (to_float(p[c]) * to_float(p[2 * hidden + c]));
+    }
+    out[(size_t)t * hidden + c] = from_float<A>(to_float(proj[(size_t)t * row + hidden + c]) * conv);
+}
+
+// The same for bfloat16 and a width that is a multiple of 8: eight channels per thread, 16-byte loads.
+__global__ void short_conv_tokens_bf16x8_kernel(const __nv_bfloat16* proj, const float* __restrict__ kernel,
+                                                __nv_bfloat16* out, const int* token_span, const int* span_begin,
+                                                int hidden, int taps) {
+    chain_release();
+    chain_wait();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= hidden) return;
+    const int t = blockIdx.y;
+    const size_t row = (size_t)3 * hidden;
+    const int first = span_begin[token_span[t]];
+    if (t - first < taps - 1) return;
+    float conv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) conv[i] = 0.0f;
+    for (int tap = 0; tap < taps; ++tap) {
+        const __nv_bfloat16* p = proj + (size_t)(t - (taps - 1) + tap) * row + c;
+        const uint4 b4 = *reinterpret_cast<const uint4*>(p);
+        const uint4 x4 = *reinterpret_cast<const uint4*>(p + 2 * hidden);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b4);
+        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 b = __bfloat1622float2(b2[i]);
+            const float2 x = __bfloat1622float2(x2[i]);
+            conv[2 * i] += kernel[(size_t)(c + 2 * i) * taps + tap] * (b.x * x.x);
+            conv[2 * i + 1] += kernel[(size_t)(c + 2 * i + 1) * taps + tap] * (b.y * x.y);
+        }
+    }
+    const uint4 c4 = *reinterpret_cast<const uint4*>(proj + (size_t)t * row + hidden + c);
+    const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&c4);
+    uint4 r;
+    __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 cc = __bfloat1622float2(c2[i]);
+        r2[i] = __floats2bfloat162_rn(cc.x * conv[2 * i], cc.y * conv[2 * i + 1]);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * hidden + c) = r;
+}
+
+// Everything that touches a request's state: the first taps-1 tokens of its span and the slot's new
+// content, one thread per (span, channel), which reads the old state into registers before it writes.
+template <typename A>
+__global__ void short_conv_spans_kernel(const A* proj, const float* __restrict__ kernel, float* state,
+                                        long long slot_stride, A* out, const int* span_begin, const int* span_slot,
+                                        int hidden, int taps) {
+    chain_release();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= hidden) return;
     const size_t row = (size_t)3 * hidden;
     float w[kMaxTaps];
 #pragma unroll
     for (int i = 0; i < kMaxTaps; ++i) w[i] = i < taps ? kernel[(size_t)c * taps + i] : 0.0f;   // constant data
     chain_wait();
-
-    if (y < tokens) {
-        const int t = y;
-        const int first = span_begin[token_span[t]];
-        if (t - first < taps - 1) return;           // handled with the slot below
-        float conv = 0.0f;
-        for (int tap = 0; tap < taps; ++tap) {
-            const A* p = proj + (size_t)(t - (taps - 1) + tap) * row;
-            conv += w[tap] * (to_float(p[c]) * to_float(p[2 * hidden + c]));
-        }
-        out[(size_t)t * hidden + c] = from_float<A>(to_float(proj[(size_t)t * row + hidden + c]) * conv);
-        return;
-    }
-
-    const int s = y - tokens;
-    if (s >= spans) return;
+    const int s = blockIdx.y;
     const int first = span_begin[s];
     const int count = span_begin[s + 1] - first;
     const int keep = taps - 1;
@@ -98,24 +148,40 @@ using namespace celeg_b200;
 
 CELEG_API int celeg_short_conv(const void* proj, const float* kernel, float* state, long long slot_stride,
                                void* out, const int* token_span, const int* span_begin, const int* span_slot,
-                               int tokens, int spans, int hidden, int taps, int act_dtype,
+                               int tokens, int spans, int hidden, int taps, int max_span, int act_dtype,
                                cudaStream_t stream) {
     CELEG_REQUIRE(tokens >= 0 && spans >= 0 && hidden > 0, "short_conv: invalid sizes tokens=%d spans=%d hidden=%d",
                   tokens, spans, hidden);
     CELEG_REQUIRE(taps >= 1 && taps <= kMaxTaps, "short_conv: kernel length %d is outside 1..%d", taps, kMaxTaps);
+    CELEG_REQUIRE(act_dtype == kFloat32 || act_dtype == kBFloat16, "short_conv: unknown dtype code %d", act_dtype);
     if (tokens == 0) return 0;
-    CELEG_REQUIRE(tokens + spans <= 65535, "short_conv: %d tokens + %d spans exceed one launch (65535)", tokens,
-                  spans);
+    CELEG_REQUIRE(tokens <= 65535 && spans <= 65535, "short_conv: %d tokens or %d spans exceed one launch (65535)",
+                  tokens, spans);
     const int threads = hidden >= 256 ? 256 : ((hidden + 31) / 32) * 32;
-    dim3 grid((hidden + threads - 1) / threads, tokens + spans);
+    dim3 span_grid((hidden + threads - 1) / threads, spans);
     if (act_dtype == kFloat32)
-        launch_chained(short_conv_kernel<float>, grid, threads, 0, stream, (const float*)proj, kernel, state,
-                       slot_stride, (float*)out, token_span, span_begin, span_slot, tokens, spans, hidden, taps);
-    else if (act_dtype == kBFloat16)
-        launch_chained(short_conv_kernel<__nv_bfloat16>, grid, threads, 0, stream, (const __nv_bfloat16*)proj,
-                       kernel, state, slot_stride, (__nv_bfloat16*)out, token_span, span_begin, span_slot, tokens,
-                       spans, hidden, taps);
+        launch_chained(short_conv_spans_kernel<float>, span_grid, threads, 0, stream, (const float*)proj, kernel, state,
+                       slot_stride, (float*)out, span_begin, span_slot, hidden, taps);
     else
-        CELEG_REQUIRE(false, "short_conv: unknown dtype code %d", act_dtype);
-    return check_launch("short_conv");
+        launch_chained(short_conv_spans_kernel<__nv_bfloat16>, span_grid, threads, 0, stream,
+                       (const __nv_bfloat16*)proj, kernel, state, slot_stride, (__nv_bfloat16*)out, span_begin,
+                       span_slot, hidden, taps);
+    int status = check_launch("short_conv (spans)");
+    if (status != 0 || max_span <= taps - 1) return status;       // no token lies past the first taps-1 of its span
+    if (act_dtype == kBFloat16 && hidden % 8 == 0 && ((((size_t)proj) | ((size_t)out)) & 15) == 0) {
+        const int vec_threads = hidden / 8 >= 128 ? 128 : ((hidden / 8 + 31) / 32) * 32;
+        dim3 grid((hidden / 8 + vec_threads - 1) / vec_threads, tokens);
+        launch_chained(short_conv_tokens_bf16x8_kernel, grid, vec_threads, 0, stream, (const __nv_bfloat16*)proj, kernel,
+                       (__nv_bfloat16*)out, token_span, span_begin, hidden, taps);
+    } else {
+        dim3 grid((hidden + threads - 1) / threads, tokens);
+        if (act_dtype == kFloat32)
+            launch_chained(short_conv_tokens_kernel<float>, grid, threads, 0, stream, (const float*)proj, kernel,
+                           (float*)out, token_span, span_begin, hidden, taps);
+        else
+            launch_chained(short_conv_tokens_kernel<__nv_bfloat16>, grid, threads, 0, stream,
+                           (const __nv_bfloat16*)proj, kernel, (__nv_bfloat16*)out, token_span, span_begin, hidden,
+                           taps);
+    }
+    return check_launch("short_conv (tokens)");
 }

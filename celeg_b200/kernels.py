@@ -40,7 +40,7 @@ _SIGNATURES = {
                           c_void_p],
     "celeg_rmsnorm_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
     "celeg_short_conv": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                         c_int, c_int, c_int, c_int, c_void_p],
+                         c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_qk_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                  c_int, c_void_p, c_int, c_void_p],
@@ -150,13 +150,16 @@ def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: 
 
 def short_conv(proj: torch.Tensor, kernel: torch.Tensor, state: torch.Tensor, slot_stride: int, out: torch.Tensor,
                token_span: torch.Tensor, span_begin: torch.Tensor, span_slot: torch.Tensor, tokens: int, spans: int,
-               hidden: int, taps: int) -> None:
-    """``state`` points at this layer's state inside slot 0; ``slot_stride`` floats separate slots."""
+               hidden: int, taps: int, max_span: Optional[int] = None) -> None:
+    """``state`` points at this layer's state inside slot 0; ``slot_stride`` floats separate slots.
+    ``max_span``: the longest span of the step if the caller knows it (saves a launch when no span is
+    longer than the kernel); default: as long as the batch."""
     _need(kernel, torch.float32, "conv kernel")
     assert state.dtype == torch.float32
     _check(library().celeg_short_conv(_ptr(proj), _ptr(kernel), _ptr(state), slot_stride, _ptr(out),
                                       _ptr(token_span), _ptr(span_begin), _ptr(span_slot), tokens, spans, hidden,
-                                      taps, dtype_code(proj.dtype), _stream()))
+                                      taps, tokens if max_span is None else max_span, dtype_code(proj.dtype),
+                                      _stream()))
 
 
 def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],

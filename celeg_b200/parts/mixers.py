@@ -186,5 +186,5 @@ class ShortConvMixer:
             rt.linear(x, self.w_in, self.projected, t)
             kernels.short_conv(self.projected, self.kernel, self.binding.state, self.binding.slot_stride,
                                self.gated, step.token_span, step.span_begin, step.span_slot, t, step.spans,
-                               self.hidden, self.taps)
+                               self.hidden, self.taps, step.max_span)
         rt.linear(self.gated, self.w_out, out, t)
