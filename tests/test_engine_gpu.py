@@ -399,3 +399,122 @@ def test_cli_generates_and_dumps_logits(models, tmp_path, capsys):
     assert np.abs(logits - plain_lfm2.forward(config, weights, prompt)[-1]).max() < 2e-4
     assert main(["--model", folder, "--prompt", "hello"]) == 1
     assert "error:" in capsys.readouterr().err
+
+
+def test_many_requests_through_a_small_pool(models):
+    """Thirty requests of random lengths through four slots and a pool that holds about two of them
+    (MAX_UTILIZATION): admission waits, pages and slots are reused, requests that find no page are
+    skipped or preempted and prefilled again; every request still produces exactly the tokens it
+    produces alone (float32, greedy)."""
+    from celeg_b200 import Engine, EngineOptions, RequestOptions, SamplingParams, SchedulerPolicy
+    folder, config, weights = models["A"]
+    rng = np.random.default_rng(40)
+    lengths = rng.integers(1, 60, size=30).tolist()
+    prompts = prompts_of(config["vocab_size"], lengths, seed=41)
+    new_tokens = rng.integers(1, 24, size=30).tolist()
+    options = EngineOptions(max_active_requests=4, max_batched_tokens=32, prefill_chunk_tokens=13, page_tokens=16,
+                            logical_kv_pages=9, scheduler_policy=SchedulerPolicy.MAX_UTILIZATION)
+    engine = Engine(folder, dtype="float32", options=options)
+    greedy = SamplingParams(temperature=0.0, top_k=1, repetition_penalty=1.0)
+    ids = [engine.submit(p, RequestOptions(max_new_tokens=n, eos_tokens=(), generation=greedy))
+           for p, n in zip(prompts, new_tokens)]
+    outputs = {i: [] for i in ids}
+    pending = set(ids)
+    steps = 0
+    while pending:
+        assert engine.step() or not engine.scheduler.has_work()
+        engine.loaded.manager.check_invariants()
+        for i in list(pending):
+            result = engine.poll(i)
+            outputs[i].extend(result.tokens)
+            if result.finished:
+                assert result.status.value == "finished", result.error
+                pending.discard(i)
+        steps += 1
+        assert steps < 3000
+    metrics = engine.metrics()
+    assert metrics.completed == 30 and metrics.failed == 0
+    assert metrics.max_step_requests > 1
+    assert engine.loaded.manager.free_slots == 4
+    assert all(g.pool.free_pages == g.pool.total_pages for g in engine.loaded.manager.groups)
+    alone = Engine(folder, dtype="float32")
+    for request_id, prompt, n in list(zip(ids, prompts, new_tokens))[::3]:
+        want = alone.generate(prompt, max_new_tokens=n, temperature=0.0, repetition_penalty=1.0, eos_tokens=())
+        assert outputs[request_id] == want, request_id
+    for request_id, n in zip(ids, new_tokens):
+        assert len(outputs[request_id]) == n
+
+
+def test_run_order_names_a_layer_twice_and_shares_a_cache(tmp_path):
+    """The order in which layers run is data. Here tiny A runs as 0, 1, 2, 3, 1, 2': the conv layer 1 a
+    second time with a state of its own, and the attention layer 2 a second time reading the keys and
+    values its first run wrote (it computes only queries there). Checked against a plain computation,
+    whole and in portions."""
+    from celeg_b200.config import (Architecture, ExecutionEntry, Lfm2Config, build_lfm2_spec, register_architecture)
+    from celeg_b200.config.lfm2_arch import lfm2_random_init
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    from celeg_b200.weights import write_random_model
+
+    def spec_with_order(config):
+        spec = build_lfm2_spec(config)
+        order = tuple(ExecutionEntry(i) for i in range(4)) + (ExecutionEntry(1), ExecutionEntry(2, cache_of=2))
+        return dataclasses.replace(spec, order=order, architecture="lfm2_twice")
+
+    register_architecture(Architecture(name="lfm2_twice", parse_config=Lfm2Config.from_dict,
+                                       resolve_config=lambda c, shapes: c.resolved_with(shapes),
+                                       build_spec=spec_with_order, random_init=lfm2_random_init), replace=True)
+    raw = copy.deepcopy(TINY_A)
+    raw["model_type"] = "lfm2_twice"
+    folder = write_random_model(str(tmp_path / "twice"), raw, 6)
+    loaded = load_model(folder, dtype="float32", max_requests=2, cache_tokens=128, max_batched_tokens=64)
+    assert len(loaded.model.state_layout.offsets) == 4            # conv layers 0, 1, 3 and the second run of 1
+    assert [len(m) for m in loaded.model.group_members] == [1]    # one attention cache, shared by both runs
+
+    config, w = plain_lfm2.load_model_folder(folder)
+    eps, d, heads, kv_heads = config["norm_eps"], 16, 4, 2
+
+    def plain_forward(tokens):
+        x = w["model.embed_tokens.weight"][np.asarray(tokens)]
+        for index, kind in enumerate(config["layer_types"]):
+            if index == 2:
+                before_attention = x
+            x = plain_lfm2.block(x, index, kind, config, w)
+        x = plain_lfm2.block(x, 1, "conv", config, w)             # layer 1 again, from an empty state
+        # layer 2 again: queries from the current stream, keys and values from its first run
+        p = "model.layers.2."
+        positions = np.arange(len(tokens))
+        n_first = plain_lfm2.rmsnorm(before_attention, w[p + "operator_norm.weight"], eps)
+        k = (n_first @ w[p + "self_attn.k_proj.weight"].T).reshape(-1, kv_heads, d)
+        v = (n_first @ w[p + "self_attn.v_proj.weight"].T).reshape(-1, kv_heads, d)
+        k = plain_lfm2.rope_split_half(plain_lfm2.rmsnorm(k, w[p + "self_attn.k_layernorm.weight"], eps), positions,
+                                       config["rope_theta"])
+        n_now = plain_lfm2.rmsnorm(x, w[p + "operator_norm.weight"], eps)
+        q = (n_now @ w[p + "self_attn.q_proj.weight"].T).reshape(-1, heads, d)
+        q = plain_lfm2.rope_split_half(plain_lfm2.rmsnorm(q, w[p + "self_attn.q_layernorm.weight"], eps), positions,
+                                       config["rope_theta"])
+        attended = np.zeros((len(tokens), heads, d))
+        for h in range(heads):
+            scores = (q[:, h] @ k[:, h // 2].T) / np.sqrt(d)
+            scores = np.where(np.arange(len(tokens))[None, :] > positions[:, None], -np.inf, scores)
+            weights_ = np.exp(scores - scores.max(axis=-1, keepdims=True))
+            weights_ /= weights_.sum(axis=-1, keepdims=True)
+            attended[:, h] = weights_ @ v[:, h // 2]
+        hidden = x + attended.reshape(len(tokens), -1) @ w[p + "self_attn.out_proj.weight"].T
+        n2 = plain_lfm2.rmsnorm(hidden, w[p + "ffn_norm.weight"], eps)
+        x = hidden + plain_lfm2.swiglu(n2, w[p + "feed_forward.w1.weight"], w[p + "feed_forward.w3.weight"],
+                                       w[p + "feed_forward.w2.weight"])
+        z = plain_lfm2.rmsnorm(x, w["model.embedding_norm.weight"], eps)
+        return z @ w["model.embed_tokens.weight"].T
+
+    (sequence,) = prompts_of(config["vocab_size"], [37], seed=42)
+    want = plain_forward(sequence)
+    step = loaded.step
+    whole = step.run([StepEntry("whole", sequence, list(range(37)))], auto_begin=True).cpu().numpy()
+    assert np.abs(whole - want).max() < 3e-4
+    step.end("whole")
+    at = 0
+    for n in (5, 2, 17, 1, 1, 11):
+        got = step.run([StepEntry("cut", sequence[at:at + n], list(range(n)))], auto_begin=True).cpu().numpy()
+        assert np.abs(got - want[at:at + n]).max() < 3e-4, at
+        at += n
