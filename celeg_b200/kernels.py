@@ -55,6 +55,8 @@ _SIGNATURES = {
                                 c_void_p, c_void_p],
     "celeg_gemv_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_longlong, c_void_p, c_void_p],
+    "celeg_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                           c_void_p],
     "celeg_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -254,6 +256,29 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, mode
         raise KernelLibraryError(f"gemv_bf16 mode {mode} writes {want}, got {y.dtype}")
     _check(library().celeg_gemv_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(y), y.stride(0), rows, n, k,
                                      mode, _ptr(conv_w), taps, _ptr(state), slot_stride, _ptr(span_slot), _stream()))
+
+
+TC_STORE, TC_STORE_F32, TC_SWIGLU = 0, 1, 2
+
+
+def gemm_tcgen05_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, epilogue: int,
+                 error_flag: torch.Tensor) -> None:
+    """y[:rows] = x[:rows] @ w.T on tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
+    TC_STORE: y bfloat16; TC_STORE_F32: y float32; TC_SWIGLU: w is [2*inner, k] (gate rows, then up rows),
+    y bfloat16 [rows, inner] = silu(gate) * up."""
+    n = w.shape[0] // 2 if epilogue == TC_SWIGLU else w.shape[0]
+    k = w.shape[1]
+    want = torch.float32 if epilogue == TC_STORE_F32 else torch.bfloat16
+    if y.dtype != want:
+        raise KernelLibraryError(f"gemm_tcgen05 epilogue {epilogue} writes {want}, got {y.dtype}")
+    assert x.shape[-1] == k and y.shape[-1] >= n
+    _check(library().celeg_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(y), y.stride(0), rows, n, k,
+                                        epilogue, _ptr(error_flag), _stream()))
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, tokens: int, inner: int) -> None:
