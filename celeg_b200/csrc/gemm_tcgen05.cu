@@ -21,6 +21,7 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -278,6 +279,201 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) tmem_dealloc(tmem_base, kTmemColumns);
 }
 
+// ---------------------------------------------------------------------------------- persistent
+// The same product as a persistent kernel: one block per SM walks over output tiles of 128 x 256.
+// Six warps: warp 0 feeds the ring with TMA, warp 1 issues the MMAs, warps 2-5 are the epilogue. The
+// 512 columns of tensor memory hold TWO accumulators, so the MMAs of the next tile run while the
+// epilogue warps drain the previous one (tcgen05.ld -> registers -> global). Tiles that run at the same
+// time share their B tile (consecutive tile numbers walk down M), which keeps the weights in L2.
+constexpr int kPersistentThreads = 192;
+constexpr int kPersistentBN = 256;
+constexpr int kPersistentStages = 4;
+
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kPersistentThreads)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                               const TcGemmParams p) {
+    constexpr int BN = kPersistentBN, STAGES = kPersistentStages;
+    constexpr unsigned kBytesA = kTileM * kTileK * 2;
+    constexpr unsigned kBytesB = BN * kTileK * 2;
+    constexpr int kOutColumns = EPI == kTcSwiGlu ? BN / 2 : BN;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], accum_full[2], accum_empty[2];
+    __shared__ unsigned tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int k_tiles = (p.k + kTileK - 1) / kTileK;
+    const int m_tiles = (p.m + kTileM - 1) / kTileM;
+    const int n_tiles = (p.n + kOutColumns - 1) / kOutColumns;
+    const int tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&accum_full[b]), 1);
+            mbar_init(smem_u32(&accum_empty[b]), 4);       // one arrival per epilogue warp
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(smem_u32(&tmem_base_slot), 512);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const unsigned tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;                                     // k-tiles issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < tiles && !abort_flag; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * kTileM;
+                const int n0 = (tile / m_tiles) * kOutColumns;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) - 1) & 1)) {
+                        atomicExch(p.error_flag, 21);
+                        abort_flag = 1;
+                        break;
+                    }
+                    const unsigned bar = smem_u32(&full_bar[s]);
+                    mbar_expect_tx(bar, kBytesA + kBytesB);
+                    const unsigned a_dst = smem_base + s * (kBytesA + kBytesB);
+                    const unsigned b_dst = a_dst + kBytesA;
+                    tma_load_2d(a_dst, &map_a, bar, kt * kTileK, m0);
+                    if (EPI == kTcSwiGlu) {
+                        tma_load_2d(b_dst, &map_b, bar, kt * kTileK, n0);
+                        tma_load_2d(b_dst + kBytesB / 2, &map_b, bar, kt * kTileK, p.n + n0);
+                    } else {
+                        tma_load_2d(b_dst, &map_b, bar, kt * kTileK, n0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr unsigned idesc = instruction_descriptor(kTileM, BN);
+            int it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < tiles && !abort_flag; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (local >= 2 && !mbar_wait(smem_u32(&accum_empty[buf]), ((local >> 1) - 1) & 1)) {
+                    atomicExch(p.error_flag, 22);
+                    abort_flag = 1;
+                    break;
+                }
+                tcgen05_fence_after();
+                const unsigned tmem_d = tmem_base + (unsigned)(buf * BN);
+                bool ok = true;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1)) {
+                        atomicExch(p.error_flag, 23);
+                        abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const unsigned a_addr = smem_base + s * (kBytesA + kBytesB);
+                    const unsigned long long desc_a = smem_descriptor(a_addr);
+                    const unsigned long long desc_b = smem_descriptor(a_addr + kBytesA);
+#pragma unroll
+                    for (int kk = 0; kk < kTileK / kUmmaK; ++kk)
+                        umma_bf16(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(smem_u32(&empty_bar[s]));
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&accum_full[buf]));
+            }
+        }
+    } else {
+        // epilogue warps 2..5; a warp may only touch the 32 TMEM lanes of its position modulo 4
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            bool ready = abort_flag == 0 && mbar_wait(smem_u32(&accum_full[buf]), (local >> 1) & 1);
+            ready = __all_sync(0xffffffffu, ready);
+            if (!ready) {
+                if (lane == 0 && abort_flag == 0) {
+                    atomicExch(p.error_flag, 24);
+                    abort_flag = 1;
+                }
+                break;
+            }
+            tcgen05_fence_after();
+            const int m0 = (tile % m_tiles) * kTileM;
+            const int n0 = (tile / m_tiles) * kOutColumns;
+            const int row = m0 + quarter * 32 + lane;
+            const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < kOutColumns; c0 += 32) {
+                float v[32];
+                tmem_load_32(lane_base + (unsigned)c0, v);
+                if (EPI == kTcSwiGlu) {
+                    float u[32];
+                    tmem_load_32(lane_base + (unsigned)(BN / 2 + c0), u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float g = __bfloat162float(__float2bfloat16_rn(v[i]));
+                        const float up = __bfloat162float(__float2bfloat16_rn(u[i]));
+                        v[i] = g / (1.0f + expf(-g)) * up;
+                    }
+                }
+                if (row < p.m) {
+                    const int col = n0 + c0;
+                    if (EPI == kTcStoreF32) {
+                        float* dst = reinterpret_cast<float*>(p.c) + (size_t)row * p.ldc + col;
+                        if (col + 32 <= p.n && (p.ldc & 3) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4)
+                                *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        } else {
+                            for (int i = 0; i < 32; ++i)
+                                if (col + i < p.n) dst[i] = v[i];
+                        }
+                    } else {
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (size_t)row * p.ldc + col;
+                        if (col + 32 <= p.n && (p.ldc & 7) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                uint4 packed;
+                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+                                h[0] = __floats2bfloat162_rn(v[i], v[i + 1]);
+                                h[1] = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+                                h[2] = __floats2bfloat162_rn(v[i + 4], v[i + 5]);
+                                h[3] = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                                *reinterpret_cast<uint4*>(dst + i) = packed;
+                            }
+                        } else {
+                            for (int i = 0; i < 32; ++i)
+                                if (col + i < p.n) dst[i] = __float2bfloat16_rn(v[i]);
+                        }
+                    }
+                }
+            }
+            // this warp is done reading the accumulator: the MMA warp may overwrite it
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&accum_empty[buf]));
+        }
+    }
+    if (abort_flag && warp == 0 && lane == 0) {
+        // leaving early: copies that were issued must land before the shared memory goes away
+        for (int s = 0; s < STAGES; ++s) mbar_wait(smem_u32(&full_bar[s]), 0);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
 // ------------------------------------------------------------------------------------------ host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -363,6 +559,29 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, const T
     return check_launch("gemm_tcgen05");
 }
 
+template <int EPI>
+static int launch_tc_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p,
+                                cudaStream_t stream) {
+    constexpr size_t smem = (size_t)kPersistentStages * (kTileM * kTileK * 2 + kPersistentBN * kTileK * 2) + 1024;
+    auto kernel = gemm_tcgen05_persistent_kernel<EPI>;
+    const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (status != cudaSuccess) {
+        set_error("gemm_tcgen05: %s", cudaGetErrorString(status));
+        return -2;
+    }
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (sms <= 0) sms = 148;
+    }
+    constexpr int out_columns = EPI == kTcSwiGlu ? kPersistentBN / 2 : kPersistentBN;
+    const int tiles = ((p.m + kTileM - 1) / kTileM) * ((p.n + out_columns - 1) / out_columns);
+    kernel<<<tiles < sms ? tiles : sms, kPersistentThreads, smem, stream>>>(map_a, map_b, p);
+    return check_launch("gemm_tcgen05 (persistent)");
+}
+
 }  // namespace celeg_b200
 
 using namespace celeg_b200;
@@ -380,18 +599,46 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
     CELEG_REQUIRE(ldc >= n && error_flag != nullptr, "gemm_tcgen05: ldc=%d is smaller than n=%d, or no error flag", ldc, n);
     CELEG_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tcgen05: unknown epilogue %d", epilogue);
     CELEG_REQUIRE((m + kTileM - 1) / kTileM <= 65535, "gemm_tcgen05: %d rows exceed one launch", m);
-    constexpr int BN = 128;
+    // Which kernel: many rows -> the persistent kernel (128 x 256 tiles, epilogue hidden under the next
+    // tile); few rows -> 128 x 128 tiles with two blocks per SM, which gives more blocks to spread the
+    // weight stream over. CELEG_B200_TC_VARIANT = 0..3 forces one (for measurements).
+    static int forced = -2;
+    if (forced == -2) {
+        const char* env = getenv("CELEG_B200_TC_VARIANT");
+        forced = env ? atoi(env) : -1;
+    }
+    const int variant = forced >= 0 ? forced : (m >= 512 ? 3 : 1);
+    const int bn = variant >= 2 ? 256 : 128;
     CUtensorMap map_a, map_b;
     if (!tensor_map_for(a, m, k, lda, kTileM, &map_a)) return -3;
     const long long b_rows = epilogue == kTcSwiGlu ? 2ll * n : n;
-    if (!tensor_map_for(b, b_rows, k, ldb, epilogue == kTcSwiGlu ? BN / 2 : BN, &map_b)) return -3;
+    if (!tensor_map_for(b, b_rows, k, ldb, epilogue == kTcSwiGlu ? bn / 2 : bn, &map_b)) return -3;
     TcGemmParams p{m, n, k, c, ldc, error_flag};
-    switch (epilogue) {
-        case kTcStoreBf16:
-            return launch_tc<BN, 6, kTcStoreBf16>(map_a, map_b, p, stream);
-        case kTcStoreF32:
-            return launch_tc<BN, 6, kTcStoreF32>(map_a, map_b, p, stream);
-        default:
-            return launch_tc<BN, 6, kTcSwiGlu>(map_a, map_b, p, stream);
+#define CELEG_TC_DISPATCH(BN, STAGES)                                                        \
+    switch (epilogue) {                                                                      \
+        case kTcStoreBf16:                                                                   \
+            return launch_tc<BN, STAGES, kTcStoreBf16>(map_a, map_b, p, stream);             \
+        case kTcStoreF32:                                                                    \
+            return launch_tc<BN, STAGES, kTcStoreF32>(map_a, map_b, p, stream);              \
+        default:                                                                             \
+            return launch_tc<BN, STAGES, kTcSwiGlu>(map_a, map_b, p, stream);                \
     }
+    if (variant == 3) {                // persistent, two accumulators, epilogue under the next tile's MMAs
+        switch (epilogue) {
+            case kTcStoreBf16:
+                return launch_tc_persistent<kTcStoreBf16>(map_a, map_b, p, stream);
+            case kTcStoreF32:
+                return launch_tc_persistent<kTcStoreF32>(map_a, map_b, p, stream);
+            default:
+                return launch_tc_persistent<kTcSwiGlu>(map_a, map_b, p, stream);
+        }
+    }
+    if (variant == 0) {
+        CELEG_TC_DISPATCH(128, 6)      // one block per SM, deep ring
+    }
+    if (variant == 2) {
+        CELEG_TC_DISPATCH(256, 4)      // wide tile, one block per SM
+    }
+    CELEG_TC_DISPATCH(128, 3)          // two blocks per SM: one's epilogue under the other's main loop
+#undef CELEG_TC_DISPATCH
 }

@@ -71,7 +71,7 @@ class StepFunction:
         self._host = self._ring[0]
         self._host_np = self._host.numpy()
         self._dev = torch.zeros(capacity, dtype=torch.int32, device=rt.device)
-        self.error_flag = torch.zeros(1, dtype=torch.int32, device=rt.device)
+        self.error_flag = rt.error_flag
         self._decode_logits = torch.empty((max_spans, model.vocab_size), dtype=torch.float32, device=rt.device)
         self._wide_logits: Optional[torch.Tensor] = None
         self.use_graphs = use_graphs
@@ -292,4 +292,5 @@ class StepFunction:
         if code:
             self.error_flag.zero_()
             raise DeviceCheckError(f"a kernel reported error code {code} (1: cache write without a page, "
-                                   f"2: attention read without a page)")
+                                   f"2: attention read without a page, 11-24: a bounded wait of the tcgen05 "
+                                   f"product ran out)")

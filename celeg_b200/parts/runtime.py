@@ -2,6 +2,7 @@
 matrix product, and the description of the step being run."""
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
@@ -54,6 +55,11 @@ class Runtime:
         self.max_requests = max_requests
         self.max_context = max_context
         self.fuse_small_batches = True       # decode steps of few rows run the fused products
+        # Products of more than 16 rows: "swiglu" = the gate|up product with its activation runs on this
+        # package's tcgen05 kernel (faster than the library product followed by the activation kernel),
+        # the others on cuBLAS; "all" = every product on the tcgen05 kernel; "none" = cuBLAS only.
+        self.tensor_core_products = os.environ.get("CELEG_B200_TC_PRODUCTS", "swiglu")
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._flat: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         self._scratch: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         kernels.library()                       # fail now, not at the first step, if it is missing
@@ -100,6 +106,10 @@ class Runtime:
         elif kernels.gemv_supported(rows, x, weight):
             kernels.gemv_bf16(x, weight, out, rows,
                               kernels.GEMV_STORE_F32 if out.dtype == torch.float32 else kernels.GEMV_STORE)
+        elif self.tensor_core_products == "all" and kernels.gemm_tcgen05_supported(x, weight):
+            kernels.gemm_tcgen05(x, weight, out, rows,
+                                 kernels.TC_STORE_F32 if out.dtype == torch.float32 else kernels.TC_STORE,
+                                 self.error_flag)
         elif out.dtype == torch.float32:
             torch.mm(x[:rows], weight.t(), out_dtype=torch.float32, out=out[:rows])
         else:

@@ -496,3 +496,48 @@ def test_greedy_sampling_fast_path(vocab):
         seen[slots[r], want] = 1
     assert got[0] == 17 and got[1] == vocab - 1 and got[2] != best2
     assert np.array_equal(seen_dev.cpu().numpy(), seen)
+
+
+@pytest.mark.parametrize("variant", ["1", "2", "3", None])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 264, 520), (17, 1000, 96), (640, 512, 2048), (2048, 384, 1024)])
+def test_gemm_tcgen05_store_and_swiglu(m, n, k, variant, monkeypatch):
+    """The TMA + tcgen05 product against float64, every kernel variant (128x128 tiles with 3 stages,
+    128x256 with 4, persistent with two accumulators, and the host's own choice), sizes that are no
+    multiple of the tiles, K with a tail, and the fused SwiGLU epilogue. The error flag stays clear."""
+    import subprocess, sys, textwrap
+    # the variant is read once per process, so each forced variant runs in a process of its own
+    code = textwrap.dedent(f"""
+        import sys, math, numpy as np, torch
+        sys.path.insert(0, {repr(str(__import__('pathlib').Path(__file__).resolve().parents[1]))})
+        from celeg_b200 import kernels
+        torch.manual_seed(1)
+        m, n, k = {m}, {n}, {k}
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(2 * n, k, device="cuda") * 0.1).to(torch.bfloat16)
+        ref = x.double() @ w.double().t()
+        y32 = torch.full((m, n), 7.0, dtype=torch.float32, device="cuda")
+        kernels.gemm_tcgen05(x, w[:n], y32, m, kernels.TC_STORE_F32, flag)
+        err = (y32.double() - ref[:, :n]).abs().max().item()
+        assert err < 1e-3 * math.sqrt(k), ("f32", err)
+        y = torch.zeros((m, n + 8), dtype=torch.bfloat16, device="cuda")
+        kernels.gemm_tcgen05(x, w[:n], y, m, kernels.TC_STORE, flag)
+        want = ref[:, :n]
+        bad = ((y[:, :n].double() - want).abs() > 1.2e-2 * (1 + want.abs())).sum().item()
+        assert bad == 0, ("bf16", bad)
+        assert float(y[:, n:].abs().sum()) == 0.0
+        act = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        kernels.gemm_tcgen05(x, w, act, m, kernels.TC_SWIGLU, flag)
+        g = ref[:, :n].to(torch.bfloat16).double(); u = ref[:, n:].to(torch.bfloat16).double()
+        want = g / (1 + torch.exp(-g)) * u
+        bad = ((act.double() - want).abs() > 2.5e-2 * (1 + want.abs())).sum().item()
+        assert bad <= m * n // 2000, ("swiglu", bad)          # a gate on a rounding edge may flip
+        assert int(flag.item()) == 0
+        print("ok")
+    """)
+    env = dict(__import__("os").environ)
+    env.pop("CELEG_B200_TC_VARIANT", None)
+    if variant is not None:
+        env["CELEG_B200_TC_VARIANT"] = variant
+    result = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0 and "ok" in result.stdout, result.stdout + result.stderr
