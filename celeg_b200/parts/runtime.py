@@ -59,6 +59,9 @@ class Runtime:
         # package's tcgen05 kernel (faster than the library product followed by the activation kernel),
         # the others on cuBLAS; "all" = every product on the tcgen05 kernel; "none" = cuBLAS only.
         self.tensor_core_products = os.environ.get("CELEG_B200_TC_PRODUCTS", "swiglu")
+        # below this many rows the library product still wins (measured at 64 rows: 1.16 against 1.37 ms
+        # per decode step): few rows mean few 128-row tiles, and the weight stream is spread over too few SMs
+        self.tensor_core_min_rows = 256
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._flat: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         self._scratch: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
@@ -118,11 +121,17 @@ class Runtime:
     def linear_swiglu(self, x: torch.Tensor, gate_up_weight: torch.Tensor, scratch: torch.Tensor,
                       out: torch.Tensor, rows: int, inner: int) -> None:
         """out[:rows] = silu(x gate^T) * (x up^T) with gate_up_weight = [gate rows; up rows]. Few
-        bfloat16 rows: one kernel; otherwise the product into ``scratch`` and the activation kernel."""
+        bfloat16 rows: one weight-streaming kernel; more bfloat16 rows: one tcgen05 kernel; otherwise the
+        product into ``scratch`` and the activation kernel."""
         if rows == 0:
             return
         if self.act_dtype == torch.bfloat16 and kernels.gemv_supported(rows, x, gate_up_weight):
             kernels.gemv_bf16(x, gate_up_weight, out, rows, kernels.GEMV_SWIGLU)
+            return
+        if (self.act_dtype == torch.bfloat16 and kernels.gemm_tcgen05_supported(x, gate_up_weight)
+                and (self.tensor_core_products == "all"
+                     or (self.tensor_core_products == "swiglu" and rows >= self.tensor_core_min_rows))):
+            kernels.gemm_tcgen05(x, gate_up_weight, out, rows, kernels.TC_SWIGLU, self.error_flag)
             return
         self.linear(x, gate_up_weight, scratch, rows)
         kernels.swiglu(scratch, out, rows, inner)
