@@ -20,6 +20,7 @@ import sys
 from typing import IO, Optional
 
 PAGE_ROUNDING = 64      # --max-tokens counts every live request rounded up to a multiple of this
+MAX_STEP_TOKENS = 8192  # tokens one pass holds; a larger step is run as several passes
 
 
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[str], done: IO[str],
@@ -34,9 +35,9 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[
     page_tokens = page_tokens or DEFAULT_PAGE_TOKENS
     if PAGE_ROUNDING % page_tokens and page_tokens % PAGE_ROUNDING:
         raise ValueError(f"page size {page_tokens} neither divides nor is a multiple of {PAGE_ROUNDING}")
+    batch_limit = max_batched_tokens or min(max(max_tokens, PAGE_ROUNDING), MAX_STEP_TOKENS)
     loaded = load_model(model_dir, dtype=dtype, device=device, cache_tokens=max_tokens, page_tokens=page_tokens,
-                        max_requests=max_requests,
-                        max_batched_tokens=max_batched_tokens or max(max_tokens, PAGE_ROUNDING))
+                        max_requests=max_requests, max_batched_tokens=batch_limit)
     step_fn = loaded.step
     for line in lines:
         line = line.strip()
@@ -47,11 +48,15 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[
         entries = [StepEntry(request_id=item["id"], tokens=item["tokens"], want=item.get("want", []))
                    for item in record.get("entries", [])]
         if entries:
-            logits = step_fn.run(entries, auto_begin=True)
-            if logits.shape[0] > 0:
-                host = logits.to("cpu", copy=True).contiguous().numpy().astype("<f4", copy=False)
+            pieces = []
+            for part in _within_limit(entries, batch_limit, StepEntry):
+                logits = step_fn.run(part, auto_begin=True)
+                if logits.shape[0] > 0:
+                    pieces.append(logits.to("cpu", copy=True).contiguous().numpy().astype("<f4", copy=False))
+            if pieces:
                 with open(os.path.join(out_dir, f"{number}.f32"), "wb") as handle:
-                    handle.write(host.tobytes())
+                    for piece in pieces:
+                        handle.write(piece.tobytes())
             else:
                 torch.cuda.current_stream().synchronize()
             step_fn.raise_on_device_error()
@@ -60,6 +65,30 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[
         done.write(f"done {number}\n")
         done.flush()
     return 0
+
+
+def _within_limit(entries, limit: int, entry_type):
+    """A step that brings more tokens than the step function's buffers hold is run as several steps, cut
+    in order (which changes no logits): yields lists of entries of at most ``limit`` tokens, every
+    wanted place kept with the portion that holds it, so the logits come out in the order asked for."""
+    total = sum(len(entry.tokens) for entry in entries)
+    if total <= limit:
+        yield entries
+        return
+    batch, room = [], limit
+    for entry in entries:
+        at = 0
+        while at < len(entry.tokens):
+            take = min(room, len(entry.tokens) - at)
+            want = [w - at for w in entry.want if at <= w < at + take]
+            batch.append(entry_type(entry.request_id, entry.tokens[at:at + take], want))
+            at += take
+            room -= take
+            if room == 0:
+                yield batch
+                batch, room = [], limit
+    if batch:
+        yield batch
 
 
 def main(argv=None) -> int:

@@ -158,3 +158,22 @@ def test_mixed_requests_with_page_reuse(models, name, dtype, tmp_path):
         got = read_logits(out, i, vocab)
         want = np.stack([full[r][p] for r, p in places])
         compare(got, want, dtype, f"{name} mixed step {i} places {places}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_larger_than_one_pass_is_cut_inside(models, dtype, tmp_path):
+    """Two requests bring 150 and 40 tokens in ONE step to a replay whose passes hold 16 tokens."""
+    from celeg_b200.engine.trace import replay
+    folder, config, weights = models["B"]
+    vocab = config["vocab_size"]
+    a, b = sequences(vocab, [150, 40], seed=15)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a, "want": [0, 17, 149]},
+                                     {"id": "b", "tokens": b, "want": [39]}], "end": ["a"]},
+             {"step": 1, "entries": [{"id": "b", "tokens": [5], "want": [0]}], "end": ["b"]}]
+    out_dir = str(tmp_path / f"cut_{dtype}")
+    text = io.StringIO("".join(json.dumps(step) + "\n" for step in steps))
+    assert replay(folder, dtype, out_dir, 256, text, io.StringIO(), max_batched_tokens=16) == 0
+    want_a = plain_lfm2.forward(config, weights, a)
+    want_b = plain_lfm2.forward(config, weights, b + [5])
+    compare(read_logits(out_dir, 0, vocab), np.stack([want_a[0], want_a[17], want_a[149], want_b[39]]), dtype, "cut")
+    compare(read_logits(out_dir, 1, vocab), want_b[40:41], dtype, "after the cut")
