@@ -1,10 +1,11 @@
 // Paged causal grouped-query attention for batches that hold prompt portions (and, beside them,
 // single decoded tokens), bfloat16, on the tensor cores:
 //
-//   grid = (query tiles, query heads). A query tile is up to 64 consecutive tokens of one span
-//   (a span = what one request brings to the step); 4 warps own 16 query rows each. Keys and
+//   grid = (query tiles, query heads). A query tile is up to 128 consecutive tokens of one span
+//   (a span = what one request brings to the step); 8 warps own 16 query rows each. Keys and
 //   values are fetched page by page through the request's block table into shared memory, 64
-//   keys at a time (cp.async, XOR-swizzled 16-byte chunks), Q K^T and P V run as
+//   keys at a time (cp.async, XOR-swizzled 16-byte chunks, two tiles in flight: the next one loads
+//   while the current one is in the tensor cores), Q K^T and P V run as
 //   mma.sync m16n8k16 with float32 accumulators, softmax is online (running maximum and
 //   denominator in float32, exponentials by exp2 of pre-scaled scores).
 //
@@ -21,8 +22,8 @@
 
 namespace celeg_b200 {
 
-constexpr int kPrefillThreads = 128;
-constexpr int kBlockM = 64;
+constexpr int kPrefillThreads = 256;
+constexpr int kBlockM = 128;
 constexpr int kBlockN = 64;
 
 struct PrefillParams {
@@ -42,14 +43,13 @@ struct PrefillParams {
 };
 
 template <int D_PAD>
-__global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kPrefillThreads, D_PAD <= 64 ? 2 : 1) attention_prefill_kernel(const PrefillParams p) {
     constexpr int kChunks = D_PAD / 8;       // 16-byte chunks per row
     constexpr int kKTiles = D_PAD / 16;      // k tiles of Q K^T
     constexpr int kOTiles = D_PAD / 8;       // n tiles of the output
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* k_s = q_s + kBlockM * D_PAD;
-    __nv_bfloat16* v_s = k_s + kBlockN * D_PAD;
+    __nv_bfloat16* kv_s = q_s + kBlockM * D_PAD;          // two stages of [K tile | V tile]
     __shared__ int tile_span, tile_first;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -103,13 +103,15 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(cons
     const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int q_row = warp * 16 + g;                 // this thread's first row; the second is q_row + 8
 
-    for (int kb = first_key / kBlockN; kb * kBlockN <= pos_last; ++kb) {
-        __syncthreads();                             // everyone is done with the previous K/V tiles
+    // asynchronous copy of the key/value tile `kb` into stage `stage`; keys outside [first_key, pos_last] are zeros
+    auto load_tile = [&](int kb, int stage) {
+        __nv_bfloat16* k_dst = kv_s + (size_t)stage * 2 * kBlockN * D_PAD;
+        __nv_bfloat16* v_dst = k_dst + kBlockN * D_PAD;
         for (int idx = tid; idx < kBlockN * kChunks; idx += kPrefillThreads) {
             const int r = idx / kChunks, ch = idx % kChunks;
             const int key = kb * kBlockN + r;
-            __nv_bfloat16* kd = k_s + tile_offset<D_PAD>(r, ch);
-            __nv_bfloat16* vd = v_s + tile_offset<D_PAD>(r, ch);
+            __nv_bfloat16* kd = k_dst + tile_offset<D_PAD>(r, ch);
+            __nv_bfloat16* vd = v_dst + tile_offset<D_PAD>(r, ch);
             bool filled = false;
             if (key >= first_key && key <= pos_last && ch * 8 < d) {     // pages before the window may be gone
                 const int page = table[key / p.page_tokens];
@@ -128,8 +130,22 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(cons
                 *reinterpret_cast<uint4*>(vd) = zero;
             }
         }
-        cp_async_wait_all();
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+
+    const int kb_first = first_key / kBlockN;
+    load_tile(kb_first, 0);                          // this group also carries the Q tile's copies
+    for (int kb = kb_first, it = 0; kb * kBlockN <= pos_last; ++kb, ++it) {
+        const bool more = (kb + 1) * kBlockN <= pos_last;
+        if (more) {
+            load_tile(kb + 1, (it + 1) & 1);         // that stage was last read two tiles ago (barrier below)
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
         __syncthreads();
+        const __nv_bfloat16* k_s = kv_s + (size_t)(it & 1) * 2 * kBlockN * D_PAD;
+        const __nv_bfloat16* v_s = k_s + kBlockN * D_PAD;
 
         // S = Q K^T for this warp's 16 rows and the 64 keys of the tile
         float s[kBlockN / 8][4];
@@ -151,19 +167,35 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(cons
             }
         }
 
-        // scale, mask, online softmax
+        // scale, mask, online softmax. A tile whose last key is not after the warp's first row (and, with
+        // a window, whose first key is inside every row's window) needs no mask at all.
         float tile_max[2] = {-INFINITY, -INFINITY};
+        const int warp_first_pos = pos0 + warp * 16;
+        const bool full_tile = kb * kBlockN + kBlockN - 1 <= warp_first_pos && warp * 16 + 15 < rows &&
+                               (p.window <= 0 || kb * kBlockN > warp_first_pos + 15 - p.window);
+        if (full_tile) {
 #pragma unroll
-        for (int nt = 0; nt < kBlockN / 8; ++nt) {
+            for (int nt = 0; nt < kBlockN / 8; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int row = q_row + (e >> 1) * 8;
-                const int key = kb * kBlockN + nt * 8 + c2 + (e & 1);
-                const int qpos = pos0 + row;
-                const bool valid = row < rows && key <= qpos && (p.window <= 0 || key > qpos - p.window);
-                const float v = valid ? s[nt][e] * p.scale_log2 : -INFINITY;
-                s[nt][e] = v;
-                tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                for (int e = 0; e < 4; ++e) {
+                    const float v = s[nt][e] * p.scale_log2;
+                    s[nt][e] = v;
+                    tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < kBlockN / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int row = q_row + (e >> 1) * 8;
+                    const int key = kb * kBlockN + nt * 8 + c2 + (e & 1);
+                    const int qpos = pos0 + row;
+                    const bool valid = row < rows && key <= qpos && (p.window <= 0 || key > qpos - p.window);
+                    const float v = valid ? s[nt][e] * p.scale_log2 : -INFINITY;
+                    s[nt][e] = v;
+                    tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                }
             }
         }
         float correction[2], safe_max[2];
@@ -211,6 +243,7 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(cons
                 mma_bf16(o[2 * np + 1], a, b[2], b[3]);
             }
         }
+        __syncthreads();                             // every warp is done with this stage
     }
 
     // normalise and store
@@ -239,7 +272,7 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(cons
 
 template <int D_PAD>
 static int launch_prefill(const PrefillParams& p, int tiles, cudaStream_t stream) {
-    const size_t smem = (size_t)(kBlockM + 2 * kBlockN) * D_PAD * sizeof(__nv_bfloat16);
+    const size_t smem = (size_t)(kBlockM + 4 * kBlockN) * D_PAD * sizeof(__nv_bfloat16);   // Q + two K/V stages
     if (smem > 40 * 1024) {       // static shared memory counts against the 48 KiB default as well
         const cudaError_t status = cudaFuncSetAttribute(attention_prefill_kernel<D_PAD>,
                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
