@@ -1,0 +1,340 @@
+// Paged grouped-query attention for decoded tokens (one query token per request), bfloat16
+// cache, split over the keys ("flash decoding"):
+//
+//   grid = (key splits, kv heads, tokens); a block serves the G = q_heads / kv_heads query heads
+//   that share one kv head over `chunk` consecutive keys, so K and V are read once per group.
+//   Each block writes an unnormalised partial result with its running maximum and denominator
+//   to scratch memory; the block that finishes last for a (token, kv head) merges the partials
+//   (log-sum-exp) and writes the output. No block waits for another: the last one is found with
+//   an atomic counter, which it resets for the next launch.
+//
+// The query heads of a group are the rows of a 16-row tensor-core tile (mma.sync m16n8k16), keys and
+// values reach shared memory by asynchronous copies through the block table, each warp walks its own
+// key tiles. Scores, maxima, exponentials and sums are float32. Any head size that is a multiple of 8
+// up to 256, any group size up to 16, any page size; other shapes go to the general kernel.
+//
+// Counterpart in celeg: gqa_decode_paged_segment_partial_kernel + gqa_decode_segment_reduce_batch_kernel
+// (src/backend/cuda/kernels/attention_paged.cuh:287-368, 456-487), one block per query head.
+//
+// The work of one (key split, kv head, token) item is a device function, so that the stand-alone
+// kernel (one item per block) and the persistent decode program (items handed to groups of four
+// warps) run the same code.
+#pragma once
+#include "common.cuh"
+#include "mma_tiles.cuh"
+
+namespace celeg_b200 {
+
+constexpr int kDecodeThreads = 128;
+constexpr int kDecodeWarps = kDecodeThreads / 32;
+constexpr int kMaxGroup = 16;
+constexpr int kMaxDecodeHeadDim = 256;
+
+struct DecodeParams {
+    const __nv_bfloat16* q;        // [tokens, q_row_stride], head h at h*head_dim
+    int q_row_stride;
+    __nv_bfloat16* out;            // [tokens, q_heads*head_dim]
+    const __nv_bfloat16* k_cache;  // [pages, kv_heads, page_tokens, head_dim]
+    const __nv_bfloat16* v_cache;
+    long long page_stride;
+    const int* positions;          // [tokens]
+    const int* token_span;         // [tokens]
+    const int* block_table;        // [spans, table_stride]
+    int table_stride;
+    int q_heads, kv_heads, head_dim, page_tokens, window, chunk, max_splits;
+    float scale;
+    float* partial_o;              // [tokens, q_heads, max_splits, head_dim]
+    float* partial_ml;             // [tokens, q_heads, max_splits, 2]
+    int* counters;                 // [tokens, kv_heads], zero between launches
+    int* error_flag;
+};
+
+__device__ __forceinline__ void bf16x8_to_float(const uint4& raw, float* f) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(p[i]);
+        f[2 * i] = v.x;
+        f[2 * i + 1] = v.y;
+    }
+}
+
+// Shared memory of one block: Q tile [16][D_PAD] + per warp a K and a V tile [BN][D_PAD], bfloat16.
+// After the key loop the K/V area is reused for the warps' partial results (float).
+template <int D_PAD, int BN>
+__host__ __device__ constexpr size_t decode_smem_bytes() {
+    return (size_t)(16 + kDecodeWarps * 2 * BN) * D_PAD * sizeof(__nv_bfloat16);
+}
+
+// What the threads of one item share beside the tiles; it lies behind them.
+struct DecodeShared {
+    float warp_max[kDecodeWarps][16], warp_sum[kDecodeWarps][16];
+    float head_max[kMaxGroup], head_sum[kMaxGroup];
+    int is_last;
+    int pad[3];
+};
+
+template <int D_PAD, int BN>
+__host__ __device__ constexpr size_t decode_item_bytes() {
+    return decode_smem_bytes<D_PAD, BN>() + sizeof(DecodeShared);
+}
+
+// 128 threads (`tid` 0..127; `sync` is a barrier among exactly them) serve the `group` query heads that share kv head `kvh` for token t over `chunk` keys.
+// The heads are the rows of a 16-row MMA tile (rows past `group` are zero). Each of the 4 warps walks
+// its own key tiles (BN keys at a time): asynchronous copies of K and V through the block table into
+// the warp's shared memory, Q K^T and P V on mma.sync, online softmax in float32; no block-wide
+// barrier inside the loop. Then the warps' results are merged in shared memory, and the block
+// either writes the output (one split) or a partial for the last block to merge.
+template <int D_PAD, int BN, typename Sync>
+__device__ __forceinline__ void attention_decode_item(const DecodeParams& p, const int split, const int kvh, const int t,
+                                                      unsigned char* smem_raw, const int tid, Sync sync) {
+    constexpr int kChunks = D_PAD / 8;
+    constexpr int kKTiles = D_PAD / 16;
+    constexpr int kOTiles = D_PAD / 8;
+    constexpr int kKeysPerLane = BN / 32;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, c2 = (lane & 3) * 2;
+    const int group = p.q_heads / p.kv_heads;
+    const int d = p.head_dim;
+    const int pos = p.positions[t];
+    const int first = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int total = pos + 1 - first;
+    const int n_splits = (total + p.chunk - 1) / p.chunk;
+    if (split >= n_splits) return;
+    const int begin = first + split * p.chunk;
+    const int end = min(begin + p.chunk, pos + 1);
+
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* k_s = q_s + 16 * D_PAD + (size_t)warp * 2 * BN * D_PAD;
+    __nv_bfloat16* v_s = k_s + BN * D_PAD;
+    DecodeShared& shared = *reinterpret_cast<DecodeShared*>(smem_raw + decode_smem_bytes<D_PAD, BN>());
+    float (&warp_max_s)[kDecodeWarps][16] = shared.warp_max;
+    float (&warp_sum_s)[kDecodeWarps][16] = shared.warp_sum;
+    float (&head_max)[kMaxGroup] = shared.head_max;
+    float (&head_sum)[kMaxGroup] = shared.head_sum;
+    int& is_last = shared.is_last;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const int* table = p.block_table + (size_t)p.token_span[t] * p.table_stride;
+
+    for (int idx = tid; idx < 16 * kChunks; idx += kDecodeThreads) {
+        const int r = idx / kChunks, ch = idx % kChunks;
+        __nv_bfloat16* dst = q_s + tile_offset<D_PAD>(r, ch);
+        if (r < group && ch * 8 < d)
+            *reinterpret_cast<uint4*>(dst) = __ldcg(reinterpret_cast<const uint4*>(
+                p.q + (size_t)t * p.q_row_stride + (size_t)(kvh * group + r) * d + ch * 8));
+        else
+            *reinterpret_cast<uint4*>(dst) = zero;
+    }
+    sync();
+
+    float o[kOTiles][4];
+#pragma unroll
+    for (int i = 0; i < kOTiles; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
+    float run_max[2] = {-INFINITY, -INFINITY};
+    float run_sum[2] = {0.0f, 0.0f};
+    const float scale_log2 = p.scale * 1.4426950408889634f;
+    const int mi = lane >> 3, lr = lane & 7;
+
+    for (int tile_begin = begin + warp * BN; tile_begin < end; tile_begin += kDecodeWarps * BN) {
+        // page offsets of this lane's keys, then the copies of the whole tile in one go
+        long long offs[kKeysPerLane];
+#pragma unroll
+        for (int i = 0; i < kKeysPerLane; ++i) {
+            const int key = tile_begin + lane + 32 * i;
+            offs[i] = -1;
+            if (key < end) {
+                const int page = table[key / p.page_tokens];
+                if (page < 0)
+                    atomicExch(p.error_flag, 2);
+                else
+                    offs[i] = (long long)page * p.page_stride + ((long long)kvh * p.page_tokens + key % p.page_tokens) * d;
+            }
+        }
+        __syncwarp();                               // every lane is done reading the previous tile
+#pragma unroll
+        for (int i = 0; i < BN * kChunks / 32; ++i) {
+            const int idx = lane + 32 * i;
+            const int r = idx / kChunks, ch = idx % kChunks;
+            long long off = -1;
+#pragma unroll
+            for (int j = 0; j < kKeysPerLane; ++j) {
+                const long long candidate = __shfl_sync(0xffffffffu, offs[j], r & 31);
+                if ((r >> 5) == j) off = candidate;
+            }
+            __nv_bfloat16* kd = k_s + tile_offset<D_PAD>(r, ch);
+            __nv_bfloat16* vd = v_s + tile_offset<D_PAD>(r, ch);
+            if (off >= 0 && ch * 8 < d) {
+                cp_async_16(kd, p.k_cache + off + ch * 8);
+                cp_async_16(vd, p.v_cache + off + ch * 8);
+            } else {
+                *reinterpret_cast<uint4*>(kd) = zero;
+                *reinterpret_cast<uint4*>(vd) = zero;
+            }
+        }
+        cp_async_wait_all();
+        __syncwarp();
+
+        float s[BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[i][e] = 0.0f;
+#pragma unroll
+        for (int kt = 0; kt < kKTiles; ++kt) {
+            unsigned a[4];
+            ldmatrix_x4(a, q_s + tile_offset<D_PAD>((mi & 1) * 8 + lr, kt * 2 + (mi >> 1)));
+#pragma unroll
+            for (int np = 0; np < BN / 16; ++np) {
+                unsigned b[4];
+                ldmatrix_x4(b, k_s + tile_offset<D_PAD>(np * 16 + (mi >> 1) * 8 + lr, kt * 2 + (mi & 1)));
+                mma_bf16(s[2 * np], a, b[0], b[1]);
+                mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+        float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = tile_begin + nt * 8 + c2 + (e & 1);
+                const float v = key < end ? s[nt][e] * scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+            }
+        }
+        float correction[2], safe_max[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            float m = tile_max[half];
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            const float new_max = fmaxf(run_max[half], m);
+            correction[half] = new_max == -INFINITY ? 1.0f : exp2f(run_max[half] - new_max);
+            safe_max[half] = new_max == -INFINITY ? 0.0f : new_max;
+            run_max[half] = new_max;
+            run_sum[half] *= correction[half];
+        }
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(s[nt][e] - safe_max[e >> 1]);
+                s[nt][e] = pv;
+                run_sum[e >> 1] += pv;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kOTiles; ++i) {
+            o[i][0] *= correction[0];
+            o[i][1] *= correction[0];
+            o[i][2] *= correction[1];
+            o[i][3] *= correction[1];
+        }
+#pragma unroll
+        for (int kt = 0; kt < BN / 16; ++kt) {
+            unsigned a[4];
+            a[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+            a[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+            a[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+            a[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+#pragma unroll
+            for (int np = 0; np < kOTiles / 2; ++np) {
+                unsigned b[4];
+                ldmatrix_x4_trans(b, v_s + tile_offset<D_PAD>(kt * 16 + (mi & 1) * 8 + lr, np * 2 + (mi >> 1)));
+                mma_bf16(o[2 * np], a, b[0], b[1]);
+                mma_bf16(o[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+    }
+
+    // row sums over the four lanes that share a row; then the warps' results meet in shared memory
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        run_sum[half] += __shfl_xor_sync(0xffffffffu, run_sum[half], 1);
+        run_sum[half] += __shfl_xor_sync(0xffffffffu, run_sum[half], 2);
+    }
+    sync();                                // every warp is done with its K/V tiles
+    float* o_s = reinterpret_cast<float*>(smem_raw + 16 * D_PAD * sizeof(__nv_bfloat16));   // [warps][group][D_PAD]
+    if ((lane & 3) == 0) {
+        warp_max_s[warp][g] = run_max[0];
+        warp_max_s[warp][g + 8] = run_max[1];
+        warp_sum_s[warp][g] = run_sum[0];
+        warp_sum_s[warp][g + 8] = run_sum[1];
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = g + half * 8;
+        if (r < group) {
+#pragma unroll
+            for (int i = 0; i < kOTiles; ++i) {
+                float* dst = o_s + ((size_t)warp * group + r) * D_PAD + i * 8 + c2;
+                dst[0] = o[i][half * 2];
+                dst[1] = o[i][half * 2 + 1];
+            }
+        }
+    }
+    sync();
+    if (tid < group) {
+        float m = -INFINITY;
+        for (int w = 0; w < kDecodeWarps; ++w) m = fmaxf(m, warp_max_s[w][tid]);
+        float sum = 0.0f;
+        for (int w = 0; w < kDecodeWarps; ++w)
+            sum += warp_max_s[w][tid] == -INFINITY ? 0.0f : warp_sum_s[w][tid] * exp2f(warp_max_s[w][tid] - m);
+        head_max[tid] = m;
+        head_sum[tid] = sum;
+    }
+    sync();
+    for (int i = tid; i < group * d; i += kDecodeThreads) {
+        const int r = i / d, col = i % d;
+        const float m = head_max[r];
+        float v = 0.0f;
+        for (int w = 0; w < kDecodeWarps; ++w) {
+            const float wm = warp_max_s[w][r];
+            if (wm != -INFINITY) v += o_s[((size_t)w * group + r) * D_PAD + col] * exp2f(wm - m);
+        }
+        const int h = kvh * group + r;
+        if (n_splits == 1)
+            p.out[((size_t)t * p.q_heads + h) * d + col] = __float2bfloat16_rn(v / head_sum[r]);
+        else
+            p.partial_o[(((size_t)t * p.q_heads + h) * p.max_splits + split) * d + col] = v;
+    }
+    if (n_splits == 1) return;
+    if (tid < group) {
+        const int h = kvh * group + tid;
+        float* ml = p.partial_ml + (((size_t)t * p.q_heads + h) * p.max_splits + split) * 2;
+        ml[0] = head_max[tid];                      // in units of log2: exponentials below use exp2
+        ml[1] = head_sum[tid];
+    }
+
+    // the item that arrives last merges the splits
+    __threadfence();
+    sync();
+    if (tid == 0) {
+        int* counter = p.counters + (size_t)t * p.kv_heads + kvh;
+        const int arrived = atomicAdd(counter, 1);
+        is_last = arrived == n_splits - 1;
+        if (is_last) *counter = 0;
+    }
+    sync();
+    if (!is_last) return;
+    __threadfence();
+    for (int item = tid; item < group * d; item += kDecodeThreads) {
+        const int r = item / d, col = item % d;
+        const int h = kvh * group + r;
+        const float* ml = p.partial_ml + ((size_t)t * p.q_heads + h) * p.max_splits * 2;
+        const float* po = p.partial_o + ((size_t)t * p.q_heads + h) * p.max_splits * d + col;
+        float m = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp) m = fmaxf(m, __ldcg(ml + 2 * sp));
+        float denom = 0.0f, total_o = 0.0f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            const float w = exp2f(__ldcg(ml + 2 * sp) - m);
+            denom += w * __ldcg(ml + 2 * sp + 1);
+            total_o += w * __ldcg(po + (size_t)sp * d);
+        }
+        p.out[((size_t)t * p.q_heads + h) * d + col] = __float2bfloat16_rn(total_o / denom);
+    }
+}
+
+}  // namespace celeg_b200

@@ -291,6 +291,7 @@ class StepFunction:
         code = int(self.error_flag.item())
         if code:
             self.error_flag.zero_()
+            self.model.reset_programs()
             raise DeviceCheckError(f"a kernel reported error code {code} (1: cache write without a page, "
                                    f"2: attention read without a page, 11-24: a bounded wait of the tcgen05 "
-                                   f"product ran out)")
+                                   f"product ran out, 31-33: a bounded wait of the decode program ran out)")

@@ -4,6 +4,7 @@ stream. Interface:
     Arrangement(layer_parts, rt)     layer_parts: dict with mixer_norm, mixer, feed_forward_norm,
                                      feed_forward (the last two may be None)
     run(stream, step)                stream: the step's ResidualStream, updated in place
+    emit_decode(builder, step)       optional: the same as operations of a decode program
 
 A part's ``forward(x, out, step)`` gets the normed activations and a buffer for its output; the
 arrangement hands that buffer to the residual stream, which adds it inside the next norm kernel.
@@ -12,6 +13,7 @@ from __future__ import annotations
 
 from typing import Mapping
 
+from .program import NormedRows, ProgramUnsupported
 from .registry import register_part
 from .runtime import ResidualStream, Runtime, StepContext
 
@@ -40,3 +42,15 @@ class PreNormResidual:
         self._sublayer(self.mixer_norm, self.mixer, self.delta_a, stream, step)
         if self.ffn is not None:
             self._sublayer(self.ffn_norm, self.ffn, self.delta_b, stream, step)
+
+    @staticmethod
+    def _emit_sublayer(norm, part, builder, step: StepContext) -> None:
+        prologue = norm.as_prologue() if hasattr(norm, "as_prologue") else None
+        if prologue is None or not hasattr(part, "emit_decode"):
+            raise ProgramUnsupported(f"{type(norm).__name__} + {type(part).__name__} cannot be part of a decode program")
+        part.emit_decode(builder, NormedRows(weight=prologue[0], eps=prologue[1]), step)
+
+    def emit_decode(self, builder, step: StepContext) -> None:
+        self._emit_sublayer(self.mixer_norm, self.mixer, builder, step)
+        if self.ffn is not None:
+            self._emit_sublayer(self.ffn_norm, self.ffn, builder, step)

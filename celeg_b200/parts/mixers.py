@@ -5,6 +5,8 @@
     bind_cache(binding)                     PagedBinding or StateBinding from the cache storage
     forward(x, out, step)                   x: normed activations [T, hidden]; writes the
                                             mixer's output (to be added to the residual) to out
+    emit_decode(builder, x, step)           optional: the same as operations of a decode program
+                                            (parts/program.py) for steps of one token per request
 
 A mixer does not know which model or layer it is in; everything it needs about the step is
 in the StepContext, everything about its cache in the binding.
@@ -18,6 +20,7 @@ import torch
 
 from .. import kernels
 from ..cache.manager import PagedNeed, StateNeed
+from . import program
 from .registry import register_part
 from .runtime import Runtime, StepContext
 
@@ -119,28 +122,53 @@ class AttentionMixer:
         self.attend(step, table)
         rt.linear(self.attended, self.w_out, out, t)
 
+    def _decode_split(self, step: StepContext):
+        """One query token per request: how the keys are split so that few requests still fill the GPU,
+        and the scratch of the split (chunk, max_splits, partial outputs, maxima and sums, counters)."""
+        rt = self.rt
+        bucket = step.context_bucket
+        if self.window:
+            bucket = min(bucket, 1 << max(8, (self.window - 1).bit_length()))
+        # enough blocks for about one and a half per SM, but no more splits than that needs: with
+        # many requests one block per (request, kv head) reads all keys and nothing is merged
+        blocks_wanted = 224
+        splits = max(1, min(32, bucket // 128, -(-blocks_wanted // (step.tokens * self.kv_heads))))
+        splits = min(32, max(splits, -(-bucket // 4096)))      # a block's keys must fit its shared memory
+        chunk = -(-bucket // splits)
+        chunk = (chunk + 63) // 64 * 64
+        max_splits = -(-bucket // chunk)
+        cap_splits = 32
+        rows = rt.max_requests * self.heads * cap_splits
+        partial_o = rt.flat_scratch("attention.partial_o", rows * self.head_dim, torch.float32)
+        partial_ml = rt.flat_scratch("attention.partial_ml", rows * 2, torch.float32)
+        counters = rt.flat_scratch("attention.counters", rt.max_requests * self.kv_heads, torch.int32, zero=True)
+        return chunk, max_splits, partial_o, partial_ml, counters
+
+    def emit_decode(self, builder, x, step: StepContext) -> None:
+        b = self.binding
+        fused = self.position.fused() if self.position is not None else {"inv_freq": None, "rotary_dim": 0}
+        if fused is None:
+            raise program.ProgramUnsupported("a position encoding without tables for the fused q/k kernel")
+        if step.tokens > self.rt.max_requests or not kernels.attention_decode_supported(
+                self.heads, self.kv_heads, self.head_dim, self.rt.act_dtype):
+            raise program.ProgramUnsupported("these attention sizes go to the general kernel")
+        table = step.block_tables[b.group]
+        builder.product(x, self.w_qkv, self.qkv)
+        builder.qk_norm_rope(self.qkv, self.q_norm, self.k_norm, fused["inv_freq"], fused["rotary_dim"],
+                             step.positions, step.token_span, table, b.k, b.v, self.heads, self.stored_kv_heads,
+                             self.head_dim, b.page_tokens, self.eps, b.owner and not self.reads_only)
+        chunk, max_splits, partial_o, partial_ml, counters = self._decode_split(step)
+        builder.attention(self.qkv, self.attended, b.k, b.v, step.positions, step.token_span, table, self.heads,
+                          self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale, chunk, max_splits,
+                          partial_o, partial_ml, counters)
+        builder.product(self.attended, self.w_out, add_to_residual=True)
+
     def attend(self, step: StepContext, table: torch.Tensor) -> None:
         b = self.binding
         rt = self.rt
         if (step.max_span == 1 and step.tokens <= rt.max_requests and
                 kernels.attention_decode_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype)):
-            # one query token per request: split the keys so that few requests still fill the GPU
-            bucket = step.context_bucket
-            if self.window:
-                bucket = min(bucket, 1 << max(8, (self.window - 1).bit_length()))
-            # enough blocks for about one and a half per SM, but no more splits than that needs: with
-            # many requests one block per (request, kv head) reads all keys and nothing is merged
-            blocks_wanted = 224
-            splits = max(1, min(32, bucket // 128, -(-blocks_wanted // (step.tokens * self.kv_heads))))
-            splits = min(32, max(splits, -(-bucket // 4096)))      # a block's keys must fit its shared memory
-            chunk = -(-bucket // splits)
-            chunk = (chunk + 63) // 64 * 64
-            max_splits = -(-bucket // chunk)
-            cap_splits = 32
-            rows = rt.max_requests * self.heads * cap_splits
-            partial_o = rt.flat_scratch("attention.partial_o", rows * self.head_dim, torch.float32)
-            partial_ml = rt.flat_scratch("attention.partial_ml", rows * 2, torch.float32)
-            counters = rt.flat_scratch("attention.counters", rt.max_requests * self.kv_heads, torch.int32, zero=True)
+            chunk, max_splits, partial_o, partial_ml, counters = self._decode_split(step)
             kernels.attention_decode(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
                                      step.token_span, table, step.tokens, self.heads, self.kv_heads,
                                      self.head_dim, b.page_tokens, self.window, self.scale, chunk, max_splits,
@@ -188,3 +216,8 @@ class ShortConvMixer:
                                self.gated, step.token_span, step.span_begin, step.span_slot, t, step.spans,
                                self.hidden, self.taps, step.max_span)
         rt.linear(self.gated, self.w_out, out, t)
+
+    def emit_decode(self, builder, x, step: StepContext) -> None:
+        builder.product(x, self.w_in, self.gated, epilogue=program.CONV, conv_kernel=self.kernel, taps=self.taps,
+                        state=self.binding.state, slot_stride=self.binding.slot_stride, span_slot=step.span_slot)
+        builder.product(self.gated, self.w_out, add_to_residual=True)

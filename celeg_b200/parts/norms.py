@@ -6,6 +6,8 @@
         delta:    activation-type [T, width] or None
         out:      activation-type [n_rows, width]
         rows:     int32 row list to gather (then the residual is left untouched)
+    as_prologue() -> (weight, eps) or None      optional: a plain RMSNorm that a product of a decode
+                                                program applies to its own operand
 """
 from __future__ import annotations
 
@@ -33,3 +35,6 @@ class RmsNorm:
     def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor, n_rows: int,
                  rows: Optional[torch.Tensor] = None) -> None:
         kernels.add_rmsnorm(residual, delta, self.weight, out, self.eps, rows=rows, n_rows=n_rows)
+
+    def as_prologue(self):
+        return self.weight, self.eps
