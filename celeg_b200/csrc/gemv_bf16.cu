@@ -39,6 +39,27 @@ struct GemvConvArgs {
     const int* span_slot;        // state slot of row i (row i is the single token of span i)
 };
 
+// The norm between two products, split over them. The product that ends a part adds its result to
+// the float32 residual stream; it can also leave behind x' = bf16(residual * w) with w the weight of the
+// RMSNorm that follows, and each block's share of every row's sum of squares. The product that begins
+// the next part takes x' as its operand and multiplies its sums by 1 / sqrt(mean square + eps) of
+// the row (the scale is a factor of the whole row, so it commutes with the product). No kernel of its
+// own for residual add + norm, nothing recomputed, no block waits for another.
+struct GemvNormArgs {
+    // this product's operand still lacks the row scale: [rows][partials_in] sums of squares, or null
+    const float* sumsq_in;
+    int partials_in;
+    int sumsq_in_stride;
+    float eps;
+    int width;                   // the mean runs over this many elements
+    // add-residual mode: also write x' for the norm that follows and this block's sums, or null
+    const float* next_w;         // [n]
+    __nv_bfloat16* xw_out;       // [m, ldxw]
+    int ldxw;
+    float* sumsq_out;            // [m][sumsq_out_stride], entry blockIdx.x
+    int sumsq_out_stride;
+};
+
 __device__ __forceinline__ uint4 ldg_stream(const void* ptr) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
@@ -69,9 +90,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsig
 template <int MT, int WT, int MODE, int kGemvUnroll, int kGemvWarps>
 __global__ void __launch_bounds__(kGemvWarps * 32)
 gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
-                 void* __restrict__ y, int ldy, int m, int n, int k, int second_tile_offset, GemvConvArgs conv) {
+                 void* __restrict__ y, int ldy, int m, int n, int k, int second_tile_offset, GemvConvArgs conv,
+                 GemvNormArgs norm) {
     constexpr int kGemvThreads = kGemvWarps * 32;
     extern __shared__ __align__(16) float partial_raw[];
+    __shared__ float row_scale[16];
+    __shared__ float squares[16][17];
     float (*partial)[WT][MT][32][4] = reinterpret_cast<float (*)[WT][MT][32][4]>(partial_raw);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, c = lane & 3;
@@ -122,6 +146,16 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
         if (!waited) {
             chain_wait();
             waited = true;
+            if (norm.sumsq_in) {
+                // the rows' scales, while the weights are on their way: a warp per row
+                for (int r = warp; r < m; r += kGemvWarps) {
+                    float total = 0.0f;
+                    for (int i = lane; i < norm.partials_in; i += 32)
+                        total += __ldcg(norm.sumsq_in + (size_t)r * norm.sumsq_in_stride + i);
+                    total = warp_sum(total);
+                    if (lane == 0) row_scale[r] = 1.0f / sqrtf(total / (float)norm.width + norm.eps);
+                }
+            }
         }
         uint4 b[kGemvUnroll][MT];
 #pragma unroll
@@ -149,7 +183,18 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
             }
         }
     }
-    if (!waited) chain_wait();
+    if (!waited) {
+        chain_wait();
+        if (norm.sumsq_in) {
+            for (int r = warp; r < m; r += kGemvWarps) {
+                float total = 0.0f;
+                for (int i = lane; i < norm.partials_in; i += 32)
+                    total += __ldcg(norm.sumsq_in + (size_t)r * norm.sumsq_in_stride + i);
+                total = warp_sum(total);
+                if (lane == 0) row_scale[r] = 1.0f / sqrtf(total / (float)norm.width + norm.eps);
+            }
+        }
+    }
     // tail of K (k % 32 in {8, 16, 24}): 8-element groups beyond the last full slice, zero-filled
     const int tail = k - slices * 32;
     if (tail > 0 && warp == (slices % kGemvWarps)) {
@@ -190,14 +235,27 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
         // accumulator element e of lane ln: weight row (ln/4) + 8*(e/2), activation row 2*(ln%4) + (e%2)
         const int out_col = row0 + (ln >> 2) + ((e >> 1) << 3);
         const int out_row = j * 8 + ((ln & 3) << 1) + (e & 1);
+        if (MODE == kGemvAddResidual && norm.next_w && out_row < m && out_col >= n)
+            squares[out_row][out_col - row0] = 0.0f;
         if (out_row >= m || out_col >= n) continue;
+        if (norm.sumsq_in) {
+            const float scale = row_scale[out_row];
+#pragma unroll
+            for (int t = 0; t < WT; ++t) sum[t] *= scale;
+        }
         if (MODE == kGemvStoreBf16) {
             reinterpret_cast<__nv_bfloat16*>(y)[(size_t)out_row * ldy + out_col] = __float2bfloat16_rn(sum[0]);
         } else if (MODE == kGemvStoreF32) {
             reinterpret_cast<float*>(y)[(size_t)out_row * ldy + out_col] = sum[0];
         } else if (MODE == kGemvAddResidual) {
+            // the product as a plain product would store it (one rounding to bfloat16), added in float32
             float* dst = reinterpret_cast<float*>(y) + (size_t)out_row * ldy + out_col;
-            *dst += sum[0];
+            const float updated = *dst + __bfloat162float(__float2bfloat16_rn(sum[0]));
+            *dst = updated;
+            if (norm.next_w) {
+                norm.xw_out[(size_t)out_row * norm.ldxw + out_col] = __float2bfloat16_rn(updated * norm.next_w[out_col]);
+                squares[out_row][out_col - row0] = updated * updated;
+            }
         } else if (MODE == kGemvConv) {
             // B, C, X as a plain product would store them (one rounding each), then the span kernel's
             // arithmetic in the same order, so that both ways give the same bits
@@ -226,11 +284,22 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
                 __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
         }
     }
+    if (MODE == kGemvAddResidual && norm.next_w) {
+        // this block's 16 columns of every row, summed in a fixed order
+        __syncthreads();
+        if (threadIdx.x < m) {
+            float total = 0.0f;
+#pragma unroll
+            for (int col = 0; col < 16; ++col) total += squares[threadIdx.x][col];
+            norm.sumsq_out[(size_t)threadIdx.x * norm.sumsq_out_stride + blockIdx.x] = total;
+        }
+    }
 }
 
 template <int MT, int WT, int MODE, int UNROLL, int WARPS>
 static int launch_one(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw, void* y, int ldy, int m,
-                      int n, int k, int tile_offset, const GemvConvArgs& conv, cudaStream_t stream) {
+                      int n, int k, int tile_offset, const GemvConvArgs& conv, const GemvNormArgs& norm,
+                      cudaStream_t stream) {
     const size_t smem = (size_t)WARPS * WT * MT * 128 * sizeof(float);
     auto kernel = gemv_bf16_kernel<MT, WT, MODE, UNROLL, WARPS>;
     if (smem > 40 * 1024) {
@@ -241,27 +310,27 @@ static int launch_one(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, i
         }
     }
     launch_chained_class(kChainGemv, kernel, (n + 15) / 16, WARPS * 32, smem, stream, x, ldx, w, ldw, y, ldy, m, n, k,
-                         tile_offset, conv);
+                         tile_offset, conv, norm);
     return check_launch("gemv_bf16");
 }
 
 template <int MT, int WARPS, int UNROLL>
 static int launch_gemv(int mode, const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw, void* y, int ldy,
-                       int m, int n, int k, const GemvConvArgs& conv, cudaStream_t stream) {
+                       int m, int n, int k, const GemvConvArgs& conv, const GemvNormArgs& norm, cudaStream_t stream) {
     switch (mode) {
         case kGemvStoreBf16:
-            return launch_one<MT, 1, kGemvStoreBf16, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, stream);
+            return launch_one<MT, 1, kGemvStoreBf16, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, norm, stream);
         case kGemvStoreF32:
-            return launch_one<MT, 1, kGemvStoreF32, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, stream);
+            return launch_one<MT, 1, kGemvStoreF32, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, norm, stream);
         case kGemvAddResidual:
-            return launch_one<MT, 1, kGemvAddResidual, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, stream);
+            return launch_one<MT, 1, kGemvAddResidual, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, norm, stream);
         case kGemvSwiGlu:
             // n = inner width; rows [0, n) are the gate, rows [n, 2n) the up projection
             return launch_one<MT, 2, kGemvSwiGlu, (UNROLL > 2 ? 2 : UNROLL) * (WARPS == 8 ? 2 : 1), WARPS>(
-                x, ldx, w, ldw, y, ldy, m, n, k, n, conv, stream);
+                x, ldx, w, ldw, y, ldy, m, n, k, n, conv, norm, stream);
         case kGemvConv:
             // n = channels; rows [0, n) are B, [n, 2n) C, [2n, 3n) X
-            return launch_one<MT, 3, kGemvConv, 2, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, n, conv, stream);
+            return launch_one<MT, 3, kGemvConv, 2, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, n, conv, norm, stream);
     }
     set_error("gemv_bf16: unknown mode %d", mode);
     return -1;
@@ -279,9 +348,9 @@ CELEG_API void celeg_gemv_set_warps(int warps) { g_gemv_warps = warps; }
 // rows), y bf16 [m, n] = silu(x gate^T) * (x up^T); 4: w is [3n, k] (B, C, X rows of the short convolution),
 // y bf16 [m, n] = C * conv(B*X) over the carried state, which is shifted (needs the conv arguments; row i
 // of x is the only token of request i in this step).
-CELEG_API int celeg_gemv_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int m, int n, int k,
-                              int mode, const float* conv_w, int taps, float* state, long long slot_stride,
-                              const int* span_slot, cudaStream_t stream) {
+static int gemv_checked(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int m, int n, int k, int mode,
+                        const float* conv_w, int taps, float* state, long long slot_stride, const int* span_slot,
+                        const GemvNormArgs& norm, cudaStream_t stream) {
     CELEG_REQUIRE(m >= 0 && n > 0 && k > 0, "gemv_bf16: invalid sizes m=%d n=%d k=%d", m, n, k);
     CELEG_REQUIRE(m <= 16, "gemv_bf16: %d activation rows exceed 16; use the library product", m);
     CELEG_REQUIRE(k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
@@ -313,12 +382,43 @@ CELEG_API int celeg_gemv_bf16(const void* x, int ldx, const void* w, int ldw, vo
     }
     if (slices <= 16 && warps > 8) warps = 8;
 #define CELEG_GEMV_DISPATCH(MT)                                                                                    \
-    if (warps == 8) return launch_gemv<MT, 8, 4>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, conv, stream);           \
-    if (warps == 16) return launch_gemv<MT, 16, 4>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, conv, stream);         \
-    return launch_gemv<MT, 32, 2>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, conv, stream);
+    if (warps == 8) return launch_gemv<MT, 8, 4>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, conv, norm, stream);           \
+    if (warps == 16) return launch_gemv<MT, 16, 4>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, conv, norm, stream);         \
+    return launch_gemv<MT, 32, 2>(mode, xp, ldx, wp, ldw, y, ldy, m, n, k, conv, norm, stream);
     if (m <= 8) {
         CELEG_GEMV_DISPATCH(1)
     }
     CELEG_GEMV_DISPATCH(2)
 #undef CELEG_GEMV_DISPATCH
+}
+
+CELEG_API int celeg_gemv_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int m, int n, int k,
+                              int mode, const float* conv_w, int taps, float* state, long long slot_stride,
+                              const int* span_slot, cudaStream_t stream) {
+    const GemvNormArgs none = {nullptr, 0, 0, 0.0f, 0, nullptr, nullptr, 0, nullptr, 0};
+    return gemv_checked(x, ldx, w, ldw, y, ldy, m, n, k, mode, conv_w, taps, state, slot_stride, span_slot, none, stream);
+}
+
+// The same product as one half of a split RMSNorm (see GemvNormArgs).
+//   sumsq_in != null: x is residual * norm weight, not yet scaled; the sums are multiplied by
+//     1 / sqrt(sum of the row's `partials_in` entries / width + eps) (any mode).
+//   next_w != null (mode 2 only): beside y += product, xw_out = bf16(y * next_w) and
+//     sumsq_out[row][block] = this block's share of sum(y^2) are written; the product has
+//     (n + 15) / 16 blocks, so sumsq_out_stride must be at least that.
+CELEG_API int celeg_gemv_bf16_split_norm(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int m, int n,
+                                         int k, int mode, const float* conv_w, int taps, float* state,
+                                         long long slot_stride, const int* span_slot, const float* sumsq_in,
+                                         int partials_in, int sumsq_in_stride, float eps, int width,
+                                         const float* next_w, void* xw_out, int ldxw, float* sumsq_out,
+                                         int sumsq_out_stride, cudaStream_t stream) {
+    CELEG_REQUIRE(!sumsq_in || (partials_in > 0 && sumsq_in_stride >= partials_in && eps > 0.0f && width > 0),
+                  "gemv_bf16: the row scale needs partials_in=%d <= stride=%d, eps > 0 and a width", partials_in,
+                  sumsq_in_stride);
+    CELEG_REQUIRE(!next_w || (mode == kGemvAddResidual && xw_out && sumsq_out && ldxw >= n &&
+                              sumsq_out_stride >= (n + 15) / 16),
+                  "gemv_bf16: the norm that follows can be prepared in mode 2 only, with outputs of ldxw=%d >= n=%d "
+                  "and a stride of at least %d sums", ldxw, n, (n + 15) / 16);
+    const GemvNormArgs norm = {sumsq_in, partials_in, sumsq_in_stride, eps, width,
+                               next_w, (__nv_bfloat16*)xw_out, ldxw, sumsq_out, sumsq_out_stride};
+    return gemv_checked(x, ldx, w, ldw, y, ldy, m, n, k, mode, conv_w, taps, state, slot_stride, span_slot, norm, stream);
 }

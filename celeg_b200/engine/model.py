@@ -177,14 +177,27 @@ class Model:
         if built is not None:
             built.run()
             return
-        kernels.embedding(self.embedding, step.token_ids[:step.tokens], self.residual,
-                          self.spec.embedding_multiplier)
+        blocks = [self.layers[entry.layer].block for entry in self.order]
+        firsts = [block.first_norm(step) if hasattr(block, "first_norm") else None for block in blocks]
+        head_norm = (self.final_norm if n_logits > 0 and step.logits_of_all_rows
+                     and rt.takes_split_norm(n_logits, self.head) else None)
+        first = stream.split(firsts[0], 1) if firsts and firsts[0] is not None and rt.small_batch(step.tokens) else None
+        if first is not None:
+            kernels.embedding(self.embedding, step.token_ids[:step.tokens], self.residual,
+                              self.spec.embedding_multiplier, prepare=first[1], next_weight=first[0])
+            stream.prepared = (firsts[0], first[1])
+        else:
+            kernels.embedding(self.embedding, step.token_ids[:step.tokens], self.residual,
+                              self.spec.embedding_multiplier)
         for position, entry in enumerate(self.order):
             layer = self.layers[entry.layer]
             if self._rebind and self.bindings[position] is not None:
                 layer.mixer.bind_cache(self.bindings[position])
+            stream.after_layer = firsts[position + 1] if position + 1 < len(blocks) else head_norm
             layer.block.run(stream, step)
+        stream.after_layer = None
         if n_logits == 0:
+            stream.prepared = None
             return
         if step.logits_of_all_rows:
             normed = stream.normed(self.final_norm, self.final_normed, n_logits)

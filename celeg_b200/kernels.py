@@ -55,6 +55,11 @@ _SIGNATURES = {
                                 c_void_p, c_void_p],
     "celeg_gemv_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_longlong, c_void_p, c_void_p],
+    "celeg_gemv_bf16_split_norm": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                   c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
+                                   c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
+    "celeg_embedding_split_norm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                                   c_void_p, c_int, c_void_p],
     "celeg_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                            c_void_p],
     "celeg_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -121,14 +126,34 @@ def _need(tensor: torch.Tensor, dtype: torch.dtype, name: str) -> None:
 
 
 # ------------------------------------------------------------------------------ wrappers
-def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, multiplier: float = 1.0) -> None:
+class SplitNorm:
+    """An RMSNorm split over the two products around it (csrc/gemv_bf16.cu, GemvNormArgs): ``xw`` holds
+    bfloat16 rows of residual * weight, ``sumsq[row, :partials]`` the pieces of each row's sum of squares;
+    the product that takes ``xw`` as its operand multiplies its sums by 1 / sqrt(sum / width + eps)."""
+    __slots__ = ("xw", "sumsq", "partials", "eps", "width")
+
+    def __init__(self, xw: torch.Tensor, sumsq: torch.Tensor, partials: int, eps: float, width: int):
+        self.xw, self.sumsq, self.partials, self.eps, self.width = xw, sumsq, partials, eps, width
+
+
+def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, multiplier: float = 1.0,
+              prepare: Optional[SplitNorm] = None, next_weight: Optional[torch.Tensor] = None) -> None:
+    """out[t] = multiplier * table[tokens[t]]. With ``prepare``: also the first half of the norm whose
+    weight is ``next_weight`` (``prepare.xw`` and one sum of squares per row are written)."""
     rows = tokens.shape[0]
     _need(tokens, torch.int32, "tokens")
     _need(out, torch.float32, "out")
     vocab, hidden = table.shape
     assert out.shape[0] >= rows and out.shape[1] == hidden
-    _check(library().celeg_embedding(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(out), rows, hidden,
-                                     vocab, multiplier, _stream()))
+    if prepare is None:
+        _check(library().celeg_embedding(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(out), rows, hidden,
+                                         vocab, multiplier, _stream()))
+        return
+    _need(next_weight, torch.float32, "next_weight")
+    assert prepare.xw.dtype == torch.bfloat16 and prepare.xw.stride(0) == hidden and prepare.partials == 1
+    _check(library().celeg_embedding_split_norm(
+        _ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(out), rows, hidden, vocab, multiplier,
+        _ptr(next_weight), _ptr(prepare.xw), _ptr(prepare.sumsq), prepare.sumsq.stride(0), _stream()))
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
@@ -241,24 +266,46 @@ def gemv_supported(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
 
-def gemv_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_STORE, *,
+def gemv_bf16(x, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_STORE, *,
               conv_w: Optional[torch.Tensor] = None, taps: int = 0, state: Optional[torch.Tensor] = None,
-              slot_stride: int = 0, span_slot: Optional[torch.Tensor] = None) -> None:
+              slot_stride: int = 0, span_slot: Optional[torch.Tensor] = None,
+              prepare: Optional[SplitNorm] = None, next_weight: Optional[torch.Tensor] = None) -> None:
     """y[:rows] = x[:rows] @ w.T for at most 16 rows, streaming w once. mode GEMV_STORE: y bfloat16;
     GEMV_STORE_F32: y float32; GEMV_ADD_RESIDUAL: y float32, accumulated; GEMV_SWIGLU: w is
     [2*inner, k] (gate rows, then up rows) and y bfloat16 [rows, inner] = silu(gate) * up; GEMV_CONV: w is
     [3*channels, k] (B, C, X rows of the short convolution's input projection), y bfloat16
     [rows, channels] = C * conv(B*X) over each request's carried state, which is shifted; row i is the
-    single token of request i, whose state slot is span_slot[i]."""
+    single token of request i, whose state slot is span_slot[i].
+    ``x`` may be a :class:`SplitNorm` (the operand still lacks its row scale; applied to the sums here).
+    With ``prepare`` (GEMV_ADD_RESIDUAL only): the first half of the norm that follows, weight
+    ``next_weight``, is written too: ``prepare.xw`` and this product's pieces of the sums of squares."""
     blocks = {GEMV_SWIGLU: 2, GEMV_CONV: 3}.get(mode, 1)
     n = w.shape[0] // blocks
     k = w.shape[1]
-    assert x.shape[-1] == k and y.shape[-1] >= n
+    scaled = x if isinstance(x, SplitNorm) else None
+    operand = scaled.xw if scaled is not None else x
+    assert operand.shape[-1] == k and y.shape[-1] >= n
     want = torch.float32 if mode in (GEMV_STORE_F32, GEMV_ADD_RESIDUAL) else torch.bfloat16
     if y.dtype != want:
         raise KernelLibraryError(f"gemv_bf16 mode {mode} writes {want}, got {y.dtype}")
-    _check(library().celeg_gemv_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(y), y.stride(0), rows, n, k,
-                                     mode, _ptr(conv_w), taps, _ptr(state), slot_stride, _ptr(span_slot), _stream()))
+    if scaled is None and prepare is None:
+        _check(library().celeg_gemv_bf16(_ptr(operand), operand.stride(0), _ptr(w), w.stride(0), _ptr(y), y.stride(0),
+                                         rows, n, k, mode, _ptr(conv_w), taps, _ptr(state), slot_stride,
+                                         _ptr(span_slot), _stream()))
+        return
+    if prepare is not None:
+        _need(next_weight, torch.float32, "next_weight")
+        if prepare.partials != (n + 15) // 16 or prepare.sumsq.stride(0) < prepare.partials:
+            raise KernelLibraryError(f"a product of {n} columns writes {(n + 15) // 16} pieces of the sums, "
+                                     f"not {prepare.partials}")
+    _check(library().celeg_gemv_bf16_split_norm(
+        _ptr(operand), operand.stride(0), _ptr(w), w.stride(0), _ptr(y), y.stride(0), rows, n, k, mode,
+        _ptr(conv_w), taps, _ptr(state), slot_stride, _ptr(span_slot),
+        _ptr(scaled.sumsq) if scaled else None, scaled.partials if scaled else 0,
+        scaled.sumsq.stride(0) if scaled else 0, scaled.eps if scaled else 0.0, scaled.width if scaled else 0,
+        _ptr(next_weight) if prepare else None, _ptr(prepare.xw) if prepare else None,
+        prepare.xw.stride(0) if prepare else 0, _ptr(prepare.sumsq) if prepare else None,
+        prepare.sumsq.stride(0) if prepare else 0, _stream()))
 
 
 TC_STORE, TC_STORE_F32, TC_SWIGLU = 0, 1, 2

@@ -2,6 +2,7 @@
 
     FeedForward(params, weights, parts, rt)
     forward(x, out, step)     x: normed activations [T, hidden]; writes the output to out
+    takes_split_norm(step)    optional, as for mixers
     emit_decode(builder, x, step)   optional: the same as operations of a decode program (parts/program.py)
 """
 from __future__ import annotations
@@ -30,6 +31,11 @@ class SwiGluFeedForward:
         self.w_down = rt.matrix(weights["down"])
         self.gate_up = rt.scratch("swiglu.gate_up", 2 * self.inner)
         self.activated = rt.scratch("swiglu.act", self.inner)
+
+    ends_with_product = True      # forward() writes `out` last, with rt.linear
+
+    def takes_split_norm(self, step: StepContext) -> bool:
+        return self.rt.takes_split_norm(step.tokens, self.w_gate_up)
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
         rt, t = self.rt, step.tokens

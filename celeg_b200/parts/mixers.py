@@ -5,6 +5,12 @@
     bind_cache(binding)                     PagedBinding or StateBinding from the cache storage
     forward(x, out, step)                   x: normed activations [T, hidden]; writes the
                                             mixer's output (to be added to the residual) to out
+    takes_split_norm(step) -> bool          optional: True if forward() hands x to the runtime's products
+                                            only, which can apply a row scale that x still lacks (then x
+                                            may be a kernels.SplitNorm instead of a tensor)
+    ends_with_product = True                optional: the last thing forward() does to ``out`` is
+                                            rt.linear(..., out, ...); the runtime may then add that product
+                                            to the residual stream itself and leave ``out`` unwritten
     emit_decode(builder, x, step)           optional: the same as operations of a decode program
                                             (parts/program.py) for steps of one token per request
 
@@ -92,6 +98,11 @@ class AttentionMixer:
         if binding.owner and self.reads_only:
             raise ValueError("an attention mixer without k/v projections cannot own a cache")
         self.binding = binding
+
+    ends_with_product = True      # forward() writes `out` last, with rt.linear
+
+    def takes_split_norm(self, step: StepContext) -> bool:
+        return self.rt.takes_split_norm(step.tokens, self.w_qkv)
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
         rt, b, t = self.rt, self.binding, step.tokens
@@ -207,6 +218,11 @@ class ShortConvMixer:
 
     def bind_cache(self, binding: StateBinding) -> None:
         self.binding = binding
+
+    ends_with_product = True      # forward() writes `out` last, with rt.linear
+
+    def takes_split_norm(self, step: StepContext) -> bool:
+        return self.rt.takes_split_norm(step.tokens, self.w_in)
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
         rt, t = self.rt, step.tokens

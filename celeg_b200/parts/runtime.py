@@ -11,30 +11,82 @@ import torch
 from .. import kernels
 
 
+class _Sink:
+    """Where a part is about to leave its output, and the norm that will read the stream next."""
+    __slots__ = ("buffer", "norm", "weight", "split", "used")
+
+    def __init__(self, buffer, norm, weight, split):
+        self.buffer, self.norm, self.weight, self.split, self.used = buffer, norm, weight, split, False
+
+
 class ResidualStream:
     """The float32 residual stream of one step, with what is still owed to it: a part writes its
     output to a buffer, the buffer becomes ``pending``, and it is added inside the next norm kernel
-    (residual add and norm are one launch)."""
+    (residual add and norm are one launch).
+
+    Steps of few rows on the bfloat16 path skip that launch: when the part that reads the stream next
+    takes a split norm (``takes_split_norm``), the product that ends a part adds to the stream itself
+    and prepares the norm that follows (``expect`` tells the runtime where that product will write),
+    and ``normed`` hands the next part a :class:`kernels.SplitNorm` instead of normalised rows."""
 
     def __init__(self, rt: "Runtime", hidden: int):
         self.rt = rt
         self.hidden = hidden
         self.residual = rt.scratch("stream.residual", hidden, torch.float32)
         self.pending: Optional[torch.Tensor] = None
+        self.prepared = None                    # (norm, SplitNorm) left by the last product
+        self.after_layer = None                 # the norm after the layer being run, if its reader takes a split norm
+        self.pieces = (hidden + 15) // 16
+        if rt.act_dtype == torch.bfloat16:
+            self.xw = rt.scratch("stream.split_norm", hidden, torch.bfloat16)
+            self.sumsq = torch.zeros((kernels.GEMV_MAX_ROWS, self.pieces), dtype=torch.float32, device=rt.device)
 
     def begin(self) -> None:
         self.pending = None
+        self.prepared = None
+        self.after_layer = None
+        self.rt.sink = None
 
-    def normed(self, norm, out: torch.Tensor, rows: int, gather: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def split(self, norm, pieces: int):
+        """(weight, SplitNorm) for a norm that can be split, else None."""
+        halves = norm.as_prologue() if hasattr(norm, "as_prologue") else None
+        if halves is None or self.rt.act_dtype != torch.bfloat16 or norm.width != self.hidden:
+            return None
+        weight, eps = halves
+        return weight, kernels.SplitNorm(self.xw, self.sumsq, pieces, eps, self.hidden)
+
+    def normed(self, norm, out: torch.Tensor, rows: int, gather: Optional[torch.Tensor] = None):
         """out = norm(stream + pending) for the first ``rows`` rows (or the gathered ones). Without
-        ``gather`` what was pending is added for good."""
+        ``gather`` what was pending is added for good. Returns ``out``, or the split norm that the
+        last product prepared for exactly this norm."""
+        if self.prepared is not None:
+            prepared_norm, split = self.prepared
+            self.prepared = None
+            if prepared_norm is norm and gather is None:
+                return split
+            raise RuntimeError("a norm was prepared for another reader than the one that asks")
         norm.add_norm(self.residual, self.pending, out, rows, rows=gather)
         if gather is None:
             self.pending = None
         return out
 
+    def expect(self, buffer: torch.Tensor, upcoming, rows: int) -> None:
+        """A part is about to write its output to ``buffer``; ``upcoming`` is the norm that reads the
+        stream after it (None when its reader wants normalised rows)."""
+        self.rt.sink = None
+        if upcoming is None or not self.rt.small_batch(rows):
+            return
+        halves = self.split(upcoming, self.pieces)
+        if halves is not None:
+            self.rt.sink = _Sink(buffer, upcoming, halves[0], halves[1])
+            self.rt.sink_residual = self.residual
+
     def add_later(self, delta: torch.Tensor) -> None:
         assert self.pending is None
+        sink, self.rt.sink = self.rt.sink, None
+        if sink is not None and sink.used:
+            self.prepared = (sink.norm, sink.split)          # the product has added to the stream already
+            return
         self.pending = delta
 
 
@@ -63,6 +115,9 @@ class Runtime:
         # per decode step): few rows mean few 128-row tiles, and the weight stream is spread over too few SMs
         self.tensor_core_min_rows = 256
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.sink: Optional[_Sink] = None         # set by the residual stream around a part's forward
+        self.sink_residual: Optional[torch.Tensor] = None
+        self.split_norms = os.environ.get("CELEG_B200_SPLIT_NORM", "1") != "0"
         self._flat: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         self._scratch: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         kernels.library()                       # fail now, not at the first step, if it is missing
@@ -92,6 +147,12 @@ class Runtime:
         """A small weight (norm scale, conv kernel) on the device in float32 (exact widening)."""
         return weight.to(device=self.device, dtype=torch.float32).contiguous()
 
+    def takes_split_norm(self, rows: int, weight: torch.Tensor) -> bool:
+        """Whether a product of ``rows`` rows with ``weight`` can take an operand that still lacks its
+        row scale (a :class:`kernels.SplitNorm`): only the small-batch kernel applies one."""
+        return (self.split_norms and self.small_batch(rows) and weight.dtype == torch.bfloat16
+                and weight.shape[1] % 8 == 0 and weight.stride(0) % 8 == 0)
+
     def small_batch(self, rows: int) -> bool:
         """Whether a step of ``rows`` tokens takes the fused small-batch products."""
         return (self.fuse_small_batches and self.act_dtype == torch.bfloat16 and
@@ -104,11 +165,22 @@ class Runtime:
         (src/backend/cuda/runtime/gemm_dispatcher.cpp:49-64); float32 accumulation everywhere."""
         if rows == 0:
             return
+        split = isinstance(x, kernels.SplitNorm)
+        operand = x.xw if split else x
         if self.act_dtype == torch.float32:
             kernels.gemm_f32(x, weight, out, rows)
-        elif kernels.gemv_supported(rows, x, weight):
+        elif kernels.gemv_supported(rows, operand, weight):
+            sink = self.sink
+            if sink is not None and out is sink.buffer and weight.shape[0] == self.sink_residual.shape[1]:
+                # the product that ends a part: added to the stream here, and the next norm prepared
+                kernels.gemv_bf16(x, weight, self.sink_residual, rows, kernels.GEMV_ADD_RESIDUAL,
+                                  prepare=sink.split, next_weight=sink.weight)
+                sink.used = True
+                return
             kernels.gemv_bf16(x, weight, out, rows,
                               kernels.GEMV_STORE_F32 if out.dtype == torch.float32 else kernels.GEMV_STORE)
+        elif split:
+            raise kernels.KernelLibraryError("an operand without its row scale reached a product that cannot apply it")
         elif self.tensor_core_products == "all" and kernels.gemm_tcgen05_supported(x, weight):
             kernels.gemm_tcgen05(x, weight, out, rows,
                                  kernels.TC_STORE_F32 if out.dtype == torch.float32 else kernels.TC_STORE,
@@ -125,7 +197,8 @@ class Runtime:
         product into ``scratch`` and the activation kernel."""
         if rows == 0:
             return
-        if self.act_dtype == torch.bfloat16 and kernels.gemv_supported(rows, x, gate_up_weight):
+        operand = x.xw if isinstance(x, kernels.SplitNorm) else x
+        if self.act_dtype == torch.bfloat16 and kernels.gemv_supported(rows, operand, gate_up_weight):
             kernels.gemv_bf16(x, gate_up_weight, out, rows, kernels.GEMV_SWIGLU)
             return
         if (self.act_dtype == torch.bfloat16 and kernels.gemm_tcgen05_supported(x, gate_up_weight)
@@ -143,8 +216,9 @@ class Runtime:
         and the caller has to run projection and convolution separately."""
         rows = step.tokens
         hidden = conv_kernel.shape[0]
+        operand = x.xw if isinstance(x, kernels.SplitNorm) else x
         if not (self.small_batch(rows) and step.max_span == 1 and step.spans == rows and taps <= 16
-                and kernels.gemv_supported(rows, x, in_weight)):
+                and kernels.gemv_supported(rows, operand, in_weight)):
             return False
         kernels.gemv_bf16(x, in_weight, out, rows, kernels.GEMV_CONV, conv_w=conv_kernel, taps=taps,
                           state=binding.state, slot_stride=binding.slot_stride, span_slot=step.span_slot)

@@ -397,7 +397,9 @@ def test_gemv_bf16_modes(m, n, k):
     before = rng.normal(size=(m, n)).astype(np.float32)
     res = dev(before)
     kernels.gemv_bf16(x_dev, w_dev, res, m, kernels.GEMV_ADD_RESIDUAL)
-    close(res, before.astype(np.float64) + want, torch.float32, scale=50 * math.sqrt(k))
+    # the product is rounded to bfloat16 as a stored product would be, then added in float32
+    err = np.abs(res.cpu().numpy() - (before.astype(np.float64) + want))
+    assert (err <= 2.0 ** -8 * np.abs(want) + 1e-5).all(), err.max()
     if n % 2 == 0:
         inner = n // 2
         act = torch.zeros((m, inner), dtype=torch.bfloat16, device="cuda")
@@ -405,6 +407,55 @@ def test_gemv_bf16_modes(m, n, k):
         gate = rounded(want[:, :inner], torch.bfloat16)
         up = rounded(want[:, inner:], torch.bfloat16)
         close(act, gate / (1 + np.exp(-gate)) * up, torch.bfloat16, scale=2.0)
+
+
+@pytest.mark.parametrize("m,width,inner", [(1, 64, 192), (8, 2048, 1024), (5, 80, 136), (16, 96, 256), (3, 40, 72)])
+def test_split_norm_over_two_products(m, width, inner):
+    """residual += x w_down^T; y = rmsnorm(residual) w_next^T, with the norm split over the two products
+    (no kernel of its own), against the formulas; also from the embedding as the first half."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(14)
+    eps = 1e-5
+    x = rounded(rng.normal(size=(m, inner)), torch.bfloat16)
+    w_down = rounded(rng.normal(size=(width, inner)) * 0.1, torch.bfloat16)
+    w_next = rounded(rng.normal(size=(48, width)) * 0.1, torch.bfloat16)
+    norm_w = (1.0 + 0.1 * rng.normal(size=width)).astype(np.float32)
+    before = rng.normal(size=(m, width)).astype(np.float32)
+    residual = dev(before)
+    pieces = (width + 15) // 16
+    split = kernels.SplitNorm(torch.zeros((m, width), dtype=torch.bfloat16, device="cuda"),
+                              torch.full((16, pieces + 3), 9.0, dtype=torch.float32, device="cuda"), pieces, eps, width)
+    kernels.gemv_bf16(dev(x, torch.bfloat16), dev(w_down, torch.bfloat16), residual, m, kernels.GEMV_ADD_RESIDUAL,
+                      prepare=split, next_weight=dev(norm_w))
+    delta = rounded(x @ w_down.T, torch.bfloat16)
+    want_residual = before.astype(np.float64) + delta
+    got_residual = residual.cpu().numpy().astype(np.float64)
+    assert np.abs(got_residual - want_residual).max() <= 2.0 ** -7 * np.abs(delta).max() + 1e-5
+    # judged against the residual the kernel really holds: the halves of the norm
+    sums = split.sumsq[:m, :pieces].sum(dim=1).cpu().numpy()
+    assert np.allclose(sums, (got_residual ** 2).sum(axis=1), rtol=1e-5)
+    close(split.xw, got_residual * norm_w, torch.bfloat16)
+    y = torch.zeros((m, 48), dtype=torch.float32, device="cuda")
+    kernels.gemv_bf16(split, dev(w_next, torch.bfloat16), y, m, kernels.GEMV_STORE_F32)
+    inv = 1.0 / np.sqrt((got_residual ** 2).mean(axis=1, keepdims=True) + eps)
+    want_y = (rounded(got_residual * norm_w, torch.bfloat16) * inv) @ w_next.T
+    close(y, want_y, torch.float32, scale=50 * math.sqrt(width))
+    # the whole norm, loosely: rounding before and after the scale differ
+    full = (rounded(got_residual * inv * norm_w, torch.bfloat16)) @ w_next.T
+    assert np.abs(y.cpu().numpy() - full).max() <= 0.02 * np.abs(full).max() + 1e-3
+
+    # the embedding as the first half
+    vocab = 50
+    table = rounded(rng.normal(size=(vocab, width)), torch.bfloat16)
+    tokens = rng.integers(0, vocab, size=m).astype(np.int32)
+    out = torch.zeros((m, width), dtype=torch.float32, device="cuda")
+    first = kernels.SplitNorm(torch.zeros((m, width), dtype=torch.bfloat16, device="cuda"),
+                              torch.zeros((16, pieces), dtype=torch.float32, device="cuda"), 1, eps, width)
+    kernels.embedding(dev(table, torch.bfloat16), dev(tokens, torch.int32), out, 2.0, prepare=first, next_weight=dev(norm_w))
+    rows = table[tokens] * 2.0
+    close(out, rows, torch.float32)
+    close(first.xw, rows * norm_w, torch.bfloat16)
+    assert np.allclose(first.sumsq[:m, 0].cpu().numpy(), (rows ** 2).sum(axis=1), rtol=1e-5)
 
 
 @pytest.mark.parametrize("m,hidden,k,taps", [(1, 64, 64, 3), (8, 2048, 2048, 3), (5, 40, 136, 4), (16, 48, 520, 2),
