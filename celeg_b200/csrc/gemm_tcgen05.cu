@@ -17,9 +17,7 @@
 //
 // celeg calls cuBLAS / cuBLASLt for these products (src/backend/cuda/runtime/gemm_dispatcher.cpp:49-64,
 // 171-190) and runs SwiGLU as a separate kernel (src/backend/cuda/kernels/qkv_rope.cuh:24-39).
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 #include <cstdlib>
 #include <mutex>
@@ -27,11 +25,7 @@
 
 namespace celeg_b200 {
 
-constexpr int kTileM = 128;
-constexpr int kTileK = 64;                 // 64 bf16 = 128 bytes: one swizzle row
-constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 128;
-constexpr unsigned kMaxPolls = 1u << 24;   // bounded waits; a healthy wait needs a few hundred polls
 
 enum TcEpilogue : int { kTcStoreBf16 = 0, kTcStoreF32 = 1, kTcSwiGlu = 2 };
 
@@ -41,99 +35,6 @@ struct TcGemmParams {
     int ldc;
     int* error_flag;
 };
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-// Polls until the phase with the given parity has completed; false after kMaxPolls polls.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    for (unsigned poll = 0; poll < kMaxPolls; ++poll) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(unsigned smem_dst, const CUtensorMap* map, unsigned bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
-            smem_dst),
-        "l"(map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(unsigned smem_result, unsigned columns) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_result), "r"(columns)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned columns) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(columns) : "memory");
-}
-
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b,
-                                          unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(
-            tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-// 32 consecutive float32 columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_load_32(unsigned taddr, float (&v)[32]) {
-    unsigned r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile written by TMA with the 128-byte swizzle: rows of
-// 128 bytes, groups of 8 rows 1024 bytes apart.
-__device__ __forceinline__ unsigned long long smem_descriptor(unsigned smem_addr) {
-    unsigned long long desc = 0;
-    desc |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);      // start address
-    desc |= (unsigned long long)1 << 16;                            // leading byte offset: unused with this swizzle
-    desc |= (unsigned long long)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
-    desc |= (unsigned long long)1 << 46;                            // descriptor version of this architecture
-    desc |= (unsigned long long)2 << 61;                            // 128-byte swizzle
-    return desc;
-}
-
-// Instruction descriptor: float32 accumulator, bfloat16 operands, both K-major, M x N tile.
-__host__ __device__ constexpr unsigned instruction_descriptor(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
-}
 
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(kGemmThreads)
@@ -509,8 +410,7 @@ struct MapKeyHash {
 };
 
 // A [rows, cols] bfloat16 matrix with `ld` elements between rows, read in boxes of box_rows x 64.
-static bool tensor_map_for(const void* base, long long rows, long long cols, long long ld, int box_rows,
-                           CUtensorMap* out) {
+bool tensor_map_for(const void* base, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
     static std::mutex mutex;
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     const MapKey key{base, rows, cols, ld, box_rows};

@@ -109,7 +109,9 @@ class Runtime:
         self.fuse_small_batches = True       # decode steps of few rows run the fused products
         # Products of more than 16 rows: "swiglu" = the gate|up product with its activation runs on this
         # package's tcgen05 kernel (faster than the library product followed by the activation kernel),
-        # the others on cuBLAS; "all" = every product on the tcgen05 kernel; "none" = cuBLAS only.
+        # the others on cuBLAS; "all" = every product on the tcgen05 kernel; "none" = cuBLAS only; "stream" =
+        # as "swiglu", and products of 17 to 128 rows on the weight-streaming tcgen05 kernel (slower than the
+        # library product as it stands; kept selectable for measurements).
         self.tensor_core_products = os.environ.get("CELEG_B200_TC_PRODUCTS", "swiglu")
         # below this many rows the library product still wins (measured at 64 rows: 1.16 against 1.37 ms
         # per decode step): few rows mean few 128-row tiles, and the weight stream is spread over too few SMs
@@ -181,6 +183,11 @@ class Runtime:
                               kernels.GEMV_STORE_F32 if out.dtype == torch.float32 else kernels.GEMV_STORE)
         elif split:
             raise kernels.KernelLibraryError("an operand without its row scale reached a product that cannot apply it")
+        elif (self.tensor_core_products == "stream" and rows <= kernels.STREAM_MAX_ROWS
+              and kernels.gemm_stream_supported(rows, x, weight)):
+            kernels.gemm_stream(x, weight, out, rows,
+                                kernels.GEMV_STORE_F32 if out.dtype == torch.float32 else kernels.GEMV_STORE,
+                                self.error_flag)
         elif self.tensor_core_products == "all" and kernels.gemm_tcgen05_supported(x, weight):
             kernels.gemm_tcgen05(x, weight, out, rows,
                                  kernels.TC_STORE_F32 if out.dtype == torch.float32 else kernels.TC_STORE,
@@ -201,9 +208,13 @@ class Runtime:
         if self.act_dtype == torch.bfloat16 and kernels.gemv_supported(rows, operand, gate_up_weight):
             kernels.gemv_bf16(x, gate_up_weight, out, rows, kernels.GEMV_SWIGLU)
             return
+        if (self.act_dtype == torch.bfloat16 and self.tensor_core_products == "stream"
+                and rows <= kernels.STREAM_MAX_ROWS and kernels.gemm_stream_supported(rows, x, gate_up_weight)):
+            kernels.gemm_stream(x, gate_up_weight, out, rows, kernels.GEMV_SWIGLU, self.error_flag)
+            return
         if (self.act_dtype == torch.bfloat16 and kernels.gemm_tcgen05_supported(x, gate_up_weight)
                 and (self.tensor_core_products == "all"
-                     or (self.tensor_core_products == "swiglu" and rows >= self.tensor_core_min_rows))):
+                     or (self.tensor_core_products in ("swiglu", "stream") and rows >= self.tensor_core_min_rows))):
             kernels.gemm_tcgen05(x, gate_up_weight, out, rows, kernels.TC_SWIGLU, self.error_flag)
             return
         self.linear(x, gate_up_weight, scratch, rows)

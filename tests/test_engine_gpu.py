@@ -518,3 +518,19 @@ def test_run_order_names_a_layer_twice_and_shares_a_cache(tmp_path):
         got = step.run([StepEntry("cut", sequence[at:at + n], list(range(n)))], auto_begin=True).cpu().numpy()
         assert np.abs(got - want[at:at + n]).max() < 3e-4, at
         at += n
+
+
+def test_decoding_twenty_requests_on_the_streaming_product(models, monkeypatch):
+    """CELEG_B200_TC_PRODUCTS=stream: steps of 17 to 128 rows run the weight-streaming tcgen05 product
+    with its fused epilogues (SwiGLU, short convolution); greedy tokens against the plain model."""
+    from celeg_b200 import Engine, EngineOptions
+    monkeypatch.setenv("CELEG_B200_TC_PRODUCTS", "stream")
+    folder, config, weights = models["B"]
+    prompts = prompts_of(config["vocab_size"], [6 + i for i in range(20)], seed=23)
+    engine = Engine(folder, dtype="bfloat16", options=EngineOptions(max_active_requests=20))
+    got = engine.generate(prompts, max_new_tokens=6, temperature=0.0, repetition_penalty=1.0, eos_tokens=())
+    agree = 0
+    for prompt, tokens in zip(prompts, got):
+        agree += tokens == plain_lfm2.generate(config, weights, prompt, 6, eos_tokens=())
+    assert agree >= 18, f"only {agree} of 20 requests decode the plain model's tokens"
+    engine.loaded.step.raise_on_device_error()

@@ -592,3 +592,84 @@ def test_gemm_tcgen05_store_and_swiglu(m, n, k, variant, monkeypatch):
         env["CELEG_B200_TC_VARIANT"] = variant
     result = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert result.returncode == 0 and "ok" in result.stdout, result.stdout + result.stderr
+
+
+@pytest.mark.parametrize("splits", [0, 1, 2, 8])
+@pytest.mark.parametrize("rows,n,k", [(64, 512, 1024), (17, 128, 64), (33, 100, 136), (128, 256, 2048), (96, 777, 520),
+                                      (20, 48, 72)])
+def test_gemm_stream_modes(rows, n, k, splits):
+    """The weight-streaming tcgen05 product (weights as the M side, k split over a cluster, partial
+    tiles added through distributed shared memory) in its store, add and SwiGLU modes."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(16)
+    lib = kernels.library()
+    lib.celeg_gemm_stream_set_splits(splits)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    try:
+        x = rounded(rng.normal(size=(rows + 2, k)), torch.bfloat16)
+        w = rounded(rng.normal(size=(n, k)) * 0.1, torch.bfloat16)
+        want = x[:rows] @ w.T
+        x_dev, w_dev = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+        assert kernels.gemm_stream_supported(rows, x_dev, w_dev)
+        y = torch.zeros((rows, n), dtype=torch.bfloat16, device="cuda")
+        kernels.gemm_stream(x_dev, w_dev, y, rows, kernels.GEMV_STORE, flag)
+        close(y, want, torch.bfloat16)
+        y32 = torch.full((rows, n), 7.0, dtype=torch.float32, device="cuda")
+        kernels.gemm_stream(x_dev, w_dev, y32, rows, kernels.GEMV_STORE_F32, flag)
+        close(y32, want, torch.float32, scale=50 * math.sqrt(k))
+        before = rng.normal(size=(rows, n)).astype(np.float32)
+        res = dev(before)
+        kernels.gemm_stream(x_dev, w_dev, res, rows, kernels.GEMV_ADD_RESIDUAL, flag)
+        err = np.abs(res.cpu().numpy() - (before.astype(np.float64) + want))
+        assert (err <= 2.0 ** -8 * np.abs(want) + 1e-5).all(), err.max()
+        if n % 2 == 0:
+            inner = n // 2
+            act = torch.zeros((rows, inner), dtype=torch.bfloat16, device="cuda")
+            kernels.gemm_stream(x_dev, w_dev, act, rows, kernels.GEMV_SWIGLU, flag)
+            gate = rounded(want[:, :inner], torch.bfloat16)
+            up = rounded(want[:, inner:], torch.bfloat16)
+            close(act, gate / (1 + np.exp(-gate)) * up, torch.bfloat16, scale=2.0)
+        assert int(flag.item()) == 0
+        # the same launch twice gives the same bits: the partial tiles are added in a fixed order
+        again = torch.zeros((rows, n), dtype=torch.float32, device="cuda")
+        kernels.gemm_stream(x_dev, w_dev, again, rows, kernels.GEMV_STORE_F32, flag)
+        assert torch.equal(again, y32)
+    finally:
+        lib.celeg_gemm_stream_set_splits(0)
+
+
+@pytest.mark.parametrize("rows,hidden,k,taps", [(20, 64, 64, 3), (64, 512, 1024, 3), (33, 40, 136, 4), (100, 48, 520, 2),
+                                                (17, 33, 64, 1)])
+def test_gemm_stream_conv_epilogue_matches_the_separate_kernels(rows, hidden, k, taps):
+    """Input projection + gate + taps over the carried state + state shift inside the streaming product,
+    against the library product followed by the span kernel, three decode steps in a row."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(17)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    w = dev(rounded(rng.normal(size=(3 * hidden, k)) * 0.1, torch.bfloat16), torch.bfloat16)
+    conv_w = dev(rng.normal(size=(hidden, taps)).astype(np.float32))
+    keep = taps - 1
+    slot_stride = keep * hidden + 8
+    slots = rng.permutation(rows + 5)[:rows].astype(np.int32)
+    state_a = dev(rng.normal(size=(rows + 5, slot_stride)).astype(np.float32))
+    state_b = state_a.clone()
+    span_slot = dev(slots)
+    token_span = dev(np.arange(rows, dtype=np.int32))
+    span_begin = dev(np.arange(rows + 1, dtype=np.int32))
+    for _ in range(3):
+        x = dev(rounded(rng.normal(size=(rows, k)), torch.bfloat16), torch.bfloat16)
+        fused = torch.zeros((rows, hidden), dtype=torch.bfloat16, device="cuda")
+        kernels.gemm_stream(x, w, fused, rows, kernels.GEMV_CONV, flag, conv_w=conv_w, taps=taps, state=state_a[:, 4:],
+                            slot_stride=slot_stride, span_slot=span_slot)
+        proj = torch.mm(x, w.t())
+        separate = torch.zeros((rows, hidden), dtype=torch.bfloat16, device="cuda")
+        kernels.short_conv(proj, conv_w, state_b[:, 4:], slot_stride, separate, token_span, span_begin, span_slot, rows,
+                           rows, hidden, taps)
+        # the two products sum in different orders, so B, C and X may each differ by one rounding of
+        # bfloat16 (2^-8 of their size) before they are multiplied: judged against the size of the outputs
+        got, want = fused.double().cpu().numpy(), separate.double().cpu().numpy()
+        size = np.sqrt((want ** 2).mean())
+        assert np.sqrt(((got - want) ** 2).mean()) <= 4e-3 * size
+        assert np.abs(got - want).max() <= 0.02 * np.abs(want).max()
+        assert torch.allclose(state_a, state_b, rtol=2e-2, atol=2e-2)
+    assert int(flag.item()) == 0
