@@ -30,10 +30,19 @@ class _Runner:
         return self.sampler.get_rng(slot)
 
     def run(self, entries: Sequence[StepEntry], sample_rows: Sequence[Tuple[int, SamplingParams]]) -> List[int]:
+        return self.collect(self.launch(entries, sample_rows))
+
+    def launch(self, entries: Sequence[StepEntry], sample_rows: Sequence[Tuple[int, SamplingParams]],
+               tokens_on_device: bool = False):
+        """Enqueues a step and its draw without waiting. ``tokens_on_device``: the entries' tokens are
+        placeholders, the real ones are what the launch before drew (same rows, same order)."""
         step = self.loaded.step
-        logits = step.run(entries)
+        logits = step.run(entries, token_source=self.sampler.out if tokens_on_device else None)
         self.sampler.mark_step(step.last_step)
-        return self.sampler.sample(logits, sample_rows)
+        return self.sampler.launch(logits, sample_rows)
+
+    def collect(self, handle) -> List[int]:
+        return self.sampler.read(handle)
 
 
 class Engine:

@@ -17,6 +17,7 @@ preempting one request instead of stalling (see :meth:`Scheduler._break_deadlock
 from __future__ import annotations
 
 import enum
+import os
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -155,6 +156,11 @@ class Scheduler:
         self.metrics = Metrics()
         self._next_id = 1
         self._hold_admission = False      # set by a preemption: the freed pages go to the others first
+        self._inflight = None             # (plan, handle) of a step that was enqueued and not yet collected
+        # one step of run-ahead needs a runner that can enqueue without waiting; CELEG_B200_RUN_AHEAD=0
+        # turns it off (for comparisons)
+        self._runs_ahead = (hasattr(runner, "launch") and hasattr(runner, "collect")
+                            and os.environ.get("CELEG_B200_RUN_AHEAD", "1") != "0")
 
     # ------------------------------------------------------------------ public
     def submit(self, prompt: Sequence[int], options: Optional[RequestOptions] = None) -> int:
@@ -212,22 +218,36 @@ class Scheduler:
         return True
 
     def has_work(self) -> bool:
-        return bool(self.queue or self.live)
+        return bool(self.queue or self.live or self._inflight is not None)
 
     # -------------------------------------------------------------------- step
     def step(self) -> bool:
         """One engine step: admit, run one batch, accept tokens, admit again. Returns whether
-        anything advanced."""
-        self._honour_cancellations()
-        if not self._hold_admission:
-            self._admit()
-        plan = self.plan()
-        if not plan.entries:
-            self._hold_admission = False
-            if self.live and self._break_deadlock():
-                return True
-            return False
-        progressed = self._execute(plan)
+        anything advanced.
+
+        When every live request is decoding and none can end this step except by an end-of-sequence
+        token, the step after is enqueued before this step's tokens are waited for: it takes its
+        input tokens from the device, where this step's draw left them, so the GPU does not idle
+        while the host reads tokens, decides and plans. A request that did end on this step's token
+        has then one more position computed in vain; its token of that step is dropped."""
+        if self._inflight is None:
+            self._honour_cancellations()
+            if not self._hold_admission:
+                self._admit()
+            plan = self.plan()
+            if not plan.entries:
+                self._hold_admission = False
+                if self.live and self._break_deadlock():
+                    return True
+                return False
+            if not self._launch(plan, tokens_on_device=False):
+                self._hold_admission = False
+                return True                                   # the launch failed; its requests have failed
+        plan, handle = self._inflight
+        self._inflight = None
+        if self._may_run_ahead(plan):
+            self._launch(self._plan_after(plan), tokens_on_device=True)
+        progressed = self._collect(plan, handle)
         self._hold_admission = False
         self._honour_cancellations()
         self._admit()
@@ -303,17 +323,62 @@ class Scheduler:
         return plan
 
     # --------------------------------------------------------------- execution
-    def _execute(self, plan: Plan) -> bool:
+    def _fail(self, plan: Plan, exc: Exception) -> None:
+        """Failure isolation: the requests of this step fail, others live on."""
+        for planned in plan.entries:
+            if not planned.request.status.terminal:
+                planned.request.error = f"{type(exc).__name__}: {exc}"
+                self._finish(planned.request, RequestStatus.FAILED)
+
+    def _launch(self, plan: Plan, tokens_on_device: bool) -> bool:
+        """Enqueues the plan's step (a runner without ``launch`` runs it to its end here)."""
         entries = [StepEntry(request_id=p.request.id, tokens=p.tokens,
                              want=[len(p.tokens) - 1] if p.samples else [])
                    for p in plan.entries]
         sample_rows = [(p.request.cache.slot, p.request.options.generation) for p in plan.entries if p.samples]
         try:
-            tokens = self.runner.run(entries, sample_rows)
-        except Exception as exc:        # failure isolation: the requests of this step fail, others live on
-            for planned in plan.entries:
-                planned.request.error = f"{type(exc).__name__}: {exc}"
-                self._finish(planned.request, RequestStatus.FAILED)
+            if self._runs_ahead:
+                handle = self.runner.launch(entries, sample_rows, tokens_on_device)
+            else:
+                handle = self.runner.run(entries, sample_rows)
+        except Exception as exc:
+            self._fail(plan, exc)
+            return False
+        self._inflight = (plan, handle)
+        return True
+
+    def _may_run_ahead(self, plan: Plan) -> bool:
+        """Whether the step after ``plan`` can be enqueued before the tokens of ``plan`` are known: the
+        same requests, one token each, whatever those tokens are (an end-of-sequence token aside)."""
+        if not self._runs_ahead or self.queue or plan.skipped_for_pages or len(plan.entries) != len(self.live):
+            return False
+        free = [group.pool.free_pages for group in self.manager.groups]
+        for planned in plan.entries:
+            request = planned.request
+            if not (planned.is_decode and planned.samples) or request.cancel_requested or request.cache is None:
+                return False
+            if len(request.generated) + 2 > request.options.max_new_tokens:
+                return False                          # this step's token may be its last
+            if request.cache.tokens + 1 > self.max_context:
+                return False
+            needed = self.manager.pages_needed(request.cache, request.cache.tokens + 1)
+            if any(n > f for n, f in zip(needed, free)):
+                return False
+            free = [f - n for f, n in zip(free, needed)]
+        return True
+
+    @staticmethod
+    def _plan_after(plan: Plan) -> Plan:
+        after = Plan()
+        after.entries = [PlannedEntry(p.request, [0], samples=True, is_decode=True) for p in plan.entries]
+        return after
+
+    def _collect(self, plan: Plan, handle) -> bool:
+        """Waits for the plan's tokens and accepts them."""
+        try:
+            tokens = self.runner.collect(handle) if self._runs_ahead else handle
+        except Exception as exc:
+            self._fail(plan, exc)
             return True
         now = time.monotonic()
         self.metrics.steps += 1
@@ -324,6 +389,9 @@ class Scheduler:
         produced = iter(tokens)
         for planned in plan.entries:
             request = planned.request
+            token = int(next(produced)) if planned.samples else None
+            if request.status.terminal:
+                continue                  # ended while this step was in flight: the position was computed in vain
             if planned.is_decode:
                 self.metrics.decode_tokens += 1
             else:
@@ -332,7 +400,7 @@ class Scheduler:
             if planned.samples:
                 if request.status is RequestStatus.PREFILL:
                     request.status = RequestStatus.DECODING
-                self._accept(request, int(next(produced)), now)
+                self._accept(request, token, now)
         return True
 
     def _accept(self, request: Request, token: int, now: float) -> None:

@@ -92,7 +92,8 @@ class StepFunction:
         return self.manager.get(request_id).tokens
 
     # ---------------------------------------------------------------------- step
-    def run(self, entries: Sequence[StepEntry], auto_begin: bool = False) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], auto_begin: bool = False,
+            token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Returns float32 logits [wanted, vocab] in the order of the entries and of ``want``.
         The tensor is a view of a buffer that the next call overwrites."""
         vocab = self.model.vocab_size
@@ -161,6 +162,12 @@ class StepFunction:
         self._host_np = self._host.numpy()
         step, logit_rows, n_words = self._stage(entries, caches, total, spans, wanted, stride, max_ctx)
         self._dev[:n_words].copy_(self._host[:n_words], non_blocking=True)
+        if token_source is not None:
+            # the tokens of this step are on the device already (what the step before drew): token i of
+            # the step is token_source[i]; the entries carry placeholders
+            if token_source.dtype != torch.int32 or token_source.numel() < total:
+                raise StepInputError("a token source must hold one int32 token for every token of the step")
+            step.token_ids.copy_(token_source[:total], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self._ring_events[slot] = event

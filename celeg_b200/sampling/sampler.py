@@ -30,6 +30,8 @@ class Sampler:
         self._partial_score = torch.zeros(max_rows * 64, dtype=torch.float32, device=device)
         self._partial_token = torch.zeros(max_rows * 64, dtype=torch.int32, device=device)
         self._out_host = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
+        self._out_hosts = [self._out_host, torch.zeros(max_rows, dtype=torch.int32).pin_memory()]
+        self._flip = 0
         self._staged = None
         self._all_greedy = False
 
@@ -51,9 +53,24 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[int, SamplingParams]]) -> List[int]:
         """One token per row of ``logits``; ``rows[i]`` = (state slot, options). Synchronises."""
-        count = len(rows)
+        return self.read(self.launch(logits, rows))
+
+    def read(self, handle) -> List[int]:
+        """Waits for a launched draw (only for it, not for what was enqueued later) and returns its tokens."""
+        event, host, count = handle
         if count == 0:
             return []
+        event.synchronize()
+        return host[:count].tolist()
+
+    def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[int, SamplingParams]]):
+        """Enqueues the draw and the copy of the tokens to pinned host memory; :meth:`read` returns
+        them. ``self.out[:len(rows)]`` holds them on the device until the next launch (a following step
+        may take its input tokens from there). At most two launches may be unread at a time, and the
+        rows or their options may change only when none is."""
+        count = len(rows)
+        if count == 0:
+            return None, None, 0
         if count > self.max_rows:
             raise ValueError(f"{count} rows to sample, the sampler was sized for {self.max_rows}")
         m = self.max_rows
@@ -78,6 +95,9 @@ class Sampler:
         else:
             kernels.sample(logits, count, self._dev_i[:m], self.seen, self.rng, self._dev_f[:m], self._dev_i[m:],
                            self._dev_f[m:2 * m], self._dev_f[2 * m:], self.out)
-        self._out_host.copy_(self.out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._out_host[:count].tolist()
+        host = self._out_hosts[self._flip]
+        self._flip ^= 1
+        host.copy_(self.out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return event, host, count

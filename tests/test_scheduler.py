@@ -243,3 +243,133 @@ def test_poll_in_pieces_and_metrics():
     assert metrics.decode_tokens == 5 and metrics.ttft_count == 1 and metrics.itl_count == 5
     with pytest.raises(KeyError):
         scheduler.poll(999)
+
+
+# ----------------------------------------------------------------------------------- run-ahead
+class AheadRunner(FakeRunner):
+    """A runner that can enqueue a step without waiting for it: the step function's host side
+    (reserve, advance) happens at launch, the tokens are computed when they are collected, and
+    a launch with ``tokens_on_device`` takes its input tokens from the draw of the launch before."""
+
+    def __init__(self, manager):
+        super().__init__(manager)
+        self.pending = []            # launched, not collected: (entries as lists, slots, from_device)
+        self.last_drawn = []         # what the latest collected-or-not launch drew, per row (filled at collect)
+        self.log = []
+
+    def launch(self, entries, sample_rows, tokens_on_device=False):
+        if self.fail_next:
+            self.fail_next = False
+            raise RuntimeError("injected step failure")
+        assert len(self.pending) <= 1, "more than two steps in flight"
+        rows = []
+        for entry in entries:
+            cache = self.manager.get(entry.request_id)
+            self.manager.reserve(cache, cache.tokens + len(entry.tokens))
+            self.manager.advance(cache, cache.tokens + len(entry.tokens))
+            rows.append((entry.request_id, cache.slot, list(entry.tokens), list(entry.want)))
+        handle = {"rows": rows, "from_device": tokens_on_device, "after": self.pending[-1] if self.pending else None}
+        self.pending.append(handle)
+        self.log.append(("launch", tokens_on_device, [r[0] for r in rows]))
+        return handle
+
+    def collect(self, handle):
+        assert self.pending and self.pending[0] is handle, "collected out of order"
+        self.pending.pop(0)
+        self.log.append(("collect", [r[0] for r in handle["rows"]]))
+        if handle["from_device"]:
+            before = handle["after"]["drawn"]
+            assert len(before) == len(handle["rows"])
+        out = []
+        for index, (request_id, slot, tokens, want) in enumerate(handle["rows"]):
+            if handle["from_device"]:
+                tokens = [before[index]]
+            self.history[slot].extend(tokens)
+            if want:
+                self.generator[slot] += 1
+                out.append((sum(self.history[slot]) + self.generator[slot]) % 50 + 10)
+        handle["drawn"] = out
+        return out
+
+
+def make_ahead(pages=64, page_tokens=4, slots=4, **option_overrides):
+    options = EngineOptions(max_active_requests=slots, max_batched_tokens=16, prefill_chunk_tokens=8,
+                            page_tokens=page_tokens, **option_overrides)
+    manager = CacheManager(page_tokens, [pages], [(("kv",), PagedNeed(1, 8, None))], StateLayout(), slots)
+    runner = AheadRunner(manager)
+    return Scheduler(manager, runner, options, max_context=128, vocab_size=100, default_eos=(7,)), runner, manager
+
+
+def test_run_ahead_gives_the_same_tokens_and_overlaps_steps():
+    scheduler, runner, manager = make_ahead()
+    prompts = [[3, 4, 5], [9, 1], [2, 2, 2, 2, 2]]
+    ids = [scheduler.submit(p, RequestOptions(max_new_tokens=9, eos_tokens=())) for p in prompts]
+    run_all(scheduler)
+    for request_id, prompt in zip(ids, prompts):
+        assert scheduler.poll(request_id).tokens == expected_output(prompt, 9, eos=())
+    # while all three decode, the next step is launched before the tokens of the last are collected
+    ahead = [i for i, entry in enumerate(runner.log) if entry[0] == "launch" and entry[1]]
+    assert len(ahead) >= 5
+    for i in ahead:                                      # each of them was enqueued before the collect of the step before
+        assert runner.log[i + 1][0] == "collect"
+    assert not runner.pending
+    assert manager.free_slots == 4
+    manager.check_invariants()
+
+
+def test_run_ahead_drops_the_token_after_an_end_of_sequence():
+    scheduler, runner, manager = make_ahead()
+    prompt = [3, 4, 5]
+    reference = expected_output(prompt, 30, eos=())
+    stop = reference[4]                                  # the fifth token ends the request
+    request_id = scheduler.submit(prompt, RequestOptions(max_new_tokens=30, eos_tokens=(stop,)))
+    other = scheduler.submit([8, 8], RequestOptions(max_new_tokens=12, eos_tokens=()))
+    run_all(scheduler)
+    assert scheduler.poll(request_id).tokens == reference[:reference.index(stop) + 1]
+    assert scheduler.poll(other).tokens == expected_output([8, 8], 12, eos=())
+    assert scheduler.status(request_id) is RequestStatus.FINISHED
+    assert not runner.pending and manager.free_slots == 4
+    manager.check_invariants()
+
+
+def test_no_run_ahead_while_requests_wait_or_prefill_or_are_about_to_end():
+    scheduler, runner, manager = make_ahead(slots=1)
+    first = scheduler.submit([1, 2, 3], RequestOptions(max_new_tokens=4, eos_tokens=()))
+    second = scheduler.submit([4, 5], RequestOptions(max_new_tokens=3, eos_tokens=()))      # waits for the slot
+    run_all(scheduler)
+    assert scheduler.poll(first).tokens == expected_output([1, 2, 3], 4, eos=())
+    assert scheduler.poll(second).tokens == expected_output([4, 5], 3, eos=())
+    # with a request queued the scheduler never ran ahead for the first; for the second it may only
+    # while two more tokens are certain
+    first_launches = [entry for entry in runner.log if entry[0] == "launch" and entry[2] == [first]]
+    assert not any(entry[1] for entry in first_launches)
+    manager.check_invariants()
+
+
+def test_run_ahead_with_cancellation_and_failure():
+    scheduler, runner, manager = make_ahead()
+    a = scheduler.submit([1, 2, 3], RequestOptions(max_new_tokens=20, eos_tokens=()))
+    b = scheduler.submit([4, 5, 6], RequestOptions(max_new_tokens=20, eos_tokens=()))
+    for _ in range(4):
+        scheduler.step()
+    scheduler.cancel(a)                                  # a step with a in it is in flight
+    for _ in range(3):
+        scheduler.step()
+    assert scheduler.status(a) is RequestStatus.CANCELLED
+    got = scheduler.poll(b).tokens
+    assert got == expected_output([4, 5, 6], 20, eos=())[:len(got)] and len(got) >= 5
+    runner.fail_next = True
+    while scheduler.has_work():
+        scheduler.step()
+    assert scheduler.status(b) in (RequestStatus.FAILED, RequestStatus.FINISHED)
+    assert manager.free_slots == 4
+    manager.check_invariants()
+
+
+def test_run_ahead_can_be_switched_off(monkeypatch):
+    monkeypatch.setenv("CELEG_B200_RUN_AHEAD", "0")
+    scheduler, runner, manager = make_ahead()
+    request_id = scheduler.submit([3, 4, 5], RequestOptions(max_new_tokens=6, eos_tokens=()))
+    run_all(scheduler)
+    assert scheduler.poll(request_id).tokens == expected_output([3, 4, 5], 6, eos=())
+    assert not any(entry[0] == "launch" for entry in runner.log)        # the plain run() path
