@@ -13,6 +13,86 @@ __global__ void qk_norm_rope_store_kernel(A* qkv, A* k_cache, A* v_cache, const 
     qk_norm_rope_unit<A>(qkv, k_cache, v_cache, args, unit, threadIdx.x & 31);
 }
 
+// The common shape (rotation over the whole head, head size 64, 128 or 256, many tokens): a warp takes
+// one token and a run of its heads, so the angles' sine and cosine, which depend on the position and the
+// pair only, are computed once for the run instead of once per head (they were most of the instructions
+// of the per-head kernel), and the page of the token is looked up once. Same arithmetic per element.
+template <typename A, int PAIRS>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_tokens_kernel(A* qkv, A* k_cache, A* v_cache, const QkNormRopeArgs a, const int run) {
+    chain_release();
+    chain_wait();
+    const int lane = threadIdx.x & 31;
+    const int heads = a.q_heads + 2 * a.kv_heads;
+    const int runs = (heads + run - 1) / run;
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= (long long)a.tokens * runs) return;
+    const int t = (int)(unit / runs);
+    const int h_begin = (int)(unit % runs) * run;
+    const int h_end = min(heads, h_begin + run);
+    constexpr int kHead = PAIRS * 64, kHalf = PAIRS * 32;
+    const int pos = a.positions[t];
+    float sn[PAIRS], cs[PAIRS];
+#pragma unroll
+    for (int j = 0; j < PAIRS; ++j) sincosf((float)pos * a.inv_freq[lane + 32 * j], &sn[j], &cs[j]);
+    long long cache_row = -1;                       // offset of (page, kv head 0, slot in page), in elements
+    if (a.store_kv && h_end > a.q_heads) {
+        const int page = a.block_table[(size_t)a.token_span[t] * a.table_stride + pos / a.page_tokens];
+        if (page < 0) {                             // the host never builds such a table
+            if (lane == 0) atomicExch(a.error_flag, 1);
+        } else {
+            cache_row = (long long)page * a.page_stride + (long long)(pos % a.page_tokens) * kHead;
+        }
+    }
+    for (int h = h_begin; h < h_end; ++h) {
+        A* vec = qkv + ((size_t)t * heads + h) * kHead;
+        const bool is_q = h < a.q_heads;
+        const bool is_k = !is_q && h < a.q_heads + a.kv_heads;
+        A* dst = vec;
+        if (!is_q) {
+            if (cache_row < 0) continue;
+            const int kvh = is_k ? h - a.q_heads : h - a.q_heads - a.kv_heads;
+            dst = (is_k ? k_cache : v_cache) + cache_row + (size_t)kvh * a.page_tokens * kHead;
+        }
+        float x[PAIRS], y[PAIRS];
+#pragma unroll
+        for (int j = 0; j < PAIRS; ++j) {
+            x[j] = to_float(load_l2(vec + lane + 32 * j));
+            y[j] = to_float(load_l2(vec + lane + 32 * j + kHalf));
+        }
+        if (!is_q && !is_k) {                       // v: plain copy
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                dst[lane + 32 * j] = from_float<A>(x[j]);
+                dst[lane + 32 * j + kHalf] = from_float<A>(y[j]);
+            }
+            continue;
+        }
+        const float* weight = is_q ? a.q_weight : a.k_weight;
+        float scale = 1.0f;
+        if (weight) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) sum += x[j] * x[j];
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) sum += y[j] * y[j];
+            sum = warp_sum(sum);
+            scale = 1.0f / sqrtf(sum / (float)kHead + a.eps);
+        }
+#pragma unroll
+        for (int j = 0; j < PAIRS; ++j) {
+            const int i = lane + 32 * j;
+            float u = x[j], v = y[j];
+            if (weight) {
+                u = u * scale * weight[i];
+                v = v * scale * weight[i + kHalf];
+            }
+            dst[i] = from_float<A>(u * cs[j] - v * sn[j]);
+            dst[i + kHalf] = from_float<A>(v * cs[j] + u * sn[j]);
+        }
+    }
+}
+
 }  // namespace celeg_b200
 
 using namespace celeg_b200;
@@ -38,6 +118,23 @@ CELEG_API int celeg_qk_norm_rope_store(void* qkv, const float* q_weight, const f
     const QkNormRopeArgs args = {q_weight, k_weight, inv_freq, positions, token_span, block_table, table_stride,
                                  page_stride, tokens, q_heads, kv_heads, head_dim, rotary_dim, page_tokens, eps,
                                  store_kv, error_flag};
+    // many tokens of the common shape: a warp per token and run of eight heads
+    if (act_dtype == kBFloat16 && inv_freq && rotary_dim == head_dim && tokens >= 64 &&
+        (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
+        const int run = 8;
+        const long long runs = (long long)tokens * ((q_heads + 2 * kv_heads + run - 1) / run);
+        const unsigned run_blocks = (unsigned)((runs + warps - 1) / warps);
+        __nv_bfloat16* q = (__nv_bfloat16*)qkv;
+        __nv_bfloat16* kc = (__nv_bfloat16*)k_cache;
+        __nv_bfloat16* vc = (__nv_bfloat16*)v_cache;
+        if (head_dim == 64)
+            launch_chained(qk_norm_rope_tokens_kernel<__nv_bfloat16, 1>, run_blocks, warps * 32, 0, stream, q, kc, vc, args, run);
+        else if (head_dim == 128)
+            launch_chained(qk_norm_rope_tokens_kernel<__nv_bfloat16, 2>, run_blocks, warps * 32, 0, stream, q, kc, vc, args, run);
+        else
+            launch_chained(qk_norm_rope_tokens_kernel<__nv_bfloat16, 4>, run_blocks, warps * 32, 0, stream, q, kc, vc, args, run);
+        return check_launch("qk_norm_rope_store");
+    }
     if (act_dtype == kFloat32)
         launch_chained(qk_norm_rope_store_kernel<float>, blocks, warps * 32, 0, stream, (float*)qkv,
                        (float*)k_cache, (float*)v_cache, args);

@@ -85,6 +85,47 @@ __device__ __forceinline__ void qk_norm_rope_unit(A* qkv, A* k_cache, A* v_cache
         return;
     }
     const float* weight = is_q ? q_weight : k_weight;
+    if (inv_freq && rotary_dim == head_dim && (head_dim & 63) == 0 && head_dim <= 256) {
+        // the common shape in one pass: a lane holds its pairs (i, i + half) in registers between the
+        // sum of squares and the rotation, so the row is read once and every load is in flight at once
+        // (same arithmetic, in the same order, as the general path below)
+        const int half_dim = head_dim >> 1;
+        const int pairs = head_dim >> 6;                       // per lane: 1, 2 or 4
+        float a[4], b[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = lane + 32 * j;
+            a[j] = j < pairs ? to_float(load_l2(vec + i)) : 0.0f;
+            b[j] = j < pairs ? to_float(load_l2(vec + i + half_dim)) : 0.0f;
+        }
+        float scale = 1.0f;
+        if (weight) {
+            // the general path adds x^2 over i = lane, lane + 32, ...: first the a's, then the b's
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sum += a[j] * a[j];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sum += b[j] * b[j];
+            sum = warp_sum(sum);
+            scale = 1.0f / sqrtf(sum / (float)head_dim + eps);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (j < pairs) {
+                const int i = lane + 32 * j;
+                float x = a[j], y = b[j];
+                if (weight) {
+                    x = x * scale * weight[i];
+                    y = y * scale * weight[i + half_dim];
+                }
+                float sn, cs;
+                sincosf((float)pos * inv_freq[i], &sn, &cs);
+                dst[i] = from_float<A>(x * cs - y * sn);
+                dst[i + half_dim] = from_float<A>(y * cs + x * sn);
+            }
+        }
+        return;
+    }
     float inv = 1.0f;
     if (weight) {
         float sum = 0.0f;

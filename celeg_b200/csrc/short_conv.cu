@@ -91,6 +91,86 @@ __global__ void short_conv_tokens_bf16x8_kernel(const __nv_bfloat16* proj, const
     *reinterpret_cast<uint4*>(out + (size_t)t * hidden + c) = r;
 }
 
+// The same again for kernels of at most four taps (LFM2 has three): a thread keeps the weights of its
+// eight channels in registers and walks over kTokensPerThread consecutive tokens with a sliding
+// window of B*X, so a row of the projection is read 1.4 times instead of `taps` times and all loads of a
+// thread are in flight together. Taps are added in the same order as in the kernels above.
+constexpr int kTokensPerThread = 8;
+constexpr int kFewTaps = 4;
+
+__global__ void __launch_bounds__(128)
+short_conv_tokens_window_kernel(const __nv_bfloat16* proj, const float* __restrict__ kernel, __nv_bfloat16* out,
+                                const int* token_span, const int* span_begin, int hidden, int taps, int tokens) {
+    chain_release();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= hidden) return;
+    float w[kFewTaps][8];                        // w[e]: the tap that meets the token e places back (tap taps-1-e)
+#pragma unroll
+    for (int e = 0; e < kFewTaps; ++e)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[e][i] = e < taps ? kernel[(size_t)(c + i) * taps + (taps - 1 - e)] : 0.0f;
+    chain_wait();
+    const int t0 = blockIdx.y * kTokensPerThread;
+    const size_t row = (size_t)3 * hidden;
+    const int keep = taps - 1;
+    constexpr int kRows = kTokensPerThread + kFewTaps - 1;
+    // rows t0 - keep .. t0 + kTokensPerThread - 1 of B and X (rows before the batch or past it: not loaded)
+    uint4 b4[kRows], x4[kRows], c4[kTokensPerThread];
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        const int t = t0 - (kFewTaps - 1) + r;
+        const bool wanted = t >= t0 - keep && t >= 0 && t < tokens;
+        b4[r] = wanted ? *reinterpret_cast<const uint4*>(proj + (size_t)t * row + c) : zero;
+        x4[r] = wanted ? *reinterpret_cast<const uint4*>(proj + (size_t)t * row + 2 * hidden + c) : zero;
+    }
+    int first[kTokensPerThread];
+#pragma unroll
+    for (int j = 0; j < kTokensPerThread; ++j) {
+        const int t = t0 + j;
+        c4[j] = t < tokens ? *reinterpret_cast<const uint4*>(proj + (size_t)t * row + hidden + c) : zero;
+        first[j] = t < tokens ? span_begin[token_span[t]] : t + 1;
+    }
+    float bx[kRows][8];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b4[r]);
+        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x4[r]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 b = __bfloat1622float2(b2[i]);
+            const float2 x = __bfloat1622float2(x2[i]);
+            bx[r][2 * i] = b.x * x.x;
+            bx[r][2 * i + 1] = b.y * x.y;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kTokensPerThread; ++j) {
+        const int t = t0 + j;
+        if (t >= tokens || t - first[j] < keep) continue;      // the span kernel's tokens
+        float conv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) conv[i] = 0.0f;
+        // oldest tap first, as everywhere: the token e places back is row j + (kFewTaps - 1) - e
+#pragma unroll
+        for (int e = kFewTaps - 1; e >= 0; --e) {
+            if (e < taps) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) conv[i] += w[e][i] * bx[j + (kFewTaps - 1) - e][i];
+            }
+        }
+        const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&c4[j]);
+        uint4 result;
+        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&result);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 cc = __bfloat1622float2(c2[i]);
+            r2[i] = __floats2bfloat162_rn(cc.x * conv[2 * i], cc.y * conv[2 * i + 1]);
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)t * hidden + c) = result;
+    }
+}
+
 // Everything that touches a request's state: the first taps-1 tokens of its span and the slot's new
 // content, one thread per (span, channel), which reads the old state into registers before it writes.
 template <typename A>
@@ -168,7 +248,13 @@ CELEG_API int celeg_short_conv(const void* proj, const float* kernel, float* sta
                        span_slot, hidden, taps);
     int status = check_launch("short_conv (spans)");
     if (status != 0 || max_span <= taps - 1) return status;       // no token lies past the first taps-1 of its span
-    if (act_dtype == kBFloat16 && hidden % 8 == 0 && ((((size_t)proj) | ((size_t)out)) & 15) == 0) {
+    if (act_dtype == kBFloat16 && hidden % 8 == 0 && ((((size_t)proj) | ((size_t)out)) & 15) == 0 && taps <= kFewTaps &&
+        tokens >= 4 * kTokensPerThread) {
+        const int vec_threads = hidden / 8 >= 128 ? 128 : ((hidden / 8 + 31) / 32) * 32;
+        dim3 grid((hidden / 8 + vec_threads - 1) / vec_threads, (tokens + kTokensPerThread - 1) / kTokensPerThread);
+        launch_chained(short_conv_tokens_window_kernel, grid, vec_threads, 0, stream, (const __nv_bfloat16*)proj, kernel,
+                       (__nv_bfloat16*)out, token_span, span_begin, hidden, taps, tokens);
+    } else if (act_dtype == kBFloat16 && hidden % 8 == 0 && ((((size_t)proj) | ((size_t)out)) & 15) == 0) {
         const int vec_threads = hidden / 8 >= 128 ? 128 : ((hidden / 8 + 31) / 32) * 32;
         dim3 grid((hidden / 8 + vec_threads - 1) / vec_threads, tokens);
         launch_chained(short_conv_tokens_bf16x8_kernel, grid, vec_threads, 0, stream, (const __nv_bfloat16*)proj, kernel,

@@ -220,16 +220,21 @@ def test_attention_generic(dtype, heads, kv_heads, head_dim, page_tokens, window
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,theta,eps", [
-    (4, 2, 16, 16, 1e4, 1e-5), (3, 1, 32, 8, 1e6, 1e-6), (5, 5, 48, 16, 5e4, 3e-6), (2, 2, 80, 32, 1e6, 1e-5),
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,theta,eps,count", [
+    (4, 2, 16, 16, 1e4, 1e-5, (9, 5, 1)), (3, 1, 32, 8, 1e6, 1e-6, (9, 5, 1)), (5, 5, 48, 16, 5e4, 3e-6, (9, 5, 1)),
+    (2, 2, 80, 32, 1e6, 1e-5, (9, 5, 1)),
+    # head sizes of 64, 128 and 256: the one-pass form per head (few tokens) and the kernel that takes a
+    # token and a run of eight heads per warp (64 tokens and more, bfloat16), heads that do not fill the runs
+    (4, 2, 64, 16, 1e6, 1e-5, (9, 5, 1)), (5, 1, 64, 16, 1e6, 1e-5, (70, 40, 1)), (9, 3, 128, 16, 1e4, 1e-6, (33, 64, 2)),
+    (2, 2, 256, 32, 5e4, 1e-5, (60, 10, 1)), (32, 8, 64, 16, 1e6, 1e-5, (100, 3, 1)),
 ])
-def test_qk_norm_rope_store(dtype, heads, kv_heads, head_dim, page_tokens, theta, eps):
+def test_qk_norm_rope_store(dtype, heads, kv_heads, head_dim, page_tokens, theta, eps, count):
     from celeg_b200 import kernels
     rng = np.random.default_rng(6)
     start = [37, 0, 255]
-    count = [9, 5, 1]
+    count = list(count)
     tokens = sum(count)
-    pages = 40
+    pages = 60
     width = (heads + 2 * kv_heads) * head_dim
     qkv = rounded(rng.normal(size=(tokens, width)), dtype)
     q_w = (1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32).astype(np.float64)
