@@ -1,0 +1,349 @@
+// Paged causal grouped-query attention for prompt portions on Blackwell's fifth-generation tensor
+// cores, for a head size of 64 (bfloat16):
+//
+//   grid = (query tiles, query heads); a query tile is up to 128 consecutive tokens of one span.
+//   Six warps. Warp 0 brings Q (one box of 128 rows x 64) and, per block of 64 keys, the K and V
+//   rows page by page through the request's block table into a two-stage ring by TMA (128-byte
+//   swizzle; a page is one box of page_tokens rows x 64). Warp 1 issues the MMAs:
+//       S[128 x 64] = Q K^T           (tcgen05.mma M128 N64 K16 x 4, both operands K-major)
+//       O'[128 x 64] = P V            (M128 N64 K16 x 4, P K-major from shared memory, V as it lies in
+//                                      the cache, keys x 64: the MN-major form of the B operand)
+//   with S and O' in tensor memory (128 columns a block, 64 KiB of shared memory: two to three blocks per
+//   SM, so one block's MMAs run under another's softmax). Warps 2-5 are the softmax: a thread owns one
+//   query row (its TMEM lane), reads S with tcgen05.ld, scales, masks (causal, window, rows past the span;
+//   blocks that every row sees whole skip the mask), keeps the running
+//   maximum and denominator in float32 (exponentials by exp2 of pre-scaled scores), writes P as
+//   bfloat16 into shared memory in the swizzled layout the MMA reads, and adds O' into its row of the
+//   output, which it keeps in registers, rescaled by the usual correction. No shuffles: a row is
+//   one thread.
+//   Every wait on an mbarrier is bounded (tcgen05.cuh); a role that gives up records a code, and the
+//   block leaves through the common exit (tensor memory released).
+//
+// Head sizes other than 64, pages that are no multiple of 8 tokens or do not divide 64, and float32
+// go to attention_prefill.cu (mma.sync) or attention_generic.cu.
+//
+// Counterparts in celeg: see attention_prefill.cu.
+#include "tcgen05.cuh"
+
+namespace celeg_b200 {
+
+constexpr int kFaThreads = 192;
+constexpr int kFaM = 128;                 // query rows per tile
+constexpr int kFaN = 64;                  // keys per block
+constexpr int kFaD = 64;
+constexpr unsigned kFaQBytes = kFaM * kFaD * 2;         // 16 KiB
+constexpr unsigned kFaKvBytes = kFaN * kFaD * 2;        // 8 KiB each for K and V
+constexpr unsigned kFaPBytes = kFaM * kFaN * 2;         // 16 KiB: rows of 64 keys = 128 bytes
+constexpr int kFaStages = 2;
+constexpr unsigned kFaSmemBytes = kFaQBytes + kFaStages * 2 * kFaKvBytes + kFaPBytes + 1024;
+constexpr unsigned kFaTmemColumns = 128;  // S: columns 0..63, O': 64..127
+
+struct FaParams {
+    __nv_bfloat16* out;            // [tokens, q_heads * 64]
+    const int* positions;          // [tokens]
+    const int* span_begin;         // [spans + 1]
+    const int* block_table;        // [spans, table_stride]
+    int table_stride;
+    int spans, q_heads, kv_heads, page_tokens, window;
+    float scale_log2;              // softmax scale * log2(e)
+    int* error_flag;
+};
+
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_arrive_one(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
+// The MN-major form of the instruction descriptor's B operand (bit 16): B is read as [k][n] with n contiguous.
+__host__ __device__ constexpr unsigned instruction_descriptor_b_mn(int m, int n) {
+    return instruction_descriptor(m, n) | (1u << 16);
+}
+
+__global__ void __launch_bounds__(kFaThreads)
+attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, const FaParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long q_full, kv_full[kFaStages], kv_empty[kFaStages], s_full, p_full, o_full;
+    __shared__ unsigned tmem_base_slot;
+    __shared__ int tile_span, tile_first;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        int seen = 0, found = -1, first = 0;
+        for (int r = 0; r < p.spans; ++r) {
+            const int len = p.span_begin[r + 1] - p.span_begin[r];
+            const int tiles = (len + kFaM - 1) / kFaM;
+            if ((int)blockIdx.x < seen + tiles) {
+                found = r;
+                first = ((int)blockIdx.x - seen) * kFaM;
+                break;
+            }
+            seen += tiles;
+        }
+        tile_span = found;
+        tile_first = first;
+        mbar_init(smem_u32(&q_full), 1);
+        for (int s = 0; s < kFaStages; ++s) {
+            mbar_init(smem_u32(&kv_full[s]), 1);
+            mbar_init(smem_u32(&kv_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&s_full), 1);
+        mbar_init(smem_u32(&p_full), 128);
+        mbar_init(smem_u32(&o_full), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(smem_u32(&tmem_base_slot), kFaTmemColumns);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const unsigned tmem_base = tmem_base_slot;
+    const int span = tile_span;
+
+    const unsigned smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const unsigned q_addr = smem_base;
+    const unsigned kv_addr = q_addr + kFaQBytes;                       // stage s: K at +s*2*kv, V behind it
+    const unsigned p_addr = kv_addr + kFaStages * 2 * kFaKvBytes;
+    unsigned char* p_ptr = smem_raw + (p_addr - smem_u32(smem_raw));
+
+    int error = 0;
+    if (span >= 0) {
+        const int h = blockIdx.y;
+        const int kvh = h / (p.q_heads / p.kv_heads);
+        const int span_len = p.span_begin[span + 1] - p.span_begin[span];
+        const int t0 = p.span_begin[span] + tile_first;
+        const int rows = min(kFaM, span_len - tile_first);
+        const int pos0 = p.positions[t0];
+        const int pos_last = pos0 + rows - 1;
+        const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+        const int block_begin = first_key / kFaN;
+        const int block_end = pos_last / kFaN + 1;
+
+        if (warp == 0 && lane == 0) {
+            // ------------------------------------------------------------------ producer
+            const int* table = p.block_table + (size_t)span * p.table_stride;
+            mbar_expect_tx(smem_u32(&q_full), kFaQBytes);
+            tma_load_2d(q_addr, &map_q, smem_u32(&q_full), h * kFaD, t0);
+            const int pages_per_block = kFaN / p.page_tokens;
+            const unsigned page_bytes = (unsigned)p.page_tokens * kFaD * 2;
+            for (int kb = block_begin; kb < block_end && !error; ++kb) {
+                const int i = kb - block_begin;
+                const int s = i % kFaStages;
+                if (i >= kFaStages && !mbar_wait(smem_u32(&kv_empty[s]), ((i / kFaStages) - 1) & 1)) {
+                    error = 61;
+                    break;
+                }
+                const unsigned bar = smem_u32(&kv_full[s]);
+                mbar_expect_tx(bar, 2 * kFaKvBytes);
+                const unsigned k_dst = kv_addr + s * 2 * kFaKvBytes;
+                const unsigned v_dst = k_dst + kFaKvBytes;
+                for (int pg = 0; pg < pages_per_block; ++pg) {
+                    const int key0 = kb * kFaN + pg * p.page_tokens;
+                    int page = 0;                     // keys nobody may see: any page of finite numbers will do
+                    if (key0 <= pos_last && key0 + p.page_tokens > first_key) {
+                        page = table[key0 / p.page_tokens];
+                        if (page < 0) {               // the host never builds such a table
+                            atomicExch(p.error_flag, 2);
+                            page = 0;
+                        }
+                    }
+                    const int row = (page * p.kv_heads + kvh) * p.page_tokens;
+                    tma_load_2d(k_dst + pg * page_bytes, &map_k, bar, 0, row);
+                    tma_load_2d(v_dst + pg * page_bytes, &map_v, bar, 0, row);
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ---------------------------------------------------------------- MMA issuer
+            constexpr unsigned idesc_s = instruction_descriptor(kFaM, kFaN);
+            constexpr unsigned idesc_o = instruction_descriptor_b_mn(kFaM, kFaD);
+            if (!mbar_wait(smem_u32(&q_full), 0)) error = 62;
+            for (int kb = block_begin; kb < block_end && !error; ++kb) {
+                const int i = kb - block_begin;
+                const int s = i % kFaStages;
+                if (!mbar_wait(smem_u32(&kv_full[s]), (i / kFaStages) & 1)) {
+                    error = 63;
+                    break;
+                }
+                tcgen05_fence_after();
+                const unsigned k_src = kv_addr + s * 2 * kFaKvBytes;
+                const unsigned long long desc_q = smem_descriptor(q_addr);
+                const unsigned long long desc_k = smem_descriptor(k_src);
+#pragma unroll
+                for (int kk = 0; kk < kFaD / kUmmaK; ++kk)
+                    umma_bf16(tmem_base, desc_q + 2 * kk, desc_k + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
+                umma_commit(smem_u32(&s_full));
+                // P of this block (the softmax threads have read S and O' of the block before by then)
+                if (!mbar_wait(smem_u32(&p_full), i & 1)) {
+                    error = 64;
+                    break;
+                }
+                tcgen05_fence_after();
+                const unsigned long long desc_v = smem_descriptor(k_src + kFaKvBytes);
+#pragma unroll
+                for (int kk = 0; kk < kFaN / kUmmaK; ++kk) {
+                    // P: 32 bytes per 16 keys inside its rows; V: 16 keys further = 16 rows of 128 bytes = 2 KiB
+                    umma_bf16(tmem_base + kFaN, smem_descriptor(p_addr) + 2 * kk, desc_v + (unsigned long long)(kk * 128),
+                              idesc_o, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&kv_empty[s]));
+                umma_commit(smem_u32(&o_full));
+            }
+        } else if (warp >= 2) {
+            // -------------------------------------------------------------------- softmax
+            const int quarter = warp & 3;                           // the TMEM lanes this warp may touch
+            const int row = quarter * 32 + lane;
+            const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16);
+            const int qpos = pos0 + row;
+            const bool live = row < rows;
+            float o[kFaD];
+#pragma unroll
+            for (int cidx = 0; cidx < kFaD; ++cidx) o[cidx] = 0.0f;
+            float run_max = -INFINITY, run_sum = 0.0f;
+            bool ok = true;
+            for (int kb = block_begin; kb < block_end; ++kb) {
+                const int i = kb - block_begin;
+                ok = ok && mbar_wait(smem_u32(&s_full), i & 1);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const int key_base = kb * kFaN;
+                const bool full = key_base + kFaN - 1 <= pos0 && rows == kFaM &&
+                                  (p.window <= 0 || key_base > pos_last - p.window);
+                // the whole row of scores in registers, pre-scaled (one pass over tensor memory)
+                float sc[kFaN];
+                {
+                    float v[32];
+                    tmem_load_32(lane_base, v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) sc[j] = v[j] * p.scale_log2;
+                    tmem_load_32(lane_base + 32u, v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) sc[32 + j] = v[j] * p.scale_log2;
+                }
+                if (!full) {
+                    // keys key_base + [lo, hi] are the ones this row sees
+                    const int hi = live ? min(kFaN - 1, qpos - key_base) : -1;
+                    const int lo = p.window > 0 ? max(0, qpos - p.window + 1 - key_base) : 0;
+#pragma unroll
+                    for (int j = 0; j < kFaN; ++j) sc[j] = (j <= hi && j >= lo) ? sc[j] : -INFINITY;
+                }
+                float block_max = sc[0];
+#pragma unroll
+                for (int j = 1; j < kFaN; ++j) block_max = fmaxf(block_max, sc[j]);
+                const float new_max = fmaxf(run_max, block_max);
+                const float correction = new_max == -INFINITY ? 1.0f : exp2f(run_max - new_max);
+                const float safe_max = new_max == -INFINITY ? 0.0f : new_max;
+                run_max = new_max;
+                float block_sum = 0.0f;
+                unsigned char* p_row = p_ptr + row * 128;
+#pragma unroll
+                for (int q8 = 0; q8 < kFaN / 8; ++q8) {
+                    uint4 packed;
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                    for (int e2 = 0; e2 < 4; ++e2) {
+                        float a, b;
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(sc[q8 * 8 + 2 * e2] - safe_max));
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(sc[q8 * 8 + 2 * e2 + 1] - safe_max));
+                        block_sum += a + b;
+                        h2[e2] = __floats2bfloat162_rn(a, b);
+                    }
+                    // 16-byte chunk q8 of this row; chunk index XOR (row % 8): the 128-byte swizzle
+                    *reinterpret_cast<uint4*>(p_row + ((q8 ^ (row & 7)) << 4)) = packed;
+                }
+                run_sum = run_sum * correction + block_sum;
+                tcgen05_fence_before();
+                fence_async_shared();                       // the MMA reads P through the async proxy
+                mbar_arrive_one(smem_u32(&p_full));
+                // O' of this block
+                ok = mbar_wait(smem_u32(&o_full), i & 1);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tcgen05_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < kFaD; c0 += 32) {
+                    float v[32];
+                    tmem_load_32(lane_base + (unsigned)(kFaN + c0), v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[c0 + j] = o[c0 + j] * correction + v[j];
+                }
+                tcgen05_fence_before();
+            }
+            if (!ok) {
+                if (lane == 0) atomicExch(p.error_flag, 65);
+            } else if (live) {
+                const float inv = run_sum > 0.0f ? 1.0f / run_sum : 0.0f;
+                __nv_bfloat16* dst = p.out + ((size_t)(t0 + row) * p.q_heads + h) * kFaD;
+#pragma unroll
+                for (int c0 = 0; c0 < kFaD; c0 += 8) {
+                    uint4 packed;
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                    for (int e2 = 0; e2 < 4; ++e2)
+                        h2[e2] = __floats2bfloat162_rn(o[c0 + 2 * e2] * inv, o[c0 + 2 * e2 + 1] * inv);
+                    *reinterpret_cast<uint4*>(dst + c0) = packed;
+                }
+            }
+        }
+        if (error) atomicExch(p.error_flag, error);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, kFaTmemColumns);
+}
+
+}  // namespace celeg_b200
+
+using namespace celeg_b200;
+
+// Whether the shapes fit this kernel (the caller then uses celeg_attention_prefill or the general kernel).
+CELEG_API int celeg_attention_prefill_tcgen05_supported(int q_heads, int kv_heads, int head_dim, int page_tokens) {
+    return head_dim == kFaD && kv_heads > 0 && q_heads % kv_heads == 0 && page_tokens >= 8 && page_tokens % 8 == 0 &&
+           kFaN % page_tokens == 0;
+}
+
+// q: [q_rows, q_row_stride] bfloat16 with head h at column h * 64 (q_rows: rows of the buffer that may be
+// read, at least `tokens`); caches [pages, kv_heads, page_tokens, 64]. tile_count = sum over spans of
+// ceil(length / 128), computed by the caller, who knows the lengths.
+CELEG_API int celeg_attention_prefill_tcgen05(const void* q, int q_row_stride, int q_rows, void* out, const void* k_cache,
+                                              const void* v_cache, int pages, const int* positions,
+                                              const int* span_begin, const int* block_table, int table_stride,
+                                              int tokens, int spans, int tile_count, int q_heads, int kv_heads,
+                                              int head_dim, int page_tokens, int window, float scale, int* error_flag,
+                                              cudaStream_t stream) {
+    CELEG_REQUIRE(celeg_attention_prefill_tcgen05_supported(q_heads, kv_heads, head_dim, page_tokens),
+                  "attention_prefill_tcgen05: head_dim=%d page_tokens=%d q_heads=%d kv_heads=%d are not taken here",
+                  head_dim, page_tokens, q_heads, kv_heads);
+    CELEG_REQUIRE(tokens >= 0 && spans >= 0 && tile_count >= 0 && pages > 0 && q_rows >= tokens && q_row_stride % 8 == 0 &&
+                      ((size_t)q & 15) == 0 && error_flag,
+                  "attention_prefill_tcgen05: invalid sizes tokens=%d spans=%d q_rows=%d q_row_stride=%d", tokens, spans,
+                  q_rows, q_row_stride);
+    if (tokens == 0 || tile_count == 0) return 0;
+    CELEG_REQUIRE(tile_count <= 65535 * 1024 && q_heads <= 65535, "attention_prefill_tcgen05: grid too large");
+    CUtensorMap map_q, map_k, map_v;
+    if (!tensor_map_for(q, q_rows, q_row_stride, q_row_stride, kFaM, &map_q)) return -2;
+    const long long cache_rows = (long long)pages * kv_heads * page_tokens;
+    if (!tensor_map_for(k_cache, cache_rows, kFaD, kFaD, page_tokens, &map_k)) return -2;
+    if (!tensor_map_for(v_cache, cache_rows, kFaD, kFaD, page_tokens, &map_v)) return -2;
+    FaParams p;
+    p.out = (__nv_bfloat16*)out;
+    p.positions = positions;
+    p.span_begin = span_begin;
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.spans = spans;
+    p.q_heads = q_heads;
+    p.kv_heads = kv_heads;
+    p.page_tokens = page_tokens;
+    p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.error_flag = error_flag;
+    const cudaError_t status = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel,
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFaSmemBytes);
+    if (status != cudaSuccess) {
+        set_error("attention_prefill_tcgen05: %s", cudaGetErrorString(status));
+        return -2;
+    }
+    attention_prefill_tcgen05_kernel<<<dim3(tile_count, q_heads), kFaThreads, kFaSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    return check_launch("attention_prefill_tcgen05");
+}

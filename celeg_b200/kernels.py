@@ -53,6 +53,9 @@ _SIGNATURES = {
     "celeg_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                 c_void_p, c_void_p],
+    "celeg_attention_prefill_tcgen05": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_float, c_void_p, c_void_p],
     "celeg_gemv_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_longlong, c_void_p, c_void_p],
     "celeg_gemv_bf16_split_norm": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
@@ -257,6 +260,28 @@ def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_c
         _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
         _ptr(span_begin), _ptr(block_table), block_table.stride(0), tokens, spans, q_heads, kv_heads, head_dim,
         page_tokens, int(window or 0), scale, _ptr(error_flag), _stream()))
+
+
+def attention_prefill_tcgen05_supported(q_heads: int, kv_heads: int, head_dim: int, page_tokens: int,
+                                        dtype: torch.dtype) -> bool:
+    """Shapes the tcgen05 kernel for prompt portions takes: head size 64, pages of 8, 16, 32 or 64 tokens."""
+    return (dtype == torch.bfloat16 and head_dim == 64 and kv_heads > 0 and q_heads % kv_heads == 0
+            and page_tokens >= 8 and page_tokens % 8 == 0 and 64 % page_tokens == 0)
+
+
+def attention_prefill_tcgen05(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_cache: torch.Tensor,
+                              v_cache: torch.Tensor, positions: torch.Tensor, span_begin: torch.Tensor,
+                              block_table: torch.Tensor, tokens: int, spans: int, tile_count: int, q_heads: int,
+                              kv_heads: int, head_dim: int, page_tokens: int, window: Optional[int], scale: float,
+                              error_flag: torch.Tensor) -> None:
+    """Prompt-portion attention on tcgen05 (S and O' in tensor memory, Q/K/V by TMA).
+    ``tile_count`` = sum over the spans of ceil(length / 128)."""
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise KernelLibraryError("attention_prefill_tcgen05 needs contiguous cache layers")
+    _check(library().celeg_attention_prefill_tcgen05(
+        _ptr(q), q_row_stride, q.shape[0], _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(positions),
+        _ptr(span_begin), _ptr(block_table), block_table.stride(0), tokens, spans, tile_count, q_heads, kv_heads,
+        head_dim, page_tokens, int(window or 0), scale, _ptr(error_flag), _stream()))
 
 
 GEMV_MAX_ROWS = 16

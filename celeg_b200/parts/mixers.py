@@ -185,6 +185,15 @@ class AttentionMixer:
                                      self.head_dim, b.page_tokens, self.window, self.scale, chunk, max_splits,
                                      partial_o, partial_ml, counters, step.error_flag)
             return
+        if (step.host_span_lengths is not None and rt.tcgen05_attention and kernels.attention_prefill_tcgen05_supported(
+                self.heads, self.kv_heads, self.head_dim, b.page_tokens, rt.act_dtype)):
+            # head size 64: S and O' in tensor memory, Q/K/V by TMA
+            tiles = sum((length + 127) // 128 for length in step.host_span_lengths)
+            kernels.attention_prefill_tcgen05(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
+                                              step.span_begin, table, step.tokens, step.spans, tiles, self.heads,
+                                              self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale,
+                                              step.error_flag)
+            return
         if kernels.attention_prefill_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype):
             kernels.attention_prefill(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
                                       step.span_begin, table, step.tokens, step.spans, self.heads, self.kv_heads,

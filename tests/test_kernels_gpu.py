@@ -383,6 +383,56 @@ def test_attention_prefill_tensor_cores(heads, kv_heads, head_dim, page_tokens, 
     close(out, want, dtype, scale=1.5)
 
 
+@pytest.mark.parametrize("heads,kv_heads,page_tokens,window,lengths,starts", [
+    (1, 1, 16, None, (128,), (0,)), (2, 1, 16, None, (200,), (0,)), (8, 2, 16, None, (130, 5, 77), (37, 0, 255)),
+    (6, 2, 8, 150, (300,), (100,)), (4, 4, 32, None, (100, 260), (0, 40)), (3, 1, 64, 70, (1, 129, 2), (500, 3, 64)),
+])
+def test_attention_prefill_tcgen05(heads, kv_heads, page_tokens, window, lengths, starts):
+    """Prompt-portion attention of head size 64 on tcgen05 (S and O' in tensor memory, Q/K/V by TMA through the
+    block table) against the formula, with tiles that end inside a block of keys, a window, several spans."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(18)
+    dtype, head_dim = torch.bfloat16, 64
+    assert kernels.attention_prefill_tcgen05_supported(heads, kv_heads, head_dim, page_tokens, dtype)
+    spans, tokens = len(lengths), sum(lengths)
+    pages_per = (max(s + n for s, n in zip(starts, lengths)) + page_tokens - 1) // page_tokens
+    pages = spans * pages_per + 3
+    order = rng.permutation(pages)
+    table = order[:spans * pages_per].reshape(spans, pages_per).astype(np.int32)
+    k_cache = np.zeros((pages, kv_heads, page_tokens, head_dim))
+    v_cache = np.zeros_like(k_cache)
+    ks, vs = [], []
+    for r, (start, n) in enumerate(zip(starts, lengths)):
+        k = rounded(rng.normal(size=(start + n, kv_heads, head_dim)), dtype)
+        v = rounded(rng.normal(size=(start + n, kv_heads, head_dim)), dtype)
+        ks.append(k)
+        vs.append(v)
+        for position in range(start + n):
+            k_cache[table[r, position // page_tokens], :, position % page_tokens] = k[position]
+            v_cache[table[r, position // page_tokens], :, position % page_tokens] = v[position]
+    # what lies in unused pages must never matter, whatever it is
+    k_cache[order[spans * pages_per:]] = 1e4
+    v_cache[order[spans * pages_per:]] = -1e4
+    positions = np.concatenate([np.arange(s, s + n) for s, n in zip(starts, lengths)])
+    token_span = np.concatenate([np.full(n, r) for r, n in enumerate(lengths)])
+    begins = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    q = rounded(rng.normal(size=(tokens, heads, head_dim)), dtype)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = np.zeros((tokens + 3, width))
+    qkv[:tokens, :heads * head_dim] = q.reshape(tokens, -1)
+    out = torch.zeros((tokens, heads * head_dim), dtype=dtype, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    scale = head_dim ** -0.5
+    tiles = sum((n + 127) // 128 for n in lengths)
+    kernels.attention_prefill_tcgen05(dev(qkv, dtype), width, out, dev(k_cache, dtype), dev(v_cache, dtype),
+                                      dev(positions.astype(np.int32)), dev(begins), dev(table), tokens, spans, tiles,
+                                      heads, kv_heads, head_dim, page_tokens, window, scale, flag)
+    assert int(flag.item()) == 0
+    want = np.stack([attention_reference(q[t], ks[token_span[t]], vs[token_span[t]], positions[t], scale, window)
+                     for t in range(tokens)]).reshape(tokens, -1)
+    close(out, want, dtype, scale=1.5)
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 64, 64), (8, 2048, 2048), (3, 70, 136), (8, 100, 8200), (16, 48, 520),
                                    (11, 1000, 96), (5, 33, 24), (2, 16, 8)])
 def test_gemv_bf16_modes(m, n, k):

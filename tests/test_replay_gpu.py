@@ -57,7 +57,7 @@ def sequences(vocab, lengths, seed):
 def models(tmp_path_factory):
     base = tmp_path_factory.mktemp("models")
     out = {}
-    for name in ("A", "B", "C"):
+    for name in ("A", "B", "C", "D"):
         folder = write_tiny(base, name)
         config, weights = plain_lfm2.load_model_folder(folder)
         out[name] = (folder, config, weights)
@@ -65,7 +65,7 @@ def models(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_requests(models, name, dtype, tmp_path):
     folder, config, weights = models[name]
     vocab = config["vocab_size"]
@@ -78,7 +78,7 @@ def test_whole_requests(models, name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_last_32_one_by_one(models, name, dtype, tmp_path):
     folder, config, weights = models[name]
     vocab = config["vocab_size"]
@@ -96,7 +96,7 @@ def test_last_32_one_by_one(models, name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_of_changing_size(models, name, dtype, tmp_path):
     folder, config, weights = models[name]
     vocab = config["vocab_size"]
@@ -117,7 +117,7 @@ def test_portions_of_changing_size(models, name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_requests_with_page_reuse(models, name, dtype, tmp_path):
     """Eight requests through a pool that holds four: portions of some beside decoded tokens of
     others; later requests get pages and slots that earlier ones gave back."""

@@ -32,7 +32,17 @@ TINY_C = {
     "bos_token_id": 1, "eos_token_id": 2, "pad_token_id": 0,
 }
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+# the head size of the full models (64), which selects the tcgen05 kernels for prompt portions: six query heads
+# on two kv heads, two attention layers beside one conv layer
+TINY_D = {
+    "model_type": "lfm2", "vocab_size": 600, "hidden_size": 192, "num_hidden_layers": 3,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64,
+    "max_position_embeddings": 512, "norm_eps": 1e-5, "conv_L_cache": 3, "rope_theta": 1000000.0,
+    "layer_types": ["full_attention", "conv", "full_attention"], "tie_word_embeddings": True,
+    "intermediate_size": 320, "bos_token_id": 1, "eos_token_id": 7, "pad_token_id": 0,
+}
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 
 def write_tiny(tmp_path, name: str, dtype=None) -> str:
