@@ -1,7 +1,7 @@
 // Paged causal grouped-query attention for batches that hold prompt portions (and, beside them,
 // single decoded tokens), bfloat16, on the tensor cores:
 //
-//   grid = (query tiles, query heads). A query tile is up to 128 consecutive tokens of one span
+//   grid = (query heads, query tiles). A query tile is up to 128 consecutive tokens of one span
 //   (a span = what one request brings to the step); 8 warps own 16 query rows each. Keys and
 //   values are fetched page by page through the request's block table into shared memory, 64
 //   keys at a time (cp.async, XOR-swizzled 16-byte chunks, two tiles in flight: the next one loads
@@ -59,9 +59,11 @@ __global__ void __launch_bounds__(kPrefillThreads, D_PAD <= 64 ? 2 : 1) attentio
         for (int r = 0; r < p.spans; ++r) {
             const int len = p.span_begin[r + 1] - p.span_begin[r];
             const int tiles = (len + kBlockM - 1) / kBlockM;
-            if ((int)blockIdx.x < seen + tiles) {
+            if ((int)blockIdx.y < seen + tiles) {
+                // the last tile of a span has the most keys: it comes first in launch order (tiles are the
+                // slow grid dimension), so that the grid drains with short tiles
                 found = r;
-                first = ((int)blockIdx.x - seen) * kBlockM;
+                first = (tiles - 1 - ((int)blockIdx.y - seen)) * kBlockM;
                 break;
             }
             seen += tiles;
@@ -72,7 +74,7 @@ __global__ void __launch_bounds__(kPrefillThreads, D_PAD <= 64 ? 2 : 1) attentio
     __syncthreads();
     const int span = tile_span;
     if (span < 0) return;
-    const int h = blockIdx.y;
+    const int h = blockIdx.x;
     const int kvh = h / (p.q_heads / p.kv_heads);
     const int d = p.head_dim;
     const int span_len = p.span_begin[span + 1] - p.span_begin[span];
@@ -281,7 +283,7 @@ static int launch_prefill(const PrefillParams& p, int tiles, cudaStream_t stream
             return -2;
         }
     }
-    dim3 grid(tiles, p.q_heads);
+    dim3 grid(p.q_heads, tiles);
     attention_prefill_kernel<D_PAD><<<grid, kPrefillThreads, smem, stream>>>(p);
     return check_launch("attention_prefill");
 }

@@ -1,15 +1,18 @@
 // Paged causal grouped-query attention for prompt portions on Blackwell's fifth-generation tensor
 // cores, for a head size of 64 (bfloat16):
 //
-//   grid = (query tiles, query heads); a query tile is up to 128 consecutive tokens of one span.
+//   grid = (query heads, query tiles); a query tile is up to 128 consecutive tokens of one span; tiles with
+//   many keys come first in launch order, so that the grid drains with short ones.
 //   Six warps. Warp 0 brings Q (one box of 128 rows x 64) and, per block of 64 keys, the K and V
 //   rows page by page through the request's block table into a two-stage ring by TMA (128-byte
 //   swizzle; a page is one box of page_tokens rows x 64). Warp 1 issues the MMAs:
 //       S[128 x 64] = Q K^T           (tcgen05.mma M128 N64 K16 x 4, both operands K-major)
 //       O'[128 x 64] = P V            (M128 N64 K16 x 4, P K-major from shared memory, V as it lies in
 //                                      the cache, keys x 64: the MN-major form of the B operand)
-//   with S and O' in tensor memory (128 columns a block, 64 KiB of shared memory: two to three blocks per
-//   SM, so one block's MMAs run under another's softmax). Warps 2-5 are the softmax: a thread owns one
+//   with S and O' in tensor memory. S, P and O' exist twice (even and odd blocks of keys): the scores of
+//   block j+1 are being multiplied while the softmax threads work on block j, and P V of block j runs while
+//   they work on block j+1 (they add O' of a block one block later). 256 columns of tensor memory and 97 KiB
+//   of shared memory a block: two blocks per SM. Warps 2-5 are the softmax: a thread owns one
 //   query row (its TMEM lane), reads S with tcgen05.ld, scales, masks (causal, window, rows past the span;
 //   blocks that every row sees whole skip the mask), keeps the running
 //   maximum and denominator in float32 (exponentials by exp2 of pre-scaled scores), writes P as
@@ -34,9 +37,9 @@ constexpr int kFaD = 64;
 constexpr unsigned kFaQBytes = kFaM * kFaD * 2;         // 16 KiB
 constexpr unsigned kFaKvBytes = kFaN * kFaD * 2;        // 8 KiB each for K and V
 constexpr unsigned kFaPBytes = kFaM * kFaN * 2;         // 16 KiB: rows of 64 keys = 128 bytes
-constexpr int kFaStages = 2;
-constexpr unsigned kFaSmemBytes = kFaQBytes + kFaStages * 2 * kFaKvBytes + kFaPBytes + 1024;
-constexpr unsigned kFaTmemColumns = 128;  // S: columns 0..63, O': 64..127
+constexpr int kFaStages = 3;
+constexpr unsigned kFaSmemBytes = kFaQBytes + kFaStages * 2 * kFaKvBytes + 2 * kFaPBytes + 1024;
+constexpr unsigned kFaTmemColumns = 256;  // S of even and odd blocks: columns 0..63, 64..127; O': 128..191, 192..255
 
 struct FaParams {
     __nv_bfloat16* out;            // [tokens, q_heads * 64]
@@ -64,7 +67,8 @@ __global__ void __launch_bounds__(kFaThreads)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const FaParams p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long q_full, kv_full[kFaStages], kv_empty[kFaStages], s_full, p_full, o_full;
+    __shared__ __align__(8) unsigned long long q_full, kv_full[kFaStages], kv_empty[kFaStages], s_full[2], p_full[2],
+        o_full[2];
     __shared__ unsigned tmem_base_slot;
     __shared__ int tile_span, tile_first;
 
@@ -74,9 +78,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         for (int r = 0; r < p.spans; ++r) {
             const int len = p.span_begin[r + 1] - p.span_begin[r];
             const int tiles = (len + kFaM - 1) / kFaM;
-            if ((int)blockIdx.x < seen + tiles) {
+            if ((int)blockIdx.y < seen + tiles) {
+                // the last tile of a span has the most keys: it goes first, so that the blocks that are
+                // still running when the grid drains are the short ones
                 found = r;
-                first = ((int)blockIdx.x - seen) * kFaM;
+                first = (tiles - 1 - ((int)blockIdx.y - seen)) * kFaM;
                 break;
             }
             seen += tiles;
@@ -88,9 +94,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             mbar_init(smem_u32(&kv_full[s]), 1);
             mbar_init(smem_u32(&kv_empty[s]), 1);
         }
-        mbar_init(smem_u32(&s_full), 1);
-        mbar_init(smem_u32(&p_full), 128);
-        mbar_init(smem_u32(&o_full), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&s_full[b]), 1);
+            mbar_init(smem_u32(&p_full[b]), 128);
+            mbar_init(smem_u32(&o_full[b]), 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 0) tmem_alloc(smem_u32(&tmem_base_slot), kFaTmemColumns);
@@ -108,7 +116,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
     int error = 0;
     if (span >= 0) {
-        const int h = blockIdx.y;
+        const int h = blockIdx.x;
         const int kvh = h / (p.q_heads / p.kv_heads);
         const int span_len = p.span_begin[span + 1] - p.span_begin[span];
         const int t0 = p.span_begin[span] + tile_first;
@@ -129,7 +137,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             for (int kb = block_begin; kb < block_end && !error; ++kb) {
                 const int i = kb - block_begin;
                 const int s = i % kFaStages;
-                if (i >= kFaStages && !mbar_wait(smem_u32(&kv_empty[s]), ((i / kFaStages) - 1) & 1)) {
+                if (i >= kFaStages && !mbar_wait_suspended(smem_u32(&kv_empty[s]), ((i / kFaStages) - 1) & 1)) {
                     error = 61;
                     break;
                 }
@@ -156,37 +164,45 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             // ---------------------------------------------------------------- MMA issuer
             constexpr unsigned idesc_s = instruction_descriptor(kFaM, kFaN);
             constexpr unsigned idesc_o = instruction_descriptor_b_mn(kFaM, kFaD);
-            if (!mbar_wait(smem_u32(&q_full), 0)) error = 62;
-            for (int kb = block_begin; kb < block_end && !error; ++kb) {
-                const int i = kb - block_begin;
+            const int blocks = block_end - block_begin;
+            const unsigned long long desc_q = smem_descriptor(q_addr);
+            // S of block i into its buffer, as soon as its keys are there
+            auto scores = [&](int i) -> bool {
                 const int s = i % kFaStages;
-                if (!mbar_wait(smem_u32(&kv_full[s]), (i / kFaStages) & 1)) {
+                if (!mbar_wait_suspended(smem_u32(&kv_full[s]), (i / kFaStages) & 1)) return false;
+                tcgen05_fence_after();
+                const unsigned long long desc_k = smem_descriptor(kv_addr + s * 2 * kFaKvBytes);
+#pragma unroll
+                for (int kk = 0; kk < kFaD / kUmmaK; ++kk)
+                    umma_bf16(tmem_base + (unsigned)((i & 1) * kFaN), desc_q + 2 * kk, desc_k + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
+                umma_commit(smem_u32(&s_full[i & 1]));
+                return true;
+            };
+            if (!mbar_wait_suspended(smem_u32(&q_full), 0)) error = 62;
+            if (!error && !scores(0)) error = 63;
+            for (int i = 0; i < blocks && !error; ++i) {
+                // the scores of the next block run while the softmax threads are busy with this one (they
+                // have read the buffer's last content: P of block i-1 was complete before this point)
+                if (i + 1 < blocks && !scores(i + 1)) {
                     error = 63;
                     break;
                 }
-                tcgen05_fence_after();
-                const unsigned k_src = kv_addr + s * 2 * kFaKvBytes;
-                const unsigned long long desc_q = smem_descriptor(q_addr);
-                const unsigned long long desc_k = smem_descriptor(k_src);
-#pragma unroll
-                for (int kk = 0; kk < kFaD / kUmmaK; ++kk)
-                    umma_bf16(tmem_base, desc_q + 2 * kk, desc_k + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
-                umma_commit(smem_u32(&s_full));
-                // P of this block (the softmax threads have read S and O' of the block before by then)
-                if (!mbar_wait(smem_u32(&p_full), i & 1)) {
+                if (!mbar_wait_suspended(smem_u32(&p_full[i & 1]), (i >> 1) & 1)) {
                     error = 64;
                     break;
                 }
                 tcgen05_fence_after();
-                const unsigned long long desc_v = smem_descriptor(k_src + kFaKvBytes);
+                const int s = i % kFaStages;
+                const unsigned long long desc_v = smem_descriptor(kv_addr + s * 2 * kFaKvBytes + kFaKvBytes);
+                const unsigned long long desc_p = smem_descriptor(p_addr + (i & 1) * kFaPBytes);
 #pragma unroll
                 for (int kk = 0; kk < kFaN / kUmmaK; ++kk) {
                     // P: 32 bytes per 16 keys inside its rows; V: 16 keys further = 16 rows of 128 bytes = 2 KiB
-                    umma_bf16(tmem_base + kFaN, smem_descriptor(p_addr) + 2 * kk, desc_v + (unsigned long long)(kk * 128),
-                              idesc_o, kk > 0 ? 1u : 0u);
+                    umma_bf16(tmem_base + (unsigned)(2 * kFaN + (i & 1) * kFaD), desc_p + 2 * kk,
+                              desc_v + (unsigned long long)(kk * 128), idesc_o, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&kv_empty[s]));
-                umma_commit(smem_u32(&o_full));
+                umma_commit(smem_u32(&o_full[i & 1]));
             }
         } else if (warp >= 2) {
             // -------------------------------------------------------------------- softmax
@@ -199,26 +215,47 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
             for (int cidx = 0; cidx < kFaD; ++cidx) o[cidx] = 0.0f;
             float run_max = -INFINITY, run_sum = 0.0f;
+            float pending_correction = 1.0f;                // of the block whose O' has not been added yet
             bool ok = true;
-            for (int kb = block_begin; kb < block_end; ++kb) {
-                const int i = kb - block_begin;
-                ok = ok && mbar_wait(smem_u32(&s_full), i & 1);
+            const int blocks = block_end - block_begin;
+            // adds O' of block i (relative to that block's maximum) into the row
+            auto add_output = [&](int i, float correction) -> bool {
+                bool done = mbar_wait(smem_u32(&o_full[i & 1]), (i >> 1) & 1);
+                done = __all_sync(0xffffffffu, done);
+                if (!done) return false;
+                tcgen05_fence_after();
+                unsigned lo[32], hi[32];
+                tmem_load_32_issue(lane_base + (unsigned)(2 * kFaN + (i & 1) * kFaD), lo);
+                tmem_load_32_issue(lane_base + (unsigned)(2 * kFaN + (i & 1) * kFaD + 32), hi);
+                tmem_load_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    o[j] = o[j] * correction + __uint_as_float(lo[j]);
+                    o[32 + j] = o[32 + j] * correction + __uint_as_float(hi[j]);
+                }
+                tcgen05_fence_before();
+                return true;
+            };
+            for (int i = 0; i < blocks; ++i) {
+                ok = ok && mbar_wait(smem_u32(&s_full[i & 1]), (i >> 1) & 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tcgen05_fence_after();
-                const int key_base = kb * kFaN;
+                const int key_base = (block_begin + i) * kFaN;
                 const bool full = key_base + kFaN - 1 <= pos0 && rows == kFaM &&
                                   (p.window <= 0 || key_base > pos_last - p.window);
-                // the whole row of scores in registers, pre-scaled (one pass over tensor memory)
+                // the whole row of scores in registers (one pass over tensor memory), not yet scaled
                 float sc[kFaN];
                 {
-                    float v[32];
-                    tmem_load_32(lane_base, v);
+                    unsigned lo[32], hi[32];
+                    tmem_load_32_issue(lane_base + (unsigned)((i & 1) * kFaN), lo);
+                    tmem_load_32_issue(lane_base + (unsigned)((i & 1) * kFaN + 32), hi);
+                    tmem_load_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) sc[j] = v[j] * p.scale_log2;
-                    tmem_load_32(lane_base + 32u, v);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) sc[32 + j] = v[j] * p.scale_log2;
+                    for (int j = 0; j < 32; ++j) {
+                        sc[j] = __uint_as_float(lo[j]);
+                        sc[32 + j] = __uint_as_float(hi[j]);
+                    }
                 }
                 if (!full) {
                     // keys key_base + [lo, hi] are the ones this row sees
@@ -227,15 +264,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
                     for (int j = 0; j < kFaN; ++j) sc[j] = (j <= hi && j >= lo) ? sc[j] : -INFINITY;
                 }
-                float block_max = sc[0];
+                // eight independent chains instead of one of 63 dependent steps (a thread has no neighbour to
+                // hide latency behind: its warp is alone on its scheduler half of the time)
+                float part_max[8];
 #pragma unroll
-                for (int j = 1; j < kFaN; ++j) block_max = fmaxf(block_max, sc[j]);
+                for (int j = 0; j < 8; ++j) part_max[j] = sc[j];
+#pragma unroll
+                for (int j = 8; j < kFaN; ++j) part_max[j & 7] = fmaxf(part_max[j & 7], sc[j]);
+                float block_max = fmaxf(fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])),
+                                        fmaxf(fmaxf(part_max[4], part_max[5]), fmaxf(part_max[6], part_max[7])));
+                block_max *= p.scale_log2;                 // the scale is positive: the maximum commutes with it
                 const float new_max = fmaxf(run_max, block_max);
                 const float correction = new_max == -INFINITY ? 1.0f : exp2f(run_max - new_max);
                 const float safe_max = new_max == -INFINITY ? 0.0f : new_max;
                 run_max = new_max;
-                float block_sum = 0.0f;
-                unsigned char* p_row = p_ptr + row * 128;
+                float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                unsigned char* p_row = p_ptr + (i & 1) * kFaPBytes + row * 128;
 #pragma unroll
                 for (int q8 = 0; q8 < kFaN / 8; ++q8) {
                     uint4 packed;
@@ -243,32 +287,26 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
                     for (int e2 = 0; e2 < 4; ++e2) {
                         float a, b;
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(sc[q8 * 8 + 2 * e2] - safe_max));
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(sc[q8 * 8 + 2 * e2 + 1] - safe_max));
-                        block_sum += a + b;
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(fmaf(sc[q8 * 8 + 2 * e2], p.scale_log2, -safe_max)));
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(fmaf(sc[q8 * 8 + 2 * e2 + 1], p.scale_log2, -safe_max)));
+                        part_sum[e2] += a + b;
                         h2[e2] = __floats2bfloat162_rn(a, b);
                     }
                     // 16-byte chunk q8 of this row; chunk index XOR (row % 8): the 128-byte swizzle
                     *reinterpret_cast<uint4*>(p_row + ((q8 ^ (row & 7)) << 4)) = packed;
                 }
-                run_sum = run_sum * correction + block_sum;
+                run_sum = run_sum * correction + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
                 tcgen05_fence_before();
                 fence_async_shared();                       // the MMA reads P through the async proxy
-                mbar_arrive_one(smem_u32(&p_full));
-                // O' of this block
-                ok = mbar_wait(smem_u32(&o_full), i & 1);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tcgen05_fence_after();
-#pragma unroll
-                for (int c0 = 0; c0 < kFaD; c0 += 32) {
-                    float v[32];
-                    tmem_load_32(lane_base + (unsigned)(kFaN + c0), v);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) o[c0 + j] = o[c0 + j] * correction + v[j];
+                mbar_arrive_one(smem_u32(&p_full[i & 1]));
+                // O' of the block before, which was multiplied meanwhile
+                if (i > 0) {
+                    ok = add_output(i - 1, pending_correction);
+                    if (!ok) break;
                 }
-                tcgen05_fence_before();
+                pending_correction = correction;
             }
+            if (ok && blocks > 0) ok = add_output(blocks - 1, pending_correction);
             if (!ok) {
                 if (lane == 0) atomicExch(p.error_flag, 65);
             } else if (live) {
@@ -319,7 +357,7 @@ CELEG_API int celeg_attention_prefill_tcgen05(const void* q, int q_row_stride, i
                   "attention_prefill_tcgen05: invalid sizes tokens=%d spans=%d q_rows=%d q_row_stride=%d", tokens, spans,
                   q_rows, q_row_stride);
     if (tokens == 0 || tile_count == 0) return 0;
-    CELEG_REQUIRE(tile_count <= 65535 * 1024 && q_heads <= 65535, "attention_prefill_tcgen05: grid too large");
+    CELEG_REQUIRE(tile_count <= 65535, "attention_prefill_tcgen05: %d query tiles exceed one launch (65535)", tile_count);
     CUtensorMap map_q, map_k, map_v;
     if (!tensor_map_for(q, q_rows, q_row_stride, q_row_stride, kFaM, &map_q)) return -2;
     const long long cache_rows = (long long)pages * kv_heads * page_tokens;
@@ -344,6 +382,6 @@ CELEG_API int celeg_attention_prefill_tcgen05(const void* q, int q_row_stride, i
         set_error("attention_prefill_tcgen05: %s", cudaGetErrorString(status));
         return -2;
     }
-    attention_prefill_tcgen05_kernel<<<dim3(tile_count, q_heads), kFaThreads, kFaSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    attention_prefill_tcgen05_kernel<<<dim3(q_heads, tile_count), kFaThreads, kFaSmemBytes, stream>>>(map_q, map_k, map_v, p);
     return check_launch("attention_prefill_tcgen05");
 }
