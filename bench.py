@@ -221,7 +221,7 @@ def program_timeline(loaded, batch: int, prompt_tokens: int, seed: int) -> dict:
         return {"phase": "program", "error": f"no program was built: {loaded.model.program_refusal}"}
     program = programs[-1]
     n = program.n_ops
-    timeline = torch.zeros(1 + 6 * n, dtype=torch.int64, device="cuda")
+    timeline = torch.zeros(1 + 2 * n, dtype=torch.int64, device="cuda")
     for _ in range(3):                       # (runs the last step again: the same cache slot, the conv state moves on)
         timeline.zero_()
         program.run(timeline)

@@ -494,7 +494,7 @@ __device__ __forceinline__ void apply_epilogue(const ProgramOp& op, const float 
 template <int MT, int WT>
 __device__ void gemv_consume(const ProgramOp& op, const ProgramLayout& layout, ProgramControl* control,
                              unsigned char* ring, const unsigned char* x_s, float* partial, int& slot, int& phase,
-                             int* error_flag, const int tid, long long* prof) {
+                             int* error_flag, const int tid) {
     const int warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, c = lane & 3;
     const int units = units_of(op), chunks = chunks_of(op);
@@ -509,7 +509,6 @@ __device__ void gemv_consume(const ProgramOp& op, const ProgramLayout& layout, P
     // byte offsets of this lane's fragments inside a stage and inside the operand
     const int w_lane = g * kProgramBoxRowBytes + c * 16;
     const int x_lane = g * x_stride + c * 16;
-    long long waited = 0, multiplied = 0, finished = 0;       // diagnostics, in registers until the end
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
         if (op.epilogue == kEpiConv && tid < MT * 128) {
             // the carried state of this thread's element will be wanted in the epilogue: bring it to L2 now
@@ -535,9 +534,7 @@ __device__ void gemv_consume(const ProgramOp& op, const ProgramLayout& layout, P
                     for (int e = 0; e < 4; ++e) acc[h][t][j][e] = 0.0f;
         for (int chunk = 0; chunk < chunks; ++chunk) {
             const unsigned parity = (unsigned)phase;
-            const long long t0 = prof ? clock64() : 0;
             wait_mbarrier(&control->full[slot], parity, control, error_flag, kErrProgramStage);
-            const long long t1 = prof ? clock64() : 0;
             const unsigned char* stage = ring + (size_t)slot * layout.stage_bytes;
             const int k0 = chunk * kc;
             const int len = min(kc, k - k0);
@@ -583,17 +580,10 @@ __device__ void gemv_consume(const ProgramOp& op, const ProgramLayout& layout, P
                     }
                 }
             }
-            const long long t15 = prof ? clock64() : 0;
             __syncwarp();
             if (lane == 0) mbar_arrive(&control->empty[slot]);
             advance_slot(slot, phase, stages);
-            if (prof) {
-                waited += t1 - t0;
-                multiplied += t15 - t1;
-                finished += clock64() - t15;
-            }
         }
-        const long long t2 = prof ? clock64() : 0;
         consumer_sync();                 // the epilogue of the unit before has read its partial tiles
 #pragma unroll
         for (int t = 0; t < WT; ++t)
@@ -619,11 +609,6 @@ __device__ void gemv_consume(const ProgramOp& op, const ProgramLayout& layout, P
             const int out_row = j * 8 + ((ln & 3) << 1) + (e & 1);
             if (out_row < op.rows && out_col < op.n) apply_epilogue<WT>(op, sum, out_row, out_col);
         }
-    }
-    if (prof) {
-        prof[0] = waited;
-        prof[1] = multiplied;
-        prof[2] = finished;
     }
 }
 
@@ -750,18 +735,13 @@ decode_program_kernel(const ProgramOp* __restrict__ ops, const int n_ops, const 
             embed_consume(op, tid);
         } else if (op.kind == kOpGemv) {
             if (units_of(op) > (int)blockIdx.x) {
-                // diagnostics of block 0: clock cycles of thread 0 waiting for stages, multiplying,
-                // reducing with the epilogue, and in the norm (four words per operation behind the stamps)
-                long long* prof = timeline && blockIdx.x == 0 && tid == 0 ? timeline + 1 + 2 * n_ops + 4 * i : nullptr;
-                const long long p0 = prof ? clock64() : 0;
                 if (op.x_source == kXNorm) norm_prologue(op, control, x_s, tid);
-                if (prof) prof[3] = clock64() - p0;
                 if (op.wt == 1)
-                    gemv_consume<MT, 1>(op, layout, control, ring, x_s, partial, slot, phase, error_flag, tid, prof);
+                    gemv_consume<MT, 1>(op, layout, control, ring, x_s, partial, slot, phase, error_flag, tid);
                 else if (op.wt == 2)
-                    gemv_consume<MT, 2>(op, layout, control, ring, x_s, partial, slot, phase, error_flag, tid, prof);
+                    gemv_consume<MT, 2>(op, layout, control, ring, x_s, partial, slot, phase, error_flag, tid);
                 else
-                    gemv_consume<MT, 3>(op, layout, control, ring, x_s, partial, slot, phase, error_flag, tid, prof);
+                    gemv_consume<MT, 3>(op, layout, control, ring, x_s, partial, slot, phase, error_flag, tid);
             }
         } else if (op.kind == kOpQkNormRope) {
             qk_consume(op, error_flag, tid);
@@ -1007,9 +987,8 @@ CELEG_API int celeg_decode_program_encode_maps(const void* ops_raw, int n_ops, c
 
 // ops: device copy of the prepared operations; maps: device copy of their tensor maps. barriers:
 // [n_ops + 1] ints, zero before the first launch (each launch leaves them zero; clear them after an
-// error). timeline: null, or [1 + 6 n_ops] zeroed device words that receive nanosecond time stamps of
-// block 0 (start; for each operation: its own share done, all blocks done) and then four cycle counts per
-// operation, for measurements. One cooperative launch.
+// error). timeline: null, or [1 + 2 n_ops] device words that receive nanosecond time stamps of block 0
+// (start; for each operation: its own share done, all blocks done), for measurements. One cooperative launch.
 CELEG_API int celeg_decode_program_run(const void* ops, int n_ops, const void* layout_raw, const void* maps,
                                        int* barriers, int* error_flag, long long* timeline, cudaStream_t stream) {
     const ProgramLayout layout = *reinterpret_cast<const ProgramLayout*>(layout_raw);

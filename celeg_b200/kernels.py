@@ -498,13 +498,12 @@ def decode_program_run(ops_device: torch.Tensor, n_ops: int, layout: ProgramLayo
                        barriers: torch.Tensor, error_flag: torch.Tensor,
                        timeline: Optional[torch.Tensor] = None) -> None:
     """One cooperative launch of the persistent kernel over prepared operations on the device.
-    ``timeline``: zeroed int64 [1 + 6 n_ops] that receives block 0's time stamps (nanoseconds): start, then
-    for each operation when its own share was done and when every block's was; then per operation four
-    cycle counts of a product (waiting for stages, multiplying, reducing + epilogue, norm)."""
+    ``timeline``: int64 [1 + 2 n_ops] that receives block 0's time stamps (nanoseconds): start, then for
+    each operation when its own share was done and when every block's was."""
     if timeline is not None:
         _need(timeline, torch.int64, "timeline")
-        if timeline.numel() < 1 + 6 * n_ops:
-            raise KernelLibraryError(f"the timeline of {n_ops} operations needs {1 + 6 * n_ops} words")
+        if timeline.numel() < 1 + 2 * n_ops:
+            raise KernelLibraryError(f"the timeline of {n_ops} operations needs {1 + 2 * n_ops} words")
     _need(barriers, torch.int32, "barriers")
     if barriers.numel() < n_ops + 1:
         raise KernelLibraryError(f"a program of {n_ops} operations needs {n_ops + 1} barrier counters")
