@@ -534,3 +534,34 @@ def test_decoding_twenty_requests_on_the_streaming_product(models, monkeypatch):
         agree += tokens == plain_lfm2.generate(config, weights, prompt, 6, eos_tokens=())
     assert agree >= 18, f"only {agree} of 20 requests decode the plain model's tokens"
     engine.loaded.step.raise_on_device_error()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_requests_that_end_on_a_token_while_the_next_step_is_in_flight(models, dtype):
+    """The scheduler enqueues the step after the one it reads while every request decodes. A request
+    that ends on an end-of-sequence token has then one position computed in vain: its output must stop at
+    that token, the others must continue as if nothing happened, and slot and pages must come back."""
+    from celeg_b200 import Engine
+    folder, config, weights = models["A"]
+    prompts = prompts_of(config["vocab_size"], [7, 19, 12, 26], seed=29)
+    free = [plain_lfm2.generate(config, weights, prompt, 24, eos_tokens=()) for prompt in prompts]
+    # each request stops at a token of its own free-running output: after 3, 9, 15 and (none) tokens
+    stops = [(free[0][3],), (free[1][9],), (free[2][15],), ()]
+    engine = Engine(folder, dtype=dtype)
+    assert engine.scheduler._runs_ahead
+    ids = [engine.submit(prompt, max_new_tokens=24, temperature=0.0, repetition_penalty=1.0, eos_tokens=stop)
+           for prompt, stop in zip(prompts, stops)]
+    while engine.scheduler.has_work():
+        engine.step()
+    agree = 0
+    for request_id, prompt, stop in zip(ids, prompts, stops):
+        want = plain_lfm2.generate(config, weights, prompt, 24, eos_tokens=stop)
+        got = engine.poll(request_id).tokens
+        assert engine.status(request_id).value == "finished"
+        if dtype == "float32":
+            assert got == want
+        agree += got == want
+    assert agree >= 3
+    engine.loaded.step.raise_on_device_error()
+    engine.loaded.manager.check_invariants()
+    assert engine.loaded.manager.free_slots == engine.options.max_active_requests
