@@ -1,4 +1,4 @@
-// Products of 17 to 128 rows of activations (decode steps of many requests, small prompt portions):
+// Products of 17 to 64 rows of activations (decode steps of many requests, small prompt portions):
 //
 //     Y[T, N] = epilogue(X[T, K] * W[N, K]^T)        bfloat16 operands, float32 accumulation
 //
@@ -13,10 +13,10 @@
 //     tcgen05.mma (M = 128, N = T, K = 16), tcgen05.commit frees the stage.
 //   * A matrix of 2,048 rows has only 16 such tiles, far too few blocks to pull the whole HBM
 //     bandwidth. The k range is therefore split over the 1, 2, 4 or 8 blocks of a thread-block
-//     cluster: each block multiplies its k slice, puts its partial [128 x T] tile into its own shared
-//     memory, and after a cluster barrier block r of the cluster adds up rows [128 r / S, 128 (r+1) / S)
-//     of all S partial tiles through distributed shared memory, in a fixed order, and runs the
-//     epilogue on them. No atomics, no second kernel, the same result every run.
+//     cluster: each block multiplies its k slice and stores rows [128 r / S, 128 (r+1) / S) of its
+//     partial [128 x T] tile into the shared memory of block r of the cluster (st.shared::cluster, one
+//     slot per sender, no waiting); after one cluster barrier block r adds up its S slots in a fixed
+//     order and runs the epilogue on its rows. No atomics, no second kernel, the same result every run.
 //   * Epilogues as in the small-batch product: store (bfloat16 or float32), add to the float32
 //     residual stream, SwiGLU, and the short convolution's gate with carried state (one token per
 //     request).
@@ -24,13 +24,15 @@
 // Every wait on an mbarrier is bounded (tcgen05.cuh); a block that gives up records an error code and
 // still takes part in the cluster barriers, which have no time limit of their own.
 //
-// Measured on a B200 at 64 rows (weights cold): 2048 x 8192 18.5 us with four splits (the library
-// product 13.3), 2048 x 2048 11.5 us (5.7), gate|up 8192 x 2048 with SwiGLU 29.8 us (15.9 with its
-// activation kernel), 65536 x 2048 74 us (55). The k loop of a block runs at the speed of the stream,
-// but each block pays set-up, the cluster barriers and an epilogue that nothing overlaps, clusters of
-// eight do not all fit the GPU at once, and wide matrices come in three and a half waves. Until a
-// persistent form with a double-buffered accumulator hides that, the engine keeps the library product for
-// these row counts and runs this kernel only when asked to (CELEG_B200_TC_PRODUCTS=stream).
+// Measured on a B200 at 64 rows (weights cold, CUDA-graph chains over rotating copies): 2048 x 8192 19.7 us
+// with four splits (the library product 13.3), 2048 x 2048 10.9 us (5.7), gate|up 8192 x 2048 with SwiGLU
+// 27.8 us (15.9 with its activation kernel), 65536 x 2048 94 us (56). A block's k loop runs at the speed of
+// the stream once it is going, but with 128 weight rows a block a matrix of 2,048 rows is 16 tiles: four
+// splits use 64 SMs, eight splits need clusters of eight, of which the GPU does not hold sixteen at once
+// (24 us); set-up, the cluster barrier and the epilogue are not overlapped with anything, and wide
+// matrices come in three and a half waves. Until tiles of 64 rows and a persistent form with a
+// double-buffered accumulator change that, the engine keeps the library product for these row counts and
+// runs this kernel only when asked to (CELEG_B200_TC_PRODUCTS=stream).
 //
 // celeg hands these products to cuBLAS (src/backend/cuda/runtime/gemm_dispatcher.cpp:49-64) and runs
 // the activation, the convolution and the residual add as kernels of their own.
@@ -39,7 +41,8 @@
 namespace celeg_b200 {
 
 constexpr int kStreamThreads = 128;
-constexpr int kStreamMaxRows = 128;
+constexpr int kStreamMaxRows = 64;
+constexpr int kStreamMaxStages = 6;
 constexpr int kStreamMaxConvTaps = 16;
 constexpr unsigned kStreamWeightTileBytes = kTileM * kTileK * 2;
 
@@ -68,13 +71,14 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 
-// A float of the shared memory of block `rank` of this cluster, at the place `local` has in this block.
-__device__ __forceinline__ float load_cluster_shared(unsigned local, unsigned rank) {
+// The address that `local` (a shared-memory address of this block) has in block `rank` of the cluster.
+__device__ __forceinline__ unsigned cluster_address(unsigned local, unsigned rank) {
     unsigned remote;
-    float v;
     asm("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote));
-    return v;
+    return remote;
+}
+__device__ __forceinline__ void store_cluster_shared(unsigned remote, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(remote), "f"(v) : "memory");
 }
 
 // MODE is a template parameter: the code of one epilogue is small, and a block runs it once, cold;
@@ -122,12 +126,12 @@ __device__ __forceinline__ void stream_epilogue(const StreamParams& p, const flo
 }
 
 // grid = (tiles of 128 weight rows, 1, splits), cluster = (1, 1, splits)
-template <int WT, int STAGES, int MODE>
+template <int WT, int MODE>
 __global__ void __launch_bounds__(kStreamThreads)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                   const StreamParams p) {
+                   const StreamParams p, const int STAGES) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], accum_bar;
+    __shared__ __align__(8) unsigned long long full_bar[kStreamMaxStages], empty_bar[kStreamMaxStages], accum_bar;
     __shared__ unsigned tmem_base_slot;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -197,8 +201,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     if (error) atomicExch(p.error_flag, error);
 
-    // the partial tile of this block: [set][token][weight row] float32, over the ring (every copy has
-    // landed and every MMA has read its stage when the accumulator is complete)
+    // Slots behind the ring, one per sender: [sender][set][token][row of mine] float32. A thread reads its
+    // row of the accumulators from tensor memory and stores it into the slot of this block in the block
+    // that owns the row; the stores are not waited for.
     __syncwarp();
     bool have = true;
     if (my_tiles > 0) {
@@ -207,9 +212,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (!have && lane == 0) atomicExch(p.error_flag, 43);
     }
     tcgen05_fence_after();
-    float* partial = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+    const int rows_here = kTileM / p.splits;
+    const unsigned slots_addr = smem_base + (unsigned)STAGES * stage_bytes;
     const int row = warp * 32 + lane;
     if (have) {
+        const unsigned owner_base = cluster_address(slots_addr, (unsigned)(row / rows_here));
+        const int mine = row % rows_here;
 #pragma unroll 1
         for (int t = 0; t < WT; ++t) {
 #pragma unroll 1
@@ -222,25 +230,28 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     for (int i = 0; i < 32; ++i) v[i] = 0.0f;
                 }
 #pragma unroll
-                for (int i = 0; i < 32; ++i) partial[((size_t)(t * p.t_pad + c0 + i)) * kTileM + row] = v[i];
+                for (int i = 0; i < 32; ++i)
+                    store_cluster_shared(owner_base + (unsigned)(((((rank * WT + t) * p.t_pad) + c0 + i) * rows_here + mine) * 4),
+                                         v[i]);
             }
         }
     } else if (warp == 0 && lane == 0) {
         // giving up: copies that were issued must land before the shared memory goes away
         for (int s = 0; s < STAGES && s < my_tiles; ++s) mbar_wait(smem_u32(&full_bar[s]), 0);
     }
-    __syncthreads();
-    if (p.splits > 1) cluster_sync_all();
+    // every block's stores are done and visible when all have passed this barrier; after it a block only
+    // reads its own shared memory, so it may leave whenever it is done
+    if (p.splits > 1)
+        cluster_sync_all();
+    else
+        __syncthreads();
 
-    // block `rank` sums rows [rank R, (rank + 1) R) of all partial tiles and finishes them. A thread
-    // keeps its weight row and walks over the tokens, four at a time: their loads (from the other
-    // blocks' shared memory, and of the residual) are all in flight before the first is used.
-    const int rows_here = kTileM / p.splits;
+    // this block's rows: the S slots summed in the order of the ranks, then the epilogue. A thread keeps
+    // its row and walks over the tokens, four at a time, the residual's loads in flight together.
+    const float* slots = reinterpret_cast<const float*>(smem_raw + (slots_addr - smem_u32(smem_raw)));
     const int local = threadIdx.x % rows_here;
     const int token_step = kStreamThreads / rows_here;
-    const int tile_row = rank * rows_here + local;
-    const int column = n0 + tile_row;
-    const unsigned partial_addr = smem_base;
+    const int column = n0 + rank * rows_here + local;
     constexpr int kBatch = 4;
     if (column < p.n) {
         for (int first = threadIdx.x / rows_here; first < p.rows; first += kBatch * token_step) {
@@ -257,18 +268,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         residual[b] = __ldcg(reinterpret_cast<const float*>(p.y) + (size_t)token * p.ldy + column);
 #pragma unroll
                     for (int t = 0; t < WT; ++t) {
-                        const unsigned at = partial_addr + (unsigned)(((t * p.t_pad + token) * kTileM + tile_row) * 4);
-                        if (p.splits > 1) {
-                            // all loads first, then the sum in the order of the ranks
-                            float piece[8];
-#pragma unroll
-                            for (int source = 0; source < 8; ++source)
-                                piece[source] = source < p.splits ? load_cluster_shared(at, (unsigned)source) : 0.0f;
-#pragma unroll
-                            for (int source = 0; source < 8; ++source) sum[b][t] += piece[source];
-                        } else {
-                            sum[b][t] = partial[(size_t)(t * p.t_pad + token) * kTileM + tile_row];
-                        }
+                        for (int source = 0; source < p.splits; ++source)
+                            sum[b][t] += slots[(size_t)(((source * WT + t) * p.t_pad) + token) * rows_here + local];
                     }
                 }
             }
@@ -279,19 +280,31 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
         }
     }
-    if (p.splits > 1) cluster_sync_all();            // nobody leaves while its shared memory may be read
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, tmem_columns);
 }
 
-template <int WT, int STAGES, int MODE>
+template <int WT, int MODE>
 static int launch_stream(const CUtensorMap& map_w, const CUtensorMap& map_x, const StreamParams& p, int tiles,
                          cudaStream_t stream) {
-    const size_t ring = (size_t)STAGES * (WT * kStreamWeightTileBytes + (size_t)p.t_pad * kTileK * 2);
-    const size_t partial = (size_t)WT * p.t_pad * kTileM * sizeof(float);
-    const size_t smem = (ring > partial ? ring : partial) + 1024;
-    auto kernel = gemm_stream_kernel<WT, STAGES, MODE>;
+    const size_t stage = WT * kStreamWeightTileBytes + (size_t)p.t_pad * kTileK * 2;
+    const size_t slots = (size_t)WT * p.t_pad * kTileM * sizeof(float);
+    static int smem_limit = 0;
+    if (smem_limit == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&smem_limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess)
+            smem_limit = 200 * 1024;
+    }
+    int stages = (int)(((size_t)smem_limit - 2048 - slots) / stage);
+    if (stages > kStreamMaxStages) stages = kStreamMaxStages;
+    if (stages < 2) {
+        set_error("gemm_stream: %d rows of %d tile sets leave no room for two stages beside the partial tiles", p.rows, WT);
+        return -1;
+    }
+    const size_t smem = (size_t)stages * stage + slots + 1024;
+    auto kernel = gemm_stream_kernel<WT, MODE>;
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (status != cudaSuccess) {
         set_error("gemm_stream: %s (shared memory %zu bytes)", cudaGetErrorString(status), smem);
@@ -309,7 +322,7 @@ static int launch_stream(const CUtensorMap& map_w, const CUtensorMap& map_x, con
     attribute[0].val.clusterDim.z = p.splits;
     config.attrs = attribute;
     config.numAttrs = 1;
-    status = cudaLaunchKernelEx(&config, kernel, map_w, map_x, p);
+    status = cudaLaunchKernelEx(&config, kernel, map_w, map_x, p, stages);
     if (status != cudaSuccess) {
         set_error("gemm_stream: launch failed: %s", cudaGetErrorString(status));
         return -2;
@@ -328,7 +341,7 @@ CELEG_API void celeg_gemm_stream_set_splits(int splits) { g_stream_splits = spli
 // mode 0: y bf16 [rows, n] = x w^T; 1: y float32; 2: y float32 += x w^T (rounded to bf16 first);
 // 3: w is [2n, k] (gate rows then up rows), y bf16 = silu(x gate^T) * (x up^T); 4: w is [3n, k] (B, C, X
 // rows of the short convolution), y bf16 = C * conv(B*X) over the carried state, which is shifted (row i
-// of x is the only token of request i in this step). 1 <= rows <= 128; x must have x_rows >= rows rows
+// of x is the only token of request i in this step). 1 <= rows <= 64; x must have x_rows >= rows rows
 // that may be read; k, ldx and ldw multiples of 8; x and w 16-byte aligned.
 CELEG_API int celeg_gemm_stream(const void* x, int ldx, int x_rows, const void* w, int ldw, void* y, int ldy, int rows,
                                 int n, int k, int mode, const float* conv_w, int taps, float* state,
@@ -376,10 +389,10 @@ CELEG_API int celeg_gemm_stream(const void* x, int ldx, int x_rows, const void* 
     if (!tensor_map_for(w, (long long)sets * n, k, ldw, kTileM, &map_w)) return -2;
     if (!tensor_map_for(x, x_rows, k, ldx, p.t_pad, &map_x)) return -2;
     switch (mode) {
-        case kStreamStoreBf16: return launch_stream<1, 6, kStreamStoreBf16>(map_w, map_x, p, tiles, stream);
-        case kStreamStoreF32: return launch_stream<1, 6, kStreamStoreF32>(map_w, map_x, p, tiles, stream);
-        case kStreamAddResidual: return launch_stream<1, 6, kStreamAddResidual>(map_w, map_x, p, tiles, stream);
-        case kStreamSwiGlu: return launch_stream<2, 4, kStreamSwiGlu>(map_w, map_x, p, tiles, stream);
-        default: return launch_stream<3, 3, kStreamConv>(map_w, map_x, p, tiles, stream);
+        case kStreamStoreBf16: return launch_stream<1, kStreamStoreBf16>(map_w, map_x, p, tiles, stream);
+        case kStreamStoreF32: return launch_stream<1, kStreamStoreF32>(map_w, map_x, p, tiles, stream);
+        case kStreamAddResidual: return launch_stream<1, kStreamAddResidual>(map_w, map_x, p, tiles, stream);
+        case kStreamSwiGlu: return launch_stream<2, kStreamSwiGlu>(map_w, map_x, p, tiles, stream);
+        default: return launch_stream<3, kStreamConv>(map_w, map_x, p, tiles, stream);
     }
 }

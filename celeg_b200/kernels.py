@@ -335,11 +335,11 @@ def gemv_bf16(x, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_S
         prepare.sumsq.stride(0) if prepare else 0, _stream()))
 
 
-STREAM_MAX_ROWS = 128
+STREAM_MAX_ROWS = 64
 
 
 def gemm_stream_supported(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Shapes the weight-streaming tcgen05 product takes (up to 128 rows of activations)."""
+    """Shapes the weight-streaming tcgen05 product takes (up to 64 rows of activations)."""
     return (0 < rows <= STREAM_MAX_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -348,7 +348,7 @@ def gemm_stream_supported(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
 def gemm_stream(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int, error_flag: torch.Tensor, *,
                 conv_w: Optional[torch.Tensor] = None, taps: int = 0, state: Optional[torch.Tensor] = None,
                 slot_stride: int = 0, span_slot: Optional[torch.Tensor] = None) -> None:
-    """y[:rows] = epilogue(x[:rows] @ w.T) for up to 128 rows on tcgen05 tensor cores, the weights streamed
+    """y[:rows] = epilogue(x[:rows] @ w.T) for up to 64 rows on tcgen05 tensor cores, the weights streamed
     once by TMA, the k range split over a thread-block cluster. Modes as :func:`gemv_bf16`
     (GEMV_STORE ... GEMV_CONV)."""
     sets = {GEMV_SWIGLU: 2, GEMV_CONV: 3}.get(mode, 1)

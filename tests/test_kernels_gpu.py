@@ -650,7 +650,7 @@ def test_gemm_tcgen05_store_and_swiglu(m, n, k, variant, monkeypatch):
 
 
 @pytest.mark.parametrize("splits", [0, 1, 2, 8])
-@pytest.mark.parametrize("rows,n,k", [(64, 512, 1024), (17, 128, 64), (33, 100, 136), (128, 256, 2048), (96, 777, 520),
+@pytest.mark.parametrize("rows,n,k", [(64, 512, 1024), (17, 128, 64), (33, 100, 136), (64, 256, 2048), (48, 777, 520),
                                       (20, 48, 72)])
 def test_gemm_stream_modes(rows, n, k, splits):
     """The weight-streaming tcgen05 product (weights as the M side, k split over a cluster, partial
@@ -693,7 +693,7 @@ def test_gemm_stream_modes(rows, n, k, splits):
         lib.celeg_gemm_stream_set_splits(0)
 
 
-@pytest.mark.parametrize("rows,hidden,k,taps", [(20, 64, 64, 3), (64, 512, 1024, 3), (33, 40, 136, 4), (100, 48, 520, 2),
+@pytest.mark.parametrize("rows,hidden,k,taps", [(20, 64, 64, 3), (64, 512, 1024, 3), (33, 40, 136, 4), (50, 48, 520, 2),
                                                 (17, 33, 64, 1)])
 def test_gemm_stream_conv_epilogue_matches_the_separate_kernels(rows, hidden, k, taps):
     """Input projection + gate + taps over the carried state + state shift inside the streaming product,
