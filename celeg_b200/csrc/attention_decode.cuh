@@ -91,7 +91,10 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     constexpr int kChunks = D_PAD / 8;
     constexpr int kKTiles = D_PAD / 16;
     constexpr int kOTiles = D_PAD / 8;
-    constexpr int kKeysPerLane = BN / 32;
+    constexpr int kStages = D_PAD <= 128 ? 2 : 1;          // stages per warp
+    constexpr int TN = BN / kStages;                       // keys per stage (the warp's shared memory is BN keys of K and of V)
+    constexpr int kKeysPerLane = TN / 32;
+    static_assert(TN % 32 == 0, "a stage holds a multiple of 32 keys");
     const int lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c2 = (lane & 3) * 2;
     const int group = p.q_heads / p.kv_heads;
@@ -105,8 +108,7 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     const int end = min(begin + p.chunk, pos + 1);
 
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* k_s = q_s + 16 * D_PAD + (size_t)warp * 2 * BN * D_PAD;
-    __nv_bfloat16* v_s = k_s + BN * D_PAD;
+    __nv_bfloat16* k_s = q_s + 16 * D_PAD + (size_t)warp * 2 * BN * D_PAD;      // this warp's stages
     DecodeShared& shared = *reinterpret_cast<DecodeShared*>(smem_raw + decode_smem_bytes<D_PAD, BN>());
     float (&warp_max_s)[kDecodeWarps][16] = shared.warp_max;
     float (&warp_sum_s)[kDecodeWarps][16] = shared.warp_sum;
@@ -137,7 +139,11 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     const float scale_log2 = p.scale * 1.4426950408889634f;
     const int mi = lane >> 3, lr = lane & 7;
 
-    for (int tile_begin = begin + warp * BN; tile_begin < end; tile_begin += kDecodeWarps * BN) {
+    // A warp's part of the shared memory is kStages stages of [K tile | V tile] of TN keys: with two
+    // stages the next tile is on its way (page lookups included) while this one is in the tensor cores.
+    auto issue = [&](const int tile_begin, const int stage) {
+        __nv_bfloat16* k_dst = k_s + (size_t)stage * 2 * TN * D_PAD;
+        __nv_bfloat16* v_dst = k_dst + TN * D_PAD;
         // page offsets of this lane's keys, then the copies of the whole tile in one go
         long long offs[kKeysPerLane];
 #pragma unroll
@@ -152,9 +158,8 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
                     offs[i] = (long long)page * p.page_stride + ((long long)kvh * p.page_tokens + key % p.page_tokens) * d;
             }
         }
-        __syncwarp();                               // every lane is done reading the previous tile
 #pragma unroll
-        for (int i = 0; i < BN * kChunks / 32; ++i) {
+        for (int i = 0; i < TN * kChunks / 32; ++i) {
             const int idx = lane + 32 * i;
             const int r = idx / kChunks, ch = idx % kChunks;
             long long off = -1;
@@ -163,8 +168,8 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
                 const long long candidate = __shfl_sync(0xffffffffu, offs[j], r & 31);
                 if ((r >> 5) == j) off = candidate;
             }
-            __nv_bfloat16* kd = k_s + tile_offset<D_PAD>(r, ch);
-            __nv_bfloat16* vd = v_s + tile_offset<D_PAD>(r, ch);
+            __nv_bfloat16* kd = k_dst + tile_offset<D_PAD>(r, ch);
+            __nv_bfloat16* vd = v_dst + tile_offset<D_PAD>(r, ch);
             if (off >= 0 && ch * 8 < d) {
                 cp_async_16(kd, p.k_cache + off + ch * 8);
                 cp_async_16(vd, p.v_cache + off + ch * 8);
@@ -173,12 +178,31 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
                 *reinterpret_cast<uint4*>(vd) = zero;
             }
         }
-        cp_async_wait_all();
+        cp_async_commit();
+    };
+    constexpr int kTileStride = kDecodeWarps * TN;
+    int tile_begin = begin + warp * TN;
+    if (kStages == 2 && tile_begin < end) issue(tile_begin, 0);
+    for (int iteration = 0; tile_begin < end; ++iteration, tile_begin += kTileStride) {
+        const int stage = kStages == 2 ? (iteration & 1) : 0;
+        if (kStages == 2) {
+            if (tile_begin + kTileStride < end) {
+                issue(tile_begin + kTileStride, stage ^ 1);
+                cp_async_wait_group<1>();
+            } else {
+                cp_async_wait_group<0>();
+            }
+        } else {
+            issue(tile_begin, 0);
+            cp_async_wait_group<0>();
+        }
         __syncwarp();
+        const __nv_bfloat16* k_t = k_s + (size_t)stage * 2 * TN * D_PAD;
+        const __nv_bfloat16* v_t = k_t + TN * D_PAD;
 
-        float s[BN / 8][4];
+        float s[TN / 8][4];
 #pragma unroll
-        for (int i = 0; i < BN / 8; ++i)
+        for (int i = 0; i < TN / 8; ++i)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[i][e] = 0.0f;
 #pragma unroll
@@ -186,16 +210,16 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
             unsigned a[4];
             ldmatrix_x4(a, q_s + tile_offset<D_PAD>((mi & 1) * 8 + lr, kt * 2 + (mi >> 1)));
 #pragma unroll
-            for (int np = 0; np < BN / 16; ++np) {
+            for (int np = 0; np < TN / 16; ++np) {
                 unsigned b[4];
-                ldmatrix_x4(b, k_s + tile_offset<D_PAD>(np * 16 + (mi >> 1) * 8 + lr, kt * 2 + (mi & 1)));
+                ldmatrix_x4(b, k_t + tile_offset<D_PAD>(np * 16 + (mi >> 1) * 8 + lr, kt * 2 + (mi & 1)));
                 mma_bf16(s[2 * np], a, b[0], b[1]);
                 mma_bf16(s[2 * np + 1], a, b[2], b[3]);
             }
         }
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < BN / 8; ++nt) {
+        for (int nt = 0; nt < TN / 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = tile_begin + nt * 8 + c2 + (e & 1);
@@ -217,7 +241,7 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
             run_sum[half] *= correction[half];
         }
 #pragma unroll
-        for (int nt = 0; nt < BN / 8; ++nt) {
+        for (int nt = 0; nt < TN / 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float pv = exp2f(s[nt][e] - safe_max[e >> 1]);
@@ -233,7 +257,7 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
             o[i][3] *= correction[1];
         }
 #pragma unroll
-        for (int kt = 0; kt < BN / 16; ++kt) {
+        for (int kt = 0; kt < TN / 16; ++kt) {
             unsigned a[4];
             a[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
             a[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
@@ -242,11 +266,12 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
 #pragma unroll
             for (int np = 0; np < kOTiles / 2; ++np) {
                 unsigned b[4];
-                ldmatrix_x4_trans(b, v_s + tile_offset<D_PAD>(kt * 16 + (mi & 1) * 8 + lr, np * 2 + (mi >> 1)));
+                ldmatrix_x4_trans(b, v_t + tile_offset<D_PAD>(kt * 16 + (mi & 1) * 8 + lr, np * 2 + (mi >> 1)));
                 mma_bf16(o[2 * np], a, b[0], b[1]);
                 mma_bf16(o[2 * np + 1], a, b[2], b[3]);
             }
         }
+            __syncwarp();                               // every lane is done with the stage before it is refilled
     }
 
     // row sums over the four lanes that share a row; then the warps' results meet in shared memory
