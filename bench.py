@@ -25,7 +25,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: LFM2-1.2B sizes
+# the sizes of LFM2-1.2B, the configuration the headline numbers are quoted on
 LFM2_1P2B = {
     "model_type": "lfm2", "vocab_size": 65536, "hidden_size": 2048, "num_hidden_layers": 16,
     "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
@@ -388,10 +388,10 @@ def run_ours(args) -> dict:
 
 def run_reference(args) -> dict:
     """The reference arm: celeg is a C++/CUDA project built with CMake (no Python package), so there
-    is nothing ``pip install /root/reference`` can install; see DESIGN.md."""
+    is nothing ``pip install`` can install from its checkout."""
     return {"impl": "reference",
             "unavailable": "celsowm/celeg is a CMake C++/CUDA project without setup.py or pyproject.toml: "
-                           "'pip install --no-index ... /root/reference' answers 'not installable'"}
+                           "'pip install --no-index ... <checkout>' answers 'not installable'"}
 
 
 def main() -> int:

@@ -36,7 +36,7 @@ def prompts_of(vocab, lengths, seed):
 
 @pytest.mark.parametrize("graphs", [False, True])
 def test_greedy_generation_matches_plain_model_float32(models, graphs):
-    """BASELINE workload of tiny A: prompts of 5, 17 and 31 tokens, 16 greedy tokens each, run
+    """The benchmark's workload in small, on tiny A: prompts of 5, 17 and 31 tokens, 16 greedy tokens each, run
     together through the scheduler."""
     from celeg_b200 import Engine
     folder, config, weights = models["A"]
