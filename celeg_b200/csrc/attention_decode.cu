@@ -44,13 +44,13 @@ CELEG_API long long celeg_attention_decode_scratch_bytes(int tokens, int q_heads
     return o + ml + counters;
 }
 
-// `counters` must be zero before the first launch; every launch leaves them zero.
-CELEG_API int celeg_attention_decode(const void* q, int q_row_stride, void* out, const void* k_cache,
-                                     const void* v_cache, long long page_stride, const int* positions,
-                                     const int* token_span, const int* block_table, int table_stride, int tokens,
-                                     int q_heads, int kv_heads, int head_dim, int page_tokens, int window,
-                                     float scale, int chunk, int max_splits, float* partial_o, float* partial_ml,
-                                     int* counters, int* error_flag, cudaStream_t stream) {
+static int attention_decode_checked(const void* q, int q_row_stride, void* out, const void* k_cache,
+                                    const void* v_cache, long long page_stride, const int* positions,
+                                    const int* token_span, const int* block_table, int table_stride, int tokens,
+                                    int q_heads, int kv_heads, int head_dim, int page_tokens, int window, float scale,
+                                    int chunk, int max_splits, float* partial_o, float* partial_ml, int* counters,
+                                    int* error_flag, int fuse_qk, const float* q_norm_w, const float* k_norm_w,
+                                    const float* inv_freq, int rotary_dim, float norm_eps, cudaStream_t stream) {
     CELEG_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && head_dim > 0 && page_tokens > 0,
                   "attention_decode: invalid sizes tokens=%d q_heads=%d kv_heads=%d head_dim=%d page_tokens=%d",
                   tokens, q_heads, kv_heads, head_dim, page_tokens);
@@ -63,6 +63,15 @@ CELEG_API int celeg_attention_decode(const void* q, int q_row_stride, void* out,
     CELEG_REQUIRE(q_row_stride % 8 == 0, "attention_decode: q row stride %d must be a multiple of 8", q_row_stride);
     CELEG_REQUIRE(chunk > 0 && max_splits > 0 && max_splits <= 65535 && tokens <= 65535 && kv_heads <= 65535,
                   "attention_decode: invalid split chunk=%d max_splits=%d", chunk, max_splits);
+    if (fuse_qk) {
+        CELEG_REQUIRE(q_row_stride >= (q_heads + 2 * kv_heads) * head_dim,
+                      "attention_decode: with the q/k post-processing fused the rows must hold q, k and v (%d < %d)",
+                      q_row_stride, (q_heads + 2 * kv_heads) * head_dim);
+        CELEG_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0 &&
+                          (norm_eps > 0.0f || (!q_norm_w && !k_norm_w)),
+                      "attention_decode: rotary_dim %d must be even and at most head_dim %d, eps positive", rotary_dim,
+                      head_dim);
+    }
     if (tokens == 0) return 0;
     DecodeParams p;
     p.q = (const __nv_bfloat16*)q;
@@ -87,10 +96,50 @@ CELEG_API int celeg_attention_decode(const void* q, int q_row_stride, void* out,
     p.partial_ml = partial_ml;
     p.counters = counters;
     p.error_flag = error_flag;
+    p.fuse_qk = fuse_qk;
+    p.q_norm_w = q_norm_w;
+    p.k_norm_w = k_norm_w;
+    p.inv_freq = inv_freq;
+    p.rotary_dim = rotary_dim;
+    p.norm_eps = norm_eps;
+    p.k_cache_w = (__nv_bfloat16*)const_cast<void*>(k_cache);
+    p.v_cache_w = (__nv_bfloat16*)const_cast<void*>(v_cache);
     dim3 grid(max_splits, kv_heads, tokens);
     if (head_dim <= 64) return launch_decode<64, 64>(p, grid, stream);
     if (head_dim <= 128) return launch_decode<128, 64>(p, grid, stream);
     return launch_decode<256, 32>(p, grid, stream);
+}
+
+// `counters` must be zero before the first launch; every launch leaves them zero.
+CELEG_API int celeg_attention_decode(const void* q, int q_row_stride, void* out, const void* k_cache,
+                                     const void* v_cache, long long page_stride, const int* positions,
+                                     const int* token_span, const int* block_table, int table_stride, int tokens,
+                                     int q_heads, int kv_heads, int head_dim, int page_tokens, int window,
+                                     float scale, int chunk, int max_splits, float* partial_o, float* partial_ml,
+                                     int* counters, int* error_flag, cudaStream_t stream) {
+    return attention_decode_checked(q, q_row_stride, out, k_cache, v_cache, page_stride, positions, token_span,
+                                    block_table, table_stride, tokens, q_heads, kv_heads, head_dim, page_tokens, window,
+                                    scale, chunk, max_splits, partial_o, partial_ml, counters, error_flag, 0, nullptr,
+                                    nullptr, nullptr, 0, 0.0f, stream);
+}
+
+// The same with the q/k post-processing of the step's tokens done inside: qkv holds the raw projection
+// rows [q heads | k heads | v heads]; per-head RMSNorm (weights may be null) and split-half rotation
+// (inv_freq may be null) are applied to q in shared memory and to the token's own key, which is written
+// into the cache with its value. The caches are written: no other kernel may read the tokens' own positions
+// in them at the same time.
+CELEG_API int celeg_attention_decode_fused(void* qkv, int q_row_stride, void* out, void* k_cache, void* v_cache,
+                                           long long page_stride, const int* positions, const int* token_span,
+                                           const int* block_table, int table_stride, int tokens, int q_heads,
+                                           int kv_heads, int head_dim, int page_tokens, int window, float scale,
+                                           int chunk, int max_splits, float* partial_o, float* partial_ml,
+                                           int* counters, int* error_flag, const float* q_norm_w,
+                                           const float* k_norm_w, const float* inv_freq, int rotary_dim, float norm_eps,
+                                           cudaStream_t stream) {
+    return attention_decode_checked(qkv, q_row_stride, out, k_cache, v_cache, page_stride, positions, token_span,
+                                    block_table, table_stride, tokens, q_heads, kv_heads, head_dim, page_tokens, window,
+                                    scale, chunk, max_splits, partial_o, partial_ml, counters, error_flag, 1, q_norm_w,
+                                    k_norm_w, inv_freq, rotary_dim, norm_eps, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -47,6 +47,19 @@ struct DecodeParams {
     float* partial_ml;             // [tokens, q_heads, max_splits, 2]
     int* counters;                 // [tokens, kv_heads], zero between launches
     int* error_flag;
+    // Optional: the q/k post-processing of the step's own token done here instead of by a kernel of its
+    // own. Then q (and the k and v behind it in the same rows: [q heads | k heads | v heads]) is the raw
+    // projection; an item normalises and rotates its query heads itself, and the item whose keys include
+    // the token's own position does the same for that key, writes it and the value into the cache and uses
+    // them from shared memory (nobody else reads that row in this launch).
+    int fuse_qk;
+    const float* q_norm_w;         // [head_dim] or null
+    const float* k_norm_w;
+    const float* inv_freq;         // [rotary_dim / 2] or null
+    int rotary_dim;
+    float norm_eps;
+    __nv_bfloat16* k_cache_w;      // the caches again, writable
+    __nv_bfloat16* v_cache_w;
 };
 
 __device__ __forceinline__ void bf16x8_to_float(const uint4& raw, float* f) {
@@ -72,7 +85,51 @@ struct DecodeShared {
     float head_max[kMaxGroup], head_sum[kMaxGroup];
     int is_last;
     int pad[3];
+    alignas(16) __nv_bfloat16 new_k[kMaxDecodeHeadDim];    // the step's own key and value (fused q/k)
+    alignas(16) __nv_bfloat16 new_v[kMaxDecodeHeadDim];
 };
+
+// Per-head RMSNorm and split-half rotation of one head that a warp holds in shared memory (element i at
+// at(i)), the arithmetic of qk_norm_rope.cuh: sum of squares, reciprocal root, angle and rotation in float32,
+// one rounding to bfloat16. `out(i)` is where element i goes (may be the same place).
+template <typename At, typename Out>
+__device__ __forceinline__ void decode_norm_rope_head(At at, Out out, const float* weight, const float* inv_freq,
+                                                      const int head_dim, const int rotary_dim, const float eps,
+                                                      const int pos, const int lane) {
+    float inv = 1.0f;
+    if (weight) {
+        float sum = 0.0f;
+        for (int i = lane; i < head_dim; i += 32) {
+            const float x = __bfloat162float(*at(i));
+            sum += x * x;
+        }
+        sum = warp_sum(sum);
+        inv = 1.0f / sqrtf(sum / (float)head_dim + eps);
+    }
+    const int half = rotary_dim >> 1;
+    for (int i = lane; i < half; i += 32) {
+        float a = __bfloat162float(*at(i));
+        float b = __bfloat162float(*at(i + half));
+        if (weight) {
+            a = a * inv * weight[i];
+            b = b * inv * weight[i + half];
+        }
+        float ra = a, rb = b;
+        if (inv_freq) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            ra = a * cs - b * sn;
+            rb = b * cs + a * sn;
+        }
+        *out(i) = __float2bfloat16_rn(ra);
+        *out(i + half) = __float2bfloat16_rn(rb);
+    }
+    for (int i = rotary_dim + lane; i < head_dim; i += 32) {
+        float a = __bfloat162float(*at(i));
+        if (weight) a = a * inv * weight[i];
+        *out(i) = __float2bfloat16_rn(a);
+    }
+}
 
 template <int D_PAD, int BN>
 __host__ __device__ constexpr size_t decode_item_bytes() {
@@ -128,6 +185,43 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
             *reinterpret_cast<uint4*>(dst) = zero;
     }
     sync();
+    const bool own_key_here = p.fuse_qk && end == pos + 1;       // this item's keys include the token's own
+    if (p.fuse_qk) {
+        const int rotary = p.inv_freq ? p.rotary_dim : (d & ~1);    // without rotation the pair loop just normalises
+        // the query heads of the group, in place in their tile: a warp per head
+        for (int r = warp; r < group; r += kDecodeWarps) {
+            auto at = [&](int i) { return q_s + tile_offset<D_PAD>(r, i >> 3) + (i & 7); };
+            decode_norm_rope_head(at, at, p.q_norm_w, p.inv_freq, d, rotary, p.norm_eps, pos, lane);
+        }
+        if (own_key_here) {
+            // the token's own key (warp 0) and value (warp 1): into shared memory and into the cache
+            const int page = table[pos / p.page_tokens];
+            if (page < 0) {
+                if (tid == 0) atomicExch(p.error_flag, 1);
+            } else {
+                const long long cache_at = (long long)page * p.page_stride +
+                                           ((long long)kvh * p.page_tokens + pos % p.page_tokens) * d;
+                const __nv_bfloat16* row = p.q + (size_t)t * p.q_row_stride;
+                if (warp == 0) {
+                    const __nv_bfloat16* raw = row + (size_t)(p.q_heads + kvh) * d;
+                    for (int i = lane; i < d; i += 32) shared.new_k[i] = __ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(raw + i)));
+                    __syncwarp();
+                    auto at = [&](int i) { return shared.new_k + i; };
+                    decode_norm_rope_head(at, at, p.k_norm_w, p.inv_freq, d, rotary, p.norm_eps, pos, lane);
+                    __syncwarp();
+                    for (int i = lane; i < d; i += 32) p.k_cache_w[cache_at + i] = shared.new_k[i];
+                } else if (warp == 1) {
+                    const __nv_bfloat16* raw = row + (size_t)(p.q_heads + p.kv_heads + kvh) * d;
+                    for (int i = lane; i < d; i += 32) {
+                        const __nv_bfloat16 v = __ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(raw + i)));
+                        shared.new_v[i] = v;
+                        p.v_cache_w[cache_at + i] = v;
+                    }
+                }
+            }
+        }
+        sync();
+    }
 
     float o[kOTiles][4];
 #pragma unroll
@@ -170,7 +264,11 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
             }
             __nv_bfloat16* kd = k_dst + tile_offset<D_PAD>(r, ch);
             __nv_bfloat16* vd = v_dst + tile_offset<D_PAD>(r, ch);
-            if (off >= 0 && ch * 8 < d) {
+            if (own_key_here && tile_begin + r == pos && ch * 8 < d) {
+                // the token's own key and value: not in the cache for this launch's readers, but here
+                *reinterpret_cast<uint4*>(kd) = *reinterpret_cast<const uint4*>(shared.new_k + ch * 8);
+                *reinterpret_cast<uint4*>(vd) = *reinterpret_cast<const uint4*>(shared.new_v + ch * 8);
+            } else if (off >= 0 && ch * 8 < d) {
                 cp_async_16(kd, p.k_cache + off + ch * 8);
                 cp_async_16(vd, p.v_cache + off + ch * 8);
             } else {

@@ -682,6 +682,11 @@ __device__ void attention_consume(const ProgramOp& op, const ProgramLayout& layo
     p.partial_ml = op.partial_ml;
     p.counters = op.counters;
     p.error_flag = error_flag;
+    p.fuse_qk = 0;                 // the program has an operation of its own for the q/k post-processing
+    p.q_norm_w = p.k_norm_w = p.inv_freq = nullptr;
+    p.rotary_dim = 0;
+    p.norm_eps = 0.0f;
+    p.k_cache_w = p.v_cache_w = nullptr;
     const GroupSync sync = {2 + group};
     unsigned char* mine = arena + (size_t)group * layout.attention_item_bytes;
     const long long items = (long long)op.rows * op.kv_heads * op.max_splits;

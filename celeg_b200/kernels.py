@@ -50,6 +50,10 @@ _SIGNATURES = {
     "celeg_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "celeg_attention_decode_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
+                                     c_void_p],
     "celeg_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                 c_void_p, c_void_p],
@@ -244,6 +248,23 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_ca
         _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim,
         page_tokens, int(window or 0), scale, chunk, max_splits, _ptr(partial_o), _ptr(partial_ml),
         _ptr(counters), _ptr(error_flag), _stream()))
+
+
+def attention_decode_fused(qkv: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_cache: torch.Tensor,
+                           v_cache: torch.Tensor, positions: torch.Tensor, token_span: torch.Tensor,
+                           block_table: torch.Tensor, tokens: int, q_heads: int, kv_heads: int, head_dim: int,
+                           page_tokens: int, window: Optional[int], scale: float, chunk: int, max_splits: int,
+                           partial_o: torch.Tensor, partial_ml: torch.Tensor, counters: torch.Tensor,
+                           error_flag: torch.Tensor, q_weight: Optional[torch.Tensor],
+                           k_weight: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                           eps: float) -> None:
+    """Decode attention over the raw q|k|v projection: per-head norm and rotation of q and of the token's own
+    key, the cache write of that key and its value, and the attention, in one launch."""
+    _check(library().celeg_attention_decode_fused(
+        _ptr(qkv), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
+        _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim, page_tokens,
+        int(window or 0), scale, chunk, max_splits, _ptr(partial_o), _ptr(partial_ml), _ptr(counters),
+        _ptr(error_flag), _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), rotary_dim, eps, _stream()))
 
 
 def attention_prefill_supported(q_heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:

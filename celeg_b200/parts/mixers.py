@@ -110,6 +110,16 @@ class AttentionMixer:
         table = step.block_tables[b.group]
         fused = self.position.fused() if self.position is not None else {"inv_freq": None, "rotary_dim": 0}
         store = b.owner and not self.reads_only
+        if (fused is not None and store and rt.fuse_decode_qk and self._decodes(step)):
+            # one token per request: norm, rotation and cache write happen inside the attention kernel
+            chunk, max_splits, partial_o, partial_ml, counters = self._decode_split(step)
+            kernels.attention_decode_fused(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
+                                           step.token_span, table, t, self.heads, self.kv_heads, self.head_dim,
+                                           b.page_tokens, self.window, self.scale, chunk, max_splits, partial_o,
+                                           partial_ml, counters, step.error_flag, self.q_norm, self.k_norm,
+                                           fused["inv_freq"], fused["rotary_dim"], self.eps)
+            rt.linear(self.attended, self.w_out, out, t)
+            return
         if fused is not None:
             kernels.qk_norm_rope_store(self.qkv, self.q_norm, self.k_norm, fused["inv_freq"], step.positions,
                                        step.token_span, table, b.k, b.v, t, self.heads, self.stored_kv_heads,
@@ -174,11 +184,16 @@ class AttentionMixer:
                           partial_o, partial_ml, counters)
         builder.product(self.attended, self.w_out, add_to_residual=True)
 
+    def _decodes(self, step: StepContext) -> bool:
+        """Whether the step goes to the split-key decode kernel (one query token per request)."""
+        rt = self.rt
+        return (step.max_span == 1 and step.tokens <= rt.max_requests and
+                kernels.attention_decode_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype))
+
     def attend(self, step: StepContext, table: torch.Tensor) -> None:
         b = self.binding
         rt = self.rt
-        if (step.max_span == 1 and step.tokens <= rt.max_requests and
-                kernels.attention_decode_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype)):
+        if self._decodes(step):
             chunk, max_splits, partial_o, partial_ml, counters = self._decode_split(step)
             kernels.attention_decode(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
                                      step.token_span, table, step.tokens, self.heads, self.kv_heads,

@@ -120,6 +120,8 @@ class Runtime:
         self.sink: Optional[_Sink] = None         # set by the residual stream around a part's forward
         self.sink_residual: Optional[torch.Tensor] = None
         self.split_norms = os.environ.get("CELEG_B200_SPLIT_NORM", "1") != "0"
+        # decode steps: q/k norm + rotation + cache write inside the attention kernel (0: a kernel of their own)
+        self.fuse_decode_qk = os.environ.get("CELEG_B200_FUSE_DECODE_QK", "1") != "0"
         # prompt-portion attention of head size 64 on tcgen05 (0: the mma.sync kernel, for comparisons)
         self.tcgen05_attention = os.environ.get("CELEG_B200_TC_ATTENTION", "1") != "0"
         self._flat: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}

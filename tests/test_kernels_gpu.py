@@ -347,6 +347,53 @@ def test_attention_decode_split_keys(heads, kv_heads, head_dim, page_tokens, win
         close(out, want, dtype)
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,window,chunk,normed", [
+    (4, 2, 16, 16, None, 64, True), (8, 2, 64, 16, None, 128, True), (6, 3, 80, 16, 37, 64, True),
+    (2, 1, 128, 32, None, 512, False), (5, 5, 48, 8, None, 64, True), (32, 8, 64, 16, None, 256, True),
+])
+def test_attention_decode_with_the_qk_step_inside(heads, kv_heads, head_dim, page_tokens, window, chunk, normed):
+    """The decode kernel fed with the raw q|k|v projection (it normalises and rotates q and the token's own
+    key, writes key and value into the cache, attends) against the separate kernels: same output, same cache."""
+    from celeg_b200 import kernels
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(19)
+    lengths = [1, 16, 17, 300, 511, 64]                    # keys of each request including the step's token
+    pages = sum((n + page_tokens - 1) // page_tokens for n in lengths) + 7
+    k_cache, v_cache, table, _, _ = paged_setup(rng, dtype, lengths, kv_heads, head_dim, page_tokens, pages)
+    tokens = len(lengths)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = dev(rounded(rng.normal(size=(tokens, width)), dtype), dtype)
+    q_w = dev((1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32)) if normed else None
+    k_w = dev((1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32)) if normed else None
+    inv_freq = dev((1e6 ** (-2.0 * np.arange(head_dim // 2) / head_dim)).astype(np.float32))
+    positions = dev(np.array([n - 1 for n in lengths], dtype=np.int32))
+    token_span = dev(np.arange(tokens, dtype=np.int32))
+    table_dev = dev(table)
+    scale, eps = head_dim ** -0.5, 1e-5
+    max_splits = (512 + chunk - 1) // chunk
+    partial_o = torch.empty(tokens * heads * max_splits * head_dim, dtype=torch.float32, device="cuda")
+    partial_ml = torch.empty(tokens * heads * max_splits * 2, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(tokens * kv_heads, dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # separate kernels on copies
+    qkv_a, k_a, v_a = qkv.clone(), k_cache.clone(), v_cache.clone()
+    kernels.qk_norm_rope_store(qkv_a, q_w, k_w, inv_freq, positions, token_span, table_dev, k_a, v_a, tokens, heads,
+                               kv_heads, head_dim, head_dim, page_tokens, eps, True, flag)
+    out_a = torch.zeros((tokens, heads * head_dim), dtype=dtype, device="cuda")
+    kernels.attention_decode(qkv_a, width, out_a, k_a, v_a, positions, token_span, table_dev, tokens, heads, kv_heads,
+                             head_dim, page_tokens, window, scale, chunk, max_splits, partial_o, partial_ml, counters, flag)
+    # one kernel, twice in a row (the second time the cache already holds the token's key: same result)
+    k_b, v_b = k_cache.clone(), v_cache.clone()
+    for _ in range(2):
+        out_b = torch.zeros_like(out_a)
+        kernels.attention_decode_fused(qkv.clone(), width, out_b, k_b, v_b, positions, token_span, table_dev, tokens,
+                                       heads, kv_heads, head_dim, page_tokens, window, scale, chunk, max_splits,
+                                       partial_o, partial_ml, counters, flag, q_w, k_w, inv_freq, head_dim, eps)
+        assert int(flag.item()) == 0 and int(counters.abs().sum().item()) == 0
+        assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
+        assert torch.equal(out_a, out_b)
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,window", [
     (4, 2, 16, 16, None), (3, 1, 32, 8, None), (5, 5, 48, 16, None), (8, 2, 64, 64, None),
     (6, 3, 80, 16, 37), (2, 1, 128, 32, None), (4, 4, 24, 16, 5), (2, 1, 256, 16, None), (4, 1, 112, 16, 100),
