@@ -326,7 +326,8 @@ static int launch_gemv(int mode, const __nv_bfloat16* x, int ldx, const __nv_bfl
             return launch_one<MT, 1, kGemvAddResidual, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, norm, stream);
         case kGemvSwiGlu:
             // n = inner width; rows [0, n) are the gate, rows [n, 2n) the up projection
-            return launch_one<MT, 2, kGemvSwiGlu, (UNROLL > 2 ? 2 : UNROLL) * (WARPS == 8 ? 2 : 1), WARPS>(
+            // (9 to 16 rows: half the loads in flight per warp, or the registers allow one block per SM only)
+            return launch_one<MT, 2, kGemvSwiGlu, (UNROLL > 2 ? 2 : UNROLL) * (WARPS == 8 && MT == 1 ? 2 : 1), WARPS>(
                 x, ldx, w, ldw, y, ldy, m, n, k, n, conv, norm, stream);
         case kGemvConv:
             // n = channels; rows [0, n) are B, [n, 2n) C, [2n, 3n) X
