@@ -248,7 +248,9 @@ def program_timeline(loaded, batch: int, prompt_tokens: int, seed: int) -> dict:
             "stages": program.layout.stages, "stage_bytes": program.layout.stage_bytes, "by_operation": table}
 
 
-def time_prefill(loaded, tokens: int, repeats: int, seed: int):
+def time_prefill(loaded, tokens: int, repeats: int, seed: int, chunk: int = 0):
+    """One prompt of ``tokens`` tokens, as one step or (``chunk`` > 0) in portions of that many tokens, each
+    portion attending to the cache the earlier ones left; the best of ``repeats`` runs."""
     import torch
     from celeg_b200.engine.step import StepEntry
     step_fn = loaded.step
@@ -257,11 +259,14 @@ def time_prefill(loaded, tokens: int, repeats: int, seed: int):
     best = None
     for i in range(repeats + 2):
         prompt = torch.randint(0, vocab, (tokens,), generator=generator).tolist()
-        entries = [StepEntry(f"prefill{i}", prompt, [tokens - 1])]
+        size = chunk if chunk > 0 else tokens
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        step_fn.run(entries, auto_begin=True)
+        for at in range(0, tokens, size):
+            portion = prompt[at:at + size]
+            want = [len(portion) - 1] if at + size >= tokens else []
+            step_fn.run([StepEntry(f"prefill{i}", portion, want)], auto_begin=True)
         stop.record()
         torch.cuda.synchronize()
         step_fn.end(f"prefill{i}")
@@ -314,28 +319,36 @@ def run_ours(args) -> dict:
     from celeg_b200.sampling import Sampler
     batch = 8
     raw = model_config(args.layers)
-    folder = model_folder(raw)
     peak, peak_source = peaks()
     max_batch = 64
-    options = EngineOptions(max_active_requests=max_batch, max_batched_tokens=PREFILL_TOKENS,
-                            prefill_chunk_tokens=PREFILL_TOKENS, page_tokens=args.page_tokens,
-                            logical_kv_pages=max_batch * CONTEXT // args.page_tokens)
-    engine = Engine(folder, max_context=CONTEXT, dtype="bfloat16", device="cuda:0", options=options,
+    context, prompt_tokens, step_tokens = CONTEXT, PROMPT_TOKENS, PREFILL_TOKENS
+    if args.phase != "all":             # other context lengths and prompt sizes, for one phase at a time
+        context = max(args.context, args.prompt_tokens + args.steps + args.warmup + 8, args.prefill_tokens)
+        prompt_tokens = args.prompt_tokens
+        step_tokens = max(PREFILL_TOKENS, args.chunk or args.prefill_tokens)
+        max_batch = max(1, args.batch)
+        raw["max_position_embeddings"] = max(raw["max_position_embeddings"], context)
+    folder = model_folder(raw)
+    options = EngineOptions(max_active_requests=max_batch, max_batched_tokens=step_tokens,
+                            prefill_chunk_tokens=step_tokens, page_tokens=args.page_tokens,
+                            logical_kv_pages=max_batch * (-(-context // args.page_tokens)))
+    engine = Engine(folder, max_context=context, dtype="bfloat16", device="cuda:0", options=options,
                     use_cuda_graph=not args.no_cuda_graph)
     loaded = engine.loaded
     sampler = Sampler(raw["vocab_size"], max_batch, max_batch, engine.device)
 
     if args.phase == "decode":          # a short run of one phase, for profilers
-        ms, launches, context = time_decode(loaded, sampler, args.batch, args.steps, args.warmup, PROMPT_TOKENS, 1)
-        return {"phase": "decode", "batch": args.batch, "ms_per_step": round(ms, 4),
+        ms, launches, context = time_decode(loaded, sampler, args.batch, args.steps, args.warmup, prompt_tokens, 1)
+        return {"phase": "decode", "batch": args.batch, "context_tokens": context, "ms_per_step": round(ms, 4),
                 "tokens_per_s": round(args.batch * 1e3 / ms, 1), "gpu_launches": launches,
                 "hbm_frac": round(decode_bytes(raw, args.batch, context) / (ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
     if args.phase == "program":
         os.environ["CELEG_B200_DECODE_PROGRAM"] = "1"
-        return program_timeline(loaded, min(args.batch, 16), PROMPT_TOKENS, 1)
+        return program_timeline(loaded, min(args.batch, 16), prompt_tokens, 1)
     if args.phase == "prefill":
-        prefill_ms = time_prefill(loaded, args.prefill_tokens, max(1, args.steps), 2)
-        return {"phase": "prefill", "tokens": args.prefill_tokens, "ms": round(prefill_ms, 3),
+        prefill_ms = time_prefill(loaded, args.prefill_tokens, max(1, min(args.steps, 5)), 2, args.chunk)
+        return {"phase": "prefill", "tokens": args.prefill_tokens, "chunk": args.chunk or args.prefill_tokens,
+                "ms": round(prefill_ms, 3),
                 "tokens_per_s": round(args.prefill_tokens * 1e3 / prefill_ms, 1),
                 "frac": round(prefill_flops(raw, args.prefill_tokens) / (prefill_ms * 1e-3)
                               / (peak["bf16_tflops"] * 1e12), 4)}
@@ -407,6 +420,10 @@ def main() -> int:
     parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "program"],
                         help="run one phase only and print a short record (for profilers)")
     parser.add_argument("--batch", type=int, default=8, help="batch of --phase decode")
+    parser.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS, help="prompt length of --phase decode")
+    parser.add_argument("--context", type=int, default=CONTEXT, help="longest request of a --phase run")
+    parser.add_argument("--chunk", type=int, default=0,
+                        help="--phase prefill: the prompt in portions of this many tokens (0: one step)")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of --phase prefill")
     args = parser.parse_args()
     if args.gpus != 1:
