@@ -198,8 +198,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
                 for (int kk = 0; kk < kFaN / kUmmaK; ++kk) {
                     // P: 32 bytes per 16 keys inside its rows; V: 16 keys further = 16 rows of 128 bytes = 2 KiB
-                    umma_bf16(tmem_base + (unsigned)(2 * kFaN + (i & 1) * kFaD), desc_p + 2 * kk,
-                              desc_v + (unsigned long long)(kk * 128), idesc_o, kk > 0 ? 1u : 0u);
+                    umma_bf16(tmem_base + (unsigned)(2 * kFaN), desc_p + 2 * kk, desc_v + (unsigned long long)(kk * 128),
+                              idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&kv_empty[s]));
                 umma_commit(smem_u32(&o_full[i & 1]));
@@ -211,32 +211,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16);
             const int qpos = pos0 + row;
             const bool live = row < rows;
-            float o[kFaD];
-#pragma unroll
-            for (int cidx = 0; cidx < kFaD; ++cidx) o[cidx] = 0.0f;
-            float run_max = -INFINITY, run_sum = 0.0f;
-            float pending_correction = 1.0f;                // of the block whose O' has not been added yet
+            // The row's statistics. `used_max` is the maximum that P and the sum are relative to; it follows
+            // the true running maximum only when that has grown by more than kFaSlack (in units of log2), so
+            // that O, which accumulates in tensor memory, is rescaled rarely: exponentials stay below
+            // 2^kFaSlack, which float32 sums and bfloat16 products hold without loss.
+            constexpr float kFaSlack = 8.0f;
+            float used_max = -INFINITY, run_sum = 0.0f;
             bool ok = true;
             const int blocks = block_end - block_begin;
-            // adds O' of block i (relative to that block's maximum) into the row
-            auto add_output = [&](int i, float correction) -> bool {
-                bool done = mbar_wait(smem_u32(&o_full[i & 1]), (i >> 1) & 1);
-                done = __all_sync(0xffffffffu, done);
-                if (!done) return false;
-                tcgen05_fence_after();
-                unsigned lo[32], hi[32];
-                tmem_load_32_issue(lane_base + (unsigned)(2 * kFaN + (i & 1) * kFaD), lo);
-                tmem_load_32_issue(lane_base + (unsigned)(2 * kFaN + (i & 1) * kFaD + 32), hi);
-                tmem_load_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    o[j] = o[j] * correction + __uint_as_float(lo[j]);
-                    o[32 + j] = o[32 + j] * correction + __uint_as_float(hi[j]);
-                }
-                tcgen05_fence_before();
-                return true;
-            };
+            const unsigned o_taddr = lane_base + (unsigned)(2 * kFaN);
+            const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
             for (int i = 0; i < blocks; ++i) {
+                // (S of block i complete also means: P V of block i-2 is complete, its P buffer is free)
                 ok = ok && mbar_wait(smem_u32(&s_full[i & 1]), (i >> 1) & 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -264,21 +250,53 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
                     for (int j = 0; j < kFaN; ++j) sc[j] = (j <= hi && j >= lo) ? sc[j] : -INFINITY;
                 }
-                // eight independent chains instead of one of 63 dependent steps (a thread has no neighbour to
-                // hide latency behind: its warp is alone on its scheduler half of the time)
-                float part_max[8];
+                // four independent chains of three-input maxima
+                float part_max[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) part_max[j] = sc[j];
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    float m = max3_f32(sc[16 * c4], sc[16 * c4 + 1], sc[16 * c4 + 2]);
 #pragma unroll
-                for (int j = 8; j < kFaN; ++j) part_max[j & 7] = fmaxf(part_max[j & 7], sc[j]);
-                float block_max = fmaxf(fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])),
-                                        fmaxf(fmaxf(part_max[4], part_max[5]), fmaxf(part_max[6], part_max[7])));
-                block_max *= p.scale_log2;                 // the scale is positive: the maximum commutes with it
-                const float new_max = fmaxf(run_max, block_max);
-                const float correction = new_max == -INFINITY ? 1.0f : exp2f(run_max - new_max);
-                const float safe_max = new_max == -INFINITY ? 0.0f : new_max;
-                run_max = new_max;
-                float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    for (int j = 3; j < 15; j += 2) m = max3_f32(m, sc[16 * c4 + j], sc[16 * c4 + j + 1]);
+                    part_max[c4] = fmaxf(m, sc[16 * c4 + 15]);
+                }
+                // (the scale is positive: the maximum commutes with it)
+                const float block_max = fmaxf(max3_f32(part_max[0], part_max[1], part_max[2]), part_max[3]) * p.scale_log2;
+                if (i == 0) {
+                    used_max = block_max;
+                } else {
+                    const float new_max = fmaxf(used_max, block_max);
+                    const bool grown = new_max > used_max + kFaSlack;          // (-inf + slack = -inf)
+                    if (__any_sync(0xffffffffu, grown)) {
+                        // O holds the sum up to block i-1 relative to used_max: wait for it, rescale the rows
+                        // that grew (the warp's other rows by 1), put it back before P of this block is published
+                        ok = mbar_wait(smem_u32(&o_full[(i - 1) & 1]), ((i - 1) >> 1) & 1);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                        const float factor = !grown ? 1.0f : (used_max == -INFINITY ? 0.0f : exp2f(used_max - new_max));
+                        const unsigned long long factor2 = pack_f32x2(factor, factor);
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            unsigned part[32];
+                            tmem_load_32_issue(o_taddr + (unsigned)(half * 32), part);
+                            tmem_load_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) {
+                                float a, b;
+                                unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(part[j]), __uint_as_float(part[j + 1])), factor2), a, b);
+                                part[j] = __float_as_uint(a);
+                                part[j + 1] = __float_as_uint(b);
+                            }
+                            tmem_store_32(o_taddr + (unsigned)(half * 32), part);
+                        }
+                        tmem_store_wait();
+                        run_sum *= factor;
+                        if (grown) used_max = new_max;
+                    }
+                }
+                const float safe_max = used_max == -INFINITY ? 0.0f : used_max;
+                const unsigned long long neg_max2 = pack_f32x2(-safe_max, -safe_max);
+                unsigned long long part_sum[4] = {0ull, 0ull, 0ull, 0ull};          // (0.0f, 0.0f) each
                 unsigned char* p_row = p_ptr + (i & 1) * kFaPBytes + row * 128;
 #pragma unroll
                 for (int q8 = 0; q8 < kFaN / 8; ++q8) {
@@ -286,27 +304,46 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
                     for (int e2 = 0; e2 < 4; ++e2) {
-                        float a, b;
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(fmaf(sc[q8 * 8 + 2 * e2], p.scale_log2, -safe_max)));
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(fmaf(sc[q8 * 8 + 2 * e2 + 1], p.scale_log2, -safe_max)));
-                        part_sum[e2] += a + b;
+                        float x0, x1, a, b;
+                        unpack_f32x2(fma_f32x2(pack_f32x2(sc[q8 * 8 + 2 * e2], sc[q8 * 8 + 2 * e2 + 1]), scale2, neg_max2), x0, x1);
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(x0));
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(x1));
+                        part_sum[e2] = add_f32x2(part_sum[e2], pack_f32x2(a, b));
                         h2[e2] = __floats2bfloat162_rn(a, b);
                     }
                     // 16-byte chunk q8 of this row; chunk index XOR (row % 8): the 128-byte swizzle
                     *reinterpret_cast<uint4*>(p_row + ((q8 ^ (row & 7)) << 4)) = packed;
                 }
-                run_sum = run_sum * correction + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
+                {
+                    float s0, s1;
+                    unpack_f32x2(add_f32x2(add_f32x2(part_sum[0], part_sum[1]), add_f32x2(part_sum[2], part_sum[3])), s0, s1);
+                    run_sum += s0 + s1;
+                }
                 tcgen05_fence_before();
                 fence_async_shared();                       // the MMA reads P through the async proxy
                 mbar_arrive_one(smem_u32(&p_full[i & 1]));
-                // O' of the block before, which was multiplied meanwhile
-                if (i > 0) {
-                    ok = add_output(i - 1, pending_correction);
-                    if (!ok) break;
-                }
-                pending_correction = correction;
             }
-            if (ok && blocks > 0) ok = add_output(blocks - 1, pending_correction);
+            // the output: O of the last block complete, divided by the denominator
+            float o[kFaD];
+            if (ok && blocks > 0) {
+                ok = mbar_wait(smem_u32(&o_full[(blocks - 1) & 1]), ((blocks - 1) >> 1) & 1);
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok) {
+                    tcgen05_fence_after();
+                    unsigned lo[32], hi[32];
+                    tmem_load_32_issue(o_taddr, lo);
+                    tmem_load_32_issue(o_taddr + 32u, hi);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        o[j] = __uint_as_float(lo[j]);
+                        o[32 + j] = __uint_as_float(hi[j]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < kFaD; ++j) o[j] = 0.0f;
+            }
             if (!ok) {
                 if (lane == 0) atomicExch(p.error_flag, 65);
             } else if (live) {
