@@ -36,10 +36,12 @@ constexpr int kFaN = 64;                  // keys per block
 constexpr int kFaD = 64;
 constexpr unsigned kFaQBytes = kFaM * kFaD * 2;         // 16 KiB
 constexpr unsigned kFaKvBytes = kFaN * kFaD * 2;        // 8 KiB each for K and V
-constexpr unsigned kFaPBytes = kFaM * kFaN * 2;         // 16 KiB: rows of 64 keys = 128 bytes
-constexpr int kFaStages = 3;
-constexpr unsigned kFaSmemBytes = kFaQBytes + kFaStages * 2 * kFaKvBytes + 2 * kFaPBytes + 1024;
-constexpr unsigned kFaTmemColumns = 256;  // S of even and odd blocks: columns 0..63, 64..127; O': 128..191, 192..255
+constexpr int kFaStages = 4;
+constexpr unsigned kFaSmemBytes = kFaQBytes + kFaStages * 2 * kFaKvBytes + 1024;
+// Tensor memory: S of even and odd blocks at columns 0..63 and 64..127, O at 128..191, P (bfloat16, two keys a
+// column) of even and odd blocks at 192..223 and 224..255
+constexpr unsigned kFaTmemColumns = 256;
+constexpr unsigned kFaOColumn = 2 * kFaN, kFaPColumn = 2 * kFaN + kFaD;
 
 struct FaParams {
     __nv_bfloat16* out;            // [tokens, q_heads * 64]
@@ -111,8 +113,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const unsigned smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const unsigned q_addr = smem_base;
     const unsigned kv_addr = q_addr + kFaQBytes;                       // stage s: K at +s*2*kv, V behind it
-    const unsigned p_addr = kv_addr + kFaStages * 2 * kFaKvBytes;
-    unsigned char* p_ptr = smem_raw + (p_addr - smem_u32(smem_raw));
 
     int error = 0;
     if (span >= 0) {
@@ -194,12 +194,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 tcgen05_fence_after();
                 const int s = i % kFaStages;
                 const unsigned long long desc_v = smem_descriptor(kv_addr + s * 2 * kFaKvBytes + kFaKvBytes);
-                const unsigned long long desc_p = smem_descriptor(p_addr + (i & 1) * kFaPBytes);
 #pragma unroll
                 for (int kk = 0; kk < kFaN / kUmmaK; ++kk) {
-                    // P: 32 bytes per 16 keys inside its rows; V: 16 keys further = 16 rows of 128 bytes = 2 KiB
-                    umma_bf16(tmem_base + (unsigned)(2 * kFaN), desc_p + 2 * kk, desc_v + (unsigned long long)(kk * 128),
-                              idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                    // P: 16 keys = 8 columns of tensor memory; V: 16 keys further = 16 rows of 128 bytes = 2 KiB
+                    umma_bf16_a_tmem(tmem_base + kFaOColumn, tmem_base + kFaPColumn + (unsigned)((i & 1) * (kFaN / 2) + kk * 8),
+                                     desc_v + (unsigned long long)(kk * 128), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&kv_empty[s]));
                 umma_commit(smem_u32(&o_full[i & 1]));
@@ -219,7 +218,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             float used_max = -INFINITY, run_sum = 0.0f;
             bool ok = true;
             const int blocks = block_end - block_begin;
-            const unsigned o_taddr = lane_base + (unsigned)(2 * kFaN);
+            const unsigned o_taddr = lane_base + kFaOColumn;
             const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
             for (int i = 0; i < blocks; ++i) {
                 // (S of block i complete also means: P V of block i-2 is complete, its P buffer is free)
@@ -297,30 +296,25 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 const float safe_max = used_max == -INFINITY ? 0.0f : used_max;
                 const unsigned long long neg_max2 = pack_f32x2(-safe_max, -safe_max);
                 unsigned long long part_sum[4] = {0ull, 0ull, 0ull, 0ull};          // (0.0f, 0.0f) each
-                unsigned char* p_row = p_ptr + (i & 1) * kFaPBytes + row * 128;
+                unsigned p_packed[kFaN / 2];
 #pragma unroll
-                for (int q8 = 0; q8 < kFaN / 8; ++q8) {
-                    uint4 packed;
-                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-                    for (int e2 = 0; e2 < 4; ++e2) {
-                        float x0, x1, a, b;
-                        unpack_f32x2(fma_f32x2(pack_f32x2(sc[q8 * 8 + 2 * e2], sc[q8 * 8 + 2 * e2 + 1]), scale2, neg_max2), x0, x1);
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(x0));
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(x1));
-                        part_sum[e2] = add_f32x2(part_sum[e2], pack_f32x2(a, b));
-                        h2[e2] = __floats2bfloat162_rn(a, b);
-                    }
-                    // 16-byte chunk q8 of this row; chunk index XOR (row % 8): the 128-byte swizzle
-                    *reinterpret_cast<uint4*>(p_row + ((q8 ^ (row & 7)) << 4)) = packed;
+                for (int j2 = 0; j2 < kFaN / 2; ++j2) {
+                    float x0, x1, a, b;
+                    unpack_f32x2(fma_f32x2(pack_f32x2(sc[2 * j2], sc[2 * j2 + 1]), scale2, neg_max2), x0, x1);
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(x0));
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(x1));
+                    part_sum[j2 & 3] = add_f32x2(part_sum[j2 & 3], pack_f32x2(a, b));
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);          // key 2 j2 in the lower half
+                    p_packed[j2] = *reinterpret_cast<const unsigned*>(&pair);
                 }
+                tmem_store_32(lane_base + kFaPColumn + (unsigned)((i & 1) * (kFaN / 2)), p_packed);
+                tmem_store_wait();
                 {
                     float s0, s1;
                     unpack_f32x2(add_f32x2(add_f32x2(part_sum[0], part_sum[1]), add_f32x2(part_sum[2], part_sum[3])), s0, s1);
                     run_sum += s0 + s1;
                 }
                 tcgen05_fence_before();
-                fence_async_shared();                       // the MMA reads P through the async proxy
                 mbar_arrive_one(smem_u32(&p_full[i & 1]));
             }
             // the output: O of the last block complete, divided by the denominator

@@ -79,6 +79,17 @@ __device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long de
         : "memory");
 }
 
+// The same with the A operand in tensor memory: row m of A is lane m, its K elements lie in consecutive
+// 32-bit columns from tmem_a on, two bfloat16 per column (the lower index in the lower half).
+__device__ __forceinline__ void umma_bf16_a_tmem(unsigned tmem_d, unsigned tmem_a, unsigned long long desc_b,
+                                                 unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(
+            tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
