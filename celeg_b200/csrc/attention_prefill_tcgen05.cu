@@ -127,37 +127,53 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int block_begin = first_key / kFaN;
         const int block_end = pos_last / kFaN + 1;
 
-        if (warp == 0 && lane == 0) {
+        if (warp == 0) {
             // ------------------------------------------------------------------ producer
+            // Lane 0 waits for the stage; then lane 2 pg brings page pg of K and lane 2 pg + 1 that of V: one
+            // thread issuing the up to 16 copies of a block one after the other took longer than the softmax
+            // of a block. Every lane looks its page up one block ahead.
             const int* table = p.block_table + (size_t)span * p.table_stride;
-            mbar_expect_tx(smem_u32(&q_full), kFaQBytes);
-            tma_load_2d(q_addr, &map_q, smem_u32(&q_full), h * kFaD, t0);
-            const int pages_per_block = kFaN / p.page_tokens;
+            if (lane == 0) {
+                mbar_expect_tx(smem_u32(&q_full), kFaQBytes);
+                tma_load_2d(q_addr, &map_q, smem_u32(&q_full), h * kFaD, t0);
+            }
+            const int pages_per_block = kFaN / p.page_tokens;          // 1 to 8
             const unsigned page_bytes = (unsigned)p.page_tokens * kFaD * 2;
-            for (int kb = block_begin; kb < block_end && !error; ++kb) {
+            const int pg = lane >> 1;
+            const bool copies = pg < pages_per_block;
+            const CUtensorMap* map = (lane & 1) ? &map_v : &map_k;
+            auto lookup = [&](int kb) -> int {
+                const int key0 = kb * kFaN + pg * p.page_tokens;
+                // (keys nobody may see: any page of finite numbers will do)
+                if (copies && kb < block_end && key0 <= pos_last && key0 + p.page_tokens > first_key)
+                    return table[key0 / p.page_tokens];
+                return 0;
+            };
+            int page_next = lookup(block_begin);
+            for (int kb = block_begin; kb < block_end; ++kb) {
                 const int i = kb - block_begin;
                 const int s = i % kFaStages;
-                if (i >= kFaStages && !mbar_wait_suspended(smem_u32(&kv_empty[s]), ((i / kFaStages) - 1) & 1)) {
-                    error = 61;
+                int page = page_next;
+                page_next = lookup(kb + 1);
+                const unsigned bar = smem_u32(&kv_full[s]);
+                int ok = 1;
+                if (lane == 0) {
+                    if (i >= kFaStages && !mbar_wait_suspended(smem_u32(&kv_empty[s]), ((i / kFaStages) - 1) & 1)) ok = 0;
+                    if (ok) mbar_expect_tx(bar, 2 * kFaKvBytes);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    error = lane == 0 ? 61 : 0;
                     break;
                 }
-                const unsigned bar = smem_u32(&kv_full[s]);
-                mbar_expect_tx(bar, 2 * kFaKvBytes);
-                const unsigned k_dst = kv_addr + s * 2 * kFaKvBytes;
-                const unsigned v_dst = k_dst + kFaKvBytes;
-                for (int pg = 0; pg < pages_per_block; ++pg) {
-                    const int key0 = kb * kFaN + pg * p.page_tokens;
-                    int page = 0;                     // keys nobody may see: any page of finite numbers will do
-                    if (key0 <= pos_last && key0 + p.page_tokens > first_key) {
-                        page = table[key0 / p.page_tokens];
-                        if (page < 0) {               // the host never builds such a table
-                            atomicExch(p.error_flag, 2);
-                            page = 0;
-                        }
+                if (copies) {
+                    if (page < 0) {                       // the host never builds such a table
+                        atomicExch(p.error_flag, 2);
+                        page = 0;
                     }
                     const int row = (page * p.kv_heads + kvh) * p.page_tokens;
-                    tma_load_2d(k_dst + pg * page_bytes, &map_k, bar, 0, row);
-                    tma_load_2d(v_dst + pg * page_bytes, &map_v, bar, 0, row);
+                    const unsigned dst = kv_addr + s * 2 * kFaKvBytes + ((lane & 1) ? kFaKvBytes : 0u) + pg * page_bytes;
+                    tma_load_2d(dst, map, bar, 0, row);
                 }
             }
         } else if (warp == 1 && lane == 0) {
