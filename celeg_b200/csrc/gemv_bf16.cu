@@ -86,12 +86,20 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsig
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The weights that the next product of the step will stream (a hint; may be empty). Each block asks the L2 for
+// its slice of them when its own loads are done: a step of a model is a chain of short kernels, and between
+// two of them (the last blocks draining, the launch, the first loads) the memory would otherwise stand idle.
+struct GemvPrefetch {
+    const char* ptr;
+    long long bytes;      // a multiple of 16
+};
+
 // MT: 8-row tiles of activations (M <= 8*MT). WT: 16-row tiles of W per block (1, or 2 for SwiGLU).
 template <int MT, int WT, int MODE, int kGemvUnroll, int kGemvWarps>
 __global__ void __launch_bounds__(kGemvWarps * 32)
 gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
                  void* __restrict__ y, int ldy, int m, int n, int k, int second_tile_offset, GemvConvArgs conv,
-                 GemvNormArgs norm) {
+                 GemvNormArgs norm, GemvPrefetch ahead) {
     constexpr int kGemvThreads = kGemvWarps * 32;
     extern __shared__ __align__(16) float partial_raw[];
     __shared__ float row_scale[16];
@@ -192,6 +200,19 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
                     total += __ldcg(norm.sumsq_in + (size_t)r * norm.sumsq_in_stride + i);
                 total = warp_sum(total);
                 if (lane == 0) row_scale[r] = 1.0f / sqrtf(total / (float)norm.width + norm.eps);
+            }
+        }
+    }
+    if (ahead.bytes > 0 && threadIdx.x == 0) {
+        // the blocks that run last ask for it: what they ask for is on its way while the grid drains
+        const int askers = min((int)gridDim.x, 148);
+        const int rank = (int)blockIdx.x - ((int)gridDim.x - askers);
+        if (rank >= 0) {
+            const long long slice = ((ahead.bytes + askers - 1) / askers + 127) & ~127LL;
+            const long long begin = (long long)rank * slice;
+            if (begin < ahead.bytes) {
+                const unsigned size = (unsigned)min(slice, ahead.bytes - begin);
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(ahead.ptr + begin), "r"(size) : "memory");
             }
         }
     }
@@ -296,6 +317,9 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
     }
 }
 
+static GemvPrefetch g_gemv_ahead = {nullptr, 0};      // the caller's hint for the next product (taken at its entry)
+static GemvPrefetch g_gemv_launch_ahead = {nullptr, 0};   // the hint of the product being launched
+
 template <int MT, int WT, int MODE, int UNROLL, int WARPS>
 static int launch_one(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw, void* y, int ldy, int m,
                       int n, int k, int tile_offset, const GemvConvArgs& conv, const GemvNormArgs& norm,
@@ -309,8 +333,10 @@ static int launch_one(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, i
             return -2;
         }
     }
+    const GemvPrefetch ahead = g_gemv_launch_ahead;
+    g_gemv_launch_ahead = {nullptr, 0};
     launch_chained_class(kChainGemv, kernel, (n + 15) / 16, WARPS * 32, smem, stream, x, ldx, w, ldw, y, ldy, m, n, k,
-                         tile_offset, conv, norm);
+                         tile_offset, conv, norm, ahead);
     return check_launch("gemv_bf16");
 }
 
@@ -345,6 +371,16 @@ using namespace celeg_b200;
 
 CELEG_API void celeg_gemv_set_warps(int warps) { g_gemv_warps = warps; }
 
+// A hint for the next celeg_gemv_bf16* launch only: `bytes` of device memory at `ptr` (the weights that the
+// product after it will read) are asked into the L2 by that launch's blocks. The memory must stay
+// allocated as long as the launch, or a CUDA graph that captured it, may run.
+CELEG_API int celeg_gemv_prefetch_next(const void* ptr, long long bytes) {
+    CELEG_REQUIRE(bytes >= 0 && (((size_t)ptr) & 15) == 0, "gemv_bf16: a prefetch of %lld bytes at an address that is "
+                  "not 16-byte aligned", bytes);
+    g_gemv_ahead = {(const char*)ptr, ptr ? (bytes & ~15LL) : 0};
+    return 0;
+}
+
 // mode 0: y bf16 [m, n] = x w^T; 1: y float32; 2: y float32 += x w^T; 3: w is [2n, k] (gate rows then up
 // rows), y bf16 [m, n] = silu(x gate^T) * (x up^T); 4: w is [3n, k] (B, C, X rows of the short convolution),
 // y bf16 [m, n] = C * conv(B*X) over the carried state, which is shifted (needs the conv arguments; row i
@@ -352,6 +388,9 @@ CELEG_API void celeg_gemv_set_warps(int warps) { g_gemv_warps = warps; }
 static int gemv_checked(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int m, int n, int k, int mode,
                         const float* conv_w, int taps, float* state, long long slot_stride, const int* span_slot,
                         const GemvNormArgs& norm, cudaStream_t stream) {
+    const GemvPrefetch ahead = g_gemv_ahead;          // a hint never outlives the call it was given for
+    g_gemv_ahead = {nullptr, 0};
+    g_gemv_launch_ahead = {nullptr, 0};
     CELEG_REQUIRE(m >= 0 && n > 0 && k > 0, "gemv_bf16: invalid sizes m=%d n=%d k=%d", m, n, k);
     CELEG_REQUIRE(m <= 16, "gemv_bf16: %d activation rows exceed 16; use the library product", m);
     CELEG_REQUIRE(k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
@@ -364,6 +403,7 @@ static int gemv_checked(const void* x, int ldx, const void* w, int ldw, void* y,
                       "gemv_bf16: the convolution epilogue needs kernel, state and slots (taps=%d, at most %d)", taps,
                       kGemvMaxConvTaps);
     if (m == 0) return 0;
+    g_gemv_launch_ahead = ahead;
     const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
     GemvConvArgs conv = {conv_w, taps, state, slot_stride, span_slot};

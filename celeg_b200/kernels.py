@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -62,6 +62,7 @@ _SIGNATURES = {
                                         c_float, c_void_p, c_void_p],
     "celeg_gemv_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_longlong, c_void_p, c_void_p],
+    "celeg_gemv_prefetch_next": [c_void_p, c_longlong],
     "celeg_gemv_bf16_split_norm": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                    c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
                                    c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
@@ -317,7 +318,8 @@ def gemv_supported(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
 def gemv_bf16(x, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_STORE, *,
               conv_w: Optional[torch.Tensor] = None, taps: int = 0, state: Optional[torch.Tensor] = None,
               slot_stride: int = 0, span_slot: Optional[torch.Tensor] = None,
-              prepare: Optional[SplitNorm] = None, next_weight: Optional[torch.Tensor] = None) -> None:
+              prepare: Optional[SplitNorm] = None, next_weight: Optional[torch.Tensor] = None,
+              ahead: Optional[Tuple[int, int]] = None) -> None:
     """y[:rows] = x[:rows] @ w.T for at most 16 rows, streaming w once. mode GEMV_STORE: y bfloat16;
     GEMV_STORE_F32: y float32; GEMV_ADD_RESIDUAL: y float32, accumulated; GEMV_SWIGLU: w is
     [2*inner, k] (gate rows, then up rows) and y bfloat16 [rows, inner] = silu(gate) * up; GEMV_CONV: w is
@@ -326,7 +328,12 @@ def gemv_bf16(x, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_S
     single token of request i, whose state slot is span_slot[i].
     ``x`` may be a :class:`SplitNorm` (the operand still lacks its row scale; applied to the sums here).
     With ``prepare`` (GEMV_ADD_RESIDUAL only): the first half of the norm that follows, weight
-    ``next_weight``, is written too: ``prepare.xw`` and this product's pieces of the sums of squares."""
+    ``next_weight``, is written too: ``prepare.xw`` and this product's pieces of the sums of squares.
+    ``ahead`` = (device address, bytes) of the weights that the step's next product will read: this launch
+    asks them into the L2 (the memory must outlive every graph that captures the launch)."""
+    if ahead is not None and ahead[1] > 0:
+        if library().celeg_gemv_prefetch_next(ctypes.c_void_p(ahead[0]), ahead[1]) != 0:      # (no launch)
+            raise KernelLibraryError(library().celeg_last_error().decode("utf-8", "replace"))
     blocks = {GEMV_SWIGLU: 2, GEMV_CONV: 3}.get(mode, 1)
     n = w.shape[0] // blocks
     k = w.shape[1]

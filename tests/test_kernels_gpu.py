@@ -511,6 +511,49 @@ def test_gemv_bf16_modes(m, n, k):
         close(act, gate / (1 + np.exp(-gate)) * up, torch.bfloat16, scale=2.0)
 
 
+@pytest.mark.parametrize("m,n,k,ahead_bytes", [(8, 2048, 256, 1 << 20), (3, 70, 136, 4096 + 48), (16, 4800, 64, 200),
+                                               (1, 16, 8, 16)])
+def test_gemv_bf16_with_a_prefetch_hint(m, n, k, ahead_bytes):
+    """A product that asks the next product's weights into the L2 gives the same bits as one that does not,
+    whatever the size of the hint (more blocks than askers, fewer, bytes that are no multiple of a slice);
+    the hint holds for one call."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(12)
+    x_dev = dev(rounded(rng.normal(size=(m, k)), torch.bfloat16), torch.bfloat16)
+    w_dev = dev(rounded(rng.normal(size=(n, k)) * 0.1, torch.bfloat16), torch.bfloat16)
+    later = torch.zeros(ahead_bytes + 64, dtype=torch.uint8, device="cuda")
+    plain = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    hinted = torch.zeros_like(plain)
+    kernels.gemv_bf16(x_dev, w_dev, plain, m, kernels.GEMV_STORE)
+    before = kernels.LAUNCHES
+    kernels.gemv_bf16(x_dev, w_dev, hinted, m, kernels.GEMV_STORE, ahead=(later.data_ptr(), ahead_bytes))
+    assert kernels.LAUNCHES == before + 1                  # the hint is no launch
+    torch.cuda.synchronize()
+    assert torch.equal(plain, hinted)
+    again = torch.zeros_like(plain)
+    kernels.gemv_bf16(x_dev, w_dev, again, m, kernels.GEMV_STORE)      # no hint left over
+    torch.cuda.synchronize()
+    assert torch.equal(plain, again)
+    with pytest.raises(kernels.KernelLibraryError):
+        kernels.gemv_bf16(x_dev, w_dev, again, m, kernels.GEMV_STORE, ahead=(later.data_ptr() + 4, 64))
+
+
+def test_runtime_learns_the_order_of_streamed_weights():
+    """The successor of a weight is what was streamed after it the last time; the hint is capped."""
+    from celeg_b200.parts.runtime import Runtime
+    rt = Runtime(torch.device("cuda:0"), torch.bfloat16, 16, max_requests=4, max_context=64)
+    rt.prefetch_bytes = 1024
+    a = torch.zeros((64, 64), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((8, 64), dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda")
+    assert rt._ahead(a) is None and rt._ahead(b) is None and rt._ahead(c) is None
+    assert rt._ahead(a) == (b.data_ptr(), 1024)            # second round: a was followed by b, ...
+    assert rt._ahead(b) == (c.data_ptr(), 1024)
+    assert rt._ahead(c) == (a.data_ptr(), 1024)            # ... and the last one by the first of the next step
+    rt.prefetch_bytes = 0
+    assert rt._ahead(a) is None
+
+
 @pytest.mark.parametrize("m,width,inner", [(1, 64, 192), (8, 2048, 1024), (5, 80, 136), (16, 96, 256), (3, 40, 72)])
 def test_split_norm_over_two_products(m, width, inner):
     """residual += x w_down^T; y = rmsnorm(residual) w_next^T, with the norm split over the two products
