@@ -54,7 +54,10 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // a predecessor wrote and before it writes anything a predecessor may still read (only constant
 // data such as weights may be touched earlier). chain_release() lets the successor start
 // launching; the successor's chain_wait() still returns only when this whole grid has finished
-// and its writes are visible, so releasing early is always safe.
+// and its writes are visible, so releasing early is always safe. It is not always faster: the
+// small-batch product releases nothing before its blocks exit (released at its start, or after its main
+// loop, a decode step of 74 kernels measured 0.75-0.90 ms instead of 0.70; with the attribute alone it is
+// 2 % faster than without).
 __device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;"); }
 

@@ -134,7 +134,6 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
             for (int e = 0; e < 4; ++e) acc[t][j][e] = 0.0f;
 
     const int slices = k / 32;                       // full 32-element slices; the tail is handled below
-    chain_release();
     bool waited = false;
     for (int s0 = warp; s0 < slices; s0 += kGemvWarps * kGemvUnroll) {
         uint4 a_lo[kGemvUnroll][WT], a_hi[kGemvUnroll][WT];
