@@ -23,8 +23,15 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-// Polls until the phase with the given parity has completed; false after kMaxPolls polls.
+// Polls until the phase with the given parity has completed; false after kMaxPolls polls or two seconds,
+// whichever comes first (a try may itself block for a while, so polls alone bound nothing).
+__device__ __forceinline__ unsigned long long global_nanoseconds() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    unsigned long long started = 0;
     for (unsigned poll = 0; poll < kMaxPolls; ++poll) {
         unsigned done;
         asm volatile(
@@ -33,6 +40,11 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
             : "r"(bar), "r"(parity)
             : "memory");
         if (done) return true;
+        if ((poll & 255u) == 255u) {
+            const unsigned long long now = global_nanoseconds();
+            if (started == 0) started = now;
+            if (now - started > 2000000000ull) return false;
+        }
     }
     return false;
 }
