@@ -116,6 +116,42 @@ def test_long_decoding(models, dtype, tol):
     engine.end("long")
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-4), ("bfloat16", 8e-2)])
+def test_a_context_of_thousands_of_tokens(tmp_path, dtype, tol):
+    """2,700 prompt tokens in portions of 1,000 (query tiles with more than forty blocks of keys behind them:
+    every ring and barrier of the attention kernels wraps many times), then tokens decoded one by one with the
+    keys split over many blocks that are merged, beside a short request that needs one block only."""
+    from celeg_b200 import Engine, EngineOptions, StepEntry
+    from celeg_b200.weights import write_random_model
+    from tiny_models import TINY_D
+    raw = copy.deepcopy(TINY_D)
+    raw["max_position_embeddings"] = 4096
+    folder = str(tmp_path / "long_context")
+    write_random_model(folder, raw, 3, torch.bfloat16)
+    config, weights = plain_lfm2.load_model_folder(folder)
+    long_seq, short_seq = prompts_of(config["vocab_size"], [2712, 40], seed=29)
+    want_long = plain_lfm2.forward(config, weights, long_seq)
+    want_short = plain_lfm2.forward(config, weights, short_seq)
+    engine = Engine(folder, dtype=dtype, max_context=4096, use_cuda_graph=True,
+                    options=EngineOptions(max_batched_tokens=1024, prefill_chunk_tokens=1024))
+    at = 0
+    for size in (1000, 1000, 700):
+        last = at + size == 2700
+        out = engine.forward([StepEntry("long", long_seq[at:at + size], [size - 1] if last else [])])
+        at += size
+    got = [out[0].cpu().numpy()]
+    engine.forward([StepEntry("short", short_seq[:28], [])])
+    for step in range(12):
+        out = engine.forward([StepEntry("long", [long_seq[2700 + step]], [0]),
+                              StepEntry("short", [short_seq[28 + step]], [0])])
+        got.append(out[0].cpu().numpy())
+        assert np.abs(out[1].cpu().numpy() - want_short[28 + step]).max() < tol, f"short request, step {step}"
+    err = np.abs(np.stack(got) - want_long[2699:2712])
+    assert err.max() < tol, f"worst at step {int(err.max(axis=1).argmax())}: {err.max():.3e}"
+    engine.end("long")
+    engine.end("short")
+
+
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 6e-2)])
 def test_first_tokens_of_a_sequence(models, dtype, tol):
     """Positions 0..5 one by one: fewer tokens than the conv kernel has taps, one key only."""
