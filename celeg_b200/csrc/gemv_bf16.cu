@@ -316,8 +316,8 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
     }
 }
 
-static GemvPrefetch g_gemv_ahead = {nullptr, 0};      // the caller's hint for the next product (taken at its entry)
-static GemvPrefetch g_gemv_launch_ahead = {nullptr, 0};   // the hint of the product being launched
+static thread_local GemvPrefetch g_gemv_ahead = {nullptr, 0};      // the caller's hint for the next product (taken at its entry)
+static thread_local GemvPrefetch g_gemv_launch_ahead = {nullptr, 0};   // the hint of the product being launched
 
 template <int MT, int WT, int MODE, int UNROLL, int WARPS>
 static int launch_one(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw, void* y, int ldy, int m,
