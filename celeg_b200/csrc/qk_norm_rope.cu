@@ -36,7 +36,7 @@ qk_norm_rope_tokens_kernel(A* qkv, A* k_cache, A* v_cache, const QkNormRopeArgs 
 #pragma unroll
     for (int j = 0; j < PAIRS; ++j) sincosf((float)pos * a.inv_freq[lane + 32 * j], &sn[j], &cs[j]);
     long long cache_row = -1;                       // offset of (page, kv head 0, slot in page), in elements
-    if (a.store_kv && h_end > a.q_heads) {
+    if (a.store_kv == 1 && h_end > a.q_heads) {
         const int page = a.block_table[(size_t)a.token_span[t] * a.table_stride + pos / a.page_tokens];
         if (page < 0) {                             // the host never builds such a table
             if (lane == 0) atomicExch(a.error_flag, 1);
@@ -49,7 +49,9 @@ qk_norm_rope_tokens_kernel(A* qkv, A* k_cache, A* v_cache, const QkNormRopeArgs 
         const bool is_q = h < a.q_heads;
         const bool is_k = !is_q && h < a.q_heads + a.kv_heads;
         A* dst = vec;
-        if (!is_q) {
+        if (!is_q && a.store_kv == 2) {
+            if (!is_k) continue;                    // k in place, v untouched
+        } else if (!is_q) {
             if (cache_row < 0) continue;
             const int kvh = is_k ? h - a.q_heads : h - a.q_heads - a.kv_heads;
             dst = (is_k ? k_cache : v_cache) + cache_row + (size_t)kvh * a.page_tokens * kHead;
@@ -110,6 +112,8 @@ CELEG_API int celeg_qk_norm_rope_store(void* qkv, const float* q_weight, const f
     CELEG_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
                   "qk_norm_rope_store: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
     CELEG_REQUIRE(eps > 0.0f || (!q_weight && !k_weight), "qk_norm_rope_store: eps must be positive");
+    CELEG_REQUIRE(store_kv >= 0 && store_kv <= 2, "qk_norm_rope_store: store_kv is 0 (q only), 1 (k and v to the cache) "
+                  "or 2 (k in place), not %d", store_kv);
     if (tokens == 0) return 0;
     const long long units = (long long)tokens * (q_heads + 2 * kv_heads);
     const int warps = 4;

@@ -39,7 +39,8 @@ struct QkNormRopeArgs {
     long long page_stride;
     int tokens, q_heads, kv_heads, head_dim, rotary_dim, page_tokens;
     float eps;
-    int store_kv;
+    int store_kv;      // 0: q heads only; 1: k (normalised, rotated) and v go to the cache; 2: k heads are
+                       // normalised and rotated in place like q heads, v heads and the cache are left alone
     int* error_flag;
 };
 
@@ -71,6 +72,9 @@ __device__ __forceinline__ void qk_norm_rope_unit(A* qkv, A* k_cache, A* v_cache
     A* dst = vec;
     if (!is_q) {
         if (!store_kv) return;
+        if (store_kv == 2 && !is_k) return;          // k heads in place (below), v heads untouched
+    }
+    if (!is_q && store_kv != 2) {
         const int logical = pos / page_tokens;
         const int page = block_table[(size_t)token_span[t] * table_stride + logical];
         if (page < 0) {                              // the host never builds such a table

@@ -206,8 +206,10 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_we
                        inv_freq: Optional[torch.Tensor], positions: torch.Tensor, token_span: torch.Tensor,
                        block_table: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
                        tokens: int, q_heads: int, kv_heads: int, head_dim: int, rotary_dim: int, page_tokens: int,
-                       eps: float, store_kv: bool, error_flag: torch.Tensor) -> None:
-    """k_cache / v_cache: one layer's pages, [pages, kv_heads, page_tokens, head_dim]."""
+                       eps: float, store_kv, error_flag: torch.Tensor) -> None:
+    """k_cache / v_cache: one layer's pages, [pages, kv_heads, page_tokens, head_dim]. ``store_kv``: False/0 = q
+    heads only; True/1 = k (normalised, rotated) and v are written to the cache; 2 = k heads are normalised and
+    rotated in place like the q heads, v heads and the cache are left alone."""
     page_stride = k_cache.stride(0) if k_cache is not None else 0
     _check(library().celeg_qk_norm_rope_store(
         _ptr(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), _ptr(positions), _ptr(token_span),

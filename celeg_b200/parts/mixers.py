@@ -129,7 +129,7 @@ class AttentionMixer:
             # unfused: normalise in place, let the position part rewrite q and k, then store
             kernels.qk_norm_rope_store(self.qkv, self.q_norm, self.k_norm, None, step.positions, step.token_span,
                                        table, b.k, b.v, t, self.heads, self.stored_kv_heads, self.head_dim, 0,
-                                       b.page_tokens, self.eps, False, step.error_flag)
+                                       b.page_tokens, self.eps, 2 if self.stored_kv_heads else 0, step.error_flag)
             rows = self.qkv[:t]
             q_width = self.heads * self.head_dim
             kv_width = self.stored_kv_heads * self.head_dim

@@ -418,6 +418,158 @@ def test_toy_mixer_with_its_own_state_is_registered_built_and_stepped(tmp_path):
     assert np.abs(logits[0] - want[0][4]).max() < 3e-4
 
 
+def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path):
+    """Two more parts from outside the package, put into a model description without a change to the
+    framework's files: a feed-forward that routes every token to one of three small experts (router logits
+    and the gate in float32), and a position encoding that rotates neighbouring pairs (2i, 2i+1) instead of
+    halves, which has no tables for the fused q/k kernel and so goes through ``apply``. Run in portions and
+    token by token through the engine's loader, cache and step function, against a plain computation."""
+    from celeg_b200.config import (Architecture, Lfm2Config, PartSpec, TensorRef, build_lfm2_spec,
+                                   register_architecture)
+    from celeg_b200.config.lfm2_arch import lfm2_random_init
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    from celeg_b200.parts import register_part
+    from celeg_b200.weights import write_random_model
+
+    experts, inner = 3, 40
+
+    @register_part("feed_forward", "toy_routed", replace=True)
+    class ToyRouted:
+        def __init__(self, params, weights, parts, rt):
+            self.rt = rt
+            self.router = rt.vector(weights["router"])                    # float32 [experts, hidden]
+            self.up = [rt.matrix(weights[f"up{e}"]) for e in range(params["experts"])]
+            self.down = [rt.matrix(weights[f"down{e}"]) for e in range(params["experts"])]
+            self.hidden_act = rt.scratch("toy.routed.act", params["inner"])
+            self.expert_out = rt.scratch("toy.routed.out", params["hidden_size"])
+
+        def forward(self, x, out, step):
+            t = step.tokens
+            logits = x[:t].float() @ self.router.t()
+            gate = torch.softmax(logits, dim=-1)
+            chosen = logits.argmax(dim=-1)
+            out[:t] = 0
+            for e in range(len(self.up)):                                 # every expert over all rows, then masked:
+                self.rt.linear(x, self.up[e], self.hidden_act, t)         # a toy part is free to be slow
+                self.hidden_act[:t] = torch.relu(self.hidden_act[:t])
+                self.rt.linear(self.hidden_act, self.down[e], self.expert_out, t)
+                weight = torch.where(chosen == e, gate[:, e], torch.zeros_like(gate[:, e]))
+                out[:t] += (self.expert_out[:t].float() * weight[:, None]).to(out.dtype)
+
+    @register_part("position", "toy_rope_pairs", replace=True)
+    class ToyPairRope:
+        def __init__(self, params, rt):
+            half = params["head_dim"] // 2
+            self.inv_freq = (params["theta"] ** (-torch.arange(half, dtype=torch.float64) / half)).to(
+                torch.float32).to(rt.device)
+
+        def fused(self):
+            return None                                                   # no tables: the mixer calls apply()
+
+        def apply(self, q, k, positions, tokens):
+            angle = positions[:tokens].float()[:, None] * self.inv_freq[None, :]
+            cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+            for view in (q, k):
+                even, odd = view[..., 0::2].float().clone(), view[..., 1::2].float().clone()
+                view[..., 0::2] = (even * cos - odd * sin).to(view.dtype)
+                view[..., 1::2] = (odd * cos + even * sin).to(view.dtype)
+
+    def toy_spec(config):
+        spec = build_lfm2_spec(config)
+        layers = list(spec.layers)
+        hidden = config.hidden_size
+        tensors = {"router": TensorRef("model.layers.0.toy_ff.router.weight", (experts, hidden))}
+        for e in range(experts):
+            tensors[f"up{e}"] = TensorRef(f"model.layers.0.toy_ff.experts.{e}.up.weight", (inner, hidden))
+            tensors[f"down{e}"] = TensorRef(f"model.layers.0.toy_ff.experts.{e}.down.weight", (hidden, inner))
+        layers[0] = dataclasses.replace(layers[0], feed_forward=PartSpec(
+            kind="toy_routed", params={"hidden_size": hidden, "experts": experts, "inner": inner}, tensors=tensors))
+        attention = layers[2].mixer
+        position = PartSpec(kind="toy_rope_pairs", params={"theta": 300.0, "head_dim": config.head_dim})
+        layers[2] = dataclasses.replace(layers[2], mixer=dataclasses.replace(attention, parts={"position": position}))
+        return dataclasses.replace(spec, layers=tuple(layers), architecture="toy_routed_lfm2")
+
+    register_architecture(Architecture(
+        name="toy_routed_lfm2", parse_config=Lfm2Config.from_dict,
+        resolve_config=lambda config, shapes: dataclasses.replace(
+            config, tie_word_embeddings=True if config.tie_word_embeddings is None else config.tie_word_embeddings),
+        build_spec=toy_spec, random_init=lfm2_random_init), replace=True)
+
+    raw = copy.deepcopy(TINY_A)
+    raw["model_type"] = "toy_routed_lfm2"
+    folder = write_random_model(str(tmp_path / "toy_routed"), raw, 9, torch.float32)
+    loaded = load_model(folder, dtype="float32", max_requests=2, cache_tokens=128, max_batched_tokens=64)
+    config, weights = plain_lfm2.load_model_folder(folder)
+    head_dim = config["hidden_size"] // config["num_attention_heads"]
+
+    def pair_rope(x, positions):
+        half = head_dim // 2
+        inv_freq = (300.0 ** (-np.arange(half) / half)).astype(np.float32).astype(np.float64)
+        angle = positions[:, None] * inv_freq[None, :]
+        cos, sin = np.cos(angle)[:, None, :], np.sin(angle)[:, None, :]
+        out = np.empty_like(x)
+        out[..., 0::2] = x[..., 0::2] * cos - x[..., 1::2] * sin
+        out[..., 1::2] = x[..., 1::2] * cos + x[..., 0::2] * sin
+        return out
+
+    def plain_forward(tokens):
+        count = len(tokens)
+        x = weights["model.embed_tokens.weight"][np.asarray(tokens)]
+        for index, kind in enumerate(config["layer_types"]):
+            p = f"model.layers.{index}."
+            if index == 0:
+                n = plain_lfm2.rmsnorm(x, weights[p + "operator_norm.weight"], config["norm_eps"])
+                h = x + plain_lfm2.short_conv_mixer(n, weights[p + "conv.in_proj.weight"], weights[p + "conv.conv.weight"],
+                                                    weights[p + "conv.out_proj.weight"])
+                n2 = plain_lfm2.rmsnorm(h, weights[p + "ffn_norm.weight"], config["norm_eps"])
+                logits = n2 @ weights[p + "toy_ff.router.weight"].T
+                gate = np.exp(logits - logits.max(axis=-1, keepdims=True))
+                gate /= gate.sum(axis=-1, keepdims=True)
+                routed = np.zeros_like(h)
+                for t in range(count):
+                    e = int(logits[t].argmax())
+                    act = np.maximum(n2[t] @ weights[p + f"toy_ff.experts.{e}.up.weight"].T, 0.0)
+                    routed[t] = gate[t, e] * (act @ weights[p + f"toy_ff.experts.{e}.down.weight"].T)
+                x = h + routed
+            elif index == 2:
+                heads, kv_heads = config["num_attention_heads"], config["num_key_value_heads"]
+                n = plain_lfm2.rmsnorm(x, weights[p + "operator_norm.weight"], config["norm_eps"])
+                q = (n @ weights[p + "self_attn.q_proj.weight"].T).reshape(count, heads, head_dim)
+                k = (n @ weights[p + "self_attn.k_proj.weight"].T).reshape(count, kv_heads, head_dim)
+                v = (n @ weights[p + "self_attn.v_proj.weight"].T).reshape(count, kv_heads, head_dim)
+                positions = np.arange(count, dtype=np.float64)
+                q = pair_rope(plain_lfm2.rmsnorm(q, weights[p + "self_attn.q_layernorm.weight"], config["norm_eps"]), positions)
+                k = pair_rope(plain_lfm2.rmsnorm(k, weights[p + "self_attn.k_layernorm.weight"], config["norm_eps"]), positions)
+                mixed = np.zeros((count, heads, head_dim))
+                for head in range(heads):
+                    kv = head // (heads // kv_heads)
+                    scores = (q[:, head] @ k[:, kv].T) / np.sqrt(head_dim)
+                    scores = np.where(np.arange(count)[None, :] > np.arange(count)[:, None], -np.inf, scores)
+                    scores = np.exp(scores - scores.max(axis=-1, keepdims=True))
+                    mixed[:, head] = (scores / scores.sum(axis=-1, keepdims=True)) @ v[:, kv]
+                h = x + mixed.reshape(count, -1) @ weights[p + "self_attn.out_proj.weight"].T
+                n2 = plain_lfm2.rmsnorm(h, weights[p + "ffn_norm.weight"], config["norm_eps"])
+                x = h + plain_lfm2.swiglu(n2, weights[p + "feed_forward.w1.weight"], weights[p + "feed_forward.w3.weight"],
+                                          weights[p + "feed_forward.w2.weight"])
+            else:
+                x = plain_lfm2.block(x, index, kind, config, weights)
+        z = plain_lfm2.rmsnorm(x, weights["model.embedding_norm.weight"], config["norm_eps"])
+        return z @ weights["model.embed_tokens.weight"].T
+
+    (sequence,) = prompts_of(config["vocab_size"], [34], seed=33)
+    want = plain_forward(sequence)
+    step = loaded.step
+    at = 0
+    for size in (9, 2, 12, 1, 1, 7, 1, 1):
+        logits = step.run([StepEntry("toy", sequence[at:at + size], list(range(size)))], auto_begin=True).cpu().numpy()
+        worst = np.abs(logits - want[at:at + size]).max(axis=1)
+        assert worst.max() < 3e-4, f"tokens {at}..{at + size}: {np.round(worst, 5).tolist()}"
+        at += size
+    assert at == len(sequence)
+    step.raise_on_device_error()
+
+
 def test_cli_generates_and_dumps_logits(models, tmp_path, capsys):
     from celeg_b200.cli import main
     folder, config, weights = models["A"]

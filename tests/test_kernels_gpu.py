@@ -276,6 +276,42 @@ def test_qk_norm_rope_store(dtype, heads, kv_heads, head_dim, page_tokens, theta
         close(v_cache[page, :, inside], v[t], dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens,with_rotation", [(5, False), (70, True), (3, True)])
+def test_qk_norm_rope_in_place_for_a_position_part_of_its_own(dtype, tokens, with_rotation):
+    """store_kv = 2: the k heads are normalised (and rotated, if tables are given) in place like the q heads;
+    v heads and the cache stay as they are. The step before a position encoding that has no tables."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(16)
+    heads, kv_heads, head_dim, eps, theta = 6, 2, 64, 1e-5, 20000.0
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = rounded(rng.normal(size=(tokens, width)), dtype)
+    q_w = (1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32).astype(np.float64)
+    k_w = (1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32).astype(np.float64)
+    positions = np.arange(11, 11 + tokens)
+    inv_freq = (theta ** (-2.0 * np.arange(head_dim // 2) / head_dim)).astype(np.float32)
+    cache = torch.full((4, kv_heads, 16, head_dim), 7.0, dtype=dtype, device="cuda")
+    table = torch.zeros((1, 8), dtype=torch.int32, device="cuda")
+    qkv_dev = dev(qkv, dtype)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kernels.qk_norm_rope_store(qkv_dev, dev(q_w, torch.float32), dev(k_w, torch.float32),
+                               dev(inv_freq) if with_rotation else None, dev(positions.astype(np.int32)),
+                               torch.zeros(tokens, dtype=torch.int32, device="cuda"), table, cache, cache, tokens,
+                               heads, kv_heads, head_dim, head_dim if with_rotation else 0, 16, eps, 2, flag)
+    assert int(flag.item()) == 0
+    q = qkv[:, :heads * head_dim].reshape(tokens, heads, head_dim)
+    k = qkv[:, heads * head_dim:(heads + kv_heads) * head_dim].reshape(tokens, kv_heads, head_dim)
+    q_want, k_want = plain_lfm2.rmsnorm(q, q_w, eps), plain_lfm2.rmsnorm(k, k_w, eps)
+    if with_rotation:
+        q_want = plain_lfm2.rope_split_half(q_want, positions, theta)
+        k_want = plain_lfm2.rope_split_half(k_want, positions, theta)
+    close(qkv_dev[:, :heads * head_dim], q_want.reshape(tokens, -1), dtype, scale=3.0)
+    close(qkv_dev[:, heads * head_dim:(heads + kv_heads) * head_dim], k_want.reshape(tokens, -1), dtype, scale=3.0)
+    assert torch.equal(qkv_dev[:, (heads + kv_heads) * head_dim:].cpu(),
+                       torch.tensor(qkv[:, (heads + kv_heads) * head_dim:]).to(dtype))
+    assert float((cache.float() - 7.0).abs().max()) == 0.0
+
+
 def test_sampling_greedy_and_seeded():
     from celeg_b200 import kernels
     rng = np.random.default_rng(7)
