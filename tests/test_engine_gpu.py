@@ -708,6 +708,101 @@ def test_run_order_names_a_layer_twice_and_shares_a_cache(tmp_path):
         at += n
 
 
+@pytest.mark.parametrize("name,dtype,tol", [("B", "float32", 4e-4), ("D", "float32", 4e-4), ("D", "bfloat16", 8e-2)])
+def test_a_layer_with_a_window_has_pages_of_its_own_and_gives_them_back(tmp_path, name, dtype, tol):
+    """One attention layer of the model sees the last 24 keys only. Its pages form a group of their own beside
+    the layers that see all keys; pages the window has passed go back to the pool and are used again (the
+    group's pool is far smaller than the sequence). A long and a short request, in portions and token by
+    token, against the plain implementation with the same window."""
+    from celeg_b200.config import Architecture, Lfm2Config, build_lfm2_spec, register_architecture
+    from celeg_b200.config.lfm2_arch import lfm2_random_init
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    from celeg_b200.weights import write_random_model
+
+    window = 24
+    raw, seed = copy.deepcopy(CONFIGS[name][0]), CONFIGS[name][1]
+    kinds = raw["layer_types"]
+    windowed = max(i for i, kind in enumerate(kinds) if kind == "full_attention")
+
+    def spec_with_window(config):
+        spec = build_lfm2_spec(config)
+        layers = list(spec.layers)
+        mixer = layers[windowed].mixer
+        layers[windowed] = dataclasses.replace(layers[windowed], mixer=dataclasses.replace(
+            mixer, params={**mixer.params, "window": window}))
+        return dataclasses.replace(spec, layers=tuple(layers), architecture="lfm2_windowed")
+
+    register_architecture(Architecture(name="lfm2_windowed", parse_config=Lfm2Config.from_dict,
+                                       resolve_config=lambda c, shapes: c.resolved_with(shapes),
+                                       build_spec=spec_with_window, random_init=lfm2_random_init), replace=True)
+    raw["model_type"] = "lfm2_windowed"
+    folder = write_random_model(str(tmp_path / "windowed"), raw, seed, torch.bfloat16)
+    loaded = load_model(folder, dtype=dtype, max_requests=2, cache_tokens=208, page_tokens=8, max_batched_tokens=64,
+                        use_graphs=True)
+    groups = loaded.model.group_members
+    assert sorted(len(m) for m in groups) == sorted([1, sum(k == "full_attention" for k in kinds) - 1])
+    config, w = plain_lfm2.load_model_folder(folder)
+    heads, kv_heads = config["num_attention_heads"], config["num_key_value_heads"]
+    head_dim = config.get("head_dim") or config["hidden_size"] // heads
+    eps = config["norm_eps"]
+
+    def plain_forward(tokens):
+        x = w["model.embed_tokens.weight"][np.asarray(tokens)]
+        for index, kind in enumerate(kinds):
+            if index != windowed:
+                x = plain_lfm2.block(x, index, kind, config, w)
+                continue
+            p = f"model.layers.{index}."
+            n = plain_lfm2.rmsnorm(x, w[p + "operator_norm.weight"], eps)
+            h = x + plain_lfm2.attention_mixer(
+                n, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.k_proj.weight"], w[p + "self_attn.v_proj.weight"],
+                w[p + "self_attn.out_proj.weight"], w[p + "self_attn.q_layernorm.weight"],
+                w[p + "self_attn.k_layernorm.weight"], heads, kv_heads, head_dim, config["rope_theta"], eps,
+                window=window)
+            n2 = plain_lfm2.rmsnorm(h, w[p + "ffn_norm.weight"], eps)
+            x = h + plain_lfm2.swiglu(n2, w[p + "feed_forward.w1.weight"], w[p + "feed_forward.w3.weight"],
+                                      w[p + "feed_forward.w2.weight"])
+        z = plain_lfm2.rmsnorm(x, w["model.embedding_norm.weight"], eps)
+        head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
+        return z @ head.T
+
+    long_seq, short_seq = prompts_of(config["vocab_size"], [170, 30], seed=44)
+    want = {"long": plain_forward(long_seq), "short": plain_forward(short_seq)}
+    seqs = {"long": long_seq, "short": short_seq}
+    step = loaded.step
+    heads_at = {"long": 0, "short": 0}
+
+    def run(portions):
+        entries = [StepEntry(n, seqs[n][heads_at[n]:heads_at[n] + size], list(range(size))) for n, size in portions]
+        logits = step.run(entries, auto_begin=True).float().cpu().numpy()
+        row = 0
+        for n, size in portions:
+            ref = want[n][heads_at[n]:heads_at[n] + size]
+            worst = np.abs(logits[row:row + size] - ref).max()
+            assert worst < tol, f"request {n}, tokens {heads_at[n]}..{heads_at[n] + size}: {worst:.3e}"
+            row += size
+            heads_at[n] += size
+
+    run([("long", 40)])
+    run([("long", 33), ("short", 9)])
+    run([("long", 2), ("short", 21)])
+    for _ in range(60):                          # decoded one by one; the short request ends on the way
+        portions = [("long", 1)]
+        if heads_at["short"] < len(short_seq):
+            portions.append(("short", 1))
+        run(portions)
+        if heads_at["short"] == len(short_seq) and "short" in loaded.manager.live_requests():
+            step.end("short")
+    run([("long", 35)])
+    assert heads_at["long"] == 170
+    step.raise_on_device_error()
+    loaded.manager.check_invariants()
+    # the windowed group holds only what the window still needs: far fewer pages than the 170 tokens
+    held = [len(loaded.manager.get("long").held_pages(g)) for g in range(len(groups))]
+    assert min(held) <= (window + 8 - 1) // 8 + 2 and max(held) >= 170 // 8, held
+
+
 def test_decoding_twenty_requests_on_the_streaming_product(models, monkeypatch):
     """CELEG_B200_TC_PRODUCTS=stream: steps of 17 to 128 rows run the weight-streaming tcgen05 product
     with its fused epilogues (SwiGLU, short convolution); greedy tokens against the plain model."""
