@@ -803,6 +803,149 @@ def test_a_layer_with_a_window_has_pages_of_its_own_and_gives_them_back(tmp_path
     assert min(held) <= (window + 8 - 1) // 8 + 2 and max(held) >= 170 // 8, held
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 4e-4), ("bfloat16", 8e-2)])
+def test_toy_norm_and_toy_arrangement(tmp_path, dtype, tol):
+    """A norm that is no RMSNorm (mean-centred, with a bias) and a block arrangement that is not pre-norm
+    residual (mixer and feed-forward side by side: y = x + Mixer(N1(x)) + FeedForward(N2(x))), both defined
+    here and registered. The norm cannot be split over the products around it and the arrangement names no
+    first norm, so on the bfloat16 path their neighbours fall back to the unsplit form; decoded tokens (few
+    rows) and prompt portions, against a plain computation."""
+    from celeg_b200.config import Architecture, Lfm2Config, PartSpec, TensorRef, build_lfm2_spec, register_architecture
+    from celeg_b200.config.lfm2_arch import lfm2_random_init
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    from celeg_b200.parts import register_part
+    from celeg_b200.weights import write_random_model
+
+    toy_eps = 1e-4
+
+    @register_part("norm", "toy_centred", replace=True)
+    class ToyCentredNorm:
+        def __init__(self, params, weights, rt):
+            self.width = int(params["width"])
+            self.weight = rt.vector(weights["weight"])
+            self.bias = rt.vector(weights["bias"])
+
+        def add_norm(self, residual, delta, out, n_rows, rows=None):
+            if rows is None:
+                if delta is not None:
+                    residual[:n_rows] += delta[:n_rows].float()
+                x = residual[:n_rows]
+            else:
+                index = rows[:n_rows].long()
+                x = residual[index] + (delta[index].float() if delta is not None else 0.0)
+            x = x - x.mean(dim=-1, keepdim=True)
+            y = x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + toy_eps) * self.weight + self.bias
+            out[:n_rows] = y.to(out.dtype)
+
+    @register_part("arrangement", "toy_side_by_side", replace=True)
+    class ToySideBySide:
+        def __init__(self, layer_parts, rt):
+            self.parts = layer_parts
+            hidden = layer_parts["mixer_norm"].width
+            self.normed_a = rt.scratch("toy.side.normed_a", hidden)
+            self.normed_b = rt.scratch("toy.side.normed_b", hidden)
+            self.delta_a = rt.scratch("toy.side.delta_a", hidden)
+            self.delta_b = rt.scratch("toy.side.delta_b", hidden)
+
+        def run(self, stream, step):
+            t = step.tokens
+            xa = stream.normed(self.parts["mixer_norm"], self.normed_a, t)     # adds what was pending
+            xb = stream.normed(self.parts["feed_forward_norm"], self.normed_b, t)
+            stream.expect(self.delta_a, None, t)
+            self.parts["mixer"].forward(xa, self.delta_a, step)
+            self.parts["feed_forward"].forward(xb, self.delta_b, step)
+            self.delta_a[:t] = (self.delta_a[:t].float() + self.delta_b[:t].float()).to(self.delta_a.dtype)
+            stream.add_later(self.delta_a)
+
+    def toy_spec(config):
+        spec = build_lfm2_spec(config)
+        layers = list(spec.layers)
+        hidden = config.hidden_size
+
+        def centred(name):
+            return PartSpec(kind="toy_centred", params={"width": hidden},
+                            tensors={"weight": TensorRef(name + ".weight", (hidden,)),
+                                     "bias": TensorRef(name + ".bias", (hidden,))})
+
+        layers[1] = dataclasses.replace(layers[1], mixer_norm=centred("model.layers.1.toy_norm"))
+        layers[2] = dataclasses.replace(layers[2], feed_forward_norm=centred("model.layers.2.toy_ffn_norm"))
+        layers[3] = dataclasses.replace(layers[3], arrangement="toy_side_by_side")
+        return dataclasses.replace(spec, layers=tuple(layers), final_norm=centred("model.toy_final_norm"),
+                                   architecture="toy_norms_lfm2")
+
+    def init(config, name, shape):
+        if name.endswith(".bias"):
+            return "linear"
+        return "norm" if "toy_" in name and name.endswith(".weight") else lfm2_random_init(config, name, shape)
+
+    register_architecture(Architecture(
+        name="toy_norms_lfm2", parse_config=Lfm2Config.from_dict,
+        resolve_config=lambda config, shapes: dataclasses.replace(
+            config, tie_word_embeddings=True if config.tie_word_embeddings is None else config.tie_word_embeddings),
+        build_spec=toy_spec, random_init=init), replace=True)
+    raw = copy.deepcopy(TINY_A)
+    raw["model_type"] = "toy_norms_lfm2"
+    folder = write_random_model(str(tmp_path / "toy_norms"), raw, 11, torch.bfloat16)
+    loaded = load_model(folder, dtype=dtype, max_requests=3, cache_tokens=192, max_batched_tokens=64, use_graphs=True)
+    config, w = plain_lfm2.load_model_folder(folder)
+    eps = config["norm_eps"]
+
+    def centred_norm(x, name):
+        x = x - x.mean(axis=-1, keepdims=True)
+        return x / np.sqrt((x * x).mean(axis=-1, keepdims=True) + toy_eps) * w[name + ".weight"] + w[name + ".bias"]
+
+    def conv_of(index, n):
+        p = f"model.layers.{index}."
+        return plain_lfm2.short_conv_mixer(n, w[p + "conv.in_proj.weight"], w[p + "conv.conv.weight"], w[p + "conv.out_proj.weight"])
+
+    def ffn_of(index, n):
+        p = f"model.layers.{index}."
+        return plain_lfm2.swiglu(n, w[p + "feed_forward.w1.weight"], w[p + "feed_forward.w3.weight"], w[p + "feed_forward.w2.weight"])
+
+    def plain_forward(tokens):
+        x = w["model.embed_tokens.weight"][np.asarray(tokens)]
+        x = plain_lfm2.block(x, 0, "conv", config, w)
+        h = x + conv_of(1, centred_norm(x, "model.layers.1.toy_norm"))
+        x = h + ffn_of(1, plain_lfm2.rmsnorm(h, w["model.layers.1.ffn_norm.weight"], eps))
+        p = "model.layers.2."
+        n = plain_lfm2.rmsnorm(x, w[p + "operator_norm.weight"], eps)
+        h = x + plain_lfm2.attention_mixer(
+            n, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.k_proj.weight"], w[p + "self_attn.v_proj.weight"],
+            w[p + "self_attn.out_proj.weight"], w[p + "self_attn.q_layernorm.weight"], w[p + "self_attn.k_layernorm.weight"],
+            config["num_attention_heads"], config["num_key_value_heads"], 16, config["rope_theta"], eps)
+        x = h + ffn_of(2, centred_norm(h, "model.layers.2.toy_ffn_norm"))
+        x = (x + conv_of(3, plain_lfm2.rmsnorm(x, w["model.layers.3.operator_norm.weight"], eps))
+             + ffn_of(3, plain_lfm2.rmsnorm(x, w["model.layers.3.ffn_norm.weight"], eps)))
+        return centred_norm(x, "model.toy_final_norm") @ w["model.embed_tokens.weight"].T
+
+    sequences = prompts_of(config["vocab_size"], [40, 33, 26], seed=45)
+    want = [plain_forward(s) for s in sequences]
+    step = loaded.step
+    at = [0, 0, 0]
+
+    def run(sizes):
+        entries, rows = [], []
+        for i, size in enumerate(sizes):
+            if size:
+                entries.append(StepEntry(f"r{i}", sequences[i][at[i]:at[i] + size], list(range(size))))
+                rows.append((i, size))
+        logits = step.run(entries, auto_begin=True).float().cpu().numpy()
+        row = 0
+        for i, size in rows:
+            worst = np.abs(logits[row:row + size] - want[i][at[i]:at[i] + size]).max()
+            assert worst < tol, f"request {i}, tokens {at[i]}..{at[i] + size}: {worst:.3e}"
+            row += size
+            at[i] += size
+
+    run([12, 0, 5])
+    run([3, 20, 1])
+    for _ in range(10):                 # three rows a step: the small-batch path, captured in a graph
+        run([1, 1, 1])
+    run([15, 3, 10])
+    step.raise_on_device_error()
+
+
 def test_decoding_twenty_requests_on_the_streaming_product(models, monkeypatch):
     """CELEG_B200_TC_PRODUCTS=stream: steps of 17 to 128 rows run the weight-streaming tcgen05 product
     with its fused epilogues (SwiGLU, short convolution); greedy tokens against the plain model."""
