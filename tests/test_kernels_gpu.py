@@ -276,6 +276,48 @@ def test_qk_norm_rope_store(dtype, heads, kv_heads, head_dim, page_tokens, theta
         close(v_cache[page, :, inside], v[t], dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("head_dim,rotary,tokens", [(64, 32, 7), (64, 32, 80), (48, 20, 5), (128, 64, 66), (16, 2, 3)])
+def test_qk_norm_rope_over_a_part_of_the_head(dtype, head_dim, rotary, tokens):
+    """rotary_dim < head_dim: elements [0, rotary) rotate in pairs (i, i + rotary/2) with angles
+    position * theta^(-2i/rotary), the others are normalised and pass; k and v land in the cache."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(17)
+    heads, kv_heads, eps, theta, page_tokens = 3, 1, 1e-5, 10000.0, 16
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = rounded(rng.normal(size=(tokens, width)), dtype)
+    q_w = (1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32).astype(np.float64)
+    k_w = (1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32).astype(np.float64)
+    positions = np.arange(3, 3 + tokens)
+    pages = (3 + tokens + page_tokens - 1) // page_tokens
+    table = dev(np.arange(pages, dtype=np.int32)[::-1].copy().reshape(1, pages))
+    k_cache = torch.zeros((pages, kv_heads, page_tokens, head_dim), dtype=dtype, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    inv_freq = (theta ** (-2.0 * np.arange(rotary // 2) / rotary)).astype(np.float32)
+    qkv_dev = dev(qkv, dtype)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kernels.qk_norm_rope_store(qkv_dev, dev(q_w, torch.float32), dev(k_w, torch.float32), dev(inv_freq),
+                               dev(positions.astype(np.int32)), torch.zeros(tokens, dtype=torch.int32, device="cuda"),
+                               table, k_cache, v_cache, tokens, heads, kv_heads, head_dim, rotary, page_tokens, eps,
+                               True, flag)
+    assert int(flag.item()) == 0
+
+    def want_of(x, weight):
+        n = plain_lfm2.rmsnorm(x, weight, eps)
+        n[..., :rotary] = plain_lfm2.rope_split_half(n[..., :rotary].copy(), positions, theta)
+        return n
+
+    q = qkv[:, :heads * head_dim].reshape(tokens, heads, head_dim)
+    k = qkv[:, heads * head_dim:(heads + kv_heads) * head_dim].reshape(tokens, kv_heads, head_dim)
+    v = qkv[:, (heads + kv_heads) * head_dim:].reshape(tokens, kv_heads, head_dim)
+    close(qkv_dev[:, :heads * head_dim], want_of(q, q_w).reshape(tokens, -1), dtype, scale=3.0)
+    k_want = want_of(k, k_w)
+    for t in range(tokens):
+        page = pages - 1 - positions[t] // page_tokens
+        close(k_cache[page, :, positions[t] % page_tokens], k_want[t], dtype, scale=3.0)
+        close(v_cache[page, :, positions[t] % page_tokens], v[t], dtype)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("tokens,with_rotation", [(5, False), (70, True), (3, True)])
 def test_qk_norm_rope_in_place_for_a_position_part_of_its_own(dtype, tokens, with_rotation):
@@ -383,11 +425,13 @@ def test_attention_decode_split_keys(heads, kv_heads, head_dim, page_tokens, win
         close(out, want, dtype)
 
 
-@pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,window,chunk,normed", [
-    (4, 2, 16, 16, None, 64, True), (8, 2, 64, 16, None, 128, True), (6, 3, 80, 16, 37, 64, True),
-    (2, 1, 128, 32, None, 512, False), (5, 5, 48, 8, None, 64, True), (32, 8, 64, 16, None, 256, True),
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,window,chunk,normed,rotary", [
+    (4, 2, 16, 16, None, 64, True, 16), (8, 2, 64, 16, None, 128, True, 64), (6, 3, 80, 16, 37, 64, True, 80),
+    (2, 1, 128, 32, None, 512, False, 128), (5, 5, 48, 8, None, 64, True, 48), (32, 8, 64, 16, None, 256, True, 64),
+    # a rotation over the first elements of a head only; the rest is normalised and passes
+    (8, 2, 64, 16, None, 128, True, 32), (3, 1, 48, 16, None, 64, True, 20),
 ])
-def test_attention_decode_with_the_qk_step_inside(heads, kv_heads, head_dim, page_tokens, window, chunk, normed):
+def test_attention_decode_with_the_qk_step_inside(heads, kv_heads, head_dim, page_tokens, window, chunk, normed, rotary):
     """The decode kernel fed with the raw q|k|v projection (it normalises and rotates q and the token's own
     key, writes key and value into the cache, attends) against the separate kernels: same output, same cache."""
     from celeg_b200 import kernels
@@ -401,7 +445,7 @@ def test_attention_decode_with_the_qk_step_inside(heads, kv_heads, head_dim, pag
     qkv = dev(rounded(rng.normal(size=(tokens, width)), dtype), dtype)
     q_w = dev((1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32)) if normed else None
     k_w = dev((1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32)) if normed else None
-    inv_freq = dev((1e6 ** (-2.0 * np.arange(head_dim // 2) / head_dim)).astype(np.float32))
+    inv_freq = dev((1e6 ** (-2.0 * np.arange(rotary // 2) / rotary)).astype(np.float32))
     positions = dev(np.array([n - 1 for n in lengths], dtype=np.int32))
     token_span = dev(np.arange(tokens, dtype=np.int32))
     table_dev = dev(table)
@@ -414,7 +458,7 @@ def test_attention_decode_with_the_qk_step_inside(heads, kv_heads, head_dim, pag
     # separate kernels on copies
     qkv_a, k_a, v_a = qkv.clone(), k_cache.clone(), v_cache.clone()
     kernels.qk_norm_rope_store(qkv_a, q_w, k_w, inv_freq, positions, token_span, table_dev, k_a, v_a, tokens, heads,
-                               kv_heads, head_dim, head_dim, page_tokens, eps, True, flag)
+                               kv_heads, head_dim, rotary, page_tokens, eps, True, flag)
     out_a = torch.zeros((tokens, heads * head_dim), dtype=dtype, device="cuda")
     kernels.attention_decode(qkv_a, width, out_a, k_a, v_a, positions, token_span, table_dev, tokens, heads, kv_heads,
                              head_dim, page_tokens, window, scale, chunk, max_splits, partial_o, partial_ml, counters, flag)
@@ -424,7 +468,7 @@ def test_attention_decode_with_the_qk_step_inside(heads, kv_heads, head_dim, pag
         out_b = torch.zeros_like(out_a)
         kernels.attention_decode_fused(qkv.clone(), width, out_b, k_b, v_b, positions, token_span, table_dev, tokens,
                                        heads, kv_heads, head_dim, page_tokens, window, scale, chunk, max_splits,
-                                       partial_o, partial_ml, counters, flag, q_w, k_w, inv_freq, head_dim, eps)
+                                       partial_o, partial_ml, counters, flag, q_w, k_w, inv_freq, rotary, eps)
         assert int(flag.item()) == 0 and int(counters.abs().sum().item()) == 0
         assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
         assert torch.equal(out_a, out_b)
