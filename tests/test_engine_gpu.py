@@ -946,6 +946,63 @@ def test_toy_norm_and_toy_arrangement(tmp_path, dtype, tol):
     step.raise_on_device_error()
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 4e-4), ("bfloat16", 8e-2)])
+def test_scale_factors_of_a_model_description(tmp_path, dtype, tol):
+    """The factors a model description may carry and LFM2 leaves at one: on the embedding, on the logits, and
+    a softmax scale that is not 1/sqrt(head size). Prompt portions and decoded tokens against the plain
+    computation with the same factors."""
+    from celeg_b200.config import Architecture, Lfm2Config, build_lfm2_spec, register_architecture
+    from celeg_b200.config.lfm2_arch import lfm2_random_init
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    from celeg_b200.weights import write_random_model
+
+    on_embedding, on_logits, softmax_scale = 3.0, 0.25, 0.4
+
+    def scaled_spec(config):
+        spec = build_lfm2_spec(config)
+        layers = list(spec.layers)
+        mixer = layers[2].mixer
+        layers[2] = dataclasses.replace(layers[2], mixer=dataclasses.replace(
+            mixer, params={**mixer.params, "softmax_scale": softmax_scale}))
+        return dataclasses.replace(spec, layers=tuple(layers), embedding_multiplier=on_embedding,
+                                   logits_multiplier=on_logits, architecture="lfm2_scaled")
+
+    register_architecture(Architecture(name="lfm2_scaled", parse_config=Lfm2Config.from_dict,
+                                       resolve_config=lambda c, shapes: c.resolved_with(shapes),
+                                       build_spec=scaled_spec, random_init=lfm2_random_init), replace=True)
+    raw = copy.deepcopy(TINY_A)
+    raw["model_type"] = "lfm2_scaled"
+    folder = write_random_model(str(tmp_path / "scaled"), raw, 13, torch.bfloat16)
+    loaded = load_model(folder, dtype=dtype, max_requests=2, cache_tokens=128, max_batched_tokens=64, use_graphs=True)
+    config, w = plain_lfm2.load_model_folder(folder)
+    w = dict(w)
+    # q . k * s = (q * s * sqrt(d)) . k / sqrt(d), and q is linear in its norm weight
+    w["model.layers.2.self_attn.q_layernorm.weight"] = w["model.layers.2.self_attn.q_layernorm.weight"] * softmax_scale * 4.0
+
+    def plain_forward(tokens):
+        x = w["model.embed_tokens.weight"][np.asarray(tokens)] * on_embedding
+        for index, kind in enumerate(config["layer_types"]):
+            x = plain_lfm2.block(x, index, kind, config, w)
+        z = plain_lfm2.rmsnorm(x, w["model.embedding_norm.weight"], config["norm_eps"])
+        return (z @ w["model.embed_tokens.weight"].T) * on_logits
+
+    sequences = prompts_of(config["vocab_size"], [30, 24], seed=46)
+    want = [plain_forward(seq) for seq in sequences]
+    step = loaded.step
+    at = [0, 0]
+    for sizes in ((11, 4), (2, 9)) + ((1, 1),) * 8 + ((9, 3),):
+        entries = [StepEntry(f"r{i}", sequences[i][at[i]:at[i] + n], list(range(n))) for i, n in enumerate(sizes)]
+        logits = step.run(entries, auto_begin=True).float().cpu().numpy()
+        row = 0
+        for i, n in enumerate(sizes):
+            worst = np.abs(logits[row:row + n] - want[i][at[i]:at[i] + n]).max()
+            assert worst < tol, f"request {i}, tokens {at[i]}..{at[i] + n}: {worst:.3e}"
+            row += n
+            at[i] += n
+    step.raise_on_device_error()
+
+
 def test_decoding_twenty_requests_on_the_streaming_product(models, monkeypatch):
     """CELEG_B200_TC_PRODUCTS=stream: steps of 17 to 128 rows run the weight-streaming tcgen05 product
     with its fused epilogues (SwiGLU, short convolution); greedy tokens against the plain model."""
