@@ -98,11 +98,9 @@ __global__ void short_conv_tokens_bf16x8_kernel(const __nv_bfloat16* proj, const
 constexpr int kTokensPerThread = 8;
 constexpr int kFewTaps = 4;
 
-__global__ void __launch_bounds__(128)
-short_conv_tokens_window_kernel(const __nv_bfloat16* proj, const float* __restrict__ kernel, __nv_bfloat16* out,
-                                const int* token_span, const int* span_begin, int hidden, int taps, int tokens) {
-    chain_release();
-    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+__device__ __forceinline__ void short_conv_window_body(const __nv_bfloat16* proj, const float* __restrict__ kernel,
+                                                       __nv_bfloat16* out, const int* token_span, const int* span_begin,
+                                                       int hidden, int taps, int tokens, const int c, const int group) {
     if (c >= hidden) return;
     float w[kFewTaps][8];                        // w[e]: the tap that meets the token e places back (tap taps-1-e)
 #pragma unroll
@@ -110,7 +108,7 @@ short_conv_tokens_window_kernel(const __nv_bfloat16* proj, const float* __restri
 #pragma unroll
         for (int i = 0; i < 8; ++i) w[e][i] = e < taps ? kernel[(size_t)(c + i) * taps + (taps - 1 - e)] : 0.0f;
     chain_wait();
-    const int t0 = blockIdx.y * kTokensPerThread;
+    const int t0 = group * kTokensPerThread;
     const size_t row = (size_t)3 * hidden;
     const int keep = taps - 1;
     constexpr int kRows = kTokensPerThread + kFewTaps - 1;
@@ -174,18 +172,16 @@ short_conv_tokens_window_kernel(const __nv_bfloat16* proj, const float* __restri
 // Everything that touches a request's state: the first taps-1 tokens of its span and the slot's new
 // content, one thread per (span, channel), which reads the old state into registers before it writes.
 template <typename A>
-__global__ void short_conv_spans_kernel(const A* proj, const float* __restrict__ kernel, float* state,
-                                        long long slot_stride, A* out, const int* span_begin, const int* span_slot,
-                                        int hidden, int taps) {
-    chain_release();
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+__device__ __forceinline__ void short_conv_spans_body(const A* proj, const float* __restrict__ kernel, float* state,
+                                                      long long slot_stride, A* out, const int* span_begin,
+                                                      const int* span_slot, int hidden, int taps, const int c,
+                                                      const int s) {
     if (c >= hidden) return;
     const size_t row = (size_t)3 * hidden;
     float w[kMaxTaps];
 #pragma unroll
     for (int i = 0; i < kMaxTaps; ++i) w[i] = i < taps ? kernel[(size_t)c * taps + i] : 0.0f;   // constant data
     chain_wait();
-    const int s = blockIdx.y;
     const int first = span_begin[s];
     const int count = span_begin[s + 1] - first;
     const int keep = taps - 1;
@@ -222,6 +218,43 @@ __global__ void short_conv_spans_kernel(const A* proj, const float* __restrict__
     }
 }
 
+template <typename A>
+__global__ void short_conv_spans_kernel(const A* proj, const float* __restrict__ kernel, float* state,
+                                        long long slot_stride, A* out, const int* span_begin, const int* span_slot,
+                                        int hidden, int taps) {
+    chain_release();
+    short_conv_spans_body<A>(proj, kernel, state, slot_stride, out, span_begin, span_slot, hidden, taps,
+                             blockIdx.x * blockDim.x + threadIdx.x, blockIdx.y);
+}
+
+__global__ void __launch_bounds__(128)
+short_conv_tokens_window_kernel(const __nv_bfloat16* proj, const float* __restrict__ kernel, __nv_bfloat16* out,
+                                const int* token_span, const int* span_begin, int hidden, int taps, int tokens) {
+    chain_release();
+    short_conv_window_body(proj, kernel, out, token_span, span_begin, hidden, taps, tokens,
+                           (blockIdx.x * blockDim.x + threadIdx.x) * 8, blockIdx.y);
+}
+
+// Both of them in one launch for prompt portions (bfloat16, at most four taps): the first blocks do the spans'
+// work, which is a chain of dependent loads per thread and would otherwise stand alone on the GPU for
+// several microseconds, the others the sliding windows; the two write different tokens.
+__global__ void __launch_bounds__(128)
+short_conv_prompt_kernel(const __nv_bfloat16* proj, const float* __restrict__ kernel, float* state, long long slot_stride,
+                         __nv_bfloat16* out, const int* token_span, const int* span_begin, const int* span_slot,
+                         int hidden, int taps, int tokens, int spans, int span_blocks_x, int window_blocks_x) {
+    chain_release();
+    int block = blockIdx.x;
+    const int span_blocks = span_blocks_x * spans;
+    if (block < span_blocks) {
+        short_conv_spans_body<__nv_bfloat16>(proj, kernel, state, slot_stride, out, span_begin, span_slot, hidden, taps,
+                                             (block % span_blocks_x) * blockDim.x + threadIdx.x, block / span_blocks_x);
+    } else {
+        block -= span_blocks;
+        short_conv_window_body(proj, kernel, out, token_span, span_begin, hidden, taps, tokens,
+                               ((block % window_blocks_x) * blockDim.x + threadIdx.x) * 8, block / window_blocks_x);
+    }
+}
+
 }  // namespace celeg_b200
 
 using namespace celeg_b200;
@@ -237,6 +270,19 @@ CELEG_API int celeg_short_conv(const void* proj, const float* kernel, float* sta
     if (tokens == 0) return 0;
     CELEG_REQUIRE(tokens <= 65535 && spans <= 65535, "short_conv: %d tokens or %d spans exceed one launch (65535)",
                   tokens, spans);
+    const bool windows = act_dtype == kBFloat16 && hidden % 8 == 0 && ((((size_t)proj) | ((size_t)out)) & 15) == 0 &&
+                         taps <= kFewTaps && tokens >= 4 * kTokensPerThread && max_span > taps - 1;
+    if (windows) {
+        const int span_blocks_x = (hidden + 127) / 128, window_blocks_x = (hidden / 8 + 127) / 128;
+        const long long blocks = (long long)span_blocks_x * spans +
+                                 (long long)window_blocks_x * ((tokens + kTokensPerThread - 1) / kTokensPerThread);
+        if (blocks <= 0x7fffffffLL) {
+            launch_chained(short_conv_prompt_kernel, (unsigned)blocks, 128, 0, stream, (const __nv_bfloat16*)proj, kernel,
+                           state, slot_stride, (__nv_bfloat16*)out, token_span, span_begin, span_slot, hidden, taps,
+                           tokens, spans, span_blocks_x, window_blocks_x);
+            return check_launch("short_conv (prompt portions)");
+        }
+    }
     const int threads = hidden >= 256 ? 256 : ((hidden + 31) / 32) * 32;
     dim3 span_grid((hidden + threads - 1) / threads, spans);
     if (act_dtype == kFloat32)
