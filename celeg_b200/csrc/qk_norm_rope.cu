@@ -95,6 +95,123 @@ qk_norm_rope_tokens_kernel(A* qkv, A* k_cache, A* v_cache, const QkNormRopeArgs 
     }
 }
 
+// The same for many tokens with 16-byte accesses: a warp per token; LANES = head size / 16 lanes share a head,
+// lane `sub` of them holds elements [8 sub, 8 sub + 8) and their rotation partners [8 (sub + LANES), ...), so a
+// warp takes 32 / LANES heads at a time. A lane's sines and cosines are computed once per token and serve
+// every head; the sum of squares meets over the LANES lanes by shuffles. Arithmetic as in the kernels above
+// (float32 throughout, one rounding at the end); only the order of the sum of squares differs.
+template <int LANES>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_tokens_vec_kernel(__nv_bfloat16* qkv, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache, const QkNormRopeArgs a) {
+    chain_release();
+    constexpr int kHead = LANES * 16, kHalf = LANES * 8, kHeadsAtOnce = 32 / LANES;
+    const int lane = threadIdx.x & 31;
+    const int sub = lane % LANES, slot = lane / LANES;
+    // constant data first: this lane's frequencies and norm weights
+    float freq[8], wq[16], wk[16];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) freq[e] = a.inv_freq[sub * 8 + e];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        wq[e] = a.q_weight ? a.q_weight[sub * 8 + e] : 1.0f;
+        wq[8 + e] = a.q_weight ? a.q_weight[kHalf + sub * 8 + e] : 1.0f;
+        wk[e] = a.k_weight ? a.k_weight[sub * 8 + e] : 1.0f;
+        wk[8 + e] = a.k_weight ? a.k_weight[kHalf + sub * 8 + e] : 1.0f;
+    }
+    chain_wait();
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= a.tokens) return;
+    const int heads = a.q_heads + 2 * a.kv_heads;
+    const int pos = a.positions[t];
+    float sn[8], cs[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sincosf((float)pos * freq[e], &sn[e], &cs[e]);
+    long long cache_row = -1;                       // offset of (page, kv head 0, slot in page), in elements
+    if (a.store_kv == 1) {
+        const int page = a.block_table[(size_t)a.token_span[t] * a.table_stride + pos / a.page_tokens];
+        if (page < 0) {                             // the host never builds such a table
+            if (lane == 0) atomicExch(a.error_flag, 1);
+        } else {
+            cache_row = (long long)page * a.page_stride + (long long)(pos % a.page_tokens) * kHead;
+        }
+    }
+    __nv_bfloat16* row = qkv + (size_t)t * heads * kHead;
+    for (int h0 = 0; h0 < heads; h0 += kHeadsAtOnce) {
+        const int h = h0 + slot;
+        const bool is_q = h < a.q_heads;
+        const bool is_k = !is_q && h < a.q_heads + a.kv_heads;
+        bool active = h < heads;
+        __nv_bfloat16* vec = row + (size_t)h * kHead;
+        __nv_bfloat16* dst = vec;
+        if (active && !is_q) {
+            if (a.store_kv == 2) {
+                active = is_k;                      // k in place, v untouched
+            } else if (cache_row < 0) {
+                active = false;                     // q heads only, or no page
+            } else {
+                const int kvh = is_k ? h - a.q_heads : h - a.q_heads - a.kv_heads;
+                dst = (is_k ? k_cache : v_cache) + cache_row + (size_t)kvh * a.page_tokens * kHead;
+            }
+        }
+        uint4 lo4 = make_uint4(0u, 0u, 0u, 0u), hi4 = lo4;
+        if (active) {
+            lo4 = __ldcg(reinterpret_cast<const uint4*>(vec + sub * 8));
+            hi4 = __ldcg(reinterpret_cast<const uint4*>(vec + kHalf + sub * 8));
+        }
+        const bool is_v = !is_q && !is_k;
+        float x[8], y[8];
+        {
+            const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lo4);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hi4);
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+                const float2 l = __bfloat1622float2(l2[e2]), u = __bfloat1622float2(h2[e2]);
+                x[2 * e2] = l.x;
+                x[2 * e2 + 1] = l.y;
+                y[2 * e2] = u.x;
+                y[2 * e2 + 1] = u.y;
+            }
+        }
+        // (every lane takes part in the shuffles; heads past the end and v heads carry zeros or are not used)
+        const float* weight = is_q ? a.q_weight : a.k_weight;
+        float sum = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += x[e] * x[e];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += y[e] * y[e];
+#pragma unroll
+        for (int offset = 1; offset < LANES; offset <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+        if (!active) continue;
+        if (is_v) {                                 // v: plain copy
+            *reinterpret_cast<uint4*>(dst + sub * 8) = lo4;
+            *reinterpret_cast<uint4*>(dst + kHalf + sub * 8) = hi4;
+            continue;
+        }
+        const float scale = weight ? 1.0f / sqrtf(sum / (float)kHead + a.eps) : 1.0f;
+        uint4 out_lo, out_hi;
+        __nv_bfloat162* ol = reinterpret_cast<__nv_bfloat162*>(&out_lo);
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out_hi);
+        float rl[8], rh[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float u = x[e], v = y[e];
+            if (weight) {
+                u = u * scale * (is_q ? wq[e] : wk[e]);
+                v = v * scale * (is_q ? wq[8 + e] : wk[8 + e]);
+            }
+            rl[e] = u * cs[e] - v * sn[e];
+            rh[e] = v * cs[e] + u * sn[e];
+        }
+#pragma unroll
+        for (int e2 = 0; e2 < 4; ++e2) {
+            ol[e2] = __floats2bfloat162_rn(rl[2 * e2], rl[2 * e2 + 1]);
+            oh[e2] = __floats2bfloat162_rn(rh[2 * e2], rh[2 * e2 + 1]);
+        }
+        *reinterpret_cast<uint4*>(dst + sub * 8) = out_lo;
+        *reinterpret_cast<uint4*>(dst + kHalf + sub * 8) = out_hi;
+    }
+}
+
 }  // namespace celeg_b200
 
 using namespace celeg_b200;
@@ -125,6 +242,21 @@ CELEG_API int celeg_qk_norm_rope_store(void* qkv, const float* q_weight, const f
     // many tokens of the common shape: a warp per token and run of eight heads
     if (act_dtype == kBFloat16 && inv_freq && rotary_dim == head_dim && tokens >= 64 &&
         (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
+        const bool aligned = ((((size_t)qkv) | ((size_t)k_cache) | ((size_t)v_cache)) & 15) == 0 &&
+                             (page_stride % 8) == 0;
+        if (aligned) {
+            const unsigned token_blocks = (unsigned)((tokens + warps - 1) / warps);
+            __nv_bfloat16* q = (__nv_bfloat16*)qkv;
+            __nv_bfloat16* kc = (__nv_bfloat16*)k_cache;
+            __nv_bfloat16* vc = (__nv_bfloat16*)v_cache;
+            if (head_dim == 64)
+                launch_chained(qk_norm_rope_tokens_vec_kernel<4>, token_blocks, warps * 32, 0, stream, q, kc, vc, args);
+            else if (head_dim == 128)
+                launch_chained(qk_norm_rope_tokens_vec_kernel<8>, token_blocks, warps * 32, 0, stream, q, kc, vc, args);
+            else
+                launch_chained(qk_norm_rope_tokens_vec_kernel<16>, token_blocks, warps * 32, 0, stream, q, kc, vc, args);
+            return check_launch("qk_norm_rope_store");
+        }
         const int run = 8;
         const long long runs = (long long)tokens * ((q_heads + 2 * kv_heads + run - 1) / run);
         const unsigned run_blocks = (unsigned)((runs + warps - 1) / warps);
