@@ -77,6 +77,8 @@ class StepFunction:
         self.use_graphs = use_graphs
         self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self._graph_launches: Dict[tuple, int] = {}
+        self._prompt_seen: Dict[tuple, int] = {}
+        self.max_prompt_graphs = 24
         self.steps_run = 0
         self.kernel_steps_graphed = 0
         self.last_step: Optional[StepContext] = None
@@ -150,7 +152,8 @@ class StepFunction:
         spans = len(entries)
         all_decode = all(len(entry.tokens) == 1 for entry in entries)
         max_ctx = max(cache.tokens + len(entry.tokens) for entry, cache in zip(entries, caches))
-        if all_decode and self.use_graphs:
+        prompt_key = self._prompt_graph_key(entries, total, wanted) if not all_decode else None
+        if (all_decode and self.use_graphs) or prompt_key is not None:
             stride = self.max_pages                         # fixed, so the captured addresses hold
         else:
             stride = (max_ctx + self.page_tokens - 1) // self.page_tokens
@@ -180,7 +183,7 @@ class StepFunction:
                 self._wide_logits = torch.empty((wanted, vocab), dtype=torch.float32, device=self.rt.device)
             logits = self._wide_logits
 
-        graph_key = (spans, wanted, _context_bucket(max_ctx)) if (all_decode and self.use_graphs and wanted <= self.max_spans) else None
+        graph_key = (spans, wanted, _context_bucket(max_ctx)) if (all_decode and self.use_graphs and wanted <= self.max_spans) else prompt_key
         if graph_key is not None:
             self._run_graphed(graph_key, step, logit_rows, wanted, logits)
         else:
@@ -189,6 +192,30 @@ class StepFunction:
             self.manager.advance(cache, cache.tokens + len(entry.tokens))
         self.steps_run += 1
         return logits[:wanted]
+
+    def _prompt_graph_key(self, entries, total: int, wanted: int):
+        """Steps with prompt portions are launched from the host kernel by kernel, which takes longer than the
+        GPU needs for portions of a few hundred tokens. Every launch shape of such a step follows from the
+        lengths of its portions, the number of wanted rows and whether those are all rows in order, so a step
+        whose shape has come before (a long prompt cut into equal portions) is captured in a CUDA graph at
+        its second coming and replayed from then on. None: run it kernel by kernel."""
+        if not self.use_graphs or wanted > self.max_spans:
+            return None
+        all_rows = wanted == total and all(tuple(e.want) == tuple(range(len(e.tokens))) for e in entries)
+        key = ("prompt", tuple(len(e.tokens) for e in entries), wanted, all_rows)
+        if key in self._graphs:
+            return key
+        if len(self._prompt_seen) > 4096:
+            self._prompt_seen.clear()
+        seen = self._prompt_seen.get(key, 0) + 1
+        self._prompt_seen[key] = seen
+        if seen < 2:
+            return None
+        prompt_graphs = [k for k in self._graphs if k and k[0] == "prompt"]
+        if len(prompt_graphs) >= self.max_prompt_graphs:     # the oldest goes (dicts keep insertion order)
+            del self._graphs[prompt_graphs[0]]
+            del self._graph_launches[prompt_graphs[0]]
+        return key
 
     def _run_graphed(self, key, step, logit_rows, wanted, logits) -> None:
         graph = self._graphs.get(key)

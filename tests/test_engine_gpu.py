@@ -1003,6 +1003,49 @@ def test_scale_factors_of_a_model_description(tmp_path, dtype, tol):
     step.raise_on_device_error()
 
 
+@pytest.mark.parametrize("name,dtype,tol", [("A", "float32", 3e-4), ("D", "bfloat16", 8e-2)])
+def test_equal_prompt_portions_are_replayed_from_a_graph(tmp_path, name, dtype, tol):
+    """A prompt cut into equal portions: the second portion of a shape is captured in a CUDA graph, the later
+    ones are replayed from it (other contexts, other pages, the same launch shapes); a portion of another
+    length and a step that mixes a portion with a decoded token run kernel by kernel or get graphs of their
+    own. All of it against the plain implementation, and the same again without graphs gives the same bits."""
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    folder = write_tiny(tmp_path, name)
+    config, weights = plain_lfm2.load_model_folder(folder)
+    long_seq, other = prompts_of(config["vocab_size"], [6 * 24 + 10, 30], seed=47)
+    want_long = plain_lfm2.forward(config, weights, long_seq)
+    want_other = plain_lfm2.forward(config, weights, other)
+
+    def run(use_graphs):
+        loaded = load_model(folder, dtype=dtype, max_requests=2, cache_tokens=256, max_batched_tokens=64,
+                            use_graphs=use_graphs)
+        step = loaded.step
+        rows = []
+        at = 0
+        for _ in range(6):                                        # six portions of 24 tokens, the last row wanted
+            rows.append(step.run([StepEntry("long", long_seq[at:at + 24], [23])], auto_begin=True).float().cpu().numpy()[0])
+            at += 24
+        graphed_after_equal_portions = step.kernel_steps_graphed
+        rows.append(step.run([StepEntry("long", long_seq[at:at + 10], [9])]).float().cpu().numpy()[0])   # another length
+        for start in (0, 12):                                     # a second request: two portions of 12 beside nothing
+            step.run([StepEntry("other", other[start:start + 12], [])], auto_begin=True)
+        mixed = step.run([StepEntry("other", other[24:30], [5]), StepEntry("long", [long_seq[5]], [0])])
+        rows.append(mixed.float().cpu().numpy()[0])
+        step.raise_on_device_error()
+        return np.stack(rows), graphed_after_equal_portions
+
+    got, graphed = run(True)
+    assert graphed == 5                      # the first portion ran kernel by kernel, the second was captured
+    ref, not_graphed = run(False)
+    assert not_graphed == 0
+    assert np.array_equal(got, ref)
+    for i in range(6):
+        assert np.abs(got[i] - want_long[24 * i + 23]).max() < tol, f"portion {i}"
+    assert np.abs(got[6] - want_long[153]).max() < tol
+    assert np.abs(got[7] - want_other[29]).max() < tol
+
+
 def test_decoding_twenty_requests_on_the_streaming_product(models, monkeypatch):
     """CELEG_B200_TC_PRODUCTS=stream: steps of 17 to 128 rows run the weight-streaming tcgen05 product
     with its fused epilogues (SwiGLU, short convolution); greedy tokens against the plain model."""
