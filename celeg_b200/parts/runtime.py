@@ -113,9 +113,11 @@ class Runtime:
         # as "swiglu", and products of 17 to 128 rows on the weight-streaming tcgen05 kernel (slower than the
         # library product as it stands; kept selectable for measurements).
         self.tensor_core_products = os.environ.get("CELEG_B200_TC_PRODUCTS", "swiglu")
-        # below this many rows the library product still wins (measured at 64 rows: 1.16 against 1.37 ms
-        # per decode step): few rows mean few 128-row tiles, and the weight stream is spread over too few SMs
-        self.tensor_core_min_rows = 256
+        # below this many rows the library product followed by the activation kernel still wins: few rows
+        # mean few 128-row tiles in too few waves. Measured, 2,048 prompt tokens in portions of 256 / 512 / 1,024 /
+        # 1,536 / 2,048 rows: 9.70 / 6.51 / 4.66 / 4.84 / 3.99 ms with this package's kernel against 9.34 / 6.15 /
+        # 4.59 / 4.76 / 4.13 ms with the library's (at 64 rows: 1.36 against 1.15 ms per decode step)
+        self.tensor_core_min_rows = 2048
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.sink: Optional[_Sink] = None         # set by the residual stream around a part's forward
         self.sink_residual: Optional[torch.Tensor] = None

@@ -1062,6 +1062,32 @@ def test_decoding_twenty_requests_on_the_streaming_product(models, monkeypatch):
     engine.loaded.step.raise_on_device_error()
 
 
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_every_product_on_the_tcgen05_kernel(tmp_path, monkeypatch, name):
+    """CELEG_B200_TC_PRODUCTS=all: every product of more than 16 rows, the gate+up product with its activation
+    included, runs on this package's TMA + tcgen05 kernel instead of the library's (by default only gate+up of
+    2,048 rows and more does). A prompt whole, in portions and beside decoded tokens, against the plain model."""
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    monkeypatch.setenv("CELEG_B200_TC_PRODUCTS", "all")
+    folder = write_tiny(tmp_path, name)
+    config, weights = plain_lfm2.load_model_folder(folder)
+    first, second = prompts_of(config["vocab_size"], [300, 150], seed=48)
+    want = [plain_lfm2.forward(config, weights, first), plain_lfm2.forward(config, weights, second)]
+    loaded = load_model(folder, dtype="bfloat16", max_requests=2, cache_tokens=512, max_batched_tokens=320)
+    step = loaded.step
+    tol = 8e-2
+    whole = step.run([StepEntry("whole", first, [0, 150, 299])], auto_begin=True).float().cpu().numpy()
+    for row, place in enumerate((0, 150, 299)):
+        assert np.abs(whole[row] - want[0][place]).max() < tol, f"whole prompt, place {place}"
+    step.end("whole")
+    got = step.run([StepEntry("a", first[:170], [169]), StepEntry("b", second[:131], [130])], auto_begin=True).float().cpu().numpy()
+    assert np.abs(got[0] - want[0][169]).max() < tol and np.abs(got[1] - want[1][130]).max() < tol
+    got = step.run([StepEntry("a", first[170:299], [128]), StepEntry("b", [second[131]], [0])]).float().cpu().numpy()
+    assert np.abs(got[0] - want[0][298]).max() < tol and np.abs(got[1] - want[1][131]).max() < tol
+    step.raise_on_device_error()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_requests_that_end_on_a_token_while_the_next_step_is_in_flight(models, dtype):
     """The scheduler enqueues the step after the one it reads while every request decodes. A request
