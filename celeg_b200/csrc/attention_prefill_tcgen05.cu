@@ -4,21 +4,25 @@
 //   grid = (query heads, query tiles); a query tile is up to 128 consecutive tokens of one span; tiles with
 //   many keys come first in launch order, so that the grid drains with short ones.
 //   Six warps. Warp 0 brings Q (one box of 128 rows x 64) and, per block of 64 keys, the K and V
-//   rows page by page through the request's block table into a two-stage ring by TMA (128-byte
-//   swizzle; a page is one box of page_tokens rows x 64). Warp 1 issues the MMAs:
+//   rows page by page through the request's block table into a four-stage ring by TMA (128-byte
+//   swizzle; a page is one box of page_tokens rows x 64): lane 0 waits for the stage, then lane 2 pg brings
+//   page pg of K and lane 2 pg + 1 that of V, each looked up one block ahead (one thread issuing a block's
+//   up to 16 copies in turn took longer than the block's softmax). Warp 1 issues the MMAs:
 //       S[128 x 64] = Q K^T           (tcgen05.mma M128 N64 K16 x 4, both operands K-major)
-//       O'[128 x 64] = P V            (M128 N64 K16 x 4, P K-major from shared memory, V as it lies in
-//                                      the cache, keys x 64: the MN-major form of the B operand)
-//   with S and O' in tensor memory. S, P and O' exist twice (even and odd blocks of keys): the scores of
-//   block j+1 are being multiplied while the softmax threads work on block j, and P V of block j runs while
-//   they work on block j+1 (they add O' of a block one block later). 256 columns of tensor memory and 97 KiB
-//   of shared memory a block: two blocks per SM. Warps 2-5 are the softmax: a thread owns one
-//   query row (its TMEM lane), reads S with tcgen05.ld, scales, masks (causal, window, rows past the span;
-//   blocks that every row sees whole skip the mask), keeps the running
-//   maximum and denominator in float32 (exponentials by exp2 of pre-scaled scores), writes P as
-//   bfloat16 into shared memory in the swizzled layout the MMA reads, and adds O' into its row of the
-//   output, which it keeps in registers, rescaled by the usual correction. No shuffles: a row is
-//   one thread.
+//       O[128 x 64] += P V            (M128 N64 K16 x 4, P from tensor memory as the A operand, V as it lies
+//                                      in the cache, keys x 64: the MN-major form of the B operand)
+//   with S, P and O in tensor memory. S and P exist twice (even and odd blocks of keys): the scores of block
+//   j+1 are being multiplied while the softmax threads work on block j, and P V of block j runs while they
+//   work on block j+1. 256 columns of tensor memory and 81 KiB of shared memory a block: two blocks per SM.
+//   Warps 2-5 are the softmax: a thread owns one query row (its TMEM lane), reads S with tcgen05.ld, masks
+//   (causal, window, rows past the span; blocks that every row sees whole skip the mask), takes the maximum,
+//   writes P = exp2(scaled S - maximum) as bfloat16 pairs into tensor memory with tcgen05.st and adds to its
+//   denominator, all in float32 (packed f32x2 arithmetic, three-input maxima). O stays in tensor memory: the
+//   maximum that P is relative to follows the true running maximum only when that has grown by more than 2^8,
+//   and only then the warp rescales its rows of O (tcgen05.ld, multiply, tcgen05.st); at the end a thread
+//   divides its row by the denominator and writes it. No shuffles: a row is one thread. Every tensor-memory
+//   load, store and wait is taken by all lanes of a warp (they are .sync.aligned); only stores to global
+//   memory are conditional.
 //   Every wait on an mbarrier is bounded (tcgen05.cuh); a role that gives up records a code, and the
 //   block leaves through the common exit (tensor memory released).
 //

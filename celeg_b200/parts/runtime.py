@@ -227,7 +227,7 @@ class Runtime:
     def linear_swiglu(self, x: torch.Tensor, gate_up_weight: torch.Tensor, scratch: torch.Tensor,
                       out: torch.Tensor, rows: int, inner: int) -> None:
         """out[:rows] = silu(x gate^T) * (x up^T) with gate_up_weight = [gate rows; up rows]. Few
-        bfloat16 rows: one weight-streaming kernel; more bfloat16 rows: one tcgen05 kernel; otherwise the
+        bfloat16 rows: one weight-streaming kernel; very many bfloat16 rows: one tcgen05 kernel; otherwise the
         product into ``scratch`` and the activation kernel."""
         if rows == 0:
             return
