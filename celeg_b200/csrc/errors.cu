@@ -39,7 +39,7 @@ bool chaining_enabled(int kernel_class) {
 
 }  // namespace celeg_b200
 
-// 1: kernels of a step are launched with programmatic stream serialization (default); 0: plain launches.
+// A bit per class of kernels (see chaining_enabled): set = launched with programmatic stream serialization.
 CELEG_API void celeg_set_chained_launch(int mask) { celeg_b200::g_chaining = mask; }
 
 CELEG_API const char* celeg_last_error() { return celeg_b200::g_error; }

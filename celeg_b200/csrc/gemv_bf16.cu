@@ -20,6 +20,9 @@
 // a narrow matrix has few blocks, and only more warps per block put enough loads in flight to keep
 // HBM busy. Any N; K must be a multiple of 8 (16-byte rows); otherwise the caller uses the library
 // product.
+// Across kernel boundaries: launched with programmatic stream serialization, a block issues its first weight
+// loads before it waits for the kernel before it (weights are constant data), and its last blocks ask the
+// first megabytes of the next product's weights into the L2 (GemvPrefetch).
 //
 // Counterpart in celeg: bf16_gemv_kernel for M = 1 (include/celeg/backend/cuda/kernels/gemv_kernels.cuh:12-44,
 // one warp per output row, no tensor cores) and cuBLAS for M > 1.
