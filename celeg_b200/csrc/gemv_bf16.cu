@@ -137,6 +137,26 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
             for (int e = 0; e < 4; ++e) acc[t][j][e] = 0.0f;
 
     const int slices = k / 32;                       // full 32-element slices; the tail is handled below
+    // Convolution epilogue with few taps: the thread that will finish element `threadIdx.x` of the block's tile
+    // fetches its request's carried taps and its channel's kernel while the weights stream, instead of
+    // after the sums are there (a chain of three dependent loads at the very end of a short kernel).
+    constexpr int kEarlyTaps = 4;
+    float early_history[kEarlyTaps - 1], early_kernel[kEarlyTaps];
+    const bool early = MODE == kGemvConv && conv.taps <= kEarlyTaps && (int)threadIdx.x < MT * 128;
+    auto fetch_early = [&]() {
+        if (!early) return;
+        const int i = threadIdx.x, j = i / 128, ln = (i % 128) / 4, e = i % 4;
+        const int out_col = row0 + (ln >> 2) + ((e >> 1) << 3);
+        const int out_row = j * 8 + ((ln & 3) << 1) + (e & 1);
+        if (out_row >= m || out_col >= n) return;
+        const int keep = conv.taps - 1;
+        const float* st = conv.state + (size_t)conv.span_slot[out_row] * conv.slot_stride + out_col;
+        const float* cw = conv.conv_w + (size_t)out_col * conv.taps;
+#pragma unroll
+        for (int tp = 0; tp < kEarlyTaps - 1; ++tp) early_history[tp] = tp < keep ? st[(size_t)tp * n] : 0.0f;
+#pragma unroll
+        for (int tp = 0; tp < kEarlyTaps; ++tp) early_kernel[tp] = tp < conv.taps ? cw[tp] : 0.0f;
+    };
     bool waited = false;
     for (int s0 = warp; s0 < slices; s0 += kGemvWarps * kGemvUnroll) {
         uint4 a_lo[kGemvUnroll][WT], a_hi[kGemvUnroll][WT];
@@ -156,6 +176,7 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
         if (!waited) {
             chain_wait();
             waited = true;
+            fetch_early();
             if (norm.sumsq_in) {
                 // the rows' scales, while the weights are on their way: a warp per row
                 for (int r = warp; r < m; r += kGemvWarps) {
@@ -195,6 +216,7 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
     }
     if (!waited) {
         chain_wait();
+        fetch_early();
         if (norm.sumsq_in) {
             for (int r = warp; r < m; r += kGemvWarps) {
                 float total = 0.0f;
@@ -290,11 +312,25 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
             float* st = conv.state + (size_t)conv.span_slot[out_row] * conv.slot_stride + out_col;   // [keep][n]
             const float* cw = conv.conv_w + (size_t)out_col * conv.taps;
             float history[kGemvMaxConvTaps];
-#pragma unroll
-            for (int tp = 0; tp < kGemvMaxConvTaps; ++tp) history[tp] = tp < keep ? st[(size_t)tp * n] : 0.0f;
             float acc_conv = 0.0f;
-            for (int tp = 0; tp < keep; ++tp) acc_conv += cw[tp] * history[tp];
-            acc_conv += cw[keep] * bx;
+            if (early && i == (int)threadIdx.x) {
+                // (same values, same order of the sum: fetched while the weights streamed)
+#pragma unroll
+                for (int tp = 0; tp < kGemvMaxConvTaps; ++tp) history[tp] = tp < kEarlyTaps - 1 ? early_history[tp] : 0.0f;
+#pragma unroll
+                for (int tp = 0; tp < kEarlyTaps - 1; ++tp)
+                    if (tp < keep) acc_conv += early_kernel[tp] * early_history[tp];
+                float last = 0.0f;
+#pragma unroll
+                for (int tp = 0; tp < kEarlyTaps; ++tp)
+                    if (tp == keep) last = early_kernel[tp];
+                acc_conv += last * bx;
+            } else {
+#pragma unroll
+                for (int tp = 0; tp < kGemvMaxConvTaps; ++tp) history[tp] = tp < keep ? st[(size_t)tp * n] : 0.0f;
+                for (int tp = 0; tp < keep; ++tp) acc_conv += cw[tp] * history[tp];
+                acc_conv += cw[keep] * bx;
+            }
             reinterpret_cast<__nv_bfloat16*>(y)[(size_t)out_row * ldy + out_col] = __float2bfloat16_rn(cc * acc_conv);
             for (int tp = 0; tp + 1 < keep; ++tp) st[(size_t)tp * n] = history[tp + 1];
             if (keep > 0) st[(size_t)(keep - 1) * n] = bx;
