@@ -143,7 +143,19 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
     constexpr int kEarlyTaps = 4;
     float early_history[kEarlyTaps - 1], early_kernel[kEarlyTaps];
     const bool early = MODE == kGemvConv && conv.taps <= kEarlyTaps && (int)threadIdx.x < MT * 128;
+    // The epilogue that adds to the residual stream likewise: the stream's old value and the next norm's weight.
+    float early_residual = 0.0f, early_next_w = 0.0f;
+    const bool early_add = MODE == kGemvAddResidual && (int)threadIdx.x < MT * 128;
     auto fetch_early = [&]() {
+        if (early_add) {
+            const int i = threadIdx.x, j = i / 128, ln = (i % 128) / 4, e = i % 4;
+            const int out_col = row0 + (ln >> 2) + ((e >> 1) << 3);
+            const int out_row = j * 8 + ((ln & 3) << 1) + (e & 1);
+            if (out_row < m && out_col < n) {
+                early_residual = reinterpret_cast<const float*>(y)[(size_t)out_row * ldy + out_col];
+                if (norm.next_w) early_next_w = norm.next_w[out_col];
+            }
+        }
         if (!early) return;
         const int i = threadIdx.x, j = i / 128, ln = (i % 128) / 4, e = i % 4;
         const int out_col = row0 + (ln >> 2) + ((e >> 1) << 3);
@@ -295,10 +307,12 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
         } else if (MODE == kGemvAddResidual) {
             // the product as a plain product would store it (one rounding to bfloat16), added in float32
             float* dst = reinterpret_cast<float*>(y) + (size_t)out_row * ldy + out_col;
-            const float updated = *dst + __bfloat162float(__float2bfloat16_rn(sum[0]));
+            const bool fetched = early_add && i == (int)threadIdx.x;       // (fetched while the weights streamed)
+            const float updated = (fetched ? early_residual : *dst) + __bfloat162float(__float2bfloat16_rn(sum[0]));
             *dst = updated;
             if (norm.next_w) {
-                norm.xw_out[(size_t)out_row * norm.ldxw + out_col] = __float2bfloat16_rn(updated * norm.next_w[out_col]);
+                const float next_w = fetched ? early_next_w : norm.next_w[out_col];
+                norm.xw_out[(size_t)out_row * norm.ldxw + out_col] = __float2bfloat16_rn(updated * next_w);
                 squares[out_row][out_col - row0] = updated * updated;
             }
         } else if (MODE == kGemvConv) {
