@@ -185,20 +185,11 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
         }
         // the first batch of weights (constant data) is already on its way when the kernel starts
         // to wait for the activations of the kernel before it
+        const bool first = !waited;
         if (!waited) {
             chain_wait();
             waited = true;
             fetch_early();
-            if (norm.sumsq_in) {
-                // the rows' scales, while the weights are on their way: a warp per row
-                for (int r = warp; r < m; r += kGemvWarps) {
-                    float total = 0.0f;
-                    for (int i = lane; i < norm.partials_in; i += 32)
-                        total += __ldcg(norm.sumsq_in + (size_t)r * norm.sumsq_in_stride + i);
-                    total = warp_sum(total);
-                    if (lane == 0) row_scale[r] = 1.0f / sqrtf(total / (float)norm.width + norm.eps);
-                }
-            }
         }
         uint4 b[kGemvUnroll][MT];
 #pragma unroll
@@ -207,6 +198,17 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
             if (s < slices) {
 #pragma unroll
                 for (int j = 0; j < MT; ++j) b[u][j] = ld_activation(x_row[j] + s * 32);
+            }
+        }
+        if (first && norm.sumsq_in) {
+            // the rows' scales (needed by the epilogue only), while weights and activations are on their
+            // way: a warp per row
+            for (int r = warp; r < m; r += kGemvWarps) {
+                float total = 0.0f;
+                for (int i = lane; i < norm.partials_in; i += 32)
+                    total += __ldcg(norm.sumsq_in + (size_t)r * norm.sumsq_in_stride + i);
+                total = warp_sum(total);
+                if (lane == 0) row_scale[r] = 1.0f / sqrtf(total / (float)norm.width + norm.eps);
             }
         }
 #pragma unroll
