@@ -175,6 +175,53 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     const int* table = p.block_table + (size_t)p.token_span[t] * p.table_stride;
 
+    // The first tile of keys and values is asked for before anything else (the query's own preparation below
+    // takes as long as the tile needs to arrive). The token's own key and value may not be in the cache yet:
+    // their row is put right in shared memory when the tile is there (see the loop).
+    // A warp's part of the shared memory is kStages stages of [K tile | V tile] of TN keys: with two
+    // stages the next tile is on its way (page lookups included) while this one is in the tensor cores.
+    auto issue = [&](const int tile_begin, const int stage) {
+        __nv_bfloat16* k_dst = k_s + (size_t)stage * 2 * TN * D_PAD;
+        __nv_bfloat16* v_dst = k_dst + TN * D_PAD;
+        // page offsets of this lane's keys, then the copies of the whole tile in one go
+        long long offs[kKeysPerLane];
+#pragma unroll
+        for (int i = 0; i < kKeysPerLane; ++i) {
+            const int key = tile_begin + lane + 32 * i;
+            offs[i] = -1;
+            if (key < end) {
+                const int page = table[key / p.page_tokens];
+                if (page < 0)
+                    atomicExch(p.error_flag, 2);
+                else
+                    offs[i] = (long long)page * p.page_stride + ((long long)kvh * p.page_tokens + key % p.page_tokens) * d;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < TN * kChunks / 32; ++i) {
+            const int idx = lane + 32 * i;
+            const int r = idx / kChunks, ch = idx % kChunks;
+            long long off = -1;
+#pragma unroll
+            for (int j = 0; j < kKeysPerLane; ++j) {
+                const long long candidate = __shfl_sync(0xffffffffu, offs[j], r & 31);
+                if ((r >> 5) == j) off = candidate;
+            }
+            __nv_bfloat16* kd = k_dst + tile_offset<D_PAD>(r, ch);
+            __nv_bfloat16* vd = v_dst + tile_offset<D_PAD>(r, ch);
+            if (off >= 0 && ch * 8 < d) {
+                cp_async_16(kd, p.k_cache + off + ch * 8);
+                cp_async_16(vd, p.v_cache + off + ch * 8);
+            } else {
+                *reinterpret_cast<uint4*>(kd) = zero;
+                *reinterpret_cast<uint4*>(vd) = zero;
+            }
+        }
+        cp_async_commit();
+    };
+    constexpr int kTileStride = kDecodeWarps * TN;
+    int tile_begin = begin + warp * TN;
+    if (kStages == 2 && tile_begin < end) issue(tile_begin, 0);
     for (int idx = tid; idx < 16 * kChunks; idx += kDecodeThreads) {
         const int r = idx / kChunks, ch = idx % kChunks;
         __nv_bfloat16* dst = q_s + tile_offset<D_PAD>(r, ch);
@@ -233,54 +280,6 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     const float scale_log2 = p.scale * 1.4426950408889634f;
     const int mi = lane >> 3, lr = lane & 7;
 
-    // A warp's part of the shared memory is kStages stages of [K tile | V tile] of TN keys: with two
-    // stages the next tile is on its way (page lookups included) while this one is in the tensor cores.
-    auto issue = [&](const int tile_begin, const int stage) {
-        __nv_bfloat16* k_dst = k_s + (size_t)stage * 2 * TN * D_PAD;
-        __nv_bfloat16* v_dst = k_dst + TN * D_PAD;
-        // page offsets of this lane's keys, then the copies of the whole tile in one go
-        long long offs[kKeysPerLane];
-#pragma unroll
-        for (int i = 0; i < kKeysPerLane; ++i) {
-            const int key = tile_begin + lane + 32 * i;
-            offs[i] = -1;
-            if (key < end) {
-                const int page = table[key / p.page_tokens];
-                if (page < 0)
-                    atomicExch(p.error_flag, 2);
-                else
-                    offs[i] = (long long)page * p.page_stride + ((long long)kvh * p.page_tokens + key % p.page_tokens) * d;
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < TN * kChunks / 32; ++i) {
-            const int idx = lane + 32 * i;
-            const int r = idx / kChunks, ch = idx % kChunks;
-            long long off = -1;
-#pragma unroll
-            for (int j = 0; j < kKeysPerLane; ++j) {
-                const long long candidate = __shfl_sync(0xffffffffu, offs[j], r & 31);
-                if ((r >> 5) == j) off = candidate;
-            }
-            __nv_bfloat16* kd = k_dst + tile_offset<D_PAD>(r, ch);
-            __nv_bfloat16* vd = v_dst + tile_offset<D_PAD>(r, ch);
-            if (own_key_here && tile_begin + r == pos && ch * 8 < d) {
-                // the token's own key and value: not in the cache for this launch's readers, but here
-                *reinterpret_cast<uint4*>(kd) = *reinterpret_cast<const uint4*>(shared.new_k + ch * 8);
-                *reinterpret_cast<uint4*>(vd) = *reinterpret_cast<const uint4*>(shared.new_v + ch * 8);
-            } else if (off >= 0 && ch * 8 < d) {
-                cp_async_16(kd, p.k_cache + off + ch * 8);
-                cp_async_16(vd, p.v_cache + off + ch * 8);
-            } else {
-                *reinterpret_cast<uint4*>(kd) = zero;
-                *reinterpret_cast<uint4*>(vd) = zero;
-            }
-        }
-        cp_async_commit();
-    };
-    constexpr int kTileStride = kDecodeWarps * TN;
-    int tile_begin = begin + warp * TN;
-    if (kStages == 2 && tile_begin < end) issue(tile_begin, 0);
     for (int iteration = 0; tile_begin < end; ++iteration, tile_begin += kTileStride) {
         const int stage = kStages == 2 ? (iteration & 1) : 0;
         if (kStages == 2) {
@@ -295,8 +294,17 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
             cp_async_wait_group<0>();
         }
         __syncwarp();
-        const __nv_bfloat16* k_t = k_s + (size_t)stage * 2 * TN * D_PAD;
-        const __nv_bfloat16* v_t = k_t + TN * D_PAD;
+        __nv_bfloat16* k_t = k_s + (size_t)stage * 2 * TN * D_PAD;
+        __nv_bfloat16* v_t = k_t + TN * D_PAD;
+        if (own_key_here && pos >= tile_begin && pos < tile_begin + TN) {
+            // the token's own key and value: not in the cache for this launch's readers, but in shared memory
+            const int r = pos - tile_begin;
+            for (int ch = lane; ch * 8 < d; ch += 32) {
+                *reinterpret_cast<uint4*>(k_t + tile_offset<D_PAD>(r, ch)) = *reinterpret_cast<const uint4*>(shared.new_k + ch * 8);
+                *reinterpret_cast<uint4*>(v_t + tile_offset<D_PAD>(r, ch)) = *reinterpret_cast<const uint4*>(shared.new_v + ch * 8);
+            }
+            __syncwarp();
+        }
 
         float s[TN / 8][4];
 #pragma unroll
