@@ -451,18 +451,62 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     sync();
     if (!is_last) return;
     __threadfence();
+    // (loads in batches of eight, all in flight together: one after the other, each used at once, a merge of
+    // n splits was 2 n round trips to the L2 at the very end of the kernel)
     for (int item = tid; item < group * d; item += kDecodeThreads) {
         const int r = item / d, col = item % d;
         const int h = kvh * group + r;
         const float* ml = p.partial_ml + ((size_t)t * p.q_heads + h) * p.max_splits * 2;
         const float* po = p.partial_o + ((size_t)t * p.q_heads + h) * p.max_splits * d + col;
         float m = -INFINITY;
-        for (int sp = 0; sp < n_splits; ++sp) m = fmaxf(m, __ldcg(ml + 2 * sp));
         float denom = 0.0f, total_o = 0.0f;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            const float w = exp2f(__ldcg(ml + 2 * sp) - m);
-            denom += w * __ldcg(ml + 2 * sp + 1);
-            total_o += w * __ldcg(po + (size_t)sp * d);
+        if (n_splits <= 8) {
+            // the common case in one round trip: maxima, sums and outputs of all splits together
+            float part_m[8], part_l[8], part_o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool have = j < n_splits;
+                part_m[j] = have ? __ldcg(ml + 2 * j) : -INFINITY;
+                part_l[j] = have ? __ldcg(ml + 2 * j + 1) : 0.0f;
+                part_o[j] = have ? __ldcg(po + (size_t)j * d) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m = fmaxf(m, part_m[j]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j < n_splits) {
+                    const float w = exp2f(part_m[j] - m);
+                    denom += w * part_l[j];
+                    total_o += w * part_o[j];
+                }
+            }
+            p.out[((size_t)t * p.q_heads + h) * d + col] = __float2bfloat16_rn(total_o / denom);
+            continue;
+        }
+        for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
+            float part[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) part[j] = sp0 + j < n_splits ? __ldcg(ml + 2 * (sp0 + j)) : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m = fmaxf(m, part[j]);
+        }
+        for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
+            float part_m[8], part_l[8], part_o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool have = sp0 + j < n_splits;
+                part_m[j] = have ? __ldcg(ml + 2 * (sp0 + j)) : -INFINITY;
+                part_l[j] = have ? __ldcg(ml + 2 * (sp0 + j) + 1) : 0.0f;
+                part_o[j] = have ? __ldcg(po + (size_t)(sp0 + j) * d) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (sp0 + j < n_splits) {                     // (in the order of the splits, as before)
+                    const float w = exp2f(part_m[j] - m);
+                    denom += w * part_l[j];
+                    total_o += w * part_o[j];
+                }
+            }
         }
         p.out[((size_t)t * p.q_heads + h) * d + col] = __float2bfloat16_rn(total_o / denom);
     }
