@@ -186,6 +186,29 @@ __device__ __forceinline__ void short_conv_spans_body(const A* proj, const float
     const int count = span_begin[s + 1] - first;
     const int keep = taps - 1;
     float* st = state + (size_t)span_slot[s] * slot_stride;     // [keep][hidden]
+    if (count == 1 && keep >= 1) {
+        // a decoded token: its three values and the carried taps are asked for together (in the general
+        // form below C is loaded only after the convolution is summed), same arithmetic in the same order
+        const A* p = proj + (size_t)first * row;
+        const A b_raw = p[c], c_raw = p[hidden + c], x_raw = p[2 * hidden + c];
+        float old_taps[kMaxTaps];
+#pragma unroll
+        for (int i = 0; i < kMaxTaps; ++i) old_taps[i] = i < keep ? st[(size_t)i * hidden + c] : 0.0f;
+        const float bx = to_float(b_raw) * to_float(x_raw);
+        float conv = 0.0f;
+#pragma unroll
+        for (int tap = 0; tap < kMaxTaps; ++tap) {
+            if (tap < keep) conv += w[tap] * old_taps[tap];
+            else if (tap == keep) conv += w[tap] * bx;
+        }
+        out[(size_t)first * hidden + c] = from_float<A>(to_float(c_raw) * conv);
+#pragma unroll
+        for (int i = 0; i < kMaxTaps; ++i) {
+            if (i + 1 < keep) st[(size_t)i * hidden + c] = old_taps[i + 1];
+            else if (i + 1 == keep) st[(size_t)i * hidden + c] = bx;
+        }
+        return;
+    }
     // history[i], i < keep: bx of the keep positions before the span; history[keep + j]: bx of span token j
     float history[2 * kMaxTaps];
 #pragma unroll
