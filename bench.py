@@ -197,57 +197,6 @@ def time_decode(loaded, sampler, batch: int, steps: int, warmup: int, prompt_tok
     return ms, launches, context
 
 
-def program_timeline(loaded, batch: int, prompt_tokens: int, seed: int) -> dict:
-    """The decode program (one persistent kernel for a decoding step, CELEG_B200_DECODE_PROGRAM=1) with the
-    time stamps its block 0 takes: per kind of operation, how long block 0 worked and how long it then
-    waited at the grid barrier. Needs a step of at most 16 requests."""
-    import ctypes
-    import torch
-    from celeg_b200 import kernels
-    from celeg_b200.engine.step import StepEntry
-    step_fn = loaded.step
-    vocab = loaded.model.vocab_size
-    generator = torch.Generator().manual_seed(seed)
-    names = [f"p{batch}_{i}" for i in range(batch)]
-    for name in names:
-        prompt = torch.randint(0, vocab, (prompt_tokens,), generator=generator).tolist()
-        for at in range(0, prompt_tokens, step_fn.max_tokens):
-            step_fn.run([StepEntry(name, prompt[at:at + step_fn.max_tokens], [])], auto_begin=True)
-    for _ in range(4):
-        step_fn.run([StepEntry(name, [int(torch.randint(0, vocab, (1,), generator=generator))], [0]) for name in names])
-    torch.cuda.synchronize()
-    programs = [p for p in loaded.model._programs.values() if p is not None]
-    if not programs:
-        return {"phase": "program", "error": f"no program was built: {loaded.model.program_refusal}"}
-    program = programs[-1]
-    n = program.n_ops
-    timeline = torch.zeros(1 + 2 * n, dtype=torch.int64, device="cuda")
-    for _ in range(3):                       # (runs the last step again: the same cache slot, the conv state moves on)
-        timeline.zero_()
-        program.run(timeline)
-    torch.cuda.synchronize()
-    step_fn.raise_on_device_error()
-    stamps = timeline.cpu().tolist()
-    ops = (kernels.ProgramOp * n).from_buffer_copy(bytes(program.ops_device.cpu().numpy().tobytes()))
-    kinds = {0: "embed", 1: "product", 2: "qk_norm_rope", 3: "attention"}
-    table = {}
-    for i in range(n):
-        op = ops[i]
-        label = kinds[op.kind] + (f" n={op.n} k={op.k} sets={op.wt} {'normed' if op.x_source else 'given'} x"
-                                  if op.kind == 1 else "")
-        own = (stamps[1 + 2 * i] - (stamps[2 * i] if i else stamps[0])) / 1e3
-        wait = (stamps[2 + 2 * i] - stamps[1 + 2 * i]) / 1e3 if i + 1 < n else 0.0
-        entry = table.setdefault(label, {"count": 0, "own_us": 0.0, "barrier_us": 0.0})
-        entry["count"] += 1
-        entry["own_us"] = round(entry["own_us"] + own, 1)
-        entry["barrier_us"] = round(entry["barrier_us"] + wait, 1)
-    for name in names:
-        step_fn.end(name)
-    return {"phase": "program", "batch": batch, "operations": n,
-            "step_us": round((stamps[2 * n - 1] - stamps[0]) / 1e3, 1),
-            "stages": program.layout.stages, "stage_bytes": program.layout.stage_bytes, "by_operation": table}
-
-
 def time_prefill(loaded, tokens: int, repeats: int, seed: int, chunk: int = 0):
     """One prompt of ``tokens`` tokens, as one step or (``chunk`` > 0) in portions of that many tokens, each
     portion attending to the cache the earlier ones left; the best of ``repeats`` runs."""
@@ -342,9 +291,6 @@ def run_ours(args) -> dict:
         return {"phase": "decode", "batch": args.batch, "context_tokens": context, "ms_per_step": round(ms, 4),
                 "tokens_per_s": round(args.batch * 1e3 / ms, 1), "gpu_launches": launches,
                 "hbm_frac": round(decode_bytes(raw, args.batch, context) / (ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
-    if args.phase == "program":
-        os.environ["CELEG_B200_DECODE_PROGRAM"] = "1"
-        return program_timeline(loaded, min(args.batch, 16), prompt_tokens, 1)
     if args.phase == "prefill":
         prefill_ms = time_prefill(loaded, args.prefill_tokens, max(1, min(args.steps, 5)), 2, args.chunk)
         return {"phase": "prefill", "tokens": args.prefill_tokens, "chunk": args.chunk or args.prefill_tokens,
@@ -417,7 +363,7 @@ def main() -> int:
                         help="fewer layers of the same sizes, when memory or time needs it")
     parser.add_argument("--page-tokens", type=int, default=16)
     parser.add_argument("--no-cuda-graph", action="store_true")
-    parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "program"],
+    parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
                         help="run one phase only and print a short record (for profilers)")
     parser.add_argument("--batch", type=int, default=8, help="batch of --phase decode")
     parser.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS, help="prompt length of --phase decode")

@@ -21,6 +21,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Callable, Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 from .pages import OutOfPages, PageError, PagePool
 
 NO_PAGE = -1
@@ -81,9 +83,27 @@ class RequestCache:
     tables: List[List[int]] = field(default_factory=list)    # per group: logical page index -> page id / NO_PAGE
     first_live_page: List[int] = field(default_factory=list)  # per group: pages below it were given back
     closed: bool = False
+    # per group: the same table as an int32 array (capacity >= length), kept in step with ``tables`` by the
+    # manager, so that a step copies a request's table into its staging buffer with one memcpy
+    arrays: List[np.ndarray] = field(default_factory=list)
 
     def held_pages(self, group: int) -> List[int]:
         return [page for page in self.tables[group] if page != NO_PAGE]
+
+    def table_array(self, group: int) -> np.ndarray:
+        """The block table of ``group`` as int32, one entry per logical page."""
+        return self.arrays[group][:len(self.tables[group])]
+
+    def _append(self, group: int, pages: Sequence[int]) -> None:
+        table = self.tables[group]
+        start = len(table)
+        table.extend(pages)
+        array = self.arrays[group]
+        if len(table) > array.shape[0]:
+            grown = np.full(max(len(table), 2 * array.shape[0], 16), NO_PAGE, dtype=np.int32)
+            grown[:start] = array[:start]
+            self.arrays[group] = array = grown
+        array[start:len(table)] = pages
 
 
 class CacheManager:
@@ -115,6 +135,10 @@ class CacheManager:
             return self._live[request_id]
         except KeyError:
             raise KeyError(f"request {request_id!r} holds no cache") from None
+
+    def find(self, request_id: Hashable) -> Optional[RequestCache]:
+        """The request's holdings, or None if it holds nothing."""
+        return self._live.get(request_id)
 
     def pages_needed(self, cache: RequestCache, new_total: int) -> List[int]:
         """Per group, how many pages must be added for positions ``[cache.tokens, new_total)``."""
@@ -150,7 +174,8 @@ class CacheManager:
             self._clear_slot(slot)
         cache = RequestCache(request_id=request_id, slot=slot,
                              tables=[[] for _ in self.groups],
-                             first_live_page=[0 for _ in self.groups])
+                             first_live_page=[0 for _ in self.groups],
+                             arrays=[np.full(16, NO_PAGE, dtype=np.int32) for _ in self.groups])
         self._live[request_id] = cache
         return cache
 
@@ -167,7 +192,8 @@ class CacheManager:
         for index, (group, count) in enumerate(zip(self.groups, needed)):
             taken = group.pool.allocate(count)
             assert taken is not None
-            cache.tables[index].extend(taken)
+            if taken:
+                cache._append(index, taken)
 
     def advance(self, cache: RequestCache, new_total: int) -> List[Tuple[int, int]]:
         """Record that positions below ``new_total`` are written; give back pages that no later
@@ -191,6 +217,7 @@ class CacheManager:
                 if page != NO_PAGE:
                     group.pool.release([page])
                     table[logical] = NO_PAGE
+                    cache.arrays[index][logical] = NO_PAGE
                     released.append((index, page))
             cache.first_live_page[index] = max(cache.first_live_page[index], min(first_page, len(table)))
         return released

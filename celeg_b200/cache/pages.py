@@ -25,6 +25,7 @@ class PagePool:
         self.page_tokens = page_tokens
         self._ref = [0] * pages
         self._free: List[int] = list(range(pages - 1, -1, -1))   # pop() yields 0, 1, 2, ...
+        self.high_water = 0                                      # most pages ever out of the pool at once
 
     @property
     def total_pages(self) -> int:
@@ -54,6 +55,7 @@ class PagePool:
         taken = [self._free.pop() for _ in range(count)]
         for page in taken:
             self._ref[page] = 1
+        self.high_water = max(self.high_water, len(self._ref) - len(self._free))
         return taken
 
     def allocate_tokens(self, tokens: int) -> Optional[List[int]]:

@@ -163,6 +163,8 @@ CELEG_API int celeg_attention_decode_fused(void* qkv, int q_row_stride, void* ou
 // is called here.
 #include <mutex>
 
+#include "attention_decode_static.h"
+
 namespace celeg_b200 {
 
 constexpr long long kStaticScratchBytes = 8ll * 1024 * 1024;

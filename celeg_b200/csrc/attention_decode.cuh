@@ -16,9 +16,8 @@
 // Counterpart in celeg: gqa_decode_paged_segment_partial_kernel + gqa_decode_segment_reduce_batch_kernel
 // (src/backend/cuda/kernels/attention_paged.cuh:287-368, 456-487), one block per query head.
 //
-// The work of one (key split, kv head, token) item is a device function, so that the stand-alone
-// kernel (one item per block) and the persistent decode program (items handed to groups of four
-// warps) run the same code.
+// The work of one (key split, kv head, token) item is a device function of a block's four warps; the
+// kernels in attention_decode.cu give one item to each block.
 #pragma once
 #include "common.cuh"
 #include "mma_tiles.cuh"
@@ -160,6 +159,12 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     const int first = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int total = pos + 1 - first;
     const int n_splits = (total + p.chunk - 1) / p.chunk;
+    if (n_splits > p.max_splits) {
+        // the launch has fewer blocks than this token has chunks of keys: its output would never be merged.
+        // Nothing is counted or written for it; the caller reads code 3.
+        if (tid == 0) atomicExch(p.error_flag, 3);
+        return;
+    }
     if (split >= n_splits) return;
     const int begin = first + split * p.chunk;
     const int end = min(begin + p.chunk, pos + 1);

@@ -18,19 +18,26 @@
  *   layer's pages [pages, kv_heads, page_tokens, head_dim] bf16 with page_stride elements between
  *   pages, positions/token_span int32 [tokens], block_table int32 [spans, table_stride],
  *   window 0 = none, chunk keys per split, max_splits >= ceil(longest context / chunk),
- *   error_flag int32 [1] on the device. Returns 0, or a negative code with a message.
+ *   error_flag int32 [1] on the device. Returns 0, or a negative code with a message. A token whose
+ *   keys need more than max_splits chunks gets no output and error_flag receives 3.
  */
 #pragma once
 
 #include <cuda_runtime.h>
 
+#if defined(__GNUC__)
+#define CELEG_B200_PUBLIC __attribute__((visibility("default")))
+#else
+#define CELEG_B200_PUBLIC
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
 
-long long celeg_attention_decode_static_capacity(void);
+CELEG_B200_PUBLIC long long celeg_attention_decode_static_capacity(void);
 
-int celeg_attention_decode_static(const void* q, int q_row_stride, void* out, const void* k_cache,
+CELEG_B200_PUBLIC int celeg_attention_decode_static(const void* q, int q_row_stride, void* out, const void* k_cache,
                                   const void* v_cache, long long page_stride, const int* positions,
                                   const int* token_span, const int* block_table, int table_stride, int tokens,
                                   int q_heads, int kv_heads, int head_dim, int page_tokens, int window,

@@ -12,9 +12,8 @@
 // paired_qk_norm_rope_kernel (src/backend/cuda/kernels/rope_pairing.cu:82-176), scale_kernel,
 // store_kv_paged_batch_kernel (src/backend/cuda/kernels/kv_cache.cuh:215-).
 //
-// The work of one (token, head) unit is a device function shared by the stand-alone kernel and the
-// persistent decode program. The projection is read past the L1 cache: in the persistent program it
-// was written by other blocks of the same launch.
+// The work of one (token, head) unit is a device function, shared by the kernels of qk_norm_rope.cu
+// and the decode attention, which does it for its own token. The projection is read past the L1 cache.
 #pragma once
 #include "common.cuh"
 

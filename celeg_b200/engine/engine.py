@@ -5,6 +5,7 @@ include/celeg/api.h:142-179): submit, step, poll, status, cancel, release, metri
 from __future__ import annotations
 
 import threading
+import time
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple, Union
 
 import torch
@@ -13,15 +14,27 @@ from ..sampling import Sampler, SamplingParams
 from .loading import LoadedModel, load_model
 from .scheduler import (EngineOptions, Metrics, PollResult, RequestOptions, RequestStatus, Scheduler,
                         SchedulerPolicy)
-from .step import StepEntry
+from .step import DeviceCheckError, StepEntry, device_error_text
 
 
 class _Runner:
-    """What the scheduler drives: the step function and the sampler."""
+    """What the scheduler drives: the step function and the sampler. Every launch is bracketed by two
+    timing events and followed by a copy of the kernels' error flag to pinned memory; ``collect`` waits
+    for the launch's last event, reads both, and raises if a kernel flagged an index that the host
+    should have made impossible, so that such a step's logits never become tokens."""
+
+    IN_FLIGHT = 4          # launches whose events and flag copies may be unread at a time (two are)
 
     def __init__(self, loaded: LoadedModel, sampler: Sampler):
         self.loaded = loaded
         self.sampler = sampler
+        self._begin = [torch.cuda.Event(enable_timing=True) for _ in range(self.IN_FLIGHT)]
+        self._end = [torch.cuda.Event(enable_timing=True) for _ in range(self.IN_FLIGHT)]
+        self._flags = torch.zeros(self.IN_FLIGHT, dtype=torch.int32).pin_memory()
+        self._next = 0
+        self._sample_seconds = 0.0
+        self._gpu_seconds = 0.0
+        self._reported = dict(loaded.step.host_seconds)
 
     def reset_request(self, slot: int, seed: int) -> None:
         self.sampler.reset_slot(slot, seed)
@@ -37,12 +50,40 @@ class _Runner:
         """Enqueues a step and its draw without waiting. ``tokens_on_device``: the entries' tokens are
         placeholders, the real ones are what the launch before drew (same rows, same order)."""
         step = self.loaded.step
+        index = self._next
+        self._next = (index + 1) % self.IN_FLIGHT
+        self._begin[index].record()
         logits = step.run(entries, token_source=self.sampler.out if tokens_on_device else None)
+        started = time.perf_counter()
         self.sampler.mark_step(step.last_step)
-        return self.sampler.launch(logits, sample_rows)
+        drawn = self.sampler.launch(logits, sample_rows)
+        self._flags[index:index + 1].copy_(step.error_flag, non_blocking=True)
+        self._end[index].record()
+        self._sample_seconds += time.perf_counter() - started
+        return index, drawn
 
     def collect(self, handle) -> List[int]:
-        return self.sampler.read(handle)
+        index, drawn = handle
+        self._end[index].synchronize()
+        self._gpu_seconds += self._begin[index].elapsed_time(self._end[index]) * 1e-3
+        code = int(self._flags[index])
+        if code:
+            step = self.loaded.step
+            step.error_flag.zero_()
+            raise DeviceCheckError(device_error_text(code))
+        return self.sampler.read(drawn)
+
+    def report_times(self, metrics: Metrics) -> None:
+        """Adds the host seconds spent since the last call, by phase, and the steps' device time."""
+        now = self.loaded.step.host_seconds
+        for name in ("check", "stage", "forward"):
+            setattr(metrics, f"host_{name}_seconds",
+                    getattr(metrics, f"host_{name}_seconds") + now[name] - self._reported[name])
+        self._reported = dict(now)
+        metrics.host_sample_seconds += self._sample_seconds
+        metrics.gpu_seconds += self._gpu_seconds
+        self._sample_seconds = 0.0
+        self._gpu_seconds = 0.0
 
 
 class Engine:

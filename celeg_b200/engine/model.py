@@ -11,7 +11,6 @@ from ..cache.manager import PagedNeed, StateLayout, StateNeed
 from ..cache.storage import CacheStorage
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
 from ..parts import PagedBinding, Runtime, StateBinding, StepContext, part_factory
-from ..parts import program as decode_program
 from ..parts.runtime import ResidualStream
 
 
@@ -62,8 +61,6 @@ class Model:
         self.final_normed = rt.scratch("model.final_normed", spec.hidden_size)
         self.bindings: List[object] = [None] * len(self.order)
         self._rebind = len({entry.layer for entry in self.order}) != len(self.order)
-        self._programs: Dict[tuple, Optional[decode_program.DecodeProgram]] = {}
-        self.program_refusal: Optional[str] = None       # why the last program could not be built, if so
         self._plan_caches()
 
     # ------------------------------------------------------------------ caches
@@ -122,50 +119,6 @@ class Model:
                 if self.bindings[position] is not None:
                     self.layers[entry.layer].mixer.bind_cache(self.bindings[position])
 
-    # ---------------------------------------------------------------- programs
-    def _program_for(self, step: StepContext, logit_rows: torch.Tensor, n_logits: int,
-                     logits: torch.Tensor) -> Optional[decode_program.DecodeProgram]:
-        """The persistent-kernel form of this step, if it is a pure decoding step of few requests on
-        the bfloat16 path and every part can emit its operations; built once per shape of step."""
-        rt = self.rt
-        if not (rt.act_dtype == torch.bfloat16 and step.max_span == 1 and step.spans == step.tokens
-                and 0 < step.tokens <= decode_program.MAX_ROWS and 0 < n_logits <= decode_program.MAX_ROWS
-                and decode_program.enabled()):
-            return None
-        key = (step.tokens, n_logits, step.logits_of_all_rows, step.context_bucket, logits.data_ptr(),
-               logit_rows.data_ptr(), tuple((t.data_ptr(), t.stride(0)) for t in step.block_tables))
-        if key in self._programs:
-            return self._programs[key]
-        built: Optional[decode_program.DecodeProgram] = None
-        try:
-            builder = decode_program.ProgramBuilder(rt, step.tokens, self.residual, step.error_flag)
-            builder.embed(self.embedding, step.token_ids, self.spec.embedding_multiplier)
-            for position, entry in enumerate(self.order):
-                layer = self.layers[entry.layer]
-                if self._rebind and self.bindings[position] is not None:
-                    layer.mixer.bind_cache(self.bindings[position])
-                if not hasattr(layer.block, "emit_decode"):
-                    raise decode_program.ProgramUnsupported(f"{type(layer.block).__name__} cannot emit operations")
-                layer.block.emit_decode(builder, step)
-            prologue = self.final_norm.as_prologue() if hasattr(self.final_norm, "as_prologue") else None
-            if prologue is None:
-                raise decode_program.ProgramUnsupported(f"{type(self.final_norm).__name__} cannot be a prologue")
-            rows = decode_program.NormedRows(weight=prologue[0], eps=prologue[1],
-                                             gather=None if step.logits_of_all_rows else logit_rows)
-            builder.product(rows, self.head, logits, epilogue=decode_program.STORE_F32, rows=n_logits,
-                            out_scale=self.spec.logits_multiplier)
-            built = builder.build()
-        except decode_program.ProgramUnsupported as refusal:
-            self.program_refusal = str(refusal)
-        self._programs[key] = built
-        return built
-
-    def reset_programs(self) -> None:
-        """After a device error: the programs' barrier counters may be left mid-count."""
-        for built in self._programs.values():
-            if built is not None:
-                built.reset()
-
     # ----------------------------------------------------------------- forward
     def forward(self, step: StepContext, logit_rows: torch.Tensor, n_logits: int, logits: torch.Tensor) -> None:
         """Run the step's tokens through every position of the run order and write the logits
@@ -173,10 +126,6 @@ class Model:
         rt = self.rt
         stream = self.stream
         stream.begin()
-        built = self._program_for(step, logit_rows, n_logits, logits)
-        if built is not None:
-            built.run()
-            return
         blocks = [self.layers[entry.layer].block for entry in self.order]
         firsts = [block.first_norm(step) if hasattr(block, "first_norm") else None for block in blocks]
         head_norm = (self.final_norm if n_logits > 0 and step.logits_of_all_rows

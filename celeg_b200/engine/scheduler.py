@@ -116,6 +116,36 @@ class Metrics:
     ttft_count: int = 0
     itl_seconds_sum: float = 0.0
     itl_count: int = 0
+    # every sample as well, for percentiles (the first ``SAMPLE_LIMIT`` of each)
+    ttft_seconds: List[float] = field(default_factory=list)
+    itl_seconds: List[float] = field(default_factory=list)
+    active_requests: int = 0
+    queued_requests: int = 0
+    # cache pages out of the pools (summed over the paged groups): now, in all, and the most at any time
+    pages_used: int = 0
+    pages_total: int = 0
+    pages_high_water: int = 0
+    # Where a step's time goes on the host, summed over steps (celeg reports host_prepare_ms,
+    # gpu_execute_ms and host_commit_ms per packed step: src/backend/cuda/packed/execution.cu:200-223):
+    # plan = cancellations, admission and the batch plan; launch = checking, staging and enqueueing the
+    # step and its draw (check / stage / forward / sample are its parts, when the runner reports them);
+    # wait = blocked until the step's tokens are on the host; commit = accepting tokens, finishing, freeing.
+    host_plan_seconds: float = 0.0
+    host_launch_seconds: float = 0.0
+    host_check_seconds: float = 0.0
+    host_stage_seconds: float = 0.0
+    host_forward_seconds: float = 0.0
+    host_sample_seconds: float = 0.0
+    host_wait_seconds: float = 0.0
+    host_commit_seconds: float = 0.0
+    gpu_seconds: float = 0.0          # device time of the steps, from events around each (0 if the runner has none)
+
+    SAMPLE_LIMIT = 1 << 20
+
+    def host_ms_per_step(self) -> Dict[str, float]:
+        steps = max(1, self.steps)
+        return {name: round(1e3 * getattr(self, f"host_{name}_seconds") / steps, 4)
+                for name in ("plan", "launch", "check", "stage", "forward", "sample", "wait", "commit")}
 
 
 @dataclass
@@ -230,11 +260,15 @@ class Scheduler:
         input tokens from the device, where this step's draw left them, so the GPU does not idle
         while the host reads tokens, decides and plans. A request that did end on this step's token
         has then one more position computed in vain; its token of that step is dropped."""
+        metrics = self.metrics
+        clock = time.perf_counter
         if self._inflight is None:
+            started = clock()
             self._honour_cancellations()
             if not self._hold_admission:
                 self._admit()
             plan = self.plan()
+            metrics.host_plan_seconds += clock() - started
             if not plan.entries:
                 self._hold_admission = False
                 if self.live and self._break_deadlock():
@@ -245,13 +279,28 @@ class Scheduler:
                 return True                                   # the launch failed; its requests have failed
         plan, handle = self._inflight
         self._inflight = None
-        if self._may_run_ahead(plan):
+        started = clock()
+        ahead = self._may_run_ahead(plan)
+        metrics.host_plan_seconds += clock() - started
+        if ahead:
             self._launch(self._plan_after(plan), tokens_on_device=True)
         progressed = self._collect(plan, handle)
+        started = clock()
         self._hold_admission = False
         self._honour_cancellations()
         self._admit()
+        self._count_holdings()
+        metrics.host_plan_seconds += clock() - started
         return progressed
+
+    def _count_holdings(self) -> None:
+        metrics = self.metrics
+        metrics.active_requests = len(self.live)
+        metrics.queued_requests = len(self.queue)
+        pools = [group.pool for group in self.manager.groups]
+        metrics.pages_used = sum(pool.used_pages for pool in pools)
+        metrics.pages_total = sum(pool.total_pages for pool in pools)
+        metrics.pages_high_water = sum(pool.high_water for pool in pools)
 
     # --------------------------------------------------------------- admission
     def _priority_key(self, request_id: int):
@@ -336,6 +385,7 @@ class Scheduler:
                              want=[len(p.tokens) - 1] if p.samples else [])
                    for p in plan.entries]
         sample_rows = [(p.request.cache.slot, p.request.options.generation) for p in plan.entries if p.samples]
+        started = time.perf_counter()
         try:
             if self._runs_ahead:
                 handle = self.runner.launch(entries, sample_rows, tokens_on_device)
@@ -344,6 +394,8 @@ class Scheduler:
         except Exception as exc:
             self._fail(plan, exc)
             return False
+        finally:
+            self.metrics.host_launch_seconds += time.perf_counter() - started
         self._inflight = (plan, handle)
         return True
 
@@ -375,11 +427,24 @@ class Scheduler:
 
     def _collect(self, plan: Plan, handle) -> bool:
         """Waits for the plan's tokens and accepts them."""
+        started = time.perf_counter()
         try:
             tokens = self.runner.collect(handle) if self._runs_ahead else handle
         except Exception as exc:
             self._fail(plan, exc)
             return True
+        finally:
+            waited = time.perf_counter()
+            self.metrics.host_wait_seconds += waited - started
+        try:
+            return self._commit(plan, tokens)
+        finally:
+            self.metrics.host_commit_seconds += time.perf_counter() - waited
+
+    def _commit(self, plan: Plan, tokens) -> bool:
+        report = getattr(self.runner, "report_times", None)
+        if report is not None:
+            report(self.metrics)
         now = time.monotonic()
         self.metrics.steps += 1
         self.metrics.skipped_for_pages += len(plan.skipped_for_pages)
@@ -411,9 +476,13 @@ class Scheduler:
             request.first_token_at = now
             self.metrics.ttft_seconds_sum += now - request.submitted_at
             self.metrics.ttft_count += 1
+            if len(self.metrics.ttft_seconds) < Metrics.SAMPLE_LIMIT:
+                self.metrics.ttft_seconds.append(now - request.submitted_at)
         else:
             self.metrics.itl_seconds_sum += now - request.last_token_at
             self.metrics.itl_count += 1
+            if len(self.metrics.itl_seconds) < Metrics.SAMPLE_LIMIT:
+                self.metrics.itl_seconds.append(now - request.last_token_at)
         request.last_token_at = now
         if token in request.eos_tokens or len(request.generated) >= request.options.max_new_tokens:
             self._finish(request, RequestStatus.FINISHED)

@@ -9,6 +9,7 @@ own position and page table, and here they are one pass.
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -68,8 +69,9 @@ class StepFunction:
         self._ring = [torch.empty(capacity, dtype=torch.int32).pin_memory() for _ in range(4)]
         self._ring_events: List[Optional[torch.cuda.Event]] = [None] * len(self._ring)
         self._ring_next = 0
+        self._ring_np = [buffer.numpy() for buffer in self._ring]
         self._host = self._ring[0]
-        self._host_np = self._host.numpy()
+        self._host_np = self._ring_np[0]
         self._dev = torch.zeros(capacity, dtype=torch.int32, device=rt.device)
         self.error_flag = rt.error_flag
         self._decode_logits = torch.empty((max_spans, model.vocab_size), dtype=torch.float32, device=rt.device)
@@ -82,6 +84,9 @@ class StepFunction:
         self.steps_run = 0
         self.kernel_steps_graphed = 0
         self.last_step: Optional[StepContext] = None
+        # host seconds spent in run(), by phase: checking the batch and reserving pages, filling and
+        # sending the step's metadata, enqueueing the model's kernels (or replaying their graph)
+        self.host_seconds = {"check": 0.0, "stage": 0.0, "forward": 0.0}
 
     # ------------------------------------------------------------------ requests
     def begin(self, request_id: Hashable):
@@ -98,6 +103,7 @@ class StepFunction:
             token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Returns float32 logits [wanted, vocab] in the order of the entries and of ``want``.
         The tensor is a view of a buffer that the next call overwrites."""
+        started = time.perf_counter()
         vocab = self.model.vocab_size
         if not entries:
             return self._decode_logits[:0]
@@ -107,29 +113,37 @@ class StepFunction:
         total = 0
         wanted = 0
         caches = []
+        find = self.manager.find
         for entry in entries:
-            if entry.request_id in seen_ids:
-                raise StepInputError(f"request {entry.request_id!r} appears twice in one step")
-            seen_ids.add(entry.request_id)
-            count = len(entry.tokens)
-            if count == 0:
-                raise StepInputError(f"request {entry.request_id!r} brings no tokens")
-            for token in entry.tokens:
-                if not 0 <= int(token) < vocab:
-                    raise StepInputError(f"request {entry.request_id!r}: token id {token} is outside the "
-                                         f"vocabulary of {vocab}")
+            request_id = entry.request_id
+            if request_id in seen_ids:
+                raise StepInputError(f"request {request_id!r} appears twice in one step")
+            seen_ids.add(request_id)
+            tokens = entry.tokens
+            count = len(tokens)
+            if count == 1:
+                low = high = int(tokens[0])
+            elif count == 0:
+                raise StepInputError(f"request {request_id!r} brings no tokens")
+            else:
+                if not isinstance(tokens, np.ndarray):
+                    tokens = entry.tokens = np.asarray(tokens, dtype=np.int64)
+                low, high = int(tokens.min()), int(tokens.max())
+            if low < 0 or high >= vocab:
+                bad = low if low < 0 else high
+                raise StepInputError(f"request {request_id!r}: token id {bad} is outside the "
+                                     f"vocabulary of {vocab}")
             for place in entry.want:
                 if not 0 <= int(place) < count:
-                    raise StepInputError(f"request {entry.request_id!r}: wanted place {place} is outside its "
+                    raise StepInputError(f"request {request_id!r}: wanted place {place} is outside its "
                                          f"{count} tokens")
-            try:
-                cache = self.manager.get(entry.request_id)
-            except KeyError:
+            cache = find(request_id)
+            if cache is None:
                 if not auto_begin:
-                    raise StepInputError(f"request {entry.request_id!r} was not begun") from None
-                cache = self.manager.open(entry.request_id)
+                    raise StepInputError(f"request {request_id!r} was not begun") from None
+                cache = self.manager.open(request_id)
             if cache.tokens + count > self.max_context:
-                raise StepInputError(f"request {entry.request_id!r} would reach {cache.tokens + count} positions, "
+                raise StepInputError(f"request {request_id!r} would reach {cache.tokens + count} positions, "
                                      f"the context limit is {self.max_context}")
             caches.append(cache)
             total += count
@@ -162,7 +176,8 @@ class StepFunction:
         if self._ring_events[slot] is not None:
             self._ring_events[slot].synchronize()
         self._host = self._ring[slot]
-        self._host_np = self._host.numpy()
+        self._host_np = self._ring_np[slot]
+        checked = time.perf_counter()
         step, logit_rows, n_words = self._stage(entries, caches, total, spans, wanted, stride, max_ctx)
         self._dev[:n_words].copy_(self._host[:n_words], non_blocking=True)
         if token_source is not None:
@@ -175,6 +190,7 @@ class StepFunction:
         event.record()
         self._ring_events[slot] = event
         self.last_step = step
+        staged = time.perf_counter()
 
         if wanted <= self.max_spans:
             logits = self._decode_logits
@@ -191,6 +207,10 @@ class StepFunction:
         for entry, cache in zip(entries, caches):
             self.manager.advance(cache, cache.tokens + len(entry.tokens))
         self.steps_run += 1
+        done = time.perf_counter()
+        self.host_seconds["check"] += checked - started
+        self.host_seconds["stage"] += staged - checked
+        self.host_seconds["forward"] += done - staged
         return logits[:wanted]
 
     def _prompt_graph_key(self, entries, total: int, wanted: int):
@@ -278,15 +298,15 @@ class StepFunction:
                 grid = tables[g]
                 grid.fill(NO_PAGE)
                 for index, cache in enumerate(caches):
-                    table = cache.tables[g]
-                    used = min(len(table), stride)
+                    table = cache.table_array(g)
+                    used = min(table.shape[0], stride)
                     grid[index, :used] = table[:used]
             lengths = [1] * spans
             row = spans
         else:
             for index, (entry, cache) in enumerate(zip(entries, caches)):
                 count = len(entry.tokens)
-                token_ids[row:row + count] = np.asarray(entry.tokens, dtype=np.int32)
+                token_ids[row:row + count] = entry.tokens
                 positions[row:row + count] = np.arange(cache.tokens, cache.tokens + count, dtype=np.int32)
                 token_span[row:row + count] = index
                 span_begin[index] = row
@@ -295,8 +315,8 @@ class StepFunction:
                     logit_rows_host[out] = row + int(place)
                     out += 1
                 for g in range(self.groups):
-                    table = cache.tables[g]
-                    used = min(len(table), stride)
+                    table = cache.table_array(g)
+                    used = min(table.shape[0], stride)
                     tables[g][index, :used] = table[:used]
                     tables[g][index, used:] = NO_PAGE
                 lengths.append(count)
@@ -325,7 +345,10 @@ class StepFunction:
         code = int(self.error_flag.item())
         if code:
             self.error_flag.zero_()
-            self.model.reset_programs()
-            raise DeviceCheckError(f"a kernel reported error code {code} (1: cache write without a page, "
-                                   f"2: attention read without a page, 11-24: a bounded wait of the tcgen05 "
-                                   f"product ran out, 31-33: a bounded wait of the decode program ran out)")
+            raise DeviceCheckError(device_error_text(code))
+
+
+def device_error_text(code: int) -> str:
+    return (f"a kernel reported error code {code} (1: cache write without a page, 2: attention read without "
+            f"a page, 3: more key splits than the launch has blocks for, 11-24 and 61-65: a bounded wait of "
+            f"a tcgen05 kernel ran out)")

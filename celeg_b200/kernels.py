@@ -79,9 +79,6 @@ _SIGNATURES = {
     "celeg_sample_greedy": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p],
     "celeg_mark_seen": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
-    "celeg_decode_program_prepare": [c_void_p, c_int, c_void_p, c_int, c_int],
-    "celeg_decode_program_encode_maps": [c_void_p, c_int, c_void_p, c_void_p],
-    "celeg_decode_program_run": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
 
@@ -458,85 +455,3 @@ def mark_seen(seen: torch.Tensor, tokens: torch.Tensor, token_span: torch.Tensor
               count: int) -> None:
     _check(library().celeg_mark_seen(_ptr(seen), seen.shape[1], _ptr(tokens), _ptr(token_span), _ptr(span_slot),
                                      count, _stream()))
-
-
-# ------------------------------------------------------------------------- decode programs
-OP_EMBED, OP_GEMV, OP_QK_NORM_ROPE, OP_ATTENTION = 0, 1, 2, 3
-X_GLOBAL, X_NORM = 0, 1
-
-
-class ProgramOp(ctypes.Structure):
-    """One operation of a decode program; mirrors ``ProgramOp`` of csrc/decode_program.cuh field by
-    field (the library reports the size of its struct and :func:`decode_program_prepare` compares)."""
-    _fields_ = (
-        [(name, c_void_p) for name in (
-            "w", "x", "y", "residual", "norm_weight", "gather", "conv_w", "state", "span_slot", "token_ids",
-            "q_weight", "k_weight", "inv_freq", "positions", "token_span", "block_table", "k_cache", "v_cache",
-            "partial_o", "partial_ml", "counters")]
-        + [(name, c_longlong) for name in ("slot_stride", "page_stride", "tile_offset")]
-        + [(name, c_int) for name in (
-            "kind", "rows", "n", "k", "wt", "epilogue", "x_source", "kc", "ldw", "ldx", "ldy", "ld_residual", "taps",
-            "table_stride", "q_heads", "kv_heads", "head_dim", "rotary_dim", "page_tokens", "window", "chunk",
-            "max_splits", "store_kv", "q_row_stride", "vocab", "x_rows")]
-        + [(name, c_float) for name in ("eps", "out_scale", "scale", "multiplier")]
-    )
-
-
-class ProgramLayout(ctypes.Structure):
-    """Tiling and shared-memory layout chosen by the library for a program."""
-    _fields_ = [(name, c_int) for name in (
-        "row_tiles", "stages", "stage_bytes", "x_bytes", "partial_bytes", "attention_groups",
-        "attention_item_bytes", "smem_bytes", "grid")] + [("reserved", c_int * 3)]
-
-
-class ProgramUnsupported(KernelLibraryError):
-    """The operations cannot run as one persistent kernel; the caller runs them one by one."""
-
-
-def decode_program_prepare(ops, sms: int = 0, smem_limit: int = 0):
-    """Checks a list of :class:`ProgramOp`, lets the library choose the tiling, and returns
-    (packed operations as bytes, layout). ``sms``/``smem_limit`` 0 = those of the current device."""
-    lib = library()
-    for name, cls in (("celeg_decode_program_op_bytes", ProgramOp), ("celeg_decode_program_layout_bytes", ProgramLayout)):
-        fn = getattr(lib, name)
-        fn.restype = c_int
-        fn.argtypes = []
-        if fn() != ctypes.sizeof(cls):
-            raise KernelLibraryError(f"{cls.__name__} has {ctypes.sizeof(cls)} bytes here and {fn()} in the library")
-    array = (ProgramOp * len(ops))(*ops)
-    layout = ProgramLayout()
-    code = lib.celeg_decode_program_prepare(ctypes.addressof(array), len(ops), ctypes.addressof(layout), sms, smem_limit)
-    if code != 0:
-        raise ProgramUnsupported(lib.celeg_last_error().decode("utf-8", "replace"))
-    return bytes(array), layout
-
-
-def decode_program_maps(packed_ops: bytes, n_ops: int, layout: ProgramLayout) -> bytes:
-    """The TMA tensor maps of a prepared program (two of 128 bytes per operation), encoded by the
-    driver for the device pointers in the operations; to be copied to the device."""
-    lib = library()
-    ops = ctypes.create_string_buffer(packed_ops, len(packed_ops))
-    maps = ctypes.create_string_buffer(2 * n_ops * 128)
-    code = lib.celeg_decode_program_encode_maps(ctypes.addressof(ops), n_ops, ctypes.addressof(layout),
-                                                ctypes.addressof(maps))
-    if code != 0:
-        raise ProgramUnsupported(lib.celeg_last_error().decode("utf-8", "replace"))
-    return maps.raw
-
-
-def decode_program_run(ops_device: torch.Tensor, n_ops: int, layout: ProgramLayout, maps_device: torch.Tensor,
-                       barriers: torch.Tensor, error_flag: torch.Tensor,
-                       timeline: Optional[torch.Tensor] = None) -> None:
-    """One cooperative launch of the persistent kernel over prepared operations on the device.
-    ``timeline``: int64 [1 + 2 n_ops] that receives block 0's time stamps (nanoseconds): start, then for
-    each operation when its own share was done and when every block's was."""
-    if timeline is not None:
-        _need(timeline, torch.int64, "timeline")
-        if timeline.numel() < 1 + 2 * n_ops:
-            raise KernelLibraryError(f"the timeline of {n_ops} operations needs {1 + 2 * n_ops} words")
-    _need(barriers, torch.int32, "barriers")
-    if barriers.numel() < n_ops + 1:
-        raise KernelLibraryError(f"a program of {n_ops} operations needs {n_ops + 1} barrier counters")
-    _check(library().celeg_decode_program_run(_ptr(ops_device), n_ops, ctypes.addressof(layout), _ptr(maps_device),
-                                              _ptr(barriers),
-                                              _ptr(error_flag), _ptr(timeline), _stream()))

@@ -7,7 +7,6 @@ stream. Interface:
                                      stream.after_layer is the norm that will read the stream after this
                                      layer if its reader takes a split norm (see ResidualStream), else None
     first_norm(step)                 optional: the norm that reads the stream first, under the same condition
-    emit_decode(builder, step)       optional: the same as operations of a decode program
 
 A part's ``forward(x, out, step)`` gets the normed activations and a buffer for its output; the
 arrangement hands that buffer to the residual stream, which adds it inside the next norm kernel.
@@ -16,7 +15,6 @@ from __future__ import annotations
 
 from typing import Mapping
 
-from .program import NormedRows, ProgramUnsupported
 from .registry import register_part
 from .runtime import ResidualStream, Runtime, StepContext
 
@@ -57,15 +55,3 @@ class PreNormResidual:
         between = self.ffn_norm if takes is not None and takes(step) else None
         self._sublayer(self.mixer_norm, self.mixer, self.delta_a, between, stream, step)
         self._sublayer(self.ffn_norm, self.ffn, self.delta_b, after, stream, step)
-
-    @staticmethod
-    def _emit_sublayer(norm, part, builder, step: StepContext) -> None:
-        prologue = norm.as_prologue() if hasattr(norm, "as_prologue") else None
-        if prologue is None or not hasattr(part, "emit_decode"):
-            raise ProgramUnsupported(f"{type(norm).__name__} + {type(part).__name__} cannot be part of a decode program")
-        part.emit_decode(builder, NormedRows(weight=prologue[0], eps=prologue[1]), step)
-
-    def emit_decode(self, builder, step: StepContext) -> None:
-        self._emit_sublayer(self.mixer_norm, self.mixer, builder, step)
-        if self.ffn is not None:
-            self._emit_sublayer(self.ffn_norm, self.ffn, builder, step)

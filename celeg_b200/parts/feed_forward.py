@@ -3,7 +3,6 @@
     FeedForward(params, weights, parts, rt)
     forward(x, out, step)     x: normed activations [T, hidden]; writes the output to out
     takes_split_norm(step)    optional, as for mixers
-    emit_decode(builder, x, step)   optional: the same as operations of a decode program (parts/program.py)
 """
 from __future__ import annotations
 
@@ -12,7 +11,6 @@ from typing import Mapping
 import torch
 
 from .. import kernels
-from . import program
 from .registry import register_part
 from .runtime import Runtime, StepContext
 
@@ -41,7 +39,3 @@ class SwiGluFeedForward:
         rt, t = self.rt, step.tokens
         rt.linear_swiglu(x, self.w_gate_up, self.gate_up, self.activated, t, self.inner)
         rt.linear(self.activated, self.w_down, out, t)
-
-    def emit_decode(self, builder, x, step: StepContext) -> None:
-        builder.product(x, self.w_gate_up, self.activated, epilogue=program.SWIGLU)
-        builder.product(self.activated, self.w_down, add_to_residual=True)

@@ -11,8 +11,6 @@
     ends_with_product = True                optional: the last thing forward() does to ``out`` is
                                             rt.linear(..., out, ...); the runtime may then add that product
                                             to the residual stream itself and leave ``out`` unwritten
-    emit_decode(builder, x, step)           optional: the same as operations of a decode program
-                                            (parts/program.py) for steps of one token per request
 
 A mixer does not know which model or layer it is in; everything it needs about the step is
 in the StepContext, everything about its cache in the binding.
@@ -26,7 +24,6 @@ import torch
 
 from .. import kernels
 from ..cache.manager import PagedNeed, StateNeed
-from . import program
 from .registry import register_part
 from .runtime import Runtime, StepContext
 
@@ -50,6 +47,31 @@ class StateBinding:
     state: torch.Tensor
     slot_stride: int
     owner: bool = True
+
+
+def decode_split(tokens: int, kv_heads: int, context_bucket: int, window: Optional[int], max_context: int):
+    """How the decode attention splits the keys of a step of ``tokens`` requests: (chunk, max_splits,
+    cap_splits). Every request's keys are cut into chunks of ``chunk`` (a multiple of 64); ``max_splits`` chunks
+    cover the step's context bucket and ``cap_splits`` >= max_splits is what the scratch is sized for, a
+    number that depends only on the longest context the runtime allows.
+
+    Few requests: enough splits for about one and a half blocks per SM. Many requests or long contexts:
+    chunks of 1,024 keys, which measured best on B200 from 4 k to 32 k keys at 1 to 64 requests (blocks of
+    4,096 keys leave a tail of idle SMs, blocks of 256 pay their start and their merge too often)."""
+    bucket = context_bucket
+    if window:
+        bucket = min(bucket, 1 << max(8, (window - 1).bit_length()))
+    longest = max_context if not window else min(max_context, 2 * window)
+    cap_splits = max(32, -(-longest // 1024) * 2)
+    blocks_wanted = 224
+    splits = max(1, min(bucket // 128, -(-blocks_wanted // max(1, tokens * kv_heads)), cap_splits))
+    chunk = min(-(-bucket // splits), 1024)
+    chunk = (chunk + 63) // 64 * 64
+    max_splits = -(-bucket // chunk)
+    if max_splits > cap_splits:             # a bucket beyond the longest context: cannot come from a valid step
+        raise ValueError(f"a context bucket of {context_bucket} keys needs {max_splits} splits, the scratch holds "
+                         f"{cap_splits} (longest context {max_context})")
+    return chunk, max_splits, cap_splits
 
 
 @register_part("mixer", "attention")
@@ -147,44 +169,13 @@ class AttentionMixer:
         """One query token per request: how the keys are split so that few requests still fill the GPU,
         and the scratch of the split (chunk, max_splits, partial outputs, maxima and sums, counters)."""
         rt = self.rt
-        bucket = step.context_bucket
-        if self.window:
-            bucket = min(bucket, 1 << max(8, (self.window - 1).bit_length()))
-        # Few requests: enough splits for about one and a half blocks per SM. Many requests or long contexts:
-        # chunks of 1,024 keys, which measured best on B200 from 4 k to 32 k keys at 1 to 64 requests (blocks
-        # of 4,096 keys leave a tail of idle SMs, blocks of 256 pay their start and their merge too often).
-        blocks_wanted = 224
-        splits = max(1, min(bucket // 128, -(-blocks_wanted // (step.tokens * self.kv_heads))))
-        chunk = min(-(-bucket // splits), 1024)
-        chunk = (chunk + 63) // 64 * 64
-        max_splits = -(-bucket // chunk)
-        longest = rt.max_context if not self.window else min(rt.max_context, 2 * self.window)
-        cap_splits = max(32, -(-longest // 1024) * 2)
-        assert max_splits <= cap_splits, (max_splits, cap_splits)
+        chunk, max_splits, cap_splits = decode_split(step.tokens, self.kv_heads, step.context_bucket, self.window,
+                                                     rt.max_context)
         rows = rt.max_requests * self.heads * cap_splits
         partial_o = rt.flat_scratch("attention.partial_o", rows * self.head_dim, torch.float32)
         partial_ml = rt.flat_scratch("attention.partial_ml", rows * 2, torch.float32)
         counters = rt.flat_scratch("attention.counters", rt.max_requests * self.kv_heads, torch.int32, zero=True)
         return chunk, max_splits, partial_o, partial_ml, counters
-
-    def emit_decode(self, builder, x, step: StepContext) -> None:
-        b = self.binding
-        fused = self.position.fused() if self.position is not None else {"inv_freq": None, "rotary_dim": 0}
-        if fused is None:
-            raise program.ProgramUnsupported("a position encoding without tables for the fused q/k kernel")
-        if step.tokens > self.rt.max_requests or not kernels.attention_decode_supported(
-                self.heads, self.kv_heads, self.head_dim, self.rt.act_dtype):
-            raise program.ProgramUnsupported("these attention sizes go to the general kernel")
-        table = step.block_tables[b.group]
-        builder.product(x, self.w_qkv, self.qkv)
-        builder.qk_norm_rope(self.qkv, self.q_norm, self.k_norm, fused["inv_freq"], fused["rotary_dim"],
-                             step.positions, step.token_span, table, b.k, b.v, self.heads, self.stored_kv_heads,
-                             self.head_dim, b.page_tokens, self.eps, b.owner and not self.reads_only)
-        chunk, max_splits, partial_o, partial_ml, counters = self._decode_split(step)
-        builder.attention(self.qkv, self.attended, b.k, b.v, step.positions, step.token_span, table, self.heads,
-                          self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale, chunk, max_splits,
-                          partial_o, partial_ml, counters)
-        builder.product(self.attended, self.w_out, add_to_residual=True)
 
     def _decodes(self, step: StepContext) -> bool:
         """Whether the step goes to the split-key decode kernel (one query token per request)."""
@@ -258,8 +249,3 @@ class ShortConvMixer:
                                self.gated, step.token_span, step.span_begin, step.span_slot, t, step.spans,
                                self.hidden, self.taps, step.max_span)
         rt.linear(self.gated, self.w_out, out, t)
-
-    def emit_decode(self, builder, x, step: StepContext) -> None:
-        builder.product(x, self.w_in, self.gated, epilogue=program.CONV, conv_kernel=self.kernel, taps=self.taps,
-                        state=self.binding.state, slot_stride=self.binding.slot_stride, span_slot=step.span_slot)
-        builder.product(self.gated, self.w_out, add_to_residual=True)

@@ -6,8 +6,8 @@
         delta:    activation-type [T, width] or None
         out:      activation-type [n_rows, width]
         rows:     int32 row list to gather (then the residual is left untouched)
-    as_prologue() -> (weight, eps) or None      optional: a plain RMSNorm that a product of a decode
-                                                program applies to its own operand
+    as_prologue() -> (weight, eps) or None      optional: a plain RMSNorm, which the runtime may split
+                                                between the products before and after it
 """
 from __future__ import annotations
 

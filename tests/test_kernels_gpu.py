@@ -425,6 +425,36 @@ def test_attention_decode_split_keys(heads, kv_heads, head_dim, page_tokens, win
         close(out, want, dtype)
 
 
+def test_attention_decode_reports_too_few_splits():
+    """A launch with fewer key splits than a token's context needs cannot merge that token's output: the
+    kernel says so through the error flag (code 3), writes nothing for the token, leaves its counters at
+    zero and serves the other tokens as usual."""
+    from celeg_b200 import kernels
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(18)
+    heads, kv_heads, head_dim, page_tokens, chunk = 4, 2, 64, 16, 64
+    lengths = [40, 300]
+    k_cache, v_cache, table, ks, vs = paged_setup(rng, dtype, lengths, kv_heads, head_dim, page_tokens, 40)
+    tokens = len(lengths)
+    q = rounded(rng.normal(size=(tokens, heads, head_dim)), dtype)
+    positions = np.array([n - 1 for n in lengths], dtype=np.int32)
+    max_splits = 2                                   # 300 keys in chunks of 64 need five
+    partial_o = torch.empty(tokens * heads * max_splits * head_dim, dtype=torch.float32, device="cuda")
+    partial_ml = torch.empty(tokens * heads * max_splits * 2, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(tokens * kv_heads, dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.full((tokens, heads * head_dim), 7.0, dtype=dtype, device="cuda")
+    scale = head_dim ** -0.5
+    kernels.attention_decode(dev(q.reshape(tokens, -1), dtype), heads * head_dim, out, k_cache, v_cache,
+                             dev(positions), dev(np.arange(tokens, dtype=np.int32)), dev(table), tokens, heads,
+                             kv_heads, head_dim, page_tokens, None, scale, chunk, max_splits, partial_o, partial_ml,
+                             counters, flag)
+    assert int(flag.item()) == 3
+    assert int(counters.abs().sum().item()) == 0
+    assert bool((out[1].float() == 7.0).all())
+    close(out[:1], attention_reference(q[0], ks[0], vs[0], 39, scale, None).reshape(1, -1), dtype)
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,window,chunk,normed,rotary", [
     (4, 2, 16, 16, None, 64, True, 16), (8, 2, 64, 16, None, 128, True, 64), (6, 3, 80, 16, 37, 64, True, 80),
     (2, 1, 128, 32, None, 512, False, 128), (5, 5, 48, 8, None, 64, True, 48), (32, 8, 64, 16, None, 256, True, 64),
