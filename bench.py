@@ -34,6 +34,27 @@ LFM2_1P2B = {
     "layer_types": ["full_attention" if i in (2, 5, 8, 10, 12, 14) else "conv" for i in range(16)],
     "bos_token_id": 1, "eos_token_id": 7, "pad_token_id": 0,
 }
+
+def _lfm2_sizes(hidden: int, heads: int, inner: int, context: int) -> dict:
+    raw = dict(LFM2_1P2B)
+    raw.update({"hidden_size": hidden, "num_attention_heads": heads, "intermediate_size": inner,
+                "max_position_embeddings": context})
+    return raw
+
+
+# The two scheduler workloads: many live requests through Engine.submit / step / poll.
+WORKLOADS = {
+    # 64 requests, prompts uniform in [256, 16,384], context 32,768, portions of prompts beside decoded tokens,
+    # 256 new tokens each, greedy: the load on the scheduler, the page pool and long-context decode attention
+    "lfm2-700m": {"config": _lfm2_sizes(1536, 24, 6912, 32768), "requests": 64, "prompt_min": 256,
+                  "prompt_max": 16384, "context": 32768, "new_tokens": 256, "temperature": 0.0,
+                  "max_batched_tokens": 2048, "prefill_chunk_tokens": 2048},
+    # 256 requests of 128 prompt tokens, context 2,048, 128 new tokens at temperature 1.0 with a seed each: the
+    # load on the host side (plan, staging, sampling options, page leases, state slots)
+    "lfm2-350m": {"config": _lfm2_sizes(1024, 16, 4608, 2048), "requests": 256, "prompt_min": 128,
+                  "prompt_max": 128, "context": 2048, "new_tokens": 128, "temperature": 1.0,
+                  "max_batched_tokens": 4096, "prefill_chunk_tokens": 256},
+}
 FULL_LAYERS = 16
 CONTEXT = 4096
 PROMPT_TOKENS = 512
@@ -345,12 +366,214 @@ def run_ours(args) -> dict:
     }
 
 
+def percentile(samples, q: float) -> float:
+    if not samples:
+        return 0.0
+    ordered = sorted(samples)
+    return ordered[min(len(ordered) - 1, int(q * len(ordered)))]
+
+
+def drive_workload(engine, prompts, request_options, max_steps: int = 10 ** 9) -> dict:
+    """Submits every prompt, then calls ``engine.step()`` until all requests are terminal, polling
+    after every step as a client would (celeg's own engine benchmark does the same:
+    src/app/benchmark/cuda/concurrent.cpp:50-72). Returns the outputs and what was measured:
+    wall time, tokens, steps, time to the first token and between tokens, the page pool's high-water
+    mark, preemptions, and where the host's time went per step (celeg's host_prepare_ms /
+    gpu_execute_ms / host_commit_ms: src/backend/cuda/packed/execution.cu:200-223). For steps in which
+    every live request decodes it also sums the bytes such a step has to read (every weight once, the
+    live requests' keys and values and fixed-size state), for the roofline."""
+    import torch
+    manager = engine.loaded.manager
+    scheduler = engine.scheduler
+    bytes_per_position = 0
+    for group, (k, _v) in zip(manager.groups, zip(engine.loaded.storage.k, engine.loaded.storage.v)):
+        bytes_per_position += 2 * k.shape[0] * k.shape[2] * k.shape[4] * k.element_size()
+    state_bytes = engine.loaded.storage.slot_elements * 4
+    weight_bytes = engine.loaded.model.weight_bytes()
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    ids = [engine.submit(prompt, options) for prompt, options in zip(prompts, request_options)]
+    outputs = {i: [] for i in ids}
+    pending = set(ids)
+    failed = {}
+    decode_steps = 0
+    decode_seconds = 0.0
+    decode_bytes_sum = 0.0
+    decode_rows = 0
+    steps = 0
+    while pending and steps < max_steps:
+        live = [scheduler.requests[i] for i in scheduler.live]
+        all_decode = bool(live) and not scheduler.queue and all(r.status.value == "decoding" for r in live)
+        positions = sum(r.cache.tokens for r in live if r.cache is not None) if all_decode else 0
+        before = time.perf_counter()
+        progressed = engine.step()
+        after = time.perf_counter()
+        steps += 1
+        if all_decode:
+            decode_steps += 1
+            decode_seconds += after - before
+            decode_rows += len(live)
+            decode_bytes_sum += weight_bytes + positions * bytes_per_position + len(live) * state_bytes
+        for request_id in list(pending):
+            result = engine.poll(request_id)
+            if result.tokens:
+                outputs[request_id].extend(result.tokens)
+            if result.finished:
+                pending.discard(request_id)
+                if result.error:
+                    failed[request_id] = result.error
+                engine.release(request_id)
+        if not progressed and pending and not scheduler.has_work():
+            raise RuntimeError("the engine made no progress although requests are pending")
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - started
+    metrics = engine.metrics()
+    generated = sum(len(tokens) for tokens in outputs.values())
+    record = {
+        "wall_s": round(wall, 4), "requests": len(ids), "failed": len(failed),
+        "prompt_tokens": sum(len(p) for p in prompts), "generated_tokens": generated,
+        "tokens_per_s": round((metrics.prefill_tokens + metrics.decode_tokens) / wall, 1),
+        "generated_tokens_per_s": round(generated / wall, 1),
+        "steps": metrics.steps, "max_step_tokens": metrics.max_step_tokens,
+        "max_step_requests": metrics.max_step_requests, "preemptions": metrics.preempted,
+        "skipped_for_pages": metrics.skipped_for_pages,
+        "ttft_ms": {"mean": round(1e3 * metrics.ttft_seconds_sum / max(1, metrics.ttft_count), 3),
+                    "p50": round(1e3 * percentile(metrics.ttft_seconds, 0.50), 3),
+                    "p99": round(1e3 * percentile(metrics.ttft_seconds, 0.99), 3)},
+        "itl_ms": {"mean": round(1e3 * metrics.itl_seconds_sum / max(1, metrics.itl_count), 3),
+                   "p50": round(1e3 * percentile(metrics.itl_seconds, 0.50), 3),
+                   "p99": round(1e3 * percentile(metrics.itl_seconds, 0.99), 3)},
+        "pages": {"high_water": metrics.pages_high_water, "total": metrics.pages_total,
+                  "page_tokens": manager.page_tokens},
+        "host_ms_per_step": metrics.host_ms_per_step(),
+        "gpu_ms_per_step": round(1e3 * metrics.gpu_seconds / max(1, metrics.steps), 4),
+        "wall_ms_per_step": round(1e3 * wall / max(1, metrics.steps), 4),
+        "decode_only": {"steps": decode_steps,
+                        "ms_per_step": round(1e3 * decode_seconds / max(1, decode_steps), 4),
+                        "tokens_per_s": round(decode_rows / decode_seconds, 1) if decode_seconds else 0.0,
+                        "gb_per_step": round(decode_bytes_sum / max(1, decode_steps) / 1e9, 4),
+                        "achieved_gbs": round(decode_bytes_sum / decode_seconds / 1e9, 1) if decode_seconds else 0.0},
+    }
+    return {"outputs": [outputs[i] for i in ids], "errors": failed, "record": record}
+
+
+def run_workload(args) -> dict:
+    """One of the two scheduler workloads at full size, through Engine.submit / step / poll."""
+    import torch
+    from celeg_b200 import Engine, EngineOptions, RequestOptions, SamplingParams, kernels
+    spec = WORKLOADS[args.workload]
+    raw = dict(spec["config"])
+    if args.layers != FULL_LAYERS:
+        raw["num_hidden_layers"] = args.layers
+        raw["layer_types"] = raw["layer_types"][:args.layers]
+    requests = args.requests or spec["requests"]
+    new_tokens = args.new_tokens or spec["new_tokens"]
+    budget = args.max_batched_tokens or spec["max_batched_tokens"]
+    chunk = args.prefill_chunk or spec["prefill_chunk_tokens"]
+    peak, peak_source = peaks()
+    folder = model_folder(raw)
+    options = EngineOptions(max_active_requests=requests, max_batched_tokens=max(budget, requests),
+                            prefill_chunk_tokens=chunk, page_tokens=args.page_tokens)
+    engine = Engine(folder, max_context=spec["context"], dtype="bfloat16", device="cuda:0", options=options,
+                    use_cuda_graph=not args.no_cuda_graph)
+    generator = torch.Generator().manual_seed(11)
+    vocab = raw["vocab_size"]
+
+    def batch(count, tag):
+        lengths = torch.randint(spec["prompt_min"], spec["prompt_max"] + 1, (count,), generator=generator).tolist()
+        prompts = [torch.randint(0, vocab, (n,), generator=generator).tolist() for n in lengths]
+        opts = [RequestOptions(max_new_tokens=new_tokens, eos_tokens=(),
+                               generation=SamplingParams(temperature=spec["temperature"],
+                                                         top_k=50 if spec["temperature"] > 0 else 1,
+                                                         top_p=1.0, repetition_penalty=1.0, seed=tag + i + 1))
+                for i in range(count)]
+        return prompts, opts
+
+    # warm-up: as many requests of the same kind with a few new tokens each, so that the library, the graphs of
+    # the decode shapes and the allocator are past their first use (the requests are finished and released
+    # before the timed run)
+    if not args.no_warmup_run:
+        warm_prompts, warm_options = batch(requests, 10_000)
+        for option in warm_options:
+            option.max_new_tokens = min(8, new_tokens)
+        drive_workload(engine, warm_prompts, warm_options)
+    engine.scheduler.metrics = type(engine.scheduler.metrics)()
+    for group in engine.loaded.manager.groups:
+        group.pool.high_water = group.pool.used_pages
+    launches_before = kernels.LAUNCHES
+    prompts, request_options = batch(requests, 0)
+    with ClockSampler() as clocks:
+        result = drive_workload(engine, prompts, request_options)
+    record = result["record"]
+    decode = record["decode_only"]
+    return {
+        "workload": args.workload, "impl": "ours", "dtype": "bf16",
+        "data": "synthetic: random weights (seed 0), uniform-random token ids and prompt lengths (seed 11)",
+        "config": {"hidden_size": raw["hidden_size"], "layers": raw["num_hidden_layers"],
+                   "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+                   "intermediate_size": raw["intermediate_size"], "vocab_size": vocab,
+                   "requests": requests, "prompt_tokens": [spec["prompt_min"], spec["prompt_max"]],
+                   "context": spec["context"], "new_tokens": new_tokens, "temperature": spec["temperature"],
+                   "max_batched_tokens": options.max_batched_tokens, "prefill_chunk_tokens": chunk,
+                   "page_tokens": args.page_tokens, "cuda_graph": not args.no_cuda_graph,
+                   "scheduler_policy": options.scheduler_policy.value},
+        **record,
+        "decode_only_roofline": {"bound": "hbm", "achieved": decode["achieved_gbs"], "peak": peak["hbm_gbs"],
+                                 "unit": "GB/s", "frac": round(decode["achieved_gbs"] / peak["hbm_gbs"], 4),
+                                 "of": peak_source},
+        "gpu_launches": kernels.LAUNCHES - launches_before,
+        "clocks": clocks.summary(),
+        "errors": list(result["errors"].values())[:3],
+    }
+
+
 def run_reference(args) -> dict:
-    """The reference arm: celeg is a C++/CUDA project built with CMake (no Python package), so there
-    is nothing ``pip install`` can install from its checkout."""
-    return {"impl": "reference",
-            "unavailable": "celsowm/celeg is a CMake C++/CUDA project without setup.py or pyproject.toml: "
-                           "'pip install --no-index ... <checkout>' answers 'not installable'"}
+    """The reference arm: celsowm/celeg's own engine, unmodified, driven through its public C API
+    (include/celeg/api.h:142-179) by ``baseline/reference_bench.py`` in a process of its own that loads
+    ``baseline/_ref/libceleg.so`` and nothing of this package. ``pip install`` of the checkout is not possible
+    (a CMake project without setup.py or pyproject.toml); ``baseline/build_reference.py`` compiles celeg's own
+    source lists into that library instead. Same model folder, batch, prompts, steps and warm-up as the other
+    arm; every number is end to end (token ids in and out on the host)."""
+    library = os.path.join(ROOT, "baseline", "_ref", "libceleg.so")
+    if not os.path.isfile(library):
+        return {"impl": "reference",
+                "unavailable": "baseline/_ref/libceleg.so is not built: celsowm/celeg is a CMake C++/CUDA project that "
+                               "pip cannot install; run `python baseline/build_reference.py <celeg checkout>` first"}
+    raw = model_config(args.layers)
+    folder = model_folder(raw)
+    command = [sys.executable, os.path.join(ROOT, "baseline", "reference_bench.py"), "--library", library,
+               "--model", folder, "--steps", str(args.steps), "--warmup", str(args.warmup), "--batch", "8",
+               "--prompt-tokens", str(PROMPT_TOKENS), "--prefill-tokens", str(PREFILL_TOKENS),
+               "--context", str(CONTEXT), "--page-tokens", str(args.page_tokens)]
+    with ClockSampler() as clocks:
+        try:
+            done = subprocess.run(command, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=1500)
+        except subprocess.TimeoutExpired:
+            return {"impl": "reference", "unavailable": "celeg's engine did not finish the workload within 1500 s"}
+    lines = [line for line in done.stdout.splitlines() if line.startswith("{")]
+    try:
+        measured = json.loads(lines[-1])
+    except (IndexError, ValueError):
+        measured = {"error": (done.stderr or done.stdout).strip().splitlines()[-1:] or ["no output"]}
+    if done.returncode != 0 or "error" in measured:
+        return {"impl": "reference", "unavailable": f"celeg's engine failed on this workload: {measured.get('error')}"[:600]}
+    value = measured["tokens_per_s"]
+    return {
+        "metric": "decode tok/s at batch 8 (LFM2-1.2B sizes, random weights, 512-token prompts, context 4096)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(measured["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights (seed 0), uniform-random token ids", "impl": "reference",
+        "config": {"model": "LFM2-1.2B sizes", "global_batch": 8, "seq_len": CONTEXT, "prompt_tokens": PROMPT_TOKENS,
+                   "parallelism": "single GPU", "layers": raw["num_hidden_layers"], "layers_of_config": FULL_LAYERS,
+                   "page_tokens": args.page_tokens, "api": "celeg_engine_* over libceleg.so (its worker thread steps)",
+                   "timing": "wall clock between polled tokens"},
+        "e2e": {"value": round(value, 1), "unit": "tokens/s", "ms_per_step": round(measured["ms_per_step"], 4)},
+        "prefill": {"value": round(measured["prefill"]["tokens_per_s"], 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(measured["prefill"]["ms"], 3)},
+        "points": {key: round(v, 1) for key, v in measured["points"].items()},
+        "clocks": clocks.summary(),
+    }
 
 
 def main() -> int:
@@ -371,13 +594,26 @@ def main() -> int:
     parser.add_argument("--chunk", type=int, default=0,
                         help="--phase prefill: the prompt in portions of this many tokens (0: one step)")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of --phase prefill")
+    parser.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                        help="run one of the scheduler workloads through Engine.submit/step/poll and print its record")
+    parser.add_argument("--requests", type=int, default=0, help="--workload: number of requests (0: the workload's own)")
+    parser.add_argument("--new-tokens", type=int, default=0, help="--workload: tokens to generate per request")
+    parser.add_argument("--max-batched-tokens", type=int, default=0, help="--workload: token budget of a step")
+    parser.add_argument("--prefill-chunk", type=int, default=0, help="--workload: longest prompt portion")
+    parser.add_argument("--no-warmup-run", action="store_true",
+                        help="--workload: skip the untimed run before the timed one (for profilers)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "reference":
+        result = run_reference(args)
+    elif args.workload:
+        result = run_workload(args)
+    else:
+        result = run_ours(args)
     print(json.dumps(result))
     return 0
 

@@ -119,6 +119,14 @@ class Model:
                 if self.bindings[position] is not None:
                     self.layers[entry.layer].mixer.bind_cache(self.bindings[position])
 
+    def weight_bytes(self) -> int:
+        """Bytes of every weight a step reads once: what the parts put on the device, and the head (a tied
+        head is the embedding table, counted once; of an untied table a step gathers a few rows only)."""
+        total = self.rt.weight_bytes
+        if self.head is not self.embedding:
+            total -= self.embedding.numel() * self.embedding.element_size()
+        return total
+
     # ----------------------------------------------------------------- forward
     def forward(self, step: StepContext, logit_rows: torch.Tensor, n_logits: int, logits: torch.Tensor) -> None:
         """Run the step's tokens through every position of the run order and write the logits

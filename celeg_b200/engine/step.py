@@ -166,7 +166,7 @@ class StepFunction:
         spans = len(entries)
         all_decode = all(len(entry.tokens) == 1 for entry in entries)
         max_ctx = max(cache.tokens + len(entry.tokens) for entry, cache in zip(entries, caches))
-        prompt_key = self._prompt_graph_key(entries, total, wanted) if not all_decode else None
+        prompt_key = self._prompt_graph_key(entries, total, wanted, max_ctx) if not all_decode else None
         if (all_decode and self.use_graphs) or prompt_key is not None:
             stride = self.max_pages                         # fixed, so the captured addresses hold
         else:
@@ -213,7 +213,7 @@ class StepFunction:
         self.host_seconds["forward"] += done - staged
         return logits[:wanted]
 
-    def _prompt_graph_key(self, entries, total: int, wanted: int):
+    def _prompt_graph_key(self, entries, total: int, wanted: int, max_ctx: int):
         """Steps with prompt portions are launched from the host kernel by kernel, which takes longer than the
         GPU needs for portions of a few hundred tokens. Every launch shape of such a step follows from the
         lengths of its portions, the number of wanted rows and whether those are all rows in order, so a step
@@ -222,7 +222,9 @@ class StepFunction:
         if not self.use_graphs or wanted > self.max_spans:
             return None
         all_rows = wanted == total and all(tuple(e.want) == tuple(range(len(e.tokens))) for e in entries)
-        key = ("prompt", tuple(len(e.tokens) for e in entries), wanted, all_rows)
+        # (single tokens at the head of the step go to the decode attention, whose launch follows the context)
+        bucket = _context_bucket(max_ctx) if len(entries[0].tokens) == 1 else 0
+        key = ("prompt", tuple(len(e.tokens) for e in entries), wanted, all_rows, bucket)
         if key in self._graphs:
             return key
         if len(self._prompt_seen) > 4096:
@@ -335,6 +337,7 @@ class StepFunction:
             block_tables=[dev[o:o + spans * stride].view(spans, stride) for o in table_offsets],
             error_flag=self.error_flag, max_span=max(lengths), max_context=max_ctx,
             context_bucket=_context_bucket(max_ctx), host_span_lengths=lengths,
+            leading_single_tokens=next((i for i, n in enumerate(lengths) if n != 1), spans),
             logits_of_all_rows=(wanted == total and
                                 all(int(logit_rows_host[i]) == i for i in range(wanted))))
         return step, view("logit_rows", max(wanted, 1)), cursor

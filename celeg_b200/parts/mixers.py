@@ -165,12 +165,12 @@ class AttentionMixer:
         self.attend(step, table)
         rt.linear(self.attended, self.w_out, out, t)
 
-    def _decode_split(self, step: StepContext):
+    def _decode_split(self, step: StepContext, tokens: Optional[int] = None):
         """One query token per request: how the keys are split so that few requests still fill the GPU,
         and the scratch of the split (chunk, max_splits, partial outputs, maxima and sums, counters)."""
         rt = self.rt
-        chunk, max_splits, cap_splits = decode_split(step.tokens, self.kv_heads, step.context_bucket, self.window,
-                                                     rt.max_context)
+        chunk, max_splits, cap_splits = decode_split(tokens or step.tokens, self.kv_heads, step.context_bucket,
+                                                     self.window, rt.max_context)
         rows = rt.max_requests * self.heads * cap_splits
         partial_o = rt.flat_scratch("attention.partial_o", rows * self.head_dim, torch.float32)
         partial_ml = rt.flat_scratch("attention.partial_ml", rows * 2, torch.float32)
@@ -184,32 +184,62 @@ class AttentionMixer:
                 kernels.attention_decode_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype))
 
     def attend(self, step: StepContext, table: torch.Tensor) -> None:
+        """Attention of the step's queries (normalised, rotated, in ``self.qkv``) over the cache, which holds the
+        step's own keys and values already. A step that is all single tokens goes to the split-key decode
+        kernel. A step that begins with single-token spans and goes on with prompt portions (the order the
+        scheduler plans: decoding requests first) is served by both: the decode kernel shares a request's keys
+        among the query heads of a group and splits long contexts, where a prompt kernel would walk the whole
+        context once per query head for one row of a 128-row tile."""
         b = self.binding
         rt = self.rt
         if self._decodes(step):
-            chunk, max_splits, partial_o, partial_ml, counters = self._decode_split(step)
-            kernels.attention_decode(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
-                                     step.token_span, table, step.tokens, self.heads, self.kv_heads,
-                                     self.head_dim, b.page_tokens, self.window, self.scale, chunk, max_splits,
-                                     partial_o, partial_ml, counters, step.error_flag)
+            self._attend_single_tokens(step, table, step.tokens)
             return
-        if (step.host_span_lengths is not None and rt.tcgen05_attention and kernels.attention_prefill_tcgen05_supported(
+        single = step.leading_single_tokens
+        if (0 < single < step.tokens and single <= rt.max_requests and step.host_span_lengths is not None
+                and kernels.attention_decode_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype)):
+            self._attend_single_tokens(step, table, single)
+            self._attend_portions(step, table, single)
+            return
+        self._attend_portions(step, table, 0)
+
+    def _attend_single_tokens(self, step: StepContext, table: torch.Tensor, count: int) -> None:
+        """The first ``count`` tokens of the step, each the only token of its span."""
+        b = self.binding
+        chunk, max_splits, partial_o, partial_ml, counters = self._decode_split(step, count)
+        kernels.attention_decode(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
+                                 step.token_span, table, count, self.heads, self.kv_heads,
+                                 self.head_dim, b.page_tokens, self.window, self.scale, chunk, max_splits,
+                                 partial_o, partial_ml, counters, step.error_flag)
+
+    def _attend_portions(self, step: StepContext, table: torch.Tensor, skip: int) -> None:
+        """The spans from ``skip`` on (the spans before it have one token each, so span ``skip`` begins at token
+        ``skip``). The kernels take token indices from ``span_begin`` and table rows by span, so a later part of
+        both arrays addresses the same buffers."""
+        b = self.binding
+        rt = self.rt
+        spans = step.spans - skip
+        span_begin = step.span_begin[skip:]
+        span_table = table[skip:]
+        lengths = step.host_span_lengths[skip:] if step.host_span_lengths is not None else None
+        if (lengths is not None and rt.tcgen05_attention and kernels.attention_prefill_tcgen05_supported(
                 self.heads, self.kv_heads, self.head_dim, b.page_tokens, rt.act_dtype)):
             # head size 64: S and O' in tensor memory, Q/K/V by TMA
-            tiles = sum((length + 127) // 128 for length in step.host_span_lengths)
+            tiles = sum((length + 127) // 128 for length in lengths)
             kernels.attention_prefill_tcgen05(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
-                                              step.span_begin, table, step.tokens, step.spans, tiles, self.heads,
+                                              span_begin, span_table, step.tokens, spans, tiles, self.heads,
                                               self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale,
                                               step.error_flag)
             return
         if kernels.attention_prefill_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype):
             kernels.attention_prefill(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
-                                      step.span_begin, table, step.tokens, step.spans, self.heads, self.kv_heads,
+                                      span_begin, span_table, step.tokens, spans, self.heads, self.kv_heads,
                                       self.head_dim, b.page_tokens, self.window, self.scale, step.error_flag)
             return
-        kernels.attention_generic(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
-                                  step.token_span, table, step.tokens, self.heads, self.kv_heads, self.head_dim,
-                                  b.page_tokens, self.window, self.scale, step.error_flag)
+        kernels.attention_generic(self.qkv[skip:], self.qkv_width, self.attended[skip:], b.k, b.v,
+                                  step.positions[skip:], step.token_span[skip:], table, step.tokens - skip,
+                                  self.heads, self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale,
+                                  step.error_flag)
 
 
 @register_part("mixer", "short_conv")

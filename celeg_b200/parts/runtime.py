@@ -136,6 +136,7 @@ class Runtime:
         self._streamed_last: Optional[int] = None
         self._flat: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         self._scratch: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
+        self.weight_bytes = 0                   # what matrix() and vector() have put on the device
         kernels.library()                       # fail now, not at the first step, if it is missing
 
     def scratch(self, tag: str, columns: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -157,11 +158,15 @@ class Runtime:
 
     def matrix(self, weight: torch.Tensor) -> torch.Tensor:
         """A projection weight on the device in the path's matrix precision."""
-        return weight.to(device=self.device, dtype=self.act_dtype).contiguous()
+        placed = weight.to(device=self.device, dtype=self.act_dtype).contiguous()
+        self.weight_bytes += placed.numel() * placed.element_size()
+        return placed
 
     def vector(self, weight: torch.Tensor) -> torch.Tensor:
         """A small weight (norm scale, conv kernel) on the device in float32 (exact widening)."""
-        return weight.to(device=self.device, dtype=torch.float32).contiguous()
+        placed = weight.to(device=self.device, dtype=torch.float32).contiguous()
+        self.weight_bytes += placed.numel() * 4
+        return placed
 
     def takes_split_norm(self, rows: int, weight: torch.Tensor) -> bool:
         """Whether a product of ``rows`` rows with ``weight`` can take an operand that still lacks its
@@ -283,4 +288,5 @@ class StepContext:
     logits_of_all_rows: bool = False  # the wanted rows are exactly rows 0..tokens-1 in order
     host_positions: Optional[list] = None
     host_span_lengths: Optional[list] = None
+    leading_single_tokens: int = 0    # how many spans at the start of the step bring exactly one token
     extras: Dict[str, object] = field(default_factory=dict)

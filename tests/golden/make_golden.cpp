@@ -2,6 +2,7 @@
 // JSON. Built and run by make_golden.sh against the reference checkout; the result is committed as
 // golden.json and compared with tests/plain_lfm2.py by tests/test_golden_reference.py.
 #include "celeg/backend/cpu/kernels.hpp"
+#include "celeg/backend/cpu/paged_kv.hpp"
 #include "celeg/backend/cpu/sampler.hpp"
 #include "celeg/model/definition.hpp"
 #include "celeg/model/runtime_types.hpp"
@@ -84,7 +85,33 @@ int main() {
             draws.push_back(static_cast<float>(celeg::CpuSampler::sample(logits, vocab, generation, seen, rng)));
         generation.temperature = 0.0f;
         draws.push_back(static_cast<float>(celeg::CpuSampler::sample(logits, vocab, generation, seen, rng)));
-        print("sampler_logits", logits); print("sampler_draws", draws, true);
+        print("sampler_logits", logits); print("sampler_draws", draws);
+    }
+    {   // causal grouped-query attention over a paged float32 cache: 4 query heads on 2 kv heads of 16, 21 keys
+        // in pages of 8 (three pages, taken from the pool out of order), the query at the last position and the
+        // same query at position 9, that is over a sequence of 10 keys ending inside the second page (celeg's
+        // chunk attention calls the kernel once per row with that row's own sequence length:
+        // src/backend/cpu/attention/paged_prefill.cpp:30). q, k and v are given as they are after norm and
+        // rotation; the kernel applies 1/sqrt(head_dim) itself.
+        const int q_heads = 4, kv_heads = 2, head_dim = 16, keys = 21, page_tokens = 8;
+        auto q = values(static_cast<size_t>(q_heads) * head_dim, 2.0f);
+        auto k = values(static_cast<size_t>(keys) * kv_heads * head_dim, 2.0f);
+        auto v = values(static_cast<size_t>(keys) * kv_heads * head_dim);
+        celeg::CpuKvPagePool pool(celeg::CpuKvCacheMode::Fp32, page_tokens,
+                                  celeg::CpuOrdinaryKvPageLayout{static_cast<size_t>(kv_heads * head_dim),
+                                                                 static_cast<size_t>(kv_heads * head_dim)});
+        std::vector<celeg::CpuKvPageId> taken;
+        for (int i = 0; i < 5; ++i) taken.push_back(pool.allocate());
+        std::vector<celeg::CpuKvPageId> pages = {taken[3], taken[0], taken[4]};
+        for (int t = 0; t < keys; ++t)
+            pool.write(pages[static_cast<size_t>(t / page_tokens)], static_cast<size_t>(t % page_tokens),
+                       k.data() + static_cast<size_t>(t) * kv_heads * head_dim,
+                       v.data() + static_cast<size_t>(t) * kv_heads * head_dim);
+        std::vector<float> last(static_cast<size_t>(q_heads) * head_dim), middle(last.size());
+        celeg::cpu_gqa_decode_paged(q.data(), pool, pages, last.data(), keys, q_heads, kv_heads, head_dim);
+        celeg::cpu_gqa_decode_paged(q.data(), pool, pages, middle.data(), 10, q_heads, kv_heads, head_dim);
+        print("attention_q", q); print("attention_k", k); print("attention_v", v);
+        print("attention_out_last", last); print("attention_out_at_9", middle, true);
     }
     std::printf("}\n");
     return 0;

@@ -1,13 +1,17 @@
 #!/bin/bash
-# Builds make_golden.cpp against a checkout of celsowm/celeg (first argument, default /root/reference)
-# with g++ on the CPU and writes golden.json beside this script. Only the reference's plain float32
-# kernels are linked: elementwise, rope, convolution, sampler, ISA detection, the thread pool and the topology probe it needs.
+# Builds make_golden.cpp against a checkout of celsowm/celeg (first argument, required) with g++ on the
+# CPU and writes golden.json beside this script. Only the reference's plain float32 kernels are linked:
+# elementwise, rope, convolution, sampler, the paged attention with its page pool and pattern policy, ISA
+# detection, the thread pool and the topology probe they need.
 set -euo pipefail
 here="$(cd "$(dirname "$0")" && pwd)"
-ref="${1:-/root/reference}"
+ref="${1:?usage: make_golden.sh /path/to/celeg}"
 build="$(mktemp -d)"
 srcs=(src/backend/cpu/kernels/elementwise.cpp src/backend/cpu/kernels/rope.cpp
       src/backend/cpu/kernels/convolution.cpp src/backend/cpu/sampler.cpp
+      src/backend/cpu/attention/paged_attention.cpp src/backend/cpu/memory/paged_kv.cpp
+      src/backend/cpu/memory/attention_policy.cpp src/model/weights/quantization.cpp
+      src/backend/cpu/runtime/numa.cpp
       src/backend/cpu/runtime/isa.cpp src/backend/cpu/runtime/thread_pool.cpp
       src/backend/cpu/runtime/topology.cpp)
 args=()

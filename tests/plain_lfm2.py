@@ -95,10 +95,9 @@ def attention_mixer(n: np.ndarray, wq: np.ndarray, wk: np.ndarray, wv: np.ndarra
                     theta: float, eps: float, positions: Optional[np.ndarray] = None,
                     window: Optional[int] = None) -> np.ndarray:
     """q,k,v projections; per-head RMSNorm of q and k (weights [d]); split-half RoPE on q and k;
-    causal grouped-query softmax(q k^T / sqrt(d)) v; out projection.
+    causal grouped-query softmax(q k^T / sqrt(d)) v (:func:`causal_attention`); out projection.
     src/backend/cpu/operators/attention_token.cpp:151-204; norm+RoPE
-    src/backend/cpu/kernels/rope.cpp:61-110; query head h reads kv head h // (heads/kv_heads) and
-    keys 0..p inclusive: src/backend/cpu/attention/paged_attention.cpp:225-283."""
+    src/backend/cpu/kernels/rope.cpp:61-110."""
     tokens = n.shape[0]
     if positions is None:
         positions = np.arange(tokens)
@@ -107,8 +106,19 @@ def attention_mixer(n: np.ndarray, wq: np.ndarray, wk: np.ndarray, wv: np.ndarra
     v = (n @ wv.T).reshape(tokens, kv_heads, head_dim)
     q = rope_split_half(rmsnorm(q, q_norm, eps), positions, theta)
     k = rope_split_half(rmsnorm(k, k_norm, eps), positions, theta)
-    group = heads // kv_heads
-    scale = 1.0 / math.sqrt(head_dim)
+    out = causal_attention(q, k, v, 1.0 / math.sqrt(head_dim), window)
+    return out.reshape(tokens, heads * head_dim) @ wo.T
+
+
+def causal_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float,
+                     window: Optional[int] = None) -> np.ndarray:
+    """softmax(q k^T * scale) v over one sequence: q [T, heads, d], k and v [T, kv_heads, d], all after norm
+    and rotation. Query head h reads kv head h // (heads / kv_heads) (paged_attention.cpp:259); the query at
+    position p reads keys 0..p (with a window only the last ``window`` of them); the scale is applied once, to
+    the dot product (paged_attention.cpp:254, :204); softmax subtracts the row maximum (:206-210).
+    src/backend/cpu/attention/paged_attention.cpp:185-283."""
+    tokens, heads, head_dim = q.shape
+    group = heads // k.shape[1]
     out = np.zeros((tokens, heads, head_dim))
     for h in range(heads):
         kh = h // group
@@ -123,7 +133,7 @@ def attention_mixer(n: np.ndarray, wq: np.ndarray, wk: np.ndarray, wv: np.ndarra
         weights = np.exp(scores)
         weights /= weights.sum(axis=-1, keepdims=True)
         out[:, h, :] = weights @ v[:, kh, :]
-    return out.reshape(tokens, heads * head_dim) @ wo.T
+    return out
 
 
 def swiglu(n: np.ndarray, w1: np.ndarray, w3: np.ndarray, w2: np.ndarray) -> np.ndarray:

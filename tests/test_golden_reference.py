@@ -2,9 +2,10 @@
 
 ``tests/golden/golden.json`` was produced on the CPU by ``tests/golden/make_golden.sh``, which builds
 ``tests/golden/make_golden.cpp`` against the reference checkout (elementwise, rope, convolution and
-sampler sources). Whole-model logits of the reference's CPU backend are not a float32 anchor (it
-quantises every weight to 4 bits and scales attention scores twice), so the anchor is per operation;
-attention itself rests on the formulas cited in ``plain_lfm2.py``.
+sampler and paged-attention sources). Whole-model logits of the reference's CPU backend are not a float32
+anchor (it quantises every weight to 4 bits and scales attention scores twice), so the anchor is per
+operation; the order of the operations in a block is pinned by ``test_whole_model_structure`` through an
+emulation of those two artefacts.
 """
 from __future__ import annotations
 
@@ -84,6 +85,23 @@ def test_plain_conv_mixer_matches_reference_kernel(golden):
     out = plain_lfm2.short_conv_mixer(proj, w_in, wide_kernel, np.eye(wide))
     assert np.allclose(out[:, :hidden].reshape(-1), golden["conv_decode_out"], rtol=2e-5, atol=2e-6)
     assert np.allclose(out[:, hidden:], 0.0)
+
+
+def test_causal_grouped_query_attention(golden):
+    """celeg's cpu_gqa_decode_paged on 21 keys over three float32 pages of 8, 4 query heads on 2 kv heads: the
+    query at the last position, and the same query at position 9 (later keys must not be read). The plain
+    function gets the same q at every position; its rows 20 and 9 are what the kernel computed."""
+    q_heads, kv_heads, head_dim, keys = 4, 2, 16, 21
+    q = golden["attention_q"].reshape(1, q_heads, head_dim).repeat(keys, axis=0)
+    k = golden["attention_k"].reshape(keys, kv_heads, head_dim)
+    v = golden["attention_v"].reshape(keys, kv_heads, head_dim)
+    got = plain_lfm2.causal_attention(q, k, v, head_dim ** -0.5)
+    assert np.allclose(got[20].reshape(-1), golden["attention_out_last"], rtol=2e-5, atol=2e-6)
+    assert np.allclose(got[9].reshape(-1), golden["attention_out_at_9"], rtol=2e-5, atol=2e-6)
+    assert not np.allclose(golden["attention_out_last"], golden["attention_out_at_9"], atol=1e-2)
+    # grouping: heads 0,1 read kv head 0 and heads 2,3 read kv head 1; swapping the kv heads must change it
+    swapped = plain_lfm2.causal_attention(q, k[:, ::-1], v[:, ::-1], head_dim ** -0.5)
+    assert not np.allclose(swapped[20].reshape(-1), golden["attention_out_last"], atol=1e-2)
 
 
 def test_sampler_draws(golden):

@@ -177,3 +177,74 @@ def test_a_step_larger_than_one_pass_is_cut_inside(models, dtype, tmp_path):
     want_b = plain_lfm2.forward(config, weights, b + [5])
     compare(read_logits(out_dir, 0, vocab), np.stack([want_a[0], want_a[17], want_a[149], want_b[39]]), dtype, "cut")
     compare(read_logits(out_dir, 1, vocab), want_b[40:41], dtype, "after the cut")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_single_tokens_before_portions_in_one_step(models, name, dtype, tmp_path):
+    """The shape of step the scheduler plans under load: decoded tokens of some requests first, then portions
+    of others' prompts. The single tokens at the head of such a step take the decode attention, the portions the
+    prompt attention, in the same pass. The decoding requests sit at very different depths (inside a first page,
+    at a page's edge, beyond 128 keys), one portion is new and one continues a prompt."""
+    folder, config, weights = models[name]
+    vocab = config["vocab_size"]
+    seqs = sequences(vocab, [72, 18, 135, 47, 40], seed=16)
+    depth = [70, 16, 131]                       # r0..r2 are this deep when the mixed steps begin
+    steps = [{"step": 0, "entries": [{"id": f"r{i}", "tokens": seqs[i][:depth[i]], "want": [depth[i] - 1]}
+                                     for i in range(3)] +
+                                    [{"id": "r4", "tokens": seqs[4][:9], "want": []}], "end": []}]
+    # two mixed steps: r0..r2 one token each, r3 begins with 30 tokens then 17, r4 goes on with 2 then 29
+    cuts3, cuts4 = [30, 17], [2, 29]
+    at3, at4 = 0, 9
+    for j in range(2):
+        entries = [{"id": f"r{i}", "tokens": [seqs[i][depth[i] + j]], "want": [0]} for i in range(3)]
+        entries.append({"id": "r3", "tokens": seqs[3][at3:at3 + cuts3[j]], "want": [0, cuts3[j] - 1]})
+        entries.append({"id": "r4", "tokens": seqs[4][at4:at4 + cuts4[j]], "want": [cuts4[j] - 1]})
+        steps.append({"step": j + 1, "entries": entries, "end": []})
+        at3 += cuts3[j]
+        at4 += cuts4[j]
+    out = run_trace(folder, dtype, steps, 5 * 192, tmp_path, "single_then_portions")
+    full = [plain_lfm2.forward(config, weights, s) for s in seqs]
+    compare(read_logits(out, 0, vocab), np.stack([full[i][depth[i] - 1] for i in range(3)]), dtype, f"{name} prompts")
+    at3, at4 = 0, 9
+    for j in range(2):
+        want = [full[i][depth[i] + j] for i in range(3)]
+        want += [full[3][at3], full[3][at3 + cuts3[j] - 1], full[4][at4 + cuts4[j] - 1]]
+        compare(read_logits(out, j + 1, vocab), np.stack(want), dtype, f"{name} mixed step {j}")
+        at3 += cuts3[j]
+        at4 += cuts4[j]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,requests", [("B", 20), ("D", 33), ("B", 64), ("D", 64)])
+def test_many_requests_decoding_together(models, name, requests, dtype, tmp_path):
+    """More requests than the small-batch kernels take (16): 20, 33 and 64 requests decode together, with the
+    switches at their defaults. Prompts of 3 to 40 tokens go in first, eight requests to a step; then four
+    steps in which every request brings one token; every row of every step against the plain model."""
+    from celeg_b200.engine.trace import replay
+    folder, config, weights = models[name]
+    vocab = config["vocab_size"]
+    rng = np.random.default_rng(17)
+    lengths = rng.integers(3, 41, size=requests).tolist()
+    seqs = sequences(vocab, [n + 4 for n in lengths], seed=18)
+    steps = []
+    for first in range(0, requests, 8):
+        group = range(first, min(first + 8, requests))
+        steps.append({"step": len(steps), "entries": [{"id": f"m{i}", "tokens": seqs[i][:lengths[i]],
+                                                       "want": [lengths[i] - 1]} for i in group], "end": []})
+    prompt_steps = len(steps)
+    for j in range(4):
+        steps.append({"step": len(steps), "entries": [{"id": f"m{i}", "tokens": [seqs[i][lengths[i] + j]], "want": [0]}
+                                                      for i in range(requests)],
+                      "end": [f"m{i}" for i in range(requests)] if j == 3 else []})
+    out_dir = str(tmp_path / f"many_{name}_{requests}_{dtype}")
+    text = io.StringIO("".join(json.dumps(step) + "\n" for step in steps))
+    assert replay(folder, dtype, out_dir, requests * 64, text, io.StringIO(), max_requests=requests) == 0
+    full = [plain_lfm2.forward(config, weights, s) for s in seqs]
+    for number in range(prompt_steps):
+        group = range(number * 8, min(number * 8 + 8, requests))
+        compare(read_logits(out_dir, number, vocab), np.stack([full[i][lengths[i] - 1] for i in group]), dtype,
+                f"{name} prompts {number}")
+    for j in range(4):
+        compare(read_logits(out_dir, prompt_steps + j, vocab),
+                np.stack([full[i][lengths[i] + j] for i in range(requests)]), dtype, f"{name} decode step {j}")
