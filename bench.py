@@ -72,8 +72,8 @@ def peaks():
         return dict(FALLBACK_PEAKS), "fallback"
 
 
-def model_config(layers: int) -> dict:
-    raw = dict(LFM2_1P2B)
+def model_config(layers: int, sizes: str = "lfm2-1.2b") -> dict:
+    raw = dict(LFM2_1P2B) if sizes == "lfm2-1.2b" else dict(WORKLOADS[sizes]["config"])
     if layers != FULL_LAYERS:
         raw["num_hidden_layers"] = layers
         raw["layer_types"] = LFM2_1P2B["layer_types"][:layers]
@@ -176,7 +176,62 @@ def prefill_flops(raw: dict, tokens: int) -> float:
     return 2.0 * tokens * linear + 2.0 * causal + 2.0 * v * h    # head on the last row only
 
 
-def time_decode(loaded, sampler, batch: int, steps: int, warmup: int, prompt_tokens: int, seed: int):
+class KernelTimer:
+    """Device time per kind of kernel: while active, every launch entry of ``celeg_b200.kernels`` and the
+    library product are bracketed by two CUDA events. Use it on steps that are launched kernel by kernel
+    (``--no-cuda-graph``); the numbers include what a launch from the host adds, so read them as shares."""
+    NAMES = ("embedding", "add_rmsnorm", "short_conv", "qk_norm_rope_store", "attention_generic", "attention_decode",
+             "attention_decode_fused", "attention_prefill", "attention_prefill_tcgen05", "gemv_bf16", "gemm_tcgen05",
+             "gemm_stream", "gemm_f32", "swiglu", "sample", "sample_greedy", "mark_seen")
+
+    def __init__(self):
+        self.pairs = []
+        self.saved = {}
+
+    def _wrap(self, name, function):
+        import torch
+
+        def timed(*args, **kwargs):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            result = function(*args, **kwargs)
+            end.record()
+            self.pairs.append((name, begin, end))
+            return result
+        return timed
+
+    def __enter__(self):
+        import torch
+        from celeg_b200 import kernels
+        for name in self.NAMES:
+            if hasattr(kernels, name):
+                self.saved[name] = getattr(kernels, name)
+                setattr(kernels, name, self._wrap(name, self.saved[name]))
+        self.saved["torch.mm"] = torch.mm
+        torch.mm = self._wrap("library product (torch.mm)", torch.mm)
+        return self
+
+    def __exit__(self, *exc):
+        import torch
+        from celeg_b200 import kernels
+        torch.mm = self.saved.pop("torch.mm")
+        for name, function in self.saved.items():
+            setattr(kernels, name, function)
+        self.saved = {}
+
+    def table(self, steps: int) -> dict:
+        import torch
+        torch.cuda.synchronize()
+        totals = {}
+        for name, begin, end in self.pairs:
+            entry = totals.setdefault(name, [0, 0.0])
+            entry[0] += 1
+            entry[1] += begin.elapsed_time(end) * 1e3
+        return {name: {"launches": round(count / steps, 1), "us": round(us / steps, 1)}
+                for name, (count, us) in sorted(totals.items(), key=lambda item: -item[1][1])}
+
+
+def time_decode(loaded, sampler, batch: int, steps: int, warmup: int, prompt_tokens: int, seed: int, timer=None):
     """Prefill ``batch`` requests, then time ``steps`` decode steps on the device."""
     import torch
     from celeg_b200 import kernels
@@ -205,11 +260,15 @@ def time_decode(loaded, sampler, batch: int, steps: int, warmup: int, prompt_tok
     torch.cuda.synchronize()
     launches_before = kernels.LAUNCHES
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if timer is not None:
+        timer.__enter__()
     start.record()
     for i in range(warmup, warmup + steps):
         one(i)
     stop.record()
     torch.cuda.synchronize()
+    if timer is not None:
+        timer.__exit__(None, None, None)
     ms = start.elapsed_time(stop) / steps
     launches = kernels.LAUNCHES - launches_before
     context = prompt_tokens + warmup + steps // 2
@@ -288,7 +347,7 @@ def run_ours(args) -> dict:
     from celeg_b200 import Engine, EngineOptions, kernels
     from celeg_b200.sampling import Sampler
     batch = 8
-    raw = model_config(args.layers)
+    raw = model_config(args.layers, args.sizes if args.phase != "all" else "lfm2-1.2b")
     peak, peak_source = peaks()
     max_batch = 64
     context, prompt_tokens, step_tokens = CONTEXT, PROMPT_TOKENS, PREFILL_TOKENS
@@ -302,16 +361,23 @@ def run_ours(args) -> dict:
     options = EngineOptions(max_active_requests=max_batch, max_batched_tokens=step_tokens,
                             prefill_chunk_tokens=step_tokens, page_tokens=args.page_tokens,
                             logical_kv_pages=max_batch * (-(-context // args.page_tokens)))
+    from celeg_b200 import KernelOptions
     engine = Engine(folder, max_context=context, dtype="bfloat16", device="cuda:0", options=options,
-                    use_cuda_graph=not args.no_cuda_graph)
+                    use_cuda_graph=not args.no_cuda_graph, kernel_options=KernelOptions.from_env())
     loaded = engine.loaded
     sampler = Sampler(raw["vocab_size"], max_batch, max_batch, engine.device)
 
     if args.phase == "decode":          # a short run of one phase, for profilers
-        ms, launches, context = time_decode(loaded, sampler, args.batch, args.steps, args.warmup, prompt_tokens, 1)
-        return {"phase": "decode", "batch": args.batch, "context_tokens": context, "ms_per_step": round(ms, 4),
-                "tokens_per_s": round(args.batch * 1e3 / ms, 1), "gpu_launches": launches,
-                "hbm_frac": round(decode_bytes(raw, args.batch, context) / (ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
+        timer = KernelTimer() if args.kernel_times else None
+        ms, launches, context = time_decode(loaded, sampler, args.batch, args.steps, args.warmup, prompt_tokens, 1,
+                                            timer=timer)
+        record = {"phase": "decode", "sizes": args.sizes, "batch": args.batch, "context_tokens": context,
+                  "ms_per_step": round(ms, 4),
+                  "tokens_per_s": round(args.batch * 1e3 / ms, 1), "gpu_launches": launches,
+                  "hbm_frac": round(decode_bytes(raw, args.batch, context) / (ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
+        if timer is not None:
+            record["kernel_us_per_step"] = timer.table(args.steps)
+        return record
     if args.phase == "prefill":
         prefill_ms = time_prefill(loaded, args.prefill_tokens, max(1, min(args.steps, 5)), 2, args.chunk)
         return {"phase": "prefill", "tokens": args.prefill_tokens, "chunk": args.chunk or args.prefill_tokens,
@@ -363,6 +429,7 @@ def run_ours(args) -> dict:
         "points": points,
         "clocks": clock_summary,
         "kernel_library": kernels.library_path(),
+        "model_fingerprint": loaded.fingerprint,
     }
 
 
@@ -474,8 +541,9 @@ def run_workload(args) -> dict:
     folder = model_folder(raw)
     options = EngineOptions(max_active_requests=requests, max_batched_tokens=max(budget, requests),
                             prefill_chunk_tokens=chunk, page_tokens=args.page_tokens)
+    from celeg_b200 import KernelOptions
     engine = Engine(folder, max_context=spec["context"], dtype="bfloat16", device="cuda:0", options=options,
-                    use_cuda_graph=not args.no_cuda_graph)
+                    use_cuda_graph=not args.no_cuda_graph, kernel_options=KernelOptions.from_env())
     generator = torch.Generator().manual_seed(11)
     vocab = raw["vocab_size"]
 
@@ -502,12 +570,19 @@ def run_workload(args) -> dict:
         group.pool.high_water = group.pool.used_pages
     launches_before = kernels.LAUNCHES
     prompts, request_options = batch(requests, 0)
+    timer = KernelTimer() if args.kernel_times else None
+    if timer is not None:
+        timer.__enter__()
     with ClockSampler() as clocks:
         result = drive_workload(engine, prompts, request_options)
+    if timer is not None:
+        timer.__exit__(None, None, None)
     record = result["record"]
+    if timer is not None:
+        record["kernel_us_per_step"] = timer.table(max(1, record["steps"]))
     decode = record["decode_only"]
     return {
-        "workload": args.workload, "impl": "ours", "dtype": "bf16",
+        "workload": args.workload, "impl": "ours", "dtype": "bf16", "model_fingerprint": engine.loaded.fingerprint,
         "data": "synthetic: random weights (seed 0), uniform-random token ids and prompt lengths (seed 11)",
         "config": {"hidden_size": raw["hidden_size"], "layers": raw["num_hidden_layers"],
                    "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
@@ -589,6 +664,11 @@ def main() -> int:
     parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
                         help="run one phase only and print a short record (for profilers)")
     parser.add_argument("--batch", type=int, default=8, help="batch of --phase decode")
+    parser.add_argument("--sizes", default="lfm2-1.2b", choices=["lfm2-1.2b", *sorted(WORKLOADS)],
+                        help="layer sizes of a --phase run")
+    parser.add_argument("--kernel-times", action="store_true",
+                        help="--phase decode and --workload: device time per kind of kernel between two events "
+                             "each (steps that replay a graph show nothing; use with --no-cuda-graph)")
     parser.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS, help="prompt length of --phase decode")
     parser.add_argument("--context", type=int, default=CONTEXT, help="longest request of a --phase run")
     parser.add_argument("--chunk", type=int, default=0,

@@ -13,6 +13,7 @@ _LAZY = {
     "RequestStatus": ("celeg_b200.engine.scheduler", "RequestStatus"),
     "SchedulerPolicy": ("celeg_b200.engine.scheduler", "SchedulerPolicy"),
     "SamplingParams": ("celeg_b200.sampling.params", "SamplingParams"),
+    "KernelOptions": ("celeg_b200.parts.options", "KernelOptions"),
     "StepEntry": ("celeg_b200.engine.step", "StepEntry"),
     "load_model": ("celeg_b200.engine.loading", "load_model"),
     "write_random_model": ("celeg_b200.weights.random_init", "write_random_model"),

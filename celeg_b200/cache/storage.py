@@ -12,7 +12,11 @@ class CacheStorage:
     """Keys and values of group g: ``k[g]``, ``v[g]`` of shape
     [layers of the group, pages, kv_heads, page_tokens, head_dim] in the path's element type,
     so one (layer, page, head) tile is a contiguous [page_tokens, head_dim] box.
-    Fixed-size state: ``state`` [slots, slot_elements] float32."""
+    Fixed-size state: ``state`` [slots, slot_elements] float32.
+
+    Every group has one page more than its pool gives out, and the slab one slot more than the manager
+    does (``scratch_pages[g]``, ``scratch_slot``): rows that a step adds to reach a launch shape it has a
+    captured graph for write there, and nothing ever reads them."""
 
     def __init__(self, groups: Sequence[Tuple[PagedNeed, int]], group_pages: Sequence[int], page_tokens: int,
                  state_layout: StateLayout, slots: int, dtype: torch.dtype, device: torch.device):
@@ -20,13 +24,15 @@ class CacheStorage:
         self.k: List[torch.Tensor] = []
         self.v: List[torch.Tensor] = []
         for (need, layers), pages in zip(groups, group_pages):
-            shape = (layers, max(pages, 1), need.kv_heads, page_tokens, need.head_dim)
+            shape = (layers, pages + 1, need.kv_heads, page_tokens, need.head_dim)
             # zeros, not empty: a page that was never written must not hold NaN bit patterns,
             # because masked keys are still multiplied by a zero weight in some kernels
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
             self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+        self.scratch_pages = [int(pages) for pages in group_pages]
+        self.scratch_slot = int(slots)
         self.slot_elements = max(state_layout.slot_elements, 4)
-        self.state = torch.zeros((max(slots, 1), self.slot_elements), dtype=torch.float32, device=device)
+        self.state = torch.zeros((slots + 1, self.slot_elements), dtype=torch.float32, device=device)
 
     def clear_slot(self, slot: int) -> None:
         self.state[slot].zero_()

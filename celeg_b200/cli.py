@@ -105,13 +105,16 @@ def run(argv=None) -> int:
     raw = read_config_json(model_dir)
     architecture = architecture_of(raw)
     if args.print_config:
+        from .engine.loading import fingerprint_of
         from .weights import TensorRepository
         repository = TensorRepository(model_dir)
         try:
             config = architecture.resolve_config(architecture.parse_config(raw), repository.shapes())
+            fingerprint = fingerprint_of(config, raw, repository)
         finally:
             repository.close()
         print(json.dumps(config.to_dict(), indent=1))
+        print(f"model_fingerprint={fingerprint}")
         if _prompt_ids(args) is None:
             return 0
 

@@ -67,4 +67,33 @@ def read_config_json(model_dir: str) -> dict:
         raise ConfigError(f"{path} is not valid JSON: {exc}") from None
     if not isinstance(raw, dict):
         raise ConfigError(f"{path} must hold a JSON object")
-    return raw
+    return merge_generation_config(raw, model_dir)
+
+
+def merge_generation_config(raw: dict, model_dir: str) -> dict:
+    """``generation_config.json`` beside config.json names the token ids that generation really uses; where
+    it gives ``bos_token_id`` or ``eos_token_id`` (a number, or a list of numbers) they replace config.json's,
+    as in celeg (src/checkpoint/catalog.cpp:95-123). A file that cannot be read as JSON is ignored there, and
+    here."""
+    path = os.path.join(model_dir, "generation_config.json")
+    if not os.path.isfile(path):
+        return raw
+    try:
+        with open(path, "r", encoding="utf-8") as handle:
+            generation = json.load(handle)
+    except (OSError, ValueError):
+        return raw
+    if not isinstance(generation, dict):
+        return raw
+    merged = dict(raw)
+    for key in ("bos_token_id", "eos_token_id"):
+        value = generation.get(key)
+        if isinstance(value, bool):
+            continue
+        if isinstance(value, (int, float)):
+            merged[key] = int(value)
+        elif isinstance(value, list):
+            ids = [int(item) for item in value if isinstance(item, (int, float)) and not isinstance(item, bool)]
+            if ids:
+                merged[key] = ids
+    return merged

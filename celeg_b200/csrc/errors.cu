@@ -26,21 +26,18 @@ int check_launch(const char* what) {
     return 0;
 }
 
-static int g_chaining = -1;
+static int g_chaining = 7;
 
 // bit 0: small-batch products, bit 1: norms, bit 2: every other chained kernel (default: all)
-bool chaining_enabled(int kernel_class) {
-    if (g_chaining < 0) {
-        const char* env = getenv("CELEG_B200_CHAINED_LAUNCH");
-        g_chaining = env ? atoi(env) : 7;
-    }
-    return (g_chaining >> kernel_class) & 1;
-}
+bool chaining_enabled(int kernel_class) { return (g_chaining >> kernel_class) & 1; }
 
 }  // namespace celeg_b200
 
 // A bit per class of kernels (see chaining_enabled): set = launched with programmatic stream serialization.
-CELEG_API void celeg_set_chained_launch(int mask) { celeg_b200::g_chaining = mask; }
+// One setting for the whole process (for measurements); every kernel launched that way waits with
+// griddepcontrol.wait before its first access to memory that an earlier kernel writes, so both settings
+// compute the same.
+CELEG_API void celeg_set_chained_launch(int mask) { celeg_b200::g_chaining = mask & 7; }
 
 CELEG_API const char* celeg_last_error() { return celeg_b200::g_error; }
 

@@ -490,8 +490,9 @@ using namespace celeg_b200;
 // epilogue 0: c bfloat16; 1: c float32; 2: b holds n gate rows then n up rows, c bfloat16 [m, n] =
 // silu(a gate^T) * (a up^T). k, lda and ldb must be multiples of 8 (16-byte rows for TMA); operands
 // 16-byte aligned. error_flag (device int) receives a code if a bounded wait inside the kernel ran out.
+// forced_variant: -1 = the kernel is chosen from the shape, 0..3 = that one (for measurements).
 CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb, void* c, int ldc, int m, int n, int k,
-                                 int epilogue, int* error_flag, cudaStream_t stream) {
+                                 int epilogue, int* error_flag, int forced_variant, cudaStream_t stream) {
     CELEG_REQUIRE(m > 0 && n > 0 && k > 0, "gemm_tcgen05: invalid sizes m=%d n=%d k=%d", m, n, k);
     CELEG_REQUIRE(k % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && lda >= k && ldb >= k,
                   "gemm_tcgen05: k=%d, lda=%d and ldb=%d must be multiples of 8 and cover k", k, lda, ldb);
@@ -501,13 +502,9 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
     CELEG_REQUIRE((m + kTileM - 1) / kTileM <= 65535, "gemm_tcgen05: %d rows exceed one launch", m);
     // Which kernel: many rows -> the persistent kernel (128 x 256 tiles, epilogue hidden under the next
     // tile); few rows -> 128 x 128 tiles with two blocks per SM, which gives more blocks to spread the
-    // weight stream over. CELEG_B200_TC_VARIANT = 0..3 forces one (for measurements).
-    static int forced = -2;
-    if (forced == -2) {
-        const char* env = getenv("CELEG_B200_TC_VARIANT");
-        forced = env ? atoi(env) : -1;
-    }
-    const int variant = forced >= 0 ? forced : (m >= 512 ? 3 : 1);
+    // weight stream over.
+    CELEG_REQUIRE(forced_variant >= -1 && forced_variant <= 3, "gemm_tcgen05: unknown variant %d", forced_variant);
+    const int variant = forced_variant >= 0 ? forced_variant : (m >= 512 ? 3 : 1);
     const int bn = variant >= 2 ? 256 : 128;
     CUtensorMap map_a, map_b;
     if (!tensor_map_for(a, m, k, lda, kTileM, &map_a)) return -3;

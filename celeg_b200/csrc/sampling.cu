@@ -57,6 +57,20 @@ __device__ __forceinline__ float penalised(const float* logits, const uint8_t* s
     return v;
 }
 
+// Order-preserving key of a score: a larger float gives a larger unsigned key. NaN gives 0 and is never a
+// candidate (no comparison with it holds in celeg's selection either).
+__device__ __forceinline__ unsigned score_key(float v) {
+    if (v != v) return 0u;
+    if (v == 0.0f) return 0x80000000u;                 // -0 and +0 are one score
+    const unsigned u = __float_as_uint(v);
+    const unsigned key = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return key == 0u ? 1u : key;
+}
+
+// One block per row. The k best (score descending, then token ascending) are found by a radix selection over
+// the scores' keys instead of k arg-max passes: four passes of 8 bits give the k-th largest key, a fifth pass
+// gathers everything above it and the ties at it with the lowest token ids, and the k candidates are ranked
+// among themselves. The vocabulary is read five or six times from the L2 instead of k times.
 __global__ void sample_kernel(const float* logits, long long ld, int vocab,
                               const int* row_slot, uint8_t* seen_base,
                               unsigned long long* rng, const float* temperature,
@@ -65,6 +79,10 @@ __global__ void sample_kernel(const float* logits, long long ld, int vocab,
     __shared__ Best scratch[33];
     __shared__ float cand_score[kMaxTopK];
     __shared__ int cand_token[kMaxTopK];
+    __shared__ float sorted_score[kMaxTopK];
+    __shared__ int sorted_token[kMaxTopK];
+    __shared__ unsigned hist[256];
+    __shared__ unsigned s_prefix, s_remaining, s_count, s_ties;
     chain_release();
     chain_wait();
     const int row = blockIdx.x;
@@ -76,56 +94,133 @@ __global__ void sample_kernel(const float* logits, long long ld, int vocab,
     int k = top_k ? top_k[row] : 1;
     const bool greedy = temp <= 0.0f || k == 1;
     k = greedy ? 1 : min(min(k, kMaxTopK), vocab);
+    auto score_of = [&](int token) {
+        float v = penalised(l, seen, token, pen);
+        if (!greedy) v = v / temp;
+        return v;
+    };
 
-    float prev_score = INFINITY;
-    int prev_token = -1;
-    for (int pick = 0; pick < k; ++pick) {
-        Best mine{0.0f, -1};
+    // the k-th largest key, 8 bits at a time from the top
+    if (threadIdx.x == 0) {
+        s_prefix = 0u;
+        s_remaining = (unsigned)k;
+    }
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
+        __syncthreads();
+        const unsigned prefix = s_prefix;
         for (int token = threadIdx.x; token < vocab; token += blockDim.x) {
-            float v = penalised(l, seen, token, pen);
-            if (!greedy) v = v / temp;
-            // only candidates that come after the previous pick in (score desc, token asc) order
-            if (pick > 0 && !better(prev_score, prev_token, v, token)) continue;
-            if (mine.token < 0 || better(v, token, mine.score, mine.token)) {
-                mine.score = v;
-                mine.token = token;
+            const unsigned key = score_key(score_of(token));
+            if (key == 0u) continue;
+            if (shift == 24 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned remaining = s_remaining, bin = 0u;
+            if (shift == 24) {
+                // fewer candidates than k (NaNs, or a tiny vocabulary): take all there are
+                unsigned have = 0u;
+                for (int i = 0; i < 256; ++i) have += hist[i];
+                remaining = min(remaining, have);
+            }
+            if (remaining > 0u) {
+                for (int i = 255; i >= 0; --i) {
+                    if (hist[i] >= remaining) {
+                        bin = (unsigned)i;
+                        break;
+                    }
+                    remaining -= hist[i];
+                }
+            }
+            s_prefix = prefix | (bin << shift);
+            s_remaining = remaining;
+            s_ties = hist[bin];
+        }
+        __syncthreads();
+        if (shift == 24 && s_remaining == 0u) break;    // nothing but NaN in the row
+    }
+    const unsigned threshold = s_prefix;
+    const unsigned need_ties = s_remaining;             // how many of the keys equal to the threshold belong to the k
+    const unsigned ties = s_ties;
+    __syncthreads();
+    if (threadIdx.x == 0) s_count = 0u;
+    __syncthreads();
+    if (need_ties > 0u) {
+        // everything above the threshold, and the ties when all of them are wanted
+        for (int token = threadIdx.x; token < vocab; token += blockDim.x) {
+            const float v = score_of(token);
+            const unsigned key = score_key(v);
+            if (key > threshold || (key == threshold && ties == need_ties)) {
+                const unsigned at = atomicAdd(&s_count, 1u);
+                if (at < (unsigned)kMaxTopK) {
+                    cand_score[at] = v;
+                    cand_token[at] = token;
+                }
             }
         }
-        const Best best = block_best(mine, scratch);
-        if (threadIdx.x == 0) {
-            cand_score[pick] = best.score;
-            cand_token[pick] = best.token;
+        __syncthreads();
+        if (ties != need_ties) {
+            // more equal scores at the threshold than places left: the lowest token ids among them, one by one
+            int previous = -1;
+            for (unsigned pick = 0; pick < need_ties; ++pick) {
+                Best mine{0.0f, -1};
+                for (int token = threadIdx.x; token < vocab; token += blockDim.x) {
+                    if (token <= previous) continue;
+                    const float v = score_of(token);
+                    if (score_key(v) != threshold) continue;
+                    if (mine.token < 0 || token < mine.token) {
+                        mine.score = v;
+                        mine.token = token;
+                    }
+                }
+                // block_best orders by score first; the scores are equal here, so the lower token wins
+                const Best best = block_best(mine, scratch);
+                if (threadIdx.x == 0 && best.token >= 0) {
+                    const unsigned at = s_count++;
+                    if (at < (unsigned)kMaxTopK) {
+                        cand_score[at] = best.score;
+                        cand_token[at] = best.token;
+                    }
+                }
+                previous = best.token;
+                if (best.token < 0) break;
+            }
+            __syncthreads();
         }
-        prev_score = best.score;
-        prev_token = best.token;
-        if (best.token < 0) {            // fewer distinct candidates than k (NaNs): stop here
-            k = pick;
-            break;
-        }
+    }
+    k = min((int)s_count, kMaxTopK);
+    // rank the candidates among themselves: score descending, then token ascending
+    for (int i = threadIdx.x; i < k; i += blockDim.x) {
+        const float sc = cand_score[i];
+        const int tk = cand_token[i];
+        int rank = 0;
+        for (int j = 0; j < k; ++j) rank += better(cand_score[j], cand_token[j], sc, tk) ? 1 : 0;
+        sorted_score[rank] = sc;
+        sorted_token[rank] = tk;
     }
     __syncthreads();
     if (threadIdx.x != 0) return;
     int chosen;
     if (greedy || k <= 1) {
-        chosen = k >= 1 ? cand_token[0] : 0;
+        chosen = k >= 1 ? sorted_token[0] : 0;
     } else {
-        const float maximum = cand_score[0];
+        const float maximum = sorted_score[0];
         float total = 0.0f;
         for (int i = 0; i < k; ++i) {
-            cand_score[i] = expf(cand_score[i] - maximum);
-            total += cand_score[i];
+            sorted_score[i] = expf(sorted_score[i] - maximum);
+            total += sorted_score[i];
         }
-        for (int i = 0; i < k; ++i) cand_score[i] /= total;
+        for (int i = 0; i < k; ++i) sorted_score[i] /= total;
         int active = k;
         const float p = top_p ? top_p[row] : 1.0f;
         if (p < 1.0f) {
             float cumulative = 0.0f;
             active = 0;
             do {
-                cumulative += cand_score[active++];
+                cumulative += sorted_score[active++];
             } while (active < k && cumulative < p);
             total = 0.0f;
-            for (int i = 0; i < active; ++i) total += cand_score[i];
+            for (int i = 0; i < active; ++i) total += sorted_score[i];
         } else {
             total = 1.0f;
         }
@@ -137,11 +232,11 @@ __global__ void sample_kernel(const float* logits, long long ld, int vocab,
         const unsigned long long bits = state * 2685821657736338717ULL;
         const float unit = (float)(((double)(bits >> 11) + 0.5) * (1.0 / 9007199254740992.0));
         float target = unit * total;
-        chosen = cand_token[active - 1];
+        chosen = sorted_token[active - 1];
         for (int i = 0; i < active; ++i) {
-            target -= cand_score[i];
+            target -= sorted_score[i];
             if (target <= 0.0f) {
-                chosen = cand_token[i];
+                chosen = sorted_token[i];
                 break;
             }
         }

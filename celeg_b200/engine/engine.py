@@ -10,6 +10,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Tuple, Union
 
 import torch
 
+from ..parts.options import KernelOptions
 from ..sampling import Sampler, SamplingParams
 from .loading import LoadedModel, load_model
 from .scheduler import (EngineOptions, Metrics, PollResult, RequestOptions, RequestStatus, Scheduler,
@@ -88,7 +89,8 @@ class _Runner:
 
 class Engine:
     def __init__(self, model_path: str, max_context: Optional[int] = None, dtype="bfloat16", device="cuda:0",
-                 options: Optional[EngineOptions] = None, use_cuda_graph: bool = True):
+                 options: Optional[EngineOptions] = None, use_cuda_graph: bool = True,
+                 kernel_options: Optional[KernelOptions] = None):
         self.options = options or EngineOptions()
         self.options.validate()
         opts = self.options
@@ -97,10 +99,12 @@ class Engine:
         self.loaded = load_model(model_path, dtype=dtype, device=device, max_context=probe_context,
                                  cache_tokens=cache_tokens, page_tokens=opts.page_tokens,
                                  max_requests=opts.max_active_requests,
-                                 max_batched_tokens=opts.max_batched_tokens, use_graphs=use_cuda_graph)
+                                 max_batched_tokens=opts.max_batched_tokens, use_graphs=use_cuda_graph,
+                                 kernel_options=kernel_options)
         self.device = self.loaded.runtime.device
         self.max_context = self.loaded.step.max_context
-        self.sampler = Sampler(self.loaded.model.vocab_size, opts.max_active_requests,
+        # (one slot more than the manager gives out: the storage's spare slot, see CacheStorage)
+        self.sampler = Sampler(self.loaded.model.vocab_size, opts.max_active_requests + 1,
                                opts.max_active_requests, self.device)
         self.scheduler = Scheduler(self.loaded.manager, _Runner(self.loaded, self.sampler), opts,
                                    self.max_context, self.loaded.model.vocab_size,

@@ -9,8 +9,10 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage
+from ..config.fingerprint import model_fingerprint
 from ..config.registry import architecture_of, read_config_json
 from ..parts import Runtime
+from ..parts.options import KernelOptions
 from ..weights.loader import load_tensors
 from ..weights.safetensors_io import TensorRepository
 from .model import Model
@@ -42,26 +44,32 @@ class LoadedModel:
     manager: CacheManager
     storage: CacheStorage
     step: StepFunction
+    fingerprint: str = ""            # hash of the resolved configuration and every tensor's name, shape and type
 
 
 def load_model(model_dir: str, dtype="bfloat16", device="cuda:0", *, max_context: Optional[int] = None,
                cache_tokens: Optional[int] = None, page_tokens: int = DEFAULT_PAGE_TOKENS,
-               max_requests: int = 8, max_batched_tokens: int = 512, use_graphs: bool = False) -> LoadedModel:
+               max_requests: int = 8, max_batched_tokens: int = 512, use_graphs: bool = False,
+               kernel_options: Optional[KernelOptions] = None) -> LoadedModel:
     """``cache_tokens``: how many positions all live requests may hold together (each request
-    rounded up to whole pages); default ``max_requests * max_context``."""
+    rounded up to whole pages); default ``max_requests * max_context``. ``kernel_options``: the
+    switches of the kernel path (defaults: what measured best)."""
     dtype = parse_dtype(dtype)
     device = torch.device(device)
     raw = read_config_json(model_dir)
     architecture = architecture_of(raw)
     repository = TensorRepository(model_dir)
     try:
-        config = architecture.resolve_config(architecture.parse_config(raw), repository.shapes())
+        shapes = repository.shapes()
+        config = architecture.resolve_config(architecture.parse_config(raw), shapes)
         spec = architecture.build_spec(config)
         tensors = load_tensors(repository, spec)
+        fingerprint = fingerprint_of(config, raw, repository)
     finally:
         repository.close()
     context = min(max_context or spec.max_context, spec.max_context) if max_context else spec.max_context
-    rt = Runtime(device, dtype, max_batched_tokens, max_requests=max_requests, max_context=context)
+    rt = Runtime(device, dtype, max_batched_tokens, max_requests=max_requests, max_context=context,
+                 options=kernel_options)
     with torch.cuda.device(device):
         model = Model(spec, tensors, rt)
         del tensors
@@ -80,4 +88,12 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0", *, max_context
         step = StepFunction(model, manager, storage, rt, max_batched_tokens, max_requests, context,
                             use_graphs=use_graphs)
     return LoadedModel(config=config, spec=spec, model=model, runtime=rt, manager=manager, storage=storage,
-                       step=step)
+                       step=step, fingerprint=fingerprint)
+
+
+def fingerprint_of(config, raw: dict, repository: TensorRepository) -> str:
+    """The model's fingerprint from its resolved configuration (``to_dict()`` where the architecture's
+    configuration has one, else config.json as read) and the checkpoint's tensor table."""
+    as_dict = config.to_dict() if hasattr(config, "to_dict") else dict(raw)
+    shapes = repository.shapes()
+    return model_fingerprint(as_dict, shapes, {name: repository.stored_dtype(name) for name in shapes})

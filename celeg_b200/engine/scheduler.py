@@ -17,7 +17,6 @@ preempting one request instead of stalling (see :meth:`Scheduler._break_deadlock
 from __future__ import annotations
 
 import enum
-import os
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -56,6 +55,8 @@ class EngineOptions:
     page_tokens: int = 16
     logical_kv_pages: int = 0                    # 0: ceil(max_context / page_tokens) * max_active_requests
     scheduler_policy: SchedulerPolicy = SchedulerPolicy.GUARANTEED_NO_EVICT
+    # while every live request decodes, enqueue the step after the one whose tokens are being read (not in celeg)
+    run_ahead: bool = True
 
     def validate(self) -> None:
         for name in ("max_active_requests", "max_batched_tokens", "prefill_chunk_tokens", "page_tokens"):
@@ -187,10 +188,8 @@ class Scheduler:
         self._next_id = 1
         self._hold_admission = False      # set by a preemption: the freed pages go to the others first
         self._inflight = None             # (plan, handle) of a step that was enqueued and not yet collected
-        # one step of run-ahead needs a runner that can enqueue without waiting; CELEG_B200_RUN_AHEAD=0
-        # turns it off (for comparisons)
-        self._runs_ahead = (hasattr(runner, "launch") and hasattr(runner, "collect")
-                            and os.environ.get("CELEG_B200_RUN_AHEAD", "1") != "0")
+        # one step of run-ahead needs a runner that can enqueue without waiting
+        self._runs_ahead = options.run_ahead and hasattr(runner, "launch") and hasattr(runner, "collect")
 
     # ------------------------------------------------------------------ public
     def submit(self, prompt: Sequence[int], options: Optional[RequestOptions] = None) -> int:

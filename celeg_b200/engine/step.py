@@ -164,7 +164,7 @@ class StepFunction:
             self.manager.reserve(cache, cache.tokens + len(entry.tokens))
 
         spans = len(entries)
-        all_decode = all(len(entry.tokens) == 1 for entry in entries)
+        all_decode = total == spans
         max_ctx = max(cache.tokens + len(entry.tokens) for entry, cache in zip(entries, caches))
         prompt_key = self._prompt_graph_key(entries, total, wanted, max_ctx) if not all_decode else None
         if (all_decode and self.use_graphs) or prompt_key is not None:
@@ -178,14 +178,17 @@ class StepFunction:
         self._host = self._ring[slot]
         self._host_np = self._ring_np[slot]
         checked = time.perf_counter()
-        step, logit_rows, n_words = self._stage(entries, caches, total, spans, wanted, stride, max_ctx)
+        # a decoding step that will be replayed from a graph takes a launch shape from a short list, so that
+        # a batch that shrinks request by request does not capture a graph for every size
+        padded = self._graph_rows(spans) if (all_decode and self.use_graphs and wanted <= self.max_spans) else spans
+        step, logit_rows, n_words = self._stage(entries, caches, total, spans, wanted, stride, max_ctx, padded)
         self._dev[:n_words].copy_(self._host[:n_words], non_blocking=True)
         if token_source is not None:
             # the tokens of this step are on the device already (what the step before drew): token i of
             # the step is token_source[i]; the entries carry placeholders
             if token_source.dtype != torch.int32 or token_source.numel() < total:
                 raise StepInputError("a token source must hold one int32 token for every token of the step")
-            step.token_ids.copy_(token_source[:total], non_blocking=True)
+            step.token_ids[:total].copy_(token_source[:total], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self._ring_events[slot] = event
@@ -199,7 +202,7 @@ class StepFunction:
                 self._wide_logits = torch.empty((wanted, vocab), dtype=torch.float32, device=self.rt.device)
             logits = self._wide_logits
 
-        graph_key = (spans, wanted, _context_bucket(max_ctx)) if (all_decode and self.use_graphs and wanted <= self.max_spans) else prompt_key
+        graph_key = (padded, wanted, _context_bucket(max_ctx)) if (all_decode and self.use_graphs and wanted <= self.max_spans) else prompt_key
         if graph_key is not None:
             self._run_graphed(graph_key, step, logit_rows, wanted, logits)
         else:
@@ -260,10 +263,25 @@ class StepFunction:
         kernels.LAUNCHES += self._graph_launches[key]      # kernels of this package inside the graph
         self.kernel_steps_graphed += 1
 
-    def _stage(self, entries, caches, total, spans, wanted, stride, max_ctx):
+    def _graph_rows(self, spans: int) -> int:
+        """The number of rows a graphed decoding step of ``spans`` requests is launched with: 1, 2, 4, 8, 12 or
+        16 (the small-batch kernels work on 8 or 16 rows whatever the number), then the next multiple of 8,
+        beyond 64 of 32."""
+        if spans <= 16:
+            rows = next(n for n in (1, 2, 4, 8, 12, 16) if n >= spans)
+        else:
+            rows = (spans + 7) // 8 * 8 if spans <= 64 else (spans + 31) // 32 * 32
+        return rows if rows <= self.max_spans else spans
+
+    def _stage(self, entries, caches, total, spans, wanted, stride, max_ctx, padded=None):
         """Fill the pinned staging buffer; returns the StepContext, the logit-row tensor and the
         number of int32 words to copy. The layout depends only on (T, R, F, stride), so steps of
-        the same shape use the same device addresses."""
+        the same shape use the same device addresses. ``padded`` > spans (decoding steps only): rows are
+        added up to that number; they carry token 0 at position 0 of the storage's spare page and slot,
+        their logits are never asked for."""
+        real_spans = spans
+        if padded is not None and padded > spans:
+            total = spans = padded
         host = self._host_np
         offsets = {}
         cursor = 0
@@ -287,11 +305,15 @@ class StepFunction:
         lengths = []
         if total == spans:
             # every request brings one token (a decode step): fill whole arrays at once
-            token_ids[:] = [entry.tokens[0] for entry in entries]
-            positions[:] = [cache.tokens for cache in caches]
+            token_ids[:real_spans] = [entry.tokens[0] for entry in entries]
+            positions[:real_spans] = [cache.tokens for cache in caches]
             token_span[:] = range(spans)
             span_begin[:spans] = range(spans)
-            span_slot[:] = [cache.slot for cache in caches]
+            span_slot[:real_spans] = [cache.slot for cache in caches]
+            if real_spans < spans:
+                token_ids[real_spans:] = 0
+                positions[real_spans:] = 0
+                span_slot[real_spans:] = self.storage.scratch_slot
             for index, entry in enumerate(entries):
                 if entry.want:
                     logit_rows_host[out] = index
@@ -303,6 +325,8 @@ class StepFunction:
                     table = cache.table_array(g)
                     used = min(table.shape[0], stride)
                     grid[index, :used] = table[:used]
+                if real_spans < spans:
+                    grid[real_spans:, 0] = self.storage.scratch_pages[g]
             lengths = [1] * spans
             row = spans
         else:

@@ -9,7 +9,7 @@ Input, one JSON object a line:
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
 For a step in which something is wanted, ``<out>/<step>.f32`` holds the logits at the wanted
 places, little-endian float32 [wanted, vocab]. After every step a line ``done <step>`` is
-printed and flushed.
+printed and flushed. ``<out>/model.json`` names the model that made the files (its fingerprint).
 """
 from __future__ import annotations
 
@@ -39,6 +39,9 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[
     loaded = load_model(model_dir, dtype=dtype, device=device, cache_tokens=max_tokens, page_tokens=page_tokens,
                         max_requests=max_requests, max_batched_tokens=batch_limit)
     step_fn = loaded.step
+    with open(os.path.join(out_dir, "model.json"), "w", encoding="utf-8") as handle:
+        json.dump({"model_fingerprint": loaded.fingerprint, "dtype": str(dtype),
+                   "vocab_size": loaded.model.vocab_size}, handle)
     for line in lines:
         line = line.strip()
         if not line:

@@ -69,9 +69,7 @@ _SIGNATURES = {
     "celeg_embedding_split_norm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
                                    c_void_p, c_int, c_void_p],
     "celeg_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                           c_void_p],
-    "celeg_gemm_stream": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                          c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p],
+                           c_int, c_void_p],
     "celeg_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -362,34 +360,6 @@ def gemv_bf16(x, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_S
         prepare.sumsq.stride(0) if prepare else 0, _stream()))
 
 
-STREAM_MAX_ROWS = 64
-
-
-def gemm_stream_supported(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Shapes the weight-streaming tcgen05 product takes (up to 64 rows of activations)."""
-    return (0 < rows <= STREAM_MAX_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-
-
-def gemm_stream(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int, error_flag: torch.Tensor, *,
-                conv_w: Optional[torch.Tensor] = None, taps: int = 0, state: Optional[torch.Tensor] = None,
-                slot_stride: int = 0, span_slot: Optional[torch.Tensor] = None) -> None:
-    """y[:rows] = epilogue(x[:rows] @ w.T) for up to 64 rows on tcgen05 tensor cores, the weights streamed
-    once by TMA, the k range split over a thread-block cluster. Modes as :func:`gemv_bf16`
-    (GEMV_STORE ... GEMV_CONV)."""
-    sets = {GEMV_SWIGLU: 2, GEMV_CONV: 3}.get(mode, 1)
-    n = w.shape[0] // sets
-    k = w.shape[1]
-    assert x.shape[-1] == k and y.shape[-1] >= n
-    want = torch.float32 if mode in (GEMV_STORE_F32, GEMV_ADD_RESIDUAL) else torch.bfloat16
-    if y.dtype != want:
-        raise KernelLibraryError(f"gemm_stream mode {mode} writes {want}, got {y.dtype}")
-    _check(library().celeg_gemm_stream(_ptr(x), x.stride(0), x.shape[0], _ptr(w), w.stride(0), _ptr(y), y.stride(0),
-                                       rows, n, k, mode, _ptr(conv_w), taps, _ptr(state), slot_stride,
-                                       _ptr(span_slot), _ptr(error_flag), _stream()))
-
-
 TC_STORE, TC_STORE_F32, TC_SWIGLU = 0, 1, 2
 
 
@@ -399,10 +369,11 @@ def gemm_tcgen05_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, epilogue: int,
-                 error_flag: torch.Tensor) -> None:
+                 error_flag: torch.Tensor, variant: int = -1) -> None:
     """y[:rows] = x[:rows] @ w.T on tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
     TC_STORE: y bfloat16; TC_STORE_F32: y float32; TC_SWIGLU: w is [2*inner, k] (gate rows, then up rows),
-    y bfloat16 [rows, inner] = silu(gate) * up."""
+    y bfloat16 [rows, inner] = silu(gate) * up. ``variant``: -1 lets the library choose the tile shape,
+    0..3 force one (128x128 with 6 or 3 stages, 128x256, persistent with two accumulators)."""
     n = w.shape[0] // 2 if epilogue == TC_SWIGLU else w.shape[0]
     k = w.shape[1]
     want = torch.float32 if epilogue == TC_STORE_F32 else torch.bfloat16
@@ -410,7 +381,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, e
         raise KernelLibraryError(f"gemm_tcgen05 epilogue {epilogue} writes {want}, got {y.dtype}")
     assert x.shape[-1] == k and y.shape[-1] >= n
     _check(library().celeg_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(y), y.stride(0), rows, n, k,
-                                        epilogue, _ptr(error_flag), _stream()))
+                                        epilogue, _ptr(error_flag), int(variant), _stream()))
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, tokens: int, inner: int) -> None:

@@ -1,5 +1,6 @@
 """Parts a model is put together from, and their registries."""
 from .registry import CATEGORIES, part_factory, register_part, registered
+from .options import KernelOptions
 from .runtime import Runtime, StepContext
 from . import norms, positions, mixers, feed_forward, arrangement  # register the built-in kinds
 from .mixers import AttentionMixer, PagedBinding, ShortConvMixer, StateBinding
@@ -8,6 +9,6 @@ from .positions import SplitHalfRope
 from .feed_forward import SwiGluFeedForward
 from .arrangement import PreNormResidual
 
-__all__ = ["CATEGORIES", "part_factory", "register_part", "registered", "Runtime", "StepContext",
+__all__ = ["CATEGORIES", "part_factory", "register_part", "registered", "KernelOptions", "Runtime", "StepContext",
            "AttentionMixer", "PagedBinding", "ShortConvMixer", "StateBinding", "RmsNorm", "SplitHalfRope",
            "SwiGluFeedForward", "PreNormResidual"]

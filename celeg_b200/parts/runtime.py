@@ -2,13 +2,13 @@
 matrix product, and the description of the step being run."""
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
 import torch
 
 from .. import kernels
+from .options import KernelOptions
 
 
 class _Sink:
@@ -96,7 +96,8 @@ class Runtime:
     rotation angles and conv state in float32)."""
 
     def __init__(self, device: torch.device, act_dtype: torch.dtype, max_tokens: int, max_requests: int = 8,
-                 max_context: int = 4096):
+                 max_context: int = 4096, options: Optional[KernelOptions] = None):
+        options = options or KernelOptions()
         if act_dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"dtype must be float32 or bfloat16, got {act_dtype}")
         self.device = torch.device(device)
@@ -106,32 +107,23 @@ class Runtime:
         self.max_tokens = max_tokens
         self.max_requests = max_requests
         self.max_context = max_context
-        self.fuse_small_batches = True       # decode steps of few rows run the fused products
-        # Products of more than 16 rows: "swiglu" = the gate|up product with its activation runs on this
-        # package's tcgen05 kernel (faster than the library product followed by the activation kernel),
-        # the others on cuBLAS; "all" = every product on the tcgen05 kernel; "none" = cuBLAS only; "stream" =
-        # as "swiglu", and products of 17 to 128 rows on the weight-streaming tcgen05 kernel (slower than the
-        # library product as it stands; kept selectable for measurements).
-        self.tensor_core_products = os.environ.get("CELEG_B200_TC_PRODUCTS", "swiglu")
-        # below this many rows the library product followed by the activation kernel still wins: few rows
-        # mean few 128-row tiles in too few waves. Measured, 2,048 prompt tokens in portions of 256 / 512 / 1,024 /
-        # 1,536 / 2,048 rows: 9.70 / 6.51 / 4.66 / 4.84 / 3.99 ms with this package's kernel against 9.34 / 6.15 /
-        # 4.59 / 4.76 / 4.13 ms with the library's (at 64 rows: 1.36 against 1.15 ms per decode step)
-        self.tensor_core_min_rows = 2048
-        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.sink: Optional[_Sink] = None         # set by the residual stream around a part's forward
-        self.sink_residual: Optional[torch.Tensor] = None
-        self.split_norms = os.environ.get("CELEG_B200_SPLIT_NORM", "1") != "0"
-        # decode steps: q/k norm + rotation + cache write inside the attention kernel (0: a kernel of their own)
-        self.fuse_decode_qk = os.environ.get("CELEG_B200_FUSE_DECODE_QK", "1") != "0"
-        # prompt-portion attention of head size 64 on tcgen05 (0: the mma.sync kernel, for comparisons)
-        self.tcgen05_attention = os.environ.get("CELEG_B200_TC_ATTENTION", "1") != "0"
+        options.validate()
+        self.options = options
+        self.fuse_small_batches = options.fuse_small_batches
+        self.tensor_core_products = options.tensor_core_products
+        self.tensor_core_min_rows = options.tensor_core_min_rows
+        self.tensor_core_variant = options.tensor_core_variant
+        self.split_norms = options.split_norms
+        self.fuse_decode_qk = options.fuse_decode_qk
+        self.tcgen05_attention = options.tcgen05_attention
         # Decode steps are a chain of short weight-streaming kernels, the same chain every step. Each of them
         # asks the first megabytes of its successor's weights into the L2, so that memory works across the
         # kernel boundary; the successor of a weight is learnt from the order of the calls (the first step of
-        # a shape runs outside graph capture). 0 switches it off. Measured at batch 8 with LFM2-1.2B sizes:
-        # 0.736 ms a step without, 0.723 with 4 MiB, 0.714 with 8, 0.734 with 16, 0.753 with 32.
-        self.prefetch_bytes = int(float(os.environ.get("CELEG_B200_PREFETCH_MB", "8")) * (1 << 20))
+        # a shape runs outside graph capture).
+        self.prefetch_bytes = int(options.prefetch_mb * (1 << 20))
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.sink: Optional[_Sink] = None         # set by the residual stream around a part's forward
+        self.sink_residual: Optional[torch.Tensor] = None
         self._weight_after: Dict[int, Tuple[int, int]] = {}
         self._streamed_last: Optional[int] = None
         self._flat: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
@@ -215,15 +207,10 @@ class Runtime:
                               ahead=self._ahead(weight))
         elif split:
             raise kernels.KernelLibraryError("an operand without its row scale reached a product that cannot apply it")
-        elif (self.tensor_core_products == "stream" and rows <= kernels.STREAM_MAX_ROWS
-              and kernels.gemm_stream_supported(rows, x, weight)):
-            kernels.gemm_stream(x, weight, out, rows,
-                                kernels.GEMV_STORE_F32 if out.dtype == torch.float32 else kernels.GEMV_STORE,
-                                self.error_flag)
         elif self.tensor_core_products == "all" and kernels.gemm_tcgen05_supported(x, weight):
             kernels.gemm_tcgen05(x, weight, out, rows,
                                  kernels.TC_STORE_F32 if out.dtype == torch.float32 else kernels.TC_STORE,
-                                 self.error_flag)
+                                 self.error_flag, self.tensor_core_variant)
         elif out.dtype == torch.float32:
             torch.mm(x[:rows], weight.t(), out_dtype=torch.float32, out=out[:rows])
         else:
@@ -240,14 +227,11 @@ class Runtime:
         if self.act_dtype == torch.bfloat16 and kernels.gemv_supported(rows, operand, gate_up_weight):
             kernels.gemv_bf16(x, gate_up_weight, out, rows, kernels.GEMV_SWIGLU, ahead=self._ahead(gate_up_weight))
             return
-        if (self.act_dtype == torch.bfloat16 and self.tensor_core_products == "stream"
-                and rows <= kernels.STREAM_MAX_ROWS and kernels.gemm_stream_supported(rows, x, gate_up_weight)):
-            kernels.gemm_stream(x, gate_up_weight, out, rows, kernels.GEMV_SWIGLU, self.error_flag)
-            return
         if (self.act_dtype == torch.bfloat16 and kernels.gemm_tcgen05_supported(x, gate_up_weight)
                 and (self.tensor_core_products == "all"
-                     or (self.tensor_core_products in ("swiglu", "stream") and rows >= self.tensor_core_min_rows))):
-            kernels.gemm_tcgen05(x, gate_up_weight, out, rows, kernels.TC_SWIGLU, self.error_flag)
+                     or (self.tensor_core_products == "swiglu" and rows >= self.tensor_core_min_rows))):
+            kernels.gemm_tcgen05(x, gate_up_weight, out, rows, kernels.TC_SWIGLU, self.error_flag,
+                                 self.tensor_core_variant)
             return
         self.linear(x, gate_up_weight, scratch, rows)
         kernels.swiglu(scratch, out, rows, inner)

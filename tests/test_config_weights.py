@@ -207,3 +207,60 @@ def test_malformed_containers_are_refused(tmp_path, case):
 def test_missing_checkpoint_is_reported(tmp_path):
     with pytest.raises(CheckpointFormatError):
         TensorRepository(str(tmp_path))
+
+
+def test_generation_config_overrides_stop_ids(tmp_path):
+    """celeg lets generation_config.json replace bos/eos (src/checkpoint/catalog.cpp:95-123): a number or a
+    list of numbers; other keys and unreadable files change nothing."""
+    from celeg_b200.config.registry import read_config_json
+    folder = tmp_path / "m"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(TINY_A))
+    assert Lfm2Config.from_dict(read_config_json(str(folder))).eos_token_ids == (7,)
+    (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": [7, 2, 11], "bos_token_id": 5,
+                                                               "pad_token_id": 3, "temperature": 0.3}))
+    config = Lfm2Config.from_dict(read_config_json(str(folder)))
+    assert config.eos_token_ids == (7, 2, 11) and config.bos_token_id == 5 and config.pad_token_id == 0
+    (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": 9}))
+    assert Lfm2Config.from_dict(read_config_json(str(folder))).eos_token_ids == (9,)
+    (folder / "generation_config.json").write_text("{ not json")
+    assert Lfm2Config.from_dict(read_config_json(str(folder))).eos_token_ids == (7,)
+    (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": []}))
+    assert Lfm2Config.from_dict(read_config_json(str(folder))).eos_token_ids == (7,)
+
+
+def test_fingerprint_follows_configuration_and_tensor_table(tmp_path):
+    """Equal for the same architecture and sizes whatever the weights' values; different as soon as a size, an
+    option or a tensor's shape or stored type differs."""
+    from celeg_b200.config.fingerprint import model_fingerprint
+    from celeg_b200.config.registry import read_config_json
+    from celeg_b200.engine.loading import fingerprint_of
+
+    def of(folder):
+        raw = read_config_json(folder)
+        architecture = architecture_of(raw)
+        repository = TensorRepository(folder)
+        try:
+            config = architecture.resolve_config(architecture.parse_config(raw), repository.shapes())
+            return fingerprint_of(config, raw, repository)
+        finally:
+            repository.close()
+
+    a0 = str(tmp_path / "a0")
+    a1 = str(tmp_path / "a1")
+    b0 = str(tmp_path / "b0")
+    f32 = str(tmp_path / "f32")
+    eps = str(tmp_path / "eps")
+    write_random_model(a0, copy.deepcopy(TINY_A), 0)
+    write_random_model(a1, copy.deepcopy(TINY_A), 1)
+    write_random_model(b0, copy.deepcopy(TINY_B), 0)
+    write_random_model(f32, copy.deepcopy(TINY_A), 0, torch.float32)
+    other = copy.deepcopy(TINY_A)
+    other["norm_eps"] = 2e-5
+    write_random_model(eps, other, 0)
+    prints = {name: of(folder) for name, folder in (("a0", a0), ("a1", a1), ("b0", b0), ("f32", f32), ("eps", eps))}
+    assert all(len(value) == 64 and int(value, 16) >= 0 for value in prints.values())
+    assert prints["a0"] == prints["a1"]
+    assert len({prints["a0"], prints["b0"], prints["f32"], prints["eps"]}) == 4
+    shapes = {"w": (2, 3)}
+    assert model_fingerprint({"x": 1}, shapes, {"w": "BF16"}) != model_fingerprint({"x": 1}, {"w": (3, 2)}, {"w": "BF16"})

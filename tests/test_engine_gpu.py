@@ -629,8 +629,140 @@ def test_many_requests_through_a_small_pool(models):
     for request_id, prompt, n in list(zip(ids, prompts, new_tokens))[::3]:
         want = alone.generate(prompt, max_new_tokens=n, temperature=0.0, repetition_penalty=1.0, eos_tokens=())
         assert outputs[request_id] == want, request_id
+    for request_id, prompt, n in list(zip(ids, prompts, new_tokens))[1::7]:
+        assert outputs[request_id] == plain_lfm2.generate(config, weights, prompt, n, eos_tokens=()), request_id
     for request_id, n in zip(ids, new_tokens):
         assert len(outputs[request_id]) == n
+
+
+def test_seeded_sampling_survives_preemption(models):
+    """Temperature 0.8 with a seed per request through a pool so small that requests are preempted (pages and
+    slot given back, generator state kept, prompt + generated tokens prefilled again): every request still draws
+    exactly what it draws alone and what the plain sampler draws from the plain model's logits (float32)."""
+    from celeg_b200 import Engine, EngineOptions, RequestOptions, SamplingParams, SchedulerPolicy
+    folder, config, weights = models["B"]
+    rng = np.random.default_rng(42)
+    lengths = rng.integers(4, 50, size=12).tolist()
+    prompts = prompts_of(config["vocab_size"], lengths, seed=43)
+    new_tokens = rng.integers(6, 30, size=12).tolist()
+    options = EngineOptions(max_active_requests=4, max_batched_tokens=32, prefill_chunk_tokens=11, page_tokens=16,
+                            logical_kv_pages=8, scheduler_policy=SchedulerPolicy.MAX_UTILIZATION)
+    engine = Engine(folder, dtype="float32", options=options)
+
+    def params(i):
+        return SamplingParams(temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.1, seed=100 + i)
+
+    ids = [engine.submit(p, RequestOptions(max_new_tokens=n, eos_tokens=(), generation=params(i)))
+           for i, (p, n) in enumerate(zip(prompts, new_tokens))]
+    outputs = {i: [] for i in ids}
+    pending = set(ids)
+    steps = 0
+    while pending:
+        engine.step()
+        engine.loaded.manager.check_invariants()
+        for i in list(pending):
+            result = engine.poll(i)
+            outputs[i].extend(result.tokens)
+            if result.finished:
+                assert result.status.value == "finished", result.error
+                pending.discard(i)
+        steps += 1
+        assert steps < 3000
+    assert engine.metrics().preempted > 0, "the pool was meant to be too small for four live requests"
+    alone = Engine(folder, dtype="float32")
+    for index, (request_id, prompt, n) in enumerate(zip(ids, prompts, new_tokens)):
+        kwargs = dict(max_new_tokens=n, temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.1,
+                      seed=100 + index, eos_tokens=())
+        assert outputs[request_id] == alone.generate(prompt, **kwargs), f"request {index} against itself alone"
+        if index % 3 == 0:
+            want = plain_lfm2.generate(config, weights, prompt, n, temperature=0.8, top_k=40, top_p=0.95,
+                                       repetition_penalty=1.1, seed=100 + index)
+            assert outputs[request_id] == want, f"request {index} against the plain model"
+
+
+def test_worker_thread_serves_requests_submitted_from_other_threads(models):
+    """``Engine.start()`` runs the steps on a worker thread (celeg: src/runtime/concurrency/worker.cpp:48-67);
+    three client threads submit and poll meanwhile; ``stop()`` joins it. Outputs equal the plain model's."""
+    import threading
+    import time
+    from celeg_b200 import Engine, EngineOptions
+    folder, config, weights = models["A"]
+    prompts = prompts_of(config["vocab_size"], [5, 9, 14, 22, 31, 40], seed=44)
+    engine = Engine(folder, dtype="float32", options=EngineOptions(max_active_requests=4, max_batched_tokens=48,
+                                                                   prefill_chunk_tokens=16))
+    engine.start()
+    assert engine.running()
+    engine.start()                                   # a second start changes nothing
+    results, errors = {}, []
+
+    def client(indices):
+        try:
+            mine = {i: engine.submit(prompts[i], max_new_tokens=10, temperature=0.0, repetition_penalty=1.0,
+                                     eos_tokens=()) for i in indices}
+            got = {i: [] for i in indices}
+            deadline = time.monotonic() + 120
+            while mine and time.monotonic() < deadline:
+                for i, request_id in list(mine.items()):
+                    result = engine.poll(request_id)
+                    got[i].extend(result.tokens)
+                    if result.finished:
+                        assert result.status.value == "finished", result.error
+                        engine.release(request_id)
+                        del mine[i]
+                time.sleep(0.001)
+            assert not mine, "requests were not served in time"
+            results.update(got)
+        except Exception as exc:                     # reported by the main thread
+            errors.append(exc)
+
+    threads = [threading.Thread(target=client, args=(indices,)) for indices in ([0, 3], [1, 4], [2, 5])]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join(timeout=180)
+    engine.stop()
+    assert not engine.running()
+    engine.stop()                                    # a second stop changes nothing
+    assert not errors, errors
+    for i, prompt in enumerate(prompts):
+        assert results[i] == plain_lfm2.generate(config, weights, prompt, 10, eos_tokens=()), i
+    engine.loaded.manager.check_invariants()
+    assert engine.loaded.manager.free_slots == 4
+    # the engine still steps by hand after the worker has gone
+    assert engine.generate(prompts[0], max_new_tokens=4, temperature=0.0, repetition_penalty=1.0,
+                           eos_tokens=()) == results[0][:4]
+
+
+@pytest.mark.parametrize("name", ["A", "C", "D"])
+def test_bfloat16_path_agrees_with_float32_path(tmp_path, name):
+    """The serving path against the true 32-bit path of the same engine on whole prompts of 150 tokens: the
+    same token has the highest logit at 95 % of the positions or more, every row's error is at most 3 % of the
+    row's norm, and greedy continuations agree until a first difference at a position where the 32-bit path
+    itself saw a near tie."""
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    folder = write_tiny(tmp_path, name)
+    config = CONFIGS[name][0]
+    prompts = prompts_of(config["vocab_size"], [150, 150, 150], seed=45)
+    rows = {}
+    for dtype in ("float32", "bfloat16"):
+        loaded = load_model(folder, dtype=dtype, max_requests=2, cache_tokens=512, max_batched_tokens=160)
+        out = []
+        for i, prompt in enumerate(prompts):
+            logits = loaded.step.run([StepEntry(f"p{i}", prompt, list(range(len(prompt))))], auto_begin=True)
+            out.append(logits.float().cpu().numpy().copy())
+            loaded.step.end(f"p{i}")
+        loaded.step.raise_on_device_error()
+        rows[dtype] = np.concatenate(out)
+    exact, served = rows["float32"], rows["bfloat16"]
+    agreement = float((exact.argmax(axis=1) == served.argmax(axis=1)).mean())
+    assert agreement >= 0.95, f"top-1 agreement {agreement:.3f}"
+    relative = np.linalg.norm(served - exact, axis=1) / np.linalg.norm(exact, axis=1)
+    assert float(relative.max()) <= 0.03, f"largest relative row error {relative.max():.4f}"
+    # where the top token differs, the 32-bit path's own margin between the two candidates is small
+    for row in np.nonzero(exact.argmax(axis=1) != served.argmax(axis=1))[0]:
+        margin = exact[row].max() - exact[row, served[row].argmax()]
+        assert margin <= 0.02 * np.linalg.norm(exact[row]) / np.sqrt(exact.shape[1]) * 10, (row, margin)
 
 
 def test_run_order_names_a_layer_twice_and_shares_a_cache(tmp_path):
@@ -1046,35 +1178,20 @@ def test_equal_prompt_portions_are_replayed_from_a_graph(tmp_path, name, dtype, 
     assert np.abs(got[7] - want_other[29]).max() < tol
 
 
-def test_decoding_twenty_requests_on_the_streaming_product(models, monkeypatch):
-    """CELEG_B200_TC_PRODUCTS=stream: steps of 17 to 128 rows run the weight-streaming tcgen05 product
-    with its fused epilogues (SwiGLU, short convolution); greedy tokens against the plain model."""
-    from celeg_b200 import Engine, EngineOptions
-    monkeypatch.setenv("CELEG_B200_TC_PRODUCTS", "stream")
-    folder, config, weights = models["B"]
-    prompts = prompts_of(config["vocab_size"], [6 + i for i in range(20)], seed=23)
-    engine = Engine(folder, dtype="bfloat16", options=EngineOptions(max_active_requests=20))
-    got = engine.generate(prompts, max_new_tokens=6, temperature=0.0, repetition_penalty=1.0, eos_tokens=())
-    agree = 0
-    for prompt, tokens in zip(prompts, got):
-        agree += tokens == plain_lfm2.generate(config, weights, prompt, 6, eos_tokens=())
-    assert agree >= 18, f"only {agree} of 20 requests decode the plain model's tokens"
-    engine.loaded.step.raise_on_device_error()
-
-
 @pytest.mark.parametrize("name", ["B", "D"])
-def test_every_product_on_the_tcgen05_kernel(tmp_path, monkeypatch, name):
-    """CELEG_B200_TC_PRODUCTS=all: every product of more than 16 rows, the gate+up product with its activation
+def test_every_product_on_the_tcgen05_kernel(tmp_path, name):
+    """``KernelOptions(tensor_core_products="all")``: every product of more than 16 rows, the gate+up product with its activation
     included, runs on this package's TMA + tcgen05 kernel instead of the library's (by default only gate+up of
     2,048 rows and more does). A prompt whole, in portions and beside decoded tokens, against the plain model."""
+    from celeg_b200 import KernelOptions
     from celeg_b200.engine.loading import load_model
     from celeg_b200.engine.step import StepEntry
-    monkeypatch.setenv("CELEG_B200_TC_PRODUCTS", "all")
     folder = write_tiny(tmp_path, name)
     config, weights = plain_lfm2.load_model_folder(folder)
     first, second = prompts_of(config["vocab_size"], [300, 150], seed=48)
     want = [plain_lfm2.forward(config, weights, first), plain_lfm2.forward(config, weights, second)]
-    loaded = load_model(folder, dtype="bfloat16", max_requests=2, cache_tokens=512, max_batched_tokens=320)
+    loaded = load_model(folder, dtype="bfloat16", max_requests=2, cache_tokens=512, max_batched_tokens=320,
+                        kernel_options=KernelOptions(tensor_core_products="all"))
     step = loaded.step
     tol = 8e-2
     whole = step.run([StepEntry("whole", first, [0, 150, 299])], auto_begin=True).float().cpu().numpy()

@@ -366,9 +366,8 @@ def test_run_ahead_with_cancellation_and_failure():
     manager.check_invariants()
 
 
-def test_run_ahead_can_be_switched_off(monkeypatch):
-    monkeypatch.setenv("CELEG_B200_RUN_AHEAD", "0")
-    scheduler, runner, manager = make_ahead()
+def test_run_ahead_can_be_switched_off():
+    scheduler, runner, manager = make_ahead(run_ahead=False)
     request_id = scheduler.submit([3, 4, 5], RequestOptions(max_new_tokens=6, eos_tokens=()))
     run_all(scheduler)
     assert scheduler.poll(request_id).tokens == expected_output([3, 4, 5], 6, eos=())
