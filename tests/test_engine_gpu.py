@@ -642,9 +642,11 @@ def test_seeded_sampling_survives_preemption(models):
     from celeg_b200 import Engine, EngineOptions, RequestOptions, SamplingParams, SchedulerPolicy
     folder, config, weights = models["B"]
     rng = np.random.default_rng(42)
-    lengths = rng.integers(4, 50, size=12).tolist()
+    # every request is admitted with three pages and needs five before it ends; the pool holds eight, so two
+    # live requests grow to four pages each and then neither can take its fifth
+    lengths = rng.integers(18, 31, size=10).tolist()
     prompts = prompts_of(config["vocab_size"], lengths, seed=43)
-    new_tokens = rng.integers(6, 30, size=12).tolist()
+    new_tokens = rng.integers(45, 61, size=10).tolist()
     options = EngineOptions(max_active_requests=4, max_batched_tokens=32, prefill_chunk_tokens=11, page_tokens=16,
                             logical_kv_pages=8, scheduler_policy=SchedulerPolicy.MAX_UTILIZATION)
     engine = Engine(folder, dtype="float32", options=options)
@@ -667,7 +669,7 @@ def test_seeded_sampling_survives_preemption(models):
                 assert result.status.value == "finished", result.error
                 pending.discard(i)
         steps += 1
-        assert steps < 3000
+        assert steps < 6000
     assert engine.metrics().preempted > 0, "the pool was meant to be too small for four live requests"
     alone = Engine(folder, dtype="float32")
     for index, (request_id, prompt, n) in enumerate(zip(ids, prompts, new_tokens)):
