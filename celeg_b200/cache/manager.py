@@ -52,7 +52,7 @@ class PagedGroup:
     key: tuple
     need: PagedNeed
     pool: PagePool
-    members: List[int] = field(default_factory=list)      # run-order positions that own a layer of this group
+    members: List[Hashable] = field(default_factory=list)  # places (run-order position, part name) that own a layer of this group
 
     @property
     def window(self) -> Optional[int]:
@@ -61,11 +61,12 @@ class PagedGroup:
 
 @dataclass
 class StateLayout:
-    offsets: Dict[int, int] = field(default_factory=dict)  # run-order position -> first float in the slot
-    sizes: Dict[int, int] = field(default_factory=dict)
+    # keyed by the place of the state in the model: (position of the run order, name of the part)
+    offsets: Dict[Hashable, int] = field(default_factory=dict)  # place -> first float in the slot
+    sizes: Dict[Hashable, int] = field(default_factory=dict)
     slot_elements: int = 0
 
-    def add(self, position: int, elements: int) -> int:
+    def add(self, position: Hashable, elements: int) -> int:
         offset = self.slot_elements
         self.offsets[position] = offset
         self.sizes[position] = elements

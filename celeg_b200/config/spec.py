@@ -30,11 +30,16 @@ class TensorRef:
 @dataclass(frozen=True)
 class PartSpec:
     """One part (norm, mixer, feed-forward, position encoding): registry kind,
-    its sizes and constants, the tensors it owns, and parts nested in it."""
+    its sizes and constants, the tensors it owns, and parts nested in it.
+
+    ``category`` names the registry the kind is looked up in ("norm", "mixer", "feed_forward",
+    "position", ...). The four named parts of a :class:`LayerSpec` need none (their place says it); a
+    nested part or an extra part of a layer states it, or carries a name that is itself a category."""
     kind: str
     params: Mapping[str, Any] = field(default_factory=dict)
     tensors: Mapping[str, TensorRef] = field(default_factory=dict)
     parts: Mapping[str, "PartSpec"] = field(default_factory=dict)
+    category: Optional[str] = None
 
     def all_tensors(self) -> List[TensorRef]:
         out = list(self.tensors.values())
@@ -53,10 +58,15 @@ class LayerSpec:
     mixer: PartSpec
     feed_forward_norm: Optional[PartSpec]
     feed_forward: Optional[PartSpec]
+    # Further parts by name, each with its ``category``: norms after the mixer or the feed-forward, a second
+    # mixer, a gate. The arrangement finds them under their names beside the four above; a part among them
+    # that asks for a cache gets one of its own.
+    extra_parts: Mapping[str, PartSpec] = field(default_factory=dict)
 
     def all_tensors(self) -> List[TensorRef]:
         out: List[TensorRef] = []
-        for part in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward):
+        for part in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward,
+                     *self.extra_parts.values()):
             if part is not None:
                 out.extend(part.all_tensors())
         return out

@@ -19,6 +19,10 @@ def _weights_of(part: PartSpec, tensors: Mapping[str, torch.Tensor]) -> Dict[str
 
 
 def build_part(category: str, part: Optional[PartSpec], tensors: Mapping[str, torch.Tensor], rt: Runtime):
+    """The part a description names, from the registry of its category. Norms are built from
+    ``(params, weights, rt)``, position encodings from ``(params, rt)``, every other category from
+    ``(params, weights, nested parts, rt)``; a nested part's category is what its description states, else
+    its name if that is a category."""
     if part is None:
         return None
     factory = part_factory(category, part.kind)
@@ -26,12 +30,14 @@ def build_part(category: str, part: Optional[PartSpec], tensors: Mapping[str, to
         return factory(part.params, _weights_of(part, tensors), rt)
     if category == "position":
         return factory(part.params, rt)
-    children = {name: build_part("position" if name == "position" else name, child, tensors, rt)
-                for name, child in part.parts.items()}
+    children = {name: build_part(child.category or name, child, tensors, rt) for name, child in part.parts.items()}
     return factory(part.params, _weights_of(part, tensors), children, rt)
 
 
 class Layer:
+    """The parts of one block, built: the four named ones and whatever else the description lists, all under
+    their names in ``parts`` (what the arrangement gets). ``cache_parts`` are those that ask for a cache."""
+
     def __init__(self, spec: LayerSpec, tensors: Mapping[str, torch.Tensor], rt: Runtime):
         self.name = spec.name
         self.parts = {
@@ -40,7 +46,15 @@ class Layer:
             "feed_forward_norm": build_part("norm", spec.feed_forward_norm, tensors, rt),
             "feed_forward": build_part("feed_forward", spec.feed_forward, tensors, rt),
         }
+        for name, part in spec.extra_parts.items():
+            if name in self.parts:
+                raise ValueError(f"layer {spec.name}: the extra part '{name}' has the name of a standard part")
+            if not part.category:
+                raise ValueError(f"layer {spec.name}: the extra part '{name}' does not state its category")
+            self.parts[name] = build_part(part.category, part, tensors, rt)
         self.mixer = self.parts["mixer"]
+        self.cache_parts = {name: part for name, part in self.parts.items()
+                            if part is not None and hasattr(part, "cache_need")}
         self.block = part_factory("arrangement", spec.arrangement)(self.parts, rt)
 
 
@@ -59,65 +73,74 @@ class Model:
         self.stream = ResidualStream(rt, spec.hidden_size)
         self.residual = self.stream.residual
         self.final_normed = rt.scratch("model.final_normed", spec.hidden_size)
-        self.bindings: List[object] = [None] * len(self.order)
+        # per position of the run order: {part name: binding} for the parts of its layer that hold a cache
+        self.bindings: List[Dict[str, object]] = [{} for _ in self.order]
         self._rebind = len({entry.layer for entry in self.order}) != len(self.order)
         self._plan_caches()
 
     # ------------------------------------------------------------------ caches
     def _plan_caches(self) -> None:
-        """Group the mixers' needs: one paged group per distinct need, one slot layout."""
+        """Group the needs of every cache-holding part: one paged group per distinct need, one slot layout.
+        A place in a cache is named by (position of the run order, name of the part in its layer)."""
         self.group_keys: List[tuple] = []
         self.group_needs: List[PagedNeed] = []
-        self.group_members: List[List[int]] = []        # run-order positions that OWN a layer of the group
+        self.group_members: List[List[tuple]] = []      # (position, part name) places that OWN a layer of the group
         self.state_layout = StateLayout()
-        self.position_group: Dict[int, Tuple[int, int]] = {}   # position -> (group, layer index in group)
+        self.position_group: Dict[tuple, Tuple[int, int]] = {}   # place -> (group, layer index in group)
         for position, entry in enumerate(self.order):
-            mixer = self.layers[entry.layer].mixer
-            need = mixer.cache_need()
-            if entry.cache_of is not None:
-                source_need = self.layers[self.order[entry.cache_of].layer].mixer.cache_need()
-                if type(need) is not type(source_need) or need != source_need:
-                    raise ValueError(f"run order position {position} reads the cache of position "
-                                     f"{entry.cache_of}, whose need {source_need} differs from its own {need}")
-                continue
-            if need is None:
-                continue
-            if isinstance(need, PagedNeed):
-                key = need.group_key()
-                if key not in self.group_keys:
-                    self.group_keys.append(key)
-                    self.group_needs.append(need)
-                    self.group_members.append([])
-                group = self.group_keys.index(key)
-                self.position_group[position] = (group, len(self.group_members[group]))
-                self.group_members[group].append(position)
-            elif isinstance(need, StateNeed):
-                self.state_layout.add(position, need.elements)
-            else:
-                raise TypeError(f"mixer of layer {entry.layer} asks for an unknown cache need {need!r}")
+            for name, part in self.layers[entry.layer].cache_parts.items():
+                need = part.cache_need()
+                if entry.cache_of is not None:
+                    source = self.layers[self.order[entry.cache_of].layer].cache_parts.get(name)
+                    source_need = source.cache_need() if source is not None else None
+                    if type(need) is not type(source_need) or need != source_need:
+                        raise ValueError(f"run order position {position} reads the cache of position "
+                                         f"{entry.cache_of}, whose need {source_need} for '{name}' differs from "
+                                         f"its own {need}")
+                    continue
+                if need is None:
+                    continue
+                place = (position, name)
+                if isinstance(need, PagedNeed):
+                    key = need.group_key()
+                    if key not in self.group_keys:
+                        self.group_keys.append(key)
+                        self.group_needs.append(need)
+                        self.group_members.append([])
+                    group = self.group_keys.index(key)
+                    self.position_group[place] = (group, len(self.group_members[group]))
+                    self.group_members[group].append(place)
+                elif isinstance(need, StateNeed):
+                    self.state_layout.add(place, need.elements)
+                else:
+                    raise TypeError(f"part '{name}' of layer {entry.layer} asks for an unknown cache need {need!r}")
 
     def attach(self, storage: CacheStorage) -> None:
-        """Give every position of the run order the place its cache lives in."""
+        """Give every cache-holding part at every position of the run order the place its cache lives in."""
         for position, entry in enumerate(self.order):
-            mixer = self.layers[entry.layer].mixer
-            need = mixer.cache_need()
-            if need is None:
-                continue
-            source = position if entry.cache_of is None else entry.cache_of
-            owner = entry.cache_of is None
-            if isinstance(need, PagedNeed):
-                group, index = self.position_group[source]
-                self.bindings[position] = PagedBinding(group=group, k=storage.k[group][index],
-                                                       v=storage.v[group][index],
-                                                       page_tokens=storage.page_tokens, owner=owner)
-            else:
-                offset = self.state_layout.offsets[source]
-                self.bindings[position] = StateBinding(state=storage.state[:, offset:],
-                                                       slot_stride=storage.state.stride(0), owner=owner)
+            for name, part in self.layers[entry.layer].cache_parts.items():
+                need = part.cache_need()
+                if need is None:
+                    continue
+                source = (position if entry.cache_of is None else entry.cache_of, name)
+                owner = entry.cache_of is None
+                if isinstance(need, PagedNeed):
+                    group, index = self.position_group[source]
+                    self.bindings[position][name] = PagedBinding(group=group, k=storage.k[group][index],
+                                                                 v=storage.v[group][index],
+                                                                 page_tokens=storage.page_tokens, owner=owner)
+                else:
+                    offset = self.state_layout.offsets[source]
+                    self.bindings[position][name] = StateBinding(state=storage.state[:, offset:],
+                                                                 slot_stride=storage.state.stride(0), owner=owner)
         if not self._rebind:
             for position, entry in enumerate(self.order):
-                if self.bindings[position] is not None:
-                    self.layers[entry.layer].mixer.bind_cache(self.bindings[position])
+                self._bind(position)
+
+    def _bind(self, position: int) -> None:
+        parts = self.layers[self.order[position].layer].cache_parts
+        for name, binding in self.bindings[position].items():
+            parts[name].bind_cache(binding)
 
     def weight_bytes(self) -> int:
         """Bytes of every weight a step reads once: what the parts put on the device, and the head (a tied
@@ -148,8 +171,8 @@ class Model:
                               self.spec.embedding_multiplier)
         for position, entry in enumerate(self.order):
             layer = self.layers[entry.layer]
-            if self._rebind and self.bindings[position] is not None:
-                layer.mixer.bind_cache(self.bindings[position])
+            if self._rebind:
+                self._bind(position)
             stream.after_layer = firsts[position + 1] if position + 1 < len(blocks) else head_norm
             layer.block.run(stream, step)
         stream.after_layer = None

@@ -376,7 +376,7 @@ def test_toy_mixer_with_its_own_state_is_registered_built_and_stepped(tmp_path):
     raw["model_type"] = "toy_lfm2"
     folder = write_random_model(str(tmp_path / "toy"), raw, 5)
     loaded = load_model(folder, dtype="float32", max_requests=3, cache_tokens=128, max_batched_tokens=64)
-    assert loaded.model.state_layout.sizes[1] == 64          # the toy's state sits in the slot beside the convs'
+    assert loaded.model.state_layout.sizes[(1, "mixer")] == 64          # the toy's state sits in the slot beside the convs'
     assert len(loaded.model.state_layout.offsets) == 3       # two conv layers (0, 3) + the toy (1)
 
     config, weights = plain_lfm2.load_model_folder(folder)
@@ -935,6 +935,145 @@ def test_a_layer_with_a_window_has_pages_of_its_own_and_gives_them_back(tmp_path
     # the windowed group holds only what the window still needs: far fewer pages than the 170 tokens
     held = [len(loaded.manager.get("long").held_pages(g)) for g in range(len(groups))]
     assert min(held) <= (window + 8 - 1) // 8 + 2 and max(held) >= 170 // 8, held
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 4e-4), ("bfloat16", 8e-2)])
+def test_toy_block_with_post_norms_and_two_mixers(tmp_path, dtype, tol):
+    """A block that the four named parts do not cover, described with a layer's ``extra_parts`` and run by an
+    arrangement defined here: a sandwich (a norm AFTER the mixer and after the feed-forward, as some
+    architectures have) whose mixer stage is an attention and a short convolution side by side:
+
+        a = PostNorm1(Attention(N1(x)) + ShortConv(N1(x)));  h = x + a;  y = h + PostNorm2(FeedForward(N2(h)))
+
+    Both mixers hold a cache (pages for one, a state slot for the other) at the same position of the run
+    order. Nothing of the package changes; prompts in portions and decoded tokens against a plain computation."""
+    from celeg_b200.config import Architecture, Lfm2Config, PartSpec, TensorRef, build_lfm2_spec, register_architecture
+    from celeg_b200.config.lfm2_arch import lfm2_random_init
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    from celeg_b200.parts import register_part
+    from celeg_b200.weights import write_random_model
+
+    @register_part("arrangement", "toy_sandwich_two_mixers", replace=True)
+    class ToySandwich:
+        def __init__(self, layer_parts, rt):
+            self.parts = layer_parts
+            hidden = layer_parts["mixer_norm"].width
+            self.normed = rt.scratch("toy.sandwich.normed", hidden)
+            self.out_a = rt.scratch("toy.sandwich.out_a", hidden)
+            self.out_b = rt.scratch("toy.sandwich.out_b", hidden)
+            self.post = rt.scratch("toy.sandwich.post", hidden)
+            self.zero = torch.zeros_like(rt.scratch("toy.sandwich.zero", hidden, torch.float32))
+
+        def _post_norm(self, norm, value, t):
+            """norm(value) with the norm kernels' interface: a float32 'residual' of zeros plus the value."""
+            self.zero[:t].zero_()
+            norm.add_norm(self.zero, value, self.post, t)
+            return self.post
+
+        def run(self, stream, step):
+            t = step.tokens
+            x = stream.normed(self.parts["mixer_norm"], self.normed, t)
+            stream.expect(self.out_a, None, t)
+            self.parts["mixer"].forward(x, self.out_a, step)
+            self.parts["second_mixer"].forward(x, self.out_b, step)
+            self.out_a[:t] = (self.out_a[:t].float() + self.out_b[:t].float()).to(self.out_a.dtype)
+            stream.add_later(self._post_norm(self.parts["post_mixer_norm"], self.out_a, t))
+            x = stream.normed(self.parts["feed_forward_norm"], self.normed, t)
+            stream.expect(self.out_a, None, t)
+            self.parts["feed_forward"].forward(x, self.out_a, step)
+            self.out_b[:t] = self._post_norm(self.parts["post_feed_forward_norm"], self.out_a, t)[:t]
+            stream.add_later(self.out_b)
+
+    def toy_spec(config):
+        spec = build_lfm2_spec(config)
+        layers = list(spec.layers)
+        hidden = config.hidden_size
+
+        def rms(name):
+            return PartSpec(kind="rmsnorm", category="norm", params={"width": hidden, "eps": config.norm_eps},
+                            tensors={"weight": TensorRef(name, (hidden,))})
+
+        # layer 2 of tiny A is the attention layer: give it layer 1's kind of mixer as a second one
+        base = "model.layers.2"
+        second = PartSpec(kind="short_conv", category="mixer", params={"hidden_size": hidden, "taps": config.conv_L_cache},
+                          tensors={"in_proj": TensorRef(f"{base}.toy_conv.in_proj.weight", (3 * hidden, hidden)),
+                                   "conv": TensorRef(f"{base}.toy_conv.conv.weight", (hidden, config.conv_L_cache)),
+                                   "out_proj": TensorRef(f"{base}.toy_conv.out_proj.weight", (hidden, hidden))})
+        layers[2] = dataclasses.replace(
+            layers[2], arrangement="toy_sandwich_two_mixers",
+            extra_parts={"second_mixer": second, "post_mixer_norm": rms(f"{base}.toy_post_mixer_norm.weight"),
+                         "post_feed_forward_norm": rms(f"{base}.toy_post_ffn_norm.weight")})
+        return dataclasses.replace(spec, layers=tuple(layers), architecture="toy_sandwich_lfm2")
+
+    def init(config, name, shape):
+        if name.endswith("toy_conv.conv.weight"):
+            return "conv"
+        return lfm2_random_init(config, name, shape)
+
+    register_architecture(Architecture(
+        name="toy_sandwich_lfm2", parse_config=Lfm2Config.from_dict,
+        resolve_config=lambda config, shapes: dataclasses.replace(
+            config, tie_word_embeddings=True if config.tie_word_embeddings is None else config.tie_word_embeddings),
+        build_spec=toy_spec, random_init=init), replace=True)
+    raw = copy.deepcopy(TINY_A)
+    raw["model_type"] = "toy_sandwich_lfm2"
+    folder = write_random_model(str(tmp_path / "toy_sandwich"), raw, 12, torch.bfloat16)
+    loaded = load_model(folder, dtype=dtype, max_requests=3, cache_tokens=192, max_batched_tokens=64, use_graphs=True)
+    # two caches at position 2: pages for the attention, a state place for the second mixer
+    assert set(loaded.model.bindings[2]) == {"mixer", "second_mixer"}
+    assert (2, "second_mixer") in loaded.model.state_layout.offsets
+    config, w = plain_lfm2.load_model_folder(folder)
+    eps = config["norm_eps"]
+    heads, kv_heads, head_dim = config["num_attention_heads"], config["num_key_value_heads"], plain_lfm2.head_dim(config)
+
+    def plain_forward(tokens):
+        x = w["model.embed_tokens.weight"][np.asarray(tokens)]
+        for index, kind in enumerate(plain_lfm2.layer_kinds(config, w)):
+            if index != 2:
+                x = plain_lfm2.block(x, index, kind, config, w)
+                continue
+            p = "model.layers.2."
+            n = plain_lfm2.rmsnorm(x, w[p + "operator_norm.weight"], eps)
+            attended = plain_lfm2.attention_mixer(
+                n, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.k_proj.weight"], w[p + "self_attn.v_proj.weight"],
+                w[p + "self_attn.out_proj.weight"], w[p + "self_attn.q_layernorm.weight"],
+                w[p + "self_attn.k_layernorm.weight"], heads, kv_heads, head_dim, config["rope_theta"], eps)
+            convolved = plain_lfm2.short_conv_mixer(n, w[p + "toy_conv.in_proj.weight"], w[p + "toy_conv.conv.weight"],
+                                                    w[p + "toy_conv.out_proj.weight"])
+            h = x + plain_lfm2.rmsnorm(attended + convolved, w[p + "toy_post_mixer_norm.weight"], eps)
+            n2 = plain_lfm2.rmsnorm(h, w[p + "ffn_norm.weight"], eps)
+            f = plain_lfm2.swiglu(n2, w[p + "feed_forward.w1.weight"], w[p + "feed_forward.w3.weight"],
+                                  w[p + "feed_forward.w2.weight"])
+            x = h + plain_lfm2.rmsnorm(f, w[p + "toy_post_ffn_norm.weight"], eps)
+        z = plain_lfm2.rmsnorm(x, w["model.embedding_norm.weight"], eps)
+        return z @ w["model.embed_tokens.weight"].T
+
+    first, second = prompts_of(config["vocab_size"], [60, 25], seed=46)
+    want = {"first": plain_forward(first), "second": plain_forward(second)}
+    seqs = {"first": first, "second": second}
+    at = {"first": 0, "second": 0}
+    step = loaded.step
+
+    def run(portions):
+        entries = [StepEntry(n, seqs[n][at[n]:at[n] + size], list(range(size))) for n, size in portions]
+        logits = step.run(entries, auto_begin=True).float().cpu().numpy()
+        row = 0
+        for n, size in portions:
+            worst = np.abs(logits[row:row + size] - want[n][at[n]:at[n] + size]).max()
+            assert worst < tol, f"request {n}, tokens {at[n]}..{at[n] + size}: {worst:.3e}"
+            row += size
+            at[n] += size
+
+    run([("first", 33)])
+    run([("first", 2), ("second", 17)])
+    for _ in range(8):                              # decoded one by one, both together (a graph from the second step on)
+        run([("first", 1), ("second", 1)])
+    step.end("second")
+    run([("first", 17)])
+    assert at["first"] == 60
+    step.raise_on_device_error()
+    loaded.manager.check_invariants()
 
 
 @pytest.mark.parametrize("dtype,tol", [("float32", 4e-4), ("bfloat16", 8e-2)])
