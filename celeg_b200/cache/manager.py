@@ -30,15 +30,21 @@ NO_PAGE = -1
 
 @dataclass(frozen=True)
 class PagedNeed:
-    """A cache that grows by ``entry_shape`` elements per position for keys and again for
-    values; ``window`` = how many most recent positions (the query's own included) a query
-    may read, ``None`` = all."""
+    """A cache that grows per position by ``kv_heads * head_dim`` elements for keys and by
+    ``kv_heads * value_head_dim`` for values (``None``: as wide as the keys; 0: nothing is kept beside the
+    keys, as for a mixer that caches one latent vector per position); ``window`` = how many most recent
+    positions (the query's own included) a query may read, ``None`` = all."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.value_head_dim is None else self.value_head_dim
 
     def group_key(self) -> tuple:
-        return ("paged", self.kv_heads, self.head_dim, self.window)
+        return ("paged", self.kv_heads, self.head_dim, self.window, self.value_dim)
 
 
 @dataclass(frozen=True)

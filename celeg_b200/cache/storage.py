@@ -10,7 +10,8 @@ from .manager import PagedNeed, StateLayout
 
 class CacheStorage:
     """Keys and values of group g: ``k[g]``, ``v[g]`` of shape
-    [layers of the group, pages, kv_heads, page_tokens, head_dim] in the path's element type,
+    [layers of the group, pages, kv_heads, page_tokens, head_dim] (values: the need's ``value_dim`` as the
+    last size, which may differ from the keys' or be 0) in the path's element type,
     so one (layer, page, head) tile is a contiguous [page_tokens, head_dim] box.
     Fixed-size state: ``state`` [slots, slot_elements] float32.
 
@@ -25,10 +26,11 @@ class CacheStorage:
         self.v: List[torch.Tensor] = []
         for (need, layers), pages in zip(groups, group_pages):
             shape = (layers, pages + 1, need.kv_heads, page_tokens, need.head_dim)
+            value_shape = (layers, pages + 1, need.kv_heads, page_tokens, need.value_dim)
             # zeros, not empty: a page that was never written must not hold NaN bit patterns,
             # because masked keys are still multiplied by a zero weight in some kernels
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v.append(torch.zeros(value_shape, dtype=dtype, device=device))
         self.scratch_pages = [int(pages) for pages in group_pages]
         self.scratch_slot = int(slots)
         self.slot_elements = max(state_layout.slot_elements, 4)

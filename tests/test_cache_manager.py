@@ -158,3 +158,18 @@ def test_random_traffic_keeps_the_books(seed):
     manager.check_invariants()
     assert all(group.pool.free_pages == group.pool.total_pages for group in manager.groups)
     assert manager.free_slots == 4 and len(cleared) == serial
+
+
+def test_values_may_be_narrower_than_keys_or_absent():
+    """A paged need states the width of what is kept beside the keys on its own: equal (attention), narrower,
+    or nothing (one latent vector per position). Needs that differ in it form groups of their own."""
+    import torch
+    from celeg_b200.cache.storage import CacheStorage
+    needs = [PagedNeed(2, 16), PagedNeed(2, 16, value_head_dim=8), PagedNeed(1, 48, value_head_dim=0)]
+    assert len({need.group_key() for need in needs}) == 3
+    assert [need.value_dim for need in needs] == [16, 8, 0]
+    storage = CacheStorage([(need, 2) for need in needs], [5, 5, 5], 4, StateLayout(), 3, torch.float32,
+                           torch.device("cpu"))
+    assert [tuple(k.shape) for k in storage.k] == [(2, 6, 2, 4, 16), (2, 6, 2, 4, 16), (2, 6, 1, 4, 48)]
+    assert [tuple(v.shape) for v in storage.v] == [(2, 6, 2, 4, 16), (2, 6, 2, 4, 8), (2, 6, 1, 4, 0)]
+    assert storage.scratch_pages == [5, 5, 5] and storage.scratch_slot == 3 and storage.state.shape[0] == 4
