@@ -67,22 +67,202 @@ __device__ __forceinline__ unsigned score_key(float v) {
     return key == 0u ? 1u : key;
 }
 
-// One block per row. The k best (score descending, then token ascending) are found by a radix selection over
-// the scores' keys instead of k arg-max passes: four passes of 8 bits give the k-th largest key, a fifth pass
-// gathers everything above it and the ties at it with the lowest token ids, and the k candidates are ranked
-// among themselves. The vocabulary is read five or six times from the L2 instead of k times.
+constexpr int kSelectPool = 1024;   // most candidates the first stage may leave for the exact selection
+
+struct SelectShared {
+    Best scratch[33];
+    float cand_score[kMaxTopK];
+    int cand_token[kMaxTopK];
+    float sorted_score[kMaxTopK];
+    int sorted_token[kMaxTopK];
+    unsigned hist[256];
+    unsigned warp_hist[32][256];     // a histogram per warp: scores crowd into a few bins of the top digits, one
+    unsigned prefix, remaining, count, ties;   // shared histogram would serialise on them
+    float thread_max[1024];
+    float pool_score[kSelectPool];
+    int pool_token[kSelectPool];
+    unsigned pool_count;
+};
+
+// The k best of n (score, token) pairs, score descending, then token ascending, into sm.sorted_*; returns how
+// many there are (fewer than k if fewer pairs have a score that is a number). All threads of the block call
+// it. A radix selection over the scores' keys: four passes of 8 bits give the k-th largest key, a fifth pass
+// gathers everything above it and the ties at it with the lowest token ids, and the candidates are ranked
+// among themselves.
+template <typename ScoreAt, typename TokenAt>
+__device__ int select_top_k(SelectShared& sm, const int n, const int k, ScoreAt score_at, TokenAt token_at) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    constexpr int kBatch = 8;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        sm.prefix = 0u;
+        sm.remaining = (unsigned)k;
+        sm.ties = 0u;
+    }
+    __syncthreads();
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = lane; i < 256; i += 32) sm.warp_hist[warp][i] = 0u;
+        __syncwarp();
+        const unsigned prefix = sm.prefix;
+        // every lane runs the same number of rounds, so that the warp-wide match below sees all lanes; eight
+        // scores per lane and round are loaded before any is used
+        for (int base = warp * 32; base < n; base += blockDim.x * kBatch) {
+            float v[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int i = base + u * blockDim.x + lane;
+                v[u] = i < n ? score_at(i) : __int_as_float(0x7fc00000);      // NaN: no contribution
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                if (base + u * (int)blockDim.x >= n) break;                 // (the same for all lanes)
+                unsigned bin = 0xffffffffu;
+                const unsigned key = score_key(v[u]);
+                if (key != 0u && (shift == 24 || (key >> (shift + 8)) == (prefix >> (shift + 8))))
+                    bin = (key >> shift) & 255u;
+                // lanes with the same bin: the lowest of them adds their number, no two lanes write one counter
+                const unsigned peers = __match_any_sync(0xffffffffu, bin);
+                if (bin != 0xffffffffu && lane == __ffs(peers) - 1) sm.warp_hist[warp][bin] += __popc(peers);
+                __syncwarp();
+            }
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+            unsigned total = 0u;
+            for (int w = 0; w < warps; ++w) total += sm.warp_hist[w][i];
+            sm.hist[i] = total;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // the bin in which the count from the top reaches what is still wanted: lane l holds bins 8l..8l+7
+            unsigned local[8], sum = 0u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                local[j] = sm.hist[lane * 8 + j];
+                sum += local[j];
+            }
+            unsigned from_top = sum;                                   // this lane's bins and all higher ones
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1) {
+                const unsigned other = __shfl_down_sync(0xffffffffu, from_top, offset);
+                if (lane + offset < 32) from_top += other;
+            }
+            const unsigned total = __shfl_sync(0xffffffffu, from_top, 0);
+            unsigned remaining = sm.remaining;
+            if (shift == 24) remaining = min(remaining, total);       // fewer candidates than k: take all there are
+            const unsigned above = from_top - sum;
+            __syncwarp();
+            if (remaining == 0u) {
+                if (lane == 0) {
+                    sm.remaining = 0u;
+                    sm.ties = 0u;
+                }
+            } else if (above < remaining && remaining <= above + sum) {
+                unsigned left = remaining - above;
+                int chosen_bin = 0;
+#pragma unroll
+                for (int j = 7; j >= 0; --j) {
+                    if (left != 0u) {
+                        if (local[j] >= left) {
+                            chosen_bin = j;
+                            sm.ties = local[j];
+                            sm.remaining = left;
+                            left = 0u;
+                        } else {
+                            left -= local[j];
+                        }
+                    }
+                }
+                sm.prefix = prefix | ((unsigned)(lane * 8 + chosen_bin) << shift);
+            }
+        }
+        __syncthreads();
+        if (shift == 24 && sm.remaining == 0u) break;    // not one score that is a number
+    }
+    const unsigned threshold = sm.prefix;
+    const unsigned need_ties = sm.remaining;             // how many of the keys equal to the threshold belong to the k
+    const unsigned ties = sm.ties;
+    __syncthreads();
+    if (threadIdx.x == 0) sm.count = 0u;
+    __syncthreads();
+    if (need_ties > 0u) {
+        // everything above the threshold, and the ties when all of them are wanted
+        for (int base = threadIdx.x; base < n; base += blockDim.x * kBatch) {
+            float v[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int i = base + u * blockDim.x;
+                v[u] = i < n ? score_at(i) : __int_as_float(0x7fc00000);
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const unsigned key = score_key(v[u]);
+                if (key != 0u && (key > threshold || (key == threshold && ties == need_ties))) {
+                    const unsigned at = atomicAdd(&sm.count, 1u);
+                    if (at < (unsigned)kMaxTopK) {
+                        sm.cand_score[at] = v[u];
+                        sm.cand_token[at] = token_at(base + u * blockDim.x);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        if (ties != need_ties) {
+            // more equal scores at the threshold than places left: the lowest token ids among them, one by one
+            int previous = -1;
+            for (unsigned pick = 0; pick < need_ties; ++pick) {
+                Best mine{0.0f, -1};
+                for (int i = threadIdx.x; i < n; i += blockDim.x) {
+                    const int token = token_at(i);
+                    if (token <= previous) continue;
+                    const float v = score_at(i);
+                    if (score_key(v) != threshold) continue;
+                    if (mine.token < 0 || token < mine.token) {
+                        mine.score = v;
+                        mine.token = token;
+                    }
+                }
+                // block_best orders by score first; the scores are equal here, so the lower token wins
+                const Best best = block_best(mine, sm.scratch);
+                if (threadIdx.x == 0 && best.token >= 0) {
+                    const unsigned at = sm.count++;
+                    if (at < (unsigned)kMaxTopK) {
+                        sm.cand_score[at] = best.score;
+                        sm.cand_token[at] = best.token;
+                    }
+                }
+                previous = best.token;
+                if (best.token < 0) break;
+            }
+            __syncthreads();
+        }
+    }
+    const int found = min((int)sm.count, kMaxTopK);
+    // rank the candidates among themselves: score descending, then token ascending
+    for (int i = threadIdx.x; i < found; i += blockDim.x) {
+        const float sc = sm.cand_score[i];
+        const int tk = sm.cand_token[i];
+        int rank = 0;
+        for (int j = 0; j < found; ++j) rank += better(sm.cand_score[j], sm.cand_token[j], sc, tk) ? 1 : 0;
+        sm.sorted_score[rank] = sc;
+        sm.sorted_token[rank] = tk;
+    }
+    __syncthreads();
+    return found;
+}
+
+// One block per row. The k best scores of the vocabulary are found in two stages. First every thread keeps
+// the largest score of its share of the vocabulary; the k-th largest of these maxima is a lower bound of the
+// k-th largest score (k different tokens reach it), so one more pass that keeps every token at or above it
+// leaves a pool of little more than k candidates for the exact selection. A pool that overflows (scores that
+// are equal by the thousand) sends the row to the exact selection over the whole vocabulary instead. The
+// vocabulary is read twice where the plain form reads it k times.
 __global__ void sample_kernel(const float* logits, long long ld, int vocab,
                               const int* row_slot, uint8_t* seen_base,
                               unsigned long long* rng, const float* temperature,
                               const int* top_k, const float* top_p,
                               const float* penalty, int* out) {
-    __shared__ Best scratch[33];
-    __shared__ float cand_score[kMaxTopK];
-    __shared__ int cand_token[kMaxTopK];
-    __shared__ float sorted_score[kMaxTopK];
-    __shared__ int sorted_token[kMaxTopK];
-    __shared__ unsigned hist[256];
-    __shared__ unsigned s_prefix, s_remaining, s_count, s_ties;
+    __shared__ SelectShared sm;
     chain_release();
     chain_wait();
     const int row = blockIdx.x;
@@ -99,107 +279,66 @@ __global__ void sample_kernel(const float* logits, long long ld, int vocab,
         if (!greedy) v = v / temp;
         return v;
     };
+    auto same = [](int i) { return i; };
+    constexpr int kBatch = 8;
 
-    // the k-th largest key, 8 bits at a time from the top
-    if (threadIdx.x == 0) {
-        s_prefix = 0u;
-        s_remaining = (unsigned)k;
+    // stage one: every thread's maximum, and the k-th largest of those
+    float mine = -INFINITY;
+    bool any = false;
+    for (int base = threadIdx.x; base < vocab; base += blockDim.x * kBatch) {
+        float v[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int token = base + u * blockDim.x;
+            v[u] = token < vocab ? score_of(token) : __int_as_float(0x7fc00000);
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            if (v[u] == v[u]) {
+                mine = any ? fmaxf(mine, v[u]) : v[u];
+                any = true;
+            }
+        }
     }
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
+    sm.thread_max[threadIdx.x] = any ? mine : __int_as_float(0x7fc00000);
+    int found = select_top_k(sm, (int)blockDim.x, k, [&](int i) { return sm.thread_max[i]; }, same);
+    bool exact_over_vocabulary = found == 0;           // no score at all: the plain path reports it the same way
+    if (found > 0) {
+        const float bound = sm.sorted_score[found - 1];
         __syncthreads();
-        const unsigned prefix = s_prefix;
-        for (int token = threadIdx.x; token < vocab; token += blockDim.x) {
-            const unsigned key = score_key(score_of(token));
-            if (key == 0u) continue;
-            if (shift == 24 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(key >> shift) & 255u], 1u);
-        }
+        if (threadIdx.x == 0) sm.pool_count = 0u;
         __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned remaining = s_remaining, bin = 0u;
-            if (shift == 24) {
-                // fewer candidates than k (NaNs, or a tiny vocabulary): take all there are
-                unsigned have = 0u;
-                for (int i = 0; i < 256; ++i) have += hist[i];
-                remaining = min(remaining, have);
+        for (int base = threadIdx.x; base < vocab; base += blockDim.x * kBatch) {
+            float v[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int token = base + u * blockDim.x;
+                v[u] = token < vocab ? score_of(token) : __int_as_float(0x7fc00000);
             }
-            if (remaining > 0u) {
-                for (int i = 255; i >= 0; --i) {
-                    if (hist[i] >= remaining) {
-                        bin = (unsigned)i;
-                        break;
-                    }
-                    remaining -= hist[i];
-                }
-            }
-            s_prefix = prefix | (bin << shift);
-            s_remaining = remaining;
-            s_ties = hist[bin];
-        }
-        __syncthreads();
-        if (shift == 24 && s_remaining == 0u) break;    // nothing but NaN in the row
-    }
-    const unsigned threshold = s_prefix;
-    const unsigned need_ties = s_remaining;             // how many of the keys equal to the threshold belong to the k
-    const unsigned ties = s_ties;
-    __syncthreads();
-    if (threadIdx.x == 0) s_count = 0u;
-    __syncthreads();
-    if (need_ties > 0u) {
-        // everything above the threshold, and the ties when all of them are wanted
-        for (int token = threadIdx.x; token < vocab; token += blockDim.x) {
-            const float v = score_of(token);
-            const unsigned key = score_key(v);
-            if (key > threshold || (key == threshold && ties == need_ties)) {
-                const unsigned at = atomicAdd(&s_count, 1u);
-                if (at < (unsigned)kMaxTopK) {
-                    cand_score[at] = v;
-                    cand_token[at] = token;
-                }
-            }
-        }
-        __syncthreads();
-        if (ties != need_ties) {
-            // more equal scores at the threshold than places left: the lowest token ids among them, one by one
-            int previous = -1;
-            for (unsigned pick = 0; pick < need_ties; ++pick) {
-                Best mine{0.0f, -1};
-                for (int token = threadIdx.x; token < vocab; token += blockDim.x) {
-                    if (token <= previous) continue;
-                    const float v = score_of(token);
-                    if (score_key(v) != threshold) continue;
-                    if (mine.token < 0 || token < mine.token) {
-                        mine.score = v;
-                        mine.token = token;
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                if (v[u] >= bound) {
+                    const unsigned at = atomicAdd(&sm.pool_count, 1u);
+                    if (at < (unsigned)kSelectPool) {
+                        sm.pool_score[at] = v[u];
+                        sm.pool_token[at] = base + u * blockDim.x;
                     }
                 }
-                // block_best orders by score first; the scores are equal here, so the lower token wins
-                const Best best = block_best(mine, scratch);
-                if (threadIdx.x == 0 && best.token >= 0) {
-                    const unsigned at = s_count++;
-                    if (at < (unsigned)kMaxTopK) {
-                        cand_score[at] = best.score;
-                        cand_token[at] = best.token;
-                    }
-                }
-                previous = best.token;
-                if (best.token < 0) break;
             }
-            __syncthreads();
         }
+        __syncthreads();
+        const unsigned pooled = sm.pool_count;
+        if (pooled <= (unsigned)kSelectPool)
+            found = select_top_k(sm, (int)pooled, k, [&](int i) { return sm.pool_score[i]; },
+                                 [&](int i) { return sm.pool_token[i]; });
+        else
+            exact_over_vocabulary = true;
     }
-    k = min((int)s_count, kMaxTopK);
-    // rank the candidates among themselves: score descending, then token ascending
-    for (int i = threadIdx.x; i < k; i += blockDim.x) {
-        const float sc = cand_score[i];
-        const int tk = cand_token[i];
-        int rank = 0;
-        for (int j = 0; j < k; ++j) rank += better(cand_score[j], cand_token[j], sc, tk) ? 1 : 0;
-        sorted_score[rank] = sc;
-        sorted_token[rank] = tk;
-    }
-    __syncthreads();
+    if (exact_over_vocabulary) found = select_top_k(sm, vocab, k, score_of, same);
+    k = found;
     if (threadIdx.x != 0) return;
+    float* sorted_score = sm.sorted_score;
+    const int* sorted_token = sm.sorted_token;
     int chosen;
     if (greedy || k <= 1) {
         chosen = k >= 1 ? sorted_token[0] : 0;
