@@ -242,10 +242,13 @@ def time_decode(loaded, sampler, batch: int, steps: int, warmup: int, prompt_tok
     generator = torch.Generator().manual_seed(seed)
     names = [f"b{batch}_{i}" for i in range(batch)]
     chunk = step_fn.max_tokens
-    for name in names:
-        prompt = torch.randint(0, vocab, (prompt_tokens,), generator=generator).tolist()
+    prompts = {name: torch.randint(0, vocab, (prompt_tokens,), generator=generator).tolist() for name in names}
+    # prompts go in as many requests to a step as the step's token limit holds
+    together = max(1, min(step_fn.max_spans, chunk // max(1, min(prompt_tokens, chunk))))
+    for first in range(0, batch, together):
+        group = names[first:first + together]
         for at in range(0, prompt_tokens, chunk):
-            step_fn.run([StepEntry(name, prompt[at:at + chunk], [])], auto_begin=True)
+            step_fn.run([StepEntry(name, prompts[name][at:at + chunk], []) for name in group], auto_begin=True)
     slots = [(loaded.manager.get(name).slot, GREEDY) for name in names]
     feed = torch.randint(0, vocab, (warmup + steps, batch), generator=generator).tolist()
 

@@ -251,46 +251,23 @@ __device__ int select_top_k(SelectShared& sm, const int n, const int k, ScoreAt 
     return found;
 }
 
-// One block per row. The k best scores of the vocabulary are found in two stages. First every thread keeps
-// the largest score of its share of the vocabulary; the k-th largest of these maxima is a lower bound of the
-// k-th largest score (k different tokens reach it), so one more pass that keeps every token at or above it
-// leaves a pool of little more than k candidates for the exact selection. A pool that overflows (scores that
-// are equal by the thousand) sends the row to the exact selection over the whole vocabulary instead. The
-// vocabulary is read twice where the plain form reads it k times.
-__global__ void sample_kernel(const float* logits, long long ld, int vocab,
-                              const int* row_slot, uint8_t* seen_base,
-                              unsigned long long* rng, const float* temperature,
-                              const int* top_k, const float* top_p,
-                              const float* penalty, int* out) {
-    __shared__ SelectShared sm;
-    chain_release();
-    chain_wait();
-    const int row = blockIdx.x;
-    const float* l = logits + (size_t)row * ld;
-    const int slot = row_slot ? row_slot[row] : row;
-    uint8_t* seen = seen_base ? seen_base + (size_t)slot * vocab : nullptr;
-    const float temp = temperature ? temperature[row] : 0.0f;
-    const float pen = penalty ? penalty[row] : 1.0f;
-    int k = top_k ? top_k[row] : 1;
-    const bool greedy = temp <= 0.0f || k == 1;
-    k = greedy ? 1 : min(min(k, kMaxTopK), vocab);
-    auto score_of = [&](int token) {
-        float v = penalised(l, seen, token, pen);
-        if (!greedy) v = v / temp;
-        return v;
-    };
-    auto same = [](int i) { return i; };
+// The k best scores of tokens [begin, end) of a row, into sm.sorted_*, in two stages. First every thread keeps
+// the largest score of its share; the k-th largest of these maxima is a lower bound of the k-th largest score
+// (k different tokens reach it), so one more pass that keeps every token at or above it leaves a pool of little
+// more than k candidates for the exact selection. A pool that overflows (scores that are equal by the thousand)
+// sends the range to the exact selection over all of it instead. The range is read twice where the plain form
+// reads it k times. Returns how many were found.
+template <typename ScoreOf>
+__device__ int range_top_k(SelectShared& sm, const int begin, const int end, const int k, ScoreOf score_of) {
     constexpr int kBatch = 8;
-
-    // stage one: every thread's maximum, and the k-th largest of those
     float mine = -INFINITY;
     bool any = false;
-    for (int base = threadIdx.x; base < vocab; base += blockDim.x * kBatch) {
+    for (int base = begin + threadIdx.x; base < end; base += blockDim.x * kBatch) {
         float v[kBatch];
 #pragma unroll
         for (int u = 0; u < kBatch; ++u) {
             const int token = base + u * blockDim.x;
-            v[u] = token < vocab ? score_of(token) : __int_as_float(0x7fc00000);
+            v[u] = token < end ? score_of(token) : __int_as_float(0x7fc00000);
         }
 #pragma unroll
         for (int u = 0; u < kBatch; ++u) {
@@ -301,87 +278,177 @@ __global__ void sample_kernel(const float* logits, long long ld, int vocab,
         }
     }
     sm.thread_max[threadIdx.x] = any ? mine : __int_as_float(0x7fc00000);
-    int found = select_top_k(sm, (int)blockDim.x, k, [&](int i) { return sm.thread_max[i]; }, same);
-    bool exact_over_vocabulary = found == 0;           // no score at all: the plain path reports it the same way
-    if (found > 0) {
-        const float bound = sm.sorted_score[found - 1];
-        __syncthreads();
-        if (threadIdx.x == 0) sm.pool_count = 0u;
-        __syncthreads();
-        for (int base = threadIdx.x; base < vocab; base += blockDim.x * kBatch) {
-            float v[kBatch];
+    int found = select_top_k(sm, (int)blockDim.x, k, [&](int i) { return sm.thread_max[i]; }, [](int i) { return i; });
+    if (found == 0) return 0;                          // not one score that is a number
+    const float bound = sm.sorted_score[found - 1];
+    __syncthreads();
+    if (threadIdx.x == 0) sm.pool_count = 0u;
+    __syncthreads();
+    for (int base = begin + threadIdx.x; base < end; base += blockDim.x * kBatch) {
+        float v[kBatch];
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int token = base + u * blockDim.x;
-                v[u] = token < vocab ? score_of(token) : __int_as_float(0x7fc00000);
-            }
+        for (int u = 0; u < kBatch; ++u) {
+            const int token = base + u * blockDim.x;
+            v[u] = token < end ? score_of(token) : __int_as_float(0x7fc00000);
+        }
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                if (v[u] >= bound) {
-                    const unsigned at = atomicAdd(&sm.pool_count, 1u);
-                    if (at < (unsigned)kSelectPool) {
-                        sm.pool_score[at] = v[u];
-                        sm.pool_token[at] = base + u * blockDim.x;
-                    }
+        for (int u = 0; u < kBatch; ++u) {
+            if (v[u] >= bound) {
+                const unsigned at = atomicAdd(&sm.pool_count, 1u);
+                if (at < (unsigned)kSelectPool) {
+                    sm.pool_score[at] = v[u];
+                    sm.pool_token[at] = base + u * blockDim.x;
                 }
             }
         }
-        __syncthreads();
-        const unsigned pooled = sm.pool_count;
-        if (pooled <= (unsigned)kSelectPool)
-            found = select_top_k(sm, (int)pooled, k, [&](int i) { return sm.pool_score[i]; },
-                                 [&](int i) { return sm.pool_token[i]; });
-        else
-            exact_over_vocabulary = true;
     }
-    if (exact_over_vocabulary) found = select_top_k(sm, vocab, k, score_of, same);
-    k = found;
-    if (threadIdx.x != 0) return;
+    __syncthreads();
+    const unsigned pooled = sm.pool_count;
+    if (pooled <= (unsigned)kSelectPool)
+        return select_top_k(sm, (int)pooled, k, [&](int i) { return sm.pool_score[i]; },
+                            [&](int i) { return sm.pool_token[i]; });
+    return select_top_k(sm, end - begin, k, [&](int i) { return score_of(begin + i); }, [&](int i) { return begin + i; });
+}
+
+// What one thread does with the k candidates in sm.sorted_*: arg-max, or softmax, top-p and the draw.
+__device__ int draw_from_sorted(SelectShared& sm, const int k, const bool greedy, const float p,
+                                unsigned long long* rng_state) {
     float* sorted_score = sm.sorted_score;
     const int* sorted_token = sm.sorted_token;
-    int chosen;
-    if (greedy || k <= 1) {
-        chosen = k >= 1 ? sorted_token[0] : 0;
+    if (greedy || k <= 1) return k >= 1 ? sorted_token[0] : 0;
+    const float maximum = sorted_score[0];
+    float total = 0.0f;
+    for (int i = 0; i < k; ++i) {
+        sorted_score[i] = expf(sorted_score[i] - maximum);
+        total += sorted_score[i];
+    }
+    for (int i = 0; i < k; ++i) sorted_score[i] /= total;
+    int active = k;
+    if (p < 1.0f) {
+        float cumulative = 0.0f;
+        active = 0;
+        do {
+            cumulative += sorted_score[active++];
+        } while (active < k && cumulative < p);
+        total = 0.0f;
+        for (int i = 0; i < active; ++i) total += sorted_score[i];
     } else {
-        const float maximum = sorted_score[0];
-        float total = 0.0f;
-        for (int i = 0; i < k; ++i) {
-            sorted_score[i] = expf(sorted_score[i] - maximum);
-            total += sorted_score[i];
-        }
-        for (int i = 0; i < k; ++i) sorted_score[i] /= total;
-        int active = k;
-        const float p = top_p ? top_p[row] : 1.0f;
-        if (p < 1.0f) {
-            float cumulative = 0.0f;
-            active = 0;
-            do {
-                cumulative += sorted_score[active++];
-            } while (active < k && cumulative < p);
-            total = 0.0f;
-            for (int i = 0; i < active; ++i) total += sorted_score[i];
-        } else {
-            total = 1.0f;
-        }
-        unsigned long long state = rng[slot];
-        state ^= state >> 12;
-        state ^= state << 25;
-        state ^= state >> 27;
-        rng[slot] = state;
-        const unsigned long long bits = state * 2685821657736338717ULL;
-        const float unit = (float)(((double)(bits >> 11) + 0.5) * (1.0 / 9007199254740992.0));
-        float target = unit * total;
-        chosen = sorted_token[active - 1];
-        for (int i = 0; i < active; ++i) {
-            target -= sorted_score[i];
-            if (target <= 0.0f) {
-                chosen = sorted_token[i];
-                break;
-            }
+        total = 1.0f;
+    }
+    unsigned long long state = *rng_state;
+    state ^= state >> 12;
+    state ^= state << 25;
+    state ^= state >> 27;
+    *rng_state = state;
+    const unsigned long long bits = state * 2685821657736338717ULL;
+    const float unit = (float)(((double)(bits >> 11) + 0.5) * (1.0 / 9007199254740992.0));
+    float target = unit * total;
+    int chosen = sorted_token[active - 1];
+    for (int i = 0; i < active; ++i) {
+        target -= sorted_score[i];
+        if (target <= 0.0f) {
+            chosen = sorted_token[i];
+            break;
         }
     }
+    return chosen;
+}
+
+struct SampleRow {
+    const float* logits;
+    uint8_t* seen;
+    int slot;
+    float temperature, penalty;
+    int k;
+    bool greedy;
+};
+
+__device__ __forceinline__ SampleRow sample_row(const float* logits, long long ld, int vocab, const int* row_slot,
+                                                uint8_t* seen_base, const float* temperature, const int* top_k,
+                                                const float* penalty, int row) {
+    SampleRow r;
+    r.logits = logits + (size_t)row * ld;
+    r.slot = row_slot ? row_slot[row] : row;
+    r.seen = seen_base ? seen_base + (size_t)r.slot * vocab : nullptr;
+    r.temperature = temperature ? temperature[row] : 0.0f;
+    r.penalty = penalty ? penalty[row] : 1.0f;
+    const int k = top_k ? top_k[row] : 1;
+    r.greedy = r.temperature <= 0.0f || k == 1;
+    r.k = r.greedy ? 1 : min(min(k, kMaxTopK), vocab);
+    return r;
+}
+
+// One block per row: selection over the whole vocabulary and the draw (many rows).
+__global__ void sample_kernel(const float* logits, long long ld, int vocab,
+                              const int* row_slot, uint8_t* seen_base,
+                              unsigned long long* rng, const float* temperature,
+                              const int* top_k, const float* top_p,
+                              const float* penalty, int* out) {
+    __shared__ SelectShared sm;
+    chain_release();
+    chain_wait();
+    const int row = blockIdx.x;
+    const SampleRow r = sample_row(logits, ld, vocab, row_slot, seen_base, temperature, top_k, penalty, row);
+    auto score_of = [&](int token) {
+        float v = penalised(r.logits, r.seen, token, r.penalty);
+        if (!r.greedy) v = v / r.temperature;
+        return v;
+    };
+    const int found = range_top_k(sm, 0, vocab, r.k, score_of);
+    if (threadIdx.x != 0) return;
+    const int chosen = draw_from_sorted(sm, found, r.greedy, top_p ? top_p[row] : 1.0f, rng ? rng + r.slot : nullptr);
     out[row] = chosen;
-    if (seen) seen[chosen] = 1;
+    if (r.seen) r.seen[chosen] = 1;
+}
+
+// Few rows: a row's vocabulary is cut into `chunks` pieces, one block each, so that a handful of rows still
+// uses many SMs; every piece leaves its own k best (part_score / part_token [rows, chunks, kMaxTopK], entries
+// past part_count are unused), and sample_merge_kernel selects among those and draws.
+__global__ void sample_chunks_kernel(const float* logits, long long ld, int vocab, const int* row_slot,
+                                     uint8_t* seen_base, const float* temperature, const int* top_k,
+                                     const float* penalty, int chunks, float* part_score, int* part_token,
+                                     int* part_count) {
+    __shared__ SelectShared sm;
+    chain_release();
+    chain_wait();
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    const SampleRow r = sample_row(logits, ld, vocab, row_slot, seen_base, temperature, top_k, penalty, row);
+    auto score_of = [&](int token) {
+        float v = penalised(r.logits, r.seen, token, r.penalty);
+        if (!r.greedy) v = v / r.temperature;
+        return v;
+    };
+    const int per = (vocab + chunks - 1) / chunks;
+    const int begin = min(vocab, chunk * per), end = min(vocab, begin + per);
+    const int found = end > begin ? range_top_k(sm, begin, end, min(r.k, end - begin), score_of) : 0;
+    const size_t base = ((size_t)row * chunks + chunk) * kMaxTopK;
+    for (int i = threadIdx.x; i < found; i += blockDim.x) {
+        part_score[base + i] = sm.sorted_score[i];
+        part_token[base + i] = sm.sorted_token[i];
+    }
+    if (threadIdx.x == 0) part_count[row * chunks + chunk] = found;
+}
+
+__global__ void sample_merge_kernel(int vocab, const int* row_slot, uint8_t* seen_base, unsigned long long* rng,
+                                    const float* temperature, const int* top_k, const float* top_p, int chunks,
+                                    const float* part_score, const int* part_token, const int* part_count,
+                                    int* out) {
+    __shared__ SelectShared sm;
+    chain_release();
+    chain_wait();
+    const int row = blockIdx.x;
+    const SampleRow r = sample_row(nullptr, 0, vocab, row_slot, seen_base, temperature, top_k, nullptr, row);
+    const size_t base = (size_t)row * chunks * kMaxTopK;
+    const int* counts = part_count + row * chunks;
+    auto score_at = [&](int i) {
+        return (i % kMaxTopK) < counts[i / kMaxTopK] ? part_score[base + i] : __int_as_float(0x7fc00000);
+    };
+    auto token_at = [&](int i) { return part_token[base + i]; };
+    const int found = select_top_k(sm, chunks * kMaxTopK, r.k, score_at, token_at);
+    if (threadIdx.x != 0) return;
+    const int chosen = draw_from_sorted(sm, found, r.greedy, top_p ? top_p[row] : 1.0f, rng ? rng + r.slot : nullptr);
+    out[row] = chosen;
+    if (r.seen) r.seen[chosen] = 1;
 }
 
 // Marks the tokens of a step as seen by their requests: slot = span_slot[token_span[i]].
@@ -464,14 +531,33 @@ __global__ void mark_seen_kernel(uint8_t* seen_base, int vocab, const int* token
 
 using namespace celeg_b200;
 
+constexpr int kSampleChunks = 16;        // pieces a row is cut into when there are few rows
+constexpr int kSampleChunkedRows = 32;   // ... which is when there are at most this many
+
+// Elements of part_score / part_token (and, divided by 128, of part_count) that celeg_sample wants as scratch to
+// cut the rows of a small batch into pieces: kSampleChunkedRows * kSampleChunks * 128.
+CELEG_API int celeg_sample_scratch_elements() { return kSampleChunkedRows * kSampleChunks * kMaxTopK; }
+
+// part_score / part_token / part_count may be null: then every row is one block whatever the number of rows.
 CELEG_API int celeg_sample(const float* logits, long long ld, int vocab, int rows, const int* row_slot,
                            uint8_t* seen, unsigned long long* rng, const float* temperature, const int* top_k,
-                           const float* top_p, const float* penalty, int* out, cudaStream_t stream) {
+                           const float* top_p, const float* penalty, int* out, float* part_score, int* part_token,
+                           int* part_count, cudaStream_t stream) {
     CELEG_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "sample: invalid sizes rows=%d vocab=%d ld=%lld", rows,
                   vocab, ld);
     CELEG_REQUIRE(rng != nullptr || temperature == nullptr, "sample: temperature sampling needs generator states");
     if (rows == 0) return 0;
     const int threads = vocab >= 16384 ? 1024 : 256;
+    if (part_score && part_token && part_count && rows <= kSampleChunkedRows && vocab >= kSampleChunks * 1024) {
+        launch_chained(sample_chunks_kernel, dim3(kSampleChunks, rows), 256, 0, stream, logits, ld, vocab, row_slot,
+                       seen, temperature, top_k, penalty, kSampleChunks, part_score, part_token, part_count);
+        const int status = check_launch("sample (pieces)");
+        if (status != 0) return status;
+        launch_chained(sample_merge_kernel, rows, 256, 0, stream, vocab, row_slot, seen, rng, temperature, top_k,
+                       top_p, kSampleChunks, (const float*)part_score, (const int*)part_token,
+                       (const int*)part_count, out);
+        return check_launch("sample (merge)");
+    }
     launch_chained(sample_kernel, rows, threads, 0, stream, logits, ld, vocab, row_slot, seen, rng, temperature,
                    top_k, top_p, penalty, out);
     return check_launch("sample");

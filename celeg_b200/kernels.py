@@ -73,7 +73,8 @@ _SIGNATURES = {
     "celeg_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                     c_void_p, c_void_p, c_void_p],
+                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "celeg_sample_scratch_elements": [],
     "celeg_sample_greedy": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p],
     "celeg_mark_seen": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
@@ -398,14 +399,27 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, accumula
                                     int(accumulate), _stream()))
 
 
+def sample_scratch(device) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Scratch that lets :func:`sample` cut the rows of a small batch into pieces (one block each): candidate
+    scores, candidate tokens and their counts."""
+    elements = int(library().celeg_sample_scratch_elements())
+    return (torch.zeros(elements, dtype=torch.float32, device=device),
+            torch.zeros(elements, dtype=torch.int32, device=device),
+            torch.zeros(elements // 128, dtype=torch.int32, device=device))
+
+
 def sample(logits: torch.Tensor, rows: int, row_slot: Optional[torch.Tensor], seen: Optional[torch.Tensor],
            rng: Optional[torch.Tensor], temperature: Optional[torch.Tensor], top_k: Optional[torch.Tensor],
-           top_p: Optional[torch.Tensor], penalty: Optional[torch.Tensor], out: torch.Tensor) -> None:
+           top_p: Optional[torch.Tensor], penalty: Optional[torch.Tensor], out: torch.Tensor,
+           scratch: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None) -> None:
+    """One token per row with celeg's rules. ``scratch`` (:func:`sample_scratch`): with it, a batch of at most
+    32 rows over a large vocabulary runs as 16 blocks per row and a merge; without it, one block per row."""
     _need(logits, torch.float32, "logits")
     _need(out, torch.int32, "out")
+    parts = scratch or (None, None, None)
     _check(library().celeg_sample(_ptr(logits), logits.stride(0), logits.shape[1], rows, _ptr(row_slot), _ptr(seen),
                                   _ptr(rng), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(penalty), _ptr(out),
-                                  _stream()))
+                                  _ptr(parts[0]), _ptr(parts[1]), _ptr(parts[2]), _stream()))
 
 
 def sample_greedy(logits: torch.Tensor, rows: int, row_slot: Optional[torch.Tensor], seen: Optional[torch.Tensor],

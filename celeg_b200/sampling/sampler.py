@@ -29,6 +29,7 @@ class Sampler:
         self.out = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self._partial_score = torch.zeros(max_rows * 64, dtype=torch.float32, device=device)
         self._partial_token = torch.zeros(max_rows * 64, dtype=torch.int32, device=device)
+        self._pieces = kernels.sample_scratch(device)        # lets a small batch's rows be cut over several blocks
         self._out_host = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
         self._out_hosts = [self._out_host, torch.zeros(max_rows, dtype=torch.int32).pin_memory()]
         self._flip = 0
@@ -94,7 +95,7 @@ class Sampler:
                                   self._partial_score, self._partial_token)
         else:
             kernels.sample(logits, count, self._dev_i[:m], self.seen, self.rng, self._dev_f[:m], self._dev_i[m:],
-                           self._dev_f[m:2 * m], self._dev_f[2 * m:], self.out)
+                           self._dev_f[m:2 * m], self._dev_f[2 * m:], self.out, scratch=self._pieces)
         host = self._out_hosts[self._flip]
         self._flip ^= 1
         host.copy_(self.out, non_blocking=True)

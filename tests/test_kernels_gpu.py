@@ -354,7 +354,8 @@ def test_qk_norm_rope_in_place_for_a_position_part_of_its_own(dtype, tokens, wit
     assert float((cache.float() - 7.0).abs().max()) == 0.0
 
 
-def test_sampling_greedy_and_seeded():
+@pytest.mark.parametrize("pieces", [False, True])
+def test_sampling_greedy_and_seeded(pieces):
     from celeg_b200 import kernels
     rng = np.random.default_rng(7)
     vocab, rows = 1000, 6
@@ -374,7 +375,7 @@ def test_sampling_greedy_and_seeded():
     seen_host = seen.copy()
     for _ in range(4):                                          # several draws advance the generators
         kernels.sample(dev(logits), rows, dev(slots), seen_dev, rng_dev, dev(temperature), dev(top_k), dev(top_p),
-                       dev(penalty), out)
+                       dev(penalty), out, scratch=kernels.sample_scratch("cuda") if pieces else None)
         got = out.cpu().numpy()
         for r in range(rows):
             slot = slots[r]
@@ -387,8 +388,9 @@ def test_sampling_greedy_and_seeded():
     assert np.array_equal(seen_dev.cpu().numpy(), seen_host)
 
 
-@pytest.mark.parametrize("vocab", [65536, 1000, 40])
-def test_sampling_with_equal_scores_and_small_vocabularies(vocab):
+@pytest.mark.parametrize("pieces", [False, True])
+@pytest.mark.parametrize("vocab", [65536, 20000, 1000, 40])
+def test_sampling_with_equal_scores_and_small_vocabularies(vocab, pieces):
     """The selection of the k best has to order equal scores by token id: rows made of a few distinct values
     (thousands of ties at the k-th place), of one value only, with -0.0 beside 0.0, with a k larger than the
     vocabulary, and with the penalty moving seen tokens across the k-th place; every draw against the plain
@@ -416,7 +418,7 @@ def test_sampling_with_equal_scores_and_small_vocabularies(vocab):
     seen_host = seen.copy()
     for draw in range(5):
         kernels.sample(dev(logits), rows, dev(slots), seen_dev, rng_dev, dev(temperature), dev(top_k), dev(top_p),
-                       dev(penalty), out)
+                       dev(penalty), out, scratch=kernels.sample_scratch("cuda") if pieces else None)
         got = out.cpu().numpy()
         for r in range(rows):
             token, new_state = plain_lfm2.sample_token(logits[r], seen_host[r], int(states[r]), float(temperature[r]),
