@@ -192,6 +192,8 @@ class KernelTimer:
         import torch
 
         def timed(*args, **kwargs):
+            if torch.cuda.is_current_stream_capturing():       # a graph is being recorded: nothing runs now
+                return function(*args, **kwargs)
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             begin.record()
             result = function(*args, **kwargs)
@@ -560,13 +562,12 @@ def run_workload(args) -> dict:
                 for i in range(count)]
         return prompts, opts
 
-    # warm-up: as many requests of the same kind with a few new tokens each, so that the library, the graphs of
-    # the decode shapes and the allocator are past their first use (the requests are finished and released
-    # before the timed run)
+    # warm-up: the same number of requests of the same kind (other prompts and lengths from the same
+    # distribution), run to their end, so that the library, the graphs of the launch shapes a draining batch
+    # goes through and the allocator are past their first use, as in a server that has been up for a while (the
+    # requests are finished and released before the timed run)
     if not args.no_warmup_run:
         warm_prompts, warm_options = batch(requests, 10_000)
-        for option in warm_options:
-            option.max_new_tokens = min(8, new_tokens)
         drive_workload(engine, warm_prompts, warm_options)
     engine.scheduler.metrics = type(engine.scheduler.metrics)()
     for group in engine.loaded.manager.groups:

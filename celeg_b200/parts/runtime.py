@@ -11,6 +11,9 @@ from .. import kernels
 from .options import KernelOptions
 
 
+LIBRARY_ROW_STEP = 64        # row counts of library products are rounded up to a multiple of this (of 8 up to it)
+
+
 class _Sink:
     """Where a part is about to leave its output, and the norm that will read the stream next."""
     __slots__ = ("buffer", "norm", "weight", "split", "used")
@@ -211,10 +214,18 @@ class Runtime:
             kernels.gemm_tcgen05(x, weight, out, rows,
                                  kernels.TC_STORE_F32 if out.dtype == torch.float32 else kernels.TC_STORE,
                                  self.error_flag, self.tensor_core_variant)
-        elif out.dtype == torch.float32:
-            torch.mm(x[:rows], weight.t(), out_dtype=torch.float32, out=out[:rows])
         else:
-            torch.mm(x[:rows], weight.t(), out=out[:rows])
+            # The library chooses its kernel per shape and looks every new shape up (tens of microseconds on
+            # the host): steps whose number of rows changes every time (decoded tokens beside portions) would pay
+            # that for every product. The product therefore runs on a row count from a coarse grid; the rows
+            # past ``rows`` hold what an earlier step left there, each row of a product depends on its own
+            # row of the operand only, and nobody reads their results.
+            step = 8 if rows <= LIBRARY_ROW_STEP else LIBRARY_ROW_STEP      # (few rows: the library has faster kernels)
+            padded = min(-(-rows // step) * step, x.shape[0], out.shape[0])
+            if out.dtype == torch.float32:
+                torch.mm(x[:padded], weight.t(), out_dtype=torch.float32, out=out[:padded])
+            else:
+                torch.mm(x[:padded], weight.t(), out=out[:padded])
 
     def linear_swiglu(self, x: torch.Tensor, gate_up_weight: torch.Tensor, scratch: torch.Tensor,
                       out: torch.Tensor, rows: int, inner: int) -> None:
