@@ -264,3 +264,19 @@ def test_fingerprint_follows_configuration_and_tensor_table(tmp_path):
     assert len({prints["a0"], prints["b0"], prints["f32"], prints["eps"]}) == 4
     shapes = {"w": (2, 3)}
     assert model_fingerprint({"x": 1}, shapes, {"w": "BF16"}) != model_fingerprint({"x": 1}, {"w": (3, 2)}, {"w": "BF16"})
+
+
+def test_kernel_options_are_typed_and_checked():
+    """The switches of the kernel path are fields of one object; the environment is read only on request."""
+    from celeg_b200 import KernelOptions
+    defaults = KernelOptions()
+    assert (defaults.tensor_core_products, defaults.split_norms, defaults.tcgen05_attention) == ("swiglu", True, True)
+    read = KernelOptions.from_env({"CELEG_B200_TENSOR_CORE_PRODUCTS": "all", "CELEG_B200_SPLIT_NORMS": "0",
+                                   "CELEG_B200_PREFETCH_MB": "4.5", "CELEG_B200_TENSOR_CORE_MIN_ROWS": "512",
+                                   "UNRELATED": "1"})
+    assert (read.tensor_core_products, read.split_norms, read.prefetch_mb, read.tensor_core_min_rows) == ("all", False, 4.5, 512)
+    assert KernelOptions.from_env({}) == defaults
+    with pytest.raises(ValueError, match="tensor_core_products"):
+        KernelOptions(tensor_core_products="stream").validate()
+    with pytest.raises(ValueError):
+        KernelOptions.from_env({"CELEG_B200_TENSOR_CORE_VARIANT": "9"})
