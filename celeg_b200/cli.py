@@ -199,6 +199,15 @@ def run(argv=None) -> int:
         print(f"runtime.decode_tokens={decoded}", file=sys.stderr)
         print(f"runtime.decode_ms={decode_s * 1e3:.3f}", file=sys.stderr)
         print(f"runtime.decode_tokens_per_second={decoded / max(decode_s, 1e-9):.3f}", file=sys.stderr)
+        # the engine's own counters (celeg: include/celeg/runtime/concurrency/metrics.hpp:8-58)
+        metrics = engine.metrics()
+        steps = max(metrics.steps, 1)
+        print(f"runtime.scheduler_steps={metrics.steps}", file=sys.stderr)
+        print(f"runtime.pages_high_water={metrics.pages_high_water}", file=sys.stderr)
+        print(f"runtime.pages_total={metrics.pages_total}", file=sys.stderr)
+        print(f"runtime.host_ms_per_step={1e3 * (metrics.host_plan_seconds + metrics.host_launch_seconds + metrics.host_commit_seconds) / steps:.4f}", file=sys.stderr)
+        print(f"runtime.gpu_ms_per_step={1e3 * metrics.gpu_seconds / steps:.4f}", file=sys.stderr)
+        print(f"runtime.model_fingerprint={engine.loaded.fingerprint}", file=sys.stderr)
     return 0
 
 
