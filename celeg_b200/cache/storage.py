@@ -15,18 +15,20 @@ class CacheStorage:
     so one (layer, page, head) tile is a contiguous [page_tokens, head_dim] box.
     Fixed-size state: ``state`` [slots, slot_elements] float32.
 
-    Every group has one page more than its pool gives out, and the slab one slot more than the manager
-    does (``scratch_pages[g]``, ``scratch_slot``): rows that a step adds to reach a launch shape it has a
-    captured graph for write there, and nothing ever reads them."""
+    Every group has some pages more than its pool gives out (``scratch_page_count`` of them, enough for 128
+    positions, from ``scratch_pages[g]`` on), and the slab one slot more than the manager does
+    (``scratch_slot``): rows that a step adds to reach a launch shape it has a captured graph for write there,
+    and nothing ever reads them."""
 
     def __init__(self, groups: Sequence[Tuple[PagedNeed, int]], group_pages: Sequence[int], page_tokens: int,
                  state_layout: StateLayout, slots: int, dtype: torch.dtype, device: torch.device):
         self.page_tokens = page_tokens
+        self.scratch_page_count = max(1, -(-128 // page_tokens))
         self.k: List[torch.Tensor] = []
         self.v: List[torch.Tensor] = []
         for (need, layers), pages in zip(groups, group_pages):
-            shape = (layers, pages + 1, need.kv_heads, page_tokens, need.head_dim)
-            value_shape = (layers, pages + 1, need.kv_heads, page_tokens, need.value_dim)
+            shape = (layers, pages + self.scratch_page_count, need.kv_heads, page_tokens, need.head_dim)
+            value_shape = (layers, pages + self.scratch_page_count, need.kv_heads, page_tokens, need.value_dim)
             # zeros, not empty: a page that was never written must not hold NaN bit patterns,
             # because masked keys are still multiplied by a zero weight in some kernels
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))

@@ -16,7 +16,7 @@ from ..parts.options import KernelOptions
 from ..weights.loader import load_tensors
 from ..weights.safetensors_io import TensorRepository
 from .model import Model
-from .step import StepFunction
+from .step import PADDING_TOKENS, StepFunction
 
 DEFAULT_PAGE_TOKENS = 16        # celeg's CUDA engine default (include/celeg/backend/cuda/concurrency.hpp:23)
 
@@ -68,8 +68,9 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0", *, max_context
     finally:
         repository.close()
     context = min(max_context or spec.max_context, spec.max_context) if max_context else spec.max_context
-    rt = Runtime(device, dtype, max_batched_tokens, max_requests=max_requests, max_context=context,
-                 options=kernel_options)
+    # (buffers hold the rows a step may be padded by when it takes its launch shape from a grid, see StepFunction)
+    rt = Runtime(device, dtype, max_batched_tokens + (PADDING_TOKENS if use_graphs else 0), max_requests=max_requests,
+                 max_context=context, options=kernel_options)
     with torch.cuda.device(device):
         model = Model(spec, tensors, rt)
         del tensors

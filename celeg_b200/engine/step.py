@@ -49,6 +49,23 @@ def _align4(n: int) -> int:
     return (n + 3) // 4 * 4
 
 
+PROMPT_TOKEN_STEP = 128       # a padded prompt step's portions are filled up to a multiple of this many tokens
+PADDING_TOKENS = PROMPT_TOKEN_STEP + 32   # most rows a step may be padded by (portions + spare single tokens)
+
+
+@dataclass
+class _PaddedPrompt:
+    """The launch shape of a padded prompt step (see ``StepFunction._padded_prompt_shape``)."""
+    key: tuple
+    singles: int             # single tokens the step really brings
+    single_rows: int         # ... and how many rows they take
+    portions: int
+    padded_tokens: int       # tokens of the portions and of the spare portion together
+    spare_tokens: int
+    spans: int
+    logit_rows: int
+
+
 class StepFunction:
     def __init__(self, model: Model, manager: CacheManager, storage: CacheStorage, rt: Runtime,
                  max_tokens: int, max_spans: int, max_context: int, use_graphs: bool = False):
@@ -62,8 +79,10 @@ class StepFunction:
         self.page_tokens = manager.page_tokens
         self.max_pages = (max_context + self.page_tokens - 1) // self.page_tokens
         self.groups = len(manager.groups)
-        capacity = (3 * _align4(max_tokens) + _align4(max_spans + 1) + _align4(max_spans) + _align4(max_tokens)
-                    + self.groups * _align4(max_spans * self.max_pages))
+        # (the runtime's buffers hold more rows than a step may bring: room for the rows a step is padded by)
+        self.buffer_tokens = max(max_tokens, rt.max_tokens)
+        capacity = (3 * _align4(self.buffer_tokens) + _align4(max_spans + 1) + _align4(max_spans)
+                    + _align4(self.buffer_tokens) + self.groups * _align4(max_spans * self.max_pages))
         # a ring of pinned staging buffers: a buffer is refilled only after the copy that read it
         # last has finished on the device
         self._ring = [torch.empty(capacity, dtype=torch.int32).pin_memory() for _ in range(4)]
@@ -81,6 +100,7 @@ class StepFunction:
         self._graph_launches: Dict[tuple, int] = {}
         self._prompt_seen: Dict[tuple, int] = {}
         self.max_prompt_graphs = 24
+        self.max_padded_graphs = 96
         self.steps_run = 0
         self.kernel_steps_graphed = 0
         self.last_step: Optional[StepContext] = None
@@ -166,7 +186,11 @@ class StepFunction:
         spans = len(entries)
         all_decode = total == spans
         max_ctx = max(cache.tokens + len(entry.tokens) for entry, cache in zip(entries, caches))
-        prompt_key = self._prompt_graph_key(entries, total, wanted, max_ctx) if not all_decode else None
+        mixed = None if all_decode else self._padded_prompt_shape(entries, wanted, max_ctx)
+        if all_decode or mixed is not None:
+            prompt_key = mixed.key if mixed is not None else None
+        else:
+            prompt_key = self._prompt_graph_key(entries, total, wanted, max_ctx)
         if (all_decode and self.use_graphs) or prompt_key is not None:
             stride = self.max_pages                         # fixed, so the captured addresses hold
         else:
@@ -181,7 +205,12 @@ class StepFunction:
         # a decoding step that will be replayed from a graph takes a launch shape from a short list, so that
         # a batch that shrinks request by request does not capture a graph for every size
         padded = self._graph_rows(spans) if (all_decode and self.use_graphs and wanted <= self.max_spans) else spans
-        step, logit_rows, n_words = self._stage(entries, caches, total, spans, wanted, stride, max_ctx, padded)
+        n_logits = wanted
+        if mixed is not None:
+            step, logit_rows, n_words = self._stage_padded_prompt(entries, caches, mixed, stride, max_ctx)
+            n_logits = mixed.logit_rows
+        else:
+            step, logit_rows, n_words = self._stage(entries, caches, total, spans, wanted, stride, max_ctx, padded)
         self._dev[:n_words].copy_(self._host[:n_words], non_blocking=True)
         if token_source is not None:
             # the tokens of this step are on the device already (what the step before drew): token i of
@@ -204,9 +233,9 @@ class StepFunction:
 
         graph_key = (padded, wanted, _context_bucket(max_ctx)) if (all_decode and self.use_graphs and wanted <= self.max_spans) else prompt_key
         if graph_key is not None:
-            self._run_graphed(graph_key, step, logit_rows, wanted, logits)
+            self._run_graphed(graph_key, step, logit_rows, n_logits, logits)
         else:
-            self.model.forward(step, logit_rows, wanted, logits)
+            self.model.forward(step, logit_rows, n_logits, logits)
         for entry, cache in zip(entries, caches):
             self.manager.advance(cache, cache.tokens + len(entry.tokens))
         self.steps_run += 1
@@ -215,6 +244,139 @@ class StepFunction:
         self.host_seconds["stage"] += staged - checked
         self.host_seconds["forward"] += done - staged
         return logits[:wanted]
+
+    def _padded_prompt_shape(self, entries, wanted: int, max_ctx: int):
+        """A step of the form the scheduler plans under load (single decoded tokens first, then prompt portions)
+        rarely has the shape of an earlier one: the number of decoding requests and the portions' lengths change
+        from step to step, and launching it kernel by kernel from the host costs more than a small step takes on
+        the device. Such a step can take a launch shape from a coarse grid instead: spare single tokens up to a
+        row count of :meth:`_graph_rows`, and one spare portion that fills the portions' tokens up to a multiple
+        of ``PROMPT_TOKEN_STEP``. Spare rows carry token 0 at positions 0.. of the storage's spare pages and
+        slot; the kernels take their bounds (attention tiles, longest span) from the grid, not from the step.
+        Returns the shape (with its graph key) once it has come twice, else None."""
+        if not self.use_graphs or wanted > self.max_spans:
+            return None
+        lengths = [len(e.tokens) for e in entries]
+        singles = next((i for i, n in enumerate(lengths) if n != 1), len(lengths))
+        portions = lengths[singles:]
+        if not portions or any(n == 1 for n in portions):
+            return None                                   # all single tokens, or a single token after a portion
+        single_rows = self._graph_rows(singles) if singles else 0
+        portion_tokens = sum(portions)
+        padded_tokens = -(-portion_tokens // PROMPT_TOKEN_STEP) * PROMPT_TOKEN_STEP
+        spare = padded_tokens - portion_tokens
+        spans = single_rows + len(portions) + (1 if spare else 0)
+        logit_rows = max(1, wanted, single_rows + len(portions))       # (a scheduler's step wants one row a span at most)
+        if (single_rows + padded_tokens > self.buffer_tokens or spans > self.max_spans or logit_rows > self.max_spans
+                or single_rows - singles > PADDING_TOKENS - PROMPT_TOKEN_STEP
+                or spare > self.storage.scratch_page_count * self.page_tokens):
+            return None
+        key = ("padded prompt", single_rows, len(portions), padded_tokens, logit_rows, _context_bucket(max_ctx))
+        if key not in self._graphs:
+            if len(self._prompt_seen) > 4096:
+                self._prompt_seen.clear()
+            seen = self._prompt_seen.get(key, 0) + 1
+            self._prompt_seen[key] = seen
+            if seen < 2:
+                return None
+            kept = [k for k in self._graphs if k and k[0] == "padded prompt"]
+            if len(kept) >= self.max_padded_graphs:          # the oldest goes (dicts keep insertion order)
+                del self._graphs[kept[0]]
+                del self._graph_launches[kept[0]]
+        return _PaddedPrompt(key, singles, single_rows, len(portions), padded_tokens, spare, spans, logit_rows)
+
+    def _stage_padded_prompt(self, entries, caches, shape: "_PaddedPrompt", stride: int, max_ctx: int):
+        """:meth:`_stage` for a step padded to ``shape``: rows are [the single tokens | spare single tokens | the
+        portions | the spare portion]; the logit rows are the wanted ones followed by repeats of row 0."""
+        host = self._host_np
+        total, spans = shape.single_rows + shape.padded_tokens, shape.spans
+        offsets = {}
+        cursor = 0
+        for name, size in (("token_ids", total), ("positions", total), ("token_span", total),
+                           ("span_begin", spans + 1), ("span_slot", spans), ("logit_rows", shape.logit_rows)):
+            offsets[name] = cursor
+            cursor += _align4(size)
+        table_offsets = []
+        for _ in range(self.groups):
+            table_offsets.append(cursor)
+            cursor += _align4(spans * stride)
+        token_ids = host[offsets["token_ids"]:offsets["token_ids"] + total]
+        positions = host[offsets["positions"]:offsets["positions"] + total]
+        token_span = host[offsets["token_span"]:offsets["token_span"] + total]
+        span_begin = host[offsets["span_begin"]:offsets["span_begin"] + spans + 1]
+        span_slot = host[offsets["span_slot"]:offsets["span_slot"] + spans]
+        logit_rows_host = host[offsets["logit_rows"]:offsets["logit_rows"] + shape.logit_rows]
+        tables = [host[o:o + spans * stride].reshape(spans, stride) for o in table_offsets]
+        for grid in tables:
+            grid.fill(NO_PAGE)
+        scratch_slot = self.storage.scratch_slot
+        row = 0
+        span = 0
+        out = 0
+        lengths = []
+
+        def real(entry, cache):
+            nonlocal row, span, out
+            count = len(entry.tokens)
+            token_ids[row:row + count] = entry.tokens
+            positions[row:row + count] = np.arange(cache.tokens, cache.tokens + count, dtype=np.int32)
+            token_span[row:row + count] = span
+            span_begin[span] = row
+            span_slot[span] = cache.slot
+            for place in entry.want:
+                logit_rows_host[out] = row + int(place)
+                out += 1
+            for g in range(self.groups):
+                table = cache.table_array(g)
+                used = min(table.shape[0], stride)
+                tables[g][span, :used] = table[:used]
+            lengths.append(count)
+            row += count
+            span += 1
+
+        def spare(count):
+            nonlocal row, span
+            token_ids[row:row + count] = 0
+            positions[row:row + count] = np.arange(count, dtype=np.int32)
+            token_span[row:row + count] = span
+            span_begin[span] = row
+            span_slot[span] = scratch_slot
+            pages = -(-count // self.page_tokens)
+            for g in range(self.groups):
+                first = self.storage.scratch_pages[g]
+                tables[g][span, :pages] = np.arange(first, first + pages, dtype=np.int32)
+            lengths.append(count)
+            row += count
+            span += 1
+
+        for entry, cache in zip(entries[:shape.singles], caches[:shape.singles]):
+            real(entry, cache)
+        for _ in range(shape.single_rows - shape.singles):
+            spare(1)
+        for entry, cache in zip(entries[shape.singles:], caches[shape.singles:]):
+            real(entry, cache)
+        if shape.spare_tokens:
+            spare(shape.spare_tokens)
+        assert row == total and span == spans and out <= shape.logit_rows
+        span_begin[spans] = row
+        logit_rows_host[out:] = 0
+        dev = self._dev
+
+        def view(name, size):
+            return dev[offsets[name]:offsets[name] + size]
+
+        step = StepContext(
+            tokens=total, spans=spans,
+            token_ids=view("token_ids", total), positions=view("positions", total),
+            token_span=view("token_span", total), span_begin=view("span_begin", spans + 1),
+            span_slot=view("span_slot", spans),
+            block_tables=[dev[o:o + spans * stride].view(spans, stride) for o in table_offsets],
+            error_flag=self.error_flag, max_span=shape.padded_tokens, max_context=max_ctx,
+            context_bucket=_context_bucket(max_ctx), host_span_lengths=lengths,
+            leading_single_tokens=shape.single_rows,
+            prompt_tile_bound=-(-shape.padded_tokens // PROMPT_TOKEN_STEP) + shape.portions + 1,
+            logits_of_all_rows=False)
+        return step, view("logit_rows", shape.logit_rows), cursor
 
     def _prompt_graph_key(self, entries, total: int, wanted: int, max_ctx: int):
         """Steps with prompt portions are launched from the host kernel by kernel, which takes longer than the

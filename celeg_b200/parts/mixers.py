@@ -225,7 +225,7 @@ class AttentionMixer:
         if (lengths is not None and rt.tcgen05_attention and kernels.attention_prefill_tcgen05_supported(
                 self.heads, self.kv_heads, self.head_dim, b.page_tokens, rt.act_dtype)):
             # head size 64: S and O' in tensor memory, Q/K/V by TMA
-            tiles = sum((length + 127) // 128 for length in lengths)
+            tiles = step.prompt_tile_bound or sum((length + 127) // 128 for length in lengths)
             kernels.attention_prefill_tcgen05(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
                                               span_begin, span_table, step.tokens, spans, tiles, self.heads,
                                               self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale,

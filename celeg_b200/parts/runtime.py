@@ -284,4 +284,7 @@ class StepContext:
     host_positions: Optional[list] = None
     host_span_lengths: Optional[list] = None
     leading_single_tokens: int = 0    # how many spans at the start of the step bring exactly one token
+    # an upper bound of the prompt attention's query tiles that does not depend on the spans' lengths (steps
+    # padded to a launch shape that a graph is replayed for); None: count the tiles from the lengths
+    prompt_tile_bound: Optional[int] = None
     extras: Dict[str, object] = field(default_factory=dict)

@@ -170,6 +170,7 @@ def test_values_may_be_narrower_than_keys_or_absent():
     assert [need.value_dim for need in needs] == [16, 8, 0]
     storage = CacheStorage([(need, 2) for need in needs], [5, 5, 5], 4, StateLayout(), 3, torch.float32,
                            torch.device("cpu"))
-    assert [tuple(k.shape) for k in storage.k] == [(2, 6, 2, 4, 16), (2, 6, 2, 4, 16), (2, 6, 1, 4, 48)]
-    assert [tuple(v.shape) for v in storage.v] == [(2, 6, 2, 4, 16), (2, 6, 2, 4, 8), (2, 6, 1, 4, 0)]
-    assert storage.scratch_pages == [5, 5, 5] and storage.scratch_slot == 3 and storage.state.shape[0] == 4
+    assert [tuple(k.shape) for k in storage.k] == [(2, 37, 2, 4, 16), (2, 37, 2, 4, 16), (2, 37, 1, 4, 48)]
+    assert [tuple(v.shape) for v in storage.v] == [(2, 37, 2, 4, 16), (2, 37, 2, 4, 8), (2, 37, 1, 4, 0)]
+    assert storage.scratch_pages == [5, 5, 5] and storage.scratch_page_count == 32
+    assert storage.scratch_slot == 3 and storage.state.shape[0] == 4

@@ -1281,7 +1281,10 @@ def test_equal_prompt_portions_are_replayed_from_a_graph(tmp_path, name, dtype, 
     """A prompt cut into equal portions: the second portion of a shape is captured in a CUDA graph, the later
     ones are replayed from it (other contexts, other pages, the same launch shapes); a portion of another
     length and a step that mixes a portion with a decoded token run kernel by kernel or get graphs of their
-    own. All of it against the plain implementation, and the same again without graphs gives the same bits."""
+    own. All of it against the plain implementation; the same again without graphs gives the same bits on the
+    float32 path (whose products sum every element in an order that does not depend on the batch) and the same
+    values to rounding on the bfloat16 path (a replayed step runs on a padded launch shape, for which the library
+    may choose another kernel)."""
     from celeg_b200.engine.loading import load_model
     from celeg_b200.engine.step import StepEntry
     folder = write_tiny(tmp_path, name)
@@ -1312,7 +1315,10 @@ def test_equal_prompt_portions_are_replayed_from_a_graph(tmp_path, name, dtype, 
     assert graphed == 5                      # the first portion ran kernel by kernel, the second was captured
     ref, not_graphed = run(False)
     assert not_graphed == 0
-    assert np.array_equal(got, ref)
+    if dtype == "float32":
+        assert np.array_equal(got, ref)
+    else:
+        assert np.abs(got - ref).max() < tol
     for i in range(6):
         assert np.abs(got[i] - want_long[24 * i + 23]).max() < tol, f"portion {i}"
     assert np.abs(got[6] - want_long[153]).max() < tol
@@ -1375,3 +1381,64 @@ def test_requests_that_end_on_a_token_while_the_next_step_is_in_flight(models, d
     engine.loaded.step.raise_on_device_error()
     engine.loaded.manager.check_invariants()
     assert engine.loaded.manager.free_slots == engine.options.max_active_requests
+
+
+@pytest.mark.parametrize("name,dtype,tol", [("A", "float32", 4e-4), ("B", "bfloat16", 8e-2), ("D", "bfloat16", 8e-2)])
+def test_steps_of_changing_mix_are_padded_to_launch_shapes_and_replayed(tmp_path, name, dtype, tol):
+    """Steps of the form the scheduler plans under load: decoded tokens of a changing number of requests first,
+    then one or two prompt portions of changing lengths. No two of them have the same shape, yet from its
+    second coming on a launch shape from the coarse grid (spare single tokens, one spare portion) is replayed
+    from a CUDA graph. Every wanted row of every step against the plain model; graphs must have been used."""
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    folder = write_tiny(tmp_path, name)
+    config, weights = plain_lfm2.load_model_folder(folder)
+    rng = np.random.default_rng(47)
+    count = 14
+    lengths = rng.integers(30, 90, size=count).tolist()
+    seqs = prompts_of(config["vocab_size"], lengths, seed=48)
+    want = [plain_lfm2.forward(config, weights, s) for s in seqs]
+    loaded = load_model(folder, dtype=dtype, max_requests=12, cache_tokens=12 * 96, max_batched_tokens=96,
+                        use_graphs=True)
+    step = loaded.step
+    at = [0] * count
+    decoding, waiting, prefilling = [], list(range(count)), []
+    steps = 0
+    while decoding or waiting or prefilling:
+        entries, places = [], []
+        for r in list(decoding):                           # single tokens first
+            entries.append(StepEntry(f"r{r}", [seqs[r][at[r]]], [0]))
+            places.append((r, at[r]))
+            at[r] += 1
+        budget = 2                                         # then up to two portions
+        while len(prefilling) < budget and waiting and len(decoding) + len(prefilling) < 10:
+            prefilling.append(waiting.pop(0))
+        started = []
+        for r in list(prefilling)[:budget]:
+            # a request's prompt is all but its last 12 tokens, which it then decodes one by one
+            left = lengths[r] - 12 - at[r]
+            n = int(min(left, rng.integers(2, 30)))
+            last = n == left
+            entries.append(StepEntry(f"r{r}", seqs[r][at[r]:at[r] + n], [n - 1] if last else []))
+            if last:
+                places.append((r, at[r] + n - 1))
+                started.append(r)
+            at[r] += n
+        logits = step.run(entries, auto_begin=True).float().cpu().numpy()
+        assert logits.shape[0] == len(places)
+        for row, (r, place) in enumerate(places):
+            worst = np.abs(logits[row] - want[r][place]).max()
+            assert worst < tol, f"step {steps}, request {r}, place {place}: {worst:.3e}"
+        for r in started:
+            prefilling.remove(r)
+            decoding.append(r)
+        for r in list(decoding):
+            if at[r] == lengths[r]:
+                decoding.remove(r)
+                step.end(f"r{r}")
+        steps += 1
+        assert steps < 2000
+    step.raise_on_device_error()
+    loaded.manager.check_invariants()
+    padded = [k for k in step._graphs if k and k[0] == "padded prompt"]
+    assert len(padded) >= 3 and step.kernel_steps_graphed > steps // 3, (len(padded), step.kernel_steps_graphed, steps)
