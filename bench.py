@@ -4,11 +4,19 @@ weights (batch 8, 512-token prompts, context 4,096), plus prefill of 2,048 token
 batch 1 and 64. Prints ONE JSON line.
 
   python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+  python bench.py --phase decode|prefill [--sizes lfm2-1.2b|lfm2-700m|lfm2-350m] [--batch B] [--prompt-tokens P]
+                  [--prefill-tokens T] [--chunk C] [--kernel-times] [--no-cuda-graph]      one phase, a short record
+  python bench.py --workload lfm2-700m|lfm2-350m [--requests N] [--new-tokens N] [--max-batched-tokens N]
+                  [--prefill-chunk N] [--kernel-times]       a scheduler workload through Engine.submit/step/poll
 
 A "step" is one decode step of the whole batch. ``value`` is timed on the device (CUDA events
 around K steps of step function + sampling kernel, synthetic token ids); ``e2e`` is the same
 through ``Engine.step()``: host token ids in through pinned memory, sampled ids back to the host
 every step. Weights (2.3 GB) are larger than L2, so no flush is needed between iterations.
+``--impl reference`` runs celsowm/celeg's own engine on the same model folder and workload through its
+C API (``baseline/reference_bench.py`` over ``baseline/_ref/libceleg.so``, which
+``baseline/build_reference.py`` builds from celeg's sources). Switches of the kernel path can be set
+for a run with ``CELEG_B200_<FIELD>`` (fields of ``celeg_b200.KernelOptions``).
 """
 from __future__ import annotations
 
