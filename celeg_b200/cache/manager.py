@@ -91,8 +91,13 @@ class RequestCache:
     first_live_page: List[int] = field(default_factory=list)  # per group: pages below it were given back
     closed: bool = False
     # per group: the same table as an int32 array (capacity >= length), kept in step with ``tables`` by the
-    # manager, so that a step copies a request's table into its staging buffer with one memcpy
+    # manager, so that a step copies a request's table into its staging buffer with one memcpy; with a
+    # manager that keeps table mirrors these are rows of the mirrors (one row per slot)
     arrays: List[np.ndarray] = field(default_factory=list)
+    # positions that fit into the pages held (the smallest group decides): while a request stays below it,
+    # no page has to be found for it and nobody needs to look at its tables
+    capacity: int = 0
+    page_tokens: int = 0
 
     def held_pages(self, group: int) -> List[int]:
         return [page for page in self.tables[group] if page != NO_PAGE]
@@ -107,19 +112,28 @@ class RequestCache:
         table.extend(pages)
         array = self.arrays[group]
         if len(table) > array.shape[0]:
+            # (a row of a mirror is as long as the longest context needs; a table that outgrows it is a
+            # request past the context limit, which the step function refuses: the row is left behind)
             grown = np.full(max(len(table), 2 * array.shape[0], 16), NO_PAGE, dtype=np.int32)
             grown[:start] = array[:start]
             self.arrays[group] = array = grown
         array[start:len(table)] = pages
+        self.capacity = min(len(t) for t in self.tables) * self.page_tokens
 
 
 class CacheManager:
     def __init__(self, page_tokens: int, group_pages: Sequence[int], groups: Sequence[Tuple[tuple, PagedNeed]],
                  state_layout: StateLayout, slots: int,
-                 clear_slot: Optional[Callable[[int], None]] = None):
+                 clear_slot: Optional[Callable[[int], None]] = None, table_capacity: Optional[int] = None):
+        """``table_capacity``: with a number, the manager keeps every group's block tables of all slots in one
+        int32 array ``table_mirrors[group][slot, :table_capacity]`` (NO_PAGE where a request holds nothing), so
+        that a step gathers the tables of its requests with one indexing operation."""
         if len(group_pages) != len(groups):
             raise ValueError("one page count per paged group is needed")
         self.page_tokens = page_tokens
+        self.table_mirrors: Optional[List[np.ndarray]] = None
+        if table_capacity is not None:
+            self.table_mirrors = [np.full((slots, max(1, table_capacity)), NO_PAGE, dtype=np.int32) for _ in groups]
         self.groups: List[PagedGroup] = [
             PagedGroup(key=key, need=need, pool=PagePool(pages, page_tokens))
             for (key, need), pages in zip(groups, group_pages)]
@@ -128,6 +142,7 @@ class CacheManager:
         self.total_slots = slots
         self._clear_slot = clear_slot
         self._live: Dict[Hashable, RequestCache] = {}
+        self._any_window = any(group.window is not None for group in self.groups)
 
     # ------------------------------------------------------------------ queries
     @property
@@ -155,6 +170,39 @@ class CacheManager:
             out.append(max(0, group.pool.pages_for(new_total) - have))
         return out
 
+    def pages_needed_each(self, caches: Sequence[RequestCache], counts: Sequence[int]) -> List[int]:
+        """Per group, the pages that must be added so that every ``caches[i]`` can take ``counts[i]`` more
+        positions. A request that stays within the pages it holds is passed over without a look at its tables."""
+        total = [0] * len(self.groups)
+        for cache, count in zip(caches, counts):
+            if cache.tokens + count > cache.capacity:
+                for index, pages in enumerate(self.pages_needed(cache, cache.tokens + count)):
+                    total[index] += pages
+        return total
+
+    def reserve_each(self, caches: Sequence[RequestCache], counts: Sequence[int]) -> None:
+        """:meth:`reserve` for every ``caches[i]`` up to ``counts[i]`` more positions (the caller has checked
+        with :meth:`pages_needed_each` that the pools hold enough)."""
+        for cache, count in zip(caches, counts):
+            if cache.tokens + count > cache.capacity:
+                self.reserve(cache, cache.tokens + count)
+            elif cache.closed:
+                raise PageError(f"request {cache.request_id!r} was closed")
+
+    def advance_each(self, caches: Sequence[RequestCache], counts: Sequence[int]) -> None:
+        """:meth:`advance` for every ``caches[i]`` by ``counts[i]`` positions."""
+        if self._any_window:
+            for cache, count in zip(caches, counts):
+                self.advance(cache, cache.tokens + count)
+            return
+        for cache, count in zip(caches, counts):
+            if count < 0:
+                raise ValueError("a request's length cannot shrink")
+            if cache.tokens + count > cache.capacity:
+                raise PageError(f"request {cache.request_id!r} advanced to {cache.tokens + count} positions "
+                                f"without pages")
+            cache.tokens += count
+
     def can_hold(self, tokens: int) -> bool:
         """Whether a NEW request of ``tokens`` positions could be given its slot and pages now."""
         if not self._free_slots:
@@ -179,10 +227,14 @@ class CacheManager:
         slot = self._free_slots.pop()
         if self._clear_slot is not None:
             self._clear_slot(slot)
+        if self.table_mirrors is not None:
+            arrays = [mirror[slot] for mirror in self.table_mirrors]           # (NO_PAGE throughout: see close)
+        else:
+            arrays = [np.full(16, NO_PAGE, dtype=np.int32) for _ in self.groups]
         cache = RequestCache(request_id=request_id, slot=slot,
                              tables=[[] for _ in self.groups],
                              first_live_page=[0 for _ in self.groups],
-                             arrays=[np.full(16, NO_PAGE, dtype=np.int32) for _ in self.groups])
+                             arrays=arrays, page_tokens=self.page_tokens)
         self._live[request_id] = cache
         return cache
 
@@ -236,7 +288,11 @@ class CacheManager:
             raise PageError(f"request {request_id!r} holds no cache (closed twice?)")
         for index, group in enumerate(self.groups):
             group.pool.release(cache.held_pages(index))
+            used = len(cache.tables[index])
             cache.tables[index] = []
+            if self.table_mirrors is not None:
+                self.table_mirrors[index][cache.slot, :used] = NO_PAGE
+        cache.capacity = 0
         self._free_slots.append(cache.slot)
         cache.closed = True
 

@@ -82,7 +82,8 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0", *, max_context
                                 zip(model.group_needs, model.group_members)],
                                group_pages, page_tokens, model.state_layout, max_requests, dtype, device)
         manager = CacheManager(page_tokens, group_pages, list(zip(model.group_keys, model.group_needs)),
-                               model.state_layout, max_requests, clear_slot=storage.clear_slot)
+                               model.state_layout, max_requests, clear_slot=storage.clear_slot,
+                               table_capacity=(context + page_tokens - 1) // page_tokens)
         for group, members in zip(manager.groups, model.group_members):
             group.members = list(members)
         model.attach(storage)

@@ -161,6 +161,12 @@ class PlannedEntry:
 class Plan:
     entries: List[PlannedEntry] = field(default_factory=list)
     skipped_for_pages: List[Request] = field(default_factory=list)
+    # a plan made by ``Scheduler._plan_after``: every entry is one token that the step before leaves on the device.
+    # Such a plan says the same as the one after it, so it is used again, and what a launch makes of a plan
+    # (the step function's entries, the sampler's rows) is kept with it.
+    ahead: bool = False
+    step_entries: Optional[list] = None
+    sample_rows: Optional[list] = None
 
 
 @dataclass
@@ -380,11 +386,14 @@ class Scheduler:
 
     def _launch(self, plan: Plan, tokens_on_device: bool) -> bool:
         """Enqueues the plan's step (a runner without ``launch`` runs it to its end here)."""
-        entries = [StepEntry(request_id=p.request.id, tokens=p.tokens,
-                             want=[len(p.tokens) - 1] if p.samples else [])
-                   for p in plan.entries]
-        sample_rows = [(p.request.cache.slot, p.request.options.generation) for p in plan.entries if p.samples]
         started = time.perf_counter()
+        if plan.step_entries is None:
+            plan.step_entries = [StepEntry(request_id=p.request.id, tokens=p.tokens,
+                                           want=[len(p.tokens) - 1] if p.samples else [])
+                                 for p in plan.entries]
+            plan.sample_rows = [(p.request.cache.slot, p.request.options.generation)
+                                for p in plan.entries if p.samples]
+        entries, sample_rows = plan.step_entries, plan.sample_rows
         try:
             if self._runs_ahead:
                 handle = self.runner.launch(entries, sample_rows, tokens_on_device)
@@ -403,24 +412,31 @@ class Scheduler:
         same requests, one token each, whatever those tokens are (an end-of-sequence token aside)."""
         if not self._runs_ahead or self.queue or plan.skipped_for_pages or len(plan.entries) != len(self.live):
             return False
-        free = [group.pool.free_pages for group in self.manager.groups]
+        free = None
+        max_context = self.max_context
         for planned in plan.entries:
             request = planned.request
-            if not (planned.is_decode and planned.samples) or request.cancel_requested or request.cache is None:
+            cache = request.cache
+            if not (planned.is_decode and planned.samples) or request.cancel_requested or cache is None:
                 return False
             if len(request.generated) + 2 > request.options.max_new_tokens:
                 return False                          # this step's token may be its last
-            if request.cache.tokens + 1 > self.max_context:
+            if cache.tokens + 1 > max_context:
                 return False
-            needed = self.manager.pages_needed(request.cache, request.cache.tokens + 1)
-            if any(n > f for n, f in zip(needed, free)):
-                return False
-            free = [f - n for f, n in zip(free, needed)]
+            if cache.tokens + 1 > cache.capacity:     # (else: room in the pages it holds)
+                if free is None:
+                    free = [group.pool.free_pages for group in self.manager.groups]
+                needed = self.manager.pages_needed(cache, cache.tokens + 1)
+                if any(n > f for n, f in zip(needed, free)):
+                    return False
+                free = [f - n for f, n in zip(free, needed)]
         return True
 
     @staticmethod
     def _plan_after(plan: Plan) -> Plan:
-        after = Plan()
+        if plan.ahead:
+            return plan                              # the same requests, one token each, again
+        after = Plan(ahead=True)
         after.entries = [PlannedEntry(p.request, [0], samples=True, is_decode=True) for p in plan.entries]
         return after
 

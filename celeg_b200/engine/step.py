@@ -129,63 +129,67 @@ class StepFunction:
             return self._decode_logits[:0]
         if len(entries) > self.max_spans:
             raise StepInputError(f"{len(entries)} requests in one step, the limit is {self.max_spans}")
-        seen_ids = set()
-        total = 0
-        wanted = 0
-        caches = []
-        find = self.manager.find
-        for entry in entries:
-            request_id = entry.request_id
-            if request_id in seen_ids:
-                raise StepInputError(f"request {request_id!r} appears twice in one step")
-            seen_ids.add(request_id)
-            tokens = entry.tokens
-            count = len(tokens)
-            if count == 1:
-                low = high = int(tokens[0])
-            elif count == 0:
-                raise StepInputError(f"request {request_id!r} brings no tokens")
-            else:
-                if not isinstance(tokens, np.ndarray):
-                    tokens = entry.tokens = np.asarray(tokens, dtype=np.int64)
-                low, high = int(tokens.min()), int(tokens.max())
-            if low < 0 or high >= vocab:
-                bad = low if low < 0 else high
-                raise StepInputError(f"request {request_id!r}: token id {bad} is outside the "
-                                     f"vocabulary of {vocab}")
-            for place in entry.want:
-                if not 0 <= int(place) < count:
-                    raise StepInputError(f"request {request_id!r}: wanted place {place} is outside its "
-                                         f"{count} tokens")
-            cache = find(request_id)
-            if cache is None:
-                if not auto_begin:
-                    raise StepInputError(f"request {request_id!r} was not begun") from None
-                cache = self.manager.open(request_id)
-            if cache.tokens + count > self.max_context:
-                raise StepInputError(f"request {request_id!r} would reach {cache.tokens + count} positions, "
-                                     f"the context limit is {self.max_context}")
-            caches.append(cache)
-            total += count
-            wanted += len(entry.want)
+        checked_entries = self._check_single_tokens(entries, auto_begin) if len(entries) >= 8 else None
+        if checked_entries is not None:
+            caches, wanted = checked_entries
+            total = len(entries)
+            counts = [1] * total
+        else:
+            seen_ids = set()
+            total = 0
+            wanted = 0
+            caches = []
+            counts = []
+            find = self.manager.find
+            for entry in entries:
+                request_id = entry.request_id
+                if request_id in seen_ids:
+                    raise StepInputError(f"request {request_id!r} appears twice in one step")
+                seen_ids.add(request_id)
+                tokens = entry.tokens
+                count = len(tokens)
+                if count == 1:
+                    low = high = int(tokens[0])
+                elif count == 0:
+                    raise StepInputError(f"request {request_id!r} brings no tokens")
+                else:
+                    if not isinstance(tokens, np.ndarray):
+                        tokens = entry.tokens = np.asarray(tokens, dtype=np.int64)
+                    low, high = int(tokens.min()), int(tokens.max())
+                if low < 0 or high >= vocab:
+                    bad = low if low < 0 else high
+                    raise StepInputError(f"request {request_id!r}: token id {bad} is outside the "
+                                         f"vocabulary of {vocab}")
+                for place in entry.want:
+                    if not 0 <= int(place) < count:
+                        raise StepInputError(f"request {request_id!r}: wanted place {place} is outside its "
+                                             f"{count} tokens")
+                cache = find(request_id)
+                if cache is None:
+                    if not auto_begin:
+                        raise StepInputError(f"request {request_id!r} was not begun") from None
+                    cache = self.manager.open(request_id)
+                if cache.tokens + count > self.max_context:
+                    raise StepInputError(f"request {request_id!r} would reach {cache.tokens + count} positions, "
+                                         f"the context limit is {self.max_context}")
+                caches.append(cache)
+                counts.append(count)
+                total += count
+                wanted += len(entry.want)
         if total > self.max_tokens:
             raise StepInputError(f"{total} tokens in one step, the limit is {self.max_tokens}")
 
         # pages for the whole batch, all or nothing
-        need = [0] * self.groups
-        for entry, cache in zip(entries, caches):
-            for g, pages in enumerate(self.manager.pages_needed(cache, cache.tokens + len(entry.tokens))):
-                need[g] += pages
+        need = self.manager.pages_needed_each(caches, counts)
         for g, group in enumerate(self.manager.groups):
             if need[g] > group.pool.free_pages:
                 raise OutOfPages(f"the step needs {need[g]} more page(s) of group {group.key}, "
                                  f"{group.pool.free_pages} free")
-        for entry, cache in zip(entries, caches):
-            self.manager.reserve(cache, cache.tokens + len(entry.tokens))
+        self.manager.reserve_each(caches, counts)
 
         spans = len(entries)
         all_decode = total == spans
-        max_ctx = max(cache.tokens + len(entry.tokens) for entry, cache in zip(entries, caches))
+        max_ctx = max(cache.tokens + count for cache, count in zip(caches, counts))
         mixed = None if all_decode else self._padded_prompt_shape(entries, wanted, max_ctx)
         if all_decode or mixed is not None:
             prompt_key = mixed.key if mixed is not None else None
@@ -236,14 +240,44 @@ class StepFunction:
             self._run_graphed(graph_key, step, logit_rows, n_logits, logits)
         else:
             self.model.forward(step, logit_rows, n_logits, logits)
-        for entry, cache in zip(entries, caches):
-            self.manager.advance(cache, cache.tokens + len(entry.tokens))
+        self.manager.advance_each(caches, counts)
         self.steps_run += 1
         done = time.perf_counter()
         self.host_seconds["check"] += checked - started
         self.host_seconds["stage"] += staged - checked
         self.host_seconds["forward"] += done - staged
         return logits[:wanted]
+
+    def _check_single_tokens(self, entries, auto_begin: bool):
+        """The checks of :meth:`run` for a step in which every request brings one token, over whole lists
+        instead of request by request (a step of hundreds of decoding requests spends more time in a loop of
+        checks than in anything else on the host). Returns (caches, wanted), or None when the step is of
+        another kind or something is wrong with it: the general loop then finds out what and says so."""
+        try:
+            if any(len(entry.tokens) != 1 for entry in entries):
+                return None
+            ids = [entry.request_id for entry in entries]
+            if len(set(ids)) != len(ids):
+                return None
+            tokens = np.asarray([entry.tokens[0] for entry in entries], dtype=np.int64)
+            if int(tokens.min()) < 0 or int(tokens.max()) >= self.model.vocab_size:
+                return None
+            wanted = 0
+            for entry in entries:
+                want = entry.want
+                if want:
+                    if len(want) != 1 or int(want[0]) != 0:
+                        return None
+                    wanted += 1
+            find = self.manager.find
+            caches = [find(request_id) for request_id in ids]
+            if any(cache is None for cache in caches):
+                return None
+            if max(cache.tokens for cache in caches) + 1 > self.max_context:
+                return None
+            return caches, wanted
+        except (TypeError, ValueError):
+            return None
 
     def _padded_prompt_shape(self, entries, wanted: int, max_ctx: int):
         """A step of the form the scheduler plans under load (single decoded tokens first, then prompt portions)
@@ -480,13 +514,21 @@ class StepFunction:
                 if entry.want:
                     logit_rows_host[out] = index
                     out += 1
+            mirrors = self.manager.table_mirrors
+            slots = span_slot[:real_spans] if mirrors is not None else None
             for g in range(self.groups):
                 grid = tables[g]
-                grid.fill(NO_PAGE)
-                for index, cache in enumerate(caches):
-                    table = cache.table_array(g)
-                    used = min(table.shape[0], stride)
-                    grid[index, :used] = table[:used]
+                if mirrors is not None and mirrors[g].shape[1] >= stride:
+                    # the tables of all slots lie in one array: the rows of this step's requests in one gather
+                    np.take(mirrors[g][:, :stride], slots, axis=0, out=grid[:real_spans])
+                    if real_spans < spans:
+                        grid[real_spans:].fill(NO_PAGE)
+                else:
+                    grid.fill(NO_PAGE)
+                    for index, cache in enumerate(caches):
+                        table = cache.table_array(g)
+                        used = min(table.shape[0], stride)
+                        grid[index, :used] = table[:used]
                 if real_spans < spans:
                     grid[real_spans:, 0] = self.storage.scratch_pages[g]
             lengths = [1] * spans

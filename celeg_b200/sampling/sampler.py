@@ -34,6 +34,7 @@ class Sampler:
         self._out_hosts = [self._out_host, torch.zeros(max_rows, dtype=torch.int32).pin_memory()]
         self._flip = 0
         self._staged = None
+        self._staged_rows = None
         self._all_greedy = False
 
     def reset_slot(self, slot: int, seed: int) -> None:
@@ -75,8 +76,11 @@ class Sampler:
         if count > self.max_rows:
             raise ValueError(f"{count} rows to sample, the sampler was sized for {self.max_rows}")
         m = self.max_rows
-        signature = tuple((slot, params) for slot, params in rows)
-        if signature != self._staged:
+        # (the very list of the launch before: a scheduler that decodes the same requests again hands it over
+        # unchanged, and comparing hundreds of rows field by field would cost more than the launch)
+        signature = self._staged if rows is self._staged_rows else tuple((slot, params) for slot, params in rows)
+        self._staged_rows = rows
+        if signature is not self._staged and signature != self._staged:
             # the rows or their options changed: stage them again (the copies of the last staging have
             # long been consumed: every call ends with a synchronisation)
             hi, hf = self._host_i.numpy(), self._host_f.numpy()
