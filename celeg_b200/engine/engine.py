@@ -47,14 +47,16 @@ class _Runner:
         return self.collect(self.launch(entries, sample_rows))
 
     def launch(self, entries: Sequence[StepEntry], sample_rows: Sequence[Tuple[int, SamplingParams]],
-               tokens_on_device: bool = False):
+               tokens_on_device: bool = False, source_rows: Optional[Sequence[int]] = None):
         """Enqueues a step and its draw without waiting. ``tokens_on_device``: the entries' tokens are
-        placeholders, the real ones are what the launch before drew (same rows, same order)."""
+        placeholders, the real ones are what the launch before drew: row i of this step takes the token of that
+        launch's row ``source_rows[i]`` (None: the same rows in the same order)."""
         step = self.loaded.step
         index = self._next
         self._next = (index + 1) % self.IN_FLIGHT
         self._begin[index].record()
-        logits = step.run(entries, token_source=self.sampler.out if tokens_on_device else None)
+        logits = step.run(entries, token_source=self.sampler.out if tokens_on_device else None,
+                          source_rows=source_rows if tokens_on_device else None)
         started = time.perf_counter()
         self.sampler.mark_step(step.last_step)
         drawn = self.sampler.launch(logits, sample_rows)

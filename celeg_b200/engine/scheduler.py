@@ -165,6 +165,7 @@ class Plan:
     # Such a plan says the same as the one after it, so it is used again, and what a launch makes of a plan
     # (the step function's entries, the sampler's rows) is kept with it.
     ahead: bool = False
+    source_rows: Optional[List[int]] = None     # which row of the step before holds each entry's token (None: the same row)
     step_entries: Optional[list] = None
     sample_rows: Optional[list] = None
 
@@ -285,10 +286,11 @@ class Scheduler:
         plan, handle = self._inflight
         self._inflight = None
         started = clock()
-        ahead = self._may_run_ahead(plan)
+        continuing = self._may_run_ahead(plan)
+        after = self._plan_after(plan, continuing) if continuing else None
         metrics.host_plan_seconds += clock() - started
-        if ahead:
-            self._launch(self._plan_after(plan), tokens_on_device=True)
+        if after is not None:
+            self._launch(after, tokens_on_device=True)
         progressed = self._collect(plan, handle)
         started = clock()
         self._hold_admission = False
@@ -396,7 +398,10 @@ class Scheduler:
         entries, sample_rows = plan.step_entries, plan.sample_rows
         try:
             if self._runs_ahead:
-                handle = self.runner.launch(entries, sample_rows, tokens_on_device)
+                if plan.source_rows is not None:
+                    handle = self.runner.launch(entries, sample_rows, tokens_on_device, source_rows=plan.source_rows)
+                else:
+                    handle = self.runner.launch(entries, sample_rows, tokens_on_device)
             else:
                 handle = self.runner.run(entries, sample_rows)
         except Exception as exc:
@@ -407,37 +412,56 @@ class Scheduler:
         self._inflight = (plan, handle)
         return True
 
-    def _may_run_ahead(self, plan: Plan) -> bool:
-        """Whether the step after ``plan`` can be enqueued before the tokens of ``plan`` are known: the
-        same requests, one token each, whatever those tokens are (an end-of-sequence token aside)."""
-        if not self._runs_ahead or self.queue or plan.skipped_for_pages or len(plan.entries) != len(self.live):
-            return False
+    def _may_run_ahead(self, plan: Plan) -> Optional[List[PlannedEntry]]:
+        """Whether the step after ``plan`` can be enqueued before the tokens of ``plan`` are known, and for
+        whom: the requests of ``plan`` that go on decoding whatever those tokens are (an end-of-sequence
+        token aside), one token each. A request that reaches its ``max_new_tokens`` with this step's token ends
+        for certain and is left out; one that has ended while ``plan`` was in flight likewise. None: not now."""
+        if not self._runs_ahead or self.queue or plan.skipped_for_pages:
+            return None
         free = None
         max_context = self.max_context
+        continuing = []
+        alive = 0
         for planned in plan.entries:
             request = planned.request
             cache = request.cache
-            if not (planned.is_decode and planned.samples) or request.cancel_requested or cache is None:
-                return False
+            if not (planned.is_decode and planned.samples) or request.cancel_requested:
+                return None
+            if cache is None:
+                if request.status.terminal:
+                    continue                              # ended while this step was in flight
+                return None
+            alive += 1
             if len(request.generated) + 2 > request.options.max_new_tokens:
-                return False                          # this step's token may be its last
+                continue                                  # this step's token is its last
             if cache.tokens + 1 > max_context:
-                return False
+                return None
             if cache.tokens + 1 > cache.capacity:     # (else: room in the pages it holds)
                 if free is None:
                     free = [group.pool.free_pages for group in self.manager.groups]
                 needed = self.manager.pages_needed(cache, cache.tokens + 1)
                 if any(n > f for n, f in zip(needed, free)):
-                    return False
+                    return None
                 free = [f - n for f, n in zip(free, needed)]
-        return True
+            continuing.append(planned)
+        if alive != len(self.live) or not continuing:
+            return None                                   # (a live request that this step does not hold)
+        return continuing
 
     @staticmethod
-    def _plan_after(plan: Plan) -> Plan:
-        if plan.ahead:
-            return plan                              # the same requests, one token each, again
+    def _plan_after(plan: Plan, continuing: List[PlannedEntry]) -> Plan:
+        if len(continuing) == len(plan.entries):
+            if plan.ahead and plan.source_rows is None:
+                return plan                              # the same requests, one token each, again
+            after = Plan(ahead=True)
+            after.entries = [PlannedEntry(p.request, [0], samples=True, is_decode=True) for p in plan.entries]
+            return after
+        # fewer requests than the step before: row i of this step takes the token of row source_rows[i] of that one
         after = Plan(ahead=True)
-        after.entries = [PlannedEntry(p.request, [0], samples=True, is_decode=True) for p in plan.entries]
+        row_of = {id(p): row for row, p in enumerate(plan.entries)}
+        after.entries = [PlannedEntry(p.request, [0], samples=True, is_decode=True) for p in continuing]
+        after.source_rows = [row_of[id(p)] for p in continuing]
         return after
 
     def _collect(self, plan: Plan, handle) -> bool:

@@ -51,6 +51,7 @@ def _align4(n: int) -> int:
 
 PROMPT_TOKEN_STEP = 128       # a padded prompt step's portions are filled up to a multiple of this many tokens
 PADDING_TOKENS = PROMPT_TOKEN_STEP + 32   # most rows a step may be padded by (portions + spare single tokens)
+PADDING_SPANS = 40             # most spans it may be padded by (spare single tokens and the spare portion)
 
 
 @dataclass
@@ -81,8 +82,12 @@ class StepFunction:
         self.groups = len(manager.groups)
         # (the runtime's buffers hold more rows than a step may bring: room for the rows a step is padded by)
         self.buffer_tokens = max(max_tokens, rt.max_tokens)
-        capacity = (3 * _align4(self.buffer_tokens) + _align4(max_spans + 1) + _align4(max_spans)
-                    + _align4(self.buffer_tokens) + self.groups * _align4(max_spans * self.max_pages))
+        # (and more spans than a step may bring: a step padded to a launch shape has spare single tokens, up to
+        # the next row count of _graph_rows, and a spare portion)
+        self.span_capacity = max_spans + PADDING_SPANS
+        capacity = (3 * _align4(self.buffer_tokens) + _align4(self.span_capacity + 1) + _align4(self.span_capacity)
+                    + _align4(self.buffer_tokens) + self.groups * _align4(self.span_capacity * self.max_pages)
+                    + _align4(self.buffer_tokens))       # (the last: source rows of a step's tokens, see run)
         # a ring of pinned staging buffers: a buffer is refilled only after the copy that read it
         # last has finished on the device
         self._ring = [torch.empty(capacity, dtype=torch.int32).pin_memory() for _ in range(4)]
@@ -93,7 +98,8 @@ class StepFunction:
         self._host_np = self._ring_np[0]
         self._dev = torch.zeros(capacity, dtype=torch.int32, device=rt.device)
         self.error_flag = rt.error_flag
-        self._decode_logits = torch.empty((max_spans, model.vocab_size), dtype=torch.float32, device=rt.device)
+        self._decode_logits = torch.empty((self.span_capacity, model.vocab_size), dtype=torch.float32,
+                                          device=rt.device)
         self._wide_logits: Optional[torch.Tensor] = None
         self.use_graphs = use_graphs
         self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
@@ -120,9 +126,11 @@ class StepFunction:
 
     # ---------------------------------------------------------------------- step
     def run(self, entries: Sequence[StepEntry], auto_begin: bool = False,
-            token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
+            token_source: Optional[torch.Tensor] = None, source_rows: Optional[Sequence[int]] = None) -> torch.Tensor:
         """Returns float32 logits [wanted, vocab] in the order of the entries and of ``want``.
-        The tensor is a view of a buffer that the next call overwrites."""
+        The tensor is a view of a buffer that the next call overwrites. ``token_source`` (int32, on the device):
+        the entries' tokens are placeholders, token i of the step is ``token_source[source_rows[i]]``
+        (``token_source[i]`` without ``source_rows``)."""
         started = time.perf_counter()
         vocab = self.model.vocab_size
         if not entries:
@@ -215,13 +223,25 @@ class StepFunction:
             n_logits = mixed.logit_rows
         else:
             step, logit_rows, n_words = self._stage(entries, caches, total, spans, wanted, stride, max_ctx, padded)
-        self._dev[:n_words].copy_(self._host[:n_words], non_blocking=True)
+        sent = n_words
+        if token_source is not None and source_rows is not None:
+            if n_words + len(source_rows) > self._host_np.shape[0]:
+                raise StepInputError("too many source rows for the staging buffer")
+            self._host_np[n_words:n_words + len(source_rows)] = source_rows
+            sent = n_words + len(source_rows)
+        self._dev[:sent].copy_(self._host[:sent], non_blocking=True)
         if token_source is not None:
             # the tokens of this step are on the device already (what the step before drew): token i of
             # the step is token_source[i]; the entries carry placeholders
             if token_source.dtype != torch.int32 or token_source.numel() < total:
                 raise StepInputError("a token source must hold one int32 token for every token of the step")
-            step.token_ids[:total].copy_(token_source[:total], non_blocking=True)
+            if source_rows is None:
+                step.token_ids[:total].copy_(token_source[:total], non_blocking=True)
+            else:
+                if len(source_rows) != total or min(source_rows) < 0 or max(source_rows) >= token_source.numel():
+                    raise StepInputError("source rows must name one row of the token source for every token")
+                # (the rows travel behind the step's metadata in the same pinned buffer and the same copy)
+                torch.index_select(token_source, 0, self._dev[n_words:n_words + total], out=step.token_ids[:total])
         event = torch.cuda.Event()
         event.record()
         self._ring_events[slot] = event
@@ -295,13 +315,20 @@ class StepFunction:
         portions = lengths[singles:]
         if not portions or any(n == 1 for n in portions):
             return None                                   # all single tokens, or a single token after a portion
-        single_rows = self._graph_rows(singles) if singles else 0
+        # (a coarser grid than a decoding step's: beside prompt portions a few spare single tokens cost nothing,
+        # and every row count less is a graph less to capture)
+        single_rows = 0
+        if singles:
+            single_rows = next((n for n in (16, 32, 64) if n >= singles), (singles + 31) // 32 * 32)
+            if single_rows > self.max_spans:
+                single_rows = self._graph_rows(singles)
         portion_tokens = sum(portions)
         padded_tokens = -(-portion_tokens // PROMPT_TOKEN_STEP) * PROMPT_TOKEN_STEP
         spare = padded_tokens - portion_tokens
         spans = single_rows + len(portions) + (1 if spare else 0)
         logit_rows = max(1, wanted, single_rows + len(portions))       # (a scheduler's step wants one row a span at most)
-        if (single_rows + padded_tokens > self.buffer_tokens or spans > self.max_spans or logit_rows > self.max_spans
+        if (single_rows + padded_tokens > self.buffer_tokens or spans > self.span_capacity
+                or logit_rows > self.span_capacity
                 or single_rows - singles > PADDING_TOKENS - PROMPT_TOKEN_STEP
                 or spare > self.storage.scratch_page_count * self.page_tokens):
             return None

@@ -1383,6 +1383,59 @@ def test_requests_that_end_on_a_token_while_the_next_step_is_in_flight(models, d
     assert engine.loaded.manager.free_slots == engine.options.max_active_requests
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_run_ahead_with_requests_that_end_at_different_steps(models, dtype, monkeypatch):
+    """Twelve requests with 3 to 25 new tokens each, some drawn with a seed, one ending on a token of its own:
+    in nearly every step some request produces its last token. The step after is still enqueued early for the
+    others and takes their tokens from the device, from the rows they had in the step before. Outputs against
+    the plain model; steps with fewer rows than their predecessor must have been launched ahead."""
+    from celeg_b200 import Engine, EngineOptions
+    from celeg_b200.engine import engine as engine_module
+    folder, config, weights = models["A"]
+    lengths = [5, 9, 3, 14, 7, 11, 4, 8, 6, 10, 12, 2]
+    news = [3, 25, 6, 9, 14, 4, 17, 8, 21, 5, 12, 10]
+    prompts = prompts_of(config["vocab_size"], lengths, seed=61)
+    sampled = {1, 4, 8}                                 # these draw with a seed, the others are greedy
+    free = plain_lfm2.generate(config, weights, prompts[3], news[3], eos_tokens=())
+    stops = {3: (free[5],)}
+    shrunk = []
+    original = engine_module._Runner.launch
+
+    def launch(self, entries, sample_rows, tokens_on_device=False, source_rows=None):
+        if source_rows is not None:
+            shrunk.append(len(source_rows))
+        return original(self, entries, sample_rows, tokens_on_device, source_rows)
+    monkeypatch.setattr(engine_module._Runner, "launch", launch)
+    engine = Engine(folder, dtype=dtype, options=EngineOptions(max_active_requests=16, max_batched_tokens=64))
+    ids = []
+    for i, (prompt, new) in enumerate(zip(prompts, news)):
+        if i in sampled:
+            ids.append(engine.submit(prompt, max_new_tokens=new, temperature=0.8, top_k=20, top_p=0.9,
+                                     repetition_penalty=1.1, seed=100 + i, eos_tokens=()))
+        else:
+            ids.append(engine.submit(prompt, max_new_tokens=new, temperature=0.0, repetition_penalty=1.0,
+                                     eos_tokens=stops.get(i, ())))
+    while engine.scheduler.has_work():
+        engine.step()
+    agree = 0
+    for i, (request_id, prompt, new) in enumerate(zip(ids, prompts, news)):
+        if i in sampled:
+            want = plain_lfm2.generate(config, weights, prompt, new, temperature=0.8, top_k=20, top_p=0.9,
+                                       repetition_penalty=1.1, seed=100 + i, eos_tokens=())
+        else:
+            want = plain_lfm2.generate(config, weights, prompt, new, eos_tokens=stops.get(i, ()))
+        got = engine.poll(request_id).tokens
+        assert engine.status(request_id).value == "finished"
+        if dtype == "float32":
+            assert got == want, (i, got, want)
+        agree += got == want
+    assert agree >= 9
+    assert len(shrunk) >= 4, shrunk
+    engine.loaded.step.raise_on_device_error()
+    engine.loaded.manager.check_invariants()
+    assert engine.loaded.manager.free_slots == engine.options.max_active_requests
+
+
 @pytest.mark.parametrize("name,dtype,tol", [("A", "float32", 4e-4), ("B", "bfloat16", 8e-2), ("D", "bfloat16", 8e-2)])
 def test_steps_of_changing_mix_are_padded_to_launch_shapes_and_replayed(tmp_path, name, dtype, tol):
     """Steps of the form the scheduler plans under load: decoded tokens of a changing number of requests first,
@@ -1398,7 +1451,7 @@ def test_steps_of_changing_mix_are_padded_to_launch_shapes_and_replayed(tmp_path
     lengths = rng.integers(30, 90, size=count).tolist()
     seqs = prompts_of(config["vocab_size"], lengths, seed=48)
     want = [plain_lfm2.forward(config, weights, s) for s in seqs]
-    loaded = load_model(folder, dtype=dtype, max_requests=12, cache_tokens=12 * 96, max_batched_tokens=96,
+    loaded = load_model(folder, dtype=dtype, max_requests=16, cache_tokens=12 * 96, max_batched_tokens=96,
                         use_graphs=True)
     step = loaded.step
     at = [0] * count

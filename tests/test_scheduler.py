@@ -257,18 +257,20 @@ class AheadRunner(FakeRunner):
         self.last_drawn = []         # what the latest collected-or-not launch drew, per row (filled at collect)
         self.log = []
 
-    def launch(self, entries, sample_rows, tokens_on_device=False):
+    def launch(self, entries, sample_rows, tokens_on_device=False, source_rows=None):
         if self.fail_next:
             self.fail_next = False
             raise RuntimeError("injected step failure")
         assert len(self.pending) <= 1, "more than two steps in flight"
+        assert source_rows is None or (tokens_on_device and len(source_rows) == len(entries))
         rows = []
         for entry in entries:
             cache = self.manager.get(entry.request_id)
             self.manager.reserve(cache, cache.tokens + len(entry.tokens))
             self.manager.advance(cache, cache.tokens + len(entry.tokens))
             rows.append((entry.request_id, cache.slot, list(entry.tokens), list(entry.want)))
-        handle = {"rows": rows, "from_device": tokens_on_device, "after": self.pending[-1] if self.pending else None}
+        handle = {"rows": rows, "from_device": tokens_on_device, "after": self.pending[-1] if self.pending else None,
+                  "source": list(source_rows) if source_rows is not None else None}
         self.pending.append(handle)
         self.log.append(("launch", tokens_on_device, [r[0] for r in rows]))
         return handle
@@ -279,11 +281,14 @@ class AheadRunner(FakeRunner):
         self.log.append(("collect", [r[0] for r in handle["rows"]]))
         if handle["from_device"]:
             before = handle["after"]["drawn"]
-            assert len(before) == len(handle["rows"])
+            source = handle["source"]
+            if source is None:
+                assert len(before) == len(handle["rows"])
+                source = list(range(len(before)))
         out = []
         for index, (request_id, slot, tokens, want) in enumerate(handle["rows"]):
             if handle["from_device"]:
-                tokens = [before[index]]
+                tokens = [before[source[index]]]
             self.history[slot].extend(tokens)
             if want:
                 self.generator[slot] += 1
@@ -328,6 +333,24 @@ def test_run_ahead_drops_the_token_after_an_end_of_sequence():
     assert scheduler.poll(request_id).tokens == reference[:reference.index(stop) + 1]
     assert scheduler.poll(other).tokens == expected_output([8, 8], 12, eos=())
     assert scheduler.status(request_id) is RequestStatus.FINISHED
+    assert not runner.pending and manager.free_slots == 4
+    manager.check_invariants()
+
+
+def test_run_ahead_goes_on_with_the_requests_that_do_not_end():
+    """Requests that reach their last token at different steps: the step after is still enqueued early, for the
+    requests that go on, and takes their tokens from the rows they had in the step before."""
+    scheduler, runner, manager = make_ahead()
+    prompts = [[3, 4, 5], [9, 1], [2, 2, 2, 2, 2], [6]]
+    news = [5, 9, 7, 12]
+    ids = [scheduler.submit(p, RequestOptions(max_new_tokens=n, eos_tokens=())) for p, n in zip(prompts, news)]
+    run_all(scheduler)
+    for request_id, prompt, n in zip(ids, prompts, news):
+        assert scheduler.poll(request_id).tokens == expected_output(prompt, n, eos=())
+    launches = [entry for entry in runner.log if entry[0] == "launch"]
+    shrinking = [i for i in range(1, len(launches))
+                 if launches[i][1] and len(launches[i][2]) < len(launches[i - 1][2])]
+    assert len(shrinking) >= 2, launches                 # run ahead with fewer rows than the step before
     assert not runner.pending and manager.free_slots == 4
     manager.check_invariants()
 
