@@ -299,7 +299,7 @@ def time_prefill(loaded, tokens: int, repeats: int, seed: int, chunk: int = 0):
     vocab = loaded.model.vocab_size
     generator = torch.Generator().manual_seed(seed)
     best = None
-    for i in range(repeats + 2):
+    for i in range(repeats + 3):
         prompt = torch.randint(0, vocab, (tokens,), generator=generator).tolist()
         size = chunk if chunk > 0 else tokens
         torch.cuda.synchronize()
@@ -312,7 +312,7 @@ def time_prefill(loaded, tokens: int, repeats: int, seed: int, chunk: int = 0):
         stop.record()
         torch.cuda.synchronize()
         step_fn.end(f"prefill{i}")
-        if i >= 2:
+        if i >= 3:                     # (the step's shape is launched from the host twice, then captured, then replayed)
             ms = start.elapsed_time(stop)
             best = ms if best is None else min(best, ms)
     return best

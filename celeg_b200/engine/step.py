@@ -51,6 +51,9 @@ def _align4(n: int) -> int:
 
 PROMPT_TOKEN_STEP = 128       # a padded prompt step's portions are filled up to a multiple of this many tokens
 PADDING_TOKENS = PROMPT_TOKEN_STEP + 32   # most rows a step may be padded by (portions + spare single tokens)
+# A prompt step's shape is captured in a CUDA graph when it comes for this many times (a capture costs about three
+# launches from the host: it pays from the coming after that on, and a shape that comes twice never pays)
+CAPTURE_AT_COMING = 3
 PADDING_SPANS = 40             # most spans it may be padded by (spare single tokens and the spare portion)
 
 
@@ -307,7 +310,7 @@ class StepFunction:
         row count of :meth:`_graph_rows`, and one spare portion that fills the portions' tokens up to a multiple
         of ``PROMPT_TOKEN_STEP``. Spare rows carry token 0 at positions 0.. of the storage's spare pages and
         slot; the kernels take their bounds (attention tiles, longest span) from the grid, not from the step.
-        Returns the shape (with its graph key) once it has come twice, else None."""
+        Returns the shape (with its graph key) once it has come ``CAPTURE_AT_COMING`` times, else None."""
         if not self.use_graphs or wanted > self.max_spans:
             return None
         lengths = [len(e.tokens) for e in entries]
@@ -338,7 +341,7 @@ class StepFunction:
                 self._prompt_seen.clear()
             seen = self._prompt_seen.get(key, 0) + 1
             self._prompt_seen[key] = seen
-            if seen < 2:
+            if seen < CAPTURE_AT_COMING:
                 return None
             kept = [k for k in self._graphs if k and k[0] == "padded prompt"]
             if len(kept) >= self.max_padded_graphs:          # the oldest goes (dicts keep insertion order)
@@ -444,7 +447,7 @@ class StepFunction:
         GPU needs for portions of a few hundred tokens. Every launch shape of such a step follows from the
         lengths of its portions, the number of wanted rows and whether those are all rows in order, so a step
         whose shape has come before (a long prompt cut into equal portions) is captured in a CUDA graph at
-        its second coming and replayed from then on. None: run it kernel by kernel."""
+        its third coming (``CAPTURE_AT_COMING``) and replayed from then on. None: run it kernel by kernel."""
         if not self.use_graphs or wanted > self.max_spans:
             return None
         all_rows = wanted == total and all(tuple(e.want) == tuple(range(len(e.tokens))) for e in entries)
@@ -457,7 +460,7 @@ class StepFunction:
             self._prompt_seen.clear()
         seen = self._prompt_seen.get(key, 0) + 1
         self._prompt_seen[key] = seen
-        if seen < 2:
+        if seen < CAPTURE_AT_COMING:
             return None
         prompt_graphs = [k for k in self._graphs if k and k[0] == "prompt"]
         if len(prompt_graphs) >= self.max_prompt_graphs:     # the oldest goes (dicts keep insertion order)

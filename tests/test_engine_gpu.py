@@ -1278,7 +1278,7 @@ def test_scale_factors_of_a_model_description(tmp_path, dtype, tol):
 
 @pytest.mark.parametrize("name,dtype,tol", [("A", "float32", 3e-4), ("D", "bfloat16", 8e-2)])
 def test_equal_prompt_portions_are_replayed_from_a_graph(tmp_path, name, dtype, tol):
-    """A prompt cut into equal portions: the second portion of a shape is captured in a CUDA graph, the later
+    """A prompt cut into equal portions: the third portion of a shape is captured in a CUDA graph, the later
     ones are replayed from it (other contexts, other pages, the same launch shapes); a portion of another
     length and a step that mixes a portion with a decoded token run kernel by kernel or get graphs of their
     own. All of it against the plain implementation; the same again without graphs gives the same bits on the
@@ -1312,7 +1312,7 @@ def test_equal_prompt_portions_are_replayed_from_a_graph(tmp_path, name, dtype, 
         return np.stack(rows), graphed_after_equal_portions
 
     got, graphed = run(True)
-    assert graphed == 5                      # the first portion ran kernel by kernel, the second was captured
+    assert graphed == 4                      # two portions ran kernel by kernel, the third was captured
     ref, not_graphed = run(False)
     assert not_graphed == 0
     if dtype == "float32":
@@ -1440,7 +1440,7 @@ def test_run_ahead_with_requests_that_end_at_different_steps(models, dtype, monk
 def test_steps_of_changing_mix_are_padded_to_launch_shapes_and_replayed(tmp_path, name, dtype, tol):
     """Steps of the form the scheduler plans under load: decoded tokens of a changing number of requests first,
     then one or two prompt portions of changing lengths. No two of them have the same shape, yet from its
-    second coming on a launch shape from the coarse grid (spare single tokens, one spare portion) is replayed
+    third coming on a launch shape from the coarse grid (spare single tokens, one spare portion) is replayed
     from a CUDA graph. Every wanted row of every step against the plain model; graphs must have been used."""
     from celeg_b200.engine.loading import load_model
     from celeg_b200.engine.step import StepEntry
@@ -1494,4 +1494,4 @@ def test_steps_of_changing_mix_are_padded_to_launch_shapes_and_replayed(tmp_path
     step.raise_on_device_error()
     loaded.manager.check_invariants()
     padded = [k for k in step._graphs if k and k[0] == "padded prompt"]
-    assert len(padded) >= 3 and step.kernel_steps_graphed > steps // 3, (len(padded), step.kernel_steps_graphed, steps)
+    assert len(padded) >= 2 and step.kernel_steps_graphed > steps // 3, (len(padded), step.kernel_steps_graphed, steps)
