@@ -105,8 +105,12 @@ static int attention_decode_checked(const void* q, int q_row_stride, void* out, 
     p.k_cache_w = (__nv_bfloat16*)const_cast<void*>(k_cache);
     p.v_cache_w = (__nv_bfloat16*)const_cast<void*>(v_cache);
     dim3 grid(max_splits, kv_heads, tokens);
-    if (head_dim <= 64) return launch_decode<64, 64>(p, grid, stream);
-    if (head_dim <= 128) return launch_decode<128, 64>(p, grid, stream);
+    // Short contexts (an item has at most two tiles of keys per warp): a block with one stage of 32 keys per warp
+    // needs half the shared memory, so twice as many items run at a time; their start and their merge, not
+    // their keys, are what such a launch consists of.
+    const bool few_keys = chunk <= 256;
+    if (head_dim <= 64) return few_keys ? launch_decode<64, 32>(p, grid, stream) : launch_decode<64, 64>(p, grid, stream);
+    if (head_dim <= 128) return few_keys ? launch_decode<128, 32>(p, grid, stream) : launch_decode<128, 64>(p, grid, stream);
     return launch_decode<256, 32>(p, grid, stream);
 }
 

@@ -147,7 +147,7 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     constexpr int kChunks = D_PAD / 8;
     constexpr int kKTiles = D_PAD / 16;
     constexpr int kOTiles = D_PAD / 8;
-    constexpr int kStages = D_PAD <= 128 ? 2 : 1;          // stages per warp
+    constexpr int kStages = (D_PAD <= 128 && BN >= 64) ? 2 : 1;     // stages per warp
     constexpr int TN = BN / kStages;                       // keys per stage (the warp's shared memory is BN keys of K and of V)
     constexpr int kKeysPerLane = TN / 32;
     static_assert(TN % 32 == 0, "a stage holds a multiple of 32 keys");
