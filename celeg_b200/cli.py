@@ -212,17 +212,7 @@ def run(argv=None) -> int:
 
 
 def _model_tensors(engine):
-    seen = set()
-    model = engine.loaded.model
-    stack = [model.embedding, model.head]
-    for layer in model.layers:
-        for part in layer.parts.values():
-            if part is not None:
-                stack.extend(v for v in vars(part).values() if hasattr(v, "data_ptr") and hasattr(v, "numel"))
-    for tensor in stack:
-        if tensor.data_ptr() not in seen:
-            seen.add(tensor.data_ptr())
-            yield tensor
+    return engine.loaded.model.weight_tensors()
 
 
 def _benchmark(engine, prompt, args, generation) -> int:

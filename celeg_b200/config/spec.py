@@ -99,14 +99,37 @@ class ModelSpec:
     embedding_multiplier: float = 1.0
     logits_multiplier: float = 1.0
     optional_tensors: Tuple[TensorRef, ...] = ()
+    # The two ends of the model as parts of the categories "input" (token ids -> rows of the residual stream) and
+    # "output" (rows -> logits). None: the built-in ones, made of the fields above (embedding table and its
+    # multiplier; final norm, tied or untied head and the logits' multiplier). A description that names its own
+    # lists every tensor they need in them; ``embedding`` still names the table (its rows are the vocabulary).
+    input: Optional[PartSpec] = None
+    output: Optional[PartSpec] = None
+
+    def input_part(self) -> PartSpec:
+        if self.input is not None:
+            return self.input
+        return PartSpec("embedding", params={"multiplier": self.embedding_multiplier},
+                        tensors={"table": self.embedding}, category="input")
+
+    def output_part(self) -> PartSpec:
+        if self.output is not None:
+            return self.output
+        return PartSpec("norm_head", params={"multiplier": self.logits_multiplier},
+                        tensors={"head": self.lm_head if self.lm_head is not None else self.embedding},
+                        parts={"norm": self.final_norm}, category="output")
 
     def all_tensors(self) -> List[TensorRef]:
-        out = [self.embedding]
+        out: List[TensorRef] = []
+        seen = set()
+        refs = list(self.input_part().all_tensors())
         for layer in self.layers:
-            out.extend(layer.all_tensors())
-        out.extend(self.final_norm.all_tensors())
-        if self.lm_head is not None:
-            out.append(self.lm_head)
+            refs.extend(layer.all_tensors())
+        refs.extend(self.output_part().all_tensors())
+        for ref in refs:                       # (a tied head names the embedding table a second time)
+            if ref.name not in seen:
+                seen.add(ref.name)
+                out.append(ref)
         return out
 
     def validate(self) -> None:

@@ -67,12 +67,13 @@ class Model:
         self.hidden_size = spec.hidden_size
         self.layers = [Layer(layer, tensors, rt) for layer in spec.layers]
         self.order = list(spec.order)
-        self.embedding = rt.matrix(tensors[spec.embedding.name])
-        self.head = self.embedding if spec.lm_head is None else rt.matrix(tensors[spec.lm_head.name])
-        self.final_norm = build_part("norm", spec.final_norm, tensors, rt)
+        # the two ends (parts of the categories "input" and "output"; the built-in ones unless the description
+        # names others)
+        self.input = build_part("input", spec.input_part(), tensors, rt)
+        self.output = build_part("output", spec.output_part(), tensors, rt)
+        rt.release_sources()
         self.stream = ResidualStream(rt, spec.hidden_size)
         self.residual = self.stream.residual
-        self.final_normed = rt.scratch("model.final_normed", spec.hidden_size)
         # per position of the run order: {part name: binding} for the parts of its layer that hold a cache
         self.bindings: List[Dict[str, object]] = [{} for _ in self.order]
         self._rebind = len({entry.layer for entry in self.order}) != len(self.order)
@@ -146,9 +147,25 @@ class Model:
         """Bytes of every weight a step reads once: what the parts put on the device, and the head (a tied
         head is the embedding table, counted once; of an untied table a step gathers a few rows only)."""
         total = self.rt.weight_bytes
-        if self.head is not self.embedding:
-            total -= self.embedding.numel() * self.embedding.element_size()
+        table, head = getattr(self.input, "table", None), getattr(self.output, "head", None)
+        if table is not None and head is not table:
+            total -= table.numel() * table.element_size()
         return total
+
+    def weight_tensors(self) -> List[torch.Tensor]:
+        """Every tensor that a part of the model holds (the ends' and the layers'), each once."""
+        found, seen = [], set()
+        holders = [self.input, self.output, getattr(self.output, "norm", None)]
+        for layer in self.layers:
+            holders.extend(layer.parts.values())
+        for holder in holders:
+            if holder is None:
+                continue
+            for value in vars(holder).values():
+                if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
+                    seen.add(value.data_ptr())
+                    found.append(value)
+        return found
 
     # ----------------------------------------------------------------- forward
     def forward(self, step: StepContext, logit_rows: torch.Tensor, n_logits: int, logits: torch.Tensor) -> None:
@@ -159,16 +176,12 @@ class Model:
         stream.begin()
         blocks = [self.layers[entry.layer].block for entry in self.order]
         firsts = [block.first_norm(step) if hasattr(block, "first_norm") else None for block in blocks]
-        head_norm = (self.final_norm if n_logits > 0 and step.logits_of_all_rows
-                     and rt.takes_split_norm(n_logits, self.head) else None)
-        first = stream.split(firsts[0], 1) if firsts and firsts[0] is not None and rt.small_batch(step.tokens) else None
-        if first is not None:
-            kernels.embedding(self.embedding, step.token_ids[:step.tokens], self.residual,
-                              self.spec.embedding_multiplier, prepare=first[1], next_weight=first[0])
-            stream.prepared = (firsts[0], first[1])
-        else:
-            kernels.embedding(self.embedding, step.token_ids[:step.tokens], self.residual,
-                              self.spec.embedding_multiplier)
+        head_norm = self.output.next_norm(step, n_logits) if hasattr(self.output, "next_norm") else None
+        first = None
+        if firsts and firsts[0] is not None and rt.small_batch(step.tokens):
+            halves = stream.split(firsts[0], 1)
+            first = (firsts[0], halves) if halves is not None else None
+        self.input.run(stream, step, first)
         for position, entry in enumerate(self.order):
             layer = self.layers[entry.layer]
             if self._rebind:
@@ -179,10 +192,4 @@ class Model:
         if n_logits == 0:
             stream.prepared = None
             return
-        if step.logits_of_all_rows:
-            normed = stream.normed(self.final_norm, self.final_normed, n_logits)
-        else:
-            normed = stream.normed(self.final_norm, self.final_normed, n_logits, gather=logit_rows)
-        rt.linear(normed, self.head, logits, n_logits)
-        if self.spec.logits_multiplier != 1.0:
-            logits[:n_logits].mul_(self.spec.logits_multiplier)
+        self.output.run(stream, step, logit_rows, n_logits, logits)

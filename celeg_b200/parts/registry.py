@@ -1,6 +1,7 @@
 """Registries of part kinds. A model description names parts by ``kind``; the class behind a
 kind is looked up here when the model is built, so a new mixer, feed-forward, norm, position
-encoding or block arrangement is added by registering a class, with no change to the engine.
+encoding, block arrangement or end of the model (what makes rows of token ids, what makes logits of rows)
+is added by registering a class, with no change to the engine.
 
 celeg dispatches over closed variants (``std::visit`` in src/backend/cuda/packed/layer_executor.cu:131-191);
 the open registry is this engine's own choice.
@@ -9,7 +10,7 @@ from __future__ import annotations
 
 from typing import Callable, Dict
 
-CATEGORIES = ("norm", "mixer", "feed_forward", "position", "arrangement")
+CATEGORIES = ("norm", "mixer", "feed_forward", "position", "arrangement", "input", "output")
 _REGISTRY: Dict[str, Dict[str, Callable]] = {category: {} for category in CATEGORIES}
 
 

@@ -130,6 +130,7 @@ class Runtime:
         self._weight_after: Dict[int, Tuple[int, int]] = {}
         self._streamed_last: Optional[int] = None
         self._flat: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
+        self._placed: Dict[tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._scratch: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         self.weight_bytes = 0                   # what matrix() and vector() have put on the device
         kernels.library()                       # fail now, not at the first step, if it is missing
@@ -152,10 +153,20 @@ class Runtime:
         return self._flat[key]
 
     def matrix(self, weight: torch.Tensor) -> torch.Tensor:
-        """A projection weight on the device in the path's matrix precision."""
+        """A projection weight on the device in the path's matrix precision. A tensor that two parts name (a
+        head tied to the embedding table) is placed once: both get the same device tensor."""
+        key = (weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()), weight.dtype)
+        held = self._placed.get(key)
+        if held is not None and held[0] is weight:
+            return held[1]
         placed = weight.to(device=self.device, dtype=self.act_dtype).contiguous()
         self.weight_bytes += placed.numel() * placed.element_size()
+        self._placed[key] = (weight, placed)
         return placed
+
+    def release_sources(self) -> None:
+        """Forget the host tensors that :meth:`matrix` has placed (call when the model is built)."""
+        self._placed = {}
 
     def vector(self, weight: torch.Tensor) -> torch.Tensor:
         """A small weight (norm scale, conv kernel) on the device in float32 (exact widening)."""

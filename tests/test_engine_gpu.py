@@ -1276,6 +1276,105 @@ def test_scale_factors_of_a_model_description(tmp_path, dtype, tol):
     step.raise_on_device_error()
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 4e-4), ("bfloat16", 8e-2)])
+def test_toy_ends_of_a_model_registered_from_outside(tmp_path, dtype, tol):
+    """The two ends of a model are parts too. A toy architecture, defined here, names ends of its own: an
+    input that normalises the embedded rows with a weight of its own before the first block, and an output
+    that caps the logits (cap * tanh(logits / cap)) and has an untied head. Nothing in the package changes;
+    prompt portions and decoded tokens (graphs included) against the plain computation."""
+    from celeg_b200 import kernels
+    from celeg_b200.config import Architecture, Lfm2Config, build_lfm2_spec, register_architecture
+    from celeg_b200.config.lfm2_arch import lfm2_random_init
+    from celeg_b200.config.spec import PartSpec, TensorRef
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    from celeg_b200.parts import register_part
+    from celeg_b200.weights import write_random_model
+
+    cap = 1.5
+
+    class NormedEmbedding:
+        def __init__(self, params, weights, parts, rt):
+            self.rt = rt
+            self.table = rt.matrix(weights["table"])
+            self.vocab_size = int(self.table.shape[0])
+            self.norm = parts["norm"]
+            self.raw = rt.scratch("toy.embedded", int(self.table.shape[1]), torch.float32)
+            self.normed = rt.scratch("toy.embedded_normed", int(self.table.shape[1]))
+
+        def run(self, stream, step, first=None):
+            rows = step.tokens
+            kernels.embedding(self.table, step.token_ids[:rows], self.raw)
+            # norm(raw) in the path's precision, then widened into the float32 stream
+            self.norm.add_norm(self.raw, None, self.normed, rows)
+            stream.residual[:rows].copy_(self.normed[:rows])
+
+    class CappedHead:
+        def __init__(self, params, weights, parts, rt):
+            self.rt = rt
+            self.norm = parts["norm"]
+            self.head = rt.matrix(weights["head"])
+            self.cap = float(params["cap"])
+            self.normed = rt.scratch("toy.final_normed", int(self.head.shape[1]))
+
+        def run(self, stream, step, logit_rows, n_logits, logits):
+            gather = None if step.logits_of_all_rows else logit_rows
+            normed = stream.normed(self.norm, self.normed, n_logits, gather=gather)
+            self.rt.linear(normed, self.head, logits, n_logits)
+            view = logits[:n_logits]
+            view.div_(self.cap).tanh_().mul_(self.cap)
+
+    register_part("input", "toy_normed_embedding", NormedEmbedding, replace=True)
+    register_part("output", "toy_capped_head", CappedHead, replace=True)
+
+    def toy_spec(config):
+        spec = build_lfm2_spec(config)
+        hidden = config.hidden_size
+        norm = dataclasses.replace(spec.final_norm, tensors={"weight": TensorRef("model.input_norm.weight", (hidden,))})
+        return dataclasses.replace(
+            spec, architecture="lfm2_toy_ends",
+            input=PartSpec("toy_normed_embedding", tensors={"table": spec.embedding}, parts={"norm": norm},
+                           category="input"),
+            output=PartSpec("toy_capped_head", params={"cap": cap},
+                            tensors={"head": TensorRef("lm_head.weight", (config.vocab_size, hidden))},
+                            parts={"norm": spec.final_norm}, category="output"))
+
+    register_architecture(Architecture(name="lfm2_toy_ends", parse_config=Lfm2Config.from_dict,
+                                       resolve_config=lambda c, shapes: c.resolved_with(shapes),
+                                       build_spec=toy_spec, random_init=lfm2_random_init), replace=True)
+    raw = copy.deepcopy(TINY_A)
+    raw["model_type"] = "lfm2_toy_ends"
+    folder = write_random_model(str(tmp_path / "toy_ends"), raw, 17, torch.bfloat16)
+    loaded = load_model(folder, dtype=dtype, max_requests=2, cache_tokens=128, max_batched_tokens=64, use_graphs=True)
+    config, w = plain_lfm2.load_model_folder(folder)
+
+    def plain_forward(tokens):
+        x = w["model.embed_tokens.weight"][np.asarray(tokens)]
+        x = plain_lfm2.rmsnorm(x, w["model.input_norm.weight"], config["norm_eps"])
+        if dtype == "bfloat16":                           # the toy input rounds its normalised rows to the path's precision
+            x = torch.from_numpy(x).to(torch.bfloat16).to(torch.float64).numpy()
+        for index, kind in enumerate(config["layer_types"]):
+            x = plain_lfm2.block(x, index, kind, config, w)
+        z = plain_lfm2.rmsnorm(x, w["model.embedding_norm.weight"], config["norm_eps"])
+        return cap * np.tanh((z @ w["lm_head.weight"].T) / cap)
+
+    sequences = prompts_of(config["vocab_size"], [30, 24], seed=52)
+    want = [plain_forward(seq) for seq in sequences]
+    step = loaded.step
+    at = [0, 0]
+    for sizes in ((11, 4), (2, 9)) + ((1, 1),) * 8 + ((9, 3),):
+        entries = [StepEntry(f"r{i}", sequences[i][at[i]:at[i] + n], list(range(n))) for i, n in enumerate(sizes)]
+        logits = step.run(entries, auto_begin=True).float().cpu().numpy()
+        row = 0
+        for i, n in enumerate(sizes):
+            worst = np.abs(logits[row:row + n] - want[i][at[i]:at[i] + n]).max()
+            assert worst < tol, f"request {i}, tokens {at[i]}..{at[i] + n}: {worst:.3e}"
+            row += n
+            at[i] += n
+    step.raise_on_device_error()
+    assert type(loaded.model.input).__name__ == "NormedEmbedding" and type(loaded.model.output).__name__ == "CappedHead"
+
+
 @pytest.mark.parametrize("name,dtype,tol", [("A", "float32", 3e-4), ("D", "bfloat16", 8e-2)])
 def test_equal_prompt_portions_are_replayed_from_a_graph(tmp_path, name, dtype, tol):
     """A prompt cut into equal portions: the third portion of a shape is captured in a CUDA graph, the later
