@@ -59,14 +59,14 @@ class _Runner:
                           source_rows=source_rows if tokens_on_device else None)
         started = time.perf_counter()
         self.sampler.mark_step(step.last_step)
-        drawn = self.sampler.launch(logits, sample_rows)
-        self._flags[index:index + 1].copy_(step.error_flag, non_blocking=True)
+        drawn = self.sampler.launch(logits, sample_rows, also_copy=(self._flags[index:index + 1], step.error_flag))
         self._end[index].record()
         self._sample_seconds += time.perf_counter() - started
         return index, drawn
 
     def collect(self, handle) -> List[int]:
         index, drawn = handle
+        tokens = self.sampler.read(drawn)                  # (waits for the copy of the tokens and of the flag)
         self._end[index].synchronize()
         self._gpu_seconds += self._begin[index].elapsed_time(self._end[index]) * 1e-3
         code = int(self._flags[index])
@@ -74,7 +74,7 @@ class _Runner:
             step = self.loaded.step
             step.error_flag.zero_()
             raise DeviceCheckError(device_error_text(code))
-        return self.sampler.read(drawn)
+        return tokens
 
     def report_times(self, metrics: Metrics) -> None:
         """Adds the host seconds spent since the last call, by phase, and the steps' device time."""

@@ -33,6 +33,10 @@ class Sampler:
         self._out_host = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
         self._out_hosts = [self._out_host, torch.zeros(max_rows, dtype=torch.int32).pin_memory()]
         self._flip = 0
+        # the drawn tokens go to the host on a stream of their own: on the stream of the kernels the copy would
+        # stand between this step's draw and the next step's first kernel
+        self._copy_stream = torch.cuda.Stream(device=device)
+        self._copied: Optional[torch.cuda.Event] = None      # the last copy out of ``out`` has finished
         self._staged = None
         self._staged_rows = None
         self._all_greedy = False
@@ -60,18 +64,25 @@ class Sampler:
     def read(self, handle) -> List[int]:
         """Waits for a launched draw (only for it, not for what was enqueued later) and returns its tokens."""
         event, host, count = handle
+        if event is not None:
+            event.synchronize()
         if count == 0:
             return []
-        event.synchronize()
         return host[:count].tolist()
 
-    def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[int, SamplingParams]]):
+    def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[int, SamplingParams]], also_copy=None):
         """Enqueues the draw and the copy of the tokens to pinned host memory; :meth:`read` returns
         them. ``self.out[:len(rows)]`` holds them on the device until the next launch (a following step
         may take its input tokens from there). At most two launches may be unread at a time, and the
-        rows or their options may change only when none is."""
+        rows or their options may change only when none is. ``also_copy`` = (pinned host tensor, device
+        tensor): copied along with the tokens (a step's error flag), there when :meth:`read` returns."""
         count = len(rows)
         if count == 0:
+            if also_copy is not None:
+                also_copy[0].copy_(also_copy[1], non_blocking=True)
+                event = torch.cuda.Event()
+                event.record()
+                return event, None, 0
             return None, None, 0
         if count > self.max_rows:
             raise ValueError(f"{count} rows to sample, the sampler was sized for {self.max_rows}")
@@ -94,6 +105,10 @@ class Sampler:
             self._dev_f.copy_(self._host_f, non_blocking=True)
             self._staged = signature
             self._all_greedy = all(params.greedy for _, params in rows)
+        if self._copied is not None:
+            # ``out`` is written again: not before its last copy has left (long done by now; the order is formal)
+            torch.cuda.current_stream().wait_event(self._copied)
+            self._copied = None
         if self._all_greedy:
             kernels.sample_greedy(logits, count, self._dev_i[:m], self.seen, self._dev_f[2 * m:], self.out,
                                   self._partial_score, self._partial_token)
@@ -102,7 +117,16 @@ class Sampler:
                            self._dev_f[m:2 * m], self._dev_f[2 * m:], self.out, scratch=self._pieces)
         host = self._out_hosts[self._flip]
         self._flip ^= 1
-        host.copy_(self.out, non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
+        main = torch.cuda.current_stream()
+        drawn = torch.cuda.Event()
+        drawn.record(main)
+        side = self._copy_stream
+        side.wait_event(drawn)
+        with torch.cuda.stream(side):
+            host.copy_(self.out, non_blocking=True)
+            if also_copy is not None:
+                also_copy[0].copy_(also_copy[1], non_blocking=True)
+            event = torch.cuda.Event()
+            event.record(side)
+        self._copied = event
         return event, host, count
