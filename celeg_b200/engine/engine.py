@@ -36,6 +36,9 @@ class _Runner:
         self._sample_seconds = 0.0
         self._gpu_seconds = 0.0
         self._reported = dict(loaded.step.host_seconds)
+        # the tokens a step feeds count as seen by their requests: marked on the way into the model, so that
+        # the marking is part of the step's graph
+        loaded.step.set_before_forward(sampler.mark_step)
 
     def reset_request(self, slot: int, seed: int) -> None:
         self.sampler.reset_slot(slot, seed)
@@ -58,7 +61,6 @@ class _Runner:
         logits = step.run(entries, token_source=self.sampler.out if tokens_on_device else None,
                           source_rows=source_rows if tokens_on_device else None)
         started = time.perf_counter()
-        self.sampler.mark_step(step.last_step)
         drawn = self.sampler.launch(logits, sample_rows, also_copy=(self._flags[index:index + 1], step.error_flag))
         self._end[index].record()
         self._sample_seconds += time.perf_counter() - started

@@ -113,6 +113,7 @@ class StepFunction:
         self.steps_run = 0
         self.kernel_steps_graphed = 0
         self.last_step: Optional[StepContext] = None
+        self.before_forward = None                # see set_before_forward
         # host seconds spent in run(), by phase: checking the batch and reserving pages, filling and
         # sending the step's metadata, enqueueing the model's kernels (or replaying their graph)
         self.host_seconds = {"check": 0.0, "stage": 0.0, "forward": 0.0}
@@ -226,6 +227,7 @@ class StepFunction:
             n_logits = mixed.logit_rows
         else:
             step, logit_rows, n_words = self._stage(entries, caches, total, spans, wanted, stride, max_ctx, padded)
+        tokens_from = None
         sent = n_words
         if token_source is not None and source_rows is not None:
             if n_words + len(source_rows) > self._host_np.shape[0]:
@@ -239,7 +241,9 @@ class StepFunction:
             if token_source.dtype != torch.int32 or token_source.numel() < total:
                 raise StepInputError("a token source must hold one int32 token for every token of the step")
             if source_rows is None:
-                step.token_ids[:total].copy_(token_source[:total], non_blocking=True)
+                if token_source.numel() < step.tokens:
+                    raise StepInputError("a token source must hold one int32 token for every row of the step")
+                tokens_from = token_source              # copied by _forward: inside the step's graph, if it has one
             else:
                 if len(source_rows) != total or min(source_rows) < 0 or max(source_rows) >= token_source.numel():
                     raise StepInputError("source rows must name one row of the token source for every token")
@@ -260,9 +264,11 @@ class StepFunction:
 
         graph_key = (padded, wanted, _context_bucket(max_ctx)) if (all_decode and self.use_graphs and wanted <= self.max_spans) else prompt_key
         if graph_key is not None:
-            self._run_graphed(graph_key, step, logit_rows, n_logits, logits)
+            if tokens_from is not None:
+                graph_key = graph_key + ("tokens on the device", tokens_from.data_ptr())
+            self._run_graphed(graph_key, step, logit_rows, n_logits, logits, tokens_from)
         else:
-            self.model.forward(step, logit_rows, n_logits, logits)
+            self._forward(step, logit_rows, n_logits, logits, tokens_from)
         self.manager.advance_each(caches, counts)
         self.steps_run += 1
         done = time.perf_counter()
@@ -468,7 +474,25 @@ class StepFunction:
             del self._graph_launches[prompt_graphs[0]]
         return key
 
-    def _run_graphed(self, key, step, logit_rows, wanted, logits) -> None:
+    def set_before_forward(self, hook) -> None:
+        """``hook(step)`` is called with every step's description before the model runs, on the step's stream and
+        inside its graph if it has one (a sampler marks the step's tokens as seen there). Graphs captured without
+        it are dropped."""
+        self.before_forward = hook
+        self._graphs.clear()
+        self._graph_launches.clear()
+
+    def _forward(self, step, logit_rows, wanted, logits, tokens_from) -> None:
+        """What a step enqueues on the device after its metadata: its tokens from the device (when the step
+        before drew them: every row of the step takes the token of the same row there; rows past the step's
+        requests get whatever lies there, they are spare), the hook, the model."""
+        if tokens_from is not None:
+            step.token_ids[:step.tokens].copy_(tokens_from[:step.tokens], non_blocking=True)
+        if self.before_forward is not None:
+            self.before_forward(step)
+        self.model.forward(step, logit_rows, wanted, logits)
+
+    def _run_graphed(self, key, step, logit_rows, wanted, logits, tokens_from=None) -> None:
         graph = self._graphs.get(key)
         if graph is None:
             # Warm up outside capture (library handles, lazy allocations), then capture. The
@@ -476,12 +500,12 @@ class StepFunction:
             # again, so the state from before the warm-up is put back in between (cache pages
             # are written with the same values both times).
             saved = self.storage.state.clone()
-            self.model.forward(step, logit_rows, wanted, logits)
+            self._forward(step, logit_rows, wanted, logits, tokens_from)
             torch.cuda.current_stream().synchronize()
             graph = torch.cuda.CUDAGraph()
             before = kernels.LAUNCHES
             with torch.cuda.graph(graph):
-                self.model.forward(step, logit_rows, wanted, logits)
+                self._forward(step, logit_rows, wanted, logits, tokens_from)
             self._graph_launches[key] = kernels.LAUNCHES - before
             self.storage.state.copy_(saved)
             self._graphs[key] = graph
