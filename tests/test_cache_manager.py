@@ -160,6 +160,70 @@ def test_random_traffic_keeps_the_books(seed):
     assert manager.free_slots == 4 and len(cleared) == serial
 
 
+@pytest.mark.parametrize("seed,windows", [(0, (None,)), (1, (None, 10)), (2, (None,)), (3, (None, 6))])
+def test_batched_calls_and_table_mirrors_agree_with_the_single_ones(seed, windows):
+    """Steps of many requests: pages_needed_each / reserve_each / advance_each against the calls for one request
+    on a twin manager, under random traffic; and the table mirrors (one int32 row per slot and group) hold
+    every live request's table, with NO_PAGE everywhere else, whatever was opened, grown and closed."""
+    import numpy as np
+    rng = random.Random(seed)
+    pages = tuple(80 for _ in windows)
+    groups = [(("g", i, w), PagedNeed(kv_heads=1, head_dim=8, window=w)) for i, w in enumerate(windows)]
+    batched = CacheManager(4, list(pages), groups, StateLayout(), 5, table_capacity=16)
+    single = CacheManager(4, list(pages), groups, StateLayout(), 5)
+    live, serial = [], 0
+    for _ in range(300):
+        action = rng.random()
+        if action < 0.2 and batched.free_slots:
+            name = f"r{serial}"
+            serial += 1
+            batched.open(name)
+            single.open(name)
+            live.append(name)
+        elif action < 0.9 and live:
+            chosen = rng.sample(live, rng.randint(1, len(live)))
+            counts = [rng.choice((1, 1, 1, 2, 5, 9)) for _ in chosen]
+            kept = [(n, c) for n, c in zip(chosen, counts) if batched.get(n).tokens + c <= 60]
+            chosen, counts = [n for n, _ in kept], [c for _, c in kept]
+            caches = [batched.get(n) for n in chosen]
+            need = batched.pages_needed_each(caches, counts)
+            want = [0] * len(windows)
+            for n, c in zip(chosen, counts):
+                twin = single.get(n)
+                for g, pages_g in enumerate(single.pages_needed(twin, twin.tokens + c)):
+                    want[g] += pages_g
+            assert need == want
+            batched.reserve_each(caches, counts)
+            batched.advance_each(caches, counts)
+            for n, c in zip(chosen, counts):
+                twin = single.get(n)
+                single.reserve(twin, twin.tokens + c)
+                single.advance(twin, twin.tokens + c)
+        elif live:
+            name = live.pop(rng.randrange(len(live)))
+            batched.close(name)
+            single.close(name)
+        batched.check_invariants()
+        assert [g.pool.free_pages for g in batched.groups] == [g.pool.free_pages for g in single.groups]
+        for name in live:
+            a, b = batched.get(name), single.get(name)
+            # (the page numbers may differ: the twin gives pages back between two requests of a step, the
+            # batched calls after all of them; which places of a table hold a page must not)
+            assert a.tokens == b.tokens and a.first_live_page == b.first_live_page
+            assert [[p == NO_PAGE for p in t] for t in a.tables] == [[p == NO_PAGE for p in t] for t in b.tables]
+            assert a.capacity == min(len(t) for t in a.tables) * 4
+        for g, mirror in enumerate(batched.table_mirrors):
+            expect = np.full_like(mirror, NO_PAGE)
+            for name in live:
+                cache = batched.get(name)
+                expect[cache.slot, :len(cache.tables[g])] = cache.tables[g]
+            assert np.array_equal(mirror, expect)
+    for name in live:
+        batched.close(name)
+    assert all(np.all(mirror == NO_PAGE) for mirror in batched.table_mirrors)
+    assert all(group.pool.free_pages == group.pool.total_pages for group in batched.groups)
+
+
 def test_values_may_be_narrower_than_keys_or_absent():
     """A paged need states the width of what is kept beside the keys on its own: equal (attention), narrower,
     or nothing (one latent vector per position). Needs that differ in it form groups of their own."""
