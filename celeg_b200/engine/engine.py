@@ -43,6 +43,11 @@ class _Runner:
     def reset_request(self, slot: int, seed: int) -> None:
         self.sampler.reset_slot(slot, seed)
 
+    def padded_singles(self, count: int) -> int:
+        """Rows that ``count`` decoded tokens take in a step that also holds prompt portions (the step function
+        pads such a step to a launch shape)."""
+        return self.loaded.step.padded_single_rows(count)
+
     def save_generator(self, slot: int) -> int:
         return self.sampler.get_rng(slot)
 

@@ -197,6 +197,7 @@ class Scheduler:
         self._inflight = None             # (plan, handle) of a step that was enqueued and not yet collected
         # one step of run-ahead needs a runner that can enqueue without waiting
         self._runs_ahead = options.run_ahead and hasattr(runner, "launch") and hasattr(runner, "collect")
+        self._padded_singles = getattr(runner, "padded_singles", None)
 
     # ------------------------------------------------------------------ public
     def submit(self, prompt: Sequence[int], options: Optional[RequestOptions] = None) -> int:
@@ -363,6 +364,10 @@ class Scheduler:
             free = [f - n for f, n in zip(free, needed)]
             plan.entries.append(PlannedEntry(request, [request.generated[-1]], samples=True, is_decode=True))
             budget -= 1
+        if prefilling and plan.entries and self._padded_singles is not None:
+            # the runner pads the decoded tokens of a mixed step to a coarser row count: the portions get what
+            # is left of the budget beside those rows, so that the step's rows stay within it
+            budget = min(budget, self.options.max_batched_tokens - self._padded_singles(len(plan.entries)))
         for request in prefilling:
             remaining = len(request.feed) - request.prefill_offset
             count = min(remaining, self.options.prefill_chunk_tokens, budget)

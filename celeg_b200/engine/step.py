@@ -226,7 +226,11 @@ class StepFunction:
             step, logit_rows, n_words = self._stage_padded_prompt(entries, caches, mixed, stride, max_ctx)
             n_logits = mixed.logit_rows
         else:
-            step, logit_rows, n_words = self._stage(entries, caches, total, spans, wanted, stride, max_ctx, padded)
+            if padded > spans and wanted == spans:
+                # every request wants its row: the spare rows' logits are computed too (nobody reads them), so
+                # that the launch shape depends on the padded row count alone
+                n_logits = padded
+            step, logit_rows, n_words = self._stage(entries, caches, total, spans, n_logits, stride, max_ctx, padded)
         tokens_from = None
         sent = n_words
         if token_source is not None and source_rows is not None:
@@ -262,7 +266,7 @@ class StepFunction:
                 self._wide_logits = torch.empty((wanted, vocab), dtype=torch.float32, device=self.rt.device)
             logits = self._wide_logits
 
-        graph_key = (padded, wanted, _context_bucket(max_ctx)) if (all_decode and self.use_graphs and wanted <= self.max_spans) else prompt_key
+        graph_key = (padded, n_logits, _context_bucket(max_ctx)) if (all_decode and self.use_graphs and wanted <= self.max_spans) else prompt_key
         if graph_key is not None:
             if tokens_from is not None:
                 graph_key = graph_key + ("tokens on the device", tokens_from.data_ptr())
@@ -276,6 +280,16 @@ class StepFunction:
         self.host_seconds["stage"] += staged - checked
         self.host_seconds["forward"] += done - staged
         return logits[:wanted]
+
+    def padded_single_rows(self, singles: int) -> int:
+        """How many rows the ``singles`` single tokens at the head of a step of prompt portions take when the step
+        is padded to a launch shape: 16, 32, 64, then multiples of 32 (a coarser grid than a decoding step's:
+        beside prompt portions a few spare single tokens cost nothing, and every row count less is a graph less
+        to capture). A scheduler that wants the step's rows to stay within its token budget counts these."""
+        if singles <= 0 or not self.use_graphs:
+            return max(0, singles)
+        rows = next((n for n in (16, 32, 64) if n >= singles), (singles + 31) // 32 * 32)
+        return rows if rows <= self.max_spans else self._graph_rows(singles)
 
     def _check_single_tokens(self, entries, auto_begin: bool):
         """The checks of :meth:`run` for a step in which every request brings one token, over whole lists
@@ -324,15 +338,11 @@ class StepFunction:
         portions = lengths[singles:]
         if not portions or any(n == 1 for n in portions):
             return None                                   # all single tokens, or a single token after a portion
-        # (a coarser grid than a decoding step's: beside prompt portions a few spare single tokens cost nothing,
-        # and every row count less is a graph less to capture)
-        single_rows = 0
-        if singles:
-            single_rows = next((n for n in (16, 32, 64) if n >= singles), (singles + 31) // 32 * 32)
-            if single_rows > self.max_spans:
-                single_rows = self._graph_rows(singles)
+        single_rows = self.padded_single_rows(singles)
         portion_tokens = sum(portions)
-        padded_tokens = -(-portion_tokens // PROMPT_TOKEN_STEP) * PROMPT_TOKEN_STEP
+        # the step's rows together are a multiple of PROMPT_TOKEN_STEP: the products work in tiles of 128 rows, and a
+        # tile more (2,112 rows where 2,048 would do) is a wave more of their blocks
+        padded_tokens = -(-(single_rows + portion_tokens) // PROMPT_TOKEN_STEP) * PROMPT_TOKEN_STEP - single_rows
         spare = padded_tokens - portion_tokens
         spans = single_rows + len(portions) + (1 if spare else 0)
         logit_rows = max(1, wanted, single_rows + len(portions))       # (a scheduler's step wants one row a span at most)
@@ -527,8 +537,8 @@ class StepFunction:
         """Fill the pinned staging buffer; returns the StepContext, the logit-row tensor and the
         number of int32 words to copy. The layout depends only on (T, R, F, stride), so steps of
         the same shape use the same device addresses. ``padded`` > spans (decoding steps only): rows are
-        added up to that number; they carry token 0 at position 0 of the storage's spare page and slot,
-        their logits are never asked for."""
+        added up to that number; they carry token 0 at position 0 of the storage's spare page and slot;
+        ``wanted`` then counts their logit rows too if the caller has them computed (nobody reads them)."""
         real_spans = spans
         if padded is not None and padded > spans:
             total = spans = padded
@@ -568,6 +578,8 @@ class StepFunction:
                 if entry.want:
                     logit_rows_host[out] = index
                     out += 1
+            if wanted > out:                       # (the spare rows of a padded step, see run)
+                logit_rows_host[out:wanted] = range(real_spans, real_spans + wanted - out)
             mirrors = self.manager.table_mirrors
             slots = span_slot[:real_spans] if mirrors is not None else None
             for g in range(self.groups):

@@ -337,6 +337,30 @@ def test_run_ahead_drops_the_token_after_an_end_of_sequence():
     manager.check_invariants()
 
 
+def test_portions_leave_room_for_the_rows_a_runner_pads_decoded_tokens_to():
+    """A runner that pads the decoded tokens of a mixed step to a coarser row count says so (``padded_singles``);
+    the plan then gives the prompt portions what the budget leaves beside those rows, not beside the tokens."""
+    scheduler, runner, manager = make_ahead(slots=4, run_ahead=False)
+    runner.padded_singles = lambda count: -(-count // 4) * 4
+    scheduler._padded_singles = runner.padded_singles
+    first = scheduler.submit([1, 2, 3], RequestOptions(max_new_tokens=20, eos_tokens=()))
+    while scheduler.status(first).value != "decoding":
+        scheduler.step()
+    second = scheduler.submit(list(range(1, 41)), RequestOptions(max_new_tokens=2, eos_tokens=()))
+    scheduler._admit()
+    plan = scheduler.plan()
+    sizes = [len(p.tokens) for p in plan.entries]
+    assert sizes[0] == 1 and not plan.entries[1].is_decode
+    # budget 16, one decoded token padded to 4 rows: 12 tokens are left, the portion limit is 8
+    assert sizes[1] == 8
+    scheduler.options.prefill_chunk_tokens = 16
+    sizes = [len(p.tokens) for p in scheduler.plan().entries]
+    assert sizes == [1, 12]
+    run_all(scheduler)
+    assert scheduler.poll(first).tokens == expected_output([1, 2, 3], 20, eos=())
+    assert scheduler.poll(second).tokens == expected_output(list(range(1, 41)), 2, eos=())
+
+
 def test_run_ahead_goes_on_with_the_requests_that_do_not_end():
     """Requests that reach their last token at different steps: the step after is still enqueued early, for the
     requests that go on, and takes their tokens from the rows they had in the step before."""
