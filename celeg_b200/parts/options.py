@@ -23,6 +23,10 @@ class KernelOptions:
     # rows: 9.70 / 6.51 / 4.66 / 4.84 / 3.99 ms with this package's kernel against 9.34 / 6.15 / 4.59 / 4.76 /
     # 4.13 ms with the library's.
     tensor_core_min_rows: int = 2048
+    # ... and below this width of the model (the product's k) too: at 2,048 rows and a width of 1,024 the library
+    # with its activation kernel takes 52 us where this package's kernel takes 62 (a tile's 16 k-steps are too
+    # few to hide its start and its epilogue); at 1,536 it is 78 against 76, at 2,048 117 against 106.
+    tensor_core_min_width: int = 1536
     # -1: the host chooses the tile shape of the tcgen05 product; 0..3 force one (for measurements)
     tensor_core_variant: int = -1
     # decode steps of few rows: residual add + RMSNorm split over the products before and after it
@@ -42,8 +46,9 @@ class KernelOptions:
             raise ValueError(f"tensor_core_products must be none, swiglu or all, got {self.tensor_core_products!r}")
         if not -1 <= self.tensor_core_variant <= 3:
             raise ValueError("tensor_core_variant must lie in -1..3")
-        if self.tensor_core_min_rows < 1 or self.prefetch_mb < 0:
-            raise ValueError("tensor_core_min_rows must be positive and prefetch_mb must not be negative")
+        if self.tensor_core_min_rows < 1 or self.tensor_core_min_width < 1 or self.prefetch_mb < 0:
+            raise ValueError("tensor_core_min_rows and tensor_core_min_width must be positive and prefetch_mb must "
+                             "not be negative")
 
     @classmethod
     def from_env(cls, environ: Optional[Mapping[str, str]] = None, prefix: str = "CELEG_B200_") -> "KernelOptions":

@@ -115,6 +115,7 @@ class Runtime:
         self.fuse_small_batches = options.fuse_small_batches
         self.tensor_core_products = options.tensor_core_products
         self.tensor_core_min_rows = options.tensor_core_min_rows
+        self.tensor_core_min_width = options.tensor_core_min_width
         self.tensor_core_variant = options.tensor_core_variant
         self.split_norms = options.split_norms
         self.fuse_decode_qk = options.fuse_decode_qk
@@ -251,7 +252,8 @@ class Runtime:
             return
         if (self.act_dtype == torch.bfloat16 and kernels.gemm_tcgen05_supported(x, gate_up_weight)
                 and (self.tensor_core_products == "all"
-                     or (self.tensor_core_products == "swiglu" and rows >= self.tensor_core_min_rows))):
+                     or (self.tensor_core_products == "swiglu" and rows >= self.tensor_core_min_rows
+                         and gate_up_weight.shape[1] >= self.tensor_core_min_width))):
             kernels.gemm_tcgen05(x, gate_up_weight, out, rows, kernels.TC_SWIGLU, self.error_flag,
                                  self.tensor_core_variant)
             return
