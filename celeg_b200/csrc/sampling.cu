@@ -547,7 +547,16 @@ CELEG_API int celeg_sample(const float* logits, long long ld, int vocab, int row
                   vocab, ld);
     CELEG_REQUIRE(rng != nullptr || temperature == nullptr, "sample: temperature sampling needs generator states");
     if (rows == 0) return 0;
-    const int threads = vocab >= 16384 ? 1024 : 256;
+    // (more rows than SMs: blocks of 512 threads, of which two run on an SM at a time (registers), so that 256 rows
+    // are one wave of blocks instead of two)
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (sms <= 0) sms = 148;
+    }
+    const int threads = vocab >= 16384 ? (rows > sms ? 512 : 1024) : 256;
     if (part_score && part_token && part_count && rows <= kSampleChunkedRows && vocab >= kSampleChunks * 1024) {
         launch_chained(sample_chunks_kernel, dim3(kSampleChunks, rows), 256, 0, stream, logits, ld, vocab, row_slot,
                        seen, temperature, top_k, penalty, kSampleChunks, part_score, part_token, part_count);
