@@ -68,6 +68,8 @@ __device__ __forceinline__ unsigned score_key(float v) {
 }
 
 constexpr int kSelectPool = 1024;   // most candidates the first stage may leave for the exact selection
+constexpr int kSelectByRank = 256;  // up to this many pairs are ranked by counting instead of by a radix selection
+constexpr int kSelectGroups = 128;  // the first stage bounds the k-th score by the k-th of this many group maxima (>= kMaxTopK)
 
 struct SelectShared {
     Best scratch[33];
@@ -94,6 +96,30 @@ __device__ int select_top_k(SelectShared& sm, const int n, const int k, ScoreAt 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     constexpr int kBatch = 8;
     __syncthreads();
+    if (n <= kSelectByRank) {
+        // Few pairs (the pool that the first stage of range_top_k leaves, its group maxima): every pair counts
+        // the pairs that come before it in the order and, if fewer than k do, takes that place. The order is
+        // total (tokens differ), so the places are a permutation. No histogram, two barriers.
+        if (threadIdx.x == 0) sm.count = 0u;
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float sc = score_at(i);
+            if (sc != sc) continue;                          // not a number: never a candidate
+            const int tk = token_at(i);
+            int rank = 0;
+            for (int j = 0; j < n; ++j) {
+                const float other = score_at(j);
+                rank += (other == other && better(other, token_at(j), sc, tk)) ? 1 : 0;
+            }
+            atomicAdd(&sm.count, 1u);
+            if (rank < k) {
+                sm.sorted_score[rank] = sc;
+                sm.sorted_token[rank] = tk;
+            }
+        }
+        __syncthreads();
+        return min((int)sm.count, k);
+    }
     if (threadIdx.x == 0) {
         sm.prefix = 0u;
         sm.remaining = (unsigned)k;
@@ -252,9 +278,9 @@ __device__ int select_top_k(SelectShared& sm, const int n, const int k, ScoreAt 
 }
 
 // The k best scores of tokens [begin, end) of a row, into sm.sorted_*, in two stages. First every thread keeps
-// the largest score of its share; the k-th largest of these maxima is a lower bound of the k-th largest score
-// (k different tokens reach it), so one more pass that keeps every token at or above it leaves a pool of little
-// more than k candidates for the exact selection. A pool that overflows (scores that are equal by the thousand)
+// the largest score of its share and groups of threads the largest of theirs; the k-th largest of these 128
+// maxima is a lower bound of the k-th largest score (k different tokens reach it), so one more pass that keeps
+// every token at or above it leaves a pool of about twice k candidates for the exact selection. A pool that overflows (scores that are equal by the thousand)
 // sends the range to the exact selection over all of it instead. The range is read twice where the plain form
 // reads it k times. Returns how many were found.
 template <typename ScoreOf>
@@ -277,10 +303,21 @@ __device__ int range_top_k(SelectShared& sm, const int begin, const int end, con
             }
         }
     }
-    sm.thread_max[threadIdx.x] = any ? mine : __int_as_float(0x7fc00000);
-    int found = select_top_k(sm, (int)blockDim.x, k, [&](int i) { return sm.thread_max[i]; }, [](int i) { return i; });
+    // the maxima of groups of neighbouring threads, kSelectGroups of them (a maximum ignores what is not a number)
+    float group_max = any ? mine : __int_as_float(0x7fc00000);
+    const int group = max(1, (int)blockDim.x / kSelectGroups);          // 8, 4 or 2 threads: a power of two within a warp
+    for (int offset = group >> 1; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, group_max, offset);
+        group_max = group_max != group_max ? other : (other != other ? group_max : fmaxf(group_max, other));
+    }
+    __syncthreads();                                   // (sm.thread_max may still be read by an earlier selection)
+    if (threadIdx.x % group == 0) sm.thread_max[threadIdx.x / group] = group_max;
+    const int groups = (int)blockDim.x / group;
+    int found = select_top_k(sm, groups, k, [&](int i) { return sm.thread_max[i]; }, [](int i) { return i; });
     if (found == 0) return 0;                          // not one score that is a number
-    const float bound = sm.sorted_score[found - 1];
+    // k groups hold a score each at or above the k-th largest maximum: a lower bound of the k-th largest score.
+    // Fewer groups with a score than k (a short range, scores that are no numbers): no bound, every score is pooled.
+    const float bound = found >= k ? sm.sorted_score[k - 1] : -INFINITY;
     __syncthreads();
     if (threadIdx.x == 0) sm.pool_count = 0u;
     __syncthreads();
