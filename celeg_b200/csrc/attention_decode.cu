@@ -16,6 +16,36 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(const 
     attention_decode_item<D_PAD, BN>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem_raw, threadIdx.x, BlockSync());
 }
 
+// One warp an item, four items a block (see attention_decode_item_solo).
+template <int D_PAD>
+__global__ void __launch_bounds__(kDecodeThreads) attention_decode_solo_kernel(const DecodeParams p, const int items) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    chain_release();
+    chain_wait();
+    const int warp = threadIdx.x >> 5;
+    const int item = blockIdx.x * kDecodeWarps + warp;
+    if (item >= items) return;
+    attention_decode_item_solo<D_PAD>(p, item % p.kv_heads, item / p.kv_heads,
+                                      smem_raw + (size_t)warp * decode_solo_warp_bytes<D_PAD>(), threadIdx.x & 31);
+}
+
+template <int D_PAD>
+static int launch_decode_solo(const DecodeParams& p, int tokens, cudaStream_t stream) {
+    constexpr size_t smem = kDecodeWarps * decode_solo_warp_bytes<D_PAD>();
+    if (smem > 40 * 1024) {
+        const cudaError_t status = cudaFuncSetAttribute(attention_decode_solo_kernel<D_PAD>,
+                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) {
+            set_error("attention_decode: %s", cudaGetErrorString(status));
+            return -2;
+        }
+    }
+    const int items = tokens * p.kv_heads;
+    launch_chained(attention_decode_solo_kernel<D_PAD>, dim3((items + kDecodeWarps - 1) / kDecodeWarps), kDecodeThreads,
+                   smem, stream, p, items);
+    return check_launch("attention_decode (one warp an item)");
+}
+
 template <int D_PAD, int BN>
 static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t stream) {
     constexpr size_t smem = decode_item_bytes<D_PAD, BN>();
@@ -34,6 +64,11 @@ static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t stream) 
 }  // namespace celeg_b200
 
 using namespace celeg_b200;
+
+static long long g_decode_solo_items = 1536;     // (measured: level with the four-warp form at 1,024 items, ahead from 2,048)
+
+// For measurements: from how many (token, kv head) items on a launch of short contexts gives a warp an item.
+CELEG_API void celeg_attention_decode_solo_items(long long items) { g_decode_solo_items = items; }
 
 // Bytes of scratch the caller must provide for `tokens` query tokens.
 CELEG_API long long celeg_attention_decode_scratch_bytes(int tokens, int q_heads, int kv_heads, int head_dim,
@@ -109,6 +144,11 @@ static int attention_decode_checked(const void* q, int q_row_stride, void* out, 
     // needs half the shared memory, so twice as many items run at a time; their start and their merge, not
     // their keys, are what such a launch consists of.
     const bool few_keys = chunk <= 256;
+    // ... and with very many such items (one split each) a warp serves an item alone
+    if (few_keys && max_splits == 1 && (head_dim & 1) == 0 && (long long)tokens * kv_heads >= g_decode_solo_items) {
+        if (head_dim <= 64) return launch_decode_solo<64>(p, tokens, stream);
+        if (head_dim <= 128) return launch_decode_solo<128>(p, tokens, stream);
+    }
     if (head_dim <= 64) return few_keys ? launch_decode<64, 32>(p, grid, stream) : launch_decode<64, 64>(p, grid, stream);
     if (head_dim <= 128) return few_keys ? launch_decode<128, 32>(p, grid, stream) : launch_decode<128, 64>(p, grid, stream);
     return launch_decode<256, 32>(p, grid, stream);

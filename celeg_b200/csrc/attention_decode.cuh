@@ -517,4 +517,229 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     }
 }
 
+// ------------------------------------------------------------------------------------------- one warp an item
+// Many requests with short contexts (hundreds of tokens x kv heads, at most a few tiles of keys each): an item is
+// too little work for four warps. What such a launch then consists of is the blocks' starts and the three
+// block-wide barriers at which the warps' partial results meet, not the keys. Here ONE warp serves an item over all
+// of its keys (one split), a block holds four independent items, and nothing is exchanged between warps: the
+// warp's own accumulators are the result. Same arithmetic per tile as above (and the same fused q/k step).
+template <int D_PAD>
+__host__ __device__ constexpr size_t decode_solo_warp_bytes() {
+    return (size_t)(16 + 2 * 32 + 2) * D_PAD * sizeof(__nv_bfloat16);      // Q tile, K tile, V tile, the own key and value
+}
+
+template <int D_PAD>
+__device__ __forceinline__ void attention_decode_item_solo(const DecodeParams& p, const int kvh, const int t,
+                                                           unsigned char* warp_smem, const int lane) {
+    constexpr int TN = 32;
+    constexpr int kChunks = D_PAD / 8;
+    constexpr int kKTiles = D_PAD / 16;
+    constexpr int kOTiles = D_PAD / 8;
+    const int g = lane >> 2, c2 = (lane & 3) * 2;
+    const int group = p.q_heads / p.kv_heads;
+    const int d = p.head_dim;
+    const int pos = p.positions[t];
+    const int first = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int end = pos + 1;
+    if (end - first > p.chunk) {
+        // more keys than the launch was laid out for (one split): nothing is written, the caller reads code 3
+        if (lane == 0) atomicExch(p.error_flag, 3);
+        return;
+    }
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(warp_smem);
+    __nv_bfloat16* k_t = q_s + 16 * D_PAD;
+    __nv_bfloat16* v_t = k_t + TN * D_PAD;
+    __nv_bfloat16* new_k = v_t + TN * D_PAD;
+    __nv_bfloat16* new_v = new_k + D_PAD;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const int* table = p.block_table + (size_t)p.token_span[t] * p.table_stride;
+
+    auto issue = [&](const int tile_begin) {
+        const int key = tile_begin + lane;
+        long long mine = -1;
+        if (key < end) {
+            const int page = table[key / p.page_tokens];
+            if (page < 0)
+                atomicExch(p.error_flag, 2);
+            else
+                mine = (long long)page * p.page_stride + ((long long)kvh * p.page_tokens + key % p.page_tokens) * d;
+        }
+#pragma unroll
+        for (int i = 0; i < TN * kChunks / 32; ++i) {
+            const int idx = lane + 32 * i;
+            const int r = idx / kChunks, ch = idx % kChunks;
+            const long long off = __shfl_sync(0xffffffffu, mine, r);
+            __nv_bfloat16* kd = k_t + tile_offset<D_PAD>(r, ch);
+            __nv_bfloat16* vd = v_t + tile_offset<D_PAD>(r, ch);
+            if (off >= 0 && ch * 8 < d) {
+                cp_async_16(kd, p.k_cache + off + ch * 8);
+                cp_async_16(vd, p.v_cache + off + ch * 8);
+            } else {
+                *reinterpret_cast<uint4*>(kd) = zero;
+                *reinterpret_cast<uint4*>(vd) = zero;
+            }
+        }
+        cp_async_commit();
+    };
+    issue(first);                                     // the first tile is on its way while the query is prepared
+    for (int idx = lane; idx < 16 * kChunks; idx += 32) {
+        const int r = idx / kChunks, ch = idx % kChunks;
+        __nv_bfloat16* dst = q_s + tile_offset<D_PAD>(r, ch);
+        if (r < group && ch * 8 < d)
+            *reinterpret_cast<uint4*>(dst) = __ldcg(reinterpret_cast<const uint4*>(
+                p.q + (size_t)t * p.q_row_stride + (size_t)(kvh * group + r) * d + ch * 8));
+        else
+            *reinterpret_cast<uint4*>(dst) = zero;
+    }
+    __syncwarp();
+    if (p.fuse_qk) {
+        const int rotary = p.inv_freq ? p.rotary_dim : (d & ~1);
+        for (int r = 0; r < group; ++r) {
+            auto at = [&](int i) { return q_s + tile_offset<D_PAD>(r, i >> 3) + (i & 7); };
+            decode_norm_rope_head(at, at, p.q_norm_w, p.inv_freq, d, rotary, p.norm_eps, pos, lane);
+        }
+        // the token's own key and value: into shared memory and into the cache
+        const int page = table[pos / p.page_tokens];
+        if (page < 0) {
+            if (lane == 0) atomicExch(p.error_flag, 1);
+        } else {
+            const long long cache_at = (long long)page * p.page_stride +
+                                       ((long long)kvh * p.page_tokens + pos % p.page_tokens) * d;
+            const __nv_bfloat16* row = p.q + (size_t)t * p.q_row_stride;
+            const __nv_bfloat16* raw_k = row + (size_t)(p.q_heads + kvh) * d;
+            const __nv_bfloat16* raw_v = row + (size_t)(p.q_heads + p.kv_heads + kvh) * d;
+            for (int i = lane; i < d; i += 32) {
+                new_k[i] = __ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(raw_k + i)));
+                const __nv_bfloat16 v = __ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(raw_v + i)));
+                new_v[i] = v;
+                p.v_cache_w[cache_at + i] = v;
+            }
+            __syncwarp();
+            auto at = [&](int i) { return new_k + i; };
+            decode_norm_rope_head(at, at, p.k_norm_w, p.inv_freq, d, rotary, p.norm_eps, pos, lane);
+            __syncwarp();
+            for (int i = lane; i < d; i += 32) p.k_cache_w[cache_at + i] = new_k[i];
+        }
+        __syncwarp();
+    }
+
+    float o[kOTiles][4];
+#pragma unroll
+    for (int i = 0; i < kOTiles; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
+    float run_max[2] = {-INFINITY, -INFINITY};
+    float run_sum[2] = {0.0f, 0.0f};
+    const float scale_log2 = p.scale * 1.4426950408889634f;
+    const int mi = lane >> 3, lr = lane & 7;
+
+    for (int tile_begin = first; tile_begin < end; tile_begin += TN) {
+        if (tile_begin > first) issue(tile_begin);
+        cp_async_wait_group<0>();
+        __syncwarp();
+        if (p.fuse_qk && pos >= tile_begin && pos < tile_begin + TN) {
+            const int r = pos - tile_begin;
+            for (int ch = lane; ch * 8 < d; ch += 32) {
+                *reinterpret_cast<uint4*>(k_t + tile_offset<D_PAD>(r, ch)) = *reinterpret_cast<const uint4*>(new_k + ch * 8);
+                *reinterpret_cast<uint4*>(v_t + tile_offset<D_PAD>(r, ch)) = *reinterpret_cast<const uint4*>(new_v + ch * 8);
+            }
+            __syncwarp();
+        }
+        float s[TN / 8][4];
+#pragma unroll
+        for (int i = 0; i < TN / 8; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[i][e] = 0.0f;
+#pragma unroll
+        for (int kt = 0; kt < kKTiles; ++kt) {
+            unsigned a[4];
+            ldmatrix_x4(a, q_s + tile_offset<D_PAD>((mi & 1) * 8 + lr, kt * 2 + (mi >> 1)));
+#pragma unroll
+            for (int np = 0; np < TN / 16; ++np) {
+                unsigned b[4];
+                ldmatrix_x4(b, k_t + tile_offset<D_PAD>(np * 16 + (mi >> 1) * 8 + lr, kt * 2 + (mi & 1)));
+                mma_bf16(s[2 * np], a, b[0], b[1]);
+                mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+        float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < TN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = tile_begin + nt * 8 + c2 + (e & 1);
+                const float v = key < end ? s[nt][e] * scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+            }
+        }
+        float correction[2], safe_max[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            float m = tile_max[half];
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            const float new_max = fmaxf(run_max[half], m);
+            correction[half] = new_max == -INFINITY ? 1.0f : exp2f(run_max[half] - new_max);
+            safe_max[half] = new_max == -INFINITY ? 0.0f : new_max;
+            run_max[half] = new_max;
+            run_sum[half] *= correction[half];
+        }
+#pragma unroll
+        for (int nt = 0; nt < TN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(s[nt][e] - safe_max[e >> 1]);
+                s[nt][e] = pv;
+                run_sum[e >> 1] += pv;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kOTiles; ++i) {
+            o[i][0] *= correction[0];
+            o[i][1] *= correction[0];
+            o[i][2] *= correction[1];
+            o[i][3] *= correction[1];
+        }
+#pragma unroll
+        for (int kt = 0; kt < TN / 16; ++kt) {
+            unsigned a[4];
+            a[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+            a[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+            a[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+            a[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+#pragma unroll
+            for (int np = 0; np < kOTiles / 2; ++np) {
+                unsigned b[4];
+                ldmatrix_x4_trans(b, v_t + tile_offset<D_PAD>(kt * 16 + (mi & 1) * 8 + lr, np * 2 + (mi >> 1)));
+                mma_bf16(o[2 * np], a, b[0], b[1]);
+                mma_bf16(o[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+        __syncwarp();                                  // every lane is done with the tile before it is refilled
+    }
+    // a row's sum over the four lanes that share it; the warp's accumulators are the item's result
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        run_sum[half] += __shfl_xor_sync(0xffffffffu, run_sum[half], 1);
+        run_sum[half] += __shfl_xor_sync(0xffffffffu, run_sum[half], 2);
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = g + half * 8;
+        if (r >= group) continue;
+        const float inv = 1.0f / run_sum[half];
+        __nv_bfloat16* dst = p.out + ((size_t)t * p.q_heads + kvh * group + r) * d;
+#pragma unroll
+        for (int i = 0; i < kOTiles; ++i) {
+            const int col = i * 8 + c2;
+            if (col + 1 < d) {
+                *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(o[i][half * 2] * inv, o[i][half * 2 + 1] * inv);
+            } else if (col < d) {
+                dst[col] = __float2bfloat16_rn(o[i][half * 2] * inv);
+            }
+        }
+    }
+}
+
 }  // namespace celeg_b200

@@ -54,6 +54,7 @@ _SIGNATURES = {
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
                                      c_void_p],
+    "celeg_attention_decode_solo_items": [c_longlong],
     "celeg_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                 c_void_p, c_void_p],

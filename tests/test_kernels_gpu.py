@@ -467,6 +467,86 @@ def test_attention_decode_split_keys(heads, kv_heads, head_dim, page_tokens, win
         close(out, want, dtype)
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,window,normed,rotary", [
+    (4, 2, 16, 16, None, True, 16), (32, 8, 64, 16, None, True, 64), (5, 5, 48, 8, None, True, 48),
+    (6, 3, 80, 16, 37, True, 80), (16, 1, 128, 64, None, False, 128), (3, 1, 48, 16, 5, True, 20),
+])
+def test_attention_decode_one_warp_an_item(heads, kv_heads, head_dim, page_tokens, window, normed, rotary):
+    """The form for very many requests with short contexts, where one warp serves a (token, kv head) item over
+    all of its keys and nothing is exchanged between warps: forced here for a handful of requests (contexts of
+    one key, a page edge, a tile edge, several tiles; a far key made to dominate), against the formula, and with
+    the q/k step inside against the separate kernels (same output, same cache), twice in a row."""
+    from celeg_b200 import kernels
+    library = kernels.library()
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(28)
+    lengths = [1, 16, 17, 32, 33, 200, 256, 64, 129]
+    chunk, max_splits = 256, 1
+    pages = sum((n + page_tokens - 1) // page_tokens for n in lengths) + 7
+    k_cache, v_cache, table, ks, vs = paged_setup(rng, dtype, lengths, kv_heads, head_dim, page_tokens, pages)
+    tokens = len(lengths)
+    q = rounded(rng.normal(size=(tokens, heads, head_dim)), dtype)
+    if not window:
+        q[5] = rounded(ks[5][2, 0][None, :].repeat(heads, 0) * 3.0, dtype)      # key 2 of 200 stands out
+    positions = np.array([n - 1 for n in lengths], dtype=np.int32)
+    token_span = np.arange(tokens, dtype=np.int32)
+    scale, eps = head_dim ** -0.5, 1e-5
+    partial_o = torch.empty(tokens * heads * head_dim, dtype=torch.float32, device="cuda")
+    partial_ml = torch.empty(tokens * heads * 2, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(tokens * kv_heads, dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    want = np.stack([attention_reference(q[t], ks[t], vs[t], int(positions[t]), scale, window)
+                     for t in range(tokens)]).reshape(tokens, -1)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = dev(rounded(rng.normal(size=(tokens, width)), dtype), dtype)
+    q_w = dev((1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32)) if normed else None
+    k_w = dev((1 + 0.05 * rng.normal(size=head_dim)).astype(np.float32)) if normed else None
+    inv_freq = dev((1e6 ** (-2.0 * np.arange(rotary // 2) / rotary)).astype(np.float32))
+    library.celeg_attention_decode_solo_items(1)
+    try:
+        out = torch.zeros((tokens, heads * head_dim), dtype=dtype, device="cuda")
+        kernels.attention_decode(dev(q.reshape(tokens, -1), dtype), heads * head_dim, out, k_cache, v_cache,
+                                 dev(positions), dev(token_span), dev(table), tokens, heads, kv_heads, head_dim,
+                                 page_tokens, window, scale, chunk, max_splits, partial_o, partial_ml, counters, flag)
+        assert int(flag.item()) == 0
+        close(out, want, dtype)
+        # the q/k step inside, against the separate kernels (which run in the four-warp form)
+        library.celeg_attention_decode_solo_items(1 << 40)
+        qkv_a, k_a, v_a = qkv.clone(), k_cache.clone(), v_cache.clone()
+        kernels.qk_norm_rope_store(qkv_a, q_w, k_w, inv_freq, dev(positions), dev(token_span), dev(table), k_a, v_a,
+                                   tokens, heads, kv_heads, head_dim, rotary, page_tokens, eps, True, flag)
+        out_a = torch.zeros_like(out)
+        kernels.attention_decode(qkv_a, width, out_a, k_a, v_a, dev(positions), dev(token_span), dev(table), tokens,
+                                 heads, kv_heads, head_dim, page_tokens, window, scale, chunk, max_splits, partial_o,
+                                 partial_ml, counters, flag)
+        library.celeg_attention_decode_solo_items(1)
+        k_b, v_b = k_cache.clone(), v_cache.clone()
+        for _ in range(2):
+            out_b = torch.zeros_like(out)
+            kernels.attention_decode_fused(qkv.clone(), width, out_b, k_b, v_b, dev(positions), dev(token_span),
+                                           dev(table), tokens, heads, kv_heads, head_dim, page_tokens, window, scale,
+                                           chunk, max_splits, partial_o, partial_ml, counters, flag, q_w, k_w,
+                                           inv_freq, rotary, eps)
+            assert int(flag.item()) == 0
+            assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
+            # one warp sums a row's tiles in another order than four warps and a merge do: equal to rounding
+            assert float((out_a.float() - out_b.float()).abs().max()) <= 2e-2 * max(1.0, float(out_a.float().abs().max()))
+    finally:
+        library.celeg_attention_decode_solo_items(1536)
+    # a context beyond what the launch was laid out for: code 3, nothing written for that token
+    library.celeg_attention_decode_solo_items(1)
+    try:
+        out = torch.full((tokens, heads * head_dim), 7.0, dtype=dtype, device="cuda")
+        kernels.attention_decode(dev(q.reshape(tokens, -1), dtype), heads * head_dim, out, k_cache, v_cache,
+                                 dev(positions), dev(token_span), dev(table), tokens, heads, kv_heads, head_dim,
+                                 page_tokens, None, scale, 128, 1, partial_o, partial_ml, counters, flag)
+        assert int(flag.item()) == 3
+        flag.zero_()
+        assert bool((out[5].float() == 7.0).all()) and bool((out[6].float() == 7.0).all())
+    finally:
+        library.celeg_attention_decode_solo_items(1536)
+
+
 def test_attention_decode_reports_too_few_splits():
     """A launch with fewer key splits than a token's context needs cannot merge that token's output: the
     kernel says so through the error flag (code 3), writes nothing for the token, leaves its counters at

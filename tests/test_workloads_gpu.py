@@ -83,3 +83,38 @@ def test_256_requests_drawing_with_a_seed_each(models):
         want = plain_lfm2.generate(config, weights, prompts[index], 12, temperature=1.0, top_k=50, top_p=1.0,
                                    repetition_penalty=1.0, seed=index + 1)
         assert result["outputs"][index] == want
+
+
+def test_256_requests_with_a_warp_per_attention_item(models):
+    """The decode attention's form for very many requests with short contexts (one warp a (token, kv head)
+    item), inside the engine: 256 requests on tiny B in bfloat16, greedy, once with that form and once with the
+    four-warp form. Both sum a row's keys in different orders, so a token may differ where two logits are
+    nearly equal: nearly all requests must agree, and every request's first token with the plain model's."""
+    from celeg_b200 import Engine, EngineOptions, RequestOptions, SamplingParams, kernels
+    folder, config, weights = models["B"]
+    rng = np.random.default_rng(62)
+    prompts = [rng.integers(0, config["vocab_size"], size=int(n)).tolist() for n in rng.integers(3, 40, size=256)]
+    options = EngineOptions(max_active_requests=256, max_batched_tokens=1024, prefill_chunk_tokens=64, page_tokens=16)
+    request_options = [RequestOptions(max_new_tokens=10, eos_tokens=(),
+                                      generation=SamplingParams(temperature=0.0, top_k=1, repetition_penalty=1.0))
+                       for _ in prompts]
+    outputs = {}
+    try:
+        for name, items in (("one warp", 1), ("four warps", 1 << 40)):
+            kernels.library().celeg_attention_decode_solo_items(items)
+            engine = Engine(folder, max_context=64, dtype="bfloat16", options=options)
+            result = bench.drive_workload(engine, prompts, request_options)
+            assert not result["errors"]
+            engine.loaded.step.raise_on_device_error()
+            engine.loaded.manager.check_invariants()
+            outputs[name] = result["outputs"]
+            del engine
+    finally:
+        kernels.library().celeg_attention_decode_solo_items(1536)
+    same = sum(1 for a, b in zip(outputs["one warp"], outputs["four warps"]) if a == b)
+    assert same >= 240, same
+    first = 0
+    for index in range(0, 256, 16):
+        want = plain_lfm2.generate(config, weights, prompts[index], 1, eos_tokens=())
+        first += outputs["one warp"][index][:1] == want
+    assert first >= 14, first
