@@ -57,6 +57,28 @@ __device__ __forceinline__ float penalised(const float* logits, const uint8_t* s
     return v;
 }
 
+// The same for tokens token .. token + 3 (token a multiple of 4, logits + token 16-byte aligned, seen + token 4-byte
+// aligned), with the division by the temperature that the callers apply to a score: one operation after the
+// other as for a single token, so that both ways give the same bits.
+__device__ __forceinline__ float4 penalised_quad(const float* logits, const uint8_t* seen, int token, float penalty,
+                                                 bool greedy, float temperature) {
+    float4 v = *reinterpret_cast<const float4*>(logits + token);
+    if (seen && penalty > 1.0f) {
+        const uchar4 marks = *reinterpret_cast<const uchar4*>(seen + token);
+        if (marks.x) v.x = v.x >= 0.0f ? v.x / penalty : v.x * penalty;
+        if (marks.y) v.y = v.y >= 0.0f ? v.y / penalty : v.y * penalty;
+        if (marks.z) v.z = v.z >= 0.0f ? v.z / penalty : v.z * penalty;
+        if (marks.w) v.w = v.w >= 0.0f ? v.w / penalty : v.w * penalty;
+    }
+    if (!greedy) {
+        v.x = v.x / temperature;
+        v.y = v.y / temperature;
+        v.z = v.z / temperature;
+        v.w = v.w / temperature;
+    }
+    return v;
+}
+
 // Order-preserving key of a score: a larger float gives a larger unsigned key. NaN gives 0 and is never a
 // candidate (no comparison with it holds in celeg's selection either).
 __device__ __forceinline__ unsigned score_key(float v) {
@@ -283,12 +305,38 @@ __device__ int select_top_k(SelectShared& sm, const int n, const int k, ScoreAt 
 // every token at or above it leaves a pool of about twice k candidates for the exact selection. A pool that overflows (scores that are equal by the thousand)
 // sends the range to the exact selection over all of it instead. The range is read twice where the plain form
 // reads it k times. Returns how many were found.
-template <typename ScoreOf>
-__device__ int range_top_k(SelectShared& sm, const int begin, const int end, const int k, ScoreOf score_of) {
+template <typename ScoreOf, typename QuadOf>
+__device__ int range_top_k(SelectShared& sm, const int begin, const int end, const int k, ScoreOf score_of,
+                           QuadOf quad_of, const bool quads) {
     constexpr int kBatch = 8;
+    constexpr int kQuads = 4;                            // 16-byte loads in flight per thread and round
+    // with `quads`, the scores of tokens begin + 4 q .. + 3 come from quad_of(begin + 4 q) (16-byte loads of
+    // the logits, 4-byte loads of the seen marks; the same arithmetic per score); the rest one by one
+    const int n4 = quads ? (end - begin) / 4 : 0;
+    const int scalar_begin = begin + 4 * n4;
     float mine = -INFINITY;
     bool any = false;
-    for (int base = begin + threadIdx.x; base < end; base += blockDim.x * kBatch) {
+    for (int q0 = threadIdx.x; q0 < n4; q0 += blockDim.x * kQuads) {
+        float4 v[kQuads];
+#pragma unroll
+        for (int u = 0; u < kQuads; ++u) {
+            const int q = q0 + u * blockDim.x;
+            const float nan = __int_as_float(0x7fc00000);
+            v[u] = q < n4 ? quad_of(begin + 4 * q) : make_float4(nan, nan, nan, nan);
+        }
+#pragma unroll
+        for (int u = 0; u < kQuads; ++u) {
+            const float part[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (part[c] == part[c]) {
+                    mine = any ? fmaxf(mine, part[c]) : part[c];
+                    any = true;
+                }
+            }
+        }
+    }
+    for (int base = scalar_begin + threadIdx.x; base < end; base += blockDim.x * kBatch) {
         float v[kBatch];
 #pragma unroll
         for (int u = 0; u < kBatch; ++u) {
@@ -321,7 +369,30 @@ __device__ int range_top_k(SelectShared& sm, const int begin, const int end, con
     __syncthreads();
     if (threadIdx.x == 0) sm.pool_count = 0u;
     __syncthreads();
-    for (int base = begin + threadIdx.x; base < end; base += blockDim.x * kBatch) {
+    for (int q0 = threadIdx.x; q0 < n4; q0 += blockDim.x * kQuads) {
+        float4 v[kQuads];
+#pragma unroll
+        for (int u = 0; u < kQuads; ++u) {
+            const int q = q0 + u * blockDim.x;
+            const float nan = __int_as_float(0x7fc00000);
+            v[u] = q < n4 ? quad_of(begin + 4 * q) : make_float4(nan, nan, nan, nan);
+        }
+#pragma unroll
+        for (int u = 0; u < kQuads; ++u) {
+            const float part[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (part[c] >= bound) {
+                    const unsigned at = atomicAdd(&sm.pool_count, 1u);
+                    if (at < (unsigned)kSelectPool) {
+                        sm.pool_score[at] = part[c];
+                        sm.pool_token[at] = begin + 4 * (q0 + u * (int)blockDim.x) + c;
+                    }
+                }
+            }
+        }
+    }
+    for (int base = scalar_begin + threadIdx.x; base < end; base += blockDim.x * kBatch) {
         float v[kBatch];
 #pragma unroll
         for (int u = 0; u < kBatch; ++u) {
@@ -431,7 +502,9 @@ __global__ void sample_kernel(const float* logits, long long ld, int vocab,
         if (!r.greedy) v = v / r.temperature;
         return v;
     };
-    const int found = range_top_k(sm, 0, vocab, r.k, score_of);
+    auto quad_of = [&](int token) { return penalised_quad(r.logits, r.seen, token, r.penalty, r.greedy, r.temperature); };
+    const bool quads = (((size_t)r.logits) & 15) == 0 && (r.seen == nullptr || (((size_t)r.seen) & 3) == 0);
+    const int found = range_top_k(sm, 0, vocab, r.k, score_of, quad_of, quads);
     if (threadIdx.x != 0) return;
     const int chosen = draw_from_sorted(sm, found, r.greedy, top_p ? top_p[row] : 1.0f, rng ? rng + r.slot : nullptr);
     out[row] = chosen;
@@ -455,9 +528,12 @@ __global__ void sample_chunks_kernel(const float* logits, long long ld, int voca
         if (!r.greedy) v = v / r.temperature;
         return v;
     };
+    auto quad_of = [&](int token) { return penalised_quad(r.logits, r.seen, token, r.penalty, r.greedy, r.temperature); };
+    const bool quads = (((size_t)r.logits) & 15) == 0 && (r.seen == nullptr || (((size_t)r.seen) & 3) == 0);
     const int per = (vocab + chunks - 1) / chunks;
     const int begin = min(vocab, chunk * per), end = min(vocab, begin + per);
-    const int found = end > begin ? range_top_k(sm, begin, end, min(r.k, end - begin), score_of) : 0;
+    const int found = end > begin ? range_top_k(sm, begin, end, min(r.k, end - begin), score_of, quad_of,
+                                                quads && (begin & 3) == 0) : 0;
     const size_t base = ((size_t)row * chunks + chunk) * kMaxTopK;
     for (int i = threadIdx.x; i < found; i += blockDim.x) {
         part_score[base + i] = sm.sorted_score[i];
