@@ -241,6 +241,75 @@ __device__ __forceinline__ void short_conv_spans_body(const A* proj, const float
     }
 }
 
+// A step in which every request brings one token (many requests decoding), bfloat16, at most kFewTaps taps: a
+// thread serves eight neighbouring channels of one request with 16-byte loads (the span kernel's decoded-token
+// path loads two bytes at a time). The same arithmetic in the same order per channel, so the same bits.
+__global__ void __launch_bounds__(128)
+short_conv_decode_bf16x8_kernel(const __nv_bfloat16* proj, const float* __restrict__ kernel, float* state,
+                                long long slot_stride, __nv_bfloat16* out, const int* span_begin, const int* span_slot,
+                                int hidden, int taps) {
+    chain_release();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= hidden) return;
+    const int keep = taps - 1;
+    float w[8][kFewTaps];                           // constant data first
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int tap = 0; tap < kFewTaps; ++tap) w[j][tap] = tap < taps ? kernel[(size_t)(c + j) * taps + tap] : 0.0f;
+    chain_wait();
+    const int s = blockIdx.y;
+    const int t = span_begin[s];
+    float* st = state + (size_t)span_slot[s] * slot_stride + c;      // [keep][hidden]
+    const __nv_bfloat16* p = proj + (size_t)t * 3 * hidden + c;
+    const uint4 b_raw = *reinterpret_cast<const uint4*>(p);
+    const uint4 c_raw = *reinterpret_cast<const uint4*>(p + hidden);
+    const uint4 x_raw = *reinterpret_cast<const uint4*>(p + 2 * hidden);
+    float old_taps[kFewTaps - 1][8];
+#pragma unroll
+    for (int tap = 0; tap < kFewTaps - 1; ++tap) {
+        float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
+        if (tap < keep) {
+            lo = *reinterpret_cast<const float4*>(st + (size_t)tap * hidden);
+            hi = *reinterpret_cast<const float4*>(st + (size_t)tap * hidden + 4);
+        }
+        old_taps[tap][0] = lo.x; old_taps[tap][1] = lo.y; old_taps[tap][2] = lo.z; old_taps[tap][3] = lo.w;
+        old_taps[tap][4] = hi.x; old_taps[tap][5] = hi.y; old_taps[tap][6] = hi.z; old_taps[tap][7] = hi.w;
+    }
+    const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b_raw);
+    const __nv_bfloat16* cc = reinterpret_cast<const __nv_bfloat16*>(&c_raw);
+    const __nv_bfloat16* xx = reinterpret_cast<const __nv_bfloat16*>(&x_raw);
+    float bx[8];
+    uint4 packed;
+    __nv_bfloat16* result = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        bx[j] = to_float(bb[j]) * to_float(xx[j]);
+        float conv = 0.0f;
+#pragma unroll
+        for (int tap = 0; tap < kFewTaps; ++tap) {
+            if (tap < keep) conv += w[j][tap] * old_taps[tap < kFewTaps - 1 ? tap : 0][j];
+            else if (tap == keep) conv += w[j][tap] * bx[j];
+        }
+        result[j] = from_float<__nv_bfloat16>(to_float(cc[j]) * conv);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * hidden + c) = packed;
+#pragma unroll
+    for (int tap = 0; tap < kFewTaps - 1; ++tap) {
+        if (tap + 1 < keep) {
+            *reinterpret_cast<float4*>(st + (size_t)tap * hidden) =
+                make_float4(old_taps[tap + 1 < kFewTaps - 1 ? tap + 1 : 0][0], old_taps[tap + 1 < kFewTaps - 1 ? tap + 1 : 0][1],
+                            old_taps[tap + 1 < kFewTaps - 1 ? tap + 1 : 0][2], old_taps[tap + 1 < kFewTaps - 1 ? tap + 1 : 0][3]);
+            *reinterpret_cast<float4*>(st + (size_t)tap * hidden + 4) =
+                make_float4(old_taps[tap + 1 < kFewTaps - 1 ? tap + 1 : 0][4], old_taps[tap + 1 < kFewTaps - 1 ? tap + 1 : 0][5],
+                            old_taps[tap + 1 < kFewTaps - 1 ? tap + 1 : 0][6], old_taps[tap + 1 < kFewTaps - 1 ? tap + 1 : 0][7]);
+        } else if (tap + 1 == keep) {
+            *reinterpret_cast<float4*>(st + (size_t)tap * hidden) = make_float4(bx[0], bx[1], bx[2], bx[3]);
+            *reinterpret_cast<float4*>(st + (size_t)tap * hidden + 4) = make_float4(bx[4], bx[5], bx[6], bx[7]);
+        }
+    }
+}
+
 template <typename A>
 __global__ void short_conv_spans_kernel(const A* proj, const float* __restrict__ kernel, float* state,
                                         long long slot_stride, A* out, const int* span_begin, const int* span_slot,
@@ -305,6 +374,16 @@ CELEG_API int celeg_short_conv(const void* proj, const float* kernel, float* sta
                            tokens, spans, span_blocks_x, window_blocks_x);
             return check_launch("short_conv (prompt portions)");
         }
+    }
+    if (act_dtype == kBFloat16 && max_span == 1 && tokens == spans && spans >= 16 && taps >= 2 && taps <= kFewTaps &&
+        hidden % 8 == 0 && (slot_stride & 3) == 0 &&
+        ((((size_t)proj) | ((size_t)out) | ((size_t)state) | ((size_t)kernel)) & 15) == 0) {
+        // every request brings one token, and there are many of them: eight channels a thread
+        const int vec_threads = hidden / 8 >= 128 ? 128 : ((hidden / 8 + 31) / 32) * 32;
+        dim3 grid((hidden / 8 + vec_threads - 1) / vec_threads, spans);
+        launch_chained(short_conv_decode_bf16x8_kernel, grid, vec_threads, 0, stream, (const __nv_bfloat16*)proj, kernel,
+                       state, slot_stride, (__nv_bfloat16*)out, span_begin, span_slot, hidden, taps);
+        return check_launch("short_conv (decoded tokens)");
     }
     const int threads = hidden >= 256 ? 256 : ((hidden + 31) / 32) * 32;
     dim3 span_grid((hidden + threads - 1) / threads, spans);
