@@ -65,6 +65,17 @@ static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t stream) 
 
 using namespace celeg_b200;
 
+static int device_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
 static long long g_decode_solo_items = 1536;     // (measured: level with the four-warp form at 1,024 items, ahead from 2,048)
 
 // For measurements: from how many (token, kv head) items on a launch of short contexts gives a warp an item.
@@ -140,12 +151,14 @@ static int attention_decode_checked(const void* q, int q_row_stride, void* out, 
     p.k_cache_w = (__nv_bfloat16*)const_cast<void*>(k_cache);
     p.v_cache_w = (__nv_bfloat16*)const_cast<void*>(v_cache);
     dim3 grid(max_splits, kv_heads, tokens);
-    // Short contexts (an item has at most two tiles of keys per warp): a block with one stage of 32 keys per warp
-    // needs half the shared memory, so twice as many items run at a time; their start and their merge, not
-    // their keys, are what such a launch consists of.
-    const bool few_keys = chunk <= 256;
+    // Short contexts (an item has at most two tiles of keys per warp), or more items than the SMs hold at three a
+    // time: a block with one stage of 32 keys per warp needs half the shared memory, so more items run at a
+    // time, which is worth more than a warp's next tile arriving under its current one (measured at 64
+    // requests: 22.6 -> 18.5 us at 540 keys, 184 -> 173 us at 8,000; at 8 requests of 8,000 keys 42 -> 33 us;
+    // with 256 items and fewer the two-stage form is ahead).
+    const bool few_keys = chunk <= 256 || (long long)tokens * kv_heads * max_splits >= 3LL * device_sms();
     // ... and with very many such items (one split each) a warp serves an item alone
-    if (few_keys && max_splits == 1 && (head_dim & 1) == 0 && (long long)tokens * kv_heads >= g_decode_solo_items) {
+    if (chunk <= 256 && max_splits == 1 && (head_dim & 1) == 0 && (long long)tokens * kv_heads >= g_decode_solo_items) {
         if (head_dim <= 64) return launch_decode_solo<64>(p, tokens, stream);
         if (head_dim <= 128) return launch_decode_solo<128>(p, tokens, stream);
     }
