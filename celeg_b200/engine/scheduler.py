@@ -288,10 +288,10 @@ class Scheduler:
         self._inflight = None
         started = clock()
         continuing = self._may_run_ahead(plan)
-        after = self._plan_after(plan, continuing) if continuing else None
+        after = self._plan_after(plan, continuing) if continuing else self._plan_ahead_of_portions(plan)
         metrics.host_plan_seconds += clock() - started
         if after is not None:
-            self._launch(after, tokens_on_device=True)
+            self._launch(after, tokens_on_device=after.ahead)
         progressed = self._collect(plan, handle)
         started = clock()
         self._hold_admission = False
@@ -467,6 +467,92 @@ class Scheduler:
         row_of = {id(p): row for row, p in enumerate(plan.entries)}
         after.entries = [PlannedEntry(p.request, [0], samples=True, is_decode=True) for p in continuing]
         after.source_rows = [row_of[id(p)] for p in continuing]
+        return after
+
+    def _plan_ahead_of_portions(self, plan: Plan) -> Optional[Plan]:
+        """The step after a ``plan`` that holds prompt portions, made before the tokens of ``plan`` are known, so
+        that the device does not wait while the host reads them, decides and plans. What the step after looks like
+        does not depend on those tokens (an end-of-sequence token aside, see :meth:`step`): a request whose prompt
+        ``plan`` completes, or which decodes in it, decodes next, with the token that ``plan`` leaves on the device
+        in its row of the draw; one that reaches ``max_new_tokens`` with that token is gone; a prompt goes on
+        from where ``plan`` leaves it. The requests are read, not changed: ``plan`` is committed later. None when
+        anything is in the way (requests waiting, cancellations, pages that may run short, a decoding request
+        that ``plan`` left out): the step after is then planned the usual way, after the tokens."""
+        if not self._runs_ahead or self.queue or plan.skipped_for_pages:
+            return None
+        options = self.options
+        decoding_next: Dict[int, int] = {}              # request id -> its row in the draw of ``plan``
+        offset_after: Dict[int, int] = {}               # request id -> prefill offset when ``plan`` is done
+        planned = set()
+        row = 0
+        for entry in plan.entries:
+            request = entry.request
+            if request.cancel_requested:
+                return None
+            if request.cache is None:
+                if request.status.terminal:
+                    row += 1 if entry.samples else 0
+                    continue                               # ended while this step was in flight
+                return None
+            planned.add(request.id)
+            if entry.samples:
+                if len(request.generated) + 2 <= request.options.max_new_tokens:
+                    decoding_next[request.id] = row        # (else: this step's token is its last)
+                row += 1
+            else:
+                offset_after[request.id] = request.prefill_offset + len(entry.tokens)
+        after = Plan()
+        budget = options.max_batched_tokens
+        free = [group.pool.free_pages for group in self.manager.groups]
+
+        def takes(cache, count) -> bool:
+            nonlocal free
+            if cache.tokens + count > self.max_context:
+                return False
+            if cache.tokens + count > cache.capacity:
+                needed = self.manager.pages_needed(cache, cache.tokens + count)
+                if any(n > f for n, f in zip(needed, free)):
+                    return False
+                free = [f - n for f, n in zip(free, needed)]
+            return True
+
+        ordered = sorted(self.live, key=self._priority_key)
+        source_rows: List[int] = []
+        prefilling = []
+        for request_id in ordered:
+            request = self.requests[request_id]
+            if request.cancel_requested or request.cache is None:
+                return None
+            if request_id in decoding_next:
+                if budget <= 0 or not takes(request.cache, 1):
+                    return None
+                after.entries.append(PlannedEntry(request, [0], samples=True, is_decode=True))
+                source_rows.append(decoding_next[request_id])
+                budget -= 1
+            elif request_id in planned and request_id not in offset_after:
+                continue                                   # ends with this step's token
+            elif request.status is RequestStatus.DECODING:
+                return None                                # decodes, but ``plan`` left it out: its token is on the host
+            else:
+                prefilling.append(request)
+        if prefilling and after.entries and self._padded_singles is not None:
+            budget = min(budget, options.max_batched_tokens - self._padded_singles(len(after.entries)))
+        for request in prefilling:
+            offset = offset_after.get(request.id, request.prefill_offset)
+            remaining = len(request.feed) - offset
+            count = min(remaining, options.prefill_chunk_tokens, budget)
+            if count <= 0:
+                continue
+            if not takes(request.cache, count):
+                return None
+            after.entries.append(PlannedEntry(request, request.feed[offset:offset + count],
+                                              samples=(count == remaining), is_decode=False))
+            budget -= count
+        if not after.entries:
+            return None
+        if source_rows:
+            after.ahead = True                             # its leading single tokens are on the device
+            after.source_rows = source_rows
         return after
 
     def _collect(self, plan: Plan, handle) -> bool:

@@ -133,8 +133,9 @@ class StepFunction:
             token_source: Optional[torch.Tensor] = None, source_rows: Optional[Sequence[int]] = None) -> torch.Tensor:
         """Returns float32 logits [wanted, vocab] in the order of the entries and of ``want``.
         The tensor is a view of a buffer that the next call overwrites. ``token_source`` (int32, on the device):
-        the entries' tokens are placeholders, token i of the step is ``token_source[source_rows[i]]``
-        (``token_source[i]`` without ``source_rows``)."""
+        without ``source_rows`` the entries' tokens are placeholders and token i of the step is ``token_source[i]``;
+        with them the single tokens at the head of the step are placeholders, token i < len(source_rows) is
+        ``token_source[source_rows[i]]``, and the other entries carry their tokens."""
         started = time.perf_counter()
         vocab = self.model.vocab_size
         if not entries:
@@ -242,17 +243,22 @@ class StepFunction:
         if token_source is not None:
             # the tokens of this step are on the device already (what the step before drew): token i of
             # the step is token_source[i]; the entries carry placeholders
-            if token_source.dtype != torch.int32 or token_source.numel() < total:
+            if token_source.dtype != torch.int32 or (source_rows is None and token_source.numel() < total):
                 raise StepInputError("a token source must hold one int32 token for every token of the step")
             if source_rows is None:
                 if token_source.numel() < step.tokens:
                     raise StepInputError("a token source must hold one int32 token for every row of the step")
                 tokens_from = token_source              # copied by _forward: inside the step's graph, if it has one
             else:
-                if len(source_rows) != total or min(source_rows) < 0 or max(source_rows) >= token_source.numel():
-                    raise StepInputError("source rows must name one row of the token source for every token")
+                # the first len(source_rows) tokens of the step (single tokens at its head) come from the device,
+                # the others are what the entries carry
+                count = len(source_rows)
+                if (count > total or min(source_rows) < 0 or max(source_rows) >= token_source.numel()
+                        or any(len(entry.tokens) != 1 for entry in entries[:count])):
+                    raise StepInputError("source rows must name a row of the token source for each of the single "
+                                         "tokens at the head of the step")
                 # (the rows travel behind the step's metadata in the same pinned buffer and the same copy)
-                torch.index_select(token_source, 0, self._dev[n_words:n_words + total], out=step.token_ids[:total])
+                torch.index_select(token_source, 0, self._dev[n_words:n_words + count], out=step.token_ids[:count])
         event = torch.cuda.Event()
         event.record()
         self._ring_events[slot] = event

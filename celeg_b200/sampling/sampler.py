@@ -24,6 +24,10 @@ class Sampler:
         # staging: [slot | top_k] int32 and [temperature | top_p | penalty] float32, one copy each
         self._host_i = torch.empty(2 * max_rows, dtype=torch.int32).pin_memory()
         self._host_f = torch.empty(3 * max_rows, dtype=torch.float32).pin_memory()
+        self._stage_ring = [(self._host_i, self._host_f, None)] + [
+            (torch.empty(2 * max_rows, dtype=torch.int32).pin_memory(),
+             torch.empty(3 * max_rows, dtype=torch.float32).pin_memory(), None) for _ in range(3)]
+        self._stage_next = 0
         self._dev_i = torch.zeros(2 * max_rows, dtype=torch.int32, device=device)
         self._dev_f = torch.zeros(3 * max_rows, dtype=torch.float32, device=device)
         self.out = torch.zeros(max_rows, dtype=torch.int32, device=device)
@@ -73,8 +77,8 @@ class Sampler:
     def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[int, SamplingParams]], also_copy=None):
         """Enqueues the draw and the copy of the tokens to pinned host memory; :meth:`read` returns
         them. ``self.out[:len(rows)]`` holds them on the device until the next launch (a following step
-        may take its input tokens from there). At most two launches may be unread at a time, and the
-        rows or their options may change only when none is. ``also_copy`` = (pinned host tensor, device
+        may take its input tokens from there). At most two launches may be unread at a time; the rows and
+        their options may change from launch to launch. ``also_copy`` = (pinned host tensor, device
         tensor): copied along with the tokens (a step's error flag), there when :meth:`read` returns."""
         count = len(rows)
         if count == 0:
@@ -92,17 +96,26 @@ class Sampler:
         signature = self._staged if rows is self._staged_rows else tuple((slot, params) for slot, params in rows)
         self._staged_rows = rows
         if signature is not self._staged and signature != self._staged:
-            # the rows or their options changed: stage them again (the copies of the last staging have
-            # long been consumed: every call ends with a synchronisation)
-            hi, hf = self._host_i.numpy(), self._host_f.numpy()
+            # the rows or their options changed: stage them again. Launches are not waited for one by one (a
+            # scheduler enqueues a step before it reads the one before), so the pinned buffers form a ring: one
+            # is written again only when the copy that read it last has left.
+            index = self._stage_next
+            self._stage_next = (index + 1) % len(self._stage_ring)
+            host_i, host_f, copied = self._stage_ring[index]
+            if copied is not None:
+                copied.synchronize()
+            hi, hf = host_i.numpy(), host_f.numpy()
             for i, (slot, params) in enumerate(rows):
                 hi[i] = slot
                 hi[m + i] = params.top_k
                 hf[i] = params.temperature
                 hf[m + i] = params.top_p
                 hf[2 * m + i] = params.repetition_penalty
-            self._dev_i.copy_(self._host_i, non_blocking=True)
-            self._dev_f.copy_(self._host_f, non_blocking=True)
+            self._dev_i.copy_(host_i, non_blocking=True)
+            self._dev_f.copy_(host_f, non_blocking=True)
+            copied = torch.cuda.Event()
+            copied.record()
+            self._stage_ring[index] = (host_i, host_f, copied)
             self._staged = signature
             self._all_greedy = all(params.greedy for _, params in rows)
         if self._copied is not None:

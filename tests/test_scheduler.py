@@ -262,7 +262,8 @@ class AheadRunner(FakeRunner):
             self.fail_next = False
             raise RuntimeError("injected step failure")
         assert len(self.pending) <= 1, "more than two steps in flight"
-        assert source_rows is None or (tokens_on_device and len(source_rows) == len(entries))
+        assert source_rows is None or (tokens_on_device and len(source_rows) <= len(entries) and
+                                       all(len(e.tokens) == 1 for e in entries[:len(source_rows)]))
         rows = []
         for entry in entries:
             cache = self.manager.get(entry.request_id)
@@ -272,7 +273,7 @@ class AheadRunner(FakeRunner):
         handle = {"rows": rows, "from_device": tokens_on_device, "after": self.pending[-1] if self.pending else None,
                   "source": list(source_rows) if source_rows is not None else None}
         self.pending.append(handle)
-        self.log.append(("launch", tokens_on_device, [r[0] for r in rows]))
+        self.log.append(("launch", tokens_on_device, [r[0] for r in rows], [len(r[2]) for r in rows]))
         return handle
 
     def collect(self, handle):
@@ -287,7 +288,7 @@ class AheadRunner(FakeRunner):
                 source = list(range(len(before)))
         out = []
         for index, (request_id, slot, tokens, want) in enumerate(handle["rows"]):
-            if handle["from_device"]:
+            if handle["from_device"] and index < len(source):
                 tokens = [before[source[index]]]
             self.history[slot].extend(tokens)
             if want:
@@ -335,6 +336,36 @@ def test_run_ahead_drops_the_token_after_an_end_of_sequence():
     assert scheduler.status(request_id) is RequestStatus.FINISHED
     assert not runner.pending and manager.free_slots == 4
     manager.check_invariants()
+
+
+def test_run_ahead_across_steps_with_prompt_portions():
+    """Prompts of several portions beside decoding requests: the step after such a step is enqueued before its
+    tokens are read too (the decoding rows take their tokens from the device, the portions theirs from the
+    host), a request whose prompt ends in a step decodes in the step after with that step's token, and one that
+    ends is left out. Same outputs as without running ahead."""
+    prompts = [list(range(1, 30)), [9, 1], list(range(40, 63)), [6, 7, 8], list(range(5, 19))]
+    news = [6, 14, 3, 9, 1]
+    outputs = {}
+    for run_ahead in (False, True):
+        scheduler, runner, manager = make_ahead(slots=5, pages=64, run_ahead=run_ahead)
+        ids = [scheduler.submit(p, RequestOptions(max_new_tokens=n, eos_tokens=())) for p, n in zip(prompts, news)]
+        run_all(scheduler)
+        outputs[run_ahead] = [scheduler.poll(i).tokens for i in ids]
+        assert not runner.pending and manager.free_slots == 5
+        manager.check_invariants()
+        if run_ahead:
+            # launches that were enqueued while the step before was still uncollected, and held a prompt portion
+            waiting, early = 0, 0
+            for entry in runner.log:
+                if entry[0] == "launch":
+                    early += 1 if waiting >= 1 and any(count > 1 for count in entry[3]) else 0
+                    waiting += 1
+                else:
+                    waiting -= 1
+            assert early >= 4, runner.log
+    for prompt, n, got in zip(prompts, news, outputs[True]):
+        assert got == expected_output(prompt, n, eos=())
+    assert outputs[True] == outputs[False]
 
 
 def test_portions_leave_room_for_the_rows_a_runner_pads_decoded_tokens_to():
