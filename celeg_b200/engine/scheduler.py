@@ -55,7 +55,7 @@ class EngineOptions:
     page_tokens: int = 16
     logical_kv_pages: int = 0                    # 0: ceil(max_context / page_tokens) * max_active_requests
     scheduler_policy: SchedulerPolicy = SchedulerPolicy.GUARANTEED_NO_EVICT
-    # while every live request decodes, enqueue the step after the one whose tokens are being read (not in celeg)
+    # enqueue the step after the one whose tokens are being read whenever it does not depend on them (not in celeg)
     run_ahead: bool = True
 
     def validate(self) -> None:
@@ -262,11 +262,13 @@ class Scheduler:
         """One engine step: admit, run one batch, accept tokens, admit again. Returns whether
         anything advanced.
 
-        When every live request is decoding and none can end this step except by an end-of-sequence
-        token, the step after is enqueued before this step's tokens are waited for: it takes its
-        input tokens from the device, where this step's draw left them, so the GPU does not idle
-        while the host reads tokens, decides and plans. A request that did end on this step's token
-        has then one more position computed in vain; its token of that step is dropped."""
+        Whenever nothing is in the way (requests waiting, cancellations, pages that may run short), the step
+        after is enqueued before this step's tokens are waited for: what it consists of does not depend on
+        them. Its decoding rows take their input tokens from the device, where this step's draw left them, its
+        prompt portions from the host; a request that reaches ``max_new_tokens`` with this step's token is
+        left out. So the GPU does not idle while the host reads tokens, decides and plans. A request that
+        ended on an end-of-sequence token of this step has then one more position computed in vain; its
+        token of that step is dropped."""
         metrics = self.metrics
         clock = time.perf_counter
         if self._inflight is None:
