@@ -355,7 +355,7 @@ class StepFunction:
         if (single_rows + padded_tokens > self.buffer_tokens or spans > self.span_capacity
                 or logit_rows > self.span_capacity
                 or single_rows - singles > PADDING_TOKENS - PROMPT_TOKEN_STEP
-                or spare > self.storage.scratch_page_count * self.page_tokens):
+                or spare > min(self.storage.scratch_page_count, self.max_pages) * self.page_tokens):     # (a table row holds max_pages)
             return None
         key = ("padded prompt", single_rows, len(portions), padded_tokens, logit_rows, _context_bucket(max_ctx))
         if key not in self._graphs:

@@ -118,3 +118,55 @@ def test_256_requests_with_a_warp_per_attention_item(models):
         want = plain_lfm2.generate(config, weights, prompts[index], 1, eos_tokens=())
         first += outputs["one warp"][index][:1] == want
     assert first >= 14, first
+
+
+@pytest.mark.parametrize("name,seed", [("A", 0), ("A", 1), ("A", 12), ("B", 0), ("B", 5), ("B", 13)])
+def test_random_requests_under_random_engine_options(models, name, seed):
+    """Options drawn at random (policy, live requests, token budget, portion size, page size down to 4 tokens,
+    pool size down to little more than one request) with a context limit of 96 tokens, so that a table row holds
+    fewer pages than a padded launch shape's spare portion may want; requests of random lengths, greedy or drawing
+    with a seed, some ending on a token, submitted a few at a time while the engine steps. Every request's output
+    against the plain implementation."""
+    import random
+    from celeg_b200 import Engine, EngineOptions, RequestOptions, SamplingParams
+    from celeg_b200.engine.scheduler import SchedulerPolicy
+    folder, config, weights = models[name]
+    rng = random.Random(seed * 7 + (1 if name == "B" else 0))
+    policy = rng.choice([SchedulerPolicy.GUARANTEED_NO_EVICT, SchedulerPolicy.MAX_UTILIZATION])
+    max_active = rng.choice([2, 4, 8, 12])
+    page_tokens = rng.choice([4, 8, 16])
+    pools = [0, max(12, 90 // page_tokens * max_active // 2), 96 // page_tokens + rng.randint(1, 12)]
+    options = EngineOptions(max_active_requests=max_active, max_batched_tokens=rng.choice([16, 24, 48, 96]),
+                            prefill_chunk_tokens=rng.choice([4, 7, 16, 32]), page_tokens=page_tokens,
+                            logical_kv_pages=rng.choice(pools), scheduler_policy=policy)
+    engine = Engine(folder, max_context=96, dtype="float32", options=options)
+    requests = []
+    for _ in range(rng.randint(10, 24)):
+        prompt = [rng.randrange(config["vocab_size"]) for _ in range(rng.randint(1, 50))]
+        new = rng.randint(1, 24)
+        if rng.random() < 0.5:
+            params = dict(temperature=0.8, top_k=rng.choice([5, 50]), top_p=rng.choice([1.0, 0.9]),
+                          repetition_penalty=rng.choice([1.0, 1.2]), seed=rng.randint(1, 1000))
+        else:
+            params = dict(temperature=0.0, top_k=1, top_p=1.0, repetition_penalty=1.0, seed=1)
+        free = plain_lfm2.generate(config, weights, prompt, new, eos_tokens=(), **params)
+        eos = (free[rng.randrange(len(free))],) if rng.random() < 0.3 else ()
+        want = plain_lfm2.generate(config, weights, prompt, new, eos_tokens=eos, **params)
+        requests.append((prompt, RequestOptions(max_new_tokens=new, eos_tokens=eos,
+                                                generation=SamplingParams(**params)), want))
+    submitted, pending, steps = [], list(range(len(requests))), 0
+    while pending or engine.scheduler.has_work():
+        for _ in range(rng.randint(0, 3)):
+            if pending:
+                index = pending.pop(0)
+                submitted.append((index, engine.submit(requests[index][0], requests[index][1])))
+        engine.step()
+        steps += 1
+        assert steps < 5000
+    for index, request_id in submitted:
+        result = engine.poll(request_id)
+        assert engine.status(request_id).value == "finished", (index, result.error)
+        assert result.tokens == requests[index][2], index
+    engine.loaded.step.raise_on_device_error()
+    engine.loaded.manager.check_invariants()
+    assert engine.loaded.manager.free_slots == max_active
