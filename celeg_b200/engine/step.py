@@ -143,61 +143,26 @@ class StepFunction:
         if len(entries) > self.max_spans:
             raise StepInputError(f"{len(entries)} requests in one step, the limit is {self.max_spans}")
         checked_entries = self._check_single_tokens(entries, auto_begin) if len(entries) >= 8 else None
-        if checked_entries is not None:
-            caches, wanted = checked_entries
-            total = len(entries)
-            counts = [1] * total
-        else:
-            seen_ids = set()
-            total = 0
-            wanted = 0
-            caches = []
-            counts = []
-            find = self.manager.find
-            for entry in entries:
-                request_id = entry.request_id
-                if request_id in seen_ids:
-                    raise StepInputError(f"request {request_id!r} appears twice in one step")
-                seen_ids.add(request_id)
-                tokens = entry.tokens
-                count = len(tokens)
-                if count == 1:
-                    low = high = int(tokens[0])
-                elif count == 0:
-                    raise StepInputError(f"request {request_id!r} brings no tokens")
-                else:
-                    if not isinstance(tokens, np.ndarray):
-                        tokens = entry.tokens = np.asarray(tokens, dtype=np.int64)
-                    low, high = int(tokens.min()), int(tokens.max())
-                if low < 0 or high >= vocab:
-                    bad = low if low < 0 else high
-                    raise StepInputError(f"request {request_id!r}: token id {bad} is outside the "
-                                         f"vocabulary of {vocab}")
-                for place in entry.want:
-                    if not 0 <= int(place) < count:
-                        raise StepInputError(f"request {request_id!r}: wanted place {place} is outside its "
-                                             f"{count} tokens")
-                cache = find(request_id)
-                if cache is None:
-                    if not auto_begin:
-                        raise StepInputError(f"request {request_id!r} was not begun") from None
-                    cache = self.manager.open(request_id)
-                if cache.tokens + count > self.max_context:
-                    raise StepInputError(f"request {request_id!r} would reach {cache.tokens + count} positions, "
-                                         f"the context limit is {self.max_context}")
-                caches.append(cache)
-                counts.append(count)
-                total += count
-                wanted += len(entry.want)
-        if total > self.max_tokens:
-            raise StepInputError(f"{total} tokens in one step, the limit is {self.max_tokens}")
-
-        # pages for the whole batch, all or nothing
-        need = self.manager.pages_needed_each(caches, counts)
-        for g, group in enumerate(self.manager.groups):
-            if need[g] > group.pool.free_pages:
-                raise OutOfPages(f"the step needs {need[g]} more page(s) of group {group.key}, "
-                                 f"{group.pool.free_pages} free")
+        opened: List[Hashable] = []               # requests that this step begins: ended again if it is refused
+        try:
+            if checked_entries is not None:
+                caches, wanted = checked_entries
+                total = len(entries)
+                counts = [1] * total
+            else:
+                caches, counts, total, wanted = self._check_entries(entries, auto_begin, opened)
+            if total > self.max_tokens:
+                raise StepInputError(f"{total} tokens in one step, the limit is {self.max_tokens}")
+            # pages for the whole batch, all or nothing
+            need = self.manager.pages_needed_each(caches, counts)
+            for g, group in enumerate(self.manager.groups):
+                if need[g] > group.pool.free_pages:
+                    raise OutOfPages(f"the step needs {need[g]} more page(s) of group {group.key}, "
+                                     f"{group.pool.free_pages} free")
+        except (StepInputError, OutOfPages):
+            for request_id in opened:
+                self.manager.close(request_id)
+            raise
         self.manager.reserve_each(caches, counts)
 
         spans = len(entries)
@@ -296,6 +261,54 @@ class StepFunction:
             return max(0, singles)
         rows = next((n for n in (16, 32, 64) if n >= singles), (singles + 31) // 32 * 32)
         return rows if rows <= self.max_spans else self._graph_rows(singles)
+
+    def _check_entries(self, entries, auto_begin: bool, opened: list):
+        """The checks of :meth:`run`, request by request. Returns (caches, counts, total, wanted); a request that
+        ``auto_begin`` opens here is added to ``opened``."""
+        vocab = self.model.vocab_size
+        seen_ids = set()
+        total = 0
+        wanted = 0
+        caches = []
+        counts = []
+        find = self.manager.find
+        for entry in entries:
+            request_id = entry.request_id
+            if request_id in seen_ids:
+                raise StepInputError(f"request {request_id!r} appears twice in one step")
+            seen_ids.add(request_id)
+            tokens = entry.tokens
+            count = len(tokens)
+            if count == 1:
+                low = high = int(tokens[0])
+            elif count == 0:
+                raise StepInputError(f"request {request_id!r} brings no tokens")
+            else:
+                if not isinstance(tokens, np.ndarray):
+                    tokens = entry.tokens = np.asarray(tokens, dtype=np.int64)
+                low, high = int(tokens.min()), int(tokens.max())
+            if low < 0 or high >= vocab:
+                bad = low if low < 0 else high
+                raise StepInputError(f"request {request_id!r}: token id {bad} is outside the "
+                                     f"vocabulary of {vocab}")
+            for place in entry.want:
+                if not 0 <= int(place) < count:
+                    raise StepInputError(f"request {request_id!r}: wanted place {place} is outside its "
+                                         f"{count} tokens")
+            cache = find(request_id)
+            if cache is None:
+                if not auto_begin:
+                    raise StepInputError(f"request {request_id!r} was not begun") from None
+                cache = self.manager.open(request_id)
+                opened.append(request_id)
+            if cache.tokens + count > self.max_context:
+                raise StepInputError(f"request {request_id!r} would reach {cache.tokens + count} positions, "
+                                     f"the context limit is {self.max_context}")
+            caches.append(cache)
+            counts.append(count)
+            total += count
+            wanted += len(entry.want)
+        return caches, counts, total, wanted
 
     def _check_single_tokens(self, entries, auto_begin: bool):
         """The checks of :meth:`run` for a step in which every request brings one token, over whole lists

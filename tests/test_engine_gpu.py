@@ -184,6 +184,7 @@ def test_step_input_errors_name_the_request(models):
 def test_out_of_pages_leaves_everything_as_it_was(models):
     from celeg_b200 import Engine, EngineOptions, StepEntry
     from celeg_b200.cache import OutOfPages
+    from celeg_b200.engine.step import StepInputError
     folder, config, weights = models["A"]
     engine = Engine(folder, dtype="float32", options=EngineOptions(logical_kv_pages=3, max_active_requests=2))
     sequence = prompts_of(config["vocab_size"], [40], seed=26)[0]
@@ -192,6 +193,10 @@ def test_out_of_pages_leaves_everything_as_it_was(models):
         engine.forward([StepEntry("a", sequence[30:32], []), StepEntry("b", sequence[:20], [])])
     engine.loaded.manager.check_invariants()
     assert engine.loaded.manager.get("a").tokens == 30
+    assert engine.loaded.manager.find("b") is None and engine.loaded.manager.free_slots == 1   # "b" was not begun
+    with pytest.raises(StepInputError, match="context"):             # nor is a request that a faulty step names
+        engine.forward([StepEntry("c", sequence[:2], []), StepEntry("a", [1] * 300, [])])
+    assert engine.loaded.manager.find("c") is None and engine.loaded.manager.free_slots == 1
     got = engine.forward([StepEntry("a", sequence[30:40], [9])])[0].cpu().numpy()
     want = plain_lfm2.forward(config, weights, sequence)[39]
     assert np.abs(got - want).max() < 2e-4
@@ -1594,3 +1599,92 @@ def test_steps_of_changing_mix_are_padded_to_launch_shapes_and_replayed(tmp_path
     loaded.manager.check_invariants()
     padded = [k for k in step._graphs if k and k[0] == "padded prompt"]
     assert len(padded) >= 2 and step.kernel_steps_graphed > steps // 3, (len(padded), step.kernel_steps_graphed, steps)
+
+
+@pytest.mark.parametrize("name,dtype,tol,seed", [("A", "float32", 4e-4, 1), ("B", "bfloat16", 8e-2, 2),
+                                                  ("C", "float32", 4e-4, 0), ("D", "bfloat16", 8e-2, 1),
+                                                  ("D", "float32", 4e-4, 3)])
+def test_random_steps_under_random_cache_shapes(tmp_path, name, dtype, tol, seed):
+    """Page size, live requests, token budget, context limit, pool size and graphs drawn at random; then steps
+    drawn at random: each live request is left out, brings a portion of some length or one token, in the
+    scheduler's order (single tokens first) or in any; places wanted at the end, nowhere or anywhere; requests
+    end early; a refused step (no pages) must leave everything as it was, and the request that holds most then
+    gives its pages back. Every wanted row against the plain model."""
+    import random
+    from celeg_b200.cache import OutOfPages
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    folder = write_tiny(tmp_path, name)
+    config, weights = plain_lfm2.load_model_folder(folder)
+    rng = random.Random(seed * 13 + ord(name))
+    page_tokens = rng.choice([4, 8, 16, 64])
+    max_requests = rng.choice([2, 3, 4, 8])
+    budget = rng.choice([32, 64, 128, 256])
+    context = rng.choice([None, 96, 200])
+    longest = min(context or config["max_position_embeddings"], rng.choice([40, 90, 150, 250]))
+    cache_tokens = max((-(-longest // page_tokens) + 1) * page_tokens,
+                       int(max_requests * longest * rng.choice([0.4, 0.7, 1.2])))
+    loaded = load_model(folder, dtype=dtype, max_requests=max_requests, cache_tokens=cache_tokens,
+                        page_tokens=page_tokens, max_batched_tokens=budget, use_graphs=rng.random() < 0.7,
+                        max_context=context)
+    step = loaded.step
+    live, made, total, steps = {}, 0, rng.randint(6, 14), 0      # id -> [tokens, plain logits, at, ends at, decodes from]
+    while live or made < total:
+        while len(live) < max_requests and made < total and rng.random() < 0.7:
+            n = rng.randint(3, longest)
+            sequence = [rng.randrange(config["vocab_size"]) for _ in range(n)]
+            live[f"q{made}"] = [sequence, None, 0, n if rng.random() < 0.7 else rng.randint(2, n), rng.randint(1, n)]
+            made += 1
+        left, chosen = budget, []
+        order = list(live)
+        rng.shuffle(order)
+        for rid in order:
+            _, _, at, ends_at, decodes_from = live[rid]
+            if rng.random() < 0.15 or left <= 0:
+                continue
+            n = 1 if at >= decodes_from or rng.random() < 0.1 else \
+                min(decodes_from - at, rng.choice([2, 3, 5, 8, 17, 33, 64, 128]))
+            n = min(n, ends_at - at, left)
+            if n > 0:
+                left -= n
+                chosen.append((rid, n))
+        if rng.random() < 0.5:
+            chosen.sort(key=lambda c: c[1] != 1)
+        entries, places = [], []
+        for rid, n in chosen:
+            sequence, _, at, _, _ = live[rid]
+            kind = rng.random()
+            wanted = [n - 1] if kind < 0.5 else [] if kind < 0.7 else \
+                sorted(rng.sample(range(n), rng.randint(1, min(n, 3))))
+            entries.append(StepEntry(rid, sequence[at:at + n], wanted))
+            places.extend((rid, at + w) for w in wanted)
+        if not entries:
+            continue
+        try:
+            out = step.run(entries, auto_begin=True)
+        except OutOfPages:
+            loaded.manager.check_invariants()
+            rid = max(live, key=lambda r: live[r][2])
+            if live[rid][2] > 0:
+                step.end(rid)
+            del live[rid]
+            continue
+        logits = out.float().cpu().numpy() if places else np.zeros((0, 1))
+        assert logits.shape[0] == len(places)
+        for row, (rid, place) in enumerate(places):
+            if live[rid][1] is None:
+                live[rid][1] = plain_lfm2.forward(config, weights, live[rid][0])
+            worst = float(np.abs(logits[row] - live[rid][1][place]).max())
+            assert worst < tol, f"step {steps}, request {rid}, place {place}: {worst:.3e}"
+        for entry in entries:
+            live[entry.request_id][2] += len(entry.tokens)
+        for rid in list(live):
+            if live[rid][2] >= live[rid][3]:
+                step.end(rid)
+                del live[rid]
+        steps += 1
+        assert steps < 5000
+    step.raise_on_device_error()
+    loaded.manager.check_invariants()
+    assert loaded.manager.free_slots == max_requests
+    assert all(group.pool.used_pages == 0 for group in loaded.manager.groups)
