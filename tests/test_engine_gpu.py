@@ -1688,3 +1688,61 @@ def test_random_steps_under_random_cache_shapes(tmp_path, name, dtype, tol, seed
     loaded.manager.check_invariants()
     assert loaded.manager.free_slots == max_requests
     assert all(group.pool.used_pages == 0 for group in loaded.manager.groups)
+
+
+@pytest.mark.parametrize("seed", [3, 6, 9, 11, 101, 317])
+def test_random_configurations_and_kernel_options_against_the_plain_model(tmp_path, seed):
+    """Every size of the configuration drawn at random (widths that are odd numbers, 1 to 8 key/value heads with
+    1 to 7 query heads each, head sizes 16 to 128 in steps of 16, any feed-forward width and vocabulary, 2 to 4
+    taps, any order of layers), and the switches of the kernel path too: the logits of a prompt in two portions
+    and of the rest token by token, on both paths, with and without graphs, against the plain model."""
+    import copy
+    import random
+    from celeg_b200 import KernelOptions
+    from celeg_b200.engine.loading import load_model
+    from celeg_b200.engine.step import StepEntry
+    from celeg_b200.weights import write_random_model
+    rng = random.Random(1000 + seed)
+    layers = rng.randint(1, 5)
+    types = [rng.choice(["conv", "full_attention"]) for _ in range(layers)]
+    if "full_attention" not in types:
+        types[rng.randrange(layers)] = "full_attention"
+    kv_heads = rng.choice([1, 2, 3, 4, 5, 8])
+    raw = {"model_type": "lfm2", "vocab_size": rng.randint(50, 3000),
+           "hidden_size": rng.randint(2, 40) * rng.choice([1, 2, 8, 16, 64]),
+           "num_hidden_layers": layers, "num_attention_heads": kv_heads * rng.choice([1, 2, 3, 4, 7]),
+           "num_key_value_heads": kv_heads, "head_dim": rng.choice([16, 32, 48, 64, 80, 96, 112, 128]),
+           "max_position_embeddings": 512, "norm_eps": rng.choice([1e-5, 1e-6, 3e-4]),
+           "conv_L_cache": rng.choice([2, 3, 4]), "rope_theta": rng.choice([1e4, 1e6, 5e5]), "layer_types": types,
+           "tie_word_embeddings": rng.random() < 0.5,
+           "intermediate_size": rng.randint(8, 400) if rng.random() < 0.5 else rng.randint(1, 30) * rng.choice([16, 128]),
+           "conv_bias": False, "bos_token_id": 1, "eos_token_id": 2, "pad_token_id": 0}
+    folder = str(tmp_path / "model")
+    write_random_model(folder, copy.deepcopy(raw), seed, torch.bfloat16)
+    config, weights = plain_lfm2.load_model_folder(folder)
+    n = rng.randint(20, 150)
+    sequence = [rng.randrange(raw["vocab_size"]) for _ in range(n)]
+    cut = rng.randint(2, n - 8)
+    middle = cut + (n - cut) // 2
+    want = plain_lfm2.forward(config, weights, sequence)
+    scale = max(1.0, float(np.abs(want).max()))
+    for dtype, tol in (("float32", 6e-4), ("bfloat16", 1e-1)):
+        for graphs in (False, True):
+            options = KernelOptions(tensor_core_products=rng.choice(["none", "swiglu", "all"]),
+                                    tensor_core_min_rows=rng.choice([1, 17, 64, 2048]),
+                                    tensor_core_min_width=rng.choice([1, 1536]),
+                                    tensor_core_variant=rng.choice([-1, -1, 0, 1, 2, 3]),
+                                    split_norms=rng.random() < 0.5, fuse_decode_qk=rng.random() < 0.5,
+                                    tcgen05_attention=rng.random() < 0.5, prefetch_mb=rng.choice([0.0, 8.0]),
+                                    fuse_small_batches=rng.random() < 0.5)
+            loaded = load_model(folder, dtype=dtype, max_requests=2, cache_tokens=512, page_tokens=rng.choice([16, 64]),
+                                max_batched_tokens=256, use_graphs=graphs, kernel_options=options)
+            step = loaded.step
+            rows = [step.run([StepEntry("a", sequence[:cut], list(range(cut)))], auto_begin=True).float().cpu().numpy()]
+            rows.append(step.run([StepEntry("a", sequence[cut:middle], list(range(middle - cut)))]).float().cpu().numpy())
+            for token in sequence[middle:]:
+                rows.append(step.run([StepEntry("a", [token], [0])]).float().cpu().numpy().copy())
+            step.raise_on_device_error()
+            worst = np.abs(np.concatenate(rows, axis=0) - want).max(axis=1)
+            assert worst.max() < tol * scale, (raw, options, dtype, graphs, int(worst.argmax()), float(worst.max()))
+            del loaded, step
