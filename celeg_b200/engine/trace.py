@@ -49,7 +49,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[
         record = json.loads(line)
         number = record["step"]
         entries = [StepEntry(request_id=item["id"], tokens=item["tokens"], want=item.get("want", []))
-                   for item in record.get("entries", [])]
+                   for item in record.get("entries", []) if len(item["tokens"]) > 0]      # (no tokens: left out)
         if entries:
             pieces = []
             for part in _within_limit(entries, batch_limit, StepEntry):
@@ -64,7 +64,8 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[
                 torch.cuda.current_stream().synchronize()
             step_fn.raise_on_device_error()
         for request_id in record.get("end", []):
-            step_fn.end(request_id)
+            if loaded.manager.find(request_id) is not None:      # (a request that never brought a token holds nothing)
+                step_fn.end(request_id)
         done.write(f"done {number}\n")
         done.flush()
     return 0

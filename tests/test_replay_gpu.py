@@ -248,3 +248,24 @@ def test_many_requests_decoding_together(models, name, requests, dtype, tmp_path
     for j in range(4):
         compare(read_logits(out_dir, prompt_steps + j, vocab),
                 np.stack([full[i][lengths[i] + j] for i in range(requests)]), dtype, f"{name} decode step {j}")
+
+
+def test_entries_without_tokens_and_ends_of_requests_that_hold_nothing(models, tmp_path):
+    """An entry without tokens is a request left out of the step; ending a request that never brought a token,
+    or that was ended before, gives nothing back and is no error; an id may come again after its end."""
+    folder, config, weights = models["A"]
+    vocab = config["vocab_size"]
+    first, second = sequences(vocab, [21, 9], seed=33)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": first[:20], "want": [19]}, {"id": "b", "tokens": [], "want": []}],
+         "end": ["b", "never"]},
+        {"step": 1, "entries": [{"id": "a", "tokens": first[20:], "want": [0]}], "end": ["a"]},
+        {"step": 2, "entries": [], "end": ["a"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": second, "want": [8]}], "end": ["a"]},
+    ]
+    out = run_trace(folder, "float32", steps, 64, tmp_path, "lenient")
+    want = plain_lfm2.forward(config, weights, first)
+    compare(read_logits(out, 0, vocab), want[19:20], "float32", "step 0")
+    compare(read_logits(out, 1, vocab), want[20:21], "float32", "step 1")
+    assert not os.path.exists(os.path.join(out, "2.f32"))
+    compare(read_logits(out, 3, vocab), plain_lfm2.forward(config, weights, second)[8:9], "float32", "step 3")
