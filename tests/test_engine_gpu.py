@@ -1693,7 +1693,7 @@ def test_random_steps_under_random_cache_shapes(tmp_path, name, dtype, tol, seed
 @pytest.mark.parametrize("seed", [3, 6, 9, 11, 101, 317])
 def test_random_configurations_and_kernel_options_against_the_plain_model(tmp_path, seed):
     """Every size of the configuration drawn at random (widths that are odd numbers, 1 to 8 key/value heads with
-    1 to 7 query heads each, head sizes 16 to 128 in steps of 16, any feed-forward width and vocabulary, 2 to 4
+    1 to 7 query heads each, head sizes 16 to 128 in steps of 16 and others up to 320, any feed-forward width and vocabulary, 2 to 4
     taps, any order of layers), and the switches of the kernel path too: the logits of a prompt in two portions
     and of the rest token by token, on both paths, with and without graphs, against the plain model."""
     import copy
@@ -1711,7 +1711,7 @@ def test_random_configurations_and_kernel_options_against_the_plain_model(tmp_pa
     raw = {"model_type": "lfm2", "vocab_size": rng.randint(50, 3000),
            "hidden_size": rng.randint(2, 40) * rng.choice([1, 2, 8, 16, 64]),
            "num_hidden_layers": layers, "num_attention_heads": kv_heads * rng.choice([1, 2, 3, 4, 7]),
-           "num_key_value_heads": kv_heads, "head_dim": rng.choice([16, 32, 48, 64, 80, 96, 112, 128]),
+           "num_key_value_heads": kv_heads, "head_dim": rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 24, 40, 200, 320]),
            "max_position_embeddings": 512, "norm_eps": rng.choice([1e-5, 1e-6, 3e-4]),
            "conv_L_cache": rng.choice([2, 3, 4]), "rope_theta": rng.choice([1e4, 1e6, 5e5]), "layer_types": types,
            "tie_word_embeddings": rng.random() < 0.5,
