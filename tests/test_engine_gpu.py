@@ -1693,9 +1693,10 @@ def test_random_steps_under_random_cache_shapes(tmp_path, name, dtype, tol, seed
 @pytest.mark.parametrize("seed", [3, 6, 9, 11, 101, 317])
 def test_random_configurations_and_kernel_options_against_the_plain_model(tmp_path, seed):
     """Every size of the configuration drawn at random (widths that are odd numbers, 1 to 8 key/value heads with
-    1 to 7 query heads each, head sizes 16 to 128 in steps of 16 and others up to 320, any feed-forward width and vocabulary, 2 to 4
-    taps, any order of layers), and the switches of the kernel path too: the logits of a prompt in two portions
-    and of the rest token by token, on both paths, with and without graphs, against the plain model."""
+    1 to 7 query heads each, head sizes 16 to 128 in steps of 16 and others up to 320, any feed-forward width
+    and vocabulary, 2 to 4 taps, any order of layers), and the switches of the kernel path too: the logits of a
+    prompt in two portions and of the rest token by token, on both paths, with and without graphs, against the
+    plain model."""
     import copy
     import random
     from celeg_b200 import KernelOptions
