@@ -49,24 +49,48 @@ class StateBinding:
     owner: bool = True
 
 
+# Blocks of the decode attention that a B200 holds at a time (148 SMs x 5): what the times of its launches at
+# 1 to 256 requests and 2 k to 130 k keys fit (see decode_split).
+DECODE_RESIDENT_BLOCKS = 740
+
+
 def decode_split(tokens: int, kv_heads: int, context_bucket: int, window: Optional[int], max_context: int):
     """How the decode attention splits the keys of a step of ``tokens`` requests: (chunk, max_splits,
     cap_splits). Every request's keys are cut into chunks of ``chunk`` (a multiple of 64); ``max_splits`` chunks
     cover the step's context bucket and ``cap_splits`` >= max_splits is what the scratch is sized for, a
     number that depends only on the longest context the runtime allows.
 
-    Few requests: enough splits for about one and a half blocks per SM. Many requests or long contexts:
-    chunks of 1,024 keys, which measured best on B200 from 4 k to 32 k keys at 1 to 64 requests (blocks of
-    4,096 keys leave a tail of idle SMs, blocks of 256 pay their start and their merge too often)."""
+    Few requests with short contexts: enough splits for about one and a half blocks per SM, chunks of at most
+    1,024 keys. Where that limit binds (many requests or long contexts) the chunk may be 2,048 or 4,096 keys:
+    fewer blocks start and fewer partial results are merged, as long as the blocks still fill the GPU as evenly.
+    The launch's blocks (requests x kv heads x splits) run in rounds of ``DECODE_RESIDENT_BLOCKS``; a count just
+    above a whole number of rounds leaves most SMs idle in the last one (1,024 blocks: 1.4 rounds, the slowest
+    choice wherever it was measured), a count below one round is bound by the bytes alone. The largest chunk
+    within a twentieth of the most even choice is taken. Measured on B200, 32 query heads on 8 kv heads of 64,
+    microseconds a layer at chunks of 1,024 / 2,048 / 4,096 keys: 64 requests at 8 k keys 173 / 168 / 196, 16 at
+    32 k 179 / 171 / 194, 8 at 65 k 188 / 175 / 200, 32 at 65 k 654 / 636 / 631, 8 at 130 k 360 / 337 / 326, 1 at
+    130 k 86 / 68 / 70, 4 at 65 k 107 / 111 / 100."""
     bucket = context_bucket
     if window:
         bucket = min(bucket, 1 << max(8, (window - 1).bit_length()))
     longest = max_context if not window else min(max_context, 2 * window)
     cap_splits = max(32, -(-longest // 1024) * 2)
     blocks_wanted = 224
-    splits = max(1, min(bucket // 128, -(-blocks_wanted // max(1, tokens * kv_heads)), cap_splits))
+    items = max(1, tokens * kv_heads)
+    splits = max(1, min(bucket // 128, -(-blocks_wanted // items), cap_splits))
     chunk = min(-(-bucket // splits), 1024)
     chunk = (chunk + 63) // 64 * 64
+    if chunk == 1024:
+        def evenness(candidate: int) -> float:
+            blocks = items * -(-bucket // candidate)
+            if blocks < DECODE_RESIDENT_BLOCKS:
+                return 1.0 if blocks >= blocks_wanted else 0.0
+            rounds = -(-blocks // DECODE_RESIDENT_BLOCKS)
+            return blocks / (rounds * DECODE_RESIDENT_BLOCKS)
+        candidates = [c for c in (1024, 2048, 4096) if c <= bucket]
+        if candidates:
+            best = max(evenness(c) for c in candidates)
+            chunk = max(c for c in candidates if evenness(c) >= best - 0.05)
     max_splits = -(-bucket // chunk)
     if max_splits > cap_splits:             # a bucket beyond the longest context: cannot come from a valid step
         raise ValueError(f"a context bucket of {context_bucket} keys needs {max_splits} splits, the scratch holds "
