@@ -61,15 +61,16 @@ def decode_split(tokens: int, kv_heads: int, context_bucket: int, window: Option
     number that depends only on the longest context the runtime allows.
 
     Few requests with short contexts: enough splits for about one and a half blocks per SM, chunks of at most
-    1,024 keys. Where that limit binds (many requests or long contexts) the chunk may be 2,048 or 4,096 keys:
-    fewer blocks start and fewer partial results are merged, as long as the blocks still fill the GPU as evenly.
-    The launch's blocks (requests x kv heads x splits) run in rounds of ``DECODE_RESIDENT_BLOCKS``; a count just
-    above a whole number of rounds leaves most SMs idle in the last one (1,024 blocks: 1.4 rounds, the slowest
-    choice wherever it was measured), a count below one round is bound by the bytes alone. The largest chunk
-    within a twentieth of the most even choice is taken. Measured on B200, 32 query heads on 8 kv heads of 64,
-    microseconds a layer at chunks of 1,024 / 2,048 / 4,096 keys: 64 requests at 8 k keys 173 / 168 / 196, 16 at
-    32 k 179 / 171 / 194, 8 at 65 k 188 / 175 / 200, 32 at 65 k 654 / 636 / 631, 8 at 130 k 360 / 337 / 326, 1 at
-    130 k 86 / 68 / 70, 4 at 65 k 107 / 111 / 100."""
+    1,024 keys. Where that limit binds (many requests or long contexts) the chunk grows up to 4,096 keys: fewer
+    blocks start and fewer partial results are merged. The launch's blocks (requests x kv heads x splits) run
+    in rounds of ``DECODE_RESIDENT_BLOCKS``. If one round can hold them, about half a round is asked for: the
+    times fall off sharply just above a whole round (2 requests at 65 k keys: 60 us with 720 blocks, 75 us with
+    816) and are flat or a little better towards half of one (1 request at 130 k: 70 us with 712 blocks, 63 us
+    with 368; at 65 k 41 us with 360 to 408). Otherwise, of 1,024 / 2,048 / 4,096 keys the largest chunk within a
+    twentieth of the most even filling of the rounds is taken (a count like 1,024 blocks, 1.4 rounds, was the
+    slowest choice wherever it was measured). Measured on B200, 32 query heads on 8 kv heads of 64, microseconds
+    a layer at chunks of 1,024 / 2,048 / 4,096 keys: 64 requests at 8 k keys 173 / 168 / 196, 16 at 32 k
+    179 / 171 / 194, 8 at 65 k 188 / 175 / 200, 32 at 65 k 654 / 636 / 631, 8 at 130 k 360 / 337 / 326."""
     bucket = context_bucket
     if window:
         bucket = min(bucket, 1 << max(8, (window - 1).bit_length()))
@@ -81,14 +82,16 @@ def decode_split(tokens: int, kv_heads: int, context_bucket: int, window: Option
     chunk = min(-(-bucket // splits), 1024)
     chunk = (chunk + 63) // 64 * 64
     if chunk == 1024:
-        def evenness(candidate: int) -> float:
-            blocks = items * -(-bucket // candidate)
-            if blocks < DECODE_RESIDENT_BLOCKS:
-                return 1.0 if blocks >= blocks_wanted else 0.0
-            rounds = -(-blocks // DECODE_RESIDENT_BLOCKS)
-            return blocks / (rounds * DECODE_RESIDENT_BLOCKS)
-        candidates = [c for c in (1024, 2048, 4096) if c <= bucket]
-        if candidates:
+        if items * -(-bucket // 4096) < DECODE_RESIDENT_BLOCKS:
+            # one round holds the launch: about half a round of blocks, in chunks of 1,024 to 4,096 keys
+            splits = max(1, DECODE_RESIDENT_BLOCKS // 2 // items)
+            chunk = min(max((-(-bucket // splits) + 63) // 64 * 64, 1024), 4096)
+        else:
+            def evenness(candidate: int) -> float:
+                blocks = items * -(-bucket // candidate)
+                rounds = -(-blocks // DECODE_RESIDENT_BLOCKS)
+                return blocks / (rounds * DECODE_RESIDENT_BLOCKS)
+            candidates = (1024, 2048, 4096)
             best = max(evenness(c) for c in candidates)
             chunk = max(c for c in candidates if evenness(c) >= best - 0.05)
     max_splits = -(-bucket // chunk)
