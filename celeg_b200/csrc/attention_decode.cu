@@ -167,6 +167,32 @@ static int attention_decode_checked(const void* q, int q_row_stride, void* out, 
     return launch_decode<256, 32>(p, grid, stream);
 }
 
+template <int D_PAD, int BN>
+static int resident_blocks_of() {
+    constexpr size_t smem = decode_item_bytes<D_PAD, BN>();
+    if (smem > 40 * 1024 &&
+        cudaFuncSetAttribute(attention_decode_kernel<D_PAD, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<D_PAD, BN>, kDecodeThreads, smem) !=
+        cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return per_sm * device_sms();
+}
+
+// How many blocks of the one-stage form (the form of launches with many blocks) the device holds at a time for
+// this head size; the host lays its splits of the keys out against this number. 0 if it cannot be asked.
+CELEG_API int celeg_attention_decode_resident_blocks(int head_dim) {
+    if (head_dim <= 64) return resident_blocks_of<64, 32>();
+    if (head_dim <= 128) return resident_blocks_of<128, 32>();
+    return resident_blocks_of<256, 32>();
+}
+
 // `counters` must be zero before the first launch; every launch leaves them zero.
 CELEG_API int celeg_attention_decode(const void* q, int q_row_stride, void* out, const void* k_cache,
                                      const void* v_cache, long long page_stride, const int* positions,

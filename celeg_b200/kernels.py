@@ -55,6 +55,7 @@ _SIGNATURES = {
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
                                      c_void_p],
     "celeg_attention_decode_solo_items": [c_longlong],
+    "celeg_attention_decode_resident_blocks": [c_int],
     "celeg_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                 c_void_p, c_void_p],
@@ -229,6 +230,11 @@ def attention_decode_supported(q_heads: int, kv_heads: int, head_dim: int, dtype
     """Shapes the split-key decode kernel takes; everything else goes to the general kernel."""
     return (dtype == torch.bfloat16 and q_heads % kv_heads == 0 and q_heads // kv_heads <= 16
             and head_dim % 8 == 0 and head_dim <= 256)
+
+
+def attention_decode_resident_blocks(head_dim: int) -> int:
+    """Blocks of the decode attention (its one-stage form) that the current device holds at a time; 0 if unknown."""
+    return max(0, int(library().celeg_attention_decode_resident_blocks(int(head_dim))))
 
 
 def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_cache: torch.Tensor,

@@ -49,12 +49,14 @@ class StateBinding:
     owner: bool = True
 
 
-# Blocks of the decode attention that a B200 holds at a time (148 SMs x 5): what the times of its launches at
-# 1 to 256 requests and 2 k to 130 k keys fit (see decode_split).
+# Blocks of the decode attention that a B200 holds at a time at a head size of 64 (148 SMs x 5): what the times
+# of its launches at 1 to 256 requests and 2 k to 130 k keys fit (see decode_split). A mixer asks the kernel
+# library for the number of its own head size on its own device.
 DECODE_RESIDENT_BLOCKS = 740
 
 
-def decode_split(tokens: int, kv_heads: int, context_bucket: int, window: Optional[int], max_context: int):
+def decode_split(tokens: int, kv_heads: int, context_bucket: int, window: Optional[int], max_context: int,
+                 resident_blocks: int = DECODE_RESIDENT_BLOCKS):
     """How the decode attention splits the keys of a step of ``tokens`` requests: (chunk, max_splits,
     cap_splits). Every request's keys are cut into chunks of ``chunk`` (a multiple of 64); ``max_splits`` chunks
     cover the step's context bucket and ``cap_splits`` >= max_splits is what the scratch is sized for, a
@@ -63,7 +65,7 @@ def decode_split(tokens: int, kv_heads: int, context_bucket: int, window: Option
     Few requests with short contexts: enough splits for about one and a half blocks per SM, chunks of at most
     1,024 keys. Where that limit binds (many requests or long contexts) the chunk grows up to 4,096 keys: fewer
     blocks start and fewer partial results are merged. The launch's blocks (requests x kv heads x splits) run
-    in rounds of ``DECODE_RESIDENT_BLOCKS``. If one round can hold them, about half a round is asked for: the
+    in rounds of ``resident_blocks``. If one round can hold them, about half a round is asked for: the
     times fall off sharply just above a whole round (2 requests at 65 k keys: 60 us with 720 blocks, 75 us with
     816) and are flat or a little better towards half of one (1 request at 130 k: 70 us with 712 blocks, 63 us
     with 368; at 65 k 41 us with 360 to 408). Otherwise, of 1,024 / 2,048 / 4,096 keys the largest chunk within a
@@ -82,15 +84,15 @@ def decode_split(tokens: int, kv_heads: int, context_bucket: int, window: Option
     chunk = min(-(-bucket // splits), 1024)
     chunk = (chunk + 63) // 64 * 64
     if chunk == 1024:
-        if items * -(-bucket // 4096) < DECODE_RESIDENT_BLOCKS:
+        if items * -(-bucket // 4096) < resident_blocks:
             # one round holds the launch: about half a round of blocks, in chunks of 1,024 to 4,096 keys
-            splits = max(1, DECODE_RESIDENT_BLOCKS // 2 // items)
+            splits = max(1, resident_blocks // 2 // items)
             chunk = min(max((-(-bucket // splits) + 63) // 64 * 64, 1024), 4096)
         else:
             def evenness(candidate: int) -> float:
                 blocks = items * -(-bucket // candidate)
-                rounds = -(-blocks // DECODE_RESIDENT_BLOCKS)
-                return blocks / (rounds * DECODE_RESIDENT_BLOCKS)
+                rounds = -(-blocks // resident_blocks)
+                return blocks / (rounds * resident_blocks)
             candidates = (1024, 2048, 4096)
             best = max(evenness(c) for c in candidates)
             chunk = max(c for c in candidates if evenness(c) >= best - 0.05)
@@ -136,6 +138,7 @@ class AttentionMixer:
         self.q_norm = rt.vector(weights["q_norm"]) if "q_norm" in weights else None
         self.k_norm = rt.vector(weights["k_norm"]) if "k_norm" in weights else None
         self.binding: Optional[PagedBinding] = None
+        self._resident_blocks: Optional[int] = None      # (asked of the kernel library at the first decode step)
         self.qkv = rt.scratch("attention.qkv", self.qkv_width)
         self.attended = rt.scratch("attention.out", q_width)
         assert kv_width >= 0
@@ -196,8 +199,10 @@ class AttentionMixer:
         """One query token per request: how the keys are split so that few requests still fill the GPU,
         and the scratch of the split (chunk, max_splits, partial outputs, maxima and sums, counters)."""
         rt = self.rt
+        if self._resident_blocks is None:
+            self._resident_blocks = kernels.attention_decode_resident_blocks(self.head_dim) or DECODE_RESIDENT_BLOCKS
         chunk, max_splits, cap_splits = decode_split(tokens or step.tokens, self.kv_heads, step.context_bucket,
-                                                     self.window, rt.max_context)
+                                                     self.window, rt.max_context, self._resident_blocks)
         rows = rt.max_requests * self.heads * cap_splits
         partial_o = rt.flat_scratch("attention.partial_o", rows * self.head_dim, torch.float32)
         partial_ml = rt.flat_scratch("attention.partial_ml", rows * 2, torch.float32)
