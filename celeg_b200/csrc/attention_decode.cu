@@ -8,8 +8,11 @@ struct BlockSync {
     __device__ __forceinline__ void operator()() const { __syncthreads(); }
 };
 
+// (the forms are laid out for five blocks per SM at head size 64 with one stage, three with two stages or at head
+// size 128: the registers must allow them too)
 template <int D_PAD, int BN>
-__global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kDecodeThreads, (D_PAD == 64 && BN == 32) ? 5 : (D_PAD <= 128 && BN <= 64 && D_PAD * BN <= 4096) ? 3 : 1)
+attention_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     chain_release();
     chain_wait();
@@ -49,6 +52,11 @@ static int launch_decode_solo(const DecodeParams& p, int tokens, cudaStream_t st
 template <int D_PAD, int BN>
 static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t stream) {
     constexpr size_t smem = decode_item_bytes<D_PAD, BN>();
+    // the merge of the splits keeps a maximum and a sum per split (of as many heads as fit) where the K/V tiles were
+    constexpr size_t tiles = (size_t)kDecodeWarps * 2 * BN * D_PAD * sizeof(__nv_bfloat16);
+    CELEG_REQUIRE((size_t)p.max_splits * 2 * sizeof(float) <= tiles,
+                  "attention_decode: the maxima and sums of %d splits do not fit the merge's %zu bytes of shared memory",
+                  p.max_splits, tiles);
     if (smem > 40 * 1024) {       // static shared memory counts against the 48 KiB default as well
         const cudaError_t status = cudaFuncSetAttribute(attention_decode_kernel<D_PAD, BN>,
                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -456,17 +456,20 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     sync();
     if (!is_last) return;
     __threadfence();
-    // (loads in batches of eight, all in flight together: one after the other, each used at once, a merge of
-    // n splits was 2 n round trips to the L2 at the very end of the kernel)
-    for (int item = tid; item < group * d; item += kDecodeThreads) {
-        const int r = item / d, col = item % d;
-        const int h = kvh * group + r;
-        const float* ml = p.partial_ml + ((size_t)t * p.q_heads + h) * p.max_splits * 2;
-        const float* po = p.partial_o + ((size_t)t * p.q_heads + h) * p.max_splits * d + col;
-        float m = -INFINITY;
-        float denom = 0.0f, total_o = 0.0f;
-        if (n_splits <= 8) {
-            // the common case in one round trip: maxima, sums and outputs of all splits together
+    // More than eight splits: the merge in three short phases, so that it costs few round trips to the L2 at the
+    // very end of the kernel whatever their number (a single request with 130 k keys has 37): all maxima and sums of the
+    // group's heads into shared memory in one go; a warp per head turns them into the splits' weights and the
+    // head's sum; then a thread takes two outputs together and the splits' partial outputs in batches of eight.
+    // (One load after the other it was 2 n round trips for n splits; a pass over the maxima before the pass over
+    // the outputs, one output after the other, 4 ceil(n / 8).) The K/V tiles' shared memory holds the weights;
+    // if all heads' do not fit at once the heads are taken in several passes (the launch checks that one head's do).
+    if (n_splits <= 8) {
+        // the common case in one round trip an output: maxima, sums and outputs of all splits together
+        for (int item = tid; item < group * d; item += kDecodeThreads) {
+            const int r = item / d, col = item % d;
+            const int h = kvh * group + r;
+            const float* ml = p.partial_ml + ((size_t)t * p.q_heads + h) * p.max_splits * 2;
+            const float* po = p.partial_o + ((size_t)t * p.q_heads + h) * p.max_splits * d + col;
             float part_m[8], part_l[8], part_o[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -475,6 +478,7 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
                 part_l[j] = have ? __ldcg(ml + 2 * j + 1) : 0.0f;
                 part_o[j] = have ? __ldcg(po + (size_t)j * d) : 0.0f;
             }
+            float m = -INFINITY, denom = 0.0f, total_o = 0.0f;
 #pragma unroll
             for (int j = 0; j < 8; ++j) m = fmaxf(m, part_m[j]);
 #pragma unroll
@@ -486,34 +490,75 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
                 }
             }
             p.out[((size_t)t * p.q_heads + h) * d + col] = __float2bfloat16_rn(total_o / denom);
-            continue;
         }
-        for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
-            float part[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) part[j] = sp0 + j < n_splits ? __ldcg(ml + 2 * (sp0 + j)) : -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) m = fmaxf(m, part[j]);
+        return;
+    }
+    constexpr int kMergeFloats = kDecodeWarps * 2 * BN * D_PAD / 2;      // the K/V tiles, counted in floats
+    const int heads_a_pass = max(1, min(group, kMergeFloats / (2 * n_splits)));
+    for (int r0 = 0; r0 < group; r0 += heads_a_pass) {
+        const int heads = min(heads_a_pass, group - r0);
+        float* merge_w = o_s;                              // [heads][n_splits] maxima, then weights
+        float* merge_l = o_s + (size_t)heads * n_splits;   // [heads][n_splits] sums
+        for (int idx = tid; idx < heads * n_splits; idx += kDecodeThreads) {
+            const int r = r0 + idx / n_splits, j = idx % n_splits;
+            const float* ml = p.partial_ml + (((size_t)t * p.q_heads + kvh * group + r) * p.max_splits + j) * 2;
+            merge_w[idx] = __ldcg(ml);
+            merge_l[idx] = __ldcg(ml + 1);
         }
-        for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
-            float part_m[8], part_l[8], part_o[8];
+        sync();
+        for (int i = warp; i < heads; i += kDecodeWarps) {
+            float* w_r = merge_w + (size_t)i * n_splits;
+            const float* l_r = merge_l + (size_t)i * n_splits;
+            float m = -INFINITY;
+            for (int j = lane; j < n_splits; j += 32) m = fmaxf(m, w_r[j]);
+            m = warp_max(m);
+            float denom = 0.0f;
+            for (int j = lane; j < n_splits; j += 32) {
+                const float w = exp2f(w_r[j] - m);
+                w_r[j] = w;
+                denom += w * l_r[j];
+            }
+            denom = warp_sum(denom);
+            if (lane == 0) head_sum[r0 + i] = denom;
+        }
+        sync();
+        const int outputs = heads * d;
+        for (int base = 0; base < outputs; base += 2 * kDecodeThreads) {
+            const float* po[2];
+            const float* w_r[2];
+            bool live[2];
+            float total_o[2] = {0.0f, 0.0f};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const bool have = sp0 + j < n_splits;
-                part_m[j] = have ? __ldcg(ml + 2 * (sp0 + j)) : -INFINITY;
-                part_l[j] = have ? __ldcg(ml + 2 * (sp0 + j) + 1) : 0.0f;
-                part_o[j] = have ? __ldcg(po + (size_t)(sp0 + j) * d) : 0.0f;
+            for (int u = 0; u < 2; ++u) {
+                const int item = base + tid + u * kDecodeThreads;
+                live[u] = item < outputs;
+                const int i = live[u] ? item / d : 0, col = live[u] ? item % d : 0;
+                po[u] = p.partial_o + ((size_t)t * p.q_heads + kvh * group + r0 + i) * p.max_splits * d + col;
+                w_r[u] = merge_w + (size_t)i * n_splits;
+            }
+            for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
+                float part_o[2][8];
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        part_o[u][j] = live[u] && sp0 + j < n_splits ? __ldcg(po[u] + (size_t)(sp0 + j) * d) : 0.0f;
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)                  // (in the order of the splits)
+                        if (sp0 + j < n_splits) total_o[u] += w_r[u][sp0 + j] * part_o[u][j];
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (sp0 + j < n_splits) {                     // (in the order of the splits, as before)
-                    const float w = exp2f(part_m[j] - m);
-                    denom += w * part_l[j];
-                    total_o += w * part_o[j];
-                }
+            for (int u = 0; u < 2; ++u) {
+                if (!live[u]) continue;
+                const int item = base + tid + u * kDecodeThreads;
+                const int r = r0 + item / d;
+                p.out[((size_t)t * p.q_heads + kvh * group + r) * d + item % d] =
+                    __float2bfloat16_rn(total_o[u] / head_sum[r]);
             }
         }
-        p.out[((size_t)t * p.q_heads + h) * d + col] = __float2bfloat16_rn(total_o / denom);
+        if (r0 + heads_a_pass < group) sync();             // the next pass writes over the weights
     }
 }
 
