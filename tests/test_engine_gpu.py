@@ -152,6 +152,39 @@ def test_a_context_of_thousands_of_tokens(tmp_path, dtype, tol):
     engine.end("short")
 
 
+def test_many_requests_decoding_over_thousands_of_keys(tmp_path):
+    """Forty requests that hold the same 4,100-token prompt (each in pages of its own) decode together: the
+    decode attention then cuts the keys into chunks of 2,048 (long contexts and enough requests to fill the GPU
+    with few splits each) instead of 1,024 and fewer. Four steps, every request's logits against the plain model."""
+    from celeg_b200 import Engine, EngineOptions, StepEntry
+    from celeg_b200.parts.mixers import decode_split
+    from celeg_b200.weights import write_random_model
+    from tiny_models import TINY_D
+    raw = copy.deepcopy(TINY_D)
+    raw["max_position_embeddings"] = 8192
+    folder = str(tmp_path / "many_long")
+    write_random_model(folder, raw, 5, torch.bfloat16)
+    config, weights = plain_lfm2.load_model_folder(folder)
+    (sequence,) = prompts_of(config["vocab_size"], [4104], seed=53)
+    want = plain_lfm2.forward(config, weights, sequence)
+    requests, prompt = 40, 4100
+    assert decode_split(requests, raw["num_key_value_heads"], 8192, None, 8192)[0] == 2048
+    engine = Engine(folder, dtype="bfloat16", max_context=8192, use_cuda_graph=True,
+                    options=EngineOptions(max_active_requests=requests, max_batched_tokens=2048,
+                                          prefill_chunk_tokens=2048))
+    for r in range(requests):
+        for at in range(0, prompt, 2048):
+            engine.forward([StepEntry(f"r{r}", sequence[at:min(at + 2048, prompt)], [])])
+    for step in range(4):
+        out = engine.forward([StepEntry(f"r{r}", [sequence[prompt + step]], [0]) for r in range(requests)])
+        got = out.float().cpu().numpy()
+        worst = np.abs(got - want[prompt + step][None, :]).max(axis=1)
+        assert worst.max() < 8e-2, f"step {step}, request {int(worst.argmax())}: {worst.max():.3e}"
+    engine.loaded.step.raise_on_device_error()
+    for r in range(requests):
+        engine.end(f"r{r}")
+
+
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 6e-2)])
 def test_first_tokens_of_a_sequence(models, dtype, tol):
     """Positions 0..5 one by one: fewer tokens than the conv kernel has taps, one key only."""

@@ -957,3 +957,38 @@ def test_gemm_tcgen05_store_and_swiglu(m, n, k, variant):
     bad = ((act.double() - want).abs() > 2.5e-2 * (1 + want.abs())).sum().item()
     assert bad <= m * n // 2000, ("swiglu", bad)          # a gate on a rounding edge may flip
     assert int(flag.item()) == 0
+
+
+@pytest.mark.parametrize("chunk", [1472, 2880, 4096])
+def test_attention_decode_long_contexts_in_large_chunks(chunk):
+    """Contexts of thousands of keys in the chunks that long contexts get (up to 4,096 keys, any multiple of 64):
+    a context that ends on a chunk's last key, one key into the next chunk, one key in all; more than eight
+    splits for one request and one split for another in the same launch; a far key made to dominate."""
+    from celeg_b200 import kernels
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(41)
+    heads, kv_heads, head_dim, page_tokens = 8, 2, 64, 16
+    lengths = [9 * chunk - 5, chunk, chunk + 1, 1, 3000]
+    pages = sum((n + page_tokens - 1) // page_tokens for n in lengths) + 3
+    k_cache, v_cache, table, ks, vs = paged_setup(rng, dtype, lengths, kv_heads, head_dim, page_tokens, pages)
+    tokens = len(lengths)
+    q = rounded(rng.normal(size=(tokens, heads, head_dim)), dtype)
+    q[0] = rounded(ks[0][chunk + 2, 0][None, :].repeat(heads, 0) * 3.0, dtype)      # a key of the second chunk stands out
+    positions = np.array([n - 1 for n in lengths], dtype=np.int32)
+    token_span = np.arange(tokens, dtype=np.int32)
+    scale = head_dim ** -0.5
+    max_splits = (max(lengths) + chunk - 1) // chunk
+    partial_o = torch.empty(tokens * heads * max_splits * head_dim, dtype=torch.float32, device="cuda")
+    partial_ml = torch.empty(tokens * heads * max_splits * 2, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(tokens * kv_heads, dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    want = np.stack([attention_reference(q[t], ks[t], vs[t], int(positions[t]), scale, None)
+                     for t in range(tokens)]).reshape(tokens, -1)
+    for _ in range(2):
+        out = torch.zeros((tokens, heads * head_dim), dtype=dtype, device="cuda")
+        kernels.attention_decode(dev(q.reshape(tokens, -1), dtype), heads * head_dim, out, k_cache, v_cache,
+                                 dev(positions), dev(token_span), dev(table), tokens, heads, kv_heads, head_dim,
+                                 page_tokens, None, scale, chunk, max_splits, partial_o, partial_ml, counters, flag)
+        assert int(flag.item()) == 0
+        assert int(counters.abs().sum().item()) == 0
+        close(out, want, dtype)
