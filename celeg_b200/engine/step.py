@@ -237,7 +237,10 @@ class StepFunction:
                 self._wide_logits = torch.empty((wanted, vocab), dtype=torch.float32, device=self.rt.device)
             logits = self._wide_logits
 
-        graph_key = (padded, n_logits, _context_bucket(max_ctx)) if (all_decode and self.use_graphs and wanted <= self.max_spans) else prompt_key
+        if all_decode and self.use_graphs and wanted <= self.max_spans:
+            graph_key = (padded, n_logits, _context_bucket(max_ctx))
+        else:
+            graph_key = prompt_key
         if graph_key is not None:
             if tokens_from is not None:
                 graph_key = graph_key + ("tokens on the device", tokens_from.data_ptr())
@@ -364,11 +367,13 @@ class StepFunction:
         padded_tokens = -(-(single_rows + portion_tokens) // PROMPT_TOKEN_STEP) * PROMPT_TOKEN_STEP - single_rows
         spare = padded_tokens - portion_tokens
         spans = single_rows + len(portions) + (1 if spare else 0)
-        logit_rows = max(1, wanted, single_rows + len(portions))       # (a scheduler's step wants one row a span at most)
+        logit_rows = max(1, wanted, single_rows + len(portions))    # (a scheduler's step wants one row a span at most)
+        # (the spare portion lives in the storage's spare pages, and its table row holds max_pages entries)
+        spare_room = min(self.storage.scratch_page_count, self.max_pages) * self.page_tokens
         if (single_rows + padded_tokens > self.buffer_tokens or spans > self.span_capacity
                 or logit_rows > self.span_capacity
                 or single_rows - singles > PADDING_TOKENS - PROMPT_TOKEN_STEP
-                or spare > min(self.storage.scratch_page_count, self.max_pages) * self.page_tokens):     # (a table row holds max_pages)
+                or spare > spare_room):
             return None
         key = ("padded prompt", single_rows, len(portions), padded_tokens, logit_rows, _context_bucket(max_ctx))
         if key not in self._graphs:
